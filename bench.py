@@ -1,0 +1,334 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-matmul hot path on B200.
+
+Headline line (one JSON object on stdout): Q4_K decode GEMV, weight 8192 x 3072,
+batch 1 -- GB/s of algorithmic bytes (GGUF weight bytes + f32 x + f32 y), timed
+on the device over a ring of weight copies larger than L2, with the roofline
+fraction against the measured HBM copy peak, the end-to-end figure through the
+host-buffer launch surface, and the CPU baseline (the oracle's restatement of
+the reference's x86 decode path) timed on this host's cores.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--extras]
+
+Under torchrun (N > 1) every rank runs the same per-GPU workload on its own GPU
+(weak scaling: the ranks are the row shards of an N-times taller matrix; a
+column-split projection needs no collective) and rank 0 prints the line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS, KIND_NAME, KIND = 8192, 3072, "q4_k", 12
+RING = 40  # weight copies cycled through: 40 x 14.16 MB = 566 MB, 4.5x the 126 MB L2
+ALGO_BYTES = ROWS * (COLS // 256) * 144 + COLS * 4 + ROWS * 4  # 14 200 832
+WORKLOAD = f"C1: Q4_K decode GEMV, weight {ROWS}x{COLS}, batch 1"
+
+
+def load_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows, self.proc, self.idx = [], None, gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+                for n, v in zip(names, r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            except Exception:
+                pass
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def synth(seed_w=0x5EED0000, seed_x=0xAC7):
+    """Seeded synthetic inputs of the workload: W ~ N(0, 0.02^2) quantized by the
+    reference's Q4_K encoder (oracle restatement), x ~ N(0, 1)."""
+    from oracle import frink_oracle as fo
+    w = (np.random.default_rng(seed_w).standard_normal((ROWS, COLS), dtype=np.float32) * np.float32(0.02))
+    x = np.random.default_rng(seed_x).standard_normal(COLS, dtype=np.float32)
+    return fo.encode(KIND, w), x
+
+
+def cpu_gemv_rate(raw, x, seconds, threads):
+    """GB/s of the oracle's x86 decode path (AVX2 fused f32 dot, rows over threads)."""
+    from oracle import frink_oracle as fo
+    ring = [raw.copy() for _ in range(8)]  # 113 MB: past the host's last-level cache
+    fo.matvec_f32(KIND, ring[0], ROWS, COLS, x, threads=threads, simd=True)
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        fo.matvec_f32(KIND, ring[n % len(ring)], ROWS, COLS, x, threads=threads, simd=True)
+        n += 1
+    dt = time.perf_counter() - t0
+    return ALGO_BYTES * n / dt / 1e9, n, dt
+
+
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return "unknown"
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's CPU implementation of the path (oracle
+    port; the reference is Rust and there is no Rust toolchain to build it with)
+    on all host threads.  A step is one full C1 GEMV."""
+    if rank != 0:
+        return
+    from oracle import frink_oracle as fo
+    raw, x = synth()
+    threads = fo.host_threads()
+    ring = [raw.copy() for _ in range(8)]
+    for i in range(args.warmup):
+        fo.matvec_f32(KIND, ring[i % 8], ROWS, COLS, x, threads=threads, simd=True)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        fo.matvec_f32(KIND, ring[i % 8], ROWS, COLS, x, threads=threads, simd=True)
+    dt = time.perf_counter() - t0
+    v = ALGO_BYTES * args.steps / dt / 1e9
+    print(json.dumps({
+        "impl": "reference", "metric": "q4_k_gemv_gbs", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 (fused dequant dot)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "arm": "frink CPU decode path (AVX2 fused f32 dot), C++ restatement"},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} full GEMVs over 8 weight copies; {cpu_model()}"},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def graph_of(n, launch):
+    import torch
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(n):
+            launch(i)
+    return g
+
+
+def timed_launches(steps, ring, launch, warmup):
+    """Device time of exactly `steps` launches (CUDA graph replays of `ring`
+    launches each, plus one graph with the remainder), CUDA events on the
+    replaying stream."""
+    import torch
+    q, r = divmod(steps, ring)
+    g_full = graph_of(ring, launch) if q else None
+    g_rem = graph_of(r, launch) if r else None
+    for _ in range(max(1, -(-warmup // ring))):
+        (g_full or g_rem).replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(q):
+        g_full.replay()
+    if g_rem:
+        g_rem.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4000)
+    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "no CUDA device: this benchmark has no CPU fallback"}))
+        sys.exit(1)
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from frink_b200 import device, gpu, build
+    build.build()
+
+    raw, x = synth()
+    raw_d = torch.from_numpy(raw).cuda()
+    ws = [device.Weights(raw_d, KIND, ROWS, COLS) for _ in range(RING)]
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.empty((1, ROWS), dtype=torch.float32, device="cuda")
+
+    def launch(i):
+        device.gemv(ws[i % RING], xd, out=yd)
+
+    for i in range(max(3, min(args.warmup, RING))):
+        launch(i)
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    device.counters(reset=True)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    barrier()
+    ms = timed_launches(args.steps, RING, launch, args.warmup)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    launches = args.steps  # one kernel of this library per step (graph replays are not seen by the host counter)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * ALGO_BYTES * args.steps / (ms * 1e-3) / 1e9
+    per_gpu = value / world
+
+    # ---- end to end: the host-buffer launch surface frink-core binds, pinned
+    # host buffers, x up and y down inside the timed region, weights resident
+    x_pin = torch.from_numpy(x).pin_memory()
+    raws = [raw.copy() for _ in range(RING)]
+    nb = COLS // 256
+    e2e_steps = max(50, min(args.steps, 1000))
+    for i in range(RING):
+        y_host = gpu.launch_q4_k_matvec(raws[i], x_pin.numpy(), ROWS, nb * 144, nb)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        y_host = gpu.launch_q4_k_matvec(raws[i % RING], x_pin.numpy(), ROWS, nb * 144, nb)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = world * ALGO_BYTES * e2e_steps / e2e_s / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, which = load_peaks()
+    from oracle import frink_oracle as fo
+    threads = fo.host_threads()
+    cpu_v, cpu_n, cpu_dt = cpu_gemv_rate(raw, x, args.cpu_seconds if world == 1 else 2.0, threads)
+    # parity spot check of what was timed (not part of any timed region)
+    want = fo.matmul_f64(KIND, raw, ROWS, COLS, fo.q8_1_round(x))[0]
+    got = yd.cpu().numpy()[0]
+    rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    rel_e2e = float(np.linalg.norm(y_host - want) / np.linalg.norm(want))
+
+    line = {
+        "metric": "q4_k_gemv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8 x int4 dp4a, f32 accumulate", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "l2": f"inputs larger than L2: ring of {RING} weight copies, {RING * ALGO_BYTES / 1e6:.0f} MB",
+                   "timing": "CUDA events around CUDA-graph replays of the launches", "algorithmic_bytes_per_step": ALGO_BYTES},
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
+                     "traffic": None, "peak_source": f"{which} HBM copy bandwidth", "frac_of_8TBs_nominal": per_gpu / 8000.0},
+        "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{cpu_n} full C1 GEMVs in {cpu_dt:.1f} s, AVX2 fused f32 dot, rows over threads; {cpu_model()}"},
+        "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4, "d2h_bytes_per_step": ROWS * 4,
+                "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
+                "api": "gpu.launch_q4_k_matvec(host weights, host x) -> host y, weights resident"},
+        "gpu_launches": launches, "clocks": clocks,
+        "parity": {"rel_l2_device": rel, "rel_l2_e2e": rel_e2e, "bar": 1e-3},
+    }
+    if args.extras and world == 1:
+        line["extras"] = extras(peak)
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extras(peak):
+    """Other kinds, batch sizes and a matrix large enough to amortise the launch."""
+    import torch
+    from frink_b200 import device
+    from oracle import frink_oracle as fo
+    out = []
+    rng = np.random.default_rng(1)
+    cases = [("q4_k", 12, 8192, 3072, 1), ("q4_k", 12, 8192, 3072, 8), ("q6_k", 14, 8192, 3072, 1), ("q8_0", 8, 8192, 3072, 1),
+             ("mxfp4", 39, 8192, 2880, 1), ("q4_k", 12, 3072, 8192, 1), ("q6_k", 14, 128256, 3072, 1), ("q4_k", 12, 65536, 8192, 1)]
+    for name, kind, rows, cols, batch in cases:
+        small = rows * cols <= 8192 * 8192
+        base = fo.encode(kind, (rng.standard_normal((min(rows, 1024), cols), dtype=np.float32) * np.float32(0.02)))
+        raw = np.tile(base, -(-rows // min(rows, 1024)))[: rows * fo.row_bytes(kind, cols)]
+        raw_d = torch.from_numpy(raw).cuda()
+        ring = max(2, int(600e6 // raw.size) + 1) if small else 2
+        ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
+        xd = torch.from_numpy(rng.standard_normal((batch, cols), dtype=np.float32)).cuda()
+        yd = torch.empty((batch, rows), dtype=torch.float32, device="cuda")
+        steps = 2000 if small else 100
+
+        def launch(i):
+            device.gemv(ws[i % ring], xd, out=yd)
+        for i in range(3):
+            launch(i)
+        ms = timed_launches(steps, ring, launch, 20)
+        nbytes = raw.size + batch * cols * 4 + batch * rows * 4
+        gbs = nbytes * steps / (ms * 1e-3) / 1e9
+        out.append({"kind": name, "rows": rows, "cols": cols, "batch": batch, "us": ms / steps * 1e3, "GBs": gbs, "frac": gbs / peak})
+        for w in ws:
+            w.release()
+    return out
+
+
+if __name__ == "__main__":
+    main()

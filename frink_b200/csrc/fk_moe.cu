@@ -1,0 +1,230 @@
+// MoE plumbing around the expert matmuls: router logits, top-k routing, the
+// token permutation that makes each expert's rows contiguous, the gated
+// activation between the two expert matmuls, and the weighted combine.
+#include "fk_common.cuh"
+
+namespace {
+
+constexpr int TOPK_PER_LANE = 8;  // n_experts <= 256
+constexpr int TOPK_MAX_K = 16;
+
+// One warp per token.  Selection is by (biased) logit, ties to the lower
+// expert id; weights by `mode` (0 softmax over all, 1 renormalised over the
+// chosen, 2 softmax over the chosen only), written in selection order.
+__global__ void route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n_experts, int k,
+                             int mode, int batch, int* __restrict__ ids_out, float* __restrict__ w_out) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= batch) return;
+    const float NEG_INF = __int_as_float(0xff800000);
+    const float* lg = logits + (size_t)t * n_experts;
+    float v[TOPK_PER_LANE];
+#pragma unroll
+    for (int j = 0; j < TOPK_PER_LANE; j++) {
+        const int e = lane + 32 * j;
+        v[j] = e < n_experts ? lg[e] + (bias ? bias[e] : 0.0f) : NEG_INF;
+    }
+    float mx = NEG_INF;
+#pragma unroll
+    for (int j = 0; j < TOPK_PER_LANE; j++) mx = fmaxf(mx, v[j]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < TOPK_PER_LANE; j++)
+        if (lane + 32 * j < n_experts) sum += expf(v[j] - mx);
+    sum = fk_warp_sum(sum);
+
+    float cv[TOPK_MAX_K];
+    int ci[TOPK_MAX_K];
+#pragma unroll 1
+    for (int s = 0; s < k; s++) {
+        float bv = NEG_INF;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < TOPK_PER_LANE; j++) {
+            const int e = lane + 32 * j;
+            if (e < n_experts && (v[j] > bv || (v[j] == bv && e < bi))) { bv = v[j]; bi = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        cv[s] = bv;
+        ci[s] = bi;
+#pragma unroll
+        for (int j = 0; j < TOPK_PER_LANE; j++)
+            if (lane + 32 * j == bi) v[j] = NEG_INF;
+    }
+    if (lane != 0) return;
+    int* ids = ids_out + (size_t)t * k;
+    float* w = w_out + (size_t)t * k;
+    if (mode == 2) {
+        float es = 0.0f;
+        for (int s = 0; s < k; s++) es += expf(cv[s] - cv[0]);
+        for (int s = 0; s < k; s++) {
+            const float e = expf(cv[s] - cv[0]);
+            w[s] = es > 0.0f ? e / es : e;
+            ids[s] = ci[s];
+        }
+        return;
+    }
+    float ts = 0.0f;
+    for (int s = 0; s < k; s++) {
+        const float p = expf(cv[s] - mx) / sum;
+        w[s] = p;
+        ts += p;
+        ids[s] = ci[s];
+    }
+    if (mode == 1)
+        for (int s = 0; s < k; s++) w[s] = w[s] / ts;
+}
+
+// logits[t][e] = router[e] . x[t], one warp per (e, t); f32 throughout.
+__global__ void router_logits_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ out,
+                                     int rows, int cols) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const float* wr = w + (size_t)row * cols;
+    const float* xt = x + (size_t)blockIdx.y * cols;
+    float acc = 0.0f;
+    for (int i = lane; i < cols; i += 32) acc += wr[i] * xt[i];
+    acc = fk_warp_sum(acc);
+    if (lane == 0) out[(size_t)blockIdx.y * rows + row] = acc;
+}
+
+// Stable counting sort of the (token, slot) pairs by expert, in one block.
+// Warp `e mod nwarps` owns expert e: it scans the pair list 32 at a time and
+// places matches with a ballot, so pairs keep ascending order inside a group
+// and the result is the same on every run.
+__global__ void permute_kernel(const int* __restrict__ ids, int pairs, int k, int n_experts, int* __restrict__ group_off,
+                               int* __restrict__ gather, int* __restrict__ pair_of) {
+    extern __shared__ int counts[];  // [n_experts + 1]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int e = warp; e < n_experts; e += nwarps) {
+        int c = 0;
+        for (int p0 = 0; p0 < pairs; p0 += 32) {
+            const int p = p0 + lane;
+            c += __popc(__ballot_sync(0xffffffffu, p < pairs && ids[p] == e));
+        }
+        if (lane == 0) counts[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < n_experts; e++) {
+            const int c = counts[e];
+            counts[e] = acc;
+            group_off[e] = acc;
+            acc += c;
+        }
+        counts[n_experts] = acc;
+        group_off[n_experts] = acc;
+    }
+    __syncthreads();
+    for (int e = warp; e < n_experts; e += nwarps) {
+        int base = counts[e];
+        for (int p0 = 0; p0 < pairs; p0 += 32) {
+            const int p = p0 + lane;
+            const bool hit = p < pairs && ids[p] == e;
+            const unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                const int pos = base + __popc(m & ((1u << lane) - 1u));
+                gather[pos] = p / k;
+                pair_of[p] = pos;
+            }
+            base += __popc(m);
+        }
+    }
+}
+
+__global__ void glu_kernel(const float* __restrict__ gate, const float* __restrict__ up, size_t n, int act, float* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = gate[i], u = up[i];
+    if (act == 0) {
+        out[i] = (g / (1.0f + expf(-g))) * u;
+    } else {
+        const float x = fminf(g, 7.0f);
+        const float y = fminf(fmaxf(u, -7.0f), 7.0f);
+        out[i] = (x / (1.0f + expf(1.702f * -x))) * (y + 1.0f);
+    }
+}
+
+__global__ void combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_of, const float* __restrict__ w,
+                               int k, int n, float* __restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = blockIdx.y;
+    if (i >= n) return;
+    float acc = 0.0f;
+    for (int j = 0; j < k; j++) {
+        const int p = pair_of ? pair_of[t * k + j] : t * k + j;
+        acc += y[(size_t)p * n + i] * w[t * k + j];
+    }
+    out[(size_t)t * n + i] = acc;
+}
+
+}  // namespace
+
+FK_EXPORT int fk_moe_route(fk_ctx* ctx, void* stream, const float* logits_dev, const float* bias_dev, int n_experts,
+                           int k, int mode, int batch, int* ids_dev, float* w_dev) {
+    if (!ctx || !logits_dev || !ids_dev || !w_dev) return fk_fail(FK_INVALID, "moe_route: null argument");
+    if (n_experts < 1 || n_experts > 32 * TOPK_PER_LANE) return fk_fail(FK_UNSUPPORTED, "moe_route: %d experts (limit %d)", n_experts, 32 * TOPK_PER_LANE);
+    if (k < 1 || k > TOPK_MAX_K || k > n_experts) return fk_fail(FK_UNSUPPORTED, "moe_route: k=%d (limit %d, experts %d)", k, TOPK_MAX_K, n_experts);
+    if (mode < 0 || mode > 2) return fk_fail(FK_INVALID, "moe_route: mode %d", mode);
+    if (batch < 1) return fk_fail(FK_INVALID, "moe_route: batch %d", batch);
+    FkDeviceGuard g(ctx->device);
+    route_kernel<<<(batch + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits_dev, bias_dev, n_experts, k, mode, batch, ids_dev, w_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts,
+                               int cols, int batch, float* logits_dev) {
+    if (!ctx || !router_dev || !x_dev || !logits_dev) return fk_fail(FK_INVALID, "router_logits: null argument");
+    if (n_experts < 1 || cols < 1 || batch < 1 || batch > 65535) return fk_fail(FK_INVALID, "router_logits: %d x %d, batch %d", n_experts, cols, batch);
+    FkDeviceGuard g(ctx->device);
+    dim3 grid((n_experts + 7) / 8, batch);
+    router_logits_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(router_dev, x_dev, logits_dev, n_experts, cols);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int k, int n_experts,
+                             int* group_off_dev, int* gather_dev, int* pair_of_dev) {
+    if (!ctx || !ids_dev || !group_off_dev || !gather_dev || !pair_of_dev) return fk_fail(FK_INVALID, "moe_permute: null argument");
+    if (pairs < 1 || k < 1 || n_experts < 1 || n_experts > 4096) return fk_fail(FK_INVALID, "moe_permute: pairs %d, k %d, experts %d", pairs, k, n_experts);
+    FkDeviceGuard g(ctx->device);
+    permute_kernel<<<1, 1024, (n_experts + 1) * sizeof(int), (cudaStream_t)stream>>>(ids_dev, pairs, k, n_experts, group_off_dev, gather_dev, pair_of_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev, size_t n, int act, float* out_dev) {
+    if (!ctx || !gate_dev || !up_dev || !out_dev) return fk_fail(FK_INVALID, "glu: null argument");
+    if (act < 0 || act > 1) return fk_fail(FK_UNSUPPORTED, "glu: activation %d", act);
+    if (n == 0) return FK_OK;
+    FkDeviceGuard g(ctx->device);
+    glu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate_dev, up_dev, n, act, out_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
+                             int batch, int k, int n, float* out_dev) {
+    if (!ctx || !y_dev || !w_dev || !out_dev) return fk_fail(FK_INVALID, "moe_combine: null argument");
+    if (batch < 1 || batch > 65535 || k < 1 || n < 1) return fk_fail(FK_INVALID, "moe_combine: batch %d, k %d, n %d", batch, k, n);
+    FkDeviceGuard g(ctx->device);
+    dim3 grid((n + 255) / 256, batch);
+    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}

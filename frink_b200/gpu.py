@@ -1,0 +1,145 @@
+"""Host-buffer launch surface: mirror of `frink_cuda::gpu`
+(crates/frink-cuda/src/gpu.rs:91-157,319-446 and src/matvec_launch.rs:485-570).
+
+Borrowed host bytes and host f32 in, a freshly owned host array out, weights
+kept resident by (pointer, length) + fingerprint.  Same names, argument meaning
+and error behaviour as the functions frink-core binds."""
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import _lib, matvec_kinds
+from ._lib import CudaError, DriverInit, KernelCompile, Launch, Unsupported, check, lib  # noqa: F401
+
+
+@dataclass
+class CudaInfo:
+    device_count: int
+    first_device_name: Optional[str]
+    total_vram_bytes: int
+    free_vram_bytes: int
+
+
+def probe():
+    """`gpu::probe`: None on any failure to find a usable device, never raises."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        from . import device
+        ctx = device.context(0)
+        name = C.create_string_buffer(128)
+        sms, mem = C.c_int(), C.c_size_t()
+        check(lib().fk_device_info(ctx, name, 128, C.byref(sms), C.byref(mem)))
+        free, total = torch.cuda.mem_get_info(0)
+        return CudaInfo(torch.cuda.device_count(), name.value.decode(), int(total), int(free))
+    except Exception:
+        return None
+
+
+def _ctx():
+    from . import device
+    return device.context(0)
+
+
+def _host(a, dt):
+    a = np.ascontiguousarray(a, dt)
+    return a, a.ctypes.data_as(C.c_void_p)
+
+
+def _launch_matvec(kind, weights, x, rows, row_bytes, n_blocks_per_row):
+    w, wp = _host(weights, np.uint8)
+    xv, xp = _host(x, np.float32)
+    if xv.size != n_blocks_per_row * kind.block_elems:
+        raise _lib.Invalid(f"{kind.fn_name}: x has {xv.size} values, the row has {n_blocks_per_row * kind.block_elems}")
+    y = np.empty(rows, np.float32)
+    check(lib().fk_launch_matvec(_ctx(), kind.tag, wp, w.size, xp, rows, row_bytes, n_blocks_per_row, y.ctypes.data_as(C.c_void_p)))
+    return y
+
+
+def launch_q4_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
+    return _launch_matvec(matvec_kinds.kind_by_name("Q4_K"), weights, x, rows, row_bytes, n_blocks_per_row)
+
+
+def launch_q6_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
+    return _launch_matvec(matvec_kinds.kind_by_name("Q6_K"), weights, x, rows, row_bytes, n_blocks_per_row)
+
+
+def launch_q8_0_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
+    return _launch_matvec(matvec_kinds.kind_by_name("Q8_0"), weights, x, rows, row_bytes, n_blocks_per_row)
+
+
+def launch_mxfp4_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
+    return _launch_matvec(matvec_kinds.kind_by_name("MXFP4"), weights, x, rows, row_bytes, n_blocks_per_row)
+
+
+@dataclass
+class MatvecLaunch:
+    """`gpu::MatvecLaunch` (matvec_launch.rs:485-493).  `kernel_src` and
+    `module_name` belong to the reference's run-time compiler and are kept only
+    so call sites read the same; this library's kernels are compiled ahead of time."""
+    fn_name: str
+    weights: np.ndarray
+    rows: int
+    row_bytes: int
+    n_blocks_per_row: int
+    kernel_src: str = ""
+    module_name: str = ""
+
+
+def matvec_launch_meta(kind_name):
+    k = matvec_kinds.kind_by_name(kind_name)
+    if k is None:
+        return None
+    return ("", "frink_b200", k.fn_name)
+
+
+def _kind_of(launch):
+    k = matvec_kinds.kind_by_name(launch.fn_name)
+    if k is None:
+        raise Unsupported(f"no kernel for {launch.fn_name}")
+    return k
+
+
+def launch_matvec_multi(x, launches):
+    """`gpu::launch_matvec_multi` (matvec_launch.rs:495-535): one upload of `x`,
+    one matvec per launch, outputs downloaded after all were enqueued."""
+    import torch
+    from . import device
+    if not launches:
+        return []
+    xd = torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda()
+    outs = []
+    for l in launches:
+        k = _kind_of(l)
+        w = _resident(k, l)
+        outs.append(device.gemv(w, xd))
+    return [o.cpu().numpy() for o in outs]
+
+
+_res = {}
+
+
+def _resident(kind, l):
+    from . import device
+    w = np.ascontiguousarray(l.weights, np.uint8)
+    key = (w.ctypes.data, w.size, kind.tag)
+    hit = _res.get(key)
+    if hit is None:
+        hit = device.Weights(w, kind.tag, l.rows, l.n_blocks_per_row * kind.block_elems)
+        _res[key] = hit
+    return hit
+
+
+def launch_dense_ffn_swiglu(gate, up, down, x):
+    """`gpu::launch_dense_ffn_swiglu` (matvec_launch.rs:537-570): x up once,
+    gate and up matvecs, silu(gate)*up, down matvec, one download."""
+    import torch
+    from . import device
+    xd = torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda()
+    g = device.gemv(_resident(_kind_of(gate), gate), xd)
+    u = device.gemv(_resident(_kind_of(up), up), xd)
+    a = device.glu(g, u, 0)
+    return device.gemv(_resident(_kind_of(down), down), a).cpu().numpy()

@@ -1,0 +1,166 @@
+/* frink_b200 -- C ABI of the B200 (sm_100a) backend for frink's
+ * dequantize-inside-the-matmul path.
+ *
+ * This library takes the place of frink-cuda's kernel set behind frink-core's
+ * `WeightMatrix` backend seam.  Every entry point below names the frink
+ * interface it replaces (file:line inside the frink project, v0.63.0).  All
+ * functions return an `fk_status`; a failing call leaves a message that
+ * `fk_last_error` returns (per calling thread).  The library is thread safe;
+ * no host allocation crosses the ABI (callers pass every output buffer).
+ *
+ * Pointers named `*_dev` are CUDA device pointers on the context's device,
+ * pointers named `*_host` are ordinary host memory.  `stream` is a
+ * `cudaStream_t` passed as `void*` (NULL = the legacy default stream).
+ *
+ * Weight bytes are ALWAYS the unmodified GGUF block bytes of the tensor
+ * (row-major, `row_bytes = cols / block_elems * block_bytes`); the library
+ * uploads them once and may rearrange them on the device.
+ */
+#ifndef FRINK_B200_H
+#define FRINK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Mirrors `CudaError::{DriverInit, KernelCompile, Launch, Unsupported}`
+ * (crates/frink-cuda/src/gpu.rs:91-104).  UNSUPPORTED keeps its contract: the
+ * caller must use a path that can compute the result, never something else. */
+typedef enum fk_status {
+    FK_OK = 0,
+    FK_DRIVER_INIT = 1,
+    FK_KERNEL = 2,
+    FK_LAUNCH = 3,
+    FK_UNSUPPORTED = 4,
+    FK_COMM = 5,
+    FK_INVALID = 6
+} fk_status;
+
+/* Block formats, by ggml type tag (crates/frink-core/src/weight_matrix.rs:43,
+ * `QuantKind`; layouts crates/frink-quant/src/lib.rs:73-75,176-197,5560-5571). */
+typedef enum fk_kind {
+    FK_Q8_0 = 8,   /* 34 B / 32 weights  */
+    FK_Q4_K = 12,  /* 144 B / 256 weights */
+    FK_Q6_K = 14,  /* 210 B / 256 weights */
+    FK_MXFP4 = 39  /* 17 B / 32 weights  */
+} fk_kind;
+
+typedef struct fk_ctx fk_ctx;
+typedef struct fk_weight_s* fk_weight;
+
+/* ---- context ------------------------------------------------------------
+ * Replaces `gpu::shared_device` / `gpu::probe` (crates/frink-cuda/src/
+ * gpu.rs:121-222): one context per device, created once, used from any thread. */
+int fk_init(int device, fk_ctx** out);
+void fk_destroy(fk_ctx* ctx);
+const char* fk_last_error(void);
+/* name[<=cap], SM count, global memory bytes: `CudaInfo` (gpu.rs:106-119). */
+int fk_device_info(fk_ctx* ctx, char* name, size_t cap, int* sm_count, size_t* mem_bytes);
+/* Counters since the last reset: H2D bytes, D2H bytes, kernel launches made
+ * by this library (crates/frink-cuda/src/counters.rs, xfer.rs). */
+int fk_counters(fk_ctx* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint64_t* launches, int reset);
+int fk_block_bytes(int kind);
+int fk_block_elems(int kind);
+
+/* ---- resident weights ---------------------------------------------------
+ * Replaces `resident_cuda_weights` (crates/frink-cuda/src/resident.rs): the
+ * GGUF bytes of `n_mats` equally shaped matrices (1 for a dense projection,
+ * `n_expert` for a stacked expert tensor), uploaded once.  `len` must equal
+ * n_mats * rows * row_bytes. */
+int fk_register_weights(fk_ctx* ctx, const uint8_t* gguf_bytes_host, size_t len, int kind, int n_mats,
+                        int rows, int cols, fk_weight* out);
+/* The same from bytes already on the device (copied; the source may be freed). */
+int fk_register_weights_dev(fk_ctx* ctx, const uint8_t* gguf_bytes_dev, size_t len, int kind, int n_mats,
+                            int rows, int cols, void* stream, fk_weight* out);
+int fk_release_weights(fk_ctx* ctx, fk_weight w);
+int fk_weight_shape(fk_weight w, int* kind, int* n_mats, int* rows, int* cols, size_t* gguf_bytes);
+
+/* ---- activation quantizer ----------------------------------------------
+ * Replaces `quantize_q8_1` (crates/frink-cuda/src/matvec_kinds/dp4a/
+ * kernels.rs:113-143): n f32 (n % 32 == 0) -> n/32 `block_q8_1` of 36 bytes
+ * (f16 d = amax/127, f16 sum, 32 x int8 = roundf(x/d)).  The GEMV and GEMM
+ * below quantize their activations with exactly this rule, fused. */
+int fk_quantize_q8_1(fk_ctx* ctx, void* stream, const float* x_dev, int n, uint8_t* y_dev);
+
+/* ---- decode GEMV, batch 1..8 ---------------------------------------------
+ * Replaces `q4_k_matvec_dp4a`, `q6_k_matvec_dp4a`, `q8_0_matvec_dp4a`,
+ * `mxfp4_matvec_dp4a` and their launch (kernels.rs:243-465,
+ * crates/frink-cuda/src/dp4a_launch.rs:185-246).
+ * y_dev[b * rows + r] = W[mat][r] . q8_1(x_dev[b * cols ..]),  0 <= b < batch. */
+int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev);
+
+/* Indexed expert GEMV: the `FX_MULTI` form (kernels.rs:166-179,
+ * dp4a_launch.rs:256-314).  Slot j (0 <= j < k) multiplies matrix
+ * `ids_dev[j]` of `w` with x_dev[j * x_stride ..] (x_stride 0 = one shared
+ * input) into y_dev[j * rows ..]. */
+int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
+                  int x_stride, float* y_dev);
+
+/* Test hook (the reference's twins expose the same integers,
+ * crates/frink-cuda/src/dp4a_twin.rs:142-231): the exact int32 dot of every
+ * run of 32 activations (16 for Q6_K) of every row against q8_1(x), computed
+ * by the GEMV kernel's own inner loop.  isums_dev is [rows][cols / run]. */
+int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int32_t* isums_dev);
+
+/* ---- prefill GEMM ---------------------------------------------------------
+ * Replaces `mul_mm_launch::launch_mul_mm` / `enqueue_mmq` (crates/frink-cuda/
+ * src/mul_mm_launch.rs:40-68, src/mmq/mod.rs:30-133):
+ * out_dev[t * rows + r] = W[mat][r] . q8_1(x_dev[t * cols ..]),  0 <= t < m. */
+int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev);
+
+/* Grouped (per-expert) GEMM, the `FX_GROUPED` form (src/mmq/mod.rs:144-226):
+ * rows [group_off[e], group_off[e+1]) of the permuted activation list belong to
+ * expert e; permuted row p reads x_dev[gather_dev[p] * cols ..] (gather NULL =
+ * identity) and writes out_dev[p * rows ..]. */
+int fk_gemm_grouped(fk_ctx* ctx, void* stream, fk_weight w, const int* group_off_dev, const int* gather_dev,
+                    const float* x_dev, int pairs, float* out_dev);
+
+/* ---- MoE routing, permute, activation, combine ----------------------------
+ * `moe_topk_f32` (crates/frink-cuda/src/prefill/kernels.rs:178-267): mode 0
+ * softmax over all experts, 1 the same renormalised over the chosen, 2 top-k by
+ * (biased) logit then softmax over the chosen (gpt-oss).  Ties -> lower id. */
+int fk_moe_route(fk_ctx* ctx, void* stream, const float* logits_dev, const float* bias_dev, int n_experts,
+                 int k, int mode, int batch, int* ids_dev, float* w_dev);
+/* `router_f32_matvec` (kernels.rs:356-378): logits[t][e] = router[e] . x[t]. */
+int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts,
+                     int cols, int batch, float* logits_dev);
+/* `moe_count_i32` + `moe_offsets_i32` + `moe_scatter_i32` (kernels.rs:271-308):
+ * pairs = batch * k (token p / k, slot p % k) grouped by expert, tokens in
+ * ascending order inside a group.  group_off_dev[n_experts + 1],
+ * gather_dev[pairs] (token of each permuted row), pair_of_dev[pairs]. */
+int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int k, int n_experts,
+                   int* group_off_dev, int* gather_dev, int* pair_of_dev);
+/* `silu_mul_f32` / `swiglu_oai_f32` (crates/frink-cuda/src/glu.rs:42,68):
+ * act 0 = silu(gate) * up, 1 = gpt-oss clamped SwiGLU (alpha 1.702, limit 7). */
+int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev, size_t n, int act,
+           float* out_dev);
+/* `moe_combine_rows_f32` (kernels.rs:332-352): out[t] = sum_j w[t][j] *
+ * y[pair_of[t*k+j]] from zero in routing order (pair_of NULL = identity). */
+int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
+                   int batch, int k, int n, float* out_dev);
+
+/* ---- host-buffer launch surface -------------------------------------------
+ * What frink-core binds (crates/frink-core/src/weight_matrix/gpu_backend.rs:
+ * 247-273,563-565): host slices in, host slice out, one call per projection.
+ * Weights are kept resident, keyed by (pointer, length) plus a byte-sample
+ * fingerprint, as crates/frink-cuda/src/resident.rs does.
+ *
+ * `gpu::launch_<kind>_matvec(weights, x, rows, row_bytes, n_blocks_per_row)`
+ * (crates/frink-cuda/src/gpu.rs:319-446). */
+int fk_launch_matvec(fk_ctx* ctx, int kind, const uint8_t* weights_host, size_t len, const float* x_host,
+                     int rows, int row_bytes, int n_blocks_per_row, float* y_host);
+/* `mul_mm_launch::launch_mul_mm(kind, weights, x_batch, n_rows, n_cols, batch,
+ * row_bytes)` (crates/frink-cuda/src/mul_mm_launch.rs:40-68);
+ * out_host[token * n_rows + row].  batch 1..8 takes the GEMV. */
+int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_host, size_t len, const float* x_batch_host,
+                     int n_rows, int n_cols, int batch, int row_bytes, float* out_host);
+/* Drops every weight the host-buffer surface made resident. */
+int fk_forget_resident(fk_ctx* ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRINK_B200_H */

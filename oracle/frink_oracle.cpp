@@ -1015,21 +1015,12 @@ void encode_block_mxfp4(const float* block, uint8_t* out) {
 void route_top_k(const float* logits, const float* bias, int n, int k, int mode, int* ids, float* w) {
     std::vector<float> v(n);
     for (int e = 0; e < n; e++) v[e] = logits[e] + (bias ? bias[e] : 0.0f);
-    std::vector<float> key(n);
-    float sum = 0.0f;
-    if (mode == 2) {
-        key = v;
-    } else {
-        float mx = -INFINITY;
-        for (int e = 0; e < n; e++) mx = std::fmax(mx, v[e]);
-        std::vector<float> exps(n);
-        for (int e = 0; e < n; e++) exps[e] = std::exp(v[e] - mx);
-        for (int e = 0; e < n; e++) sum += exps[e];
-        for (int e = 0; e < n; e++) key[e] = exps[e] / sum;
-    }
+    // Selection is by (biased) logit, as the device kernel selects; softmax is
+    // monotonic, so this is the host's order by probability with the tie rule
+    // made explicit (two logits that round to one probability stay ordered).
     std::vector<int> idx(n);
     for (int e = 0; e < n; e++) idx[e] = e;
-    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return key[a] > key[b]; });
+    std::stable_sort(idx.begin(), idx.end(), [&](int a, int b) { return v[a] > v[b]; });
     int kk = std::min(k, n);
     if (mode == 2) {
         float mx = -INFINITY;
@@ -1040,8 +1031,13 @@ void route_top_k(const float* logits, const float* bias, int n, int k, int mode,
         for (int s = 0; s < kk; s++) { ids[s] = idx[s]; w[s] = es > 0.0f ? ex[s] / es : ex[s]; }
         return;
     }
+    float mx = -INFINITY, sum = 0.0f;
+    for (int e = 0; e < n; e++) mx = std::fmax(mx, v[e]);
+    std::vector<float> exps(n);
+    for (int e = 0; e < n; e++) exps[e] = std::exp(v[e] - mx);
+    for (int e = 0; e < n; e++) sum += exps[e];
     float ts = 0.0f;
-    for (int s = 0; s < kk; s++) { ids[s] = idx[s]; w[s] = key[idx[s]]; ts += w[s]; }
+    for (int s = 0; s < kk; s++) { ids[s] = idx[s]; w[s] = exps[idx[s]] / sum; ts += w[s]; }
     if (mode == 1) for (int s = 0; s < kk; s++) w[s] /= ts;
 }
 

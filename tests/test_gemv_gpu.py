@@ -1,0 +1,162 @@
+"""Parity of the decode GEMV (through the C ABI) against the CPU oracle.
+
+Bar: the q8_1 activation bytes and every per-run int32 dot are bit-exact; the
+f32 outputs stay within relative L2 1e-3 and max-abs 2e-3 * |y|_inf of the f64
+dequantize-then-dot of the activations the kernel reads (their q8_1 rounding)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import frink_oracle as fo
+from tests.helpers import max_abs_over_inf, rel_l2, synth_acts, synth_weights
+
+pytestmark = pytest.mark.gpu
+
+REL_L2, MAX_ABS = 1e-3, 2e-3
+KINDS = [fo.Q4_K, fo.Q6_K, fo.Q8_0, fo.MXFP4]
+
+
+def _case(kind, rows, cols, batch, seed):
+    from frink_b200 import device
+    raw = fo.encode(kind, synth_weights(rows, cols, seed))
+    x = synth_acts(batch, cols, seed + 1)
+    w = device.Weights(raw, kind, rows, cols)
+    return raw, x, w
+
+
+def _check(got, raw, kind, rows, cols, x):
+    want = fo.matmul_f64(kind, raw, rows, cols, fo.q8_1_round(x))
+    assert got.shape == want.shape
+    assert np.isfinite(got).all()
+    r, m = rel_l2(got, want), max_abs_over_inf(got, want)
+    assert r <= REL_L2 and m <= MAX_ABS, (r, m)
+    return want
+
+
+def test_q8_1_bytes_are_bit_exact():
+    from frink_b200 import device
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal(64 * 32).astype(np.float32) * np.float32(3.0)
+    x[:32] = 0.0
+    x[32:64] = [127.0, 2.5, -3.5, 0.5, -0.5, 126.5] + [0.0] * 26  # exact ties
+    x[64:96] *= np.float32(1e-30)
+    got = device.quantize_q8_1_host(x)
+    assert np.array_equal(got, fo.quantize_q8_1(x))
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("rows,cols", [(64, 1024), (37, 768), (5, 256), (1, 2048), (130, 2880)])
+def test_per_run_integer_dots_are_bit_exact(kind, rows, cols):
+    from frink_b200 import device
+    if cols % fo.block_elems(kind):
+        pytest.skip("not a whole number of blocks")
+    raw, x, w = _case(kind, rows, cols, 1, 100 + rows)
+    got = device.gemv_isums(w, torch.from_numpy(x[0]).cuda()).cpu().numpy()
+    want = fo.matrix_isums(kind, raw, rows, cols, fo.quantize_q8_1(x[0]))
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("batch", [1, 2, 3, 4, 5, 8])
+def test_gemv_matches_oracle(kind, batch):
+    from frink_b200 import device
+    rows, cols = 515, (2880 if kind == fo.MXFP4 else 3072)
+    raw, x, w = _case(kind, rows, cols, batch, 200 + batch)
+    xd = torch.from_numpy(x).cuda()
+    y = torch.full((batch, rows), float("nan"), device="cuda")  # every element must be written
+    device.gemv(w, xd, out=y)
+    got = y.cpu().numpy()
+    want = _check(got, raw, kind, rows, cols, x)
+    # deterministic: a second launch gives the same bits
+    y2 = device.gemv(w, xd).cpu().numpy()
+    assert np.array_equal(got, y2)
+    if batch == 1:
+        # the reference's device-test convention: its kernel twin, relative 1e-4
+        # (crates/frink-cuda/src/gpu.rs:881-905)
+        y8 = fo.quantize_q8_1(x[0])
+        rb = fo.row_bytes(kind, cols)
+        twin = np.array([fo.dp4a_row(kind, raw[r * rb:(r + 1) * rb], y8) for r in range(rows)], np.float32)
+        scale = np.abs(fo.dequant(kind, raw).reshape(rows, cols).astype(np.float64) * fo.q8_1_round(x[0])).sum(axis=1)
+        assert np.all(np.abs(got[0] - twin) <= 1e-5 * scale + 1e-4 * np.maximum(np.abs(twin), 1.0) * 1e-2)
+        # reported, not gated: distance to frink's CPU paths on the raw activations
+        l2 = fo.matmul_q8(kind, raw, rows, cols, x)
+        l0 = fo.matvec_f32(kind, raw, rows, cols, x)
+        print(f"kind {kind}: rel-L2 to oracle(q8_1 acts) {rel_l2(got, want):.2e}; to CPU int-dot path {rel_l2(got, l2):.2e}; "
+              f"to CPU f32-dot path on raw x {rel_l2(got, l0):.2e}")
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_edge_shapes(kind):
+    from frink_b200 import device
+    be = fo.block_elems(kind)
+    for rows, cols in [(1, max(be, 32)), (3, 256), (2, 8192), (1025, 512)]:
+        raw, x, w = _case(kind, rows, cols, 2, 300 + rows)
+        got = device.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+        want = fo.matmul_f64(kind, raw, rows, cols, fo.q8_1_round(x))
+        # short rows have no averaging: hold them to the absolute part of the bar
+        assert max_abs_over_inf(got, want) <= MAX_ABS, (rows, cols)
+    # all-zero activations and all-zero weights
+    raw, x, w = _case(kind, 8, 512, 1, 1)
+    assert not device.gemv(w, torch.zeros(512, device="cuda")).cpu().numpy().any()
+    wz = device.Weights(fo.encode(kind, np.zeros((8, 512), np.float32)), kind, 8, 512)
+    assert not device.gemv(wz, torch.from_numpy(x[0]).cuda()).cpu().numpy().any()
+
+
+@pytest.mark.parametrize("kind", KINDS)
+def test_indexed_expert_gemv(kind):
+    from frink_b200 import device
+    n_exp, rows, cols, k = 6, 96, 768 if kind != fo.MXFP4 else 2880, 4
+    rng = np.random.default_rng(9)
+    raws = [fo.encode(kind, synth_weights(rows, cols, 400 + e)) for e in range(n_exp)]
+    w = device.Weights(np.concatenate(raws), kind, rows, cols, n_mats=n_exp)
+    ids = np.array([4, 0, 5, 4], np.int32)
+    x = rng.standard_normal((k, cols)).astype(np.float32)
+    idd = torch.from_numpy(ids).cuda()
+    got = device.gemv_multi(w, idd, torch.from_numpy(x).cuda()).cpu().numpy()
+    for j in range(k):
+        want = fo.matmul_f64(kind, raws[ids[j]], rows, cols, fo.q8_1_round(x[j]))[0]
+        assert rel_l2(got[j], want) <= REL_L2 and max_abs_over_inf(got[j], want) <= MAX_ABS
+    shared = device.gemv_multi(w, idd, torch.from_numpy(x[0]).cuda()).cpu().numpy()
+    for j in range(k):
+        want = fo.matmul_f64(kind, raws[ids[j]], rows, cols, fo.q8_1_round(x[0]))[0]
+        assert rel_l2(shared[j], want) <= REL_L2
+    # matrix m of a stack through the plain entry
+    y = device.gemv(w, torch.from_numpy(x[1]).cuda(), mat=3).cpu().numpy()
+    assert rel_l2(y, fo.matmul_f64(kind, raws[3], rows, cols, fo.q8_1_round(x[1]))[0]) <= REL_L2
+
+
+def test_host_buffer_surface_and_errors():
+    from frink_b200 import _lib, device, gpu, matvec_kinds, mul_mm_launch
+    assert gpu.probe() is not None
+    rows, cols = 200, 1024
+    for name, fn in [("Q4_K", gpu.launch_q4_k_matvec), ("Q6_K", gpu.launch_q6_k_matvec),
+                     ("Q8_0", gpu.launch_q8_0_matvec), ("MXFP4", gpu.launch_mxfp4_matvec)]:
+        k = matvec_kinds.kind_by_name(name)
+        raw = fo.encode(k.tag, synth_weights(rows, cols, 7))
+        x = synth_acts(1, cols, 8)[0]
+        rb = fo.row_bytes(k.tag, cols)
+        y = fn(raw, x, rows, rb, cols // k.block_elems)
+        want = fo.matmul_f64(k.tag, raw, rows, cols, matvec_kinds.matvec_reads(k.fn_name, cols // k.block_elems, x))[0]
+        assert rel_l2(y, want) <= REL_L2
+        assert np.array_equal(y, fn(raw, x, rows, rb, cols // k.block_elems))  # resident second call
+        xb = synth_acts(4, cols, 9)
+        out = mul_mm_launch.launch_mul_mm(k, raw, xb, rows, cols, 4, rb).reshape(4, rows)
+        assert rel_l2(out, fo.matmul_f64(k.tag, raw, rows, cols, fo.q8_1_round(xb))) <= REL_L2
+        with pytest.raises(_lib.Invalid):
+            fn(raw, x, rows, rb + 1, cols // k.block_elems)
+    with pytest.raises(_lib.Unsupported):
+        device.Weights(np.zeros(18 * 4, np.uint8), 2, 1, 128)  # Q4_0: no kernel here
+    with pytest.raises(_lib.Invalid):
+        device.Weights(np.zeros(100, np.uint8), 12, 1, 256)
+    c = device.counters()
+    assert c["launches"] > 0 and c["h2d_bytes"] > 0
+
+
+def test_config1_shape_q4_k_8192x3072():
+    """BASELINE config 1 at full size: Q4_K 8192 x 3072, batch 1."""
+    from frink_b200 import device
+    raw, x, w = _case(fo.Q4_K, 8192, 3072, 1, 0x5EED)
+    got = device.gemv(w, torch.from_numpy(x[0]).cuda()).cpu().numpy()
+    _check(got[None], raw, fo.Q4_K, 8192, 3072, x)
+    isums = device.gemv_isums(w, torch.from_numpy(x[0]).cuda()).cpu().numpy()
+    assert np.array_equal(isums, fo.matrix_isums(fo.Q4_K, raw, 8192, 3072, fo.quantize_q8_1(x[0])))

@@ -1,0 +1,61 @@
+"""MoE plumbing kernels against the oracle: routing (ids exact, weights to f32
+rounding), the expert permutation, the gated activations and the combine."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import frink_oracle as fo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n_experts,k,mode", [(128, 8, 1), (128, 4, 2), (64, 6, 0), (8, 2, 1), (256, 16, 1), (5, 5, 0)])
+def test_route_matches_oracle(n_experts, k, mode):
+    from frink_b200 import device
+    rng = np.random.default_rng(n_experts + k)
+    logits = rng.standard_normal((33, n_experts)).astype(np.float32)
+    logits[3, :] = 0.25          # all tied: lower ids first
+    logits[4, 1] = logits[4, 0]  # a tie at the top
+    bias = rng.standard_normal(n_experts).astype(np.float32) if mode == 2 else None
+    ids, w = device.moe_route(torch.from_numpy(logits).cuda(), k, mode, None if bias is None else torch.from_numpy(bias).cuda())
+    wi, ww = fo.route_top_k(logits, k, mode, bias)
+    assert np.array_equal(ids.cpu().numpy(), wi)
+    assert np.allclose(w.cpu().numpy(), ww, rtol=2e-6, atol=1e-8)
+
+
+def test_permute_groups_pairs_by_expert_in_token_order():
+    from frink_b200 import device
+    rng = np.random.default_rng(2)
+    n_experts, k, batch = 128, 8, 512
+    ids = np.stack([rng.choice(n_experts, k, replace=False) for _ in range(batch)]).astype(np.int32)
+    off, gather, pair_of = [t.cpu().numpy() for t in device.moe_permute(torch.from_numpy(ids).cuda(), n_experts)]
+    flat = ids.ravel()
+    assert off[0] == 0 and off[-1] == batch * k and np.array_equal(np.diff(off), np.bincount(flat, minlength=n_experts))
+    order = np.argsort(flat, kind="stable")
+    assert np.array_equal(gather, order // k)
+    assert np.array_equal(pair_of[order], np.arange(batch * k))
+    # one pair, and an expert nobody chose
+    off, gather, pair_of = [t.cpu().numpy() for t in device.moe_permute(torch.tensor([[2]], dtype=torch.int32).cuda(), 4)]
+    assert list(off) == [0, 0, 0, 1, 1] and list(gather) == [0] and list(pair_of) == [0]
+
+
+def test_glu_combine_and_router_logits():
+    from frink_b200 import device
+    rng = np.random.default_rng(3)
+    g = (rng.standard_normal(5000) * 4).astype(np.float32)
+    u = (rng.standard_normal(5000) * 4).astype(np.float32)
+    gd, ud = torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()
+    assert np.allclose(device.glu(gd, ud, 0).cpu().numpy(), fo.silu_mul(g, u), rtol=2e-6, atol=1e-7)
+    assert np.allclose(device.glu(gd, ud, 1).cpu().numpy(), fo.swiglu_oai(g, u), rtol=2e-6, atol=1e-7)
+    batch, k, n = 7, 4, 333
+    ys = rng.standard_normal((batch * k, n)).astype(np.float32)
+    w = rng.random((batch, k)).astype(np.float32)
+    perm = rng.permutation(batch * k).astype(np.int32)
+    out = device.moe_combine(torch.from_numpy(ys).cuda(), torch.from_numpy(perm).cuda(), torch.from_numpy(w).cuda(), batch, k).cpu().numpy()
+    for t in range(batch):
+        want = fo.combine(ys[perm[t * k:(t + 1) * k]], w[t])
+        assert np.allclose(out[t], want, rtol=1e-6, atol=1e-6)
+    router = (rng.standard_normal((128, 2048)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((5, 2048)).astype(np.float32)
+    lg = device.router_logits(torch.from_numpy(router).cuda(), torch.from_numpy(x).cuda()).cpu().numpy()
+    assert np.allclose(lg, x.astype(np.float64) @ router.astype(np.float64).T, rtol=1e-4, atol=1e-5)
