@@ -185,6 +185,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--case", default=None, help="kind:rows:cols:batch -- plain launches of one GEMV shape (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -203,6 +204,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     from frink_b200 import device, gpu, build
     build.build()
+
+    if args.case:
+        return single_case(args)
 
     raw, x = synth()
     raw_d = torch.from_numpy(raw).cuda()
@@ -295,6 +299,39 @@ def main():
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def single_case(args):
+    """`--case kind:rows:cols:batch`: `--steps` plain (un-graphed) launches of one
+    GEMV shape over a ring of weight copies larger than L2; what the ncu captures
+    under profiles/ run."""
+    import torch
+    from frink_b200 import device
+    from oracle import frink_oracle as fo
+    name, rows, cols, batch = args.case.split(":")
+    kind, rows, cols, batch = fo.KINDS[name], int(rows), int(cols), int(batch)
+    rng = np.random.default_rng(1)
+    base_rows = min(rows, 1024)
+    base = fo.encode(kind, (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(0.02)))
+    raw = np.tile(base, -(-rows // base_rows))[: rows * fo.row_bytes(kind, cols)]
+    raw_d = torch.from_numpy(raw).cuda()
+    ring = max(2, int(400e6 // raw.size) + 1)
+    ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
+    xd = torch.from_numpy(rng.standard_normal((batch, cols), dtype=np.float32)).cuda()
+    yd = torch.empty((batch, rows), dtype=torch.float32, device="cuda")
+    for i in range(args.warmup):
+        device.gemv(ws[i % ring], xd, out=yd)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        device.gemv(ws[i % ring], xd, out=yd)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    nbytes = raw.size + batch * cols * 4 + batch * rows * 4
+    print(json.dumps({"case": args.case, "steps": args.steps, "us_per_launch_incl_host": ms / args.steps * 1e3,
+                      "algorithmic_bytes": nbytes, "ring": ring}))
 
 
 def extras(peak):

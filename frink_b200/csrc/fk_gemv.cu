@@ -43,21 +43,6 @@ __device__ __forceinline__ int dp4a4(const uint4& a, const int4& b) {
     s = __dp4a((int)a.z, b.z, s);
     return __dp4a((int)a.w, b.w, s);
 }
-__device__ __forceinline__ uint32_t byte_of(uint32_t s0, uint32_t s1, uint32_t s2, int k) {
-    const uint32_t w = k < 4 ? s0 : (k < 8 ? s1 : s2);
-    return (w >> (8 * (k & 3))) & 0xFFu;
-}
-// 6-bit scale and min of Q4_K sub-block j from the 12 packed bytes.
-__device__ __forceinline__ void q4k_scale_min(uint32_t s0, uint32_t s1, uint32_t s2, int j, int* sc, int* m) {
-    if (j < 4) {
-        *sc = byte_of(s0, s1, s2, j) & 63;
-        *m = byte_of(s0, s1, s2, j + 4) & 63;
-    } else {
-        const uint32_t b = byte_of(s0, s1, s2, j + 4);
-        *sc = (b & 0x0F) | ((byte_of(s0, s1, s2, j - 4) >> 6) << 4);
-        *m = (b >> 4) | ((byte_of(s0, s1, s2, j) >> 6) << 4);
-    }
-}
 // Four E2M1 codes (the four nibbles of the low 16 bits of `w`) to their doubled
 // int8 values {0,1,2,3,4,6,8,12} with sign, one per byte, in nibble order.
 __device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
@@ -73,7 +58,221 @@ __device__ __forceinline__ float e8m0_half(uint32_t e) {
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
 }
 
-template <int KIND, int NB, bool DUMP>
+// ---------------------------------------------------------------------------
+// A "piece" is what one lane holds of one weight row for one trip of the warp
+// along K: 16 bytes of packed weights plus the scale words that go with them.
+// load() only issues global loads (so a batch of pieces can be in flight
+// together); eat() unpacks and accumulates.
+//   Q4_K : 8 lanes per 144-byte super-block, a trip covers 4 super-blocks.
+//          Lane c owns quant bytes [16c, 16c+16): low nibbles are 16 weights of
+//          sub-block 2g, high nibbles 16 weights of sub-block 2g+1 (g = c/2).
+//   Q6_K : 8 lanes per super-block; lane c owns ql bytes [16c, 16c+16) and the
+//          matching 16 qh bytes: two runs of 16 weights (groups g_lo, g_lo+4).
+//   Q8_0 : a lane owns 16 int8 (half a block); a trip covers 512 weights.
+//   MXFP4: a lane owns one block's 16 code bytes; a trip covers 1024 weights.
+struct Smem {
+    const int8_t* q;   // [NB][cols]
+    const float* d;    // [NB][cols/32]
+    const float* s;    // Q4_K: d * run sum
+    const int* b16;    // Q6_K: sums of 16
+    int cols, nb32;
+};
+
+template <int KIND> struct Piece;
+
+template <> struct Piece<FK_Q4_K> {
+    uint4 hd, wq;
+    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 8) + 3) >> 2; }
+    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
+        hd = make_uint4(0, 0, 0, 0);
+        wq = make_uint4(0, 0, 0, 0);
+        if (row_ok && sb < nsb) {
+            const uint8_t* p = wb + ((size_t)row * nsb + sb) * 144;
+            hd = ldg16(p);
+            wq = ldg16(p + 16 + 16 * (lane & 7));
+        }
+    }
+    template <int NB, bool DUMP>
+    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
+        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
+        const bool live = sb < nsb;
+        const int sbs = live ? sb : 0;
+        const int c = lane & 7, g = c >> 1, h = c & 1;
+        // 6-bit scales and mins of sub-blocks 2g, 2g+1, two at a time from the
+        // 16-bit words of the 12 packed bytes
+        const uint32_t w0 = hd.y, w1 = hd.z, w2 = hd.w;
+        uint32_t sc2, m2;
+        if (g < 2) {
+            const uint32_t s_lo = g ? (w0 >> 16) : (w0 & 0xFFFF), s_hi = g ? (w1 >> 16) : (w1 & 0xFFFF);
+            sc2 = s_lo & 0x3F3F;
+            m2 = s_hi & 0x3F3F;
+        } else {
+            const uint32_t A = (g & 1) ? (w2 >> 16) : (w2 & 0xFFFF);
+            const uint32_t B = (g & 1) ? (w0 >> 16) : (w0 & 0xFFFF);
+            const uint32_t C = (g & 1) ? (w1 >> 16) : (w1 & 0xFFFF);
+            sc2 = (A & 0x0F0F) | ((B & 0xC0C0) >> 2);
+            m2 = ((A >> 4) & 0x0F0F) | ((C & 0xC0C0) >> 2);
+        }
+        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF)), dmin = fk_h2f((uint16_t)(hd.x >> 16));
+        const float f_lo = d * (float)(sc2 & 0xFF), f_hi = d * (float)(sc2 >> 8);
+        // the two lanes sharing a sub-block (h = 0, 1) each carry half its min term
+        const float mm_lo = 0.5f * dmin * (float)(m2 & 0xFF), mm_hi = 0.5f * dmin * (float)(m2 >> 8);
+        uint4 lo, hi;
+        lo.x = wq.x & 0x0F0F0F0Fu; hi.x = (wq.x >> 4) & 0x0F0F0F0Fu;
+        lo.y = wq.y & 0x0F0F0F0Fu; hi.y = (wq.y >> 4) & 0x0F0F0F0Fu;
+        lo.z = wq.z & 0x0F0F0F0Fu; hi.z = (wq.z >> 4) & 0x0F0F0F0Fu;
+        lo.w = wq.w & 0x0F0F0F0Fu; hi.w = (wq.w >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256 + 64 * g + 16 * h;
+            const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 32);
+            const float2 d8 = *(const float2*)(sm.d + b * sm.nb32 + sbs * 8 + 2 * g);
+            const float2 s8 = *(const float2*)(sm.s + b * sm.nb32 + sbs * 8 + 2 * g);
+            int il = dp4a4(lo, ua), ih = dp4a4(hi, ub);
+            acc[b] += f_lo * d8.x * (float)il + f_hi * d8.y * (float)ih - (mm_lo * s8.x + mm_hi * s8.y);
+            if (DUMP && b == 0) {
+                il += __shfl_xor_sync(0xffffffffu, il, 1);
+                ih += __shfl_xor_sync(0xffffffffu, ih, 1);
+                if (live && h == 0 && row_ok) {
+                    int32_t* o = a.isums + (size_t)row * sm.nb32 + sb * 8 + 2 * g;
+                    o[0] = il;
+                    o[1] = ih;
+                }
+            }
+        }
+    }
+};
+
+template <> struct Piece<FK_Q8_0> {
+    uint4 wq;
+    uint32_t dbits;
+    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 4) + 31) >> 5; }
+    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+        const int ci = trip * 32 + lane;
+        wq = make_uint4(0, 0, 0, 0);
+        dbits = 0;
+        if (row_ok && ci < (a.cols >> 4)) {
+            wq = ldg16(wb + a.plane_off[0] + (size_t)row * a.cols + (size_t)ci * 16);
+            dbits = __ldg((const uint16_t*)(wb + a.plane_off[1]) + (size_t)row * (a.cols >> 5) + (ci >> 1));
+        }
+    }
+    template <int NB, bool DUMP>
+    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
+        const int ci = trip * 32 + lane;
+        const bool live = ci < (sm.cols >> 4);
+        const int cs = live ? ci : 0;
+        const float dw = fk_h2f((uint16_t)dbits);
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int4 ua = *(const int4*)(sm.q + (size_t)b * sm.cols + cs * 16);
+            int is = dp4a4(wq, ua);
+            acc[b] += dw * sm.d[b * sm.nb32 + (cs >> 1)] * (float)is;
+            if (DUMP && b == 0) {
+                is += __shfl_xor_sync(0xffffffffu, is, 1);
+                if (live && !(lane & 1) && row_ok) a.isums[(size_t)row * sm.nb32 + (ci >> 1)] = is;
+            }
+        }
+    }
+};
+
+template <> struct Piece<FK_Q6_K> {
+    uint4 ql, qh;
+    int sc_lo, sc_hi;
+    uint32_t dbits;
+    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 8) + 3) >> 2; }
+    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
+        const int c = lane & 7, hf = c >> 2, q = c & 3;
+        ql = make_uint4(0, 0, 0, 0);
+        qh = ql;
+        sc_lo = sc_hi = 0;
+        dbits = 0;
+        if (row_ok && sb < nsb) {
+            const size_t r = (size_t)row;
+            ql = ldg16(wb + a.plane_off[0] + r * (a.cols >> 1) + (size_t)sb * 128 + 16 * c);
+            qh = ldg16(wb + a.plane_off[1] + r * (a.cols >> 2) + (size_t)sb * 64 + 32 * hf + 16 * (q & 1));
+            const int8_t* sc = (const int8_t*)(wb + a.plane_off[2]) + r * (a.cols >> 4) + sb * 16 + 8 * hf + q;
+            sc_lo = __ldg(sc);
+            sc_hi = __ldg(sc + 4);
+            dbits = __ldg((const uint16_t*)(wb + a.plane_off[3]) + r * nsb + sb);
+        }
+    }
+    template <int NB, bool DUMP>
+    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
+        const int nsb = sm.cols >> 8, sb = trip * 4 + (lane >> 3);
+        const bool live = sb < nsb;
+        const int sbs = live ? sb : 0;
+        const int c = lane & 7, hf = c >> 2, q = c & 3;
+        const int g_lo = 8 * hf + q, g_hi = g_lo + 4;
+        const int shift = 2 * (q >> 1);
+        const float d = fk_h2f((uint16_t)dbits);
+        const float f_lo = d * (float)sc_lo, f_hi = d * (float)sc_hi;
+        uint4 vl, vh;
+        vl.x = (ql.x & 0x0F0F0F0Fu) | (((qh.x >> shift) & 0x03030303u) << 4);
+        vl.y = (ql.y & 0x0F0F0F0Fu) | (((qh.y >> shift) & 0x03030303u) << 4);
+        vl.z = (ql.z & 0x0F0F0F0Fu) | (((qh.z >> shift) & 0x03030303u) << 4);
+        vl.w = (ql.w & 0x0F0F0F0Fu) | (((qh.w >> shift) & 0x03030303u) << 4);
+        vh.x = ((ql.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> (shift + 4)) & 0x03030303u) << 4);
+        vh.y = ((ql.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (shift + 4)) & 0x03030303u) << 4);
+        vh.z = ((ql.z >> 4) & 0x0F0F0F0Fu) | (((qh.z >> (shift + 4)) & 0x03030303u) << 4);
+        vh.w = ((ql.w >> 4) & 0x0F0F0F0Fu) | (((qh.w >> (shift + 4)) & 0x03030303u) << 4);
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256;
+            const int4 ua = *(const int4*)(q8 + 16 * g_lo), ub = *(const int4*)(q8 + 16 * g_hi);
+            const float d8lo = sm.d[b * sm.nb32 + sbs * 8 + (g_lo >> 1)], d8hi = sm.d[b * sm.nb32 + sbs * 8 + (g_hi >> 1)];
+            const int* b16 = sm.b16 + b * (sm.cols >> 4) + sbs * 16;
+            // codes are stored +32: sum((c - 32) * u) = sum(c * u) - 32 * sum(u)
+            const int il = dp4a4(vl, ua) - 32 * b16[g_lo];
+            const int ih = dp4a4(vh, ub) - 32 * b16[g_hi];
+            acc[b] += f_lo * d8lo * (float)il + f_hi * d8hi * (float)ih;
+            if (DUMP && b == 0 && live && row_ok) {
+                int32_t* o = a.isums + (size_t)row * (sm.cols >> 4) + sb * 16;
+                o[g_lo] = il;
+                o[g_hi] = ih;
+            }
+        }
+    }
+};
+
+template <> struct Piece<FK_MXFP4> {
+    uint4 wq;
+    uint32_t e;
+    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 5) + 31) >> 5; }
+    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+        const int kb = trip * 32 + lane;
+        wq = make_uint4(0, 0, 0, 0);
+        e = 0xFFFFFFFFu;
+        if (row_ok && kb < (a.cols >> 5)) {
+            wq = ldg16(wb + a.plane_off[0] + (size_t)row * (a.cols >> 1) + (size_t)kb * 16);
+            e = __ldg(wb + a.plane_off[1] + (size_t)row * (a.cols >> 5) + kb);
+        }
+    }
+    template <int NB, bool DUMP>
+    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
+        const int kb = trip * 32 + lane;
+        const bool live = kb < sm.nb32;
+        const int ks = live ? kb : 0;
+        const float dw = e == 0xFFFFFFFFu ? 0.0f : e8m0_half(e);
+        uint4 va, vb;
+        va.x = e2m1x2_4(wq.x); va.y = e2m1x2_4(wq.x >> 16);
+        va.z = e2m1x2_4(wq.y); va.w = e2m1x2_4(wq.y >> 16);
+        vb.x = e2m1x2_4(wq.z); vb.y = e2m1x2_4(wq.z >> 16);
+        vb.z = e2m1x2_4(wq.w); vb.w = e2m1x2_4(wq.w >> 16);
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int8_t* q8 = sm.q + (size_t)b * sm.cols + ks * 32;
+            const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 16);
+            const int is = dp4a4(va, ua) + dp4a4(vb, ub);
+            acc[b] += dw * sm.d[b * sm.nb32 + ks] * (float)is;
+            if (DUMP && b == 0 && live && row_ok) a.isums[(size_t)row * sm.nb32 + kb] = is;
+        }
+    }
+};
+
+// U = trips whose loads a lane issues back to back before it consumes any.
+template <int KIND, int NB, bool DUMP, int U>
 __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int cols = a.cols, rows = a.rows;
@@ -89,6 +288,20 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
     const float* x = a.x + (size_t)slot * a.x_stride;
     float* y = a.y + (size_t)slot * a.batch * rows;
+
+    const int gwarp = blockIdx.x * GEMV_WARPS + warp;
+    const int twarps = gridDim.x * GEMV_WARPS;
+    const int ntrips = Piece<KIND>::trips(cols);
+
+    // The first batch of weight loads goes out before the activations are
+    // touched, so HBM latency overlaps the quantization.
+    Piece<KIND> pc[U][R];
+    int rp = gwarp;
+#pragma unroll
+    for (int u = 0; u < U; u++)
+#pragma unroll
+        for (int r = 0; r < R; r++)
+            pc[u][r].load(a, wb, rp * R + r, u, lane, rp * R + r < rows && u < ntrips);
 
     // ---- activations -> q8_1 in shared memory
     for (int run = warp; run < NB * nb32; run += GEMV_WARPS) {
@@ -114,11 +327,9 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
         }
     }
     __syncthreads();
+    Smem sm{sq, sd, ss, sb16, cols, nb32};
 
-    const int gwarp = blockIdx.x * GEMV_WARPS + warp;
-    const int twarps = gridDim.x * GEMV_WARPS;
-
-    for (int rp = gwarp; rp * R < rows; rp += twarps) {
+    for (; rp * R < rows; rp += twarps) {
         const int row0 = rp * R;
         float acc[R][NB];
 #pragma unroll
@@ -126,194 +337,20 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
 #pragma unroll
             for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
 
-        if (KIND == FK_Q4_K) {
-            const int nsb = cols >> 8;
-            const size_t row_bytes = (size_t)nsb * 144;
-            const int c = lane & 7, g = c >> 1, h = c & 1;
-            for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
-                const int sb = sb0 + (lane >> 3);
-                const bool live = sb < nsb;
-                const int sbs = live ? sb : 0;
-                uint4 wq[R];
-                float f_lo[R], f_hi[R], mm_lo[R], mm_hi[R];
+        for (int t0 = 0; t0 < ntrips; t0 += U) {
+            if (t0 > 0 || rp != gwarp) {
 #pragma unroll
-                for (int r = 0; r < R; r++) {
-                    uint4 hd = make_uint4(0, 0, 0, 0);
-                    wq[r] = make_uint4(0, 0, 0, 0);
-                    if (live && row0 + r < rows) {
-                        const uint8_t* p = wb + (size_t)(row0 + r) * row_bytes + (size_t)sb * 144;
-                        hd = ldg16(p);
-                        wq[r] = ldg16(p + 16 + 16 * c);
-                    }
-                    const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF)), dmin = fk_h2f((uint16_t)(hd.x >> 16));
-                    int sc0, m0, sc1, m1;
-                    q4k_scale_min(hd.y, hd.z, hd.w, 2 * g, &sc0, &m0);
-                    q4k_scale_min(hd.y, hd.z, hd.w, 2 * g + 1, &sc1, &m1);
-                    f_lo[r] = d * (float)sc0;
-                    f_hi[r] = d * (float)sc1;
-                    // the two lanes sharing a sub-block (h = 0, 1) each carry half its min term
-                    mm_lo[r] = 0.5f * dmin * (float)m0;
-                    mm_hi[r] = 0.5f * dmin * (float)m1;
-                }
+                for (int u = 0; u < U; u++)
 #pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const int8_t* q8 = sq + (size_t)b * cols + sbs * 256 + 64 * g + 16 * h;
-                    const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 32);
-                    const float2 d8 = *(const float2*)(sd + b * nb32 + sbs * 8 + 2 * g);
-                    const float2 s8 = *(const float2*)(ss + b * nb32 + sbs * 8 + 2 * g);
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        uint4 lo, hi;
-                        lo.x = wq[r].x & 0x0F0F0F0Fu; hi.x = (wq[r].x >> 4) & 0x0F0F0F0Fu;
-                        lo.y = wq[r].y & 0x0F0F0F0Fu; hi.y = (wq[r].y >> 4) & 0x0F0F0F0Fu;
-                        lo.z = wq[r].z & 0x0F0F0F0Fu; hi.z = (wq[r].z >> 4) & 0x0F0F0F0Fu;
-                        lo.w = wq[r].w & 0x0F0F0F0Fu; hi.w = (wq[r].w >> 4) & 0x0F0F0F0Fu;
-                        int il = dp4a4(lo, ua), ih = dp4a4(hi, ub);
-                        acc[r][b] += f_lo[r] * d8.x * (float)il + f_hi[r] * d8.y * (float)ih -
-                                     (mm_lo[r] * s8.x + mm_hi[r] * s8.y);
-                        if (DUMP && b == 0) {
-                            il += __shfl_xor_sync(0xffffffffu, il, 1);
-                            ih += __shfl_xor_sync(0xffffffffu, ih, 1);
-                            if (live && h == 0 && row0 + r < rows) {
-                                int32_t* o = a.isums + (size_t)(row0 + r) * nb32 + sb * 8 + 2 * g;
-                                o[0] = il;
-                                o[1] = ih;
-                            }
-                        }
-                    }
-                }
+                    for (int r = 0; r < R; r++)
+                        pc[u][r].load(a, wb, row0 + r, t0 + u, lane, row0 + r < rows && t0 + u < ntrips);
             }
-        } else if (KIND == FK_Q8_0) {
-            const uint8_t* qsp = wb + a.plane_off[0];
-            const uint16_t* dp = (const uint16_t*)(wb + a.plane_off[1]);
-            const int nchunk = cols >> 4;
-            for (int c0 = 0; c0 < nchunk; c0 += 32) {
-                const int ci = c0 + lane;
-                const bool live = ci < nchunk;
-                const int cs = live ? ci : 0;
-                uint4 wq[R];
-                float dw[R];
 #pragma unroll
-                for (int r = 0; r < R; r++) {
-                    wq[r] = make_uint4(0, 0, 0, 0);
-                    dw[r] = 0.0f;
-                    if (live && row0 + r < rows) {
-                        wq[r] = ldg16(qsp + (size_t)(row0 + r) * cols + (size_t)ci * 16);
-                        dw[r] = fk_h2f(__ldg(dp + (size_t)(row0 + r) * nb32 + (ci >> 1)));
-                    }
-                }
+            for (int u = 0; u < U; u++)
 #pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const int4 ua = *(const int4*)(sq + (size_t)b * cols + cs * 16);
-                    const float d8 = sd[b * nb32 + (cs >> 1)];
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        int is = dp4a4(wq[r], ua);
-                        acc[r][b] += dw[r] * d8 * (float)is;
-                        if (DUMP && b == 0) {
-                            is += __shfl_xor_sync(0xffffffffu, is, 1);
-                            if (live && !(lane & 1) && row0 + r < rows)
-                                a.isums[(size_t)(row0 + r) * nb32 + (ci >> 1)] = is;
-                        }
-                    }
-                }
-            }
-        } else if (KIND == FK_Q6_K) {
-            const uint8_t* qlp = wb + a.plane_off[0];
-            const uint8_t* qhp = wb + a.plane_off[1];
-            const int8_t* scp = (const int8_t*)(wb + a.plane_off[2]);
-            const uint16_t* dp = (const uint16_t*)(wb + a.plane_off[3]);
-            const int nsb = cols >> 8;
-            const int c = lane & 7, hf = c >> 2, q = c & 3;
-            const int g_lo = 8 * hf + q, g_hi = g_lo + 4;
-            const int shift = 2 * (q >> 1);
-            for (int sb0 = 0; sb0 < nsb; sb0 += 4) {
-                const int sb = sb0 + (lane >> 3);
-                const bool live = sb < nsb;
-                const int sbs = live ? sb : 0;
-                uint4 vl[R], vh[R];
-                float f_lo[R], f_hi[R];
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    uint4 ql = make_uint4(0, 0, 0, 0), qh = ql;
-                    f_lo[r] = 0.0f;
-                    f_hi[r] = 0.0f;
-                    if (live && row0 + r < rows) {
-                        const size_t row = (size_t)(row0 + r);
-                        ql = ldg16(qlp + row * (cols >> 1) + (size_t)sb * 128 + 16 * c);
-                        qh = ldg16(qhp + row * (cols >> 2) + (size_t)sb * 64 + 32 * hf + 16 * (q & 1));
-                        const int8_t* sc = scp + row * (cols >> 4) + sb * 16;
-                        const float d = fk_h2f(__ldg(dp + row * nsb + sb));
-                        f_lo[r] = d * (float)__ldg(sc + g_lo);
-                        f_hi[r] = d * (float)__ldg(sc + g_hi);
-                    }
-                    vl[r].x = (ql.x & 0x0F0F0F0Fu) | (((qh.x >> shift) & 0x03030303u) << 4);
-                    vl[r].y = (ql.y & 0x0F0F0F0Fu) | (((qh.y >> shift) & 0x03030303u) << 4);
-                    vl[r].z = (ql.z & 0x0F0F0F0Fu) | (((qh.z >> shift) & 0x03030303u) << 4);
-                    vl[r].w = (ql.w & 0x0F0F0F0Fu) | (((qh.w >> shift) & 0x03030303u) << 4);
-                    vh[r].x = ((ql.x >> 4) & 0x0F0F0F0Fu) | (((qh.x >> (shift + 4)) & 0x03030303u) << 4);
-                    vh[r].y = ((ql.y >> 4) & 0x0F0F0F0Fu) | (((qh.y >> (shift + 4)) & 0x03030303u) << 4);
-                    vh[r].z = ((ql.z >> 4) & 0x0F0F0F0Fu) | (((qh.z >> (shift + 4)) & 0x03030303u) << 4);
-                    vh[r].w = ((ql.w >> 4) & 0x0F0F0F0Fu) | (((qh.w >> (shift + 4)) & 0x03030303u) << 4);
-                }
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const int8_t* q8 = sq + (size_t)b * cols + sbs * 256;
-                    const int4 ua = *(const int4*)(q8 + 16 * g_lo), ub = *(const int4*)(q8 + 16 * g_hi);
-                    const float d8lo = sd[b * nb32 + sbs * 8 + (g_lo >> 1)], d8hi = sd[b * nb32 + sbs * 8 + (g_hi >> 1)];
-                    const int s_lo = sb16[b * (cols >> 4) + sbs * 16 + g_lo], s_hi = sb16[b * (cols >> 4) + sbs * 16 + g_hi];
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        // codes are stored +32: sum((c - 32) * u) = sum(c * u) - 32 * sum(u)
-                        const int il = dp4a4(vl[r], ua) - 32 * s_lo;
-                        const int ih = dp4a4(vh[r], ub) - 32 * s_hi;
-                        acc[r][b] += f_lo[r] * d8lo * (float)il + f_hi[r] * d8hi * (float)ih;
-                        if (DUMP && b == 0 && live && row0 + r < rows) {
-                            int32_t* o = a.isums + (size_t)(row0 + r) * (cols >> 4) + sb * 16;
-                            o[g_lo] = il;
-                            o[g_hi] = ih;
-                        }
-                    }
-                }
-            }
-        } else {  // FK_MXFP4
-            const uint8_t* cp = wb + a.plane_off[0];
-            const uint8_t* ep = wb + a.plane_off[1];
-            for (int k0 = 0; k0 < nb32; k0 += 32) {
-                const int kb = k0 + lane;
-                const bool live = kb < nb32;
-                const int ks = live ? kb : 0;
-                uint4 va[R], vb[R];
-                float dw[R];
-#pragma unroll
-                for (int r = 0; r < R; r++) {
-                    uint4 wq = make_uint4(0, 0, 0, 0);
-                    dw[r] = 0.0f;
-                    if (live && row0 + r < rows) {
-                        wq = ldg16(cp + (size_t)(row0 + r) * (cols >> 1) + (size_t)kb * 16);
-                        dw[r] = e8m0_half(__ldg(ep + (size_t)(row0 + r) * nb32 + kb));
-                    }
-                    va[r].x = e2m1x2_4(wq.x); va[r].y = e2m1x2_4(wq.x >> 16);
-                    va[r].z = e2m1x2_4(wq.y); va[r].w = e2m1x2_4(wq.y >> 16);
-                    vb[r].x = e2m1x2_4(wq.z); vb[r].y = e2m1x2_4(wq.z >> 16);
-                    vb[r].z = e2m1x2_4(wq.w); vb[r].w = e2m1x2_4(wq.w >> 16);
-                }
-#pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const int8_t* q8 = sq + (size_t)b * cols + ks * 32;
-                    const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 16);
-                    const float d8 = sd[b * nb32 + ks];
-#pragma unroll
-                    for (int r = 0; r < R; r++) {
-                        const int is = dp4a4(va[r], ua) + dp4a4(vb[r], ub);
-                        acc[r][b] += dw[r] * d8 * (float)is;
-                        if (DUMP && b == 0 && live && row0 + r < rows)
-                            a.isums[(size_t)(row0 + r) * nb32 + kb] = is;
-                    }
-                }
-            }
+                for (int r = 0; r < R; r++)
+                    pc[u][r].template eat<NB, DUMP>(a, sm, row0 + r, t0 + u, lane, row0 + r < rows && t0 + u < ntrips, acc[r]);
         }
-
 #pragma unroll
         for (int r = 0; r < R; r++)
 #pragma unroll
@@ -335,11 +372,16 @@ template <int KIND, int NB, bool DUMP>
 int launch_one(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, int slots) {
     const size_t smem = gemv_smem_bytes(KIND, NB, a.cols);
     if (smem > 220 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv: %d columns x batch %d needs %zu B of shared memory", a.cols, NB, smem);
-    auto kern = gemv_kernel<KIND, NB, DUMP>;
+    constexpr int U = NB <= 2 ? 3 : (NB <= 4 ? 2 : 1);
+    auto kern = gemv_kernel<KIND, NB, DUMP, U>;
     if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
     const int pairs = (a.rows + R - 1) / R;
     const int need = (pairs + GEMV_WARPS - 1) / GEMV_WARPS;
-    int per_slot = (2 * ctx->sm_count + slots - 1) / slots;
+    // a persistent grid: as many blocks as are resident at once, no second wave
+    int occ = 0;
+    FK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem), FK_KERNEL);
+    if (occ < 1) occ = 1;
+    int per_slot = (occ * ctx->sm_count + slots - 1) / slots;
     if (per_slot < 1) per_slot = 1;
     dim3 grid((unsigned)(need < per_slot ? need : per_slot), (unsigned)slots);
     kern<<<grid, GEMV_THREADS, smem, st>>>(a);
