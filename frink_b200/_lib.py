@@ -20,6 +20,7 @@ SYMBOLS = {
     "fk_last_error": (C.c_char_p, []),
     "fk_device_info": (_I, [_P, C.c_char_p, _SZ, C.POINTER(_I), C.POINTER(_SZ)]),
     "fk_counters": (_I, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), _I]),
+    "fk_device_error": (_I, [_P, C.POINTER(_I), _I]),
     "fk_block_bytes": (_I, [_I]),
     "fk_block_elems": (_I, [_I]),
     "fk_register_weights": (_I, [_P, _P, _SZ, _I, _I, _I, _I, C.POINTER(_P)]),

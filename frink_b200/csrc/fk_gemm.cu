@@ -1,12 +1,666 @@
-// Prefill GEMM (placeholder while the tcgen05 kernel is brought up).
+// Prefill GEMM over resident quantized weights: int8 tensor-core MMA
+// (tcgen05.mma kind::i8, accumulators in tensor memory) on q8_1 activations,
+// with the exact per-32-run rescale done by the epilogue warps.
+//
+//   out[t][r] = sum_kb  dw[r][kb] * dx[t][kb] * ( sum_{k in kb} wq[r][k] * xq[t][k] )   (- Q4_K min term)
+//
+// The inner sum is an exact int32 (one MMA of K = 32 per run kb), so every
+// integer this kernel produces equals the GEMV's and the oracle's.  Because the
+// weight scale and the activation scale both change every 32 K, an accumulator
+// is drained from tensor memory after every K = 32 step and scaled on the CUDA
+// cores; that rescale, not the tensor pipe, bounds this kernel.
+//
+// One CTA = 128 weight rows x BN tokens, 14 warps with fixed roles:
+//   warps 0-7   epilogue: TMEM -> registers (tcgen05.ld), f32 rescale, store
+//   warps 8-11  unpack: packed weights (global) -> int8 tile in shared memory
+//               (128-byte swizzle, the layout the MMA descriptor names)
+//   warp 12     TMA producer: activation int8 tile + its scale tiles (and the
+//               weight tile itself for Q8_0, whose int8 plane needs no unpacking)
+//   warp 13     MMA issuer (one elected lane) + TMEM allocation
+// Stages (K = 128 each) and TMEM accumulators are rings guarded by mbarriers;
+// every wait is bounded and raises the context's error word instead of
+// spinning forever.
 #include "fk_common.cuh"
 
-FK_EXPORT int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev) {
-    (void)ctx; (void)stream; (void)w; (void)mat; (void)x_dev; (void)m; (void)out_dev;
-    return fk_fail(FK_UNSUPPORTED, "gemm: not built yet");
+#include <cuda.h>
+
+namespace {
+
+constexpr int BM = 128;           // weight rows per CTA (MMA M)
+constexpr int KSTAGE = 128;       // K per pipeline stage (4 MMAs of K = 32)
+constexpr int NSTAGE = 4;
+constexpr int EPI_WARPS = 8, UNPACK_WARPS = 4;
+constexpr int GEMM_THREADS = (EPI_WARPS + UNPACK_WARPS + 2) * 32;  // 448
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+struct GemmArgs {
+    const uint8_t* w;         // matrix 0 of the weight handle
+    size_t mat_stride;
+    size_t plane_off[4];
+    int kind, rows, cols;
+    int mat;                  // dense: the matrix; grouped: ignored
+    const int* tile_expert;   // grouped: expert of each token tile (nullptr = dense)
+    const int* n_tiles_dev;   // grouped: number of live token tiles (nullptr = all of gridDim.y)
+    const int* out_row;       // padded token row -> output row, -1 = padding
+    float* out;
+    int* err;
+};
+
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after WAIT_LIMIT polls, records where, and lets the
+// caller run on (its results are then garbage, the host sees the error word).
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return;
+    atomicCAS(err, 0, code);
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    // the predicate is "accumulate onto D": always false here, every run starts a fresh accumulator
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024
+// bytes apart: start address, LBO = 16 B (unused by this layout), SBO = 1024 B,
+// descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// kind::i8: D = s32 (2 at bit 4), A and B signed 8-bit (1 at bits 7 and 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
+    uint32_t pos, neg, out;
+    const uint32_t sel = w & 0x7777u;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pos) : "r"(0x03020100u), "r"(0x0C080604u), "r"(sel));
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(0xFDFEFF00u), "r"(0xF4F8FAFCu), "r"(sel));
+    const uint32_t pick = 0x3210u | ((w & 0x8888u) >> 1);
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(pos), "r"(neg), "r"(pick));
+    return out;
+}
+__device__ __forceinline__ float e8m0_half(uint32_t e) {
+    return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
+}
+
+// Shared memory map (offsets from a 1024-byte aligned base).
+template <int BN> struct Smem {
+    static constexpr int A_BYTES = BM * KSTAGE;          // 16 KB
+    static constexpr int B_BYTES = BN * KSTAGE;
+    static constexpr int DX_BYTES = 4 * BN * 4;          // [4 runs][BN] f32
+    static constexpr int STAGE = A_BYTES + B_BYTES + 2 * DX_BYTES;
+    static constexpr int BARS = NSTAGE * STAGE;          // barrier block
+    static constexpr int TOTAL = BARS + 256 + 1024;      // + alignment slack
+    static constexpr int NACC = 512 / BN;                // TMEM accumulator ring
+};
+
+// Weight scale of row `row`, run `kb`; Q4_K also the min scale.  Q6_K rows are
+// (weight row, half-run) pairs, see the unpack warps.
+struct WScale { float dw, mw; };
+
+template <int KIND>
+__device__ __forceinline__ void load_wscales(const GemmArgs& a, const uint8_t* wb, int row, bool row_ok, int kb0, int nkb, WScale* ws) {
+    // scales of runs kb0 .. kb0+3 of this thread's row
+#pragma unroll
+    for (int j = 0; j < 4; j++) ws[j] = {0.0f, 0.0f};
+    if (!row_ok) return;
+    if (KIND == FK_Q4_K) {
+        const int sb = kb0 >> 3;
+        const uint4 hd = ldg16(wb + ((size_t)row * (a.cols >> 8) + sb) * 144);
+        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF)), dmin = fk_h2f((uint16_t)(hd.x >> 16));
+        const uint32_t s[3] = {hd.y, hd.z, hd.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int q = (kb0 & 7) + j;  // sub-block 0..7
+            uint32_t sc, m;
+            if (q < 4) {
+                sc = (s[0] >> (8 * q)) & 63;
+                m = (s[1] >> (8 * q)) & 63;
+            } else {
+                const uint32_t b = (s[2] >> (8 * (q - 4))) & 0xFF;
+                sc = (b & 0x0F) | ((((s[0] >> (8 * (q - 4))) & 0xFF) >> 6) << 4);
+                m = (b >> 4) | ((((s[1] >> (8 * (q - 4))) & 0xFF) >> 6) << 4);
+            }
+            if (kb0 + j < nkb) ws[j] = {d * (float)sc, dmin * (float)m};
+        }
+    } else if (KIND == FK_Q8_0) {
+        const uint16_t* dp = (const uint16_t*)(wb + a.plane_off[1]) + (size_t)row * (a.cols >> 5);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (kb0 + j < nkb) ws[j].dw = fk_h2f(__ldg(dp + kb0 + j));
+    } else if (KIND == FK_MXFP4) {
+        const uint8_t* ep = wb + a.plane_off[1] + (size_t)row * (a.cols >> 5);
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (kb0 + j < nkb) ws[j].dw = e8m0_half(__ldg(ep + kb0 + j));
+    } else {  // FK_Q6_K: `row` = 2 * weight row + half; its scale of run kb is sc[2 * kb + half]
+        const int wrow = row >> 1, half = row & 1;
+        const int sb = kb0 >> 3;
+        const float d = fk_h2f(__ldg((const uint16_t*)(wb + a.plane_off[3]) + (size_t)wrow * (a.cols >> 8) + sb));
+        const int8_t* sc = (const int8_t*)(wb + a.plane_off[2]) + (size_t)wrow * (a.cols >> 4) + 2 * kb0 + half;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (kb0 + j < nkb) ws[j].dw = d * (float)__ldg(sc + 2 * j);
+    }
+}
+
+// One thread = one tile row: its 128 int8 of stage `st` (K range [128 st, 128 st + 128))
+// written as eight 16-byte chunks at their swizzled places.
+template <int KIND>
+__device__ __forceinline__ void unpack_row(const GemmArgs& a, const uint8_t* wb, int r, int row, bool row_ok, int st, uint8_t* a_tile) {
+    uint4 o[8];
+#pragma unroll
+    for (int c = 0; c < 8; c++) o[c] = make_uint4(0, 0, 0, 0);
+    const int k0 = st * KSTAGE;
+    if (row_ok && k0 < a.cols) {
+        if (KIND == FK_Q4_K) {
+            // 128 weights = 64 quant bytes: two groups of 32 bytes; low nibbles are
+            // the first 32 weights of a group, high nibbles the next 32
+            const uint8_t* p = wb + ((size_t)row * (a.cols >> 8) + (k0 >> 8)) * 144 + 16 + ((k0 >> 7) & 1) * 64;
+#pragma unroll
+            for (int g = 0; g < 2; g++) {
+                const uint4 q0 = ldg16(p + 32 * g), q1 = ldg16(p + 32 * g + 16);
+                o[4 * g + 0] = make_uint4(q0.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q0.z & 0x0F0F0F0Fu, q0.w & 0x0F0F0F0Fu);
+                o[4 * g + 1] = make_uint4(q1.x & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, q1.z & 0x0F0F0F0Fu, q1.w & 0x0F0F0F0Fu);
+                o[4 * g + 2] = make_uint4((q0.x >> 4) & 0x0F0F0F0Fu, (q0.y >> 4) & 0x0F0F0F0Fu, (q0.z >> 4) & 0x0F0F0F0Fu, (q0.w >> 4) & 0x0F0F0F0Fu);
+                o[4 * g + 3] = make_uint4((q1.x >> 4) & 0x0F0F0F0Fu, (q1.y >> 4) & 0x0F0F0F0Fu, (q1.z >> 4) & 0x0F0F0F0Fu, (q1.w >> 4) & 0x0F0F0F0Fu);
+            }
+        } else if (KIND == FK_MXFP4) {
+            // 4 blocks of 16 code bytes; bytes come out as (elem j, elem j+16) pairs,
+            // the order the activation plane of this kind is stored in
+            const uint8_t* p = wb + a.plane_off[0] + (size_t)row * (a.cols >> 1) + (k0 >> 1);
+#pragma unroll
+            for (int b = 0; b < 4; b++) {
+                if (k0 + 32 * b < a.cols) {
+                    const uint4 q = ldg16(p + 16 * b);
+                    o[2 * b] = make_uint4(e2m1x2_4(q.x), e2m1x2_4(q.x >> 16), e2m1x2_4(q.y), e2m1x2_4(q.y >> 16));
+                    o[2 * b + 1] = make_uint4(e2m1x2_4(q.z), e2m1x2_4(q.z >> 16), e2m1x2_4(q.w), e2m1x2_4(q.w >> 16));
+                }
+            }
+        } else if (KIND == FK_Q6_K) {
+            // tile row = (weight row, half): the 6-bit codes minus 32 of this K range,
+            // with the 16 weights of the OTHER half of every run of 32 zeroed, so
+            // that one K = 32 MMA yields the exact dot of a 16-weight scale group
+            const int wrow = row >> 1, half = row & 1;
+            const int sb = k0 >> 8, hf = (k0 >> 7) & 1;
+            const uint8_t* ql = wb + a.plane_off[0] + (size_t)wrow * (a.cols >> 1) + (size_t)sb * 128 + 64 * hf;
+            const uint8_t* qh = wb + a.plane_off[1] + (size_t)wrow * (a.cols >> 2) + (size_t)sb * 64 + 32 * hf;
+            const uint4 h0 = ldg16(qh), h1 = ldg16(qh + 16);
+            const uint32_t hh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+            // element e = 32 * qd + l (qd = 0..3, l = 0..31): ql byte (l + 32 * (qd & 1)),
+            // nibble (qd >> 1), qh byte l bits [2 qd, 2 qd + 2)
+#pragma unroll
+            for (int qd = 0; qd < 4; qd++) {
+                const uint4 l0 = ldg16(ql + 32 * (qd & 1)), l1 = ldg16(ql + 32 * (qd & 1) + 16);
+                const uint32_t ll[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+                uint32_t v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const uint32_t nib = (qd >> 1) ? ((ll[i] >> 4) & 0x0F0F0F0Fu) : (ll[i] & 0x0F0F0F0Fu);
+                    const uint32_t c6 = nib | (((hh[i] >> (2 * qd)) & 0x03030303u) << 4);
+                    v[i] = __vsub4(c6, 0x20202020u);
+                }
+                // run of 32 = chunks (2 qd, 2 qd + 1): keep this row's half
+                o[2 * qd + half] = make_uint4(v[4 * half], v[4 * half + 1], v[4 * half + 2], v[4 * half + 3]);
+            }
+        }
+    }
+    if (KIND != FK_Q8_0) {
+        uint8_t* dst = a_tile + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; c++) *(uint4*)(dst + ((c ^ (r & 7)) << 4)) = o[c];
+    }
+}
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_dx,
+            const __grid_constant__ CUtensorMap map_sx, const __grid_constant__ CUtensorMap map_w) {
+    using S = Smem<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32(smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int ttile = blockIdx.y;
+    if (a.n_tiles_dev && ttile >= *a.n_tiles_dev) return;
+    const int mat = a.tile_expert ? a.tile_expert[ttile] : a.mat;
+    const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
+    // Q6_K tile rows are (weight row, half) pairs: 64 weight rows per CTA
+    constexpr int WROWS = KIND == FK_Q6_K ? BM / 2 : BM;
+    const int wrow0 = blockIdx.x * WROWS;
+    const int tok0 = ttile * BN;
+    const int nkb = a.cols >> 5;
+    const int nst = (nkb + 3) >> 2;
+
+    // barriers: full_b[NSTAGE], full_a[NSTAGE], empty[NSTAGE], acc_full[NACC], acc_empty[NACC], then the TMEM base word
+    const uint32_t bar0 = sbase + S::BARS;
+    auto full_b = [&](int s) { return bar0 + 8u * s; };
+    auto full_a = [&](int s) { return bar0 + 8u * (NSTAGE + s); };
+    auto empty = [&](int s) { return bar0 + 8u * (2 * NSTAGE + s); };
+    auto acc_full = [&](int b) { return bar0 + 8u * (3 * NSTAGE + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8u * (3 * NSTAGE + S::NACC + b); };
+    uint32_t* tmem_word = (uint32_t*)(smem + S::BARS + 8 * (3 * NSTAGE + 2 * S::NACC));
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; s++) {
+            mbar_init(full_b(s), 1);
+            mbar_init(full_a(s), UNPACK_WARPS);
+            mbar_init(empty(s), 1 + EPI_WARPS);
+        }
+        for (int b = 0; b < S::NACC; b++) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), EPI_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == EPI_WARPS + UNPACK_WARPS + 1) {  // the MMA warp owns tensor memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_word)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_word;
+
+    if (warp < EPI_WARPS) {
+        // ------------------------------------------------------------ epilogue
+        const int quad = warp & 3, chalf = warp >> 2;
+        const int r = quad * 32 + lane;                // tile row = TMEM lane
+        const int row = KIND == FK_Q6_K ? 2 * wrow0 + r : wrow0 + r;   // scale row id (pair id for Q6_K)
+        const bool row_ok = (KIND == FK_Q6_K ? (wrow0 + (r >> 1)) : (wrow0 + r)) < a.rows;
+        constexpr int CW = BN / 2;                     // columns this warp owns
+        float acc[CW];
+#pragma unroll
+        for (int i = 0; i < CW; i++) acc[i] = 0.0f;
+        const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * CW;
+        WScale ws[4], ws_next[4];
+        load_wscales<KIND>(a, wb, row, row_ok, 0, nkb, ws_next);
+        for (int st = 0; st < nst; st++) {
+            const int s = st % NSTAGE;
+#pragma unroll
+            for (int j = 0; j < 4; j++) ws[j] = ws_next[j];
+            if (st + 1 < nst) load_wscales<KIND>(a, wb, row, row_ok, 4 * (st + 1), nkb, ws_next);
+            mbar_wait(full_b(s), (st / NSTAGE) & 1, a.err, 10);   // the scale tiles of this stage have landed
+            const float* sdx = (const float*)(smem + s * S::STAGE + S::A_BYTES + S::B_BYTES);
+            const float* ssx = sdx + 4 * BN;
+#pragma unroll 1
+            for (int j = 0; j < 4; j++) {
+                const int kb = 4 * st + j;
+                if (kb >= nkb) break;
+                const int buf = kb % S::NACC;
+                mbar_wait(acc_full(buf), (kb / S::NACC) & 1, a.err, 11);
+                tc_fence_after();
+                const float dw = ws[j].dw, mw = ws[j].mw;
+#pragma unroll
+                for (int c0 = 0; c0 < CW; c0 += 32) {
+                    uint32_t v[32];
+                    tc_ld32(taddr0 + buf * BN + c0, v);
+                    tc_wait_ld();
+                    if (c0 + 32 >= CW) {  // last read of this accumulator: hand it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(buf));
+                    }
+                    const float* dxp = sdx + j * BN + chalf * CW + c0;
+                    const float* sxp = ssx + j * BN + chalf * CW + c0;
+#pragma unroll
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 dx = *(const float4*)(dxp + i);
+                        const float dxa[4] = {dx.x, dx.y, dx.z, dx.w};
+                        float sxa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (KIND == FK_Q4_K) {
+                            const float4 sx = *(const float4*)(sxp + i);
+                            sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
+                        }
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
+                            const float f = __int_as_float((int)v[i + e] + 0x4B400000) - 12582912.0f;
+                            float t = acc[c0 + i + e] + (dw * dxa[e]) * f;
+                            if (KIND == FK_Q4_K) t -= mw * sxa[e];
+                            acc[c0 + i + e] = t;
+                        }
+                    }
+                }
+            }
+            // this warp is done with the stage's scale tiles
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));
+        }
+        // ---- store: out[out_row[token]][weight row]
+        if (KIND == FK_Q6_K) {
+#pragma unroll
+            for (int i = 0; i < CW; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
+        }
+        const int orow = KIND == FK_Q6_K ? wrow0 + (r >> 1) : wrow0 + r;
+        const bool writer = row_ok && (KIND != FK_Q6_K || !(r & 1));
+#pragma unroll 4
+        for (int i = 0; i < CW; i++) {
+            const int dst = a.out_row[tok0 + chalf * CW + i];
+            if (writer && dst >= 0) a.out[(size_t)dst * a.rows + orow] = acc[i];
+        }
+    } else if (warp < EPI_WARPS + UNPACK_WARPS) {
+        // ------------------------------------------------- weight unpack warps
+        if (KIND != FK_Q8_0) {
+            const int r = (warp - EPI_WARPS) * 32 + lane;
+            const int row = KIND == FK_Q6_K ? 2 * wrow0 + r : wrow0 + r;
+            const bool row_ok = (KIND == FK_Q6_K ? (wrow0 + (r >> 1)) : (wrow0 + r)) < a.rows;
+            for (int st = 0; st < nst; st++) {
+                const int s = st % NSTAGE;
+                if (st >= NSTAGE) mbar_wait(empty(s), ((st / NSTAGE) - 1) & 1, a.err, 20);
+                unpack_row<KIND>(a, wb, r, row, row_ok, st, smem + s * S::STAGE);
+                fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full_a(s));
+            }
+        }
+    } else if (warp == EPI_WARPS + UNPACK_WARPS) {
+        // --------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            constexpr uint32_t TX = S::B_BYTES + S::DX_BYTES + (KIND == FK_Q4_K ? S::DX_BYTES : 0) + (KIND == FK_Q8_0 ? S::A_BYTES : 0);
+            for (int st = 0; st < nst; st++) {
+                const int s = st % NSTAGE;
+                if (st >= NSTAGE) mbar_wait(empty(s), ((st / NSTAGE) - 1) & 1, a.err, 30);
+                const uint32_t sa = sbase + s * S::STAGE;
+                mbar_expect_tx(full_b(s), TX);
+                tma_load_2d(sa + S::A_BYTES, &map_q, st * KSTAGE, tok0, full_b(s));
+                tma_load_2d(sa + S::A_BYTES + S::B_BYTES, &map_dx, tok0, 4 * st, full_b(s));
+                if (KIND == FK_Q4_K) tma_load_2d(sa + S::A_BYTES + S::B_BYTES + S::DX_BYTES, &map_sx, tok0, 4 * st, full_b(s));
+                if (KIND == FK_Q8_0) tma_load_2d(sa, &map_w, st * KSTAGE, wrow0, full_b(s));
+            }
+        }
+    } else {
+        // ----------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t IDESC = umma_idesc_i8(BM, BN);
+            for (int st = 0; st < nst; st++) {
+                const int s = st % NSTAGE;
+                mbar_wait(full_b(s), (st / NSTAGE) & 1, a.err, 40);
+                if (KIND != FK_Q8_0) mbar_wait(full_a(s), (st / NSTAGE) & 1, a.err, 41);
+                tc_fence_after();
+                const uint32_t sa = sbase + s * S::STAGE;
+                const uint64_t da = umma_desc(sa), db = umma_desc(sa + S::A_BYTES);
+                for (int j = 0; j < 4; j++) {
+                    const int kb = 4 * st + j;
+                    if (kb >= nkb) break;
+                    const int buf = kb % S::NACC;
+                    if (kb >= S::NACC) mbar_wait(acc_empty(buf), ((kb / S::NACC) - 1) & 1, a.err, 42);
+                    tc_fence_after();
+                    // K advances 32 bytes inside the 128-byte swizzle atom: +2 in the 16-byte address field
+                    tc_mma_i8(tmem_base + buf * BN, da + 2 * j, db + 2 * j, IDESC);
+                    tc_commit(acc_full(buf));
+                }
+                tc_commit(empty(s));   // arrives once the MMAs that read this stage are done
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == EPI_WARPS + UNPACK_WARPS + 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Activation plan: q8_1 of every (padded) token row into an int8 plane
+// [n_pad][kpad] (row-major, K inner; MXFP4 keeps each run as (j, j+16) pairs)
+// plus run-major scale planes dx[nkb][n_pad] and, for Q4_K, sx = dx * run sum.
+__global__ void quantize_acts_kernel(const float* __restrict__ x, const int* __restrict__ src_row, int n_pad, int cols, int kind,
+                                     int8_t* __restrict__ q, float* __restrict__ dx, float* __restrict__ sx) {
+    const int nkb = cols >> 5;
+    const long long run = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (run >= (long long)n_pad * nkb) return;
+    const int t = (int)(run / nkb), kb = (int)(run - (long long)t * nkb);
+    const int src = src_row[t];
+    const float v = src >= 0 ? x[(size_t)src * cols + kb * 32 + lane] : 0.0f;
+    float d;
+    int qsum;
+    const int qv = fk_q8_1_lane(v, &d, &qsum);
+    const int pos = kind == FK_MXFP4 ? (((lane & 15) << 1) | (lane >> 4)) : lane;
+    q[(size_t)t * cols + kb * 32 + pos] = (int8_t)qv;
+    if (lane == 0) {
+        dx[(size_t)kb * n_pad + t] = d;
+        if (sx) sx[(size_t)kb * n_pad + t] = d * (float)qsum;
+    }
+}
+
+// Dense plan: padded row t reads token t (t < m) and writes output row t.
+__global__ void dense_plan_kernel(int m, int n_pad, int* src_row, int* out_row) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n_pad) {
+        src_row[t] = t < m ? t : -1;
+        out_row[t] = t < m ? t : -1;
+    }
+}
+
+// Grouped plan (one block): every expert's rows padded up to whole tiles of BN.
+// Permuted row p of expert e lands at pad_off[e] + (p - group_off[e]).
+__global__ void grouped_plan_kernel(const int* __restrict__ group_off, const int* __restrict__ gather, int n_experts, int bn,
+                                    int n_pad, int* src_row, int* out_row, int* tile_expert, int* n_tiles) {
+    extern __shared__ int pad_off[];  // [n_experts + 1]
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < n_experts; e++) {
+            pad_off[e] = acc;
+            const int cnt = group_off[e + 1] - group_off[e];
+            const int tiles = (cnt + bn - 1) / bn;
+            for (int i = 0; i < tiles; i++) tile_expert[acc / bn + i] = e;
+            acc += tiles * bn;
+        }
+        pad_off[n_experts] = acc;
+        *n_tiles = acc / bn;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_pad; t += blockDim.x) {
+        src_row[t] = -1;
+        out_row[t] = -1;
+    }
+    __syncthreads();
+    for (int e = 0; e < n_experts; e++) {
+        const int g0 = group_off[e], cnt = group_off[e + 1] - g0;
+        for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
+            src_row[pad_off[e] + i] = gather ? gather[g0 + i] : g0 + i;
+            out_row[pad_off[e] + i] = g0 + i;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// 2-D row-major tensor [outer][inner] of `esize`-byte elements, box [box_outer][box_inner].
+int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
+             uint32_t box_outer, CUtensorMapSwizzle sw) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fk_fail(FK_DRIVER_INIT, "gemm: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {inner * (uint64_t)esize};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fk_fail(FK_LAUNCH, "gemm: cuTensorMapEncodeTiled failed (%d) for a [%llu][%llu] tensor", (int)r,
+                                          (unsigned long long)outer, (unsigned long long)inner);
+    return FK_OK;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+template <int KIND, int BN>
+int launch_gemm(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorMap& mq, const CUtensorMap& mdx, const CUtensorMap& msx,
+                const CUtensorMap& mw, int n_token_tiles) {
+    auto kern = gemm_kernel<KIND, BN>;
+    constexpr int SMEM = Smem<BN>::TOTAL;
+    FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM), FK_KERNEL);
+    constexpr int WROWS = KIND == FK_Q6_K ? BM / 2 : BM;
+    dim3 grid((a.rows + WROWS - 1) / WROWS, n_token_tiles);
+    kern<<<grid, GEMM_THREADS, SMEM, st>>>(a, mq, mdx, msx, mw);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+template <int BN>
+int launch_by_kind(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorMap& mq, const CUtensorMap& mdx, const CUtensorMap& msx,
+                   const CUtensorMap& mw, int n_token_tiles) {
+    switch (a.kind) {
+        case FK_Q4_K: return launch_gemm<FK_Q4_K, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+        case FK_Q6_K: return launch_gemm<FK_Q6_K, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+        case FK_Q8_0: return launch_gemm<FK_Q8_0, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+        case FK_MXFP4: return launch_gemm<FK_MXFP4, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+    }
+    return fk_fail(FK_UNSUPPORTED, "gemm: kind %d has no kernel", a.kind);
+}
+
+// Shared body of fk_gemm (group_off == nullptr) and fk_gemm_grouped.
+int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* group_off, const int* gather, const float* x,
+                int n_tokens, float* out) {
+    const bool grouped = group_off != nullptr;
+    const int bn = grouped ? 64 : 128;
+    const int n_tiles_max = grouped ? (n_tokens + bn - 1) / bn + w->n_mats : (n_tokens + bn - 1) / bn;
+    const int n_pad = n_tiles_max * bn;
+    const int nkb = w->cols / 32;
+    // scratch: q plane | dx | sx | src_row | out_row | tile_expert | n_tiles
+    size_t off_q = 0, off_dx = align_up(off_q + (size_t)n_pad * w->cols, 1024);
+    size_t off_sx = align_up(off_dx + (size_t)nkb * n_pad * 4, 1024);
+    size_t off_src = align_up(off_sx + (size_t)nkb * n_pad * 4, 1024);
+    size_t off_out = off_src + (size_t)n_pad * 4, off_te = off_out + (size_t)n_pad * 4;
+    size_t off_nt = off_te + (size_t)n_tiles_max * 4, total = off_nt + 16;
+    int rc = fk_ensure_scratch(ctx, total);
+    if (rc) return rc;
+    uint8_t* sc = ctx->scratch;
+    int8_t* q = (int8_t*)(sc + off_q);
+    float* dx = (float*)(sc + off_dx);
+    float* sx = (float*)(sc + off_sx);
+    int* src_row = (int*)(sc + off_src);
+    int* out_row = (int*)(sc + off_out);
+    int* tile_expert = (int*)(sc + off_te);
+    int* n_tiles = (int*)(sc + off_nt);
+
+    if (grouped) {
+        grouped_plan_kernel<<<1, 1024, (w->n_mats + 1) * sizeof(int), st>>>(group_off, gather, w->n_mats, bn, n_pad, src_row, out_row,
+                                                                             tile_expert, n_tiles);
+    } else {
+        dense_plan_kernel<<<(n_pad + 255) / 256, 256, 0, st>>>(n_tokens, n_pad, src_row, out_row);
+    }
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    const long long runs = (long long)n_pad * nkb;
+    quantize_acts_kernel<<<(unsigned)((runs + 7) / 8), 256, 0, st>>>(x, src_row, n_pad, w->cols, w->kind, q, dx, w->kind == FK_Q4_K ? sx : nullptr);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches += 2;
+
+    CUtensorMap mq, mdx, msx, mw;
+    if ((rc = make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, w->cols, n_pad, KSTAGE, bn, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_map(&mdx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if ((rc = make_map(&msx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    mw = mq;
+    if (w->kind == FK_Q8_0) {
+        // the int8 plane of ONE matrix as a [rows][cols] tensor: rows past the end read as zeros
+        if (grouped) return fk_fail(FK_UNSUPPORTED, "gemm_grouped: stacked Q8_0 experts are not wired to the TMA weight path yet");
+        if ((rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->dev + (size_t)mat * w->mat_stride + w->plane_off[0], w->cols, w->rows,
+                           KSTAGE, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    }
+    GemmArgs a;
+    a.w = w->dev;
+    a.mat_stride = w->mat_stride;
+    for (int i = 0; i < 4; i++) a.plane_off[i] = w->plane_off[i];
+    a.kind = w->kind;
+    a.rows = w->rows;
+    a.cols = w->cols;
+    a.mat = mat;
+    a.tile_expert = grouped ? tile_expert : nullptr;
+    a.n_tiles_dev = grouped ? n_tiles : nullptr;
+    a.out_row = out_row;
+    a.out = out;
+    a.err = ctx->err_flag;
+    return grouped ? launch_by_kind<64>(ctx, st, a, mq, mdx, msx, mw, n_tiles_max) : launch_by_kind<128>(ctx, st, a, mq, mdx, msx, mw, n_tiles_max);
+}
+
+}  // namespace
+
+FK_EXPORT int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev) {
+    if (!ctx || !w || !x_dev || !out_dev) return fk_fail(FK_INVALID, "gemm: null argument");
+    if (m < 1) return fk_fail(FK_INVALID, "gemm: m=%d", m);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemm: matrix %d of %d", mat, w->n_mats);
+    FkDeviceGuard g(ctx->device);
+    return gemm_common(ctx, (cudaStream_t)stream, w, mat, nullptr, nullptr, x_dev, m, out_dev);
+}
+
 FK_EXPORT int fk_gemm_grouped(fk_ctx* ctx, void* stream, fk_weight w, const int* group_off_dev, const int* gather_dev,
                               const float* x_dev, int pairs, float* out_dev) {
-    (void)ctx; (void)stream; (void)w; (void)group_off_dev; (void)gather_dev; (void)x_dev; (void)pairs; (void)out_dev;
-    return fk_fail(FK_UNSUPPORTED, "gemm_grouped: not built yet");
+    if (!ctx || !w || !group_off_dev || !x_dev || !out_dev) return fk_fail(FK_INVALID, "gemm_grouped: null argument");
+    if (pairs < 1) return fk_fail(FK_INVALID, "gemm_grouped: pairs=%d", pairs);
+    FkDeviceGuard g(ctx->device);
+    return gemm_common(ctx, (cudaStream_t)stream, w, 0, group_off_dev, gather_dev, x_dev, pairs, out_dev);
+}
+
+// The error word kernels raise when a bounded wait gives up: 0 = none.
+FK_EXPORT int fk_device_error(fk_ctx* ctx, int* code, int reset) {
+    if (!ctx || !code) return fk_fail(FK_INVALID, "device_error: null argument");
+    FkDeviceGuard g(ctx->device);
+    FK_CUDA(cudaMemcpy(code, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost), FK_LAUNCH);
+    if (reset && *code) FK_CUDA(cudaMemset(ctx->err_flag, 0, sizeof(int)), FK_LAUNCH);
+    return FK_OK;
 }

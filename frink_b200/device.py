@@ -52,6 +52,13 @@ def counters(reset=False, device=None):
     return {"h2d_bytes": h.value, "d2h_bytes": d.value, "launches": n.value}
 
 
+def device_error(reset=True, device=None):
+    """The word a kernel raises when a bounded wait gave up (0 = none)."""
+    code = C.c_int()
+    check(lib().fk_device_error(context(device), C.byref(code), int(reset)))
+    return code.value
+
+
 class Weights:
     """Resident quantized weights: `n_mats` equally shaped matrices given as
     their GGUF block bytes (numpy / CPU tensor: uploaded; CUDA tensor: copied

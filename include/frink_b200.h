@@ -62,6 +62,9 @@ int fk_device_info(fk_ctx* ctx, char* name, size_t cap, int* sm_count, size_t* m
 /* Counters since the last reset: H2D bytes, D2H bytes, kernel launches made
  * by this library (crates/frink-cuda/src/counters.rs, xfer.rs). */
 int fk_counters(fk_ctx* ctx, uint64_t* h2d_bytes, uint64_t* d2h_bytes, uint64_t* launches, int reset);
+/* The word a kernel raises when one of its bounded waits gives up (0 = none);
+ * no counterpart in the reference, whose kernels have no waits. */
+int fk_device_error(fk_ctx* ctx, int* code, int reset);
 int fk_block_bytes(int kind);
 int fk_block_elems(int kind);
 
