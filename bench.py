@@ -185,6 +185,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (BASELINE config 2)")
     ap.add_argument("--case", default=None, help="kind:rows:cols:batch -- plain launches of one GEMV shape (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -294,6 +295,8 @@ def main():
         "gpu_launches": launches, "clocks": clocks,
         "parity": {"rel_l2_device": rel, "rel_l2_e2e": rel_e2e, "bar": 1e-3},
     }
+    if world == 1 and not args.no_gemm:
+        line["gemm"] = gemm_sweep()
     if args.extras and world == 1:
         line["extras"] = extras(peak)
     print(json.dumps(line))
@@ -302,14 +305,16 @@ def main():
 
 
 def single_case(args):
-    """`--case kind:rows:cols:batch`: `--steps` plain (un-graphed) launches of one
-    GEMV shape over a ring of weight copies larger than L2; what the ncu captures
-    under profiles/ run."""
+    """`--case [gemv:|gemm:]kind:rows:cols:n`: `--steps` plain (un-graphed) launches of
+    one shape over a ring of weight copies larger than L2 (n = batch for the GEMV,
+    tokens for the GEMM); what the ncu captures under profiles/ run."""
     import torch
     from frink_b200 import device
     from oracle import frink_oracle as fo
-    name, rows, cols, batch = args.case.split(":")
-    kind, rows, cols, batch = fo.KINDS[name], int(rows), int(cols), int(batch)
+    parts = args.case.split(":")
+    op = parts.pop(0) if parts[0] in ("gemv", "gemm") else "gemv"
+    name, rows, cols, n = parts
+    kind, rows, cols, n = fo.KINDS[name], int(rows), int(cols), int(n)
     rng = np.random.default_rng(1)
     base_rows = min(rows, 1024)
     base = fo.encode(kind, (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(0.02)))
@@ -317,21 +322,86 @@ def single_case(args):
     raw_d = torch.from_numpy(raw).cuda()
     ring = max(2, int(400e6 // raw.size) + 1)
     ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
-    xd = torch.from_numpy(rng.standard_normal((batch, cols), dtype=np.float32)).cuda()
-    yd = torch.empty((batch, rows), dtype=torch.float32, device="cuda")
+    xd = torch.from_numpy(rng.standard_normal((n, cols), dtype=np.float32)).cuda()
+    yd = torch.empty((n, rows), dtype=torch.float32, device="cuda")
+    run = (lambda i: device.gemm(ws[i % ring], xd, out=yd)) if op == "gemm" else (lambda i: device.gemv(ws[i % ring], xd, out=yd))
     for i in range(args.warmup):
-        device.gemv(ws[i % ring], xd, out=yd)
+        run(i)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
-        device.gemv(ws[i % ring], xd, out=yd)
+        run(i)
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1)
-    nbytes = raw.size + batch * cols * 4 + batch * rows * 4
+    nbytes = raw.size + n * cols * 4 + n * rows * 4
     print(json.dumps({"case": args.case, "steps": args.steps, "us_per_launch_incl_host": ms / args.steps * 1e3,
-                      "algorithmic_bytes": nbytes, "ring": ring}))
+                      "algorithmic_bytes": nbytes, "flops": 2.0 * n * rows * cols, "ring": ring,
+                      "device_error_word": device.device_error()}))
+
+
+def int8_peak_tops():
+    """Dense int8 tensor throughput of this GPU as cuBLASLt delivers it (8192^3,
+    torch._int_mm), the measured denominator beside the nominal 4500 TOPS."""
+    import torch
+    try:
+        a = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device="cuda").t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = 1e9
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def gemm_sweep(m=512, steps=200):
+    """BASELINE config 2: M = 512 tokens against 3072x3072, 8192x3072, 3072x8192
+    in Q4_K, Q6_K, Q8_0 (plus MXFP4 on the 2880-wide shapes).  TFLOPS = 2*M*N*K
+    over the whole fk_gemm call (activation quantization + plan + MMA kernel),
+    CUDA-graph replays over a ring of weight copies larger than L2."""
+    import torch
+    from frink_b200 import device
+    from oracle import frink_oracle as fo
+    rng = np.random.default_rng(2)
+    peak = int8_peak_tops()
+    cells = []
+    shapes = [(3072, 3072), (8192, 3072), (3072, 8192)]
+    todo = [(k, r, c) for k in ("q4_k", "q6_k", "q8_0") for (r, c) in shapes] + [("mxfp4", 2880, 2880), ("mxfp4", 8192, 2880)]
+    for name, rows, cols in todo:
+        kind = fo.KINDS[name]
+        base_rows = min(rows, 512)
+        base = fo.encode(kind, (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(0.02)))
+        raw = np.tile(base, -(-rows // base_rows))[: rows * fo.row_bytes(kind, cols)]
+        raw_d = torch.from_numpy(raw).cuda()
+        ring = max(2, int(300e6 // raw.size) + 1)
+        ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
+        xd = torch.from_numpy(rng.standard_normal((m, cols), dtype=np.float32)).cuda()
+        out = torch.empty((m, rows), dtype=torch.float32, device="cuda")
+
+        def launch(i):
+            device.gemm(ws[i % ring], xd, out=out)
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        ms = timed_launches(steps, ring, launch, 10)
+        tf = 2.0 * m * rows * cols * steps / (ms * 1e-3) / 1e12
+        cells.append({"kind": name, "rows": rows, "cols": cols, "m": m, "us": ms / steps * 1e3, "tflops": tf,
+                      "frac_of_measured_int8": tf / peak if peak else None, "frac_of_nominal_4500": tf / 4500.0})
+        for w in ws:
+            w.release()
+    err = device.device_error()
+    return {"cells": cells, "int8_peak_tops_measured": peak, "int8_peak_tops_nominal": 4500.0, "device_error_word": err,
+            "note": "bit-exact int8 per-32-run path; the f32 rescale after every K=32 MMA bounds it, not the tensor pipe"}
 
 
 def extras(peak):

@@ -10,13 +10,13 @@
 // is drained from tensor memory after every K = 32 step and scaled on the CUDA
 // cores; that rescale, not the tensor pipe, bounds this kernel.
 //
-// One CTA = 128 weight rows x BN tokens, 14 warps with fixed roles:
+// One CTA = 128 weight rows x BN tokens, 12 warps with fixed roles:
 //   warps 0-7   epilogue: TMEM -> registers (tcgen05.ld), f32 rescale, store
-//   warps 8-11  unpack: packed weights (global) -> int8 tile in shared memory
+//   warps 8-9   unpack: packed weights (global) -> int8 tile in shared memory
 //               (128-byte swizzle, the layout the MMA descriptor names)
-//   warp 12     TMA producer: activation int8 tile + its scale tiles (and the
+//   warp 10     TMA producer: activation int8 tile + its scale tiles (and the
 //               weight tile itself for Q8_0, whose int8 plane needs no unpacking)
-//   warp 13     MMA issuer (one elected lane) + TMEM allocation
+//   warp 11     MMA issuer (one elected lane) + TMEM allocation
 // Stages (K = 128 each) and TMEM accumulators are rings guarded by mbarriers;
 // every wait is bounded and raises the context's error word instead of
 // spinning forever.
@@ -29,8 +29,8 @@ namespace {
 constexpr int BM = 128;           // weight rows per CTA (MMA M)
 constexpr int KSTAGE = 128;       // K per pipeline stage (4 MMAs of K = 32)
 constexpr int NSTAGE = 4;
-constexpr int EPI_WARPS = 8, UNPACK_WARPS = 4;
-constexpr int GEMM_THREADS = (EPI_WARPS + UNPACK_WARPS + 2) * 32;  // 448
+constexpr int EPI_WARPS = 8, UNPACK_WARPS = 2;
+constexpr int GEMM_THREADS = (EPI_WARPS + UNPACK_WARPS + 2) * 32;  // 384: 168 registers a thread
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 struct GemmArgs {
@@ -66,8 +66,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: gives up after WAIT_LIMIT polls, records where, and lets the
 // caller run on (its results are then garbage, the host sees the error word).
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
+    }
     atomicCAS(err, 0, code);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
@@ -97,6 +98,12 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The 32 registers a tcgen05.ld filled are defined, as far as the compiler can
+// tell, at the load itself; this pins their first use behind the wait.
+__device__ __forceinline__ void tc_ld_fence(uint32_t* v) {
+#pragma unroll
+    for (int i = 0; i < 32; i++) asm volatile("" : "+r"(v[i]) :: "memory");
+}
 
 // K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024
 // bytes apart: start address, LBO = 16 B (unused by this layout), SBO = 1024 B,
@@ -126,6 +133,12 @@ __device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
 }
 __device__ __forceinline__ float e8m0_half(uint32_t e) {
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
+}
+
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
 }
 
 // Shared memory map (offsets from a 1024-byte aligned base).
@@ -189,71 +202,97 @@ __device__ __forceinline__ void load_wscales(const GemmArgs& a, const uint8_t* w
     }
 }
 
-// One thread = one tile row: its 128 int8 of stage `st` (K range [128 st, 128 st + 128))
-// written as eight 16-byte chunks at their swizzled places.
+// Packed bytes of one weight row for stage `st` (K range [128 st, 128 st + 128)),
+// as loaded (nothing decoded yet, so the loads of the next stage can be in
+// flight while this stage is written).
+template <int KIND> struct RawRow { uint4 q[KIND == FK_Q6_K ? 6 : 4]; };
+
 template <int KIND>
-__device__ __forceinline__ void unpack_row(const GemmArgs& a, const uint8_t* wb, int r, int row, bool row_ok, int st, uint8_t* a_tile) {
-    uint4 o[8];
+__device__ __forceinline__ void load_raw(const GemmArgs& a, const uint8_t* wb, int wrow, bool ok, int st, RawRow<KIND>& raw) {
+    constexpr int N = KIND == FK_Q6_K ? 6 : 4;
 #pragma unroll
-    for (int c = 0; c < 8; c++) o[c] = make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < N; i++) raw.q[i] = make_uint4(0, 0, 0, 0);
     const int k0 = st * KSTAGE;
-    if (row_ok && k0 < a.cols) {
-        if (KIND == FK_Q4_K) {
-            // 128 weights = 64 quant bytes: two groups of 32 bytes; low nibbles are
-            // the first 32 weights of a group, high nibbles the next 32
-            const uint8_t* p = wb + ((size_t)row * (a.cols >> 8) + (k0 >> 8)) * 144 + 16 + ((k0 >> 7) & 1) * 64;
+    if (!ok || k0 >= a.cols || KIND == FK_Q8_0) return;
+    if (KIND == FK_Q4_K) {
+        // 128 weights = 64 quant bytes: two groups of 32 bytes
+        const uint8_t* p = wb + ((size_t)wrow * (a.cols >> 8) + (k0 >> 8)) * 144 + 16 + ((k0 >> 7) & 1) * 64;
 #pragma unroll
-            for (int g = 0; g < 2; g++) {
-                const uint4 q0 = ldg16(p + 32 * g), q1 = ldg16(p + 32 * g + 16);
-                o[4 * g + 0] = make_uint4(q0.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q0.z & 0x0F0F0F0Fu, q0.w & 0x0F0F0F0Fu);
-                o[4 * g + 1] = make_uint4(q1.x & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, q1.z & 0x0F0F0F0Fu, q1.w & 0x0F0F0F0Fu);
-                o[4 * g + 2] = make_uint4((q0.x >> 4) & 0x0F0F0F0Fu, (q0.y >> 4) & 0x0F0F0F0Fu, (q0.z >> 4) & 0x0F0F0F0Fu, (q0.w >> 4) & 0x0F0F0F0Fu);
-                o[4 * g + 3] = make_uint4((q1.x >> 4) & 0x0F0F0F0Fu, (q1.y >> 4) & 0x0F0F0F0Fu, (q1.z >> 4) & 0x0F0F0F0Fu, (q1.w >> 4) & 0x0F0F0F0Fu);
-            }
-        } else if (KIND == FK_MXFP4) {
-            // 4 blocks of 16 code bytes; bytes come out as (elem j, elem j+16) pairs,
-            // the order the activation plane of this kind is stored in
-            const uint8_t* p = wb + a.plane_off[0] + (size_t)row * (a.cols >> 1) + (k0 >> 1);
+        for (int i = 0; i < 4; i++) raw.q[i] = ldg16(p + 16 * i);
+    } else if (KIND == FK_MXFP4) {
+        const uint8_t* p = wb + a.plane_off[0] + (size_t)wrow * (a.cols >> 1) + (k0 >> 1);
 #pragma unroll
-            for (int b = 0; b < 4; b++) {
-                if (k0 + 32 * b < a.cols) {
-                    const uint4 q = ldg16(p + 16 * b);
-                    o[2 * b] = make_uint4(e2m1x2_4(q.x), e2m1x2_4(q.x >> 16), e2m1x2_4(q.y), e2m1x2_4(q.y >> 16));
-                    o[2 * b + 1] = make_uint4(e2m1x2_4(q.z), e2m1x2_4(q.z >> 16), e2m1x2_4(q.w), e2m1x2_4(q.w >> 16));
-                }
-            }
-        } else if (KIND == FK_Q6_K) {
-            // tile row = (weight row, half): the 6-bit codes minus 32 of this K range,
-            // with the 16 weights of the OTHER half of every run of 32 zeroed, so
-            // that one K = 32 MMA yields the exact dot of a 16-weight scale group
-            const int wrow = row >> 1, half = row & 1;
-            const int sb = k0 >> 8, hf = (k0 >> 7) & 1;
-            const uint8_t* ql = wb + a.plane_off[0] + (size_t)wrow * (a.cols >> 1) + (size_t)sb * 128 + 64 * hf;
-            const uint8_t* qh = wb + a.plane_off[1] + (size_t)wrow * (a.cols >> 2) + (size_t)sb * 64 + 32 * hf;
-            const uint4 h0 = ldg16(qh), h1 = ldg16(qh + 16);
-            const uint32_t hh[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-            // element e = 32 * qd + l (qd = 0..3, l = 0..31): ql byte (l + 32 * (qd & 1)),
-            // nibble (qd >> 1), qh byte l bits [2 qd, 2 qd + 2)
+        for (int b = 0; b < 4; b++)
+            if (k0 + 32 * b < a.cols) raw.q[b] = ldg16(p + 16 * b);
+    } else {  // FK_Q6_K: 64 ql bytes + 32 qh bytes of this half super-block
+        const int sb = k0 >> 8, hf = (k0 >> 7) & 1;
+        const uint8_t* ql = wb + a.plane_off[0] + (size_t)wrow * (a.cols >> 1) + (size_t)sb * 128 + 64 * hf;
+        const uint8_t* qh = wb + a.plane_off[1] + (size_t)wrow * (a.cols >> 2) + (size_t)sb * 64 + 32 * hf;
 #pragma unroll
-            for (int qd = 0; qd < 4; qd++) {
-                const uint4 l0 = ldg16(ql + 32 * (qd & 1)), l1 = ldg16(ql + 32 * (qd & 1) + 16);
-                const uint32_t ll[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
-                uint32_t v[8];
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint32_t nib = (qd >> 1) ? ((ll[i] >> 4) & 0x0F0F0F0Fu) : (ll[i] & 0x0F0F0F0Fu);
-                    const uint32_t c6 = nib | (((hh[i] >> (2 * qd)) & 0x03030303u) << 4);
-                    v[i] = __vsub4(c6, 0x20202020u);
-                }
-                // run of 32 = chunks (2 qd, 2 qd + 1): keep this row's half
-                o[2 * qd + half] = make_uint4(v[4 * half], v[4 * half + 1], v[4 * half + 2], v[4 * half + 3]);
-            }
-        }
+        for (int i = 0; i < 4; i++) raw.q[i] = ldg16(ql + 16 * i);
+        raw.q[4] = ldg16(qh);
+        raw.q[5] = ldg16(qh + 16);
     }
-    if (KIND != FK_Q8_0) {
-        uint8_t* dst = a_tile + r * 128;
+}
+
+__device__ __forceinline__ void store_tile_row(uint8_t* a_tile, int r, const uint4* o) {
+    uint8_t* dst = a_tile + r * 128;
 #pragma unroll
-        for (int c = 0; c < 8; c++) *(uint4*)(dst + ((c ^ (r & 7)) << 4)) = o[c];
+    for (int c = 0; c < 8; c++) *(uint4*)(dst + ((c ^ (r & 7)) << 4)) = o[c];
+}
+
+// Decode one weight row's 128 weights of a stage to int8 and write them as tile
+// row(s), eight 16-byte chunks each at their swizzled places.  Q4_K, MXFP4:
+// tile row `r`.  Q6_K: tile rows 2 r' and 2 r' + 1 (r = 2 r'), the codes minus
+// 32 with the 16 weights of the OTHER half of every run of 32 zeroed, so that
+// one K = 32 MMA yields the exact dot of a 16-weight scale group.
+template <int KIND>
+__device__ __forceinline__ void store_raw(const RawRow<KIND>& raw, int r, uint8_t* a_tile) {
+    uint4 o[8];
+    if (KIND == FK_Q4_K) {
+        // low nibbles are the first 32 weights of a 32-byte group, high nibbles the next 32
+#pragma unroll
+        for (int g = 0; g < 2; g++) {
+            const uint4 q0 = raw.q[2 * g], q1 = raw.q[2 * g + 1];
+            o[4 * g + 0] = make_uint4(q0.x & 0x0F0F0F0Fu, q0.y & 0x0F0F0F0Fu, q0.z & 0x0F0F0F0Fu, q0.w & 0x0F0F0F0Fu);
+            o[4 * g + 1] = make_uint4(q1.x & 0x0F0F0F0Fu, q1.y & 0x0F0F0F0Fu, q1.z & 0x0F0F0F0Fu, q1.w & 0x0F0F0F0Fu);
+            o[4 * g + 2] = make_uint4((q0.x >> 4) & 0x0F0F0F0Fu, (q0.y >> 4) & 0x0F0F0F0Fu, (q0.z >> 4) & 0x0F0F0F0Fu, (q0.w >> 4) & 0x0F0F0F0Fu);
+            o[4 * g + 3] = make_uint4((q1.x >> 4) & 0x0F0F0F0Fu, (q1.y >> 4) & 0x0F0F0F0Fu, (q1.z >> 4) & 0x0F0F0F0Fu, (q1.w >> 4) & 0x0F0F0F0Fu);
+        }
+        store_tile_row(a_tile, r, o);
+    } else if (KIND == FK_MXFP4) {
+        // bytes come out as (elem j, elem j+16) pairs, the order the activation
+        // plane of this kind is stored in; an absent block (past the last column) is zeros
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            const uint4 q = raw.q[b];
+            o[2 * b] = make_uint4(e2m1x2_4(q.x), e2m1x2_4(q.x >> 16), e2m1x2_4(q.y), e2m1x2_4(q.y >> 16));
+            o[2 * b + 1] = make_uint4(e2m1x2_4(q.z), e2m1x2_4(q.z >> 16), e2m1x2_4(q.w), e2m1x2_4(q.w >> 16));
+        }
+        store_tile_row(a_tile, r, o);
+    } else if (KIND == FK_Q6_K) {
+        const uint32_t hh[8] = {raw.q[4].x, raw.q[4].y, raw.q[4].z, raw.q[4].w, raw.q[5].x, raw.q[5].y, raw.q[5].z, raw.q[5].w};
+        uint4 o1[8];
+        // element e = 32 * qd + l (qd = 0..3, l = 0..31): ql byte (l + 32 * (qd & 1)),
+        // nibble (qd >> 1), qh byte l bits [2 qd, 2 qd + 2)
+#pragma unroll
+        for (int qd = 0; qd < 4; qd++) {
+            const uint4 l0 = raw.q[2 * (qd & 1)], l1 = raw.q[2 * (qd & 1) + 1];
+            const uint32_t ll[8] = {l0.x, l0.y, l0.z, l0.w, l1.x, l1.y, l1.z, l1.w};
+            uint32_t v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t nib = (qd >> 1) ? ((ll[i] >> 4) & 0x0F0F0F0Fu) : (ll[i] & 0x0F0F0F0Fu);
+                const uint32_t c6 = nib | (((hh[i] >> (2 * qd)) & 0x03030303u) << 4);
+                v[i] = __vsub4(c6, 0x20202020u);
+            }
+            o[2 * qd] = make_uint4(v[0], v[1], v[2], v[3]);       // half 0 keeps the first 16 of the run
+            o[2 * qd + 1] = make_uint4(0, 0, 0, 0);
+            o1[2 * qd] = make_uint4(0, 0, 0, 0);
+            o1[2 * qd + 1] = make_uint4(v[4], v[5], v[6], v[7]);  // half 1 the last 16
+        }
+        store_tile_row(a_tile, r, o);
+        store_tile_row(a_tile, r + 1, o1);
     }
 }
 
@@ -315,57 +354,76 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
         const int row = KIND == FK_Q6_K ? 2 * wrow0 + r : wrow0 + r;   // scale row id (pair id for Q6_K)
         const bool row_ok = (KIND == FK_Q6_K ? (wrow0 + (r >> 1)) : (wrow0 + r)) < a.rows;
         constexpr int CW = BN / 2;                     // columns this warp owns
+        constexpr int NCH = CW / 32;                   // 32-column chunks per accumulator
         float acc[CW];
 #pragma unroll
         for (int i = 0; i < CW; i++) acc[i] = 0.0f;
         const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * CW;
         WScale ws[4], ws_next[4];
         load_wscales<KIND>(a, wb, row, row_ok, 0, nkb, ws_next);
+        // TMEM reads are double-buffered: chunk u+1 is in flight while chunk u is scaled.
+        uint32_t v[2][32];
+        auto issue = [&](int kb, int c, uint32_t* dst) {
+            const int buf = kb % S::NACC;
+            if (c == 0) {
+                mbar_wait(acc_full(buf), (kb / S::NACC) & 1, a.err, 11);
+                tc_fence_after();
+            }
+            tc_ld32(taddr0 + buf * BN + c * 32, dst);
+        };
+        auto release = [&](int kb) {   // every column of this accumulator has been read by this warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(kb % S::NACC));
+        };
+        issue(0, 0, v[0]);
+        tc_wait_ld();
+        tc_ld_fence(v[0]);
+        if (NCH == 1) release(0);
         for (int st = 0; st < nst; st++) {
             const int s = st % NSTAGE;
 #pragma unroll
             for (int j = 0; j < 4; j++) ws[j] = ws_next[j];
             if (st + 1 < nst) load_wscales<KIND>(a, wb, row, row_ok, 4 * (st + 1), nkb, ws_next);
             mbar_wait(full_b(s), (st / NSTAGE) & 1, a.err, 10);   // the scale tiles of this stage have landed
-            const float* sdx = (const float*)(smem + s * S::STAGE + S::A_BYTES + S::B_BYTES);
-            const float* ssx = sdx + 4 * BN;
-#pragma unroll 1
+            // the stage's scale tiles: dx [4][BN] then (Q4_K) sx [4][BN], as shared-space addresses
+            const uint32_t sdx_s = sbase + s * S::STAGE + S::A_BYTES + S::B_BYTES;
+            // kept rolled where the register double buffer allows it (two chunks per
+            // accumulator): the unrolled body is slower
+#pragma unroll(NCH == 1 ? 4 : 1)
             for (int j = 0; j < 4; j++) {
                 const int kb = 4 * st + j;
-                if (kb >= nkb) break;
-                const int buf = kb % S::NACC;
-                mbar_wait(acc_full(buf), (kb / S::NACC) & 1, a.err, 11);
-                tc_fence_after();
-                const float dw = ws[j].dw, mw = ws[j].mw;
+                const float dw = j == 0 ? ws[0].dw : (j == 1 ? ws[1].dw : (j == 2 ? ws[2].dw : ws[3].dw));
+                const float mw = j == 0 ? ws[0].mw : (j == 1 ? ws[1].mw : (j == 2 ? ws[2].mw : ws[3].mw));
 #pragma unroll
-                for (int c0 = 0; c0 < CW; c0 += 32) {
-                    uint32_t v[32];
-                    tc_ld32(taddr0 + buf * BN + c0, v);
-                    tc_wait_ld();
-                    if (c0 + 32 >= CW) {  // last read of this accumulator: hand it back
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(acc_empty(buf));
-                    }
-                    const float* dxp = sdx + j * BN + chalf * CW + c0;
-                    const float* sxp = ssx + j * BN + chalf * CW + c0;
+                for (int c = 0; c < NCH; c++) {
+                    if (kb < nkb) {
+                        uint32_t* cur = v[(j * NCH + c) & 1];
+                        uint32_t* nxt = v[(j * NCH + c + 1) & 1];
+                        const int kb_n = c + 1 < NCH ? kb : kb + 1, c_n = c + 1 < NCH ? c + 1 : 0;
+                        if (kb_n < nkb) issue(kb_n, c_n, nxt);
+                        const uint32_t dxs = sdx_s + (uint32_t)(j * BN + chalf * CW + c * 32) * 4u;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        const float4 dx = *(const float4*)(dxp + i);
-                        const float dxa[4] = {dx.x, dx.y, dx.z, dx.w};
-                        float sxa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        if (KIND == FK_Q4_K) {
-                            const float4 sx = *(const float4*)(sxp + i);
-                            sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
+                        for (int i = 0; i < 32; i += 4) {
+                            const float4 dx = lds128(dxs + 4u * i);
+                            const float dxa[4] = {dx.x, dx.y, dx.z, dx.w};
+                            float sxa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                            if (KIND == FK_Q4_K) {
+                                const float4 sx = lds128(dxs + 16u * BN + 4u * i);
+                                sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
+                                const float f = __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
+                                float t = fmaf(dw * dxa[e], f, acc[c * 32 + i + e]);
+                                if (KIND == FK_Q4_K) t = fmaf(-mw, sxa[e], t);
+                                acc[c * 32 + i + e] = t;
+                            }
                         }
-#pragma unroll
-                        for (int e = 0; e < 4; e++) {
-                            // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
-                            const float f = __int_as_float((int)v[i + e] + 0x4B400000) - 12582912.0f;
-                            float t = acc[c0 + i + e] + (dw * dxa[e]) * f;
-                            if (KIND == FK_Q4_K) t -= mw * sxa[e];
-                            acc[c0 + i + e] = t;
-                        }
+                        tc_wait_ld();
+                        tc_ld_fence(nxt);
+                        if (kb_n < nkb && c_n == NCH - 1) release(kb_n);
                     }
                 }
             }
@@ -374,30 +432,38 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
             if (lane == 0) mbar_arrive(empty(s));
         }
         // ---- store: out[out_row[token]][weight row]
-        if (KIND == FK_Q6_K) {
-#pragma unroll
-            for (int i = 0; i < CW; i++) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 1);
-        }
         const int orow = KIND == FK_Q6_K ? wrow0 + (r >> 1) : wrow0 + r;
         const bool writer = row_ok && (KIND != FK_Q6_K || !(r & 1));
 #pragma unroll 4
         for (int i = 0; i < CW; i++) {
+            float v0 = acc[i];
+            if (KIND == FK_Q6_K) v0 += __shfl_xor_sync(0xffffffffu, v0, 1);   // the two halves of a weight row sit in neighbouring lanes
             const int dst = a.out_row[tok0 + chalf * CW + i];
-            if (writer && dst >= 0) a.out[(size_t)dst * a.rows + orow] = acc[i];
+            if (writer && dst >= 0) a.out[(size_t)dst * a.rows + orow] = v0;
         }
     } else if (warp < EPI_WARPS + UNPACK_WARPS) {
         // ------------------------------------------------- weight unpack warps
         if (KIND != FK_Q8_0) {
-            const int r = (warp - EPI_WARPS) * 32 + lane;
-            const int row = KIND == FK_Q6_K ? 2 * wrow0 + r : wrow0 + r;
-            const bool row_ok = (KIND == FK_Q6_K ? (wrow0 + (r >> 1)) : (wrow0 + r)) < a.rows;
+            // 64 threads: Q6_K one weight row (two tile rows) each, the others two rows each
+            constexpr int NR = KIND == FK_Q6_K ? 1 : 2;
+            const int t = (warp - EPI_WARPS) * 32 + lane;
+            RawRow<KIND> cur[NR], nxt[NR];
+#pragma unroll
+            for (int i = 0; i < NR; i++) load_raw<KIND>(a, wb, wrow0 + t + 64 * i, wrow0 + t + 64 * i < a.rows, 0, cur[i]);
             for (int st = 0; st < nst; st++) {
                 const int s = st % NSTAGE;
+                if (st + 1 < nst) {
+#pragma unroll
+                    for (int i = 0; i < NR; i++) load_raw<KIND>(a, wb, wrow0 + t + 64 * i, wrow0 + t + 64 * i < a.rows, st + 1, nxt[i]);
+                }
                 if (st >= NSTAGE) mbar_wait(empty(s), ((st / NSTAGE) - 1) & 1, a.err, 20);
-                unpack_row<KIND>(a, wb, r, row, row_ok, st, smem + s * S::STAGE);
+#pragma unroll
+                for (int i = 0; i < NR; i++) store_raw<KIND>(cur[i], KIND == FK_Q6_K ? 2 * t : t + 64 * i, smem + s * S::STAGE);
                 fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a(s));
+#pragma unroll
+                for (int i = 0; i < NR; i++) cur[i] = nxt[i];
             }
         }
     } else if (warp == EPI_WARPS + UNPACK_WARPS) {
