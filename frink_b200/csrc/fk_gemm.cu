@@ -722,6 +722,96 @@ FK_EXPORT int fk_gemm_grouped(fk_ctx* ctx, void* stream, fk_weight w, const int*
     return gemm_common(ctx, (cudaStream_t)stream, w, 0, group_off_dev, gather_dev, x_dev, pairs, out_dev);
 }
 
+// ---------------------------------------------------------------------------
+// fk_gemm without any allocation.
+//
+// Some callers cannot allocate device memory at the moment they need a GEMM: a
+// host thread that is inside a CUDA stream capture (cudaMalloc is not allowed
+// there), a serving loop that must not hit the implicit device-wide
+// synchronisation of cudaMalloc/cudaFree, or a process whose memory budget was
+// handed out up front.  fk_gemm grows the context's scratch block on demand,
+// so it is not for them.  This variant keeps its scratch (the int8 activation
+// plane, the two scale planes and the row tables) in the fixed array below,
+// which every GPU that loads this library holds from load to exit.
+constexpr size_t FK_GEMM_STATIC_BYTES = 6u << 20;   // 6 MiB: e.g. 512 tokens x 8192 columns
+static __device__ __align__(256) uint8_t fk_gemm_static_scratch[FK_GEMM_STATIC_BYTES];
+
+namespace {
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+std::mutex g_static_mu;
+uint8_t* g_static_ptr[64] = {nullptr};
+
+int static_scratch(fk_ctx* ctx, uint8_t** out) {
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (ctx->device < 0 || ctx->device >= 64) return fk_fail(FK_INVALID, "gemm_static: device %d", ctx->device);
+    if (!g_static_ptr[ctx->device]) {
+        void* p = nullptr;
+        FK_CUDA(cudaGetSymbolAddress(&p, fk_gemm_static_scratch), FK_DRIVER_INIT);
+        g_static_ptr[ctx->device] = (uint8_t*)p;
+    }
+    *out = g_static_ptr[ctx->device];
+    return FK_OK;
+}
+}  // namespace
+
+FK_EXPORT int fk_gemm_static(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev) {
+    if (!ctx || !w || !x_dev || !out_dev) return fk_fail(FK_INVALID, "gemm_static: null argument");
+    if (m < 1) return fk_fail(FK_INVALID, "gemm_static: m=%d", m);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemm_static: matrix %d of %d", mat, w->n_mats);
+    FkDeviceGuard g(ctx->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int bn = 128;
+    const int n_tiles = (m + bn - 1) / bn, n_pad = n_tiles * bn, nkb = w->cols / 32;
+    // the same carve-up as fk_gemm's: q plane | dx | sx | src_row | out_row
+    const size_t off_dx = align_up((size_t)n_pad * w->cols, 1024);
+    const size_t off_sx = align_up(off_dx + (size_t)nkb * n_pad * 4, 1024);
+    const size_t off_src = align_up(off_sx + (size_t)nkb * n_pad * 4, 1024);
+    const size_t off_out = off_src + (size_t)n_pad * 4, total = off_out + (size_t)n_pad * 4;
+    if (total > FK_GEMM_STATIC_BYTES)
+        return fk_fail(FK_INVALID, "gemm_static: %d tokens x %d columns needs %zu bytes of scratch, the fixed block holds %zu (use fk_gemm)",
+                       m, w->cols, total, (size_t)FK_GEMM_STATIC_BYTES);
+    uint8_t* sc = nullptr;
+    int rc = static_scratch(ctx, &sc);
+    if (rc) return rc;
+    int8_t* q = (int8_t*)sc;
+    float* dx = (float*)(sc + off_dx);
+    float* sx = (float*)(sc + off_sx);
+    int* src_row = (int*)(sc + off_src);
+    int* out_row = (int*)(sc + off_out);
+    // Nothing in the block has to start at zero: the two kernels below write every
+    // word the GEMM reads (padding rows included) before it reads them.
+    dense_plan_kernel<<<(n_pad + 255) / 256, 256, 0, st>>>(m, n_pad, src_row, out_row);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    const long long runs = (long long)n_pad * nkb;
+    quantize_acts_kernel<<<(unsigned)((runs + 7) / 8), 256, 0, st>>>(x_dev, src_row, n_pad, w->cols, w->kind, q, dx, w->kind == FK_Q4_K ? sx : nullptr);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches += 2;
+    CUtensorMap mq, mdx, msx, mw;
+    if ((rc = make_map(&mq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q, w->cols, n_pad, KSTAGE, bn, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
+    if ((rc = make_map(&mdx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    if ((rc = make_map(&msx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
+    mw = mq;
+    if (w->kind == FK_Q8_0 &&
+        (rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->dev + (size_t)mat * w->mat_stride + w->plane_off[0], w->cols, w->rows, KSTAGE,
+                       BM, CU_TENSOR_MAP_SWIZZLE_128B)))
+        return rc;
+    GemmArgs a;
+    a.w = w->dev;
+    a.mat_stride = w->mat_stride;
+    for (int i = 0; i < 4; i++) a.plane_off[i] = w->plane_off[i];
+    a.kind = w->kind;
+    a.rows = w->rows;
+    a.cols = w->cols;
+    a.mat = mat;
+    a.tile_expert = nullptr;
+    a.n_tiles_dev = nullptr;
+    a.out_row = out_row;
+    a.out = out_dev;
+    a.err = ctx->err_flag;
+    return launch_by_kind<128>(ctx, st, a, mq, mdx, msx, mw, n_tiles);
+}
+
 // The error word kernels raise when a bounded wait gives up: 0 = none.
 FK_EXPORT int fk_device_error(fk_ctx* ctx, int* code, int reset) {
     if (!ctx || !code) return fk_fail(FK_INVALID, "device_error: null argument");

@@ -147,6 +147,18 @@ def gemm(w, x, mat=0, out=None):
     return y
 
 
+def gemm_static(w, x, mat=0, out=None):
+    """`gemm` through the entry point that allocates nothing on the device: its
+    scratch is a fixed block inside the library, so it can be used where device
+    allocation is off limits (`out` must then be given: torch allocating the
+    result would defeat the point).  Shapes too large for the block raise Invalid."""
+    x = _f32(x)
+    assert x.dim() == 2 and x.shape[1] == w.cols
+    y = out if out is not None else torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
+    check(lib().fk_gemm_static(w._ctx, _stream(), w.handle, mat, _ptr(x), x.shape[0], _ptr(y)))
+    return y
+
+
 def gemm_grouped(w, group_off, gather, x, pairs, out=None):
     """Permuted row p (expert e where group_off[e] <= p < group_off[e+1]) reads
     x[gather[p]] and writes out[p]."""

@@ -114,6 +114,19 @@ int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* 
  * out_dev[t * rows + r] = W[mat][r] . q8_1(x_dev[t * cols ..]),  0 <= t < m. */
 int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev);
 
+/* fk_gemm for callers that cannot allocate device memory when they need it (a
+ * thread inside a stream capture, a serving loop that must avoid cudaMalloc's
+ * device-wide synchronisation, a process on a fixed memory budget).  It has no
+ * counterpart in the reference.  Same arguments and results as fk_gemm; its
+ * scratch lives in a fixed 6 MiB block inside the library (held by every GPU
+ * that loads it, from load to exit) and the call makes no cudaMalloc/cudaFree.
+ * Shapes whose scratch does not fit (about m_padded * (cols + cols / 4) bytes,
+ * m padded to 128) are refused with FK_INVALID.  The first call on a device
+ * looks the block's address up (cudaGetSymbolAddress); make that call before
+ * any stream capture.  Every call shares the block: two calls that overlap on
+ * the GPU (different streams, no ordering) race; calls on one stream do not. */
+int fk_gemm_static(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev);
+
 /* Grouped (per-expert) GEMM, the `FX_GROUPED` form (src/mmq/mod.rs:144-226):
  * rows [group_off[e], group_off[e+1]) of the permuted activation list belong to
  * expert e; permuted row p reads x_dev[gather_dev[p] * cols ..] (gather NULL =
