@@ -1,0 +1,195 @@
+"""Multi-GPU sharding of the path: tensor parallel for dense projections,
+expert parallel for routed layers, one process per GPU over `torch.distributed`
+(NCCL on the GPUs, gloo in the CPU tests).
+
+The reference is single-device (crates/frink-cuda/src/gpu.rs:219; "tensor,
+pipeline and multi-node parallelism" are under "Not now",
+docs/plans/north-star.md:170-174), so nothing here mirrors reference code; it
+shards the reference's tensors so that every rank's local work is the
+single-GPU path unchanged.
+
+* Column split (`shard_rows`): a rank holds whole quantized rows -- wq/wk/wv,
+  gate/up.  No communication; the activation is replicated.
+* Row split (`shard_cols`): a rank holds a K range of every row, cut on block
+  boundaries (a q8_1 run never straddles a cut, so every per-run integer is the
+  single-GPU integer) -- wo/down.  Partial outputs are all-reduced (sum, f32).
+* Experts: rank r owns experts [r E/P, (r+1) E/P).  Decode (activation
+  replicated): each rank runs the chosen experts it owns and the weighted
+  partial sums are all-reduced.  Prefill with tokens sharded over ranks: rows
+  travel to their experts' owners and back with two all-to-alls, and the source
+  combines them in routing order, which reproduces the single-GPU result
+  bit for bit.
+
+`ops` is the compute backend (`frink_b200.device` on GPUs)."""
+import numpy as np
+import torch
+import torch.distributed as dist
+
+BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 39: (17, 32)}   # kind -> (bytes, elems)
+
+
+def shard_rows(raw, kind, rows, cols, rank, world):
+    """GGUF bytes of rows [rank rows/world, (rank+1) rows/world) -> (bytes, local rows)."""
+    if rows % world:
+        raise ValueError(f"{rows} rows do not split over {world} ranks")
+    bb, be = BLOCK[kind]
+    rb = cols // be * bb
+    lo = rank * (rows // world)
+    raw = np.ascontiguousarray(raw, np.uint8).ravel()
+    return raw[lo * rb:(lo + rows // world) * rb], rows // world
+
+
+def shard_cols(raw, kind, rows, cols, rank, world):
+    """GGUF bytes of the K range [rank cols/world, (rank+1) cols/world) of every row,
+    cut on block boundaries -> (bytes, local cols).  Refused when a cut would fall
+    inside a block (e.g. 3072 columns of a 256-wide format over 8 ranks)."""
+    bb, be = BLOCK[kind]
+    nblk = cols // be
+    if nblk % world:
+        raise ValueError(f"{nblk} blocks of {be} per row do not split over {world} ranks")
+    per = nblk // world
+    m = np.ascontiguousarray(raw, np.uint8).reshape(rows, nblk, bb)
+    return np.ascontiguousarray(m[:, rank * per:(rank + 1) * per]).ravel(), per * be
+
+
+def _world(group=None):
+    if not dist.is_available() or not dist.is_initialized():
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+class ColumnParallelLinear:
+    """y_local = W[rows of this rank] x; `gather=True` all-gathers the row shards."""
+
+    def __init__(self, ops, raw, kind, rows, cols, group=None, gather=False):
+        self.ops, self.group, self.gather = ops, group, gather
+        self.rank, self.world = _world(group)
+        local, self.rows_local = shard_rows(raw, kind, rows, cols, self.rank, self.world)
+        self.rows, self.cols = rows, cols
+        self.w = ops.Weights(local, kind, self.rows_local, cols)
+
+    def __call__(self, x):
+        x2 = x if x.dim() == 2 else x[None]
+        y = self.ops.gemv(self.w, x2) if x2.shape[0] <= 8 else self.ops.gemm(self.w, x2)
+        if self.gather and self.world > 1:
+            parts = [torch.empty_like(y) for _ in range(self.world)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=1)
+        return y if x.dim() == 2 else y[0]
+
+
+class RowParallelLinear:
+    """y = sum over ranks of W[:, K range of the rank] x[K range]: one all-reduce."""
+
+    def __init__(self, ops, raw, kind, rows, cols, group=None, input_is_sharded=False):
+        self.ops, self.group, self.input_is_sharded = ops, group, input_is_sharded
+        self.rank, self.world = _world(group)
+        local, self.cols_local = shard_cols(raw, kind, rows, cols, self.rank, self.world)
+        self.rows, self.cols = rows, cols
+        self.w = ops.Weights(local, kind, rows, self.cols_local)
+
+    def __call__(self, x):
+        x2 = x if x.dim() == 2 else x[None]
+        if not self.input_is_sharded:
+            x2 = x2[:, self.rank * self.cols_local:(self.rank + 1) * self.cols_local].contiguous()
+        y = self.ops.gemv(self.w, x2) if x2.shape[0] <= 8 else self.ops.gemm(self.w, x2)
+        if self.world > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        return y if x.dim() == 2 else y[0]
+
+
+class TensorParallelFFN:
+    """SwiGLU FFN: gate/up column-split, down row-split, one all-reduce per call
+    (the dense form of `gpu::launch_dense_ffn_swiglu`, sharded)."""
+
+    def __init__(self, ops, gate_raw, up_raw, down_raw, kind_gu, kind_down, hidden, ffn, group=None):
+        self.ops = ops
+        self.gate = ColumnParallelLinear(ops, gate_raw, kind_gu, ffn, hidden, group)
+        self.up = ColumnParallelLinear(ops, up_raw, kind_gu, ffn, hidden, group)
+        self.down = RowParallelLinear(ops, down_raw, kind_down, hidden, ffn, group, input_is_sharded=True)
+
+    def __call__(self, x):
+        a = self.ops.glu(self.gate(x), self.up(x), 0)
+        return self.down(a)
+
+
+class ExpertParallelLayer:
+    """A routed layer whose experts are split over the ranks of `group`."""
+
+    def __init__(self, ops, router, gate_raw, up_raw, down_raw, kind, n_experts, hidden, ffn, k, mode=1, act=0, group=None):
+        from .prefill import RoutedLayer
+        self.ops, self.group = ops, group
+        self.rank, self.world = _world(group)
+        if n_experts % self.world:
+            raise ValueError(f"{n_experts} experts do not split over {self.world} ranks")
+        self.n_experts, self.n_local = n_experts, n_experts // self.world
+        self.e0 = self.rank * self.n_local
+        self.hidden, self.ffn, self.k = hidden, ffn, k
+        bb, be = BLOCK[kind]
+
+        def local(raw, rows, cols):
+            per = rows * (cols // be) * bb
+            raw = np.ascontiguousarray(raw, np.uint8).ravel()
+            return ops.Weights(raw[self.e0 * per:(self.e0 + self.n_local) * per], kind, rows, cols, n_mats=self.n_local)
+
+        self.layer = RoutedLayer(router, local(gate_raw, ffn, hidden), local(up_raw, ffn, hidden), local(down_raw, hidden, ffn),
+                                 k=k, mode=mode, act=act, n_experts=n_experts)
+
+    # ---- decode: activation replicated, partial combine, one all-reduce
+    def decode(self, x):
+        from .prefill import route
+        ops, L = self.ops, self.layer
+        ids, w = route(L, x, ops)                       # replicated: every rank routes the same way
+        ids1, w1 = ids.reshape(-1), w.reshape(-1)
+        mine = (ids1 >= self.e0) & (ids1 < self.e0 + self.n_local)
+        out = torch.zeros(self.hidden, dtype=torch.float32, device=x.device)
+        n = int(mine.sum().item())
+        if n:
+            lid = (ids1[mine] - self.e0).to(torch.int32).contiguous()
+            g = ops.gemv_multi(L.gate, lid, x)
+            u = ops.gemv_multi(L.up, lid, x)
+            y = ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act))
+            out = ops.moe_combine(y, None, w1[mine].contiguous()[None], 1, n)[0]
+        if self.world > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    # ---- prefill: tokens sharded over ranks, dispatch / combine all-to-all
+    def prefill(self, x_local):
+        from .prefill import experts_forward_grouped, route
+        ops, L, k, P = self.ops, self.layer, self.k, self.world
+        b = x_local.shape[0]
+        ids, w = route(L, x_local, ops)
+        ids1 = ids.reshape(-1).to(torch.int64)
+        order = torch.argsort(ids1, stable=True)        # by expert, hence by owner rank; tokens ascending inside
+        send_rows = x_local[(order // k)].contiguous()
+        send_ids = ids1[order].to(torch.int32).contiguous()
+        send_cnt = torch.bincount(ids1 // self.n_local, minlength=P).to(torch.int64)
+        recv_cnt = torch.empty_like(send_cnt)
+        if P > 1:
+            dist.all_to_all_single(recv_cnt, send_cnt, group=self.group)
+        else:
+            recv_cnt.copy_(send_cnt)
+        s_cnt, r_cnt = send_cnt.cpu().tolist(), recv_cnt.cpu().tolist()
+        n_recv = int(sum(r_cnt))
+        rows = torch.empty((n_recv, self.hidden), dtype=torch.float32, device=x_local.device)
+        rids = torch.empty(n_recv, dtype=torch.int32, device=x_local.device)
+        if P > 1:
+            dist.all_to_all_single(rows, send_rows, r_cnt, s_cnt, group=self.group)
+            dist.all_to_all_single(rids, send_ids, r_cnt, s_cnt, group=self.group)
+        else:
+            rows, rids = send_rows, send_ids
+        y = torch.empty((n_recv, self.hidden), dtype=torch.float32, device=x_local.device)
+        if n_recv:
+            lid = (rids - self.e0).to(torch.int32).reshape(-1, 1).contiguous()
+            group_off, gather, pair_of = ops.moe_permute(lid, self.n_local)
+            yp = experts_forward_grouped(L, rows, group_off, gather, n_recv, ops)
+            y = yp[pair_of.to(torch.int64)]            # back to arrival order
+        back = torch.empty((b * k, self.hidden), dtype=torch.float32, device=x_local.device)
+        if P > 1:
+            dist.all_to_all_single(back, y.contiguous(), s_cnt, r_cnt, group=self.group)
+        else:
+            back = y
+        inv = torch.empty_like(order)
+        inv[order] = torch.arange(b * k, device=order.device)
+        return ops.moe_combine(back, inv.to(torch.int32), w, b, k)

@@ -1,0 +1,87 @@
+"""The resident routed (MoE) layer: mirror of `frink_cuda::prefill::moe_device`
+(crates/frink-cuda/src/prefill/moe_device.rs:241-318 `run_device_routed`, decode;
+:320-438 `run_device_routed_batch` + :463-519 `grouped_proj`, prefill).
+
+Everything stays on the device: router logits -> top-k -> (prefill) expert
+permutation -> gate, up -> gated activation -> down -> weighted combine in
+routing order.  `ops` is the set of device calls (`frink_b200.device` by default);
+the multi-GPU layer in `parallel.py` reuses these functions with sharded experts."""
+from dataclasses import dataclass
+from typing import Any, Optional
+
+SOFTMAX, SOFTMAX_RENORM, SOFTMAX_OVER_CHOSEN = 0, 1, 2   # `DeviceGating`: fk_moe_route modes
+SILU, SWIGLU_OAI = 0, 1                                   # `GluCuda`
+
+
+@dataclass
+class RoutedLayer:
+    """`ExpertProjCuda` x3 + `RouterCuda` (crates/frink-cuda/src/prefill/mod.rs:73-315):
+    stacked expert tensors as one handle each, the f32 router, and the gating."""
+    router: Any            # f32 [n_experts, hidden]
+    gate: Any              # Weights, n_mats = n_experts, rows = ffn, cols = hidden
+    up: Any
+    down: Any              # rows = hidden, cols = ffn
+    k: int
+    mode: int = SOFTMAX_RENORM
+    act: int = SILU
+    router_bias: Optional[Any] = None
+    n_experts: Optional[int] = None
+
+    def __post_init__(self):
+        if self.n_experts is None:
+            self.n_experts = self.gate.n_mats
+
+
+def _ops(ops):
+    if ops is None:
+        from . import device
+        return device
+    return ops
+
+
+def route(layer, x, ops=None):
+    """Router logits and top-k: ids [batch, k] int32, weights [batch, k] in routing order."""
+    ops = _ops(ops)
+    logits = ops.router_logits(layer.router, x)
+    return ops.moe_route(logits, layer.k, layer.mode, layer.router_bias)
+
+
+def run_device_routed(layer, x, ops=None):
+    """Decode: one token `x` [hidden] (or a few, [b, hidden], one after another).
+    gate and up are one indexed launch each with the k chosen experts as slots."""
+    ops = _ops(ops)
+    if x.dim() == 2:
+        import torch
+        return torch.stack([run_device_routed(layer, x[t], ops) for t in range(x.shape[0])])
+    ids, w = route(layer, x, ops)
+    ids1 = ids.reshape(-1)
+    g = ops.gemv_multi(layer.gate, ids1, x)
+    u = ops.gemv_multi(layer.up, ids1, x)
+    a = ops.glu(g, u, layer.act)
+    y = ops.gemv_multi(layer.down, ids1, a)
+    return ops.moe_combine(y, None, w, 1, layer.k)[0]
+
+
+def experts_forward_grouped(layer, x, group_off, gather, pairs, ops=None):
+    """gate/up/GLU/down for `pairs` permuted rows grouped by expert (`grouped_proj` x3)."""
+    ops = _ops(ops)
+    g = ops.gemm_grouped(layer.gate, group_off, gather, x, pairs)
+    u = ops.gemm_grouped(layer.up, group_off, gather, x, pairs)
+    a = ops.glu(g, u, layer.act)
+    return ops.gemm_grouped(layer.down, group_off, None, a, pairs)
+
+
+def run_device_routed_batch(layer, x, ops=None):
+    """Prefill: x [batch, hidden].  Pairs are grouped by expert (tokens ascending
+    inside a group), each projection is ONE grouped GEMM over all experts."""
+    ops = _ops(ops)
+    batch = x.shape[0]
+    ids, w = route(layer, x, ops)
+    group_off, gather, pair_of = ops.moe_permute(ids, layer.n_experts)
+    y = experts_forward_grouped(layer, x, group_off, gather, batch * layer.k, ops)
+    return ops.moe_combine(y, pair_of, w, batch, layer.k)
+
+
+def routed_batch_supported(batch):
+    """`prefill::routed_batch_supported`: from this batch on the grouped GEMM path is taken."""
+    return batch > 8

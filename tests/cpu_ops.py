@@ -1,0 +1,79 @@
+"""A CPU stand-in for `frink_b200.device` built on the oracle, for the tests of
+the host-side sharding logic (`frink_b200.parallel`) under gloo.  TEST ONLY."""
+import numpy as np
+import torch
+
+from oracle import frink_oracle as fo
+
+
+class Weights:
+    def __init__(self, raw, kind, rows, cols, n_mats=1, device=None):
+        self.raw = np.ascontiguousarray(raw, np.uint8).ravel().copy()
+        self.kind, self.rows, self.cols, self.n_mats = kind, rows, cols, n_mats
+        self.per = rows * fo.row_bytes(kind, cols)
+
+    def mat(self, m):
+        return self.raw[m * self.per:(m + 1) * self.per]
+
+
+def _mm(w, m, x):
+    x = np.ascontiguousarray(x, np.float32).reshape(-1, w.cols)
+    return fo.matmul_f64(w.kind, w.mat(m), w.rows, w.cols, fo.q8_1_round(x), threads=1).astype(np.float32)
+
+
+def gemv(w, x, mat=0, out=None):
+    y = torch.from_numpy(_mm(w, mat, x.numpy()))
+    return y if x.dim() > 1 else y[0]
+
+
+def gemm(w, x, mat=0, out=None):
+    return torch.from_numpy(_mm(w, mat, x.numpy()))
+
+
+def gemv_multi(w, ids, x, out=None):
+    xs = x.numpy()
+    return torch.from_numpy(np.stack([_mm(w, int(e), xs if xs.ndim == 1 else xs[j])[0] for j, e in enumerate(ids.tolist())]))
+
+
+def gemm_grouped(w, group_off, gather, x, pairs, out=None):
+    off = group_off.tolist()
+    xs = x.numpy()
+    y = np.zeros((pairs, w.rows), np.float32)
+    for e in range(w.n_mats):
+        lo, hi = off[e], off[e + 1]
+        if hi > lo:
+            idx = gather.numpy()[lo:hi] if gather is not None else np.arange(lo, hi)
+            y[lo:hi] = _mm(w, e, xs[idx])
+    return torch.from_numpy(y)
+
+
+def glu(g, u, act=0, out=None):
+    f = fo.silu_mul if act == 0 else fo.swiglu_oai
+    return torch.from_numpy(f(g.numpy().ravel(), u.numpy().ravel()).reshape(g.shape))
+
+
+def router_logits(router, x):
+    x2 = x if x.dim() == 2 else x[None]
+    return (x2.double() @ router.double().T).float()
+
+
+def moe_route(logits, k, mode, bias=None):
+    l2 = logits if logits.dim() == 2 else logits[None]
+    ids, w = fo.route_top_k(l2.numpy(), k, mode, None if bias is None else bias.numpy())
+    return torch.from_numpy(ids), torch.from_numpy(w)
+
+
+def moe_permute(ids, n_experts):
+    flat = ids.numpy().ravel()
+    k = ids.shape[-1]
+    order = np.argsort(flat, kind="stable")
+    off = np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=n_experts))]).astype(np.int32)
+    pair_of = np.empty(flat.size, np.int32)
+    pair_of[order] = np.arange(flat.size, dtype=np.int32)
+    return torch.from_numpy(off), torch.from_numpy((order // k).astype(np.int32)), torch.from_numpy(pair_of)
+
+
+def moe_combine(y, pair_of, w, batch, k, out=None):
+    ys, ws = y.numpy(), w.numpy().reshape(batch, k)
+    po = pair_of.numpy() if pair_of is not None else np.arange(batch * k)
+    return torch.from_numpy(np.stack([fo.combine(ys[po[t * k:(t + 1) * k]], ws[t]) for t in range(batch)]))

@@ -1,0 +1,61 @@
+"""The routed MoE layer (decode and prefill forms) against the oracle's
+composition of the reference's host functions: route_top_k -> per expert
+gate/up -> SwiGLU -> down -> combine in routing order."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import frink_oracle as fo
+from tests.helpers import max_abs_over_inf, rel_l2, synth_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_layer(raws, kind, router, x, k, mode, hidden, ffn, act):
+    """crates/frink-moe/src/lib.rs:567 (route), :1068 (run_expert), :1246 (combine), with
+    every matvec taken on the q8_1-rounded activation the device reads."""
+    logits = (x.astype(np.float32) @ router.T.astype(np.float32)).astype(np.float32)
+    ids, w = fo.route_top_k(logits, k, mode)
+    out = np.zeros((x.shape[0], hidden), np.float32)
+    for t in range(x.shape[0]):
+        ys = []
+        for e in ids[t]:
+            g = fo.matmul_f64(kind, raws["gate"][e], ffn, hidden, fo.q8_1_round(x[t]))[0].astype(np.float32)
+            u = fo.matmul_f64(kind, raws["up"][e], ffn, hidden, fo.q8_1_round(x[t]))[0].astype(np.float32)
+            a = fo.silu_mul(g, u) if act == 0 else fo.swiglu_oai(g, u)
+            ys.append(fo.matmul_f64(kind, raws["down"][e], hidden, ffn, fo.q8_1_round(a))[0].astype(np.float32))
+        out[t] = fo.combine(np.stack(ys), w[t])
+    return ids, out
+
+
+def build_layer(kind, n_exp, hidden, ffn, k, mode, act, seed):
+    from frink_b200 import device, prefill
+    rng = np.random.default_rng(seed)
+    raws = {n: [fo.encode(kind, synth_weights(r, c, seed + 10 * i + j)) for j in range(n_exp)]
+            for i, (n, r, c) in enumerate((("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)))}
+    router = (rng.standard_normal((n_exp, hidden)) * 0.5).astype(np.float32)
+    mk = lambda n, r, c: device.Weights(np.concatenate(raws[n]), kind, r, c, n_mats=n_exp)
+    layer = prefill.RoutedLayer(torch.from_numpy(router).cuda(), mk("gate", ffn, hidden), mk("up", ffn, hidden), mk("down", hidden, ffn),
+                                k=k, mode=mode, act=act)
+    return raws, router, layer
+
+
+@pytest.mark.parametrize("kind,hidden,ffn,act,mode", [(fo.Q4_K, 512, 768, 0, 1), (fo.MXFP4, 576, 576, 1, 2), (fo.Q6_K, 256, 512, 0, 0)])
+def test_routed_layer_decode_and_prefill(kind, hidden, ffn, act, mode):
+    from frink_b200 import device, prefill
+    n_exp, k = 16, 4
+    raws, router, layer = build_layer(kind, n_exp, hidden, ffn, k, mode, act, 900)
+    rng = np.random.default_rng(4)
+    x = rng.standard_normal((40, hidden)).astype(np.float32)
+    ids_want, want = oracle_layer(raws, kind, router, x, k, mode, hidden, ffn, act)
+    xd = torch.from_numpy(x).cuda()
+    ids, _ = prefill.route(layer, xd)
+    assert np.array_equal(ids.cpu().numpy(), ids_want)
+    got_b = prefill.run_device_routed_batch(layer, xd).cpu().numpy()
+    torch.cuda.synchronize()
+    assert device.device_error() == 0
+    assert rel_l2(got_b, want) <= 1e-3 and max_abs_over_inf(got_b, want) <= 2e-3
+    got_d = prefill.run_device_routed(layer, xd[:3]).cpu().numpy()
+    assert rel_l2(got_d, want[:3]) <= 1e-3 and max_abs_over_inf(got_d, want[:3]) <= 2e-3
+    # decode and prefill read the same integers: they agree to f32 summation noise
+    assert rel_l2(got_d, got_b[:3]) <= 5e-6

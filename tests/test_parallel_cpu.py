@@ -1,0 +1,109 @@
+"""Host-side sharding logic of `frink_b200.parallel` on CPU: world_size-2 gloo
+ranks with the oracle standing in for the device kernels.  Checks that the
+sharded result equals the unsharded one (bit-exact where the design promises it)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import frink_oracle as fo
+from tests.helpers import rel_l2, synth_weights
+
+
+def _run(rank, world, port, fn, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ret[rank] = fn(rank, world)
+    finally:
+        dist.destroy_process_group()
+
+
+def spawn(fn, world=2):
+    port = 29500 + os.getpid() % 2000
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_run, args=(world, port, fn, ret), nprocs=world, join=True)
+    return [ret[r] for r in range(world)]
+
+
+def test_shard_helpers():
+    from frink_b200 import parallel
+    raw = fo.encode(fo.Q4_K, synth_weights(8, 1024, 1))
+    a, r = parallel.shard_rows(raw, fo.Q4_K, 8, 1024, 1, 2)
+    assert r == 4 and np.array_equal(a, raw[4 * 576:])
+    b, c = parallel.shard_cols(raw, fo.Q4_K, 8, 1024, 1, 2)
+    assert c == 512 and np.array_equal(b.reshape(8, 288), raw.reshape(8, 576)[:, 288:])
+    # a K shard dequantizes to the K range of the full matrix
+    assert np.array_equal(fo.dequant(fo.Q4_K, b).reshape(8, 512), fo.dequant(fo.Q4_K, raw).reshape(8, 1024)[:, 512:])
+    with pytest.raises(ValueError):
+        parallel.shard_cols(fo.encode(fo.Q4_K, synth_weights(2, 768, 1)), fo.Q4_K, 2, 768, 0, 2)   # 3 blocks over 2 ranks
+    with pytest.raises(ValueError):
+        parallel.shard_rows(raw, fo.Q4_K, 8, 1024, 0, 3)
+
+
+def _tp_case(rank, world):
+    from frink_b200 import parallel
+    from tests import cpu_ops
+    hidden, ffn = 512, 1024
+    g = fo.encode(fo.Q4_K, synth_weights(ffn, hidden, 11))
+    u = fo.encode(fo.Q4_K, synth_weights(ffn, hidden, 12))
+    d = fo.encode(fo.Q6_K, synth_weights(hidden, ffn, 13))
+    x = torch.from_numpy(np.random.default_rng(5).standard_normal((3, hidden)).astype(np.float32))
+    col = parallel.ColumnParallelLinear(cpu_ops, g, fo.Q4_K, ffn, hidden, gather=True)
+    y_col = col(x).numpy()
+    ffn_tp = parallel.TensorParallelFFN(cpu_ops, g, u, d, fo.Q4_K, fo.Q6_K, hidden, ffn)
+    y_ffn = ffn_tp(x).numpy()
+    return y_col, y_ffn
+
+
+def test_tensor_parallel_matches_single_rank():
+    from tests import cpu_ops
+    hidden, ffn = 512, 1024
+    g = fo.encode(fo.Q4_K, synth_weights(ffn, hidden, 11))
+    u = fo.encode(fo.Q4_K, synth_weights(ffn, hidden, 12))
+    d = fo.encode(fo.Q6_K, synth_weights(hidden, ffn, 13))
+    x = torch.from_numpy(np.random.default_rng(5).standard_normal((3, hidden)).astype(np.float32))
+    wg, wu, wd = cpu_ops.Weights(g, fo.Q4_K, ffn, hidden), cpu_ops.Weights(u, fo.Q4_K, ffn, hidden), cpu_ops.Weights(d, fo.Q6_K, hidden, ffn)
+    want_col = cpu_ops.gemv(wg, x).numpy()
+    want_ffn = cpu_ops.gemv(wd, cpu_ops.glu(cpu_ops.gemv(wg, x), cpu_ops.gemv(wu, x))).numpy()
+    for y_col, y_ffn in spawn(_tp_case):
+        assert np.array_equal(y_col, want_col)                 # whole rows: nothing changes
+        assert rel_l2(y_ffn, want_ffn) <= 1e-5                # K split: only the f32 summation order
+    
+
+def _ep_case(rank, world):
+    from frink_b200 import parallel
+    from tests import cpu_ops
+    n_exp, hidden, ffn, k = 8, 256, 512, 2
+    raws = {n: np.concatenate([fo.encode(fo.Q4_K, synth_weights(r, c, 100 * i + e)) for e in range(n_exp)])
+            for i, (n, r, c) in enumerate((("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)))}
+    router = torch.from_numpy((np.random.default_rng(1).standard_normal((n_exp, hidden)) * 0.5).astype(np.float32))
+    ep = parallel.ExpertParallelLayer(cpu_ops, router, raws["gate"], raws["up"], raws["down"], fo.Q4_K, n_exp, hidden, ffn, k)
+    x = torch.from_numpy(np.random.default_rng(2).standard_normal((6, hidden)).astype(np.float32))
+    dec = ep.decode(x[0]).numpy()
+    per = 6 // world
+    pre = ep.prefill(x[rank * per:(rank + 1) * per]).numpy()
+    return dec, pre
+
+
+def test_expert_parallel_matches_single_rank():
+    from frink_b200 import prefill
+    from tests import cpu_ops
+    n_exp, hidden, ffn, k = 8, 256, 512, 2
+    raws = {n: np.concatenate([fo.encode(fo.Q4_K, synth_weights(r, c, 100 * i + e)) for e in range(n_exp)])
+            for i, (n, r, c) in enumerate((("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)))}
+    router = torch.from_numpy((np.random.default_rng(1).standard_normal((n_exp, hidden)) * 0.5).astype(np.float32))
+    mk = lambda n, r, c: cpu_ops.Weights(raws[n], fo.Q4_K, r, c, n_mats=n_exp)
+    layer = prefill.RoutedLayer(router, mk("gate", ffn, hidden), mk("up", ffn, hidden), mk("down", hidden, ffn), k=k, mode=1)
+    x = torch.from_numpy(np.random.default_rng(2).standard_normal((6, hidden)).astype(np.float32))
+    want = prefill.run_device_routed_batch(layer, x, cpu_ops).numpy()
+    want_dec = prefill.run_device_routed(layer, x[0], cpu_ops).numpy()
+    assert rel_l2(want_dec, want[0]) <= 1e-6
+    res = spawn(_ep_case)
+    for rank, (dec, pre) in enumerate(res):
+        assert rel_l2(dec, want_dec) <= 1e-6                   # partial sums all-reduced: order of two adds
+        assert np.array_equal(pre, want[rank * 3:(rank + 1) * 3])   # dispatch/combine keeps the single-rank order: same bits
