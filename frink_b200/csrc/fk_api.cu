@@ -106,29 +106,36 @@ size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 // GGUF blocks -> planes (layouts in fk_common.cuh).  One thread per block; run
 // once per tensor.
-__global__ void split_q8_0(const uint8_t* __restrict__ src, size_t n_blocks, int8_t* __restrict__ qs, uint16_t* __restrict__ d) {
+__global__ void split_q8_0(const uint8_t* __restrict__ src, size_t n_blocks, int bpr, int8_t* __restrict__ qs, size_t qs_stride,
+                           uint8_t* __restrict__ d, size_t d_stride) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
+    const size_t row = b / bpr, i0 = b % bpr;
     const uint8_t* s = src + b * 34;
-    d[b] = (uint16_t)(s[0] | (s[1] << 8));
-    for (int i = 0; i < 32; i++) qs[b * 32 + i] = (int8_t)s[2 + i];
+    *(uint16_t*)(d + row * d_stride + i0 * 2) = (uint16_t)(s[0] | (s[1] << 8));
+    int8_t* q = qs + row * qs_stride + i0 * 32;
+    for (int i = 0; i < 32; i++) q[i] = (int8_t)s[2 + i];
 }
-__global__ void split_q6_k(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ ql, uint8_t* __restrict__ qh,
-                           int8_t* __restrict__ sc, uint16_t* __restrict__ d) {
+__global__ void split_q6_k(const uint8_t* __restrict__ src, size_t n_blocks, int bpr, uint8_t* __restrict__ ql, size_t ql_stride,
+                           uint8_t* __restrict__ qh, size_t qh_stride, uint8_t* __restrict__ sc, size_t sc_stride,
+                           uint8_t* __restrict__ d, size_t d_stride) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
+    const size_t row = b / bpr, i0 = b % bpr;
     const uint8_t* s = src + b * 210;
-    for (int i = 0; i < 128; i++) ql[b * 128 + i] = s[i];
-    for (int i = 0; i < 64; i++) qh[b * 64 + i] = s[128 + i];
-    for (int i = 0; i < 16; i++) sc[b * 16 + i] = (int8_t)s[192 + i];
-    d[b] = (uint16_t)(s[208] | (s[209] << 8));
+    for (int i = 0; i < 128; i++) ql[row * ql_stride + i0 * 128 + i] = s[i];
+    for (int i = 0; i < 64; i++) qh[row * qh_stride + i0 * 64 + i] = s[128 + i];
+    for (int i = 0; i < 16; i++) sc[row * sc_stride + i0 * 16 + i] = s[192 + i];
+    *(uint16_t*)(d + row * d_stride + i0 * 2) = (uint16_t)(s[208] | (s[209] << 8));
 }
-__global__ void split_mxfp4(const uint8_t* __restrict__ src, size_t n_blocks, uint8_t* __restrict__ codes, uint8_t* __restrict__ e) {
+__global__ void split_mxfp4(const uint8_t* __restrict__ src, size_t n_blocks, int bpr, uint8_t* __restrict__ codes, size_t c_stride,
+                            uint8_t* __restrict__ e, size_t e_stride) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
+    const size_t row = b / bpr, i0 = b % bpr;
     const uint8_t* s = src + b * 17;
-    e[b] = s[0];
-    for (int i = 0; i < 16; i++) codes[b * 16 + i] = s[1 + i];
+    e[row * e_stride + i0] = s[0];
+    for (int i = 0; i < 16; i++) codes[row * c_stride + i0 * 16 + i] = s[1 + i];
 }
 
 int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n_mats, int rows, int cols,
@@ -144,17 +151,20 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
     w->gguf_bytes = len;
     w->device = ctx->device;
     const size_t n = (size_t)rows * cols;
-    size_t plane[4] = {0, 0, 0, 0};
+    auto pad16 = [](size_t v) { return (v + 15) & ~(size_t)15; };
+    size_t stride[4] = {0, 0, 0, 0};
+    const size_t c = (size_t)cols;
     switch (kind) {
-        case FK_Q4_K: plane[0] = (size_t)rows * w->gguf_row_bytes; break;
-        case FK_Q8_0: plane[0] = n; plane[1] = n / 32 * 2; break;
-        case FK_Q6_K: plane[0] = n / 2; plane[1] = n / 4; plane[2] = n / 16; plane[3] = n / 256 * 2; break;
-        case FK_MXFP4: plane[0] = n / 2; plane[1] = n / 32; break;
+        case FK_Q4_K: stride[0] = w->gguf_row_bytes; break;
+        case FK_Q8_0: stride[0] = c; stride[1] = pad16(c / 16); break;
+        case FK_Q6_K: stride[0] = c / 2; stride[1] = c / 4; stride[2] = c / 16; stride[3] = pad16(c / 256 * 2); break;
+        case FK_MXFP4: stride[0] = c / 2; stride[1] = pad16(c / 32); break;
     }
     size_t off = 0;
     for (int i = 0; i < 4; i++) {
         w->plane_off[i] = off;
-        off += align256(plane[i]);
+        w->plane_stride[i] = stride[i];
+        off += align256((size_t)rows * stride[i]) + (stride[i] ? 256 : 0);   // slack: rounded-up copies may read past the last row
     }
     w->mat_stride = off;
     cudaError_t e = cudaMalloc(&w->dev, (size_t)n_mats * w->mat_stride);
@@ -164,7 +174,9 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
     }
     const size_t mat_raw = (size_t)rows * w->gguf_row_bytes;
     const size_t blocks = n / be;
+    const int bpr = cols / be;
     const unsigned grid = (unsigned)((blocks + 255) / 256);
+    e = cudaMemsetAsync(w->dev, 0, (size_t)n_mats * w->mat_stride, st);   // row padding of the scale planes reads as zeros
     for (int m = 0; m < n_mats && e == cudaSuccess; m++) {
         const uint8_t* src = raw_dev + (size_t)m * mat_raw;
         uint8_t* dst = w->dev + (size_t)m * w->mat_stride;
@@ -173,14 +185,17 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
                 e = cudaMemcpyAsync(dst, src, mat_raw, cudaMemcpyDeviceToDevice, st);
                 break;
             case FK_Q8_0:
-                split_q8_0<<<grid, 256, 0, st>>>(src, blocks, (int8_t*)(dst + w->plane_off[0]), (uint16_t*)(dst + w->plane_off[1]));
+                split_q8_0<<<grid, 256, 0, st>>>(src, blocks, bpr, (int8_t*)(dst + w->plane_off[0]), w->plane_stride[0],
+                                                 dst + w->plane_off[1], w->plane_stride[1]);
                 break;
             case FK_Q6_K:
-                split_q6_k<<<grid, 256, 0, st>>>(src, blocks, dst + w->plane_off[0], dst + w->plane_off[1],
-                                                 (int8_t*)(dst + w->plane_off[2]), (uint16_t*)(dst + w->plane_off[3]));
+                split_q6_k<<<grid, 256, 0, st>>>(src, blocks, bpr, dst + w->plane_off[0], w->plane_stride[0], dst + w->plane_off[1],
+                                                 w->plane_stride[1], dst + w->plane_off[2], w->plane_stride[2], dst + w->plane_off[3],
+                                                 w->plane_stride[3]);
                 break;
             case FK_MXFP4:
-                split_mxfp4<<<grid, 256, 0, st>>>(src, blocks, dst + w->plane_off[0], dst + w->plane_off[1]);
+                split_mxfp4<<<grid, 256, 0, st>>>(src, blocks, bpr, dst + w->plane_off[0], w->plane_stride[0], dst + w->plane_off[1],
+                                                  w->plane_stride[1]);
                 break;
         }
         if (e == cudaSuccess) e = cudaGetLastError();

@@ -27,9 +27,11 @@
 //   Q6_K : ql   [rows][cols/2]    u8        | qh [rows][cols/4]   u8
 //          sc   [rows][cols/16]   int8      | d  [rows][cols/256] f16
 //   MXFP4: code [rows][cols/2]    u8        | e  [rows][cols/32]  u8 (E8M0)
-// Every plane starts on a 256-byte boundary.  Bytes inside a plane keep the
-// GGUF block's own order, so the nibble/bit pairing rules of the formats are
-// unchanged.
+// Every plane starts on a 256-byte boundary and every plane's row stride is a
+// multiple of 16 bytes (the small scale planes are padded per row), so any row
+// range of any plane can be moved with 16-byte loads or bulk copies.  Bytes
+// inside a plane keep the GGUF block's own order, so the nibble/bit pairing
+// rules of the formats are unchanged.
 struct fk_weight_s {
     int kind;
     int n_mats;
@@ -39,6 +41,7 @@ struct fk_weight_s {
     size_t gguf_row_bytes;  // bytes of one row in GGUF form
     size_t mat_stride;      // device bytes between consecutive matrices
     size_t plane_off[4];    // byte offset of each plane inside one matrix
+    size_t plane_stride[4]; // bytes between consecutive rows of each plane (multiples of 16)
     uint8_t* dev;           // device allocation (n_mats * mat_stride)
     int device;
 };

@@ -37,6 +37,7 @@ struct GemmArgs {
     const uint8_t* w;         // matrix 0 of the weight handle
     size_t mat_stride;
     size_t plane_off[4];
+    size_t plane_stride[4];
     int kind, rows, cols;
     int mat;                  // dense: the matrix; grouped: ignored
     const int* tile_expert;   // grouped: expert of each token tile (nullptr = dense)
@@ -182,20 +183,20 @@ __device__ __forceinline__ void load_wscales(const GemmArgs& a, const uint8_t* w
             if (kb0 + j < nkb) ws[j] = {d * (float)sc, dmin * (float)m};
         }
     } else if (KIND == FK_Q8_0) {
-        const uint16_t* dp = (const uint16_t*)(wb + a.plane_off[1]) + (size_t)row * (a.cols >> 5);
+        const uint16_t* dp = (const uint16_t*)(wb + a.plane_off[1] + (size_t)row * a.plane_stride[1]);
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (kb0 + j < nkb) ws[j].dw = fk_h2f(__ldg(dp + kb0 + j));
     } else if (KIND == FK_MXFP4) {
-        const uint8_t* ep = wb + a.plane_off[1] + (size_t)row * (a.cols >> 5);
+        const uint8_t* ep = wb + a.plane_off[1] + (size_t)row * a.plane_stride[1];
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (kb0 + j < nkb) ws[j].dw = e8m0_half(__ldg(ep + kb0 + j));
     } else {  // FK_Q6_K: `row` = 2 * weight row + half; its scale of run kb is sc[2 * kb + half]
         const int wrow = row >> 1, half = row & 1;
         const int sb = kb0 >> 3;
-        const float d = fk_h2f(__ldg((const uint16_t*)(wb + a.plane_off[3]) + (size_t)wrow * (a.cols >> 8) + sb));
-        const int8_t* sc = (const int8_t*)(wb + a.plane_off[2]) + (size_t)wrow * (a.cols >> 4) + 2 * kb0 + half;
+        const float d = fk_h2f(__ldg((const uint16_t*)(wb + a.plane_off[3] + (size_t)wrow * a.plane_stride[3]) + sb));
+        const int8_t* sc = (const int8_t*)(wb + a.plane_off[2] + (size_t)wrow * a.plane_stride[2]) + 2 * kb0 + half;
 #pragma unroll
         for (int j = 0; j < 4; j++)
             if (kb0 + j < nkb) ws[j].dw = d * (float)__ldg(sc + 2 * j);
@@ -691,7 +692,7 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
     GemmArgs a;
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
-    for (int i = 0; i < 4; i++) a.plane_off[i] = w->plane_off[i];
+    for (int i = 0; i < 4; i++) { a.plane_off[i] = w->plane_off[i]; a.plane_stride[i] = w->plane_stride[i]; }
     a.kind = w->kind;
     a.rows = w->rows;
     a.cols = w->cols;
@@ -799,7 +800,7 @@ FK_EXPORT int fk_gemm_static(fk_ctx* ctx, void* stream, fk_weight w, int mat, co
     GemmArgs a;
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
-    for (int i = 0; i < 4; i++) a.plane_off[i] = w->plane_off[i];
+    for (int i = 0; i < 4; i++) { a.plane_off[i] = w->plane_off[i]; a.plane_stride[i] = w->plane_stride[i]; }
     a.kind = w->kind;
     a.rows = w->rows;
     a.cols = w->cols;

@@ -1,27 +1,41 @@
 // Decode GEMV (batch 1..8) over resident quantized weights, and its indexed
 // (one expert per slot) form.
 //
-// Shape of the kernel: a persistent grid of 512-thread blocks.  Each block
-// first quantizes the activations to q8_1 into shared memory (one warp per run
-// of 32 values, the rule of fk_q8_1_lane), then its warps walk pairs of weight
-// rows.  A lane owns one 16-byte piece of packed weights per row and trip --
-// every global load is a 128-bit load of consecutive addresses across the warp
-// -- unpacks it in registers, takes exact int32 dot products against the int8
-// activations with dp4a, scales them into an f32 accumulator per (row, batch
-// column), and the warp reduces with shuffles.  Weight bytes are read once for
-// the whole batch.
+// The kernel is HBM-bound, so its shape is set by how many weight bytes it can
+// keep in flight.  One persistent block of 16 warps per SM.  Every warp owns a
+// private ring of shared-memory stages; a stage holds the packed bytes of two
+// weight rows for a range of K, brought in by bulk asynchronous copies
+// (cp.async.bulk, completion counted on the stage's own mbarrier).  A warp
+// issues the copies for all of its stages before anything else, so a block's
+// whole share of a small matrix (96 KB per SM for 8192 x 3072 Q4_K) is
+// requested in its first cycles; no register is tied up by bytes in flight and
+// no block-wide synchronisation is needed, because the warp that fills a stage
+// is the warp that drains it.  While the copies fly the block quantizes the
+// activations to q8_1 into shared memory (a float4 per thread, eight lanes per
+// run of 32 values, the rule of fk_q8_1_lane; all loads issued before any use).
+//
+// Draining a stage: a lane owns one 16-byte piece of packed weights per row and
+// trip, unpacks it in registers, takes exact int32 dot products against the
+// int8 activations with dp4a, scales them into an f32 accumulator per (row,
+// batch column); the warp reduces with shuffles.  Weight bytes are read once
+// for the whole batch.  Every wait on an mbarrier is bounded and raises the
+// context's error word instead of spinning forever.
 #include "fk_common.cuh"
 
 namespace {
 
 constexpr int GEMV_THREADS = 512;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int R = 2;  // weight rows a warp carries at once
+constexpr int R = 2;            // weight rows per stage
+constexpr int MAX_STAGES = 4;
+constexpr int SMEM_BUDGET = 225 * 1024;
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 struct GemvArgs {
     const uint8_t* w;
     size_t mat_stride;
     size_t plane_off[4];
+    size_t plane_stride[4];
     const int* ids;
     int mat;
     const float* x;
@@ -29,20 +43,68 @@ struct GemvArgs {
     float* y;
     int rows, cols, batch;
     int32_t* isums;
+    int* err;
+    // staging plan (host-computed)
+    int trips_per_chunk;   // trips of K a stage covers
+    int nchunks;           // stages per row pair
+    int nstages;           // ring depth
+    int stage_bytes;       // bytes of one stage (R rows, all planes)
+    int row_bytes_stage;   // bytes of one row inside a stage
+    int act_bytes;         // activation region at the start of shared memory
 };
 
-__device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
+// ------------------------------------------------------------------ PTX glue
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return;
+    atomicCAS(err, 0, 50);   // gave up: results are garbage from here, the host reads the word
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int lds_s8(uint32_t addr) {
+    int v;
+    asm volatile("ld.shared.s8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
 __device__ __forceinline__ int dp4a4(const uint4& a, const int4& b) {
     int s = __dp4a((int)a.x, b.x, 0);
     s = __dp4a((int)a.y, b.y, s);
     s = __dp4a((int)a.z, b.z, s);
     return __dp4a((int)a.w, b.w, s);
 }
+// Exact int32 -> f32 for |v| < 2^22 on the integer and FP32 pipes (no conversion unit).
+__device__ __forceinline__ float i2f(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
 // Four E2M1 codes (the four nibbles of the low 16 bits of `w`) to their doubled
 // int8 values {0,1,2,3,4,6,8,12} with sign, one per byte, in nibble order.
 __device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
@@ -59,18 +121,26 @@ __device__ __forceinline__ float e8m0_half(uint32_t e) {
 }
 
 // ---------------------------------------------------------------------------
-// A "piece" is what one lane holds of one weight row for one trip of the warp
-// along K: 16 bytes of packed weights plus the scale words that go with them.
-// load() only issues global loads (so a batch of pieces can be in flight
-// together); eat() unpacks and accumulates.
-//   Q4_K : 8 lanes per 144-byte super-block, a trip covers 4 super-blocks.
-//          Lane c owns quant bytes [16c, 16c+16): low nibbles are 16 weights of
-//          sub-block 2g, high nibbles 16 weights of sub-block 2g+1 (g = c/2).
-//   Q6_K : 8 lanes per super-block; lane c owns ql bytes [16c, 16c+16) and the
-//          matching 16 qh bytes: two runs of 16 weights (groups g_lo, g_lo+4).
-//   Q8_0 : a lane owns 16 int8 (half a block); a trip covers 512 weights.
-//   MXFP4: a lane owns one block's 16 code bytes; a trip covers 1024 weights.
-struct Smem {
+// Per-kind geometry.  A "trip" is what one pass of the 32 lanes covers of a row:
+//   Q4_K : 4 super-blocks (1024 weights); 8 lanes per 144-byte block; lane c owns
+//          quant bytes [16c, 16c+16): low nibbles are 16 weights of sub-block 2g,
+//          high nibbles 16 weights of sub-block 2g+1 (g = c/2).
+//   Q6_K : 4 super-blocks; lane c of a block owns ql bytes [16c, 16c+16) and the
+//          matching 16 qh bytes: two runs of 16 weights (groups g_lo, g_lo + 4).
+//   Q8_0 : 512 weights; a lane owns 16 int8 (half a block).
+//   MXFP4: 1024 weights; a lane owns one block's 16 code bytes.
+// PLANES / TB: bytes of each plane one trip of one row occupies in a stage
+// (Q6_K's 4th plane, the f16 super-scales, is staged as the whole row).
+template <int KIND> struct Geo;
+template <> struct Geo<FK_Q4_K> { static constexpr int PLANES = 1, TRIP_COLS = 1024, TB0 = 576, TB1 = 0, TB2 = 0; };
+template <> struct Geo<FK_Q8_0> { static constexpr int PLANES = 2, TRIP_COLS = 512, TB0 = 512, TB1 = 32, TB2 = 0; };
+template <> struct Geo<FK_Q6_K> { static constexpr int PLANES = 4, TRIP_COLS = 1024, TB0 = 512, TB1 = 256, TB2 = 64; };
+template <> struct Geo<FK_MXFP4> { static constexpr int PLANES = 2, TRIP_COLS = 1024, TB0 = 512, TB1 = 32, TB2 = 0; };
+template <int KIND> __host__ __device__ constexpr int trip_bytes(int p) {
+    return p == 0 ? Geo<KIND>::TB0 : (p == 1 ? Geo<KIND>::TB1 : (p == 2 ? Geo<KIND>::TB2 : 0));
+}
+
+struct Act {
     const int8_t* q;   // [NB][cols]
     const float* d;    // [NB][cols/32]
     const float* s;    // Q4_K: d * run sum
@@ -78,27 +148,33 @@ struct Smem {
     int cols, nb32;
 };
 
-template <int KIND> struct Piece;
+// Where the pieces of (row r of the stage, plane p) start inside a stage.
+template <int KIND>
+__device__ __forceinline__ uint32_t plane_at(const GemvArgs& a, uint32_t stage, int r, int p) {
+    uint32_t off = stage + r * a.row_bytes_stage;
+    if (p > 0) off += Geo<KIND>::TB0 * a.trips_per_chunk;
+    if (p > 1) off += Geo<KIND>::TB1 * a.trips_per_chunk;
+    if (p > 2) off += Geo<KIND>::TB2 * a.trips_per_chunk;
+    return off;
+}
 
-template <> struct Piece<FK_Q4_K> {
-    uint4 hd, wq;
-    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 8) + 3) >> 2; }
-    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+// One lane's share of one row for one trip: unpack, dot, scale.  `trip` is the
+// trip's index in the row (it places the activations), `tl` its index inside the
+// stage (it places the weights).
+template <int KIND, int NB, bool DUMP>
+__device__ __forceinline__ void eat(const GemvArgs& a, const Act& sm, uint32_t stage, int r, int row, bool row_ok, int trip, int tl,
+                                    int lane, float* acc) {
+    if (KIND == FK_Q4_K) {
         const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
-        hd = make_uint4(0, 0, 0, 0);
-        wq = make_uint4(0, 0, 0, 0);
-        if (row_ok && sb < nsb) {
-            const uint8_t* p = wb + ((size_t)row * nsb + sb) * 144;
-            hd = ldg16(p);
-            wq = ldg16(p + 16 + 16 * (lane & 7));
-        }
-    }
-    template <int NB, bool DUMP>
-    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
-        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
-        const bool live = sb < nsb;
-        const int sbs = live ? sb : 0;
+        const bool live = sb < nsb && row_ok;
+        const int sbs = sb < nsb ? sb : 0;
         const int c = lane & 7, g = c >> 1, h = c & 1;
+        const uint32_t blk = stage + r * a.row_bytes_stage + (tl * 4 + (lane >> 3)) * 144;
+        uint4 hd = make_uint4(0, 0, 0, 0), wq = hd;
+        if (live) {
+            hd = lds16(blk);
+            wq = lds16(blk + 16 + 16 * c);
+        }
         // 6-bit scales and mins of sub-blocks 2g, 2g+1, two at a time from the
         // 16-bit words of the 12 packed bytes
         const uint32_t w0 = hd.y, w1 = hd.z, w2 = hd.w;
@@ -114,10 +190,11 @@ template <> struct Piece<FK_Q4_K> {
             sc2 = (A & 0x0F0F) | ((B & 0xC0C0) >> 2);
             m2 = ((A >> 4) & 0x0F0F) | ((C & 0xC0C0) >> 2);
         }
-        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF)), dmin = fk_h2f((uint16_t)(hd.x >> 16));
-        const float f_lo = d * (float)(sc2 & 0xFF), f_hi = d * (float)(sc2 >> 8);
+        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF));
         // the two lanes sharing a sub-block (h = 0, 1) each carry half its min term
-        const float mm_lo = 0.5f * dmin * (float)(m2 & 0xFF), mm_hi = 0.5f * dmin * (float)(m2 >> 8);
+        const float dmh = 0.5f * fk_h2f((uint16_t)(hd.x >> 16));
+        const int sc_lo = sc2 & 0xFF, sc_hi = sc2 >> 8;
+        const float fm_lo = dmh * i2f(m2 & 0xFF), fm_hi = dmh * i2f(m2 >> 8);
         uint4 lo, hi;
         lo.x = wq.x & 0x0F0F0F0Fu; hi.x = (wq.x >> 4) & 0x0F0F0F0Fu;
         lo.y = wq.y & 0x0F0F0F0Fu; hi.y = (wq.y >> 4) & 0x0F0F0F0Fu;
@@ -130,84 +207,56 @@ template <> struct Piece<FK_Q4_K> {
             const float2 d8 = *(const float2*)(sm.d + b * sm.nb32 + sbs * 8 + 2 * g);
             const float2 s8 = *(const float2*)(sm.s + b * sm.nb32 + sbs * 8 + 2 * g);
             int il = dp4a4(lo, ua), ih = dp4a4(hi, ub);
-            acc[b] += f_lo * d8.x * (float)il + f_hi * d8.y * (float)ih - (mm_lo * s8.x + mm_hi * s8.y);
+            // |il * sc| <= 16 * 15 * 127 * 63 < 2^22: the products stay exact integers
+            acc[b] += d * (d8.x * i2f(il * sc_lo) + d8.y * i2f(ih * sc_hi)) - (fm_lo * s8.x + fm_hi * s8.y);
             if (DUMP && b == 0) {
                 il += __shfl_xor_sync(0xffffffffu, il, 1);
                 ih += __shfl_xor_sync(0xffffffffu, ih, 1);
-                if (live && h == 0 && row_ok) {
+                if (live && h == 0) {
                     int32_t* o = a.isums + (size_t)row * sm.nb32 + sb * 8 + 2 * g;
                     o[0] = il;
                     o[1] = ih;
                 }
             }
         }
-    }
-};
-
-template <> struct Piece<FK_Q8_0> {
-    uint4 wq;
-    uint32_t dbits;
-    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 4) + 31) >> 5; }
-    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+    } else if (KIND == FK_Q8_0) {
         const int ci = trip * 32 + lane;
-        wq = make_uint4(0, 0, 0, 0);
-        dbits = 0;
-        if (row_ok && ci < (a.cols >> 4)) {
-            wq = ldg16(wb + a.plane_off[0] + (size_t)row * a.cols + (size_t)ci * 16);
-            dbits = __ldg((const uint16_t*)(wb + a.plane_off[1]) + (size_t)row * (a.cols >> 5) + (ci >> 1));
+        const bool live = ci < (sm.cols >> 4) && row_ok;
+        const int cs = ci < (sm.cols >> 4) ? ci : 0;
+        uint4 wq = make_uint4(0, 0, 0, 0);
+        float dw = 0.0f;
+        if (live) {
+            wq = lds16(plane_at<KIND>(a, stage, r, 0) + (tl * 32 + lane) * 16);
+            dw = fk_h2f((uint16_t)lds_u16(plane_at<KIND>(a, stage, r, 1) + (tl * 16 + (lane >> 1)) * 2));
         }
-    }
-    template <int NB, bool DUMP>
-    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
-        const int ci = trip * 32 + lane;
-        const bool live = ci < (sm.cols >> 4);
-        const int cs = live ? ci : 0;
-        const float dw = fk_h2f((uint16_t)dbits);
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const int4 ua = *(const int4*)(sm.q + (size_t)b * sm.cols + cs * 16);
             int is = dp4a4(wq, ua);
-            acc[b] += dw * sm.d[b * sm.nb32 + (cs >> 1)] * (float)is;
+            acc[b] += dw * sm.d[b * sm.nb32 + (cs >> 1)] * i2f(is);
             if (DUMP && b == 0) {
                 is += __shfl_xor_sync(0xffffffffu, is, 1);
-                if (live && !(lane & 1) && row_ok) a.isums[(size_t)row * sm.nb32 + (ci >> 1)] = is;
+                if (live && !(lane & 1)) a.isums[(size_t)row * sm.nb32 + (ci >> 1)] = is;
             }
         }
-    }
-};
-
-template <> struct Piece<FK_Q6_K> {
-    uint4 ql, qh;
-    int sc_lo, sc_hi;
-    uint32_t dbits;
-    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 8) + 3) >> 2; }
-    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
-        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
-        const int c = lane & 7, hf = c >> 2, q = c & 3;
-        ql = make_uint4(0, 0, 0, 0);
-        qh = ql;
-        sc_lo = sc_hi = 0;
-        dbits = 0;
-        if (row_ok && sb < nsb) {
-            const size_t r = (size_t)row;
-            ql = ldg16(wb + a.plane_off[0] + r * (a.cols >> 1) + (size_t)sb * 128 + 16 * c);
-            qh = ldg16(wb + a.plane_off[1] + r * (a.cols >> 2) + (size_t)sb * 64 + 32 * hf + 16 * (q & 1));
-            const int8_t* sc = (const int8_t*)(wb + a.plane_off[2]) + r * (a.cols >> 4) + sb * 16 + 8 * hf + q;
-            sc_lo = __ldg(sc);
-            sc_hi = __ldg(sc + 4);
-            dbits = __ldg((const uint16_t*)(wb + a.plane_off[3]) + r * nsb + sb);
-        }
-    }
-    template <int NB, bool DUMP>
-    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
+    } else if (KIND == FK_Q6_K) {
         const int nsb = sm.cols >> 8, sb = trip * 4 + (lane >> 3);
-        const bool live = sb < nsb;
-        const int sbs = live ? sb : 0;
+        const bool live = sb < nsb && row_ok;
+        const int sbs = sb < nsb ? sb : 0;
         const int c = lane & 7, hf = c >> 2, q = c & 3;
         const int g_lo = 8 * hf + q, g_hi = g_lo + 4;
         const int shift = 2 * (q >> 1);
-        const float d = fk_h2f((uint16_t)dbits);
-        const float f_lo = d * (float)sc_lo, f_hi = d * (float)sc_hi;
+        const int bl = tl * 4 + (lane >> 3);   // super-block inside the stage
+        uint4 ql = make_uint4(0, 0, 0, 0), qh = ql;
+        float f_lo = 0.0f, f_hi = 0.0f;
+        if (live) {
+            const uint32_t p2 = plane_at<KIND>(a, stage, r, 2);
+            ql = lds16(plane_at<KIND>(a, stage, r, 0) + bl * 128 + 16 * c);
+            qh = lds16(plane_at<KIND>(a, stage, r, 1) + bl * 64 + 32 * hf + 16 * (q & 1));
+            const float d = fk_h2f((uint16_t)lds_u16(plane_at<KIND>(a, stage, r, 3) + sb * 2));   // the whole row's super-scales are staged
+            f_lo = d * i2f(lds_s8(p2 + bl * 16 + g_lo));
+            f_hi = d * i2f(lds_s8(p2 + bl * 16 + g_hi));
+        }
         uint4 vl, vh;
         vl.x = (ql.x & 0x0F0F0F0Fu) | (((qh.x >> shift) & 0x03030303u) << 4);
         vl.y = (ql.y & 0x0F0F0F0Fu) | (((qh.y >> shift) & 0x03030303u) << 4);
@@ -226,35 +275,23 @@ template <> struct Piece<FK_Q6_K> {
             // codes are stored +32: sum((c - 32) * u) = sum(c * u) - 32 * sum(u)
             const int il = dp4a4(vl, ua) - 32 * b16[g_lo];
             const int ih = dp4a4(vh, ub) - 32 * b16[g_hi];
-            acc[b] += f_lo * d8lo * (float)il + f_hi * d8hi * (float)ih;
-            if (DUMP && b == 0 && live && row_ok) {
+            acc[b] += f_lo * d8lo * i2f(il) + f_hi * d8hi * i2f(ih);
+            if (DUMP && b == 0 && live) {
                 int32_t* o = a.isums + (size_t)row * (sm.cols >> 4) + sb * 16;
                 o[g_lo] = il;
                 o[g_hi] = ih;
             }
         }
-    }
-};
-
-template <> struct Piece<FK_MXFP4> {
-    uint4 wq;
-    uint32_t e;
-    static __device__ __forceinline__ int trips(int cols) { return ((cols >> 5) + 31) >> 5; }
-    __device__ __forceinline__ void load(const GemvArgs& a, const uint8_t* wb, int row, int trip, int lane, bool row_ok) {
+    } else {  // FK_MXFP4
         const int kb = trip * 32 + lane;
-        wq = make_uint4(0, 0, 0, 0);
-        e = 0xFFFFFFFFu;
-        if (row_ok && kb < (a.cols >> 5)) {
-            wq = ldg16(wb + a.plane_off[0] + (size_t)row * (a.cols >> 1) + (size_t)kb * 16);
-            e = __ldg(wb + a.plane_off[1] + (size_t)row * (a.cols >> 5) + kb);
+        const bool live = kb < sm.nb32 && row_ok;
+        const int ks = kb < sm.nb32 ? kb : 0;
+        uint4 wq = make_uint4(0, 0, 0, 0);
+        float dw = 0.0f;
+        if (live) {
+            wq = lds16(plane_at<KIND>(a, stage, r, 0) + (tl * 32 + lane) * 16);
+            dw = e8m0_half(lds_u8(plane_at<KIND>(a, stage, r, 1) + tl * 32 + lane));
         }
-    }
-    template <int NB, bool DUMP>
-    __device__ __forceinline__ void eat(const GemvArgs& a, const Smem& sm, int row, int trip, int lane, bool row_ok, float* acc) const {
-        const int kb = trip * 32 + lane;
-        const bool live = kb < sm.nb32;
-        const int ks = live ? kb : 0;
-        const float dw = e == 0xFFFFFFFFu ? 0.0f : e8m0_half(e);
         uint4 va, vb;
         va.x = e2m1x2_4(wq.x); va.y = e2m1x2_4(wq.x >> 16);
         va.z = e2m1x2_4(wq.y); va.w = e2m1x2_4(wq.y >> 16);
@@ -265,16 +302,34 @@ template <> struct Piece<FK_MXFP4> {
             const int8_t* q8 = sm.q + (size_t)b * sm.cols + ks * 32;
             const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 16);
             const int is = dp4a4(va, ua) + dp4a4(vb, ub);
-            acc[b] += dw * sm.d[b * sm.nb32 + ks] * (float)is;
-            if (DUMP && b == 0 && live && row_ok) a.isums[(size_t)row * sm.nb32 + kb] = is;
+            acc[b] += dw * sm.d[b * sm.nb32 + ks] * i2f(is);
+            if (DUMP && b == 0 && live) a.isums[(size_t)row * sm.nb32 + kb] = is;
         }
     }
-};
+}
 
-// U = trips whose loads a lane issues back to back before it consumes any.
-template <int KIND, int NB, bool DUMP, int U>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
-    extern __shared__ __align__(16) uint8_t smem[];
+// Bytes of plane p that chunk `kc` of a row occupies, and where they start in
+// the row.  Sizes are multiples of 16 (plane strides are), the last chunk of a
+// row is clipped to the row.
+template <int KIND>
+__device__ __forceinline__ void chunk_span(const GemvArgs& a, int p, int kc, uint32_t* off, uint32_t* bytes) {
+    if (KIND == FK_Q6_K && p == 3) {   // the f16 super-scales: the whole (padded) row, every chunk
+        *off = 0;
+        *bytes = (uint32_t)a.plane_stride[3];
+        return;
+    }
+    const uint32_t tb = trip_bytes<KIND>(p);
+    const uint32_t o = (uint32_t)kc * a.trips_per_chunk * tb;
+    const uint32_t stride = (uint32_t)a.plane_stride[p];
+    uint32_t n = a.trips_per_chunk * tb;
+    if (o + n > stride) n = stride - o;
+    *off = o;
+    *bytes = n;
+}
+
+template <int KIND, int NB, bool DUMP>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
     const int cols = a.cols, rows = a.rows;
     const int nb32 = cols >> 5;
     int8_t* sq = (int8_t*)smem;                       // [NB][cols] int8
@@ -289,99 +344,186 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     const float* x = a.x + (size_t)slot * a.x_stride;
     float* y = a.y + (size_t)slot * a.batch * rows;
 
+    // ---- this warp's ring: stages, then one mbarrier per stage
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t ring = sbase + a.act_bytes + warp * (a.nstages * a.stage_bytes);
+    const uint32_t bars = sbase + a.act_bytes + GEMV_WARPS * (a.nstages * a.stage_bytes) + warp * (MAX_STAGES * 8);
+    if (lane == 0) {
+        for (int s = 0; s < a.nstages; s++) mbar_init(bars + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+
     const int gwarp = blockIdx.x * GEMV_WARPS + warp;
     const int twarps = gridDim.x * GEMV_WARPS;
-    const int ntrips = Piece<KIND>::trips(cols);
+    const int npairs = (rows + R - 1) / R;
+    const int my_pairs = gwarp < npairs ? (npairs - gwarp + twarps - 1) / twarps : 0;
+    const int njobs = my_pairs * a.nchunks;           // a job = one stage fill = (row pair, K chunk)
+    const int ntrips = (cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
 
-    // The first batch of weight loads goes out before the activations are
-    // touched, so HBM latency overlaps the quantization.
-    Piece<KIND> pc[U][R];
-    int rp = gwarp;
-#pragma unroll
-    for (int u = 0; u < U; u++)
-#pragma unroll
-        for (int r = 0; r < R; r++)
-            pc[u][r].load(a, wb, rp * R + r, u, lane, rp * R + r < rows && u < ntrips);
+    // Fill stage (job % nstages) with job `q`: lane c < R * PLANES copies plane
+    // (c % PLANES) of row (c / PLANES); lane 0 announces the byte total first.
+    auto fill = [&](int q) {
+        const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
+        const int s = q % a.nstages;
+        const uint32_t stage = ring + s * a.stage_bytes, bar = bars + 8 * s;
+        constexpr int P = Geo<KIND>::PLANES;
+        const int r = lane / P, p = lane % P;
+        const int row = pair * R + r;
+        uint32_t off = 0, bytes = 0;
+        if (lane < R * P && row < rows) chunk_span<KIND>(a, p, kc, &off, &bytes);
+        const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
+        if (lane == 0) mbar_expect_tx(bar, total);
+        __syncwarp();
+        if (bytes) bulk_g2s(plane_at<KIND>(a, stage, r, p), wb + a.plane_off[p] + (size_t)row * a.plane_stride[p] + off, bytes, bar);
+    };
 
-    // ---- activations -> q8_1 in shared memory
-    for (int run = warp; run < NB * nb32; run += GEMV_WARPS) {
-        const int b = run / nb32, kb = run - b * nb32;
-        const float v = b < a.batch ? x[(size_t)b * cols + kb * 32 + lane] : 0.0f;
-        float d;
-        int qsum;
-        const int q = fk_q8_1_lane(v, &d, &qsum);
-        // MXFP4 keeps each run as (elem j, elem j+16) pairs: the order its
-        // nibble decode produces bytes in.
-        const int pos = KIND == FK_MXFP4 ? (((lane & 15) << 1) | (lane >> 4)) : lane;
-        sq[(size_t)b * cols + kb * 32 + pos] = (int8_t)q;
-        if (KIND == FK_Q6_K) {
-            const int half_sum = __reduce_add_sync(0xffffffffu, lane < 16 ? q : 0);
-            if (lane == 0) {
-                sb16[b * (cols >> 4) + 2 * kb] = half_sum;
-                sb16[b * (cols >> 4) + 2 * kb + 1] = qsum - half_sum;
+    // Every stage of the ring is requested before the activations are touched.
+    const int pre = njobs < a.nstages ? njobs : a.nstages;
+    for (int q = 0; q < pre; q++) fill(q);
+
+    // ---- activations -> q8_1 in shared memory.  A thread takes one float4, eight
+    // lanes make a run of 32; all of a thread's loads go out before any is used,
+    // so the block pays one L2 round trip, not one per run.
+    {
+        const int c4 = cols >> 2, items = NB * c4;
+        constexpr int QU = 4;
+        for (int base = 0; base < items; base += GEMV_THREADS * QU) {
+            float4 v[QU];
+#pragma unroll
+            for (int u = 0; u < QU; u++) {
+                const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+                v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (idx < items) {
+                    const int b = idx / c4, k4 = idx - b * c4;
+                    if (b < a.batch) v[u] = __ldg((const float4*)(x + (size_t)b * cols) + k4);
+                }
             }
-        }
-        if (lane == 0) {
-            sd[b * nb32 + kb] = d;
-            if (KIND == FK_Q4_K) ss[b * nb32 + kb] = d * (float)qsum;
+#pragma unroll
+            for (int u = 0; u < QU; u++) {
+                const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+                const bool ok = idx < items;
+                const int b = ok ? idx / c4 : 0, k4 = ok ? idx - b * c4 : 0;
+                const int kb = k4 >> 3, quad = k4 & 7;
+                // the rule of fk_q8_1_lane over the eight lanes of the run (max and integer sums are order-free)
+                unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+                mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+                mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+                mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
+                const float amax = __uint_as_float(mb);
+                const float d = amax / 127.0f;
+                int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+                if (amax != 0.0f) {
+                    q0 = (int)roundf(v[u].x / d);
+                    q1 = (int)roundf(v[u].y / d);
+                    q2 = (int)roundf(v[u].z / d);
+                    q3 = (int)roundf(v[u].w / d);
+                }
+                int s16 = q0 + q1 + q2 + q3;
+                s16 += __shfl_xor_sync(0xffffffffu, s16, 1);
+                s16 += __shfl_xor_sync(0xffffffffu, s16, 2);           // sum of this lane's half run (16 values)
+                const int qsum = s16 + __shfl_xor_sync(0xffffffffu, s16, 4);
+                if (ok) {
+                    int8_t* dst = sq + (size_t)b * cols + kb * 32;
+                    if (KIND == FK_MXFP4) {
+                        // each run is kept as (elem j, elem j+16) pairs: the order the nibble decode produces bytes in
+                        const int e = 4 * quad;
+                        dst[(((e + 0) & 15) << 1) | ((e + 0) >> 4)] = (int8_t)q0;
+                        dst[(((e + 1) & 15) << 1) | ((e + 1) >> 4)] = (int8_t)q1;
+                        dst[(((e + 2) & 15) << 1) | ((e + 2) >> 4)] = (int8_t)q2;
+                        dst[(((e + 3) & 15) << 1) | ((e + 3) >> 4)] = (int8_t)q3;
+                    } else {
+                        *(uint32_t*)(dst + 4 * quad) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                                                       ((uint32_t)(q3 & 0xFF) << 24);
+                    }
+                    if (KIND == FK_Q6_K && (quad & 3) == 0) sb16[b * (cols >> 4) + 2 * kb + (quad >> 2)] = s16;
+                    if (quad == 0) {
+                        const float dq = fk_h2f(fk_f2h(d));   // the stored f16 scale, widened
+                        sd[b * nb32 + kb] = dq;
+                        if (KIND == FK_Q4_K) ss[b * nb32 + kb] = dq * (float)qsum;
+                    }
+                }
+            }
         }
     }
     __syncthreads();
-    Smem sm{sq, sd, ss, sb16, cols, nb32};
+    const Act sm{sq, sd, ss, sb16, cols, nb32};
 
-    for (; rp * R < rows; rp += twarps) {
-        const int row0 = rp * R;
-        float acc[R][NB];
+    float acc[R][NB];
+    for (int q = 0; q < njobs; q++) {
+        const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
+        const int s = q % a.nstages;
+        const uint32_t stage = ring + s * a.stage_bytes;
+        const int row0 = pair * R;
+        if (kc == 0) {
 #pragma unroll
-        for (int r = 0; r < R; r++)
+            for (int r = 0; r < R; r++)
 #pragma unroll
-            for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
-
-        for (int t0 = 0; t0 < ntrips; t0 += U) {
-            if (t0 > 0 || rp != gwarp) {
-#pragma unroll
-                for (int u = 0; u < U; u++)
-#pragma unroll
-                    for (int r = 0; r < R; r++)
-                        pc[u][r].load(a, wb, row0 + r, t0 + u, lane, row0 + r < rows && t0 + u < ntrips);
-            }
-#pragma unroll
-            for (int u = 0; u < U; u++)
-#pragma unroll
-                for (int r = 0; r < R; r++)
-                    pc[u][r].template eat<NB, DUMP>(a, sm, row0 + r, t0 + u, lane, row0 + r < rows && t0 + u < ntrips, acc[r]);
+                for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
         }
+        mbar_wait(bars + 8 * s, (q / a.nstages) & 1, a.err);
+        const int t0 = kc * a.trips_per_chunk;
+        const int t1 = t0 + a.trips_per_chunk < ntrips ? t0 + a.trips_per_chunk : ntrips;
+        for (int t = t0; t < t1; t++) {
 #pragma unroll
-        for (int r = 0; r < R; r++)
+            for (int r = 0; r < R; r++) eat<KIND, NB, DUMP>(a, sm, stage, r, row0 + r, row0 + r < rows, t, t - t0, lane, acc[r]);
+        }
+        // every lane has consumed the stage: refill it with the job one ring ahead
+        __syncwarp();
+        if (q + a.nstages < njobs) fill(q + a.nstages);
+        if (kc == a.nchunks - 1) {
 #pragma unroll
-            for (int b = 0; b < NB; b++) {
-                const float s = fk_warp_sum(acc[r][b]);
-                if (lane == 0 && row0 + r < rows && b < a.batch) y[(size_t)b * rows + row0 + r] = s;
-            }
+            for (int r = 0; r < R; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const float v = fk_warp_sum(acc[r][b]);
+                    if (lane == 0 && row0 + r < rows && b < a.batch) y[(size_t)b * rows + row0 + r] = v;
+                }
+        }
     }
 }
 
-size_t gemv_smem_bytes(int kind, int nb, int cols) {
+size_t act_smem_bytes(int kind, int nb, int cols) {
     size_t s = (size_t)nb * cols + (size_t)nb * (cols / 32) * 4;
     if (kind == FK_Q4_K) s += (size_t)nb * (cols / 32) * 4;
     if (kind == FK_Q6_K) s += (size_t)nb * (cols / 16) * 4;
-    return s;
+    return (s + 127) & ~(size_t)127;
+}
+
+// Bytes of one row's share of a stage that covers `t` trips.
+template <int KIND>
+int row_stage_bytes(const fk_weight_s* w, int t) {
+    int b = 0;
+    for (int p = 0; p < 3; p++) b += trip_bytes<KIND>(p) * t;
+    if (KIND == FK_Q6_K) b += (int)w->plane_stride[3];
+    return b;
 }
 
 template <int KIND, int NB, bool DUMP>
-int launch_one(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, int slots) {
-    const size_t smem = gemv_smem_bytes(KIND, NB, a.cols);
-    if (smem > 220 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv: %d columns x batch %d needs %zu B of shared memory", a.cols, NB, smem);
-    constexpr int U = NB <= 2 ? 3 : (NB <= 4 ? 2 : 1);
-    auto kern = gemv_kernel<KIND, NB, DUMP, U>;
-    if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, int slots) {
+    const int act = (int)act_smem_bytes(KIND, NB, a.cols);
+    const int bars = GEMV_WARPS * MAX_STAGES * 8;
+    const int ring_budget = (SMEM_BUDGET - act - bars) / GEMV_WARPS;   // bytes of ring a warp may have
+    const int ntrips = (a.cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
+    // the largest K chunk that still leaves a ring of two stages; a whole row when it fits
+    int t = ntrips;
+    while (t > 1 && 2 * R * row_stage_bytes<KIND>(w, t) > ring_budget) t--;
+    if (ring_budget <= 0 || 2 * R * row_stage_bytes<KIND>(w, t) > ring_budget)
+        return fk_fail(FK_UNSUPPORTED, "gemv: %d columns x batch %d does not fit shared memory", a.cols, NB);
+    a.trips_per_chunk = t;
+    a.nchunks = (ntrips + t - 1) / t;
+    a.row_bytes_stage = row_stage_bytes<KIND>(w, t);
+    a.stage_bytes = R * a.row_bytes_stage;
+    a.nstages = ring_budget / a.stage_bytes;
+    if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
+    a.act_bytes = act;
+    const size_t smem = (size_t)act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
+    auto kern = gemv_kernel<KIND, NB, DUMP>;
+    FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
     const int pairs = (a.rows + R - 1) / R;
     const int need = (pairs + GEMV_WARPS - 1) / GEMV_WARPS;
-    // a persistent grid: as many blocks as are resident at once, no second wave
-    int occ = 0;
-    FK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem), FK_KERNEL);
-    if (occ < 1) occ = 1;
-    int per_slot = (occ * ctx->sm_count + slots - 1) / slots;
+    // a persistent grid: one block per SM, shared out over the slots
+    int per_slot = ctx->sm_count / slots;
     if (per_slot < 1) per_slot = 1;
     dim3 grid((unsigned)(need < per_slot ? need : per_slot), (unsigned)slots);
     kern<<<grid, GEMV_THREADS, smem, st>>>(a);
@@ -391,12 +533,12 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, int slots) {
 }
 
 template <int KIND>
-int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, int slots, bool dump) {
-    if (dump) return launch_one<KIND, 1, true>(ctx, st, a, slots);
-    if (a.batch <= 1) return launch_one<KIND, 1, false>(ctx, st, a, slots);
-    if (a.batch <= 2) return launch_one<KIND, 2, false>(ctx, st, a, slots);
-    if (a.batch <= 4) return launch_one<KIND, 4, false>(ctx, st, a, slots);
-    return launch_one<KIND, 8, false>(ctx, st, a, slots);
+int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight_s* w, int slots, bool dump) {
+    if (dump) return launch_one<KIND, 1, true>(ctx, st, a, w, slots);
+    if (a.batch <= 1) return launch_one<KIND, 1, false>(ctx, st, a, w, slots);
+    if (a.batch <= 2) return launch_one<KIND, 2, false>(ctx, st, a, w, slots);
+    if (a.batch <= 4) return launch_one<KIND, 4, false>(ctx, st, a, w, slots);
+    return launch_one<KIND, 8, false>(ctx, st, a, w, slots);
 }
 
 // ---- standalone q8_1 quantizer (36-byte blocks), one warp per run
@@ -420,10 +562,13 @@ __global__ void quantize_q8_1_kernel(const float* __restrict__ x, int n_runs, ui
 
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev) {
-    GemvArgs a;
+    GemvArgs a{};
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
-    for (int i = 0; i < 4; i++) a.plane_off[i] = w->plane_off[i];
+    for (int i = 0; i < 4; i++) {
+        a.plane_off[i] = w->plane_off[i];
+        a.plane_stride[i] = w->plane_stride[i];
+    }
     a.ids = ids_dev;
     a.mat = mat;
     a.x = x_dev;
@@ -433,12 +578,13 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
     a.cols = w->cols;
     a.batch = batch;
     a.isums = isums_dev;
+    a.err = ctx->err_flag;
     const bool dump = isums_dev != nullptr;
     switch (w->kind) {
-        case FK_Q4_K: return launch_kind<FK_Q4_K>(ctx, st, a, slots, dump);
-        case FK_Q6_K: return launch_kind<FK_Q6_K>(ctx, st, a, slots, dump);
-        case FK_Q8_0: return launch_kind<FK_Q8_0>(ctx, st, a, slots, dump);
-        case FK_MXFP4: return launch_kind<FK_MXFP4>(ctx, st, a, slots, dump);
+        case FK_Q4_K: return launch_kind<FK_Q4_K>(ctx, st, a, w, slots, dump);
+        case FK_Q6_K: return launch_kind<FK_Q6_K>(ctx, st, a, w, slots, dump);
+        case FK_Q8_0: return launch_kind<FK_Q8_0>(ctx, st, a, w, slots, dump);
+        case FK_MXFP4: return launch_kind<FK_MXFP4>(ctx, st, a, w, slots, dump);
     }
     return fk_fail(FK_UNSUPPORTED, "gemv: kind %d has no kernel", w->kind);
 }
@@ -458,6 +604,7 @@ FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
     if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv: null argument");
     if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv: batch %d outside 1..8 (use fk_gemm)", batch);
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv: matrix %d of %d", mat, w->n_mats);
+    if ((uintptr_t)x_dev & 15) return fk_fail(FK_INVALID, "gemv: x_dev must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr);
 }
@@ -467,6 +614,7 @@ FK_EXPORT int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* i
     if (!ctx || !w || !ids_dev || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_multi: null argument");
     if (k < 1 || k > 65535) return fk_fail(FK_INVALID, "gemv_multi: k=%d", k);
     if (x_stride != 0 && x_stride < w->cols) return fk_fail(FK_INVALID, "gemv_multi: x_stride %d < cols %d", x_stride, w->cols);
+    if (((uintptr_t)x_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi: x_dev must be 16-byte aligned and x_stride a multiple of 4");
     FkDeviceGuard g(ctx->device);
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr);
 }
@@ -474,6 +622,7 @@ FK_EXPORT int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* i
 FK_EXPORT int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int32_t* isums_dev) {
     if (!ctx || !w || !x_dev || !isums_dev) return fk_fail(FK_INVALID, "gemv_isums: null argument");
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_isums: matrix %d of %d", mat, w->n_mats);
+    if ((uintptr_t)x_dev & 15) return fk_fail(FK_INVALID, "gemv_isums: x_dev must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
     // y is not wanted: park it in the context's scratch
     int rc = fk_ensure_scratch(ctx, (size_t)w->rows * sizeof(float));
