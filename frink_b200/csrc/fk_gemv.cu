@@ -26,7 +26,7 @@ namespace {
 
 constexpr int GEMV_THREADS = 512;
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
-constexpr int R = 2;            // weight rows per stage
+constexpr int LR = 2;           // weight rows a lane carries at once
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_BUDGET = 225 * 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
@@ -48,7 +48,7 @@ struct GemvArgs {
     int trips_per_chunk;   // trips of K a stage covers
     int nchunks;           // stages per row pair
     int nstages;           // ring depth
-    int stage_bytes;       // bytes of one stage (R rows, all planes)
+    int stage_bytes;       // bytes of one stage (its rows, all planes)
     int row_bytes_stage;   // bytes of one row inside a stage
     int act_bytes;         // activation region at the start of shared memory
 };
@@ -122,20 +122,23 @@ __device__ __forceinline__ float e8m0_half(uint32_t e) {
 
 // ---------------------------------------------------------------------------
 // Per-kind geometry.  A "trip" is what one pass of the 32 lanes covers of a row:
-//   Q4_K : 4 super-blocks (1024 weights); 8 lanes per 144-byte block; lane c owns
-//          quant bytes [16c, 16c+16): low nibbles are 16 weights of sub-block 2g,
-//          high nibbles 16 weights of sub-block 2g+1 (g = c/2).
+//   Q4_K : 4 super-blocks (1024 weights) per HALF warp; a stage holds four rows,
+//          lanes 0-15 take rows 0-1, lanes 16-31 rows 2-3.  4 lanes per 144-byte
+//          block; lane g owns quant bytes [32g, 32g+32): low nibbles are the 32
+//          weights of sub-block 2g, high nibbles those of sub-block 2g+1, so a
+//          lane decodes one pair of 6-bit scales per 32 bytes of weights.
 //   Q6_K : 4 super-blocks; lane c of a block owns ql bytes [16c, 16c+16) and the
 //          matching 16 qh bytes: two runs of 16 weights (groups g_lo, g_lo + 4).
 //   Q8_0 : 512 weights; a lane owns 16 int8 (half a block).
 //   MXFP4: 1024 weights; a lane owns one block's 16 code bytes.
-// PLANES / TB: bytes of each plane one trip of one row occupies in a stage
-// (Q6_K's 4th plane, the f16 super-scales, is staged as the whole row).
+// ROWS: rows per stage (a lane always carries two of them).  PLANES / TB: bytes
+// of each plane one trip of one row occupies in a stage (Q6_K's 4th plane, the
+// f16 super-scales, is staged as the whole row).
 template <int KIND> struct Geo;
-template <> struct Geo<FK_Q4_K> { static constexpr int PLANES = 1, TRIP_COLS = 1024, TB0 = 576, TB1 = 0, TB2 = 0; };
-template <> struct Geo<FK_Q8_0> { static constexpr int PLANES = 2, TRIP_COLS = 512, TB0 = 512, TB1 = 32, TB2 = 0; };
-template <> struct Geo<FK_Q6_K> { static constexpr int PLANES = 4, TRIP_COLS = 1024, TB0 = 512, TB1 = 256, TB2 = 64; };
-template <> struct Geo<FK_MXFP4> { static constexpr int PLANES = 2, TRIP_COLS = 1024, TB0 = 512, TB1 = 32, TB2 = 0; };
+template <> struct Geo<FK_Q4_K> { static constexpr int ROWS = 4, PLANES = 1, TRIP_COLS = 1024, TB0 = 576, TB1 = 0, TB2 = 0; };
+template <> struct Geo<FK_Q8_0> { static constexpr int ROWS = 2, PLANES = 2, TRIP_COLS = 512, TB0 = 512, TB1 = 32, TB2 = 0; };
+template <> struct Geo<FK_Q6_K> { static constexpr int ROWS = 2, PLANES = 4, TRIP_COLS = 1024, TB0 = 512, TB1 = 256, TB2 = 64; };
+template <> struct Geo<FK_MXFP4> { static constexpr int ROWS = 2, PLANES = 2, TRIP_COLS = 1024, TB0 = 512, TB1 = 32, TB2 = 0; };
 template <int KIND> __host__ __device__ constexpr int trip_bytes(int p) {
     return p == 0 ? Geo<KIND>::TB0 : (p == 1 ? Geo<KIND>::TB1 : (p == 2 ? Geo<KIND>::TB2 : 0));
 }
@@ -158,68 +161,76 @@ __device__ __forceinline__ uint32_t plane_at(const GemvArgs& a, uint32_t stage, 
     return off;
 }
 
+__device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {   // unsigned bytes of a x signed bytes of b
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// Q4_K, one trip of the lane's two rows.  The lane's half warp covers 4
+// super-blocks; the lane owns sub-blocks 2g, 2g+1 of one of them (64 weights,
+// 32 quant bytes) in both rows, against the same 64 activations.
+template <int NB, bool DUMP>
+__device__ __forceinline__ void eat_q4_k(const GemvArgs& a, const Act& sm, uint32_t stage, int row0, int trip, int tl, int lane,
+                                         float (*acc)[NB]) {
+    const int nsb = a.cols >> 8;
+    const int hw = lane >> 4, sbl = (lane >> 2) & 3, g = lane & 3;
+    const int sb = trip * 4 + sbl;
+    const bool live_sb = sb < nsb;
+    const int sbs = live_sb ? sb : 0;
+    const int sh = 16 * (g & 1);
+#pragma unroll
+    for (int r = 0; r < LR; r++) {
+        const int row = row0 + hw * LR + r;
+        const bool live = live_sb && row < a.rows;
+        const uint32_t blk = stage + (hw * LR + r) * a.row_bytes_stage + (tl * 4 + sbl) * 144;
+        uint4 hd = make_uint4(0, 0, 0, 0), q0 = hd, q1 = hd;
+        if (live) {
+            hd = lds16(blk);
+            q0 = lds16(blk + 16 + 32 * g);
+            q1 = lds16(blk + 32 + 32 * g);
+        }
+        // 6-bit scales / mins of sub-blocks 2g, 2g+1: 16-bit word (g & 1) of each of
+        // the three scale words; sub-blocks 4..7 borrow their top two bits
+        const uint32_t a0 = hd.y >> sh, a1 = hd.z >> sh, a2 = hd.w >> sh;
+        const uint32_t sc2 = g < 2 ? (a0 & 0x3F3F) : ((a2 & 0x0F0F) | ((a0 & 0xC0C0) >> 2));
+        const uint32_t m2 = g < 2 ? (a1 & 0x3F3F) : (((a2 >> 4) & 0x0F0F) | ((a1 & 0xC0C0) >> 2));
+        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF)), ndmin = -fk_h2f((uint16_t)(hd.x >> 16));
+        const float fsc_lo = (float)(uint8_t)sc2, fsc_hi = (float)(uint8_t)(sc2 >> 8);
+        const float fm_lo = (float)(uint8_t)m2, fm_hi = (float)(uint8_t)(m2 >> 8);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256 + 64 * g;
+            const int4 u0 = *(const int4*)q8, u1 = *(const int4*)(q8 + 16), u2 = *(const int4*)(q8 + 32), u3 = *(const int4*)(q8 + 48);
+            const int ulo[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            const int uhi[8] = {u2.x, u2.y, u2.z, u2.w, u3.x, u3.y, u3.z, u3.w};
+            const float2 d8 = *(const float2*)(sm.d + b * sm.nb32 + sbs * 8 + 2 * g);
+            const float2 s8 = *(const float2*)(sm.s + b * sm.nb32 + sbs * 8 + 2 * g);
+            int il = 0, ih = 0;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                il = __dp4a((int)(w[i] & 0x0F0F0F0Fu), ulo[i], il);
+                ih = dp4a_us(w[i] & 0xF0F0F0F0u, uhi[i], ih);   // 16 x the high-nibble dot
+            }
+            ih >>= 4;
+            acc[r][b] += d * (fsc_lo * d8.x * (float)il + fsc_hi * d8.y * (float)ih) + ndmin * (fm_lo * s8.x + fm_hi * s8.y);
+            if (DUMP && b == 0 && live) {
+                int32_t* o = a.isums + (size_t)row * sm.nb32 + sb * 8 + 2 * g;
+                o[0] = il;
+                o[1] = ih;
+            }
+        }
+    }
+}
+
 // One lane's share of one row for one trip: unpack, dot, scale.  `trip` is the
 // trip's index in the row (it places the activations), `tl` its index inside the
 // stage (it places the weights).
 template <int KIND, int NB, bool DUMP>
 __device__ __forceinline__ void eat(const GemvArgs& a, const Act& sm, uint32_t stage, int r, int row, bool row_ok, int trip, int tl,
                                     int lane, float* acc) {
-    if (KIND == FK_Q4_K) {
-        const int nsb = a.cols >> 8, sb = trip * 4 + (lane >> 3);
-        const bool live = sb < nsb && row_ok;
-        const int sbs = sb < nsb ? sb : 0;
-        const int c = lane & 7, g = c >> 1, h = c & 1;
-        const uint32_t blk = stage + r * a.row_bytes_stage + (tl * 4 + (lane >> 3)) * 144;
-        uint4 hd = make_uint4(0, 0, 0, 0), wq = hd;
-        if (live) {
-            hd = lds16(blk);
-            wq = lds16(blk + 16 + 16 * c);
-        }
-        // 6-bit scales and mins of sub-blocks 2g, 2g+1, two at a time from the
-        // 16-bit words of the 12 packed bytes
-        const uint32_t w0 = hd.y, w1 = hd.z, w2 = hd.w;
-        uint32_t sc2, m2;
-        if (g < 2) {
-            const uint32_t s_lo = g ? (w0 >> 16) : (w0 & 0xFFFF), s_hi = g ? (w1 >> 16) : (w1 & 0xFFFF);
-            sc2 = s_lo & 0x3F3F;
-            m2 = s_hi & 0x3F3F;
-        } else {
-            const uint32_t A = (g & 1) ? (w2 >> 16) : (w2 & 0xFFFF);
-            const uint32_t B = (g & 1) ? (w0 >> 16) : (w0 & 0xFFFF);
-            const uint32_t C = (g & 1) ? (w1 >> 16) : (w1 & 0xFFFF);
-            sc2 = (A & 0x0F0F) | ((B & 0xC0C0) >> 2);
-            m2 = ((A >> 4) & 0x0F0F) | ((C & 0xC0C0) >> 2);
-        }
-        const float d = fk_h2f((uint16_t)(hd.x & 0xFFFF));
-        // the two lanes sharing a sub-block (h = 0, 1) each carry half its min term
-        const float dmh = 0.5f * fk_h2f((uint16_t)(hd.x >> 16));
-        const int sc_lo = sc2 & 0xFF, sc_hi = sc2 >> 8;
-        const float fm_lo = dmh * i2f(m2 & 0xFF), fm_hi = dmh * i2f(m2 >> 8);
-        uint4 lo, hi;
-        lo.x = wq.x & 0x0F0F0F0Fu; hi.x = (wq.x >> 4) & 0x0F0F0F0Fu;
-        lo.y = wq.y & 0x0F0F0F0Fu; hi.y = (wq.y >> 4) & 0x0F0F0F0Fu;
-        lo.z = wq.z & 0x0F0F0F0Fu; hi.z = (wq.z >> 4) & 0x0F0F0F0Fu;
-        lo.w = wq.w & 0x0F0F0F0Fu; hi.w = (wq.w >> 4) & 0x0F0F0F0Fu;
-#pragma unroll
-        for (int b = 0; b < NB; b++) {
-            const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256 + 64 * g + 16 * h;
-            const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 32);
-            const float2 d8 = *(const float2*)(sm.d + b * sm.nb32 + sbs * 8 + 2 * g);
-            const float2 s8 = *(const float2*)(sm.s + b * sm.nb32 + sbs * 8 + 2 * g);
-            int il = dp4a4(lo, ua), ih = dp4a4(hi, ub);
-            // |il * sc| <= 16 * 15 * 127 * 63 < 2^22: the products stay exact integers
-            acc[b] += d * (d8.x * i2f(il * sc_lo) + d8.y * i2f(ih * sc_hi)) - (fm_lo * s8.x + fm_hi * s8.y);
-            if (DUMP && b == 0) {
-                il += __shfl_xor_sync(0xffffffffu, il, 1);
-                ih += __shfl_xor_sync(0xffffffffu, ih, 1);
-                if (live && h == 0) {
-                    int32_t* o = a.isums + (size_t)row * sm.nb32 + sb * 8 + 2 * g;
-                    o[0] = il;
-                    o[1] = ih;
-                }
-            }
-        }
-    } else if (KIND == FK_Q8_0) {
+    if (KIND == FK_Q8_0) {
         const int ci = trip * 32 + lane;
         const bool live = ci < (sm.cols >> 4) && row_ok;
         const int cs = ci < (sm.cols >> 4) ? ci : 0;
@@ -354,14 +365,17 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     }
     __syncwarp();
 
-    const int gwarp = blockIdx.x * GEMV_WARPS + warp;
+    // consecutive row groups go to consecutive BLOCKS, so a matrix with fewer groups
+    // than warps still spreads over every SM
+    const int gwarp = warp * gridDim.x + blockIdx.x;
     const int twarps = gridDim.x * GEMV_WARPS;
-    const int npairs = (rows + R - 1) / R;
+    constexpr int RS = Geo<KIND>::ROWS;               // rows per stage
+    const int npairs = (rows + RS - 1) / RS;
     const int my_pairs = gwarp < npairs ? (npairs - gwarp + twarps - 1) / twarps : 0;
     const int njobs = my_pairs * a.nchunks;           // a job = one stage fill = (row pair, K chunk)
     const int ntrips = (cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
 
-    // Fill stage (job % nstages) with job `q`: lane c < R * PLANES copies plane
+    // Fill stage (job % nstages) with job `q`: lane c < ROWS * PLANES copies plane
     // (c % PLANES) of row (c / PLANES); lane 0 announces the byte total first.
     auto fill = [&](int q) {
         const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
@@ -369,9 +383,9 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         const uint32_t stage = ring + s * a.stage_bytes, bar = bars + 8 * s;
         constexpr int P = Geo<KIND>::PLANES;
         const int r = lane / P, p = lane % P;
-        const int row = pair * R + r;
+        const int row = pair * RS + r;
         uint32_t off = 0, bytes = 0;
-        if (lane < R * P && row < rows) chunk_span<KIND>(a, p, kc, &off, &bytes);
+        if (lane < RS * P && row < rows) chunk_span<KIND>(a, p, kc, &off, &bytes);
         const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
         if (lane == 0) mbar_expect_tx(bar, total);
         __syncwarp();
@@ -381,6 +395,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // Every stage of the ring is requested before the activations are touched.
     const int pre = njobs < a.nstages ? njobs : a.nstages;
     for (int q = 0; q < pre; q++) fill(q);
+    // Launched with programmatic stream serialization: this grid may start while the
+    // previous kernel of the stream is still running.  Weights are constants, so their
+    // copies go out at once; x (and y) may belong to that kernel, so wait for it here,
+    // and let the next grid start its own weight copies.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- activations -> q8_1 in shared memory.  A thread takes one float4, eight
     // lanes make a run of 32; all of a thread's loads go out before any is used,
@@ -449,15 +469,15 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     __syncthreads();
     const Act sm{sq, sd, ss, sb16, cols, nb32};
 
-    float acc[R][NB];
+    float acc[LR][NB];
     for (int q = 0; q < njobs; q++) {
         const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
         const int s = q % a.nstages;
         const uint32_t stage = ring + s * a.stage_bytes;
-        const int row0 = pair * R;
+        const int row0 = pair * RS;
         if (kc == 0) {
 #pragma unroll
-            for (int r = 0; r < R; r++)
+            for (int r = 0; r < LR; r++)
 #pragma unroll
                 for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
         }
@@ -465,19 +485,31 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         const int t0 = kc * a.trips_per_chunk;
         const int t1 = t0 + a.trips_per_chunk < ntrips ? t0 + a.trips_per_chunk : ntrips;
         for (int t = t0; t < t1; t++) {
+            if (KIND == FK_Q4_K) {
+                eat_q4_k<NB, DUMP>(a, sm, stage, row0, t, t - t0, lane, acc);
+            } else {
 #pragma unroll
-            for (int r = 0; r < R; r++) eat<KIND, NB, DUMP>(a, sm, stage, r, row0 + r, row0 + r < rows, t, t - t0, lane, acc[r]);
+                for (int r = 0; r < LR; r++) eat<KIND, NB, DUMP>(a, sm, stage, r, row0 + r, row0 + r < rows, t, t - t0, lane, acc[r]);
+            }
         }
         // every lane has consumed the stage: refill it with the job one ring ahead
         __syncwarp();
         if (q + a.nstages < njobs) fill(q + a.nstages);
         if (kc == a.nchunks - 1) {
+            // Q4_K: a half warp per row pair; the others: the whole warp on one pair
+            const int hw = KIND == FK_Q4_K ? lane >> 4 : 0;
 #pragma unroll
-            for (int r = 0; r < R; r++)
+            for (int r = 0; r < LR; r++)
 #pragma unroll
                 for (int b = 0; b < NB; b++) {
-                    const float v = fk_warp_sum(acc[r][b]);
-                    if (lane == 0 && row0 + r < rows && b < a.batch) y[(size_t)b * rows + row0 + r] = v;
+                    float v = acc[r][b];
+                    if (KIND != FK_Q4_K) v += __shfl_xor_sync(0xffffffffu, v, 16);
+                    v += __shfl_xor_sync(0xffffffffu, v, 8);
+                    v += __shfl_xor_sync(0xffffffffu, v, 4);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    const int row = row0 + hw * LR + r;
+                    if ((lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0) && row < rows && b < a.batch) y[(size_t)b * rows + row] = v;
                 }
         }
     }
@@ -505,29 +537,41 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     const int bars = GEMV_WARPS * MAX_STAGES * 8;
     const int ring_budget = (SMEM_BUDGET - act - bars) / GEMV_WARPS;   // bytes of ring a warp may have
     const int ntrips = (a.cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
-    // the largest K chunk that still leaves a ring of two stages; a whole row when it fits
+    // the largest K chunk that still leaves a ring of two stages (a whole row when it
+    // fits): bulk copies pay a fixed cost each, and small ones (a trip of Q6_K's
+    // scale planes is 64 and 32 bytes) cost more than the overlap they would buy
+    constexpr int RS = Geo<KIND>::ROWS;
     int t = ntrips;
-    while (t > 1 && 2 * R * row_stage_bytes<KIND>(w, t) > ring_budget) t--;
-    if (ring_budget <= 0 || 2 * R * row_stage_bytes<KIND>(w, t) > ring_budget)
+    while (t > 1 && 2 * RS * row_stage_bytes<KIND>(w, t) > ring_budget) t--;
+    if (ring_budget <= 0 || 2 * RS * row_stage_bytes<KIND>(w, t) > ring_budget)
         return fk_fail(FK_UNSUPPORTED, "gemv: %d columns x batch %d does not fit shared memory", a.cols, NB);
     a.trips_per_chunk = t;
     a.nchunks = (ntrips + t - 1) / t;
     a.row_bytes_stage = row_stage_bytes<KIND>(w, t);
-    a.stage_bytes = R * a.row_bytes_stage;
+    a.stage_bytes = RS * a.row_bytes_stage;
     a.nstages = ring_budget / a.stage_bytes;
     if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
     a.act_bytes = act;
     const size_t smem = (size_t)act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
     auto kern = gemv_kernel<KIND, NB, DUMP>;
     FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
-    const int pairs = (a.rows + R - 1) / R;
-    const int need = (pairs + GEMV_WARPS - 1) / GEMV_WARPS;
+    const int pairs = (a.rows + RS - 1) / RS;
+    const int need = (pairs + 3) / 4;   // at least four row groups a block, else the activation quantization dominates
     // a persistent grid: one block per SM, shared out over the slots
     int per_slot = ctx->sm_count / slots;
     if (per_slot < 1) per_slot = 1;
     dim3 grid((unsigned)(need < per_slot ? need : per_slot), (unsigned)slots);
-    kern<<<grid, GEMV_THREADS, smem, st>>>(a);
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FK_CUDA(cudaLaunchKernelEx(&cfg, kern, a), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }
