@@ -10,13 +10,14 @@
 // is drained from tensor memory after every K = 32 step and scaled on the CUDA
 // cores; that rescale, not the tensor pipe, bounds this kernel.
 //
-// One CTA = 128 weight rows x BN tokens, 12 warps with fixed roles:
-//   warps 0-7   epilogue: TMEM -> registers (tcgen05.ld), f32 rescale, store
-//   warps 8-9   unpack: packed weights (global) -> int8 tile in shared memory
+// One CTA = 128 weight rows x BN tokens, E + 4 warps with fixed roles:
+//   warps 0..E-1  epilogue (E = 4 per 32 token columns: 16 for BN = 128): TMEM ->
+//               registers (tcgen05.ld), f32 rescale, store
+//   next 2      unpack: packed weights (global) -> int8 tile in shared memory
 //               (128-byte swizzle, the layout the MMA descriptor names)
-//   warp 10     TMA producer: activation int8 tile + its scale tiles (and the
+//   next 1      TMA producer: activation int8 tile + its scale tiles (and the
 //               weight tile itself for Q8_0, whose int8 plane needs no unpacking)
-//   warp 11     MMA issuer (one elected lane) + TMEM allocation
+//   last        MMA issuer (one elected lane) + TMEM allocation
 // Stages (K = 128 each) and TMEM accumulators are rings guarded by mbarriers;
 // every wait is bounded and raises the context's error word instead of
 // spinning forever.
@@ -29,8 +30,10 @@ namespace {
 constexpr int BM = 128;           // weight rows per CTA (MMA M)
 constexpr int KSTAGE = 128;       // K per pipeline stage (4 MMAs of K = 32)
 constexpr int NSTAGE = 4;
-constexpr int EPI_WARPS = 8, UNPACK_WARPS = 2;
-constexpr int GEMM_THREADS = (EPI_WARPS + UNPACK_WARPS + 2) * 32;  // 384: 168 registers a thread
+constexpr int UNPACK_WARPS = 2;
+// epilogue warps: four (one per TMEM lane quadrant) for every 32 token columns of the tile
+__host__ __device__ constexpr int epi_warps(int bn) { return bn / 32 * 4; }
+__host__ __device__ constexpr int gemm_threads(int bn) { return (epi_warps(bn) + UNPACK_WARPS + 2) * 32; }
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 struct GemmArgs {
@@ -98,12 +101,20 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
           "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The 32 registers a tcgen05.ld filled are defined, as far as the compiler can
 // tell, at the load itself; this pins their first use behind the wait.
+template <int N>
 __device__ __forceinline__ void tc_ld_fence(uint32_t* v) {
 #pragma unroll
-    for (int i = 0; i < 32; i++) asm volatile("" : "+r"(v[i]) :: "memory");
+    for (int i = 0; i < N; i++) asm volatile("" : "+r"(v[i]) :: "memory");
 }
 
 // K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024
@@ -298,10 +309,11 @@ __device__ __forceinline__ void store_raw(const RawRow<KIND>& raw, int r, uint8_
 }
 
 template <int KIND, int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_dx,
             const __grid_constant__ CUtensorMap map_sx, const __grid_constant__ CUtensorMap map_w) {
     using S = Smem<BN>;
+    constexpr int EPI_WARPS = epi_warps(BN);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32(smem);
@@ -354,33 +366,28 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
         const int r = quad * 32 + lane;                // tile row = TMEM lane
         const int row = KIND == FK_Q6_K ? 2 * wrow0 + r : wrow0 + r;   // scale row id (pair id for Q6_K)
         const bool row_ok = (KIND == FK_Q6_K ? (wrow0 + (r >> 1)) : (wrow0 + r)) < a.rows;
-        constexpr int CW = BN / 2;                     // columns this warp owns
-        constexpr int NCH = CW / 32;                   // 32-column chunks per accumulator
+        constexpr int CW = 32;                         // token columns this warp owns
         float acc[CW];
 #pragma unroll
         for (int i = 0; i < CW; i++) acc[i] = 0.0f;
         const uint32_t taddr0 = tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * CW;
         WScale ws[4], ws_next[4];
         load_wscales<KIND>(a, wb, row, row_ok, 0, nkb, ws_next);
-        // TMEM reads are double-buffered: chunk u+1 is in flight while chunk u is scaled.
-        uint32_t v[2][32];
+        // TMEM reads are double-buffered in halves of 16 columns: while one half is
+        // scaled the next one (or the next run's first) is already in flight, so a warp's
+        // chain per run is its arithmetic, not the accumulator hand-off latency.
+        uint32_t v[2][16];
         auto issue = [&](int kb, int c, uint32_t* dst) {
             const int buf = kb % S::NACC;
             if (c == 0) {
                 mbar_wait(acc_full(buf), (kb / S::NACC) & 1, a.err, 11);
                 tc_fence_after();
             }
-            tc_ld32(taddr0 + buf * BN + c * 32, dst);
-        };
-        auto release = [&](int kb) {   // every column of this accumulator has been read by this warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(kb % S::NACC));
+            tc_ld16(taddr0 + buf * BN + c * 16, dst);
         };
         issue(0, 0, v[0]);
         tc_wait_ld();
-        tc_ld_fence(v[0]);
-        if (NCH == 1) release(0);
+        tc_ld_fence<16>(v[0]);
         for (int st = 0; st < nst; st++) {
             const int s = st % NSTAGE;
 #pragma unroll
@@ -389,42 +396,44 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
             mbar_wait(full_b(s), (st / NSTAGE) & 1, a.err, 10);   // the scale tiles of this stage have landed
             // the stage's scale tiles: dx [4][BN] then (Q4_K) sx [4][BN], as shared-space addresses
             const uint32_t sdx_s = sbase + s * S::STAGE + S::A_BYTES + S::B_BYTES;
-            // kept rolled where the register double buffer allows it (two chunks per
-            // accumulator): the unrolled body is slower
-#pragma unroll(NCH == 1 ? 4 : 1)
+            // Rolled on purpose: the unrolled body falls out of the instruction cache.
+#pragma unroll 1
             for (int j = 0; j < 4; j++) {
                 const int kb = 4 * st + j;
+                if (kb >= nkb) break;
                 const float dw = j == 0 ? ws[0].dw : (j == 1 ? ws[1].dw : (j == 2 ? ws[2].dw : ws[3].dw));
                 const float mw = j == 0 ? ws[0].mw : (j == 1 ? ws[1].mw : (j == 2 ? ws[2].mw : ws[3].mw));
 #pragma unroll
-                for (int c = 0; c < NCH; c++) {
-                    if (kb < nkb) {
-                        uint32_t* cur = v[(j * NCH + c) & 1];
-                        uint32_t* nxt = v[(j * NCH + c + 1) & 1];
-                        const int kb_n = c + 1 < NCH ? kb : kb + 1, c_n = c + 1 < NCH ? c + 1 : 0;
-                        if (kb_n < nkb) issue(kb_n, c_n, nxt);
-                        const uint32_t dxs = sdx_s + (uint32_t)(j * BN + chalf * CW + c * 32) * 4u;
+                for (int c = 0; c < 2; c++) {
+                    uint32_t* cur = v[c];
+                    uint32_t* nxt = v[c ^ 1];
+                    const int kb_n = c == 0 ? kb : kb + 1, c_n = c ^ 1;
+                    if (kb_n < nkb) issue(kb_n, c_n, nxt);
+                    const uint32_t dxs = sdx_s + (uint32_t)(j * BN + chalf * CW + c * 16) * 4u;
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const float4 dx = lds128(dxs + 4u * i);
-                            const float dxa[4] = {dx.x, dx.y, dx.z, dx.w};
-                            float sxa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                            if (KIND == FK_Q4_K) {
-                                const float4 sx = lds128(dxs + 16u * BN + 4u * i);
-                                sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
-                            }
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
-                                const float f = __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
-                                float t = fmaf(dw * dxa[e], f, acc[c * 32 + i + e]);
-                                if (KIND == FK_Q4_K) t = fmaf(-mw, sxa[e], t);
-                                acc[c * 32 + i + e] = t;
-                            }
+                    for (int i = 0; i < 16; i += 4) {
+                        const float4 dx = lds128(dxs + 4u * i);
+                        const float dxa[4] = {dx.x, dx.y, dx.z, dx.w};
+                        float sxa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        if (KIND == FK_Q4_K) {
+                            const float4 sx = lds128(dxs + 16u * BN + 4u * i);
+                            sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
                         }
-                        tc_wait_ld();
-                        tc_ld_fence(nxt);
-                        if (kb_n < nkb && c_n == NCH - 1) release(kb_n);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
+                            const float f = __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
+                            float t = fmaf(dw * dxa[e], f, acc[c * 16 + i + e]);
+                            if (KIND == FK_Q4_K) t = fmaf(-mw, sxa[e], t);
+                            acc[c * 16 + i + e] = t;
+                        }
+                    }
+                    tc_wait_ld();
+                    tc_ld_fence<16>(nxt);
+                    if (kb_n < nkb && c_n == 1) {   // both halves of that accumulator are in registers: hand it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(acc_empty(kb_n % S::NACC));
                     }
                 }
             }
@@ -623,7 +632,7 @@ int launch_gemm(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorM
     FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM), FK_KERNEL);
     constexpr int WROWS = KIND == FK_Q6_K ? BM / 2 : BM;
     dim3 grid((a.rows + WROWS - 1) / WROWS, n_token_tiles);
-    kern<<<grid, GEMM_THREADS, SMEM, st>>>(a, mq, mdx, msx, mw);
+    kern<<<grid, gemm_threads(BN), SMEM, st>>>(a, mq, mdx, msx, mw);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
