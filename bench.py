@@ -186,6 +186,9 @@ def main():
     ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (BASELINE config 2)")
+    ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
+                    help="whole-model pp512 / tg128 tokens per second (BASELINE configs 3 and 4) instead of the GEMV line")
+    ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
     ap.add_argument("--case", default=None, help="kind:rows:cols:batch -- plain launches of one GEMV shape (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -208,6 +211,8 @@ def main():
 
     if args.case:
         return single_case(args)
+    if args.model:
+        return model_bench(args, rank, world, local)
 
     raw, x = synth()
     raw_d = torch.from_numpy(raw).cuda()
@@ -339,6 +344,140 @@ def single_case(args):
     print(json.dumps({"case": args.case, "steps": args.steps, "us_per_launch_incl_host": ms / args.steps * 1e3,
                       "algorithmic_bytes": nbytes, "flops": 2.0 * n * rows * cols, "ring": ring,
                       "device_error_word": device.device_error()}))
+
+
+def use_more_bits(i, n):
+    """Which layers the Q4_K_M recipe gives Q6_K for attn_v / ffn_down
+    (crates/frink-cli/src/quantize/recipe.rs, llama.cpp's rule)."""
+    return i < n // 8 or i >= 7 * n // 8 or (i - n // 8) % 3 == 2
+
+
+def synth_model(name, n_layers=0):
+    """Random-init weights of the named shape, quantized by the reference's encoders
+    (oracle restatement).  To keep set-up short, two distinct layers of bytes are
+    generated per quantization pattern and the other layers reuse them (each layer still
+    gets its own device copy, so nothing is shared in HBM or L2); the embedding is 4096
+    distinct rows tiled to the vocabulary.  Throughput does not depend on the values."""
+    from frink_b200.decoder import DecoderConfig, LayerWeights
+    from oracle import frink_oracle as fo
+    Q4, Q6, Q8 = fo.Q4_K, fo.Q6_K, fo.Q8_0
+    if name == "llama3b":
+        cfg = DecoderConfig(n_layers=28, hidden=3072, n_heads=24, n_kv=8, head_dim=128, ffn=8192, vocab=128256, rope_theta=500000.0, eps=1e-5)
+    elif name == "qwen3moe":
+        cfg = DecoderConfig(n_layers=48, hidden=2048, n_heads=32, n_kv=4, head_dim=128, ffn=768, vocab=151936, rope_theta=1000000.0,
+                            eps=1e-6, neox=True, qk_norm=True, n_experts=128, top_k=8, route_mode=1)
+    else:
+        cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv=2, head_dim=128, ffn=1024, vocab=4096)
+    if n_layers:
+        cfg.n_layers = n_layers
+    rng = np.random.default_rng(0x5EED0000)
+    H, hd = cfg.hidden, cfg.head_dim
+    cache = {}
+
+    def enc(tag, kind, rows, cols, variant):
+        key = (tag, kind, rows, cols, variant)
+        if key not in cache:
+            base_rows = min(rows, 2048)
+            w = (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(0.02))
+            raw = fo.encode(kind, w)
+            cache[key] = np.tile(raw, -(-rows // base_rows))[: rows * fo.row_bytes(kind, cols)].copy()
+        return cache[key]
+
+    layers = []
+    for i in range(cfg.n_layers):
+        var = i % 2
+        if cfg.n_experts:
+            kd = {"wq": Q8, "wk": Q8, "wv": Q8, "wo": Q8, "experts": Q4}
+            E = cfg.n_experts
+            ex = lambda tag, r, c: np.tile(enc(tag, Q4, r, c, var), E)   # one expert's bytes per (layer variant), stacked E times
+            layers.append(LayerWeights(
+                attn_norm=np.ones(H, np.float32), wq=enc("wq", Q8, cfg.n_heads * hd, H, var), wk=enc("wk", Q8, cfg.n_kv * hd, H, var),
+                wv=enc("wv", Q8, cfg.n_kv * hd, H, var), wo=enc("wo", Q8, H, cfg.n_heads * hd, var), ffn_norm=np.ones(H, np.float32),
+                gate=ex("eg", cfg.ffn, H), up=ex("eu", cfg.ffn, H), down=ex("ed", H, cfg.ffn),
+                router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=np.ones(hd, np.float32),
+                k_norm=np.ones(hd, np.float32), kinds=kd))
+        else:
+            more = use_more_bits(i, cfg.n_layers)
+            kd = {"wq": Q4, "wk": Q4, "wv": Q6 if more else Q4, "wo": Q4, "gate": Q4, "up": Q4, "down": Q6 if more else Q4}
+            layers.append(LayerWeights(
+                attn_norm=np.ones(H, np.float32), wq=enc("wq", kd["wq"], cfg.n_heads * hd, H, var), wk=enc("wk", kd["wk"], cfg.n_kv * hd, H, var),
+                wv=enc("wv", kd["wv"], cfg.n_kv * hd, H, var), wo=enc("wo", kd["wo"], H, cfg.n_heads * hd, var), ffn_norm=np.ones(H, np.float32),
+                gate=enc("gate", kd["gate"], cfg.ffn, H, var), up=enc("up", kd["up"], cfg.ffn, H, var), down=enc("down", kd["down"], H, cfg.ffn, var),
+                kinds=kd))
+    tok_kind = Q6
+    base = fo.encode(tok_kind, (rng.standard_normal((4096, H), dtype=np.float32) * np.float32(0.02)))
+    tok = np.tile(base, -(-cfg.vocab // 4096))[: cfg.vocab * fo.row_bytes(tok_kind, H)].copy()
+    return cfg, layers, tok, tok_kind, np.ones(H, np.float32)
+
+
+def model_bench(args, rank, world, local):
+    """pp512 / tg128 of a random-init model of the named shape: prefill of 512 random
+    token ids (GEMM path), then 128 greedy tokens with the decode step replayed from a
+    CUDA graph.  Under torchrun, dense layers are tensor parallel and experts expert
+    parallel.  Times are CUDA events, max over ranks; weights stay resident."""
+    import torch
+    import torch.distributed as dist
+    from frink_b200 import device
+    from frink_b200.decoder import Decoder
+    cfg, layers, tok, tok_kind, out_norm = synth_model(args.model, args.layers)
+    dec = Decoder(cfg, layers, tok, tok_kind, out_norm, max_seq=1024)
+    del layers
+    S, G = (512, 128) if args.model != "tiny" else (64, 16)
+    prompt = torch.from_numpy(np.random.default_rng(0x70C).integers(0, cfg.vocab, S).astype(np.int32)).cuda()
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn):
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = fn()
+        e1.record()
+        sync()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms, r
+
+    pp = []
+    for _ in range(1 + 3):       # one warm-up, three timed
+        dec.reset()
+        ms, first = timed(lambda: dec.prefill(prompt))
+        pp.append(ms)
+    pp_ms = float(np.median(pp[1:]))
+    cur = first.clone()
+    use_graph = world == 1 or cfg.n_experts == 0 or hasattr(device, "moe_local_slots")
+    if use_graph:
+        g, out = dec.capture_decode(cur)
+        step = lambda: (g.replay(), cur.copy_(out))
+    else:
+        step = lambda: cur.copy_(dec.decode_step(cur))
+    for _ in range(3):
+        step()
+    dec.pos.fill_(S)
+    toks = []
+
+    def run_decode():
+        for _ in range(G):
+            step()
+            toks.append(cur.clone())
+    tg_ms, _ = timed(run_decode)
+    err = device.device_error()
+    if rank == 0:
+        wbytes = sum(v.w.gguf_bytes for L in dec.layers for v in L.values() if hasattr(v, "w") and hasattr(v.w, "gguf_bytes"))
+        print(json.dumps({
+            "metric": "pp512_tg128_tok_s", "model": args.model, "n_gpus": world, "layers": cfg.n_layers,
+            "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
+            "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) + ("+ep%d" % world if cfg.n_experts else ""),
+            "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
+            "tokens_head": [int(t.item()) for t in toks[:8]]}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def int8_peak_tops():

@@ -352,7 +352,7 @@ FK_EXPORT int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_hos
     FK_CUDA(cudaMemcpyAsync(ctx->x_dev, x_batch_host, xn * sizeof(float), cudaMemcpyHostToDevice, nullptr), FK_LAUNCH);
     ctx->h2d += xn * sizeof(float);
     if (batch <= 8) {
-        rc = fk_gemv_launch(ctx, nullptr, w, nullptr, 0, 1, ctx->x_dev, 0, batch, ctx->y_dev, nullptr);
+        rc = fk_gemv_launch(ctx, nullptr, w, nullptr, 0, 1, ctx->x_dev, 0, batch, ctx->y_dev, nullptr, nullptr, nullptr);
     } else {
         ctx->mu.unlock();  // fk_gemm takes the lock itself when it grows scratch
         rc = fk_gemm(ctx, nullptr, w, 0, ctx->x_dev, batch, ctx->y_dev);

@@ -102,8 +102,17 @@ static inline int fk_kind_block_elems(int kind) {
 static inline int fk_kind_run(int kind) { return kind == FK_Q6_K ? 16 : 32; }
 
 // internal entry points of the kernel files ----------------------------------
+struct FkGemvFused {
+    const float* norm_w;
+    float norm_eps;
+    const float* glu_up;
+    int glu_act;
+    int accumulate;
+    int x_ld;
+};
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
-                   const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev);
+                   const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
+                   const FkGemvFused* fused);
 int fk_ensure_scratch(fk_ctx* ctx, size_t bytes);
 
 // device helpers --------------------------------------------------------------

@@ -37,9 +37,17 @@ struct GemvArgs {
     size_t plane_off[4];
     size_t plane_stride[4];
     const int* ids;
+    const int* n_active;   // indexed form: slots >= *n_active do nothing (null = all run)
     int mat;
     const float* x;
-    int x_stride;
+    int x_stride;          // floats between the inputs of consecutive slots
+    int x_ld;              // floats between batch rows of x (and of glu_up)
+    // fused prologue / epilogue (all optional)
+    const float* norm_w;   // RMSNorm weight: the kernel reads rmsnorm(x) * norm_w instead of x
+    float norm_eps;
+    const float* glu_up;   // gated activation: the kernel reads act(x) * glu_up, x being the gate
+    int glu_act;           // 0 SiLU, 1 the clamped gpt-oss form
+    int accumulate;        // y += result instead of y = result
     float* y;
     int rows, cols, batch;
     int32_t* isums;
@@ -350,6 +358,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slot = blockIdx.y;
+    if (a.n_active && slot >= *a.n_active) return;
     const int mat = a.ids ? a.ids[slot] : a.mat;
     const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
     const float* x = a.x + (size_t)slot * a.x_stride;
@@ -405,6 +414,28 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // ---- activations -> q8_1 in shared memory.  A thread takes one float4, eight
     // lanes make a run of 32; all of a thread's loads go out before any is used,
     // so the block pays one L2 round trip, not one per run.
+    __shared__ float s_scale[8];
+    __shared__ double s_part[GEMV_WARPS];
+    if (a.norm_w) {
+        // fused RMSNorm: squares in f32, summed in f64, the mean rounded to f32, 1/sqrtf(mean + eps)
+        const int c4n = cols >> 2;
+        for (int b = 0; b < a.batch; b++) {
+            double sq = 0.0;
+            for (int i = threadIdx.x; i < c4n; i += GEMV_THREADS) {
+                const float4 v = __ldg((const float4*)(x + (size_t)b * a.x_ld) + i);
+                sq += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
+            }
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            if (lane == 0) s_part[warp] = sq;
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                double t = 0.0;
+                for (int i = 0; i < GEMV_WARPS; i++) t += s_part[i];
+                s_scale[b] = 1.0f / sqrtf((float)(t / (double)cols) + a.norm_eps);
+            }
+            __syncthreads();
+        }
+    }
     {
         const int c4 = cols >> 2, items = NB * c4;
         constexpr int QU = 4;
@@ -416,7 +447,30 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                 v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (idx < items) {
                     const int b = idx / c4, k4 = idx - b * c4;
-                    if (b < a.batch) v[u] = __ldg((const float4*)(x + (size_t)b * cols) + k4);
+                    if (b < a.batch) {
+                        v[u] = __ldg((const float4*)(x + (size_t)b * a.x_ld) + k4);
+                        if (a.norm_w) {
+                            const float4 nw = __ldg((const float4*)a.norm_w + k4);
+                            const float sc = s_scale[b];
+                            v[u].x = v[u].x * sc * nw.x; v[u].y = v[u].y * sc * nw.y;
+                            v[u].z = v[u].z * sc * nw.z; v[u].w = v[u].w * sc * nw.w;
+                        }
+                        if (a.glu_up) {
+                            const float4 up = __ldg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
+                            float g[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                            const float uu[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                if (a.glu_act == 0) {
+                                    g[e] = (g[e] / (1.0f + expf(-g[e]))) * uu[e];
+                                } else {
+                                    const float xg = fminf(g[e], 7.0f), yu = fminf(fmaxf(uu[e], -7.0f), 7.0f);
+                                    g[e] = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                                }
+                            }
+                            v[u] = make_float4(g[0], g[1], g[2], g[3]);
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -509,7 +563,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                     v += __shfl_xor_sync(0xffffffffu, v, 2);
                     v += __shfl_xor_sync(0xffffffffu, v, 1);
                     const int row = row0 + hw * LR + r;
-                    if ((lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0) && row < rows && b < a.batch) y[(size_t)b * rows + row] = v;
+                    if ((lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0) && row < rows && b < a.batch) {
+                        float* dst = y + (size_t)b * rows + row;
+                        *dst = a.accumulate ? *dst + v : v;
+                    }
                 }
         }
     }
@@ -605,8 +662,19 @@ __global__ void quantize_q8_1_kernel(const float* __restrict__ x, int n_runs, ui
 }  // namespace
 
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
-                   const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev) {
+                   const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
+                   const FkGemvFused* fused) {
     GemvArgs a{};
+    a.n_active = n_active_dev;
+    a.x_ld = w->cols;
+    if (fused) {
+        a.norm_w = fused->norm_w;
+        a.norm_eps = fused->norm_eps;
+        a.glu_up = fused->glu_up;
+        a.glu_act = fused->glu_act;
+        a.accumulate = fused->accumulate;
+        if (fused->x_ld) a.x_ld = fused->x_ld;
+    }
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
     for (int i = 0; i < 4; i++) {
@@ -650,7 +718,22 @@ FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv: matrix %d of %d", mat, w->n_mats);
     if ((uintptr_t)x_dev & 15) return fk_fail(FK_INVALID, "gemv: x_dev must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
-    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr);
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, nullptr);
+}
+
+FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate) {
+    if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_fused: null argument");
+    if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv_fused: batch %d outside 1..8", batch);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_fused: matrix %d of %d", mat, w->n_mats);
+    if (x_ld == 0) x_ld = w->cols;
+    if (x_ld < w->cols || (x_ld & 3)) return fk_fail(FK_INVALID, "gemv_fused: x_ld %d (columns %d, must be a multiple of 4)", x_ld, w->cols);
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)glu_up_dev & 15) || ((uintptr_t)norm_weight_dev & 15))
+        return fk_fail(FK_INVALID, "gemv_fused: inputs must be 16-byte aligned");
+    if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused: activation %d", glu_act);
+    FkDeviceGuard g(ctx->device);
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld};
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
 }
 
 FK_EXPORT int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
@@ -660,7 +743,17 @@ FK_EXPORT int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* i
     if (x_stride != 0 && x_stride < w->cols) return fk_fail(FK_INVALID, "gemv_multi: x_stride %d < cols %d", x_stride, w->cols);
     if (((uintptr_t)x_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi: x_dev must be 16-byte aligned and x_stride a multiple of 4");
     FkDeviceGuard g(ctx->device);
-    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr);
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, nullptr);
+}
+
+FK_EXPORT int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
+                                   int x_stride, float* y_dev, const int* n_active_dev) {
+    if (!ctx || !w || !ids_dev || !x_dev || !y_dev || !n_active_dev) return fk_fail(FK_INVALID, "gemv_multi_active: null argument");
+    if (k < 1 || k > 65535) return fk_fail(FK_INVALID, "gemv_multi_active: k=%d", k);
+    if (x_stride != 0 && x_stride < w->cols) return fk_fail(FK_INVALID, "gemv_multi_active: x_stride %d < cols %d", x_stride, w->cols);
+    if (((uintptr_t)x_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_active: x_dev must be 16-byte aligned and x_stride a multiple of 4");
+    FkDeviceGuard g(ctx->device);
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr, n_active_dev, nullptr);
 }
 
 FK_EXPORT int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int32_t* isums_dev) {
@@ -671,5 +764,5 @@ FK_EXPORT int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
     // y is not wanted: park it in the context's scratch
     int rc = fk_ensure_scratch(ctx, (size_t)w->rows * sizeof(float));
     if (rc) return rc;
-    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, 1, (float*)ctx->scratch, isums_dev);
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, 1, (float*)ctx->scratch, isums_dev, nullptr, nullptr);
 }

@@ -167,7 +167,54 @@ __global__ void combine_kernel(const float* __restrict__ y, const int* __restric
     out[(size_t)t * n + i] = acc;
 }
 
+// One warp: the chosen experts of one token that fall in [e0, e0 + n_local), packed
+// to the front in routing order with their weights; the rest padded with expert 0 /
+// weight 0.  *out_n = how many.
+__global__ void local_slots_kernel(const int* __restrict__ ids, const float* __restrict__ w, int k, int e0, int n_local,
+                                   int* __restrict__ out_ids, float* __restrict__ out_w, int* __restrict__ out_n) {
+    const int lane = threadIdx.x;
+    const int id = lane < k ? ids[lane] : -1;
+    const bool mine = id >= e0 && id < e0 + n_local;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    const int n = __popc(m);
+    if (lane < k) {
+        out_ids[lane] = 0;
+        out_w[lane] = 0.0f;
+    }
+    __syncwarp();
+    if (mine) {
+        const int p = __popc(m & ((1u << lane) - 1u));
+        out_ids[p] = id - e0;
+        out_w[p] = w[lane];
+    }
+    if (lane == 0) *out_n = n;
+}
+
+// Every kernel of a decode step asks for the same shared-memory carve-out as the GEMV
+// (the maximum): an SM that alternates between kernels with different carve-outs
+// re-partitions its L1 between them, which costs more than these kernels run.
+template <typename K> void fk_carveout(K kern) {
+    static thread_local const void* done[64];
+    static thread_local int n = 0;
+    for (int i = 0; i < n; i++) if (done[i] == (const void*)kern) return;
+    cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (n < 64) done[n++] = (const void*)kern;
+}
+#define FK_CARVEOUT(k) fk_carveout(k)
+
 }  // namespace
+
+FK_EXPORT int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int k, int e0, int n_local,
+                                 int* out_ids_dev, float* out_w_dev, int* out_n_dev) {
+    if (!ctx || !ids_dev || !w_dev || !out_ids_dev || !out_w_dev || !out_n_dev) return fk_fail(FK_INVALID, "moe_local_slots: null argument");
+    if (k < 1 || k > 32) return fk_fail(FK_UNSUPPORTED, "moe_local_slots: k=%d (limit 32)", k);
+    FkDeviceGuard g(ctx->device);
+    FK_CARVEOUT(local_slots_kernel);
+    local_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ids_dev, w_dev, k, e0, n_local, out_ids_dev, out_w_dev, out_n_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
 
 FK_EXPORT int fk_moe_route(fk_ctx* ctx, void* stream, const float* logits_dev, const float* bias_dev, int n_experts,
                            int k, int mode, int batch, int* ids_dev, float* w_dev) {
@@ -177,6 +224,7 @@ FK_EXPORT int fk_moe_route(fk_ctx* ctx, void* stream, const float* logits_dev, c
     if (mode < 0 || mode > 2) return fk_fail(FK_INVALID, "moe_route: mode %d", mode);
     if (batch < 1) return fk_fail(FK_INVALID, "moe_route: batch %d", batch);
     FkDeviceGuard g(ctx->device);
+    FK_CARVEOUT(route_kernel);
     route_kernel<<<(batch + 3) / 4, 128, 0, (cudaStream_t)stream>>>(logits_dev, bias_dev, n_experts, k, mode, batch, ids_dev, w_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
@@ -189,6 +237,7 @@ FK_EXPORT int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_de
     if (n_experts < 1 || cols < 1 || batch < 1 || batch > 65535) return fk_fail(FK_INVALID, "router_logits: %d x %d, batch %d", n_experts, cols, batch);
     FkDeviceGuard g(ctx->device);
     dim3 grid((n_experts + 7) / 8, batch);
+    FK_CARVEOUT(router_logits_kernel);
     router_logits_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(router_dev, x_dev, logits_dev, n_experts, cols);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
@@ -200,6 +249,7 @@ FK_EXPORT int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int 
     if (!ctx || !ids_dev || !group_off_dev || !gather_dev || !pair_of_dev) return fk_fail(FK_INVALID, "moe_permute: null argument");
     if (pairs < 1 || k < 1 || n_experts < 1 || n_experts > 4096) return fk_fail(FK_INVALID, "moe_permute: pairs %d, k %d, experts %d", pairs, k, n_experts);
     FkDeviceGuard g(ctx->device);
+    FK_CARVEOUT(permute_kernel);
     permute_kernel<<<1, 1024, (n_experts + 1) * sizeof(int), (cudaStream_t)stream>>>(ids_dev, pairs, k, n_experts, group_off_dev, gather_dev, pair_of_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
@@ -211,6 +261,7 @@ FK_EXPORT int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const flo
     if (act < 0 || act > 1) return fk_fail(FK_UNSUPPORTED, "glu: activation %d", act);
     if (n == 0) return FK_OK;
     FkDeviceGuard g(ctx->device);
+    FK_CARVEOUT(glu_kernel);
     glu_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gate_dev, up_dev, n, act, out_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
@@ -223,6 +274,7 @@ FK_EXPORT int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, cons
     if (batch < 1 || batch > 65535 || k < 1 || n < 1) return fk_fail(FK_INVALID, "moe_combine: batch %d, k %d, n %d", batch, k, n);
     FkDeviceGuard g(ctx->device);
     dim3 grid((n + 255) / 256, batch);
+    FK_CARVEOUT(combine_kernel);
     combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;

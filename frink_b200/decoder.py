@@ -1,0 +1,249 @@
+"""A minimal resident decoder over the quantized matmuls: what frink-models'
+CUDA glue drives through `frink_cuda::prefill::launch_stack`
+(crates/frink-models/src/decoder/cuda_prefill.rs:89, crates/frink-cuda/src/prefill/
+layer.rs:44 `run_layer_resident`), reduced to the dense Llama graph and the
+Qwen3-MoE graph: RMSNorm -> q/k/v -> RoPE -> KV append -> causal GQA -> wo ->
+residual -> RMSNorm -> SwiGLU FFN or routed experts -> residual; final norm,
+output head, greedy argmax.  Everything stays on the device; the position is a
+device word so one decode step can be captured in a CUDA graph and replayed.
+
+With a process group, dense projections are tensor parallel (q/k/v/gate/up split
+by rows = heads, wo/down split by columns, one all-reduce each) and routed
+experts are expert parallel (`parallel.ExpertParallelLayer.decode`)."""
+from dataclasses import dataclass, field
+from typing import Any, List, Optional
+
+import torch
+
+from . import parallel
+from .prefill import RoutedLayer, run_device_routed, run_device_routed_batch
+
+
+@dataclass
+class DecoderConfig:
+    n_layers: int
+    hidden: int
+    n_heads: int
+    n_kv: int
+    head_dim: int
+    ffn: int
+    vocab: int
+    rope_theta: float = 500000.0
+    eps: float = 1e-5
+    neox: bool = False          # Llama: adjacent pairs; Qwen3: split halves
+    qk_norm: bool = False       # Qwen3 per-head RMSNorm on q and k
+    n_experts: int = 0          # > 0: routed FFN
+    top_k: int = 0
+    route_mode: int = 1
+
+
+@dataclass
+class LayerWeights:
+    """GGUF bytes (numpy uint8) + kinds of one layer; norms as f32 numpy."""
+    attn_norm: Any
+    wq: Any
+    wk: Any
+    wv: Any
+    wo: Any
+    ffn_norm: Any
+    gate: Any = None
+    up: Any = None
+    down: Any = None
+    router: Any = None          # f32 [n_experts, hidden]
+    q_norm: Any = None
+    k_norm: Any = None
+    kinds: dict = field(default_factory=dict)   # name -> fk_kind
+
+
+class _Linear:
+    """rows x cols projection, batch <= 8 through the GEMV, above through the GEMM."""
+
+    def __init__(self, ops, raw, kind, rows, cols):
+        self.ops = ops
+        self.w = ops.Weights(raw, kind, rows, cols)
+
+    def __call__(self, x):
+        return self.ops.gemv(self.w, x) if x.shape[0] <= 8 else self.ops.gemm(self.w, x)
+
+
+class _Merged:
+    """Projections that read the same input and share a block format, stacked by rows
+    into one weight handle: one launch (and one activation quantization) instead of
+    several, as the reference shares one quantized input between q/k/v and gate/up
+    (crates/frink-cuda/src/dp4a_launch.rs:56-62).  Returns the outputs as column slices."""
+
+    def __init__(self, ops, parts, kind, cols):
+        import numpy as np
+        self.ops, self.splits = ops, [r for _, r in parts]
+        raw = np.concatenate([np.ascontiguousarray(b, np.uint8).ravel() for b, _ in parts])
+        self.w = ops.Weights(raw, kind, sum(self.splits), cols)
+
+    def __call__(self, x):
+        y = self.ops.gemv(self.w, x) if x.shape[0] <= 8 else self.ops.gemm(self.w, x)
+        outs, o = [], 0
+        for r in self.splits:
+            outs.append(y[:, o:o + r] if x.shape[0] == 1 else y[:, o:o + r].contiguous())
+            o += r
+        return outs
+
+
+class Decoder:
+    def __init__(self, cfg: DecoderConfig, layers: List[LayerWeights], tok_embd, tok_kind, out_norm, output=None, output_kind=None,
+                 max_seq=1024, ops=None, group=None, device="cuda"):
+        if ops is None:
+            from . import device as ops
+        self.cfg, self.ops, self.group, self.dev = cfg, ops, group, device
+        self.rank, self.world = parallel._world(group) if group is not None or torch.distributed.is_initialized() else (0, 1)
+        T = self.world
+        if cfg.n_heads % T or cfg.n_kv % T:
+            raise ValueError(f"{cfg.n_heads}/{cfg.n_kv} heads do not split over {T} ranks")
+        self.h_loc, self.kv_loc = cfg.n_heads // T, cfg.n_kv // T
+        hd, H = cfg.head_dim, cfg.hidden
+        f32 = lambda a: torch.as_tensor(a, dtype=torch.float32).to(device).contiguous()
+        self.embd = ops.Weights(tok_embd, tok_kind, cfg.vocab, H)
+        self.head = self.embd if output is None else ops.Weights(output, output_kind, cfg.vocab, H)
+        self.out_norm = f32(out_norm)
+        self.layers = []
+        for L in layers:
+            k = L.kinds
+            d = {"attn_norm": f32(L.attn_norm), "ffn_norm": f32(L.ffn_norm)}
+            # q/k/v (and gate/up) as row shards of this rank, stacked where the formats agree
+            sh = lambda raw, kind, rows: parallel.shard_rows(raw, kind, rows, H, self.rank, T)
+            qkv = [(sh(L.wq, k["wq"], cfg.n_heads * hd), k["wq"]), (sh(L.wk, k["wk"], cfg.n_kv * hd), k["wk"]),
+                   (sh(L.wv, k["wv"], cfg.n_kv * hd), k["wv"])]
+            if k["wq"] == k["wk"] == k["wv"]:
+                d["qkv"] = _Merged(ops, [p for p, _ in qkv], k["wq"], H)
+            elif k["wq"] == k["wk"]:
+                d["qk"] = _Merged(ops, [qkv[0][0], qkv[1][0]], k["wq"], H)
+                d["wv"] = _Linear(ops, qkv[2][0][0], k["wv"], qkv[2][0][1], H)
+            else:
+                for name, ((raw, rows), kind) in zip(("wq", "wk", "wv"), qkv):
+                    d[name] = _Linear(ops, raw, kind, rows, H)
+            if T == 1:
+                d["wo"] = _Linear(ops, L.wo, k["wo"], H, cfg.n_heads * hd)
+            else:
+                d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True)
+            if cfg.qk_norm:
+                d["q_norm"], d["k_norm"] = f32(L.q_norm), f32(L.k_norm)
+            if cfg.n_experts:
+                router = f32(L.router)
+                if T == 1:
+                    mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
+                    d["moe"] = RoutedLayer(router, mk(L.gate, cfg.ffn, H), mk(L.up, cfg.ffn, H), mk(L.down, H, cfg.ffn), k=cfg.top_k,
+                                           mode=cfg.route_mode)
+                else:
+                    d["ep"] = parallel.ExpertParallelLayer(ops, router, L.gate, L.up, L.down, k["experts"], cfg.n_experts, H, cfg.ffn,
+                                                           cfg.top_k, mode=cfg.route_mode, group=group)
+            else:
+                gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, self.rank, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, self.rank, T)]
+                if k["gate"] == k["up"]:
+                    d["gate_up"] = _Merged(ops, gu, k["gate"], H)
+                else:
+                    d["gate"] = _Linear(ops, gu[0][0], k["gate"], gu[0][1], H)
+                    d["up"] = _Linear(ops, gu[1][0], k["up"], gu[1][1], H)
+                if T == 1:
+                    d["down"] = _Linear(ops, L.down, k["down"], H, cfg.ffn)
+                else:
+                    d["down"] = parallel.RowParallelLinear(ops, L.down, k["down"], H, cfg.ffn, group, input_is_sharded=True)
+            d["k"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
+            d["v"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
+            self.layers.append(d)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)
+        self.max_seq = max_seq
+        self._graph = None
+
+    def reset(self):
+        self.pos.zero_()
+
+    # ---- one forward over n rows (token ids on the device); returns logits of the last row
+    def forward(self, ids):
+        ops, cfg = self.ops, self.cfg
+        hd = cfg.head_dim
+        n = ids.numel()
+        x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
+        pending = None                                      # a block output not yet added to x
+        for L in self.layers:
+            h = ops.rmsnorm(x, L["attn_norm"], cfg.eps, residual=pending)
+            if "qkv" in L:
+                q, k, v = L["qkv"](h)
+            elif "qk" in L:
+                (q, k), v = L["qk"](h), L["wv"](h)
+            else:
+                q, k, v = L["wq"](h), L["wk"](h), L["wv"](h)
+            if cfg.qk_norm:
+                q = ops.rmsnorm(q.view(-1, hd), L["q_norm"], cfg.eps).view(n, -1)
+                k = ops.rmsnorm(k.view(-1, hd), L["k_norm"], cfg.eps).view(n, -1)
+            ops.rope(q, self.h_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
+            ops.rope(k, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
+            ops.kv_append(L["k"], k, self.pos)
+            ops.kv_append(L["v"], v, self.pos)
+            a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
+            o = L["wo"](a)
+            h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps, residual=o)
+            if "moe" in L:
+                pending = run_device_routed(L["moe"], h2, ops) if n <= 8 else run_device_routed_batch(L["moe"], h2, ops)
+            elif "ep" in L:
+                pending = torch.stack([L["ep"].decode(h2[t]) for t in range(n)]) if n <= 8 else self._ep_prefill(L["ep"], h2)
+            else:
+                g_, u_ = L["gate_up"](h2) if "gate_up" in L else (L["gate"](h2), L["up"](h2))
+                pending = L["down"](ops.glu(g_.contiguous(), u_.contiguous(), 0))
+        last = x[n - 1:n].contiguous()
+        hn = ops.rmsnorm(last, self.out_norm, cfg.eps, residual=pending[n - 1:n].contiguous())
+        logits = ops.gemv(self.head, hn)
+        ops.add_int_(self.pos, n)
+        return logits
+
+    def _ep_prefill(self, ep, h2):
+        """Activations are replicated under TP, so every rank holds all rows: each takes
+        its share of the rows through the dispatch/combine path and the results are gathered."""
+        n, P, r = h2.shape[0], self.world, self.rank
+        per = -(-n // P)
+        lo, hi = min(n, r * per), min(n, (r + 1) * per)
+        mine = ep.prefill(h2[lo:hi].contiguous()) if hi > lo else h2.new_zeros((0, h2.shape[1]))
+        parts = [h2.new_empty((min(n, (i + 1) * per) - min(n, i * per), h2.shape[1])) for i in range(P)]
+        for i in range(P):   # row counts may differ by rank: one broadcast per owner
+            buf = mine if i == r else parts[i]
+            if buf.shape[0]:
+                torch.distributed.broadcast(buf, src=torch.distributed.get_global_rank(self.group, i) if self.group is not None else i,
+                                            group=self.group)
+        parts[r] = mine
+        return torch.cat(parts)
+
+    def prefill(self, ids):
+        """Prompt of S token ids -> the first generated token (device int32 [1])."""
+        return self.ops.argmax(self.forward(ids))
+
+    def decode_step(self, tok):
+        return self.ops.argmax(self.forward(tok))
+
+    def capture_decode(self, tok):
+        """Capture one decode step (reads `tok`, writes the returned tensor, advances
+        the position word) into a CUDA graph; `replay()` runs it again."""
+        pos0 = self.pos.clone()
+        for _ in range(2):                      # warm up outside the capture, then put the position back
+            self.decode_step(tok)
+        self.pos.copy_(pos0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self.decode_step(tok)
+        self.pos.copy_(pos0)
+        self._graph, self._gout = g, out
+        return g, out
+
+    def generate(self, prompt_ids, n_new, use_graph=False):
+        """Greedy: returns the n_new generated token ids (list of int)."""
+        tok = self.prefill(prompt_ids)
+        outs = [tok.clone()]
+        if use_graph and n_new > 1:
+            cur = tok.clone()
+            g, out = self.capture_decode(cur)
+            for _ in range(n_new - 1):
+                g.replay()
+                cur.copy_(out)
+                outs.append(out.clone())
+        else:
+            for _ in range(n_new - 1):
+                tok = self.decode_step(tok)
+                outs.append(tok.clone())
+        return [int(t.item()) for t in outs]

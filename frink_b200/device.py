@@ -120,6 +120,28 @@ def gemv(w, x, mat=0, out=None):
     return y if x.dim() > 1 or out is not None else y[0]
 
 
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False):
+    """gemv with its elementwise neighbours folded in: reads rmsnorm(x) * norm_weight, or
+    act(x) * glu_up (x the gate), and/or adds into `out` instead of overwriting it.
+    x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4."""
+    assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
+    batch, ld = x.shape[0], x.stride(0) if x.shape[0] > 1 else max(x.stride(0), w.cols)
+    if glu_up is not None:
+        assert glu_up.shape == x.shape and glu_up.stride(1) == 1 and (batch == 1 or glu_up.stride(0) == x.stride(0))
+    y = out if out is not None else torch.empty((batch, w.rows), dtype=torch.float32, device=x.device)
+    check(lib().fk_gemv_fused(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
+                              _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
+                              _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate))))
+    return y
+
+
+def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache):
+    """One launch: rotate q and k in place (rows at pos[0] + r) and append k, v to the caches."""
+    n = q.shape[0]
+    check(lib().fk_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), n, n_heads, n_kv, head_dim,
+                           _ptr(_i32(pos)), float(theta), int(neox), _ptr(k_cache), _ptr(v_cache)))
+
+
 def gemv_multi(w, ids, x, out=None):
     """Slot j: matrix ids[j] of `w` times x[j] (or the one shared x) -> out[j]."""
     ids, x = _i32(ids), _f32(x)
@@ -128,6 +150,24 @@ def gemv_multi(w, ids, x, out=None):
     y = out if out is not None else torch.empty((k, w.rows), dtype=torch.float32, device=x.device)
     check(lib().fk_gemv_multi(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(x), stride, _ptr(y)))
     return y
+
+
+def gemv_multi_active(w, ids, x, n_active, out):
+    """gemv_multi whose slots >= n_active[0] (a device word) are skipped; `out` keeps its contents there."""
+    ids, x = _i32(ids), _f32(x)
+    stride = 0 if x.dim() == 1 else x.stride(0)
+    check(lib().fk_gemv_multi_active(w._ctx, _stream(), w.handle, _ptr(ids), ids.numel(), _ptr(x), stride, _ptr(out), _ptr(_i32(n_active))))
+    return out
+
+
+def moe_local_slots(ids, w, e0, n_local):
+    ids, w = _i32(ids).reshape(-1), _f32(w).reshape(-1)
+    k = ids.numel()
+    oi = torch.empty(k, dtype=torch.int32, device=ids.device)
+    ow = torch.empty(k, dtype=torch.float32, device=ids.device)
+    on = torch.empty(1, dtype=torch.int32, device=ids.device)
+    check(lib().fk_moe_local_slots(context(ids.device), _stream(), _ptr(ids), _ptr(w), k, e0, n_local, _ptr(oi), _ptr(ow), _ptr(on)))
+    return oi, ow, on
 
 
 def gemv_isums(w, x, mat=0):
@@ -214,3 +254,64 @@ def moe_combine(y, pair_of, w, batch, k, out=None):
     check(lib().fk_moe_combine(context(y.device), _stream(), _ptr(y), _ptr(_i32(pair_of)) if pair_of is not None else None,
                                _ptr(w), batch, k, n, _ptr(o)))
     return o
+
+
+# ---- decoder glue -----------------------------------------------------------
+def get_rows(w, ids, mat=0, out=None):
+    ids = _i32(ids)
+    o = out if out is not None else torch.empty((ids.numel(), w.cols), dtype=torch.float32, device=ids.device)
+    check(lib().fk_get_rows(w._ctx, _stream(), w.handle, mat, _ptr(ids), ids.numel(), _ptr(o)))
+    return o
+
+
+def rmsnorm(x, weight, eps, residual=None, out=None):
+    """out = rmsnorm(x (+ residual)) * weight; with `residual`, x is updated in place to the sum."""
+    assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+    x2 = x if x.dim() == 2 else x[None]
+    o = out if out is not None else torch.empty_like(x2)
+    r = _f32(residual) if residual is not None else None
+    check(lib().fk_rmsnorm(context(x.device), _stream(), _ptr(x2), _ptr(r), _ptr(_f32(weight)), x2.shape[0], x2.shape[1], float(eps), _ptr(o)))
+    return o if x.dim() == 2 else o[0]
+
+
+def rope(x, n_heads, head_dim, pos, theta, neox=False):
+    """In place; x is [n_rows, n_heads * head_dim], `pos` an int32 device word."""
+    assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous()
+    n_rows = 1 if x.dim() == 1 else x.shape[0]
+    check(lib().fk_rope(context(x.device), _stream(), _ptr(x), n_rows, n_heads, head_dim, _ptr(_i32(pos)), float(theta), int(neox)))
+    return x
+
+
+def add_(a, b):
+    assert a.is_contiguous() and b.is_contiguous()
+    check(lib().fk_add(context(a.device), _stream(), _ptr(a), _ptr(_f32(b)), a.numel()))
+    return a
+
+
+def kv_append(cache, src, pos):
+    """cache [T, row] rows [*pos, *pos + n) <- src [n, row]."""
+    src = _f32(src)
+    n = 1 if src.dim() == 1 else src.shape[0]
+    check(lib().fk_kv_append(context(cache.device), _stream(), _ptr(cache), _ptr(src), cache.shape[1], n, _ptr(_i32(pos))))
+
+
+def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
+    q = _f32(q)
+    q2 = q if q.dim() == 2 else q[None]
+    o = out if out is not None else torch.empty_like(q2)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    check(lib().fk_attention(context(q.device), _stream(), _ptr(q2), _ptr(k_cache), _ptr(v_cache), q2.shape[0], n_heads, n_kv, head_dim,
+                             _ptr(_i32(pos)), sc, _ptr(o)))
+    return o if q.dim() == 2 else o[0]
+
+
+def argmax(x, out=None):
+    x = _f32(x)
+    x2 = x if x.dim() == 2 else x[None]
+    o = out if out is not None else torch.empty(x2.shape[0], dtype=torch.int32, device=x.device)
+    check(lib().fk_argmax(context(x.device), _stream(), _ptr(x2), x2.shape[0], x2.shape[1], _ptr(o)))
+    return o
+
+
+def add_int_(p, v):
+    check(lib().fk_add_int(context(p.device), _stream(), _ptr(_i32(p)), int(v)))

@@ -138,18 +138,30 @@ class ExpertParallelLayer:
     # ---- decode: activation replicated, partial combine, one all-reduce
     def decode(self, x):
         from .prefill import route
-        ops, L = self.ops, self.layer
+        ops, L, k = self.ops, self.layer, self.k
         ids, w = route(L, x, ops)                       # replicated: every rank routes the same way
-        ids1, w1 = ids.reshape(-1), w.reshape(-1)
-        mine = (ids1 >= self.e0) & (ids1 < self.e0 + self.n_local)
-        out = torch.zeros(self.hidden, dtype=torch.float32, device=x.device)
-        n = int(mine.sum().item())
-        if n:
-            lid = (ids1[mine] - self.e0).to(torch.int32).contiguous()
-            g = ops.gemv_multi(L.gate, lid, x)
-            u = ops.gemv_multi(L.up, lid, x)
-            y = ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act))
-            out = ops.moe_combine(y, None, w1[mine].contiguous()[None], 1, n)[0]
+        if hasattr(ops, "moe_local_slots"):
+            # all on the device: the chosen experts this rank owns move to the front, the
+            # indexed matvecs skip the other slots, whose zeroed outputs carry weight 0
+            lid, lw, n = ops.moe_local_slots(ids, w, self.e0, self.n_local)
+            g = torch.zeros((k, self.ffn), dtype=torch.float32, device=x.device)
+            u = torch.zeros_like(g)
+            y = torch.zeros((k, self.hidden), dtype=torch.float32, device=x.device)
+            ops.gemv_multi_active(L.gate, lid, x, n, g)
+            ops.gemv_multi_active(L.up, lid, x, n, u)
+            ops.gemv_multi_active(L.down, lid, ops.glu(g, u, L.act), n, y)
+            out = ops.moe_combine(y, None, lw[None], 1, k)[0]
+        else:
+            ids1, w1 = ids.reshape(-1), w.reshape(-1)
+            mine = (ids1 >= self.e0) & (ids1 < self.e0 + self.n_local)
+            out = torch.zeros(self.hidden, dtype=torch.float32, device=x.device)
+            n = int(mine.sum().item())
+            if n:
+                lid = (ids1[mine] - self.e0).to(torch.int32).contiguous()
+                g = ops.gemv_multi(L.gate, lid, x)
+                u = ops.gemv_multi(L.up, lid, x)
+                y = ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act))
+                out = ops.moe_combine(y, None, w1[mine].contiguous()[None], 1, n)[0]
         if self.world > 1:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out

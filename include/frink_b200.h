@@ -95,12 +95,29 @@ int fk_quantize_q8_1(fk_ctx* ctx, void* stream, const float* x_dev, int n, uint8
  * y_dev[b * rows + r] = W[mat][r] . q8_1(x_dev[b * cols ..]),  0 <= b < batch. */
 int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev);
 
+/* fk_gemv with the elementwise neighbours of a decode step folded in (the reference
+ * runs them as separate kernels: `fused_add_rmsnorm_f32` crates/frink-cuda/src/gpu.rs:459,
+ * `silu_mul_f32` src/glu.rs:68, `add_rows_f32` src/prefill/kernels.rs:70).  All optional:
+ * norm_weight_dev: the matvec reads rmsnorm(x) * norm_weight (squares summed in f64);
+ * glu_up_dev: the matvec reads act(x) * glu_up, x being the gate (act 0 SiLU, 1 gpt-oss);
+ * accumulate != 0: y += W x (the residual add).  x_ld = floats between batch rows of x
+ * and glu_up (0 = cols). */
+int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                  const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate);
+
 /* Indexed expert GEMV: the `FX_MULTI` form (kernels.rs:166-179,
  * dp4a_launch.rs:256-314).  Slot j (0 <= j < k) multiplies matrix
  * `ids_dev[j]` of `w` with x_dev[j * x_stride ..] (x_stride 0 = one shared
  * input) into y_dev[j * rows ..]. */
 int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
                   int x_stride, float* y_dev);
+
+/* fk_gemv_multi whose slots >= *n_active_dev do nothing (their outputs are left as
+ * they are).  Expert-parallel decode runs only the chosen experts a rank owns
+ * without a host round trip for the count; no counterpart in the single-device
+ * reference. */
+int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
+                         int x_stride, float* y_dev, const int* n_active_dev);
 
 /* Test hook (the reference's twins expose the same integers,
  * crates/frink-cuda/src/dp4a_twin.rs:142-231): the exact int32 dot of every
@@ -149,6 +166,11 @@ int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_dev, const f
  * gather_dev[pairs] (token of each permuted row), pair_of_dev[pairs]. */
 int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int k, int n_experts,
                    int* group_off_dev, int* gather_dev, int* pair_of_dev);
+/* Expert-parallel decode (no reference counterpart): of one token's k routed
+ * experts, those in [e0, e0 + n_local) packed to the front in routing order as
+ * local ids with their weights (the rest: expert 0, weight 0); *out_n = count. */
+int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int k, int e0, int n_local,
+                       int* out_ids_dev, float* out_w_dev, int* out_n_dev);
 /* `silu_mul_f32` / `swiglu_oai_f32` (crates/frink-cuda/src/glu.rs:42,68):
  * act 0 = silu(gate) * up, 1 = gpt-oss clamped SwiGLU (alpha 1.702, limit 7). */
 int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev, size_t n, int act,
@@ -157,6 +179,37 @@ int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev
  * y[pair_of[t*k+j]] from zero in routing order (pair_of NULL = identity). */
 int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
                    int batch, int k, int n, float* out_dev);
+
+/* ---- decoder glue (next-row components: enough to run a decoder and report
+ * prefill / decode tokens per second; f32 throughout) -------------------------
+ * `get_rows` (crates/frink-cuda/src/get_rows.rs:52): out[i] = dequantized row ids[i]. */
+int fk_get_rows(fk_ctx* ctx, void* stream, fk_weight w, int mat, const int* ids_dev, int n, float* out_dev);
+/* `rmsnorm_rows_f32` / `fused_add_rmsnorm_f32` (crates/frink-cuda/src/prefill/kernels.rs:26,
+ * src/gpu.rs:459): if residual_dev is given, x += residual first (kept in x); then
+ * out = x * (1/sqrt(mean(x^2) + eps)) * weight, squares summed in f64
+ * (crates/frink-core/src/matmul.rs:87-95). */
+int fk_rmsnorm(fk_ctx* ctx, void* stream, float* x_dev, const float* residual_dev, const float* weight_dev, int n_rows, int cols,
+               float eps, float* out_dev);
+/* `rope_rows_f32` (kernels.rs:402): in place over [n_rows][n_heads][head_dim]; row r is
+ * at position *pos_dev + r; neox 0 rotates pairs (2i, 2i+1), else (i, i + head_dim/2). */
+int fk_rope(fk_ctx* ctx, void* stream, float* x_dev, int n_rows, int n_heads, int head_dim, const int* pos_dev, float theta, int neox);
+/* rope of q and k and the KV append of one step in one launch: q [n][n_heads*hd] and
+ * k [n][n_kv*hd] are rotated in place (rows at *pos + r), then k and v rows are
+ * written to the caches at *pos.  q_ld / kv_ld = floats between rows. */
+int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const float* v_dev, int q_ld, int kv_ld, int n_rows, int n_heads,
+               int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev);
+/* `add_rows_f32` (kernels.rs:70): a += b. */
+int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n);
+/* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */
+int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev);
+/* `causal_gqa_prefill_f32` / `decode_attn_*` (kernels.rs:488, src/decode_attn.rs:125):
+ * query row r at position *pos + r attends keys 0..=*pos + r of K/V [T][n_kv][head_dim]. */
+int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_dev, const float* v_dev, int n_q, int n_heads, int n_kv,
+                 int head_dim, const int* pos_dev, float scale, float* out_dev);
+/* Greedy sampling: index of the largest of each row, ties to the lower index. */
+int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);
+/* *p += v on the device (the position word of a captured decode step). */
+int fk_add_int(fk_ctx* ctx, void* stream, int* p_dev, int v);
 
 /* ---- host-buffer launch surface -------------------------------------------
  * What frink-core binds (crates/frink-core/src/weight_matrix/gpu_backend.rs:
