@@ -29,7 +29,7 @@ SYMBOLS = {
     "fk_weight_shape": (_I, [_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_SZ)]),
     "fk_quantize_q8_1": (_I, [_P, _P, _P, _I, _P]),
     "fk_gemv": (_I, [_P, _P, _P, _I, _P, _I, _P]),
-    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I]),
+    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
     "fk_gemv_multi": (_I, [_P, _P, _P, _P, _I, _P, _I, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "fk_moe_local_slots": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
@@ -48,7 +48,7 @@ SYMBOLS = {
     "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P]),
     "fk_add": (_I, [_P, _P, _P, _P, _SZ]),
     "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P]),
-    "fk_attention": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P]),
+    "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),
     "fk_add_int": (_I, [_P, _P, _P, _I]),
     "fk_launch_matvec": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _P]),

@@ -36,7 +36,8 @@ def build(force=False, verbose=False):
         o = os.path.join(CSRC, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            extra = os.environ.get("FK_NVCC_EXTRA", "").split()     # e.g. -DFK_TRACE (kernel phase stamps)
+            cmd = [_nvcc()] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             subprocess.check_call(cmd)
     if force or _stale(LIB, objs):
         subprocess.check_call([_nvcc(), "-shared", "-o", LIB] + objs + ["-lcudart"])

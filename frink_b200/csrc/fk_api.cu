@@ -48,6 +48,11 @@ FK_EXPORT int fk_init(int device, fk_ctx** out) {
     FkDeviceGuard g(device);
     e = cudaMalloc(&ctx->err_flag, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_ws, 64 * 64 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_cnt, 64 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->argmax_cnt, 0, 64 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->attn_cnt, 4096 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->attn_cnt, 0, 4096 * sizeof(unsigned));
     if (e != cudaSuccess) {
         delete ctx;
         return fk_fail(FK_DRIVER_INIT, "context allocation: %s", cudaGetErrorString(e));
@@ -64,6 +69,9 @@ FK_EXPORT void fk_destroy(fk_ctx* ctx) {
     cudaFree(ctx->y_dev);
     cudaFree(ctx->scratch);
     cudaFree(ctx->err_flag);
+    cudaFree(ctx->argmax_ws);
+    cudaFree(ctx->argmax_cnt);
+    cudaFree(ctx->attn_cnt);
     delete ctx;
 }
 

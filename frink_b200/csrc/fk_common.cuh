@@ -64,6 +64,12 @@ struct fk_ctx {
     size_t scratch_cap = 0;
     // device word kernels raise when a bounded wait gives up
     int* err_flag = nullptr;
+    // argmax: per-(row, block) keys and per-row arrival counters (64 x 64 keys, 64 counters);
+    // one argmax in flight per context
+    unsigned long long* argmax_ws = nullptr;
+    unsigned* argmax_cnt = nullptr;
+    // decode attention: arrival counters per (query row, head), 4096 of them
+    unsigned* attn_cnt = nullptr;
     std::atomic<uint64_t> h2d{0}, d2h{0}, launches{0};
 };
 
@@ -109,6 +115,8 @@ struct FkGemvFused {
     int glu_act;
     int accumulate;
     int x_ld;
+    const uint8_t* pf_ptr;          // L2 prefetch of the next kernel's weights (may be null)
+    unsigned long long pf_bytes;
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,

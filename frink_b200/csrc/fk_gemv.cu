@@ -48,6 +48,13 @@ struct GemvArgs {
     const float* glu_up;   // gated activation: the kernel reads act(x) * glu_up, x being the gate
     int glu_act;           // 0 SiLU, 1 the clamped gpt-oss form
     int accumulate;        // y += result instead of y = result
+    // bytes the NEXT kernel of the stream will stream (its weights): requested into L2
+    // while this kernel runs, so the next one starts on warm lines
+    const uint8_t* pf_ptr;
+    unsigned long long pf_bytes;
+#ifdef FK_TRACE
+    int trace_slot;
+#endif
     float* y;
     int rows, cols, batch;
     int32_t* isums;
@@ -175,6 +182,18 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, int b, int c) {   // unsigned
     return d;
 }
 
+// Where 16-byte chunk `c` of a row of quantized activations sits in shared memory.
+// The lanes of a quarter warp (one shared-memory access phase) read chunks whose
+// natural addresses fall on the same banks (Q4_K: 64 bytes apart per lane, 256 per
+// block; Q6_K: groups q and q + 8; MXFP4: 32 bytes apart), so a few low bits of the
+// chunk index are XOR-ed with higher ones; every phase then covers all 32 banks.
+template <int KIND> __device__ __forceinline__ int act_chunk(int c) {
+    if (KIND == FK_Q4_K) return c ^ ((c >> 3) & 3);
+    if (KIND == FK_Q6_K) return c ^ (((c >> 3) & 1) << 2);
+    if (KIND == FK_MXFP4) return c ^ ((c >> 3) & 1);
+    return c;
+}
+
 // Q4_K, one trip of the lane's two rows.  The lane's half warp covers 4
 // super-blocks; the lane owns sub-blocks 2g, 2g+1 of one of them (64 weights,
 // 32 quant bytes) in both rows, against the same 64 activations.
@@ -210,7 +229,9 @@ __device__ __forceinline__ void eat_q4_k(const GemvArgs& a, const Act& sm, uint3
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256 + 64 * g;
-            const int4 u0 = *(const int4*)q8, u1 = *(const int4*)(q8 + 16), u2 = *(const int4*)(q8 + 32), u3 = *(const int4*)(q8 + 48);
+            const int sw = (2 * sbs + (g >> 1)) & 3;   // act_chunk<FK_Q4_K> for chunks 16 sbs + 4 g + j: j ^ sw
+            const int4 u0 = *(const int4*)(q8 + 16 * sw), u1 = *(const int4*)(q8 + 16 * (1 ^ sw)), u2 = *(const int4*)(q8 + 16 * (2 ^ sw)),
+                       u3 = *(const int4*)(q8 + 16 * (3 ^ sw));
             const int ulo[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
             const int uhi[8] = {u2.x, u2.y, u2.z, u2.w, u3.x, u3.y, u3.z, u3.w};
             const float2 d8 = *(const float2*)(sm.d + b * sm.nb32 + sbs * 8 + 2 * g);
@@ -288,7 +309,7 @@ __device__ __forceinline__ void eat(const GemvArgs& a, const Act& sm, uint32_t s
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const int8_t* q8 = sm.q + (size_t)b * sm.cols + sbs * 256;
-            const int4 ua = *(const int4*)(q8 + 16 * g_lo), ub = *(const int4*)(q8 + 16 * g_hi);
+            const int4 ua = *(const int4*)(q8 + 16 * act_chunk<FK_Q6_K>(g_lo)), ub = *(const int4*)(q8 + 16 * act_chunk<FK_Q6_K>(g_hi));
             const float d8lo = sm.d[b * sm.nb32 + sbs * 8 + (g_lo >> 1)], d8hi = sm.d[b * sm.nb32 + sbs * 8 + (g_hi >> 1)];
             const int* b16 = sm.b16 + b * (sm.cols >> 4) + sbs * 16;
             // codes are stored +32: sum((c - 32) * u) = sum(c * u) - 32 * sum(u)
@@ -319,7 +340,8 @@ __device__ __forceinline__ void eat(const GemvArgs& a, const Act& sm, uint32_t s
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const int8_t* q8 = sm.q + (size_t)b * sm.cols + ks * 32;
-            const int4 ua = *(const int4*)q8, ub = *(const int4*)(q8 + 16);
+            const int sw = 16 * ((ks >> 2) & 1);   // act_chunk<FK_MXFP4> for chunks 2 ks, 2 ks + 1
+            const int4 ua = *(const int4*)(q8 + sw), ub = *(const int4*)(q8 + (16 ^ sw));
             const int is = dp4a4(va, ua) + dp4a4(vb, ub);
             acc[b] += dw * sm.d[b * sm.nb32 + ks] * i2f(is);
             if (DUMP && b == 0 && live) a.isums[(size_t)row * sm.nb32 + kb] = is;
@@ -346,9 +368,29 @@ __device__ __forceinline__ void chunk_span(const GemvArgs& a, int p, int kc, uin
     *bytes = n;
 }
 
+#ifdef FK_TRACE
+__device__ unsigned long long fk_trace_buf[64][160][12];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TR(slot_, who_) do { if (who_) fk_trace_buf[a.trace_slot & 63][blockIdx.x][slot_] = gtime(); } while (0)
+#define TRMAX(slot_, who_) do { if (who_) atomicMax(&fk_trace_buf[a.trace_slot & 63][blockIdx.x][slot_], gtime()); } while (0)
+extern "C" __attribute__((visibility("default"))) int fk_trace_read(void* host, size_t bytes, int clear) {
+    if (cudaMemcpyFromSymbol(host, fk_trace_buf, bytes) != cudaSuccess) return 1;
+    if (clear) { void* p; cudaGetSymbolAddress(&p, fk_trace_buf); cudaMemset(p, 0, sizeof(fk_trace_buf)); }
+    return 0;
+}
+#else
+#define TR(slot_, who_) do { } while (0)
+#define TRMAX(slot_, who_) do { } while (0)
+#endif
+
 template <int KIND, int NB, bool DUMP>
 __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
+    TR(0, threadIdx.x == 0);
     const int cols = a.cols, rows = a.rows;
     const int nb32 = cols >> 5;
     int8_t* sq = (int8_t*)smem;                       // [NB][cols] int8
@@ -373,6 +415,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
+    TR(8, threadIdx.x == 0);
 
     // consecutive row groups go to consecutive BLOCKS, so a matrix with fewer groups
     // than warps still spreads over every SM
@@ -384,32 +427,58 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     const int njobs = my_pairs * a.nchunks;           // a job = one stage fill = (row pair, K chunk)
     const int ntrips = (cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
 
-    // Fill stage (job % nstages) with job `q`: lane c < ROWS * PLANES copies plane
-    // (c % PLANES) of row (c / PLANES); lane 0 announces the byte total first.
-    auto fill = [&](int q) {
-        const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
-        const int s = q % a.nstages;
-        const uint32_t stage = ring + s * a.stage_bytes, bar = bars + 8 * s;
-        constexpr int P = Geo<KIND>::PLANES;
-        const int r = lane / P, p = lane % P;
-        const int row = pair * RS + r;
+    // Filling a stage: lane c < ROWS * PLANES copies plane (c % PLANES) of row (c / PLANES);
+    // lane 0 announces the byte total first.  Jobs are filled in order, so the stage, the
+    // row group and the K chunk of the next fill are carried along instead of divided out,
+    // and what a lane copies (plane, offsets, sizes) is worked out once.
+    constexpr int P = Geo<KIND>::PLANES;
+    const int f_r = lane / P, f_p = lane % P;
+    const bool f_on = lane < RS * P;
+    const bool f_whole = KIND == FK_Q6_K && f_p == 3;                // the f16 super-scales: the whole row, every chunk
+    const size_t f_poff = f_p == 0 ? a.plane_off[0] : f_p == 1 ? a.plane_off[1] : f_p == 2 ? a.plane_off[2] : a.plane_off[3];
+    const uint32_t f_pstride = (uint32_t)(f_p == 0 ? a.plane_stride[0] : f_p == 1 ? a.plane_stride[1] : f_p == 2 ? a.plane_stride[2] : a.plane_stride[3]);
+    const uint32_t f_chunk = f_whole ? f_pstride : (uint32_t)a.trips_per_chunk * (uint32_t)trip_bytes<KIND>(f_p);
+    const uint32_t f_dst = plane_at<KIND>(a, 0u, f_r, f_p);
+    const uint8_t* f_src = wb + f_poff + (size_t)f_r * f_pstride;
+    int f_stage = 0, f_kc = 0, f_pair = gwarp;
+    auto fill = [&]() {
+        const uint32_t stage = ring + f_stage * a.stage_bytes, bar = bars + 8 * f_stage;
+        const int row = f_pair * RS + f_r;
         uint32_t off = 0, bytes = 0;
-        if (lane < RS * P && row < rows) chunk_span<KIND>(a, p, kc, &off, &bytes);
+        if (f_on && row < rows) {
+            off = f_whole ? 0u : (uint32_t)f_kc * f_chunk;
+            bytes = off + f_chunk > f_pstride ? f_pstride - off : f_chunk;
+        }
         const uint32_t total = __reduce_add_sync(0xffffffffu, bytes);
         if (lane == 0) mbar_expect_tx(bar, total);
         __syncwarp();
-        if (bytes) bulk_g2s(plane_at<KIND>(a, stage, r, p), wb + a.plane_off[p] + (size_t)row * a.plane_stride[p] + off, bytes, bar);
+        if (bytes) bulk_g2s(stage + f_dst, f_src + (size_t)f_pair * RS * f_pstride + off, bytes, bar);
+        if (++f_stage == a.nstages) f_stage = 0;
+        if (++f_kc == a.nchunks) { f_kc = 0; f_pair += twarps; }
     };
 
     // Every stage of the ring is requested before the activations are touched.
     const int pre = njobs < a.nstages ? njobs : a.nstages;
-    for (int q = 0; q < pre; q++) fill(q);
+    for (int q = 0; q < pre; q++) fill();
+    if (a.pf_bytes && warp == 0) {
+        // this block's share of the next kernel's weights, 16 KB per request
+        constexpr unsigned long long PIECE = 16384;
+        const unsigned long long nblk = (unsigned long long)gridDim.x * gridDim.y, me = (unsigned long long)blockIdx.y * gridDim.x + blockIdx.x;
+        const unsigned long long pieces = (a.pf_bytes + PIECE - 1) / PIECE;
+        for (unsigned long long i = me + (unsigned long long)lane * nblk; i < pieces; i += 32ull * nblk) {
+            const unsigned long long off = i * PIECE;
+            const uint32_t n = (uint32_t)(a.pf_bytes - off < PIECE ? a.pf_bytes - off : PIECE) & ~15u;
+            if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.pf_ptr + off), "r"(n) : "memory");
+        }
+    }
+    TR(1, threadIdx.x == 0);
     // Launched with programmatic stream serialization: this grid may start while the
     // previous kernel of the stream is still running.  Weights are constants, so their
     // copies go out at once; x (and y) may belong to that kernel, so wait for it here,
     // and let the next grid start its own weight copies.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    TR(2, threadIdx.x == 0);
 
     // ---- activations -> q8_1 in shared memory.  A thread takes one float4, eight
     // lanes make a run of 32; all of a thread's loads go out before any is used,
@@ -446,7 +515,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                 const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
                 v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (idx < items) {
-                    const int b = idx / c4, k4 = idx - b * c4;
+                    const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
                     if (b < a.batch) {
                         v[u] = __ldg((const float4*)(x + (size_t)b * a.x_ld) + k4);
                         if (a.norm_w) {
@@ -475,9 +544,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
             }
 #pragma unroll
             for (int u = 0; u < QU; u++) {
+                if (base + u * GEMV_THREADS + warp * 32 >= items) continue;   // nothing for this warp here (the same for all its lanes)
                 const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
                 const bool ok = idx < items;
-                const int b = ok ? idx / c4 : 0, k4 = ok ? idx - b * c4 : 0;
+                const int b = !ok || NB == 1 ? 0 : idx / c4, k4 = ok ? idx - b * c4 : 0;
                 const int kb = k4 >> 3, quad = k4 & 7;
                 // the rule of fk_q8_1_lane over the eight lanes of the run (max and integer sums are order-free)
                 unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
@@ -485,6 +555,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                 mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
                 mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
                 const float amax = __uint_as_float(mb);
+                TR(9, threadIdx.x == 0 && u == 0 && base == 0);
                 const float d = amax / 127.0f;
                 int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
                 if (amax != 0.0f) {
@@ -498,17 +569,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                 s16 += __shfl_xor_sync(0xffffffffu, s16, 2);           // sum of this lane's half run (16 values)
                 const int qsum = s16 + __shfl_xor_sync(0xffffffffu, s16, 4);
                 if (ok) {
-                    int8_t* dst = sq + (size_t)b * cols + kb * 32;
+                    int8_t* rowq = sq + (size_t)b * cols;
                     if (KIND == FK_MXFP4) {
                         // each run is kept as (elem j, elem j+16) pairs: the order the nibble decode produces bytes in
                         const int e = 4 * quad;
-                        dst[(((e + 0) & 15) << 1) | ((e + 0) >> 4)] = (int8_t)q0;
-                        dst[(((e + 1) & 15) << 1) | ((e + 1) >> 4)] = (int8_t)q1;
-                        dst[(((e + 2) & 15) << 1) | ((e + 2) >> 4)] = (int8_t)q2;
-                        dst[(((e + 3) & 15) << 1) | ((e + 3) >> 4)] = (int8_t)q3;
+                        const int qv[4] = {q0, q1, q2, q3};
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const int pos = (((e + i) & 15) << 1) | ((e + i) >> 4);
+                            rowq[16 * act_chunk<KIND>(2 * kb + (pos >> 4)) + (pos & 15)] = (int8_t)qv[i];
+                        }
                     } else {
-                        *(uint32_t*)(dst + 4 * quad) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
-                                                       ((uint32_t)(q3 & 0xFF) << 24);
+                        *(uint32_t*)(rowq + 16 * act_chunk<KIND>(k4 >> 2) + 4 * (k4 & 3)) =
+                            (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
                     }
                     if (KIND == FK_Q6_K && (quad & 3) == 0) sb16[b * (cols >> 4) + 2 * kb + (quad >> 2)] = s16;
                     if (quad == 0) {
@@ -520,13 +593,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
             }
         }
     }
+    TR(10, threadIdx.x == 0);
+    TR(11, threadIdx.x == GEMV_THREADS - 1);
     __syncthreads();
+    TR(3, threadIdx.x == 0);
     const Act sm{sq, sd, ss, sb16, cols, nb32};
 
     float acc[LR][NB];
+    int pair = gwarp, kc = 0, s = 0;
+    uint32_t phase = 0;
     for (int q = 0; q < njobs; q++) {
-        const int pair = gwarp + (q / a.nchunks) * twarps, kc = q % a.nchunks;
-        const int s = q % a.nstages;
         const uint32_t stage = ring + s * a.stage_bytes;
         const int row0 = pair * RS;
         if (kc == 0) {
@@ -535,7 +611,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 #pragma unroll
                 for (int b = 0; b < NB; b++) acc[r][b] = 0.0f;
         }
-        mbar_wait(bars + 8 * s, (q / a.nstages) & 1, a.err);
+        mbar_wait(bars + 8 * s, phase, a.err);
+        TR(4, threadIdx.x == 0 && q == 0);
         const int t0 = kc * a.trips_per_chunk;
         const int t1 = t0 + a.trips_per_chunk < ntrips ? t0 + a.trips_per_chunk : ntrips;
         for (int t = t0; t < t1; t++) {
@@ -548,8 +625,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         }
         // every lane has consumed the stage: refill it with the job one ring ahead
         __syncwarp();
-        if (q + a.nstages < njobs) fill(q + a.nstages);
-        if (kc == a.nchunks - 1) {
+        TR(5, threadIdx.x == 0 && q == 0);
+        if (q + a.nstages < njobs) fill();
+        const bool row_done = kc == a.nchunks - 1;
+        if (row_done) {
             // Q4_K: a half warp per row pair; the others: the whole warp on one pair
             const int hw = KIND == FK_Q4_K ? lane >> 4 : 0;
 #pragma unroll
@@ -569,7 +648,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                     }
                 }
         }
+        if (++s == a.nstages) { s = 0; phase ^= 1u; }
+        if (++kc == a.nchunks) { kc = 0; pair += twarps; }
     }
+    TR(6, threadIdx.x == 0);
+    TRMAX(7, lane == 0);
 }
 
 size_t act_smem_bytes(int kind, int nb, int cols) {
@@ -665,6 +748,10 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
                    const FkGemvFused* fused) {
     GemvArgs a{};
+#ifdef FK_TRACE
+    static int trace_seq = 0;
+    a.trace_slot = trace_seq++;
+#endif
     a.n_active = n_active_dev;
     a.x_ld = w->cols;
     if (fused) {
@@ -673,6 +760,8 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.glu_up = fused->glu_up;
         a.glu_act = fused->glu_act;
         a.accumulate = fused->accumulate;
+        a.pf_ptr = fused->pf_ptr;
+        a.pf_bytes = fused->pf_bytes;
         if (fused->x_ld) a.x_ld = fused->x_ld;
     }
     a.w = w->dev;
@@ -722,7 +811,7 @@ FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
 }
 
 FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
-                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate) {
+                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next) {
     if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_fused: null argument");
     if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv_fused: batch %d outside 1..8", batch);
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_fused: matrix %d of %d", mat, w->n_mats);
@@ -732,7 +821,13 @@ FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
         return fk_fail(FK_INVALID, "gemv_fused: inputs must be 16-byte aligned");
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused: activation %d", glu_act);
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld};
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, nullptr, 0};
+    if (next) {
+        // at most 48 MB: what stays resident in L2 beside this kernel's own stream
+        const size_t total = (size_t)next->n_mats * next->mat_stride, cap = (size_t)48 << 20;
+        f.pf_ptr = next->dev;
+        f.pf_bytes = total < cap ? total : cap;
+    }
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
 }
 

@@ -67,14 +67,27 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     const int r = blockIdx.x;
     float* xr = x + (size_t)r * cols;
     const float* rr = res ? res + (size_t)r * cols : nullptr;
+    const bool vec = (cols & 3) == 0;       // rows then start on 16-byte boundaries (bases come from 256-byte aligned allocations)
     double s = 0.0;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        float v = xr[i];
-        if (rr) {
-            v += rr[i];
-            xr[i] = v;
+    if (vec) {
+        for (int i = threadIdx.x; i < (cols >> 2); i += blockDim.x) {
+            float4 v = ((const float4*)xr)[i];
+            if (rr) {
+                const float4 q = ((const float4*)rr)[i];
+                v.x += q.x; v.y += q.y; v.z += q.z; v.w += q.w;
+                ((float4*)xr)[i] = v;
+            }
+            s += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
         }
-        s += (double)(v * v);
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            float v = xr[i];
+            if (rr) {
+                v += rr[i];
+                xr[i] = v;
+            }
+            s += (double)(v * v);
+        }
     }
     __shared__ double part[32];
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
@@ -89,7 +102,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     const float mean = (float)(part[0] / (double)cols);
     const float scale = 1.0f / sqrtf(mean + eps);
     float* orow = out + (size_t)r * cols;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) orow[i] = xr[i] * scale * w[i];
+    if (vec) {
+        for (int i = threadIdx.x; i < (cols >> 2); i += blockDim.x) {
+            const float4 v = ((const float4*)xr)[i], g = ((const float4*)w)[i];
+            ((float4*)orow)[i] = make_float4(v.x * scale * g.x, v.y * scale * g.y, v.z * scale * g.z, v.w * scale * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) orow[i] = xr[i] * scale * w[i];
+    }
 }
 
 // ---- RoPE in place over [n_rows][n_heads][head_dim]; row r sits at *pos + r.
@@ -159,78 +179,125 @@ __global__ void kv_append_kernel(float* __restrict__ cache, const float* __restr
     if (i < row_elems * n_rows) cache[(size_t)(*pos) * row_elems + i] = src[i];
 }
 
-// ---- causal grouped-query attention.  One block per (query row, head), 4 warps;
-// warp w takes key tiles w, w + 4, ...; inside a tile lane j scores key j against
-// the query (held in shared memory), the tile's probabilities stay in the lanes
-// and reach the V accumulation by shuffle (lane l owns channels 4l..4l+3).
-// Query row r sits at *pos + r and sees keys 0 ..= *pos + r of the K/V buffers
-// [T][n_kv][head_dim].  head_dim <= 128, a multiple of 4.
-constexpr int ATT_WARPS = 4;
-__global__ void __launch_bounds__(ATT_WARPS * 32)
-attn_kernel(const float* __restrict__ q, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
-            const int* __restrict__ pos, float scale, float* __restrict__ out) {
+// ---- causal grouped-query attention for a few query rows (decode).  Query row r sits at
+// *pos + r and sees keys 0 ..= *pos + r of the K/V buffers [T][n_kv][head_dim];
+// head_dim <= 128, a multiple of 4.  The keys of one (row, head) are cut over
+// gridDim.x blocks (the grid is fixed so that a captured launch stays valid while
+// *pos grows; the cut is made on the device).  A block walks its keys in tiles of 64:
+// eight lanes share one key's dot product (coalesced 128-byte pieces of the K row),
+// the tile's probabilities sit in two registers per lane, and warp w folds V rows
+// w, w + 4, ... with lane l owning channels 4l..4l+3.  Each block parks (max, sum,
+// unnormalised output) in the workspace; the block that arrives last for the
+// (row, head) merges them and rewinds the arrival counter.
+constexpr int AD_WARPS = 4, AD_TK = 64, AD_REC = 132, AD_MAX_SPLITS = 64, AD_MAX_CNT = 4096;
+__global__ void __launch_bounds__(AD_WARPS * 32)
+attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
+            const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt) {
     __shared__ __align__(16) float sq[128];
-    __shared__ float sm_m[ATT_WARPS], sm_s[ATT_WARPS];
-    __shared__ __align__(16) float sm_acc[ATT_WARPS][128];
-    const int r = blockIdx.x, h = blockIdx.y, kvh = h / (n_heads / n_kv);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __shared__ float s_p[AD_TK];
+    __shared__ __align__(16) float s_acc[AD_WARPS][128];
+    __shared__ bool last;
+    const int split = blockIdx.x, S = gridDim.x, h = blockIdx.y, r = blockIdx.z, kvh = h / (n_heads / n_kv);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
     const int n_keys = *pos + r + 1;
-    const float* qr = q + ((size_t)r * n_heads + h) * head_dim;
+    const int chunk = ((n_keys + S - 1) / S + 15) & ~15;
+    const int c0 = split * chunk, c1 = min(n_keys, c0 + chunk);
+    const float* qr = q + (size_t)r * q_ld + (size_t)h * head_dim;
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) sq[i] = qr[i];
     __syncthreads();
     const size_t kv_stride = (size_t)n_kv * head_dim;
+    const int hd4 = head_dim >> 2;
     float m = -INFINITY, s = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    const bool owns = 4 * lane < head_dim;
-    for (int t0 = warp * 32; t0 < n_keys; t0 += ATT_WARPS * 32) {
-        const int key = t0 + lane;
-        float sc = -INFINITY;
-        if (key < n_keys) {
-            const float4* kr = (const float4*)(kbuf + (size_t)key * kv_stride + (size_t)kvh * head_dim);
-            float d = 0.0f;
-            for (int i = 0; i < head_dim / 4; i++) {
-                const float4 kv = kr[i], qv = *(const float4*)(sq + 4 * i);
-                d += kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
-            }
-            sc = d * scale;
+    const bool owns = lane < hd4;
+    for (int t0 = c0; t0 < c1; t0 += AD_TK) {
+        const int nk = min(AD_TK, c1 - t0);
+        // this warp's V rows are requested now, beside the K rows, and used after the softmax
+        float4 vv[AD_TK / AD_WARPS];
+#pragma unroll
+        for (int jj = 0; jj < AD_TK / AD_WARPS; jj++) {
+            const int j = warp + AD_WARPS * jj;
+            vv[jj] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (j < nk && owns) vv[jj] = *(const float4*)(vbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim + 4 * lane);
         }
-        float tm = sc;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int j = warp * 16 + i * 4 + (lane >> 3);
+            float d = 0.0f;
+            if (j < nk) {
+                const float4* kr = (const float4*)(kbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim);
+#pragma unroll 4
+                for (int f = sub; f < hd4; f += 8) {
+                    const float4 kv = kr[f], qv = *(const float4*)(sq + 4 * f);
+                    d += kv.x * qv.x + kv.y * qv.y + kv.z * qv.z + kv.w * qv.w;
+                }
+            }
+            d += __shfl_xor_sync(0xffffffffu, d, 4);
+            d += __shfl_xor_sync(0xffffffffu, d, 2);
+            d += __shfl_xor_sync(0xffffffffu, d, 1);
+            if (sub == 0 && j < nk) s_p[j] = d * scale;
+        }
+        __syncthreads();
+        // every warp works out the tile's max and sum for itself (same values in all four)
+        const float sc0 = lane < nk ? s_p[lane] : -INFINITY, sc1 = lane + 32 < nk ? s_p[lane + 32] : -INFINITY;
+        float tm = fmaxf(sc0, sc1);
         for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
         const float m_new = fmaxf(m, tm);
-        const float p = key < n_keys ? expf(sc - m_new) : 0.0f;
-        float ts = p;
+        const float p0 = lane < nk ? expf(sc0 - m_new) : 0.0f, p1 = lane + 32 < nk ? expf(sc1 - m_new) : 0.0f;
+        float ts = p0 + p1;
         for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
         const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first tile
         s = s * corr + ts;
         acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
-        const int cnt = min(32, n_keys - t0);
-        for (int j = 0; j < cnt; j++) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            if (owns) {
-                const float4 vv = *(const float4*)(vbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim + 4 * lane);
-                acc.x += pj * vv.x; acc.y += pj * vv.y; acc.z += pj * vv.z; acc.w += pj * vv.w;
-            }
+#pragma unroll
+        for (int jj = 0; jj < AD_TK / AD_WARPS; jj++) {
+            const int j = warp + AD_WARPS * jj;
+            const float pj = __shfl_sync(0xffffffffu, jj < 8 ? p0 : p1, j & 31);
+            acc.x += pj * vv[jj].x; acc.y += pj * vv[jj].y; acc.z += pj * vv[jj].z; acc.w += pj * vv[jj].w;
         }
         m = m_new;
+        __syncthreads();
     }
-    if (lane == 0) { sm_m[warp] = m; sm_s[warp] = s; }
-    if (owns) *(float4*)(&sm_acc[warp][4 * lane]) = acc;
+    *(float4*)(&s_acc[warp][4 * lane]) = acc;
     __syncthreads();
-    if (warp == 0 && owns) {
-        float gm = -INFINITY;
-        for (int w = 0; w < ATT_WARPS; w++) gm = fmaxf(gm, sm_m[w]);
-        float gs = 0.0f;
-        float4 o = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int w = 0; w < ATT_WARPS; w++) {
-            const float c = sm_m[w] == -INFINITY ? 0.0f : expf(sm_m[w] - gm);
-            gs += sm_s[w] * c;
-            const float4 a = *(const float4*)(&sm_acc[w][4 * lane]);
-            o.x += a.x * c; o.y += a.y * c; o.z += a.z * c; o.w += a.w * c;
-        }
-        const float inv = 1.0f / gs;
-        float* orow = out + ((size_t)r * n_heads + h) * head_dim + 4 * lane;
-        orow[0] = o.x * inv; orow[1] = o.y * inv; orow[2] = o.z * inv; orow[3] = o.w * inv;
+    float* rec = ws + ((size_t)(r * n_heads + h) * S + split) * AD_REC;
+    if (threadIdx.x < head_dim) {
+        const int t = threadIdx.x;
+        rec[t] = s_acc[0][t] + s_acc[1][t] + s_acc[2][t] + s_acc[3][t];
     }
+    if (threadIdx.x == 0) { rec[128] = m; rec[129] = s; }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(&cnt[r * n_heads + h], 1u) == (unsigned)(S - 1);
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    // merge: warp 0 turns the parked maxima into one weight per block, then each thread
+    // folds its channel over the blocks (loads that do not wait on one another)
+    __shared__ float s_c[AD_MAX_SPLITS];
+    __shared__ float s_gs;
+    const float* all = ws + (size_t)(r * n_heads + h) * S * AD_REC;
+    if (warp == 0) {
+        const bool h0 = lane < S, h1 = lane + 32 < S;
+        const float m0 = h0 ? __ldcg(all + lane * AD_REC + 128) : -INFINITY, m1 = h1 ? __ldcg(all + (lane + 32) * AD_REC + 128) : -INFINITY;
+        const float s0 = h0 ? __ldcg(all + lane * AD_REC + 129) : 0.0f, s1 = h1 ? __ldcg(all + (lane + 32) * AD_REC + 129) : 0.0f;
+        float gm = fmaxf(m0, m1);
+        for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+        const float w0 = m0 == -INFINITY ? 0.0f : expf(m0 - gm), w1 = m1 == -INFINITY ? 0.0f : expf(m1 - gm);   // -inf: an empty share
+        float gs = s0 * w0 + s1 * w1;
+        for (int o = 16; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+        if (h0) s_c[lane] = w0;
+        if (h1) s_c[lane + 32] = w1;
+        if (lane == 0) s_gs = gs;
+    }
+    __syncthreads();
+    if (threadIdx.x < head_dim) {
+        float o = 0.0f;
+#pragma unroll 8
+        for (int i = 0; i < S; i++) o += __ldcg(all + i * AD_REC + threadIdx.x) * s_c[i];
+        out[((size_t)r * n_heads + h) * head_dim + threadIdx.x] = o / s_gs;
+    }
+    if (threadIdx.x == 0) cnt[r * n_heads + h] = 0;
 }
 
 // ---- the same attention for a prefill batch: a block takes 32 consecutive query rows
@@ -239,7 +306,7 @@ attn_kernel(const float* __restrict__ q, const float* __restrict__ kbuf, const f
 // banks) and shared by the block's 32 rows.
 constexpr int PF_ROWS = 32, PF_WARPS = 8, PF_RPW = PF_ROWS / PF_WARPS;
 __global__ void __launch_bounds__(PF_WARPS * 32)
-attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_q, int n_heads, int n_kv,
+attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_q, int n_heads, int n_kv,
                     int head_dim, const int* __restrict__ pos, float scale, float* __restrict__ out) {
     extern __shared__ __align__(16) float sm[];
     const int kpad = head_dim + 4;
@@ -254,7 +321,7 @@ attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ kbuf,
     for (int i = threadIdx.x; i < PF_ROWS * hd4; i += blockDim.x) {
         const int rr = i / hd4, c = i % hd4;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (r0 + rr < n_q) v = *(const float4*)(q + ((size_t)(r0 + rr) * n_heads + h) * head_dim + 4 * c);
+        if (r0 + rr < n_q) v = *(const float4*)(q + (size_t)(r0 + rr) * q_ld + (size_t)h * head_dim + 4 * c);
         *(float4*)(sq + rr * head_dim + 4 * c) = v;
     }
     float m[PF_RPW], s[PF_RPW];
@@ -326,33 +393,51 @@ attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ kbuf,
     }
 }
 
-// ---- greedy argmax of each row (ties -> lower index); also advances *pos_inc if given
-__global__ void argmax_kernel(const float* __restrict__ x, int n, int* __restrict__ out) {
-    const float* xr = x + (size_t)blockIdx.x * n;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = xr[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
-    }
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
-    __syncthreads();
-    if (threadIdx.x < 32) {
-        bv = threadIdx.x < (blockDim.x >> 5) ? sv[threadIdx.x] : -INFINITY;
-        bi = threadIdx.x < (blockDim.x >> 5) ? si[threadIdx.x] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+// ---- greedy argmax of each row (ties -> lower index, NaN never wins).  A row is cut
+// over gridDim.x blocks; each folds its slice into one 64-bit key (order-preserving
+// float bits above, ~index below, so an unsigned max picks the largest value and
+// then the lowest index), parks it in the context's workspace, and the block that
+// arrives last for the row reduces the parked keys and rewinds the row's counter.
+constexpr int ARGMAX_MAX_BLOCKS = 64, ARGMAX_MAX_ROWS = 64;
+__device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
+    unsigned u = __float_as_uint(v != v ? -INFINITY : v);
+    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    return ((unsigned long long)u << 32) | (unsigned)(~i);
+}
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float* __restrict__ x, int n, int* __restrict__ out, unsigned long long* __restrict__ ws, unsigned* __restrict__ cnt) {
+    const int row = blockIdx.y;
+    const float* xr = x + (size_t)row * n;
+    unsigned long long best = 0ull;
+    if ((n & 3) == 0 && !((uintptr_t)x & 15)) {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < (n >> 2); i += gridDim.x * blockDim.x) {
+            const float4 v = ((const float4*)xr)[i];
+            best = max(best, max(max(argmax_key(v.x, 4 * i), argmax_key(v.y, 4 * i + 1)), max(argmax_key(v.z, 4 * i + 2), argmax_key(v.w, 4 * i + 3))));
         }
-        if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    } else {
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) best = max(best, argmax_key(xr[i], i));
+    }
+    __shared__ unsigned long long sk[8];
+    __shared__ bool last;
+    for (int o = 16; o > 0; o >>= 1) best = max(best, __shfl_xor_sync(0xffffffffu, best, o));
+    if ((threadIdx.x & 31) == 0) sk[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < 8; i++) best = max(best, sk[i]);
+        ws[row * ARGMAX_MAX_BLOCKS + blockIdx.x] = best;
+        __threadfence();
+        last = atomicAdd(&cnt[row], 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last && threadIdx.x < 32) {
+        __threadfence();
+        unsigned long long b = 0ull;
+        for (int i = threadIdx.x; i < (int)gridDim.x; i += 32) b = max(b, ((volatile unsigned long long*)ws)[row * ARGMAX_MAX_BLOCKS + i]);
+        for (int o = 16; o > 0; o >>= 1) b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+        if (threadIdx.x == 0) {
+            out[row] = (int)(~(unsigned)(b & 0xffffffffull));
+            cnt[row] = 0;
+        }
     }
 }
 
@@ -391,8 +476,12 @@ FK_EXPORT int fk_rmsnorm(fk_ctx* ctx, void* stream, float* x_dev, const float* r
                          float eps, float* out_dev) {
     if (!ctx || !x_dev || !weight_dev || !out_dev || n_rows < 1 || cols < 1) return fk_fail(FK_INVALID, "rmsnorm: bad argument");
     FkDeviceGuard g(ctx->device);
+    const bool aligned = !(((uintptr_t)x_dev | (uintptr_t)residual_dev | (uintptr_t)weight_dev | (uintptr_t)out_dev) & 15);
+    if ((cols & 3) == 0 && !aligned) return fk_fail(FK_INVALID, "rmsnorm: buffers must be 16-byte aligned");
+    int threads = n_rows <= 8 ? ((cols / 4 + 31) / 32) * 32 : 256;
+    threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
     FK_CARVEOUT(rmsnorm_kernel);
-    rmsnorm_kernel<<<n_rows, 256, 0, (cudaStream_t)stream>>>(x_dev, residual_dev, weight_dev, cols, eps, out_dev);
+    rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x_dev, residual_dev, weight_dev, cols, eps, out_dev);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -442,21 +531,29 @@ FK_EXPORT int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const fl
     return FK_OK;
 }
 
-FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_dev, const float* v_dev, int n_q, int n_heads, int n_kv,
-                           int head_dim, const int* pos_dev, float scale, float* out_dev) {
+FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
+                           int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev) {
     if (!ctx || !q_dev || !k_dev || !v_dev || !pos_dev || !out_dev) return fk_fail(FK_INVALID, "attention: null argument");
     if (n_q < 1 || n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > 65535)
         return fk_fail(FK_UNSUPPORTED, "attention: %d queries, %d/%d heads of %d", n_q, n_heads, n_kv, head_dim);
+    if (q_ld == 0) q_ld = n_heads * head_dim;
+    if (q_ld < n_heads * head_dim || (q_ld & 3) || ((uintptr_t)q_dev & 15)) return fk_fail(FK_INVALID, "attention: query row stride %d", q_ld);
     FkDeviceGuard g(ctx->device);
     if (n_q >= 16) {
         const size_t smem = (size_t)(PF_ROWS * head_dim + 32 * (head_dim + 4) + 32 * head_dim) * sizeof(float);
         FK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
         FK_CARVEOUT(attn_prefill_kernel);
         attn_prefill_kernel<<<dim3((n_q + PF_ROWS - 1) / PF_ROWS, n_heads), PF_WARPS * 32, smem, (cudaStream_t)stream>>>(
-            q_dev, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev);
+            q_dev, q_ld, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev);
     } else {
+        if (n_q * n_heads > AD_MAX_CNT) return fk_fail(FK_UNSUPPORTED, "attention: %d rows x %d heads", n_q, n_heads);
+        int splits = 4 * ctx->sm_count / (n_heads * n_q);
+        splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
+        const int rc = fk_ensure_scratch(ctx, (size_t)n_q * n_heads * splits * AD_REC * sizeof(float));
+        if (rc != FK_OK) return rc;
         FK_CARVEOUT(attn_kernel);
-        attn_kernel<<<dim3(n_q, n_heads), ATT_WARPS * 32, 0, (cudaStream_t)stream>>>(q_dev, k_dev, v_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev);
+        attn_kernel<<<dim3(splits, n_heads, n_q), AD_WARPS * 32, 0, (cudaStream_t)stream>>>(q_dev, q_ld, k_dev, v_dev, n_heads, n_kv, head_dim, pos_dev,
+                                                                                           scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt);
     }
     FK_LAUNCH_CHECK();
     return FK_OK;
@@ -464,9 +561,12 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, const 
 
 FK_EXPORT int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev) {
     if (!ctx || !x_dev || !out_dev || n_rows < 1 || n < 1) return fk_fail(FK_INVALID, "argmax: bad argument");
+    if (n_rows > ARGMAX_MAX_ROWS) return fk_fail(FK_UNSUPPORTED, "argmax: %d rows (at most %d per call)", n_rows, ARGMAX_MAX_ROWS);
     FkDeviceGuard g(ctx->device);
+    int blocks = (n + 2047) / 2048;
+    blocks = blocks < 1 ? 1 : blocks > ARGMAX_MAX_BLOCKS ? ARGMAX_MAX_BLOCKS : blocks;
     FK_CARVEOUT(argmax_kernel);
-    argmax_kernel<<<n_rows, 1024, 0, (cudaStream_t)stream>>>(x_dev, n, out_dev);
+    argmax_kernel<<<dim3(blocks, n_rows), 256, 0, (cudaStream_t)stream>>>(x_dev, n, out_dev, ctx->argmax_ws, ctx->argmax_cnt);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }

@@ -160,6 +160,8 @@ class Decoder:
         ops, cfg = self.ops, self.cfg
         hd = cfg.head_dim
         n = ids.numel()
+        if n <= 8 and self.world == 1 and hasattr(ops, "gemv_fused"):
+            return self._forward_fused(ids)
         x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
         pending = None                                      # a block output not yet added to x
         for L in self.layers:
@@ -173,10 +175,13 @@ class Decoder:
             if cfg.qk_norm:
                 q = ops.rmsnorm(q.view(-1, hd), L["q_norm"], cfg.eps).view(n, -1)
                 k = ops.rmsnorm(k.view(-1, hd), L["k_norm"], cfg.eps).view(n, -1)
-            ops.rope(q, self.h_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
-            ops.rope(k, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
-            ops.kv_append(L["k"], k, self.pos)
-            ops.kv_append(L["v"], v, self.pos)
+            if hasattr(ops, "rope_kv"):
+                ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"])
+            else:
+                ops.rope(q, self.h_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
+                ops.rope(k, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
+                ops.kv_append(L["k"], k, self.pos)
+                ops.kv_append(L["v"], v, self.pos)
             a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
             o = L["wo"](a)
             h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps, residual=o)
@@ -190,6 +195,50 @@ class Decoder:
         last = x[n - 1:n].contiguous()
         hn = ops.rmsnorm(last, self.out_norm, cfg.eps, residual=pending[n - 1:n].contiguous())
         logits = ops.gemv(self.head, hn)
+        ops.add_int_(self.pos, n)
+        return logits
+
+    def _forward_fused(self, ids):
+        """The decode form on one GPU (at most 8 rows): each RMSNorm rides in the prologue of
+        the matvec that reads it, SiLU(gate) * up in the prologue of the down projection, and
+        wo / down add straight into the residual stream; q, k, v stay column slices of the
+        merged projection's output.  Six launches per dense layer."""
+        ops, cfg = self.ops, self.cfg
+        hd, n = cfg.head_dim, ids.numel()
+        hq, kvw = self.h_loc * hd, self.kv_loc * hd
+        x = ops.get_rows(self.embd, ids)
+        # each matvec asks for the next one's weights to be warmed into L2 while it streams its own
+        wof = lambda d, name: d[name].w if name in d else None
+        for li, L in enumerate(self.layers):
+            nxt = self.layers[li + 1] if li + 1 < len(self.layers) else None
+            after_ffn = (wof(nxt, "qkv") or wof(nxt, "qk") or wof(nxt, "wq")) if nxt is not None else self.head
+            first_ffn = wof(L, "gate_up") or wof(L, "gate")
+            if "qkv" in L:
+                qkv = ops.gemv_fused(L["qkv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wo"].w)
+                q, k, v = qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]
+            else:
+                h = ops.rmsnorm(x, L["attn_norm"], cfg.eps)
+                if "qk" in L:
+                    (q, k), v = L["qk"](h), L["wv"](h)
+                else:
+                    q, k, v = L["wq"](h), L["wk"](h), L["wv"](h)
+            if cfg.qk_norm:
+                q = ops.rmsnorm(q.contiguous().view(-1, hd), L["q_norm"], cfg.eps).view(n, -1)
+                k = ops.rmsnorm(k.contiguous().view(-1, hd), L["k_norm"], cfg.eps).view(n, -1)
+                v = v.contiguous()
+            ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"])
+            a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
+            ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True, prefetch=first_ffn)
+            if "moe" in L:
+                h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
+                ops.add_(x, run_device_routed(L["moe"], h2, ops))
+            elif "gate_up" in L:
+                gu = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, prefetch=L["down"].w)
+                ops.gemv_fused(L["down"].w, gu[:, :cfg.ffn], glu_up=gu[:, cfg.ffn:], out=x, accumulate=True, prefetch=after_ffn)
+            else:
+                h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
+                ops.gemv_fused(L["down"].w, L["gate"](h2), glu_up=L["up"](h2), out=x, accumulate=True, prefetch=after_ffn)
+        logits = ops.gemv_fused(self.head, x[n - 1:n], norm_weight=self.out_norm, eps=cfg.eps)
         ops.add_int_(self.pos, n)
         return logits
 

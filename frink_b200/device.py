@@ -120,10 +120,11 @@ def gemv(w, x, mat=0, out=None):
     return y if x.dim() > 1 or out is not None else y[0]
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, prefetch=None):
     """gemv with its elementwise neighbours folded in: reads rmsnorm(x) * norm_weight, or
     act(x) * glu_up (x the gate), and/or adds into `out` instead of overwriting it.
-    x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4."""
+    x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4.
+    prefetch: the Weights the next matvec of the stream reads (warmed into L2 meanwhile)."""
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
     batch, ld = x.shape[0], x.stride(0) if x.shape[0] > 1 else max(x.stride(0), w.cols)
     if glu_up is not None:
@@ -131,7 +132,8 @@ def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, gl
     y = out if out is not None else torch.empty((batch, w.rows), dtype=torch.float32, device=x.device)
     check(lib().fk_gemv_fused(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
                               _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
-                              _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate))))
+                              _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate)),
+                              prefetch.handle if prefetch is not None else None))
     return y
 
 
@@ -296,11 +298,14 @@ def kv_append(cache, src, pos):
 
 
 def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
-    q = _f32(q)
+    """q: [n, n_heads * head_dim] with any row stride that is a multiple of 4 floats (a column
+    slice of a merged q/k/v output works), or one row."""
+    assert q.is_cuda and q.dtype == torch.float32 and q.stride(-1) == 1
     q2 = q if q.dim() == 2 else q[None]
-    o = out if out is not None else torch.empty_like(q2)
+    o = out if out is not None else torch.empty((q2.shape[0], n_heads * head_dim), dtype=torch.float32, device=q.device)
     sc = float(scale) if scale is not None else head_dim ** -0.5
-    check(lib().fk_attention(context(q.device), _stream(), _ptr(q2), _ptr(k_cache), _ptr(v_cache), q2.shape[0], n_heads, n_kv, head_dim,
+    ld = q2.stride(0) if q2.shape[0] > 1 else 0
+    check(lib().fk_attention(context(q.device), _stream(), _ptr(q2), ld, _ptr(k_cache), _ptr(v_cache), q2.shape[0], n_heads, n_kv, head_dim,
                              _ptr(_i32(pos)), sc, _ptr(o)))
     return o if q.dim() == 2 else o[0]
 

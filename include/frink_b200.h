@@ -101,9 +101,11 @@ int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev,
  * norm_weight_dev: the matvec reads rmsnorm(x) * norm_weight (squares summed in f64);
  * glu_up_dev: the matvec reads act(x) * glu_up, x being the gate (act 0 SiLU, 1 gpt-oss);
  * accumulate != 0: y += W x (the residual add).  x_ld = floats between batch rows of x
- * and glu_up (0 = cols). */
+ * and glu_up (0 = cols).  next (may be null): the weights the NEXT matvec of the stream
+ * will read; this launch asks for up to 48 MB of them to be brought into L2 while it
+ * runs, which hides the next launch's start-up behind this one's stream. */
 int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
-                  const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate);
+                  const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next);
 
 /* Indexed expert GEMV: the `FX_MULTI` form (kernels.rs:166-179,
  * dp4a_launch.rs:256-314).  Slot j (0 <= j < k) multiplies matrix
@@ -203,10 +205,14 @@ int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n
 /* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */
 int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev);
 /* `causal_gqa_prefill_f32` / `decode_attn_*` (kernels.rs:488, src/decode_attn.rs:125):
- * query row r at position *pos + r attends keys 0..=*pos + r of K/V [T][n_kv][head_dim]. */
-int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_dev, const float* v_dev, int n_q, int n_heads, int n_kv,
-                 int head_dim, const int* pos_dev, float scale, float* out_dev);
-/* Greedy sampling: index of the largest of each row, ties to the lower index. */
+ * query row r at position *pos + r attends keys 0..=*pos + r of K/V [T][n_kv][head_dim].
+ * q_ld = floats between query rows (0 = n_heads * head_dim).  With fewer than 16 query rows
+ * the keys are split over many blocks that meet in a workspace of the context: one such
+ * call in flight per context. */
+int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
+                 int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev);
+/* Greedy sampling: index of the largest of each row, ties to the lower index; at most
+ * 64 rows per call, and one call in flight per context (it uses a workspace of the context). */
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);
 /* *p += v on the device (the position word of a captured decode step). */
 int fk_add_int(fk_ctx* ctx, void* stream, int* p_dev, int v);

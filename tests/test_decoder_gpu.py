@@ -59,14 +59,76 @@ def test_rmsnorm_rope_attention_argmax():
     assert list(device.argmax(torch.from_numpy(lg).cuda()).cpu().numpy()) == [int(np.argmax(lg[0])), 77, int(np.argmax(lg[2]))]
 
 
-def small_llama(seed=1):
+@pytest.mark.parametrize("kind", [fo.Q4_K, fo.Q6_K, fo.Q8_0, fo.MXFP4])
+@pytest.mark.parametrize("batch", [1, 3])
+def test_fused_gemv_equals_the_separate_kernels(kind, batch):
+    """The matvec with RMSNorm / SiLU*up in its prologue and the residual add in its
+    epilogue against the same steps as separate launches (which the other tests tie
+    to the oracle)."""
+    from frink_b200 import device
+    rng = np.random.default_rng(5 + batch)
+    rows, cols = 520, 1024
+    w = device.Weights(fo.encode(kind, synth_weights(rows, cols, 11)), kind, rows, cols)
+    x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float32)).cuda()
+    nw = torch.from_numpy((1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)).cuda()
+    want = device.gemv(w, device.rmsnorm(x.clone(), nw, 1e-5))
+    got = device.gemv_fused(w, x, norm_weight=nw, eps=1e-5)
+    assert torch.allclose(got, want, rtol=1e-5, atol=1e-6)
+    # gate | up as the two halves of one wider buffer, as the merged projection leaves them
+    gu = torch.from_numpy(rng.standard_normal((batch, 2 * cols)).astype(np.float32)).cuda()
+    for act in (0, 1):
+        want = device.gemv(w, device.glu(gu[:, :cols].contiguous(), gu[:, cols:].contiguous(), act))
+        got = device.gemv_fused(w, gu[:, :cols], glu_up=gu[:, cols:], glu_act=act)
+        assert torch.equal(got, want)
+    res = torch.from_numpy(rng.standard_normal((batch, rows)).astype(np.float32)).cuda()
+    out = res.clone()
+    device.gemv_fused(w, x, out=out, accumulate=True)
+    assert torch.equal(out, res + device.gemv(w, x))
+    assert device.device_error() == 0
+
+
+def test_rope_kv_strided_attention_and_wide_argmax():
+    from frink_b200 import device
+    rng = np.random.default_rng(9)
+    nh, nkv, hd, n, p0 = 8, 2, 128, 3, 11
+    hq, kvw = nh * hd, nkv * hd
+    qkv = torch.from_numpy(rng.standard_normal((n, hq + 2 * kvw)).astype(np.float32)).cuda()
+    pos = torch.tensor([p0], dtype=torch.int32).cuda()
+    for neox in (False, True):
+        q0, k0, v0 = (t.contiguous() for t in (qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]))
+        kc0 = torch.from_numpy(rng.standard_normal((32, kvw)).astype(np.float32)).cuda()
+        vc0 = torch.from_numpy(rng.standard_normal((32, kvw)).astype(np.float32)).cuda()
+        kc1, vc1 = kc0.clone(), vc0.clone()
+        device.rope(q0, nh, hd, pos, 1e4, neox)
+        device.rope(k0, nkv, hd, pos, 1e4, neox)
+        device.kv_append(kc0, k0, pos)
+        device.kv_append(vc0, v0, pos)
+        buf = qkv.clone()
+        q1, k1, v1 = buf[:, :hq], buf[:, hq:hq + kvw], buf[:, hq + kvw:]
+        device.rope_kv(q1, k1, v1, nh, nkv, hd, pos, 1e4, neox, kc1, vc1)
+        assert torch.equal(q1, q0) and torch.equal(k1, k0) and torch.equal(kc1, kc0) and torch.equal(vc1, vc0)
+        # a query that is a column slice of a wider buffer
+        a0 = device.attention(q0, kc0, vc0, nh, nkv, hd, pos)
+        a1 = device.attention(q1, kc1, vc1, nh, nkv, hd, pos)
+        assert torch.equal(a0, a1)
+    # argmax over a vocabulary-sized row: many blocks per row, ties inside and across blocks
+    lg = rng.standard_normal((3, 128256)).astype(np.float32)
+    lg[1, 120000] = lg[1, 513] = lg[1, 70001] = 9.5
+    lg[2, 128255] = 11.0
+    lg[0, 5] = np.nan
+    want = [int(np.nanargmax(lg[0])), 513, 128255]
+    for _ in range(2):   # the second call finds the arrival counters rewound
+        assert list(device.argmax(torch.from_numpy(lg).cuda()).cpu().numpy()) == want
+
+
+def small_llama(seed=1, uniform=False):
     from frink_b200.decoder import DecoderConfig, LayerWeights
     cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv=2, head_dim=128, ffn=1024, vocab=2048)
     rng = np.random.default_rng(seed)
     H, hd = cfg.hidden, cfg.head_dim
     layers = []
     for li in range(cfg.n_layers):
-        kd = {"wq": fo.Q4_K, "wk": fo.Q4_K, "wv": fo.Q6_K, "wo": fo.Q4_K, "gate": fo.Q4_K, "up": fo.Q4_K, "down": fo.Q6_K}
+        kd = {"wq": fo.Q4_K, "wk": fo.Q4_K, "wv": fo.Q4_K if uniform else fo.Q6_K, "wo": fo.Q4_K, "gate": fo.Q4_K, "up": fo.Q4_K, "down": fo.Q6_K}
         enc = lambda name, r, c, s: fo.encode(kd[name], (rng.standard_normal((r, c)) * s).astype(np.float32))
         layers.append(LayerWeights(
             attn_norm=1 + 0.1 * rng.standard_normal(H), wq=enc("wq", cfg.n_heads * hd, H, 0.05), wk=enc("wk", cfg.n_kv * hd, H, 0.05),
@@ -78,9 +140,12 @@ def small_llama(seed=1):
     return cfg, layers, tok, (1 + 0.1 * rng.standard_normal(H)).astype(np.float32), head
 
 
-def test_small_llama_greedy_tokens_match_the_oracle():
+@pytest.mark.parametrize("uniform", [False, True])
+def test_small_llama_greedy_tokens_match_the_oracle(uniform):
+    """uniform: q, k and v share a block format and run as one merged, norm-fused matvec;
+    otherwise v is Q6_K (the usual K-quant mix) and the norm stays a kernel of its own."""
     from frink_b200.decoder import Decoder
-    cfg, layers, tok, out_norm, head = small_llama()
+    cfg, layers, tok, out_norm, head = small_llama(uniform=uniform)
     dec = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=128)
     ora = od.OracleDecoder(cfg, layers, tok, fo.Q6_K, out_norm, head, fo.Q6_K)
     prompt = np.random.default_rng(0x70C).integers(0, cfg.vocab, 20).astype(np.int32)
