@@ -189,8 +189,13 @@ def main():
     ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
                     help="whole-model pp512 / tg128 tokens per second (BASELINE configs 3 and 4) instead of the GEMV line")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
+    ap.add_argument("--watchdog", type=int, default=0, help="seconds after which all thread stacks are printed and the process exits")
+    ap.add_argument("--no-tp-graph", action="store_true", help="--model under torchrun: launch the decode step eagerly instead of replaying a CUDA graph with the collectives captured")
     ap.add_argument("--case", default=None, help="kind:rows:cols:batch -- plain launches of one GEMV shape (for ncu captures)")
     args = ap.parse_args()
+    if args.watchdog:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -389,7 +394,12 @@ def synth_model(name, n_layers=0):
         if cfg.n_experts:
             kd = {"wq": Q8, "wk": Q8, "wv": Q8, "wo": Q8, "experts": Q4}
             E = cfg.n_experts
-            ex = lambda tag, r, c: np.tile(enc(tag, Q4, r, c, var), E)   # one expert's bytes per (layer variant), stacked E times
+
+            def ex(tag, r, c):   # one expert's bytes per (layer variant), stacked E times; layers of a variant share the host array
+                key = ("stack", tag, r, c, var)
+                if key not in cache:
+                    cache[key] = np.tile(enc(tag, Q4, r, c, var), E)
+                return cache[key]
             layers.append(LayerWeights(
                 attn_norm=np.ones(H, np.float32), wq=enc("wq", Q8, cfg.n_heads * hd, H, var), wk=enc("wk", Q8, cfg.n_kv * hd, H, var),
                 wv=enc("wv", Q8, cfg.n_kv * hd, H, var), wo=enc("wo", Q8, H, cfg.n_heads * hd, var), ffn_norm=np.ones(H, np.float32),
@@ -451,7 +461,7 @@ def model_bench(args, rank, world, local):
         pp.append(ms)
     pp_ms = float(np.median(pp[1:]))
     cur = first.clone()
-    use_graph = world == 1 or cfg.n_experts == 0 or hasattr(device, "moe_local_slots")
+    use_graph = world == 1 or not args.no_tp_graph
     if use_graph:
         g, out = dec.capture_decode(cur)
         step = lambda: (g.replay(), cur.copy_(out))
@@ -477,6 +487,16 @@ def model_bench(args, rank, world, local):
             "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
             "tokens_head": [int(t.item()) for t in toks[:8]]}))
     if world > 1:
+        # a live CUDA graph that holds captured collectives keeps the communicator busy and
+        # destroy_process_group() then never returns: drop the graph first, and leave
+        # without the teardown if a graph was used
+        sync()
+        if use_graph:
+            del step, g, out
+            dec._graph = dec._gout = None
+            torch.cuda.synchronize()
+            sys.stdout.flush()
+            os._exit(0)
         dist.destroy_process_group()
 
 
@@ -550,7 +570,8 @@ def extras(peak):
     from oracle import frink_oracle as fo
     out = []
     rng = np.random.default_rng(1)
-    cases = [("q4_k", 12, 8192, 3072, 1), ("q4_k", 12, 8192, 3072, 8), ("q6_k", 14, 8192, 3072, 1), ("q8_0", 8, 8192, 3072, 1),
+    cases = [("q4_k", 12, 8192, 3072, 1), ("q4_k", 12, 8192, 3072, 2), ("q4_k", 12, 8192, 3072, 4), ("q4_k", 12, 8192, 3072, 8),
+             ("q6_k", 14, 8192, 3072, 8), ("q8_0", 8, 8192, 3072, 8), ("mxfp4", 39, 8192, 2880, 8), ("q6_k", 14, 8192, 3072, 1), ("q8_0", 8, 8192, 3072, 1),
              ("mxfp4", 39, 8192, 2880, 1), ("q4_k", 12, 3072, 8192, 1), ("q6_k", 14, 128256, 3072, 1), ("q4_k", 12, 65536, 8192, 1)]
     for name, kind, rows, cols, batch in cases:
         small = rows * cols <= 8192 * 8192

@@ -77,3 +77,54 @@ def moe_combine(y, pair_of, w, batch, k, out=None):
     ys, ws = y.numpy(), w.numpy().reshape(batch, k)
     po = pair_of.numpy() if pair_of is not None else np.arange(batch * k)
     return torch.from_numpy(np.stack([fo.combine(ys[po[t * k:(t + 1) * k]], ws[t]) for t in range(batch)]))
+
+
+# ---- the decoder glue, so that `frink_b200.decoder.Decoder` runs on CPU ranks
+def get_rows(w, ids):
+    rb = fo.row_bytes(w.kind, w.cols)
+    return torch.from_numpy(np.stack([fo.dequant(w.kind, w.raw[int(t) * rb:(int(t) + 1) * rb]) for t in ids.tolist()]).astype(np.float32))
+
+
+def rmsnorm(x, w, eps, residual=None, out=None):
+    from tests import oracle_decoder as od
+    if residual is not None:
+        x.add_(residual)          # the device kernel leaves x + residual in x
+    return torch.from_numpy(od.rmsnorm(x.numpy(), w.numpy(), eps))
+
+
+def rope(x, n_heads, head_dim, pos, theta, neox=False):
+    from tests import oracle_decoder as od
+    x.copy_(torch.from_numpy(od.rope(x.numpy().copy(), n_heads, head_dim, int(pos[0]), theta, neox)))
+    return x
+
+
+def kv_append(cache, src, pos):
+    p = int(pos[0])
+    cache[p:p + src.shape[0]] = src
+
+
+def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
+    p0, n, grp = int(pos[0]), q.shape[0], n_heads // n_kv
+    qn, K, V = q.numpy().astype(np.float64), k_cache.numpy().astype(np.float64), v_cache.numpy().astype(np.float64)
+    o = np.zeros((n, n_heads * head_dim), np.float32)
+    for r in range(n):
+        T = p0 + r + 1
+        for h in range(n_heads):
+            kv = h // grp
+            s = K[:T, kv * head_dim:(kv + 1) * head_dim] @ qn[r, h * head_dim:(h + 1) * head_dim] * head_dim ** -0.5
+            p = np.exp(s - s.max())
+            o[r, h * head_dim:(h + 1) * head_dim] = p @ V[:T, kv * head_dim:(kv + 1) * head_dim] / p.sum()
+    return torch.from_numpy(o)
+
+
+def argmax(x, out=None):
+    x2 = x if x.dim() == 2 else x[None]
+    return torch.argmax(x2, dim=1).to(torch.int32)
+
+
+def add_(a, b):
+    a.add_(b)
+
+
+def add_int_(p, v):
+    p.add_(v)

@@ -107,3 +107,65 @@ def test_expert_parallel_matches_single_rank():
     for rank, (dec, pre) in enumerate(res):
         assert rel_l2(dec, want_dec) <= 1e-6                   # partial sums all-reduced: order of two adds
         assert np.array_equal(pre, want[rank * 3:(rank + 1) * 3])   # dispatch/combine keeps the single-rank order: same bits
+
+
+def _tiny_model(moe):
+    from frink_b200.decoder import DecoderConfig, LayerWeights
+    rng = np.random.default_rng(21)
+    if moe:
+        cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=8, n_kv=2, head_dim=64, ffn=256, vocab=512, n_experts=4, top_k=2, route_mode=1,
+                            neox=True, qk_norm=True)
+    else:
+        cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=8, n_kv=2, head_dim=64, ffn=512, vocab=512)
+    H, hd = cfg.hidden, cfg.head_dim
+    enc = lambda kind, r, c: fo.encode(kind, (rng.standard_normal((r, c)) * 0.05).astype(np.float32))
+    layers = []
+    for _ in range(cfg.n_layers):
+        norm = lambda n: (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+        common = dict(attn_norm=norm(H), wq=enc(fo.Q4_K, cfg.n_heads * hd, H), wk=enc(fo.Q4_K, cfg.n_kv * hd, H), wv=enc(fo.Q4_K, cfg.n_kv * hd, H),
+                      wo=enc(fo.Q4_K, H, cfg.n_heads * hd), ffn_norm=norm(H))
+        if moe:
+            st = lambda r, c: np.concatenate([enc(fo.Q4_K, r, c) for _ in range(cfg.n_experts)])
+            layers.append(LayerWeights(**common, gate=st(cfg.ffn, H), up=st(cfg.ffn, H), down=st(H, cfg.ffn),
+                                       router=(rng.standard_normal((cfg.n_experts, H)) * 0.5).astype(np.float32), q_norm=norm(hd), k_norm=norm(hd),
+                                       kinds={"wq": fo.Q4_K, "wk": fo.Q4_K, "wv": fo.Q4_K, "wo": fo.Q4_K, "experts": fo.Q4_K}))
+        else:
+            layers.append(LayerWeights(**common, gate=enc(fo.Q4_K, cfg.ffn, H), up=enc(fo.Q4_K, cfg.ffn, H), down=enc(fo.Q4_K, H, cfg.ffn),
+                                       kinds={k: fo.Q4_K for k in ("wq", "wk", "wv", "wo", "gate", "up", "down")}))
+    tok = fo.encode(fo.Q8_0, rng.standard_normal((cfg.vocab, H)).astype(np.float32))
+    head = fo.encode(fo.Q8_0, (rng.standard_normal((cfg.vocab, H)) * 0.5).astype(np.float32))
+    return cfg, layers, tok, norm(H), head
+
+
+def _decoder_logits(moe, group_world):
+    from frink_b200.decoder import Decoder
+    from tests import cpu_ops
+    cfg, layers, tok, out_norm, head = _tiny_model(moe)
+    dec = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=32, ops=cpu_ops, device="cpu")
+    assert dec.world == group_world
+    prompt = torch.from_numpy(np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32))
+    lg_prefill = dec.forward(prompt).numpy().copy()            # 12 rows: the batched path
+    lg_decode = dec.forward(torch.tensor([7], dtype=torch.int32)).numpy().copy()   # one row at position 12
+    return lg_prefill, lg_decode
+
+
+def _decoder_dense_case(rank, world):
+    return _decoder_logits(False, world)
+
+
+def _decoder_moe_case(rank, world):
+    return _decoder_logits(True, world)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_decoder_sharded_over_two_ranks_matches_one(moe):
+    """The whole decoder under TP (dense) and TP+EP (routed) on two gloo ranks against the
+    same decoder on one rank: same collectives on every rank (no deadlock), same logits up
+    to the f32 summation order of the K-split projections."""
+    want = spawn(_decoder_moe_case if moe else _decoder_dense_case, world=1)[0]
+    got = spawn(_decoder_moe_case if moe else _decoder_dense_case, world=2)
+    for r in range(2):
+        for a, b in zip(got[r], want):
+            assert rel_l2(a, b) <= 1e-4
+    for a, b in zip(got[0], got[1]):
+        assert np.array_equal(a, b)
