@@ -93,7 +93,7 @@ FK_EXPORT int fk_counters(fk_ctx* ctx, uint64_t* h2d, uint64_t* d2h, uint64_t* l
 }
 
 int fk_ensure_scratch(fk_ctx* ctx, size_t bytes) {
-    std::lock_guard<std::mutex> lk(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     if (bytes <= ctx->scratch_cap) return FK_OK;
     size_t cap = bytes + (bytes >> 2) + 4096;
     uint8_t* p = nullptr;
@@ -295,7 +295,7 @@ uint64_t fingerprint(const uint8_t* p, size_t len) {
 int resident(fk_ctx* ctx, int kind, const uint8_t* host, size_t len, int rows, int cols, fk_weight* out) {
     const uint64_t fp = fingerprint(host, len);
     {
-        std::lock_guard<std::mutex> lk(ctx->mu);
+        std::lock_guard<std::recursive_mutex> lk(ctx->mu);
         auto it = ctx->resident.find({host, len});
         if (it != ctx->resident.end()) {
             fk_weight w = it->second.second;
@@ -310,7 +310,7 @@ int resident(fk_ctx* ctx, int kind, const uint8_t* host, size_t len, int rows, i
     fk_weight w = nullptr;
     int rc = fk_register_weights(ctx, host, len, kind, 1, rows, cols, &w);
     if (rc) return rc;
-    std::lock_guard<std::mutex> lk(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     ctx->resident[{host, len}] = {fp, w};
     *out = w;
     return FK_OK;
@@ -329,7 +329,7 @@ int grow(float** p, size_t* cap, size_t floats) {
 
 FK_EXPORT int fk_forget_resident(fk_ctx* ctx) {
     if (!ctx) return fk_fail(FK_INVALID, "forget_resident: null context");
-    std::lock_guard<std::mutex> lk(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     FkDeviceGuard g(ctx->device);
     for (auto& kv : ctx->resident) {
         cudaFree(kv.second.second->dev);
@@ -353,7 +353,7 @@ FK_EXPORT int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_hos
     if (rc) return rc;
     // one stream (the default one) and one pair of staging buffers: calls from
     // several host threads take turns, as the reference's do on its one stream
-    std::lock_guard<std::mutex> lk(ctx->mu);
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     const size_t xn = (size_t)batch * n_cols, yn = (size_t)batch * n_rows;
     if ((rc = grow(&ctx->x_dev, &ctx->x_cap, xn))) return rc;
     if ((rc = grow(&ctx->y_dev, &ctx->y_cap, yn))) return rc;

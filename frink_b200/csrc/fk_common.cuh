@@ -51,7 +51,7 @@ struct fk_ctx {
     int sm_count;
     size_t mem_bytes;
     char name[128];
-    std::mutex mu;
+    std::recursive_mutex mu;   // recursive: the host-buffer surface holds it across launches that may grow the scratch block
     // host-buffer surface: (host ptr, len) -> (fingerprint, weights)
     std::map<std::pair<const void*, size_t>, std::pair<uint64_t, fk_weight>> resident;
     // scratch for the host-buffer surface, grown on demand

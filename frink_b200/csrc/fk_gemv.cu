@@ -30,6 +30,7 @@ constexpr int LR = 2;           // weight rows a lane carries at once
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_BUDGET = 225 * 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
+constexpr int MMA_MIN_BATCH = 3;   // from this batch on the tensor-core form is used
 
 struct GemvArgs {
     const uint8_t* w;
@@ -66,6 +67,13 @@ struct GemvArgs {
     int stage_bytes;       // bytes of one stage (its rows, all planes)
     int row_bytes_stage;   // bytes of one row inside a stage
     int act_bytes;         // activation region at the start of shared memory
+    // plan of the tensor-core form (batches of 3..8)
+    int m_ks;              // warps that share one group of 16 rows, each on its own part of K
+    int m_kpart_units;     // units of K per such part
+    int m_chunk_units;     // units of K a stage covers
+    int m_xs;              // bytes between batch rows of the quantized activations
+    int m_sd_off, m_red_off;
+    int m_srs[4], m_spo[4];   // stage layout: bytes between rows of plane p, offset of plane p
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -82,9 +90,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded in polls AND in time (two seconds): a copy that never lands costs the launch
+// seconds, not minutes, and the host finds word 50 in the context's error flag.
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++)
+    if (mbar_try_wait(bar, parity)) return;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
+        if ((i & 63) == 63 && (*(volatile int*)err != 0 || global_ns() - t0 > 2000000000ull)) break;
+    }
     atomicCAS(err, 0, 50);   // gave up: results are garbage from here, the host reads the word
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -655,6 +674,406 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     TRMAX(7, lane == 0);
 }
 
+
+// ===========================================================================
+// Batches of 3..8: the per-run integer dots on the int8 tensor-core instruction
+// (mma.sync m16n8k32: 16 weight rows x one run of 32 x 8 batch columns), so the
+// weights are unpacked once whatever the batch.  A warp owns a group of 16 rows
+// for a part of K; KS warps of the same block share a group (rows/16 groups alone
+// would leave most warps idle) and their partial sums meet in shared memory in a
+// fixed order.  Each lane ends up with rows g, g+8 x batch columns 2t, 2t+1
+// (g = lane / 4, t = lane % 4), scales them per run in f32 like the dp4a form,
+// and nothing crosses lanes.  The exact int32 dots per run are the same numbers.
+constexpr int MM_ROWS = 16;
+template <int KIND> struct MGeo;
+template <> struct MGeo<FK_Q4_K> { static constexpr int UNIT = 256, PLANES = 1, PB0 = 144, PB1 = 0, PB2 = 0; };
+template <> struct MGeo<FK_Q8_0> { static constexpr int UNIT = 256, PLANES = 2, PB0 = 256, PB1 = 16, PB2 = 0; };
+template <> struct MGeo<FK_Q6_K> { static constexpr int UNIT = 256, PLANES = 4, PB0 = 128, PB1 = 64, PB2 = 16; };
+template <> struct MGeo<FK_MXFP4> { static constexpr int UNIT = 512, PLANES = 2, PB0 = 256, PB1 = 16, PB2 = 0; };
+template <int KIND> __host__ __device__ constexpr int unit_bytes(int p) {
+    return p == 0 ? MGeo<KIND>::PB0 : (p == 1 ? MGeo<KIND>::PB1 : (p == 2 ? MGeo<KIND>::PB2 : 0));
+}
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ float byte_f(uint32_t w, int i) { return (float)((w >> (8 * i)) & 0xFFu); }
+// Q6_K codes (0..63, the value + 32) in the four bytes of v -> signed bytes
+__device__ __forceinline__ uint32_t q6_signed(uint32_t v) {
+    const uint32_t r = v ^ 0x20202020u, neg = r & 0x20202020u;
+    return r | (neg << 1) | (neg << 2);
+}
+
+// One stage (units cu0..cu1 of K) of the warp's 16 rows against the batch.
+template <int KIND>
+__device__ __forceinline__ void mma_eat(const GemvArgs& a, uint32_t stage, int cu0, int cu1, uint32_t xrow, const float* sdT, const float* ssT,
+                                        int nb32, int lane, float (&acc)[4]) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t r0 = stage + a.m_spo[0] + g * a.m_srs[0], r8 = r0 + 8 * a.m_srs[0];
+    if (KIND == FK_Q4_K) {
+        for (int u = cu0; u < cu1; u++) {
+            const uint32_t bg = r0 + (u - cu0) * 144, bh = r8 + (u - cu0) * 144;
+            const uint4 hg = lds16(bg), hh = lds16(bh);
+            // 6-bit scales and mins of the 8 sub-blocks, one per byte: [0..3] and [4..7]
+            const uint32_t scg[2] = {hg.y & 0x3F3F3F3Fu, (hg.w & 0x0F0F0F0Fu) | ((hg.y >> 2) & 0x30303030u)};
+            const uint32_t mng[2] = {hg.z & 0x3F3F3F3Fu, ((hg.w >> 4) & 0x0F0F0F0Fu) | ((hg.z >> 2) & 0x30303030u)};
+            const uint32_t sch[2] = {hh.y & 0x3F3F3F3Fu, (hh.w & 0x0F0F0F0Fu) | ((hh.y >> 2) & 0x30303030u)};
+            const uint32_t mnh[2] = {hh.z & 0x3F3F3F3Fu, ((hh.w >> 4) & 0x0F0F0F0Fu) | ((hh.z >> 2) & 0x30303030u)};
+            const float dg = fk_h2f((uint16_t)(hg.x & 0xFFFF)), ndming = -fk_h2f((uint16_t)(hg.x >> 16));
+            const float dh = fk_h2f((uint16_t)(hh.x & 0xFFFF)), ndminh = -fk_h2f((uint16_t)(hh.x >> 16));
+#pragma unroll
+            for (int j = 0; j < 4; j++) {      // 32 quant bytes: low nibbles = run 2j, high nibbles = run 2j + 1
+                const uint32_t w0 = lds32(bg + 16 + 32 * j + 4 * t), w2 = lds32(bg + 32 + 32 * j + 4 * t);
+                const uint32_t w1 = lds32(bh + 16 + 32 * j + 4 * t), w3 = lds32(bh + 32 + 32 * j + 4 * t);
+                const int run = u * 8 + 2 * j;
+                const uint32_t xl = xrow + run * 32 + 4 * t;
+                int dl[4], dh4[4];
+                mma_s8(dl, w0 & 0x0F0F0F0Fu, w1 & 0x0F0F0F0Fu, w2 & 0x0F0F0F0Fu, w3 & 0x0F0F0F0Fu, lds32(xl), lds32(xl + 16));
+                mma_s8(dh4, (w0 >> 4) & 0x0F0F0F0Fu, (w1 >> 4) & 0x0F0F0F0Fu, (w2 >> 4) & 0x0F0F0F0Fu, (w3 >> 4) & 0x0F0F0F0Fu, lds32(xl + 32),
+                       lds32(xl + 48));
+                const float2 dxl = *(const float2*)(sdT + run * 8 + 2 * t), dxh = *(const float2*)(sdT + run * 8 + 8 + 2 * t);
+                const float2 sxl = *(const float2*)(ssT + run * 8 + 2 * t), sxh = *(const float2*)(ssT + run * 8 + 8 + 2 * t);
+                const int jb = 2 * (j & 1);
+                const float sgl = dg * byte_f(scg[j >> 1], jb), sgh = dg * byte_f(scg[j >> 1], jb + 1);
+                const float shl = dh * byte_f(sch[j >> 1], jb), shh = dh * byte_f(sch[j >> 1], jb + 1);
+                const float mgl = ndming * byte_f(mng[j >> 1], jb), mgh = ndming * byte_f(mng[j >> 1], jb + 1);
+                const float mhl = ndminh * byte_f(mnh[j >> 1], jb), mhh = ndminh * byte_f(mnh[j >> 1], jb + 1);
+                acc[0] += sgl * dxl.x * i2f(dl[0]) + sgh * dxh.x * i2f(dh4[0]) + (mgl * sxl.x + mgh * sxh.x);
+                acc[1] += sgl * dxl.y * i2f(dl[1]) + sgh * dxh.y * i2f(dh4[1]) + (mgl * sxl.y + mgh * sxh.y);
+                acc[2] += shl * dxl.x * i2f(dl[2]) + shh * dxh.x * i2f(dh4[2]) + (mhl * sxl.x + mhh * sxh.x);
+                acc[3] += shl * dxl.y * i2f(dl[3]) + shh * dxh.y * i2f(dh4[3]) + (mhl * sxl.y + mhh * sxh.y);
+            }
+        }
+    } else if (KIND == FK_Q8_0) {
+        const uint32_t s0 = stage + a.m_spo[1] + g * a.m_srs[1], s8 = s0 + 8 * a.m_srs[1];
+        for (int u = cu0; u < cu1; u++) {
+#pragma unroll
+            for (int r = 0; r < 8; r++) {
+                const int run = u * 8 + r;
+                if (run >= nb32) break;
+                const uint32_t o = ((u - cu0) * 8 + r) * 32 + 4 * t;
+                const uint32_t xl = xrow + run * 32 + 4 * t;
+                int d4[4];
+                mma_s8(d4, lds32(r0 + o), lds32(r8 + o), lds32(r0 + o + 16), lds32(r8 + o + 16), lds32(xl), lds32(xl + 16));
+                const float wg = fk_h2f((uint16_t)lds_u16(s0 + ((u - cu0) * 8 + r) * 2)), wh = fk_h2f((uint16_t)lds_u16(s8 + ((u - cu0) * 8 + r) * 2));
+                const float2 dx = *(const float2*)(sdT + run * 8 + 2 * t);
+                acc[0] += wg * dx.x * i2f(d4[0]);
+                acc[1] += wg * dx.y * i2f(d4[1]);
+                acc[2] += wh * dx.x * i2f(d4[2]);
+                acc[3] += wh * dx.y * i2f(d4[3]);
+            }
+        }
+    } else if (KIND == FK_MXFP4) {
+        const uint32_t s0 = stage + a.m_spo[1] + g * a.m_srs[1], s8 = s0 + 8 * a.m_srs[1];
+        for (int u = cu0; u < cu1; u++) {
+#pragma unroll 4
+            for (int r = 0; r < 16; r++) {
+                const int run = u * 16 + r;
+                if (run >= nb32) break;
+                const uint32_t o = ((u - cu0) * 16 + r) * 16 + 4 * t;
+                const uint32_t wg = lds32(r0 + o), wh = lds32(r8 + o);
+                // code byte i holds elements i and i + 16; the activations of a run are stored in that (i, i + 16) order
+                const uint32_t xl = xrow + run * 32 + 8 * t;
+                int d4[4];
+                mma_s8(d4, e2m1x2_4(wg), e2m1x2_4(wh), e2m1x2_4(wg >> 16), e2m1x2_4(wh >> 16), lds32(xl), lds32(xl + 4));
+                const float fg = e8m0_half(lds_u8(s0 + (u - cu0) * 16 + r)), fh = e8m0_half(lds_u8(s8 + (u - cu0) * 16 + r));
+                const float2 dx = *(const float2*)(sdT + run * 8 + 2 * t);
+                acc[0] += fg * dx.x * i2f(d4[0]);
+                acc[1] += fg * dx.y * i2f(d4[1]);
+                acc[2] += fh * dx.x * i2f(d4[2]);
+                acc[3] += fh * dx.y * i2f(d4[3]);
+            }
+        }
+    } else {   // FK_Q6_K
+        const uint32_t h0 = stage + a.m_spo[1] + g * a.m_srs[1], h8 = h0 + 8 * a.m_srs[1];
+        const uint32_t c0 = stage + a.m_spo[2] + g * a.m_srs[2], c8 = c0 + 8 * a.m_srs[2];
+        const uint32_t d0 = stage + a.m_spo[3] + g * a.m_srs[3], d8 = d0 + 8 * a.m_srs[3];
+        for (int u = cu0; u < cu1; u++) {
+            const float dg = fk_h2f((uint16_t)lds_u16(d0 + u * 2)), dh = fk_h2f((uint16_t)lds_u16(d8 + u * 2));   // the whole row's super-scales are staged
+            const uint4 scg = lds16(c0 + (u - cu0) * 16), sch = lds16(c8 + (u - cu0) * 16);
+            const uint32_t sgw[4] = {scg.x, scg.y, scg.z, scg.w}, shw[4] = {sch.x, sch.y, sch.z, sch.w};
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const uint32_t qh_o = (u - cu0) * 64 + 32 * hf + 4 * t;
+                const uint32_t hg0 = lds32(h0 + qh_o), hg1 = lds32(h0 + qh_o + 16), hh0 = lds32(h8 + qh_o), hh1 = lds32(h8 + qh_o + 16);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {      // elements 128 hf + 32 e ..: ql bytes 64 hf + 32 (e & 1) + l, nibble e >> 1, qh bits 2e
+                    const uint32_t ql_o = (u - cu0) * 128 + 64 * hf + 32 * (e & 1) + 4 * t;
+                    const int sh = 4 * (e >> 1);
+                    const uint32_t lg0 = lds32(r0 + ql_o), lg1 = lds32(r0 + ql_o + 16), lh0 = lds32(r8 + ql_o), lh1 = lds32(r8 + ql_o + 16);
+                    const uint32_t ag0 = q6_signed(((lg0 >> sh) & 0x0F0F0F0Fu) | (((hg0 >> (2 * e)) & 0x03030303u) << 4));
+                    const uint32_t ag1 = q6_signed(((lg1 >> sh) & 0x0F0F0F0Fu) | (((hg1 >> (2 * e)) & 0x03030303u) << 4));
+                    const uint32_t ah0 = q6_signed(((lh0 >> sh) & 0x0F0F0F0Fu) | (((hh0 >> (2 * e)) & 0x03030303u) << 4));
+                    const uint32_t ah1 = q6_signed(((lh1 >> sh) & 0x0F0F0F0Fu) | (((hh1 >> (2 * e)) & 0x03030303u) << 4));
+                    const int run = u * 8 + hf * 4 + e;
+                    const uint32_t xl = xrow + run * 32 + 4 * t;
+                    const uint32_t b0 = lds32(xl), b1 = lds32(xl + 16);
+                    int dl[4], dh4[4];
+                    mma_s8(dl, ag0, ah0, 0u, 0u, b0, b1);     // the first 16 of the run: scale 8 hf + 2 e
+                    mma_s8(dh4, 0u, 0u, ag1, ah1, b0, b1);    // the second 16: scale 8 hf + 2 e + 1
+                    const int si = 8 * hf + 2 * e;
+                    const float fgl = dg * (float)(int8_t)(sgw[si >> 2] >> (8 * (si & 3))), fgh = dg * (float)(int8_t)(sgw[si >> 2] >> (8 * (si & 3) + 8));
+                    const float fhl = dh * (float)(int8_t)(shw[si >> 2] >> (8 * (si & 3))), fhh = dh * (float)(int8_t)(shw[si >> 2] >> (8 * (si & 3) + 8));
+                    const float2 dx = *(const float2*)(sdT + run * 8 + 2 * t);
+                    acc[0] += dx.x * (fgl * i2f(dl[0]) + fgh * i2f(dh4[0]));
+                    acc[1] += dx.y * (fgl * i2f(dl[1]) + fgh * i2f(dh4[1]));
+                    acc[2] += dx.x * (fhl * i2f(dl[2]) + fhh * i2f(dh4[2]));
+                    acc[3] += dx.y * (fhl * i2f(dl[3]) + fhh * i2f(dh4[3]));
+                }
+            }
+        }
+    }
+}
+
+// The activations of the tensor-core form are quantized ONCE per launch by this kernel
+// (a block per batch row), not by every block of the matvec: it writes the exact image
+// of the matvec's activation region -- int8 rows `xs` bytes apart (16 more than a row,
+// so the eight batch rows of a B fragment fall on different banks), then the stored
+// scales as [run][8] and, for Q4_K, scale * run sum as [run][8] -- and each matvec
+// block pulls the image in with one bulk copy.  RMSNorm and the gated activation ride
+// here when asked for.
+constexpr int IMG_THREADS = 1024;
+template <int KIND>
+__global__ void __launch_bounds__(IMG_THREADS) act_image_kernel(const GemvArgs a, uint8_t* __restrict__ img) {
+    const int cols = a.cols, nb32 = cols >> 5, c4 = cols >> 2, b = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int8_t* sq = (int8_t*)img;
+    float* sdT = (float*)(img + a.m_sd_off);
+    float* ssT = sdT + nb32 * 8;
+    const float* x = a.x + (size_t)b * a.x_ld;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    __shared__ double s_part[IMG_THREADS / 32];
+    __shared__ float s_scale;
+    if (a.norm_w) {
+        double sqs = 0.0;
+        for (int i = threadIdx.x; i < c4; i += IMG_THREADS) {
+            const float4 v = __ldg((const float4*)x + i);
+            sqs += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
+        }
+        for (int o = 16; o > 0; o >>= 1) sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
+        if (lane == 0) s_part[warp] = sqs;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double tsum = 0.0;
+            for (int i = 0; i < IMG_THREADS / 32; i++) tsum += s_part[i];
+            s_scale = 1.0f / sqrtf((float)(tsum / (double)cols) + a.norm_eps);
+        }
+        __syncthreads();
+    }
+    // c4 is a multiple of 8, so the eight lanes of a run always hold the same run
+    for (int base = 0; base < c4; base += IMG_THREADS) {
+        const int k4 = base + (int)threadIdx.x;
+        const bool ok = k4 < c4;
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (ok) {
+            v = __ldg((const float4*)x + k4);
+            if (a.norm_w) {
+                const float4 nw = __ldg((const float4*)a.norm_w + k4);
+                const float sc = s_scale;
+                v.x = v.x * sc * nw.x; v.y = v.y * sc * nw.y; v.z = v.z * sc * nw.z; v.w = v.w * sc * nw.w;
+            }
+            if (a.glu_up) {
+                const float4 up = __ldg((const float4*)(a.glu_up + (size_t)b * a.x_ld) + k4);
+                float gt[4] = {v.x, v.y, v.z, v.w};
+                const float uu[4] = {up.x, up.y, up.z, up.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    if (a.glu_act == 0) {
+                        gt[e] = (gt[e] / (1.0f + expf(-gt[e]))) * uu[e];
+                    } else {
+                        const float xg = fminf(gt[e], 7.0f), yu = fminf(fmaxf(uu[e], -7.0f), 7.0f);
+                        gt[e] = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                    }
+                }
+                v = make_float4(gt[0], gt[1], gt[2], gt[3]);
+            }
+        }
+        const int kb = k4 >> 3, quad = k4 & 7;
+        unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+        mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+        mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
+        const float amax = __uint_as_float(mb);
+        const float d = amax / 127.0f;
+        int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+        if (amax != 0.0f) {
+            q0 = (int)roundf(v.x / d);
+            q1 = (int)roundf(v.y / d);
+            q2 = (int)roundf(v.z / d);
+            q3 = (int)roundf(v.w / d);
+        }
+        int qsum = q0 + q1 + q2 + q3;
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+        qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
+        if (ok) {
+            int8_t* rowq = sq + (size_t)b * a.m_xs + kb * 32;
+            if (KIND == FK_MXFP4) {
+                // a run is kept as (elem j, elem j + 16) pairs: the order the nibble decode produces bytes in
+                const int e = 4 * quad;
+                const int qv[4] = {q0, q1, q2, q3};
+#pragma unroll
+                for (int i = 0; i < 4; i++) rowq[(((e + i) & 15) << 1) | ((e + i) >> 4)] = (int8_t)qv[i];
+            } else {
+                *(uint32_t*)(rowq + 4 * quad) = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+            }
+            if (quad == 0) {
+                const float dq = fk_h2f(fk_f2h(d));
+                sdT[kb * 8 + b] = dq;
+                if (KIND == FK_Q4_K) ssT[kb * 8 + b] = dq * (float)qsum;
+            }
+        }
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArgs a, const uint8_t* __restrict__ img) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    TR(0, threadIdx.x == 0);
+    const int cols = a.cols, rows = a.rows, nb32 = cols >> 5, batch = a.batch;
+    const int xs = a.m_xs;
+    int8_t* sq = (int8_t*)smem;                        // [batch][xs] int8
+    float* sdT = (float*)(smem + a.m_sd_off);           // [nb32][8] stored scale, widened
+    float* ssT = sdT + nb32 * 8;                        // Q4_K: [nb32][8] scale * run sum
+    float4* red = (float4*)(smem + a.m_red_off);        // [2][warps][32] partial sums of the K parts
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint8_t* wb = a.w + (size_t)a.mat * a.mat_stride;
+    float* y = a.y;
+
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t ring = sbase + a.act_bytes + warp * (a.nstages * a.stage_bytes);
+    const uint32_t bars = sbase + a.act_bytes + GEMV_WARPS * (a.nstages * a.stage_bytes) + warp * (MAX_STAGES * 8);
+    const uint32_t xbar = sbase + a.act_bytes + GEMV_WARPS * (a.nstages * a.stage_bytes) + GEMV_WARPS * (MAX_STAGES * 8);
+    if (lane == 0) {
+        for (int s = 0; s < a.nstages; s++) mbar_init(bars + 8 * s, 1);
+        if (warp == 0) mbar_init(xbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    constexpr int UNIT = MGeo<KIND>::UNIT, P = MGeo<KIND>::PLANES;
+    const int KS = a.m_ks, gi = warp / KS, kp = warp % KS, GPR = GEMV_WARPS / KS;
+    const int ngroups = (rows + MM_ROWS - 1) / MM_ROWS;
+    const int units = (cols + UNIT - 1) / UNIT;
+    const int u0 = min(units, kp * a.m_kpart_units), u1 = min(units, u0 + a.m_kpart_units);
+    const int nch = (u1 - u0 + a.m_chunk_units - 1) / a.m_chunk_units;       // 0 for a part past the end of K
+    const int first = gi * gridDim.x + blockIdx.x, gstride = GPR * gridDim.x;
+    const int nrounds = first < ngroups ? (ngroups - first + gstride - 1) / gstride : 0;
+    const int njobs = nrounds * nch;
+
+    // ---- filling a stage: up to two (row, plane) pieces per lane
+    constexpr int NPIECE = (MM_ROWS * P + 31) / 32;
+    uint32_t f_dst[NPIECE], f_ub[NPIECE], f_pstride[NPIECE];
+    const uint8_t* f_src[NPIECE];
+    int f_r[NPIECE];
+    bool f_whole[NPIECE];
+#pragma unroll
+    for (int i = 0; i < NPIECE; i++) {
+        const int c = lane + 32 * i, r = c / P, p = c % P;
+        f_r[i] = c < MM_ROWS * P ? r : -1;
+        f_whole[i] = KIND == FK_Q6_K && p == 3;
+        const size_t poff = p == 0 ? a.plane_off[0] : p == 1 ? a.plane_off[1] : p == 2 ? a.plane_off[2] : a.plane_off[3];
+        f_pstride[i] = (uint32_t)(p == 0 ? a.plane_stride[0] : p == 1 ? a.plane_stride[1] : p == 2 ? a.plane_stride[2] : a.plane_stride[3]);
+        f_ub[i] = (uint32_t)unit_bytes<KIND>(p);
+        const int srs = p == 0 ? a.m_srs[0] : p == 1 ? a.m_srs[1] : p == 2 ? a.m_srs[2] : a.m_srs[3];
+        const int spo = p == 0 ? a.m_spo[0] : p == 1 ? a.m_spo[1] : p == 2 ? a.m_spo[2] : a.m_spo[3];
+        f_dst[i] = (uint32_t)(spo + r * srs);
+        f_src[i] = wb + poff + (size_t)r * f_pstride[i];
+    }
+    int f_stage = 0, f_ch = 0, f_group = first;
+    auto fill = [&]() {
+        const uint32_t stage = ring + f_stage * a.stage_bytes, bar = bars + 8 * f_stage;
+        const int cu0 = u0 + f_ch * a.m_chunk_units, cu1 = min(u1, cu0 + a.m_chunk_units);
+        uint32_t off[NPIECE], bytes[NPIECE], mine = 0;
+#pragma unroll
+        for (int i = 0; i < NPIECE; i++) {
+            off[i] = 0;
+            bytes[i] = 0;
+            if (f_r[i] >= 0 && f_group * MM_ROWS + f_r[i] < rows) {
+                if (f_whole[i]) {
+                    bytes[i] = f_pstride[i];
+                } else {
+                    off[i] = (uint32_t)cu0 * f_ub[i];
+                    bytes[i] = (uint32_t)(cu1 - cu0) * f_ub[i];
+                    if (off[i] + bytes[i] > f_pstride[i]) bytes[i] = f_pstride[i] - off[i];   // the ragged end of a row (strides are padded to 16)
+                }
+                mine += bytes[i];
+            }
+        }
+        const uint32_t total = __reduce_add_sync(0xffffffffu, mine);
+        if (lane == 0) mbar_expect_tx(bar, total);
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < NPIECE; i++)
+            if (bytes[i]) bulk_g2s(stage + f_dst[i], f_src[i] + (size_t)f_group * MM_ROWS * f_pstride[i] + off[i], bytes[i], bar);
+        if (++f_stage == a.nstages) f_stage = 0;
+        if (++f_ch == nch) { f_ch = 0; f_group += gstride; }
+    };
+    const int pre = njobs < a.nstages ? njobs : a.nstages;
+    for (int q = 0; q < pre; q++) fill();
+    TR(1, threadIdx.x == 0);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // ---- the activation image: one bulk copy, every thread waits for it
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(xbar, (uint32_t)a.m_red_off);
+        bulk_g2s(sbase, img, (uint32_t)a.m_red_off, xbar);
+    }
+    mbar_wait(xbar, 0, a.err);
+    TR(3, threadIdx.x == 0);
+
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t xrow = smem_u32(sq) + (uint32_t)min(g, batch - 1) * xs;   // columns past the batch re-read its last row; their sums are dropped
+    int s = 0, group = first;
+    uint32_t phase = 0;
+    for (int round = 0; round < nrounds; round++) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int ch = 0; ch < nch; ch++) {
+            mbar_wait(bars + 8 * s, phase, a.err);
+            TR(4, threadIdx.x == 0 && round == 0 && ch == 0);
+            const int cu0 = u0 + ch * a.m_chunk_units, cu1 = min(u1, cu0 + a.m_chunk_units);
+            mma_eat<KIND>(a, ring + s * a.stage_bytes, cu0, cu1, xrow, sdT, ssT, nb32, lane, acc);
+            __syncwarp();
+            TR(5, threadIdx.x == 0 && round == 0 && ch == 0);
+            if ((round * nch + ch) + a.nstages < njobs) fill();
+            if (++s == a.nstages) { s = 0; phase ^= 1u; }
+        }
+        if (KS > 1) {
+            float4* rb = red + (round & 1) * (GEMV_WARPS * 32);
+            rb[warp * 32 + lane] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            asm volatile("bar.sync %0, %1;" ::"r"(1 + gi), "r"(KS * 32) : "memory");
+            if (kp == 0) {
+                for (int j = 1; j < KS; j++) {
+                    const float4 o = rb[(warp + j) * 32 + lane];
+                    acc[0] += o.x; acc[1] += o.y; acc[2] += o.z; acc[3] += o.w;
+                }
+            }
+        }
+        if (kp == 0) {
+            const int rg = group * MM_ROWS + g;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
+                if (row < rows && b < batch) {
+                    float* dst = y + (size_t)b * rows + row;
+                    *dst = a.accumulate ? *dst + acc[i] : acc[i];
+                }
+            }
+        }
+        group += gstride;
+    }
+    TR(6, threadIdx.x == 0);
+    TRMAX(7, lane == 0);
+}
+
 size_t act_smem_bytes(int kind, int nb, int cols) {
     size_t s = (size_t)nb * cols + (size_t)nb * (cols / 32) * 4;
     if (kind == FK_Q4_K) s += (size_t)nb * (cols / 32) * 4;
@@ -716,8 +1135,90 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     return FK_OK;
 }
 
+// Plan and launch of the tensor-core form; returns FK_UNSUPPORTED (quietly) when a
+// stage of one unit does not fit, and the caller falls back to the dp4a form.
+template <int KIND>
+int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, bool* fits) {
+    constexpr int UNIT = MGeo<KIND>::UNIT, P = MGeo<KIND>::PLANES;
+    *fits = false;
+    const int units = (a.cols + UNIT - 1) / UNIT, nb32 = a.cols / 32;
+    const int ngroups = (a.rows + MM_ROWS - 1) / MM_ROWS;
+    int ks = 1;
+    while (ks < GEMV_WARPS && ngroups * ks * 2 <= ctx->sm_count * GEMV_WARPS && ks * 2 <= units) ks *= 2;
+    a.m_ks = ks;
+    a.m_kpart_units = (units + ks - 1) / ks;
+    a.m_xs = a.cols + 16;
+    size_t act = (size_t)a.batch * a.m_xs;
+    act = (act + 15) & ~(size_t)15;
+    a.m_sd_off = (int)act;
+    act += (size_t)nb32 * 32 * (KIND == FK_Q4_K ? 2 : 1);
+    act = (act + 15) & ~(size_t)15;
+    a.m_red_off = (int)act;
+    act += 2 * GEMV_WARPS * 32 * 16;
+    act = (act + 127) & ~(size_t)127;
+    const int bars = GEMV_WARPS * MAX_STAGES * 8 + 16;   // + the barrier of the activation image
+    const int ring_budget = ((int)SMEM_BUDGET - (int)act - bars) / GEMV_WARPS;
+    auto layout = [&](int cu, int* srs, int* spo) {
+        int off = 0;
+        for (int p = 0; p < P; p++) {
+            int b = (KIND == FK_Q6_K && p == 3) ? (int)w->plane_stride[3] : cu * unit_bytes<KIND>(p);
+            b = (b + 15) & ~15;
+            if ((b & 31) == 0) b += 16;        // rows 16 mod 32 bytes apart: the eight rows of a fragment load hit different banks
+            srs[p] = b;
+            spo[p] = off;
+            off += MM_ROWS * b;
+        }
+        return off;
+    };
+    int srs[4] = {0, 0, 0, 0}, spo[4] = {0, 0, 0, 0};
+    int cu = a.m_kpart_units;
+    while (cu > 1 && 2 * layout(cu, srs, spo) > ring_budget) cu--;
+    const int stage = layout(cu, srs, spo);
+    if (ring_budget <= 0 || stage > ring_budget) return FK_UNSUPPORTED;
+    *fits = true;
+    a.m_chunk_units = cu;
+    for (int p = 0; p < 4; p++) { a.m_srs[p] = srs[p]; a.m_spo[p] = spo[p]; }
+    a.stage_bytes = stage;
+    a.nstages = ring_budget / stage;
+    if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
+    a.act_bytes = (int)act;
+    const size_t smem = act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
+    auto kern = gemv_mma_kernel<KIND>;
+    FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+    // the activation image lives in the context's scratch block (stream-ordered like its other users)
+    const int rcs = fk_ensure_scratch(ctx, (size_t)a.m_red_off);
+    if (rcs != FK_OK) return rcs;
+    const uint8_t* img = ctx->scratch;
+    const int gpr = GEMV_WARPS / ks;
+    int blocks = (ngroups + gpr - 1) / gpr;
+    if (blocks > ctx->sm_count) blocks = ctx->sm_count;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaLaunchConfig_t icfg = cfg;
+    icfg.gridDim = dim3((unsigned)a.batch);
+    icfg.blockDim = dim3(IMG_THREADS);
+    icfg.dynamicSmemBytes = 0;
+    FK_CUDA(cudaLaunchKernelEx(&icfg, act_image_kernel<KIND>, a, ctx->scratch), FK_LAUNCH);
+    FK_CUDA(cudaLaunchKernelEx(&cfg, kern, a, img), FK_LAUNCH);
+    ctx->launches += 2;
+    return FK_OK;
+}
+
 template <int KIND>
 int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight_s* w, int slots, bool dump) {
+    if (!dump && a.batch >= MMA_MIN_BATCH && slots == 1 && !a.ids) {
+        bool fits = false;
+        const int rc = launch_mma<KIND>(ctx, st, a, w, &fits);
+        if (fits) return rc;
+    }
     if (dump) return launch_one<KIND, 1, true>(ctx, st, a, w, slots);
     if (a.batch <= 1) return launch_one<KIND, 1, false>(ctx, st, a, w, slots);
     if (a.batch <= 2) return launch_one<KIND, 2, false>(ctx, st, a, w, slots);

@@ -89,12 +89,13 @@ def test_gemv_matches_oracle(kind, batch):
 def test_edge_shapes(kind):
     from frink_b200 import device
     be = fo.block_elems(kind)
-    for rows, cols in [(1, max(be, 32)), (3, 256), (2, 8192), (1025, 512)]:
-        raw, x, w = _case(kind, rows, cols, 2, 300 + rows)
-        got = device.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
-        want = fo.matmul_f64(kind, raw, rows, cols, fo.q8_1_round(x))
-        # short rows have no averaging: hold them to the absolute part of the bar
-        assert max_abs_over_inf(got, want) <= MAX_ABS, (rows, cols)
+    for rows, cols in [(1, max(be, 32)), (3, 256), (2, 8192), (1025, 512), (40, 8192 + 256)]:
+        for batch in (2, 7):     # 7: the tensor-core form (row groups of 16, K split over warps)
+            raw, x, w = _case(kind, rows, cols, batch, 300 + rows)
+            got = device.gemv(w, torch.from_numpy(x).cuda()).cpu().numpy()
+            want = fo.matmul_f64(kind, raw, rows, cols, fo.q8_1_round(x))
+            # short rows have no averaging: hold them to the absolute part of the bar
+            assert max_abs_over_inf(got, want) <= MAX_ABS, (rows, cols, batch)
     # all-zero activations and all-zero weights
     raw, x, w = _case(kind, 8, 512, 1, 1)
     assert not device.gemv(w, torch.zeros(512, device="cuda")).cpu().numpy().any()
