@@ -716,6 +716,11 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
 
 }  // namespace
 
+// A [outer][inner] tensor of 32-bit words, unswizzled, for the other kernel files.
+int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    return make_map((CUtensorMap*)map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, base, inner_words, outer, box_inner, box_outer, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
 FK_EXPORT int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev) {
     if (!ctx || !w || !x_dev || !out_dev) return fk_fail(FK_INVALID, "gemm: null argument");
     if (m < 1) return fk_fail(FK_INVALID, "gemm: m=%d", m);

@@ -22,6 +22,9 @@
 // context's error word instead of spinning forever.
 #include "fk_common.cuh"
 
+#include <cuda.h>
+#include <string.h>
+
 namespace {
 
 constexpr int GEMV_THREADS = 512;
@@ -935,7 +938,8 @@ __global__ void __launch_bounds__(IMG_THREADS) act_image_kernel(const GemvArgs a
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArgs a, const uint8_t* __restrict__ img) {
+__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArgs a, const uint8_t* __restrict__ img,
+                                                                   const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(128) uint8_t smem[];
     TR(0, threadIdx.x == 0);
     const int cols = a.cols, rows = a.rows, nb32 = cols >> 5, batch = a.batch;
@@ -991,6 +995,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArg
     auto fill = [&]() {
         const uint32_t stage = ring + f_stage * a.stage_bytes, bar = bars + 8 * f_stage;
         const int cu0 = u0 + f_ch * a.m_chunk_units, cu1 = min(u1, cu0 + a.m_chunk_units);
+        if (KIND == FK_Q4_K) {
+            // the 16 rows x chunk of blocks as ONE tiled copy (the matrix is a [rows][row words] tensor);
+            // the box always has the full size: rows or blocks past the end arrive as zeros
+            if (lane == 0) {
+                mbar_expect_tx(bar, (uint32_t)a.stage_bytes);
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                             ::"r"(stage), "l"(&wmap), "r"(cu0 * 36), "r"(f_group * MM_ROWS), "r"(bar) : "memory");
+            }
+            if (++f_stage == a.nstages) f_stage = 0;
+            if (++f_ch == nch) { f_ch = 0; f_group += gstride; }
+            return;
+        }
         uint32_t off[NPIECE], bytes[NPIECE], mine = 0;
 #pragma unroll
         for (int i = 0; i < NPIECE; i++) {
@@ -1163,7 +1179,9 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
         for (int p = 0; p < P; p++) {
             int b = (KIND == FK_Q6_K && p == 3) ? (int)w->plane_stride[3] : cu * unit_bytes<KIND>(p);
             b = (b + 15) & ~15;
-            if ((b & 31) == 0) b += 16;        // rows 16 mod 32 bytes apart: the eight rows of a fragment load hit different banks
+            // rows 16 mod 32 bytes apart: the eight rows of a fragment load hit different banks
+            // (Q4_K arrives as a dense tile: an odd number of 144-byte blocks per chunk does it)
+            if ((b & 31) == 0 && KIND != FK_Q4_K) b += 16;
             srs[p] = b;
             spo[p] = off;
             off += MM_ROWS * b;
@@ -1172,7 +1190,13 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
     };
     int srs[4] = {0, 0, 0, 0}, spo[4] = {0, 0, 0, 0};
     int cu = a.m_kpart_units;
-    while (cu > 1 && 2 * layout(cu, srs, spo) > ring_budget) cu--;
+    if (KIND == FK_Q4_K) {
+        if (cu > 7) cu = 7;                 // a tile is at most 256 words wide
+        if ((cu & 1) == 0) cu--;
+        while (cu > 1 && 2 * layout(cu, srs, spo) > ring_budget) cu -= 2;
+    } else {
+        while (cu > 1 && 2 * layout(cu, srs, spo) > ring_budget) cu--;
+    }
     const int stage = layout(cu, srs, spo);
     if (ring_budget <= 0 || stage > ring_budget) return FK_UNSUPPORTED;
     *fits = true;
@@ -1206,8 +1230,15 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
     icfg.gridDim = dim3((unsigned)a.batch);
     icfg.blockDim = dim3(IMG_THREADS);
     icfg.dynamicSmemBytes = 0;
+    alignas(64) CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    if (KIND == FK_Q4_K) {
+        const int rcm = fk_make_map_u32(&wmap, (void*)(w->dev + (size_t)a.mat * w->mat_stride + w->plane_off[0]), w->plane_stride[0] / 4,
+                                        (uint64_t)a.rows, (uint32_t)(36 * cu), MM_ROWS);
+        if (rcm != FK_OK) return rcm;
+    }
     FK_CUDA(cudaLaunchKernelEx(&icfg, act_image_kernel<KIND>, a, ctx->scratch), FK_LAUNCH);
-    FK_CUDA(cudaLaunchKernelEx(&cfg, kern, a, img), FK_LAUNCH);
+    FK_CUDA(cudaLaunchKernelEx(&cfg, kern, a, img, wmap), FK_LAUNCH);
     ctx->launches += 2;
     return FK_OK;
 }
