@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import frink_oracle as fo
+from tests.helpers import synth_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -59,3 +60,34 @@ def test_glu_combine_and_router_logits():
     x = rng.standard_normal((5, 2048)).astype(np.float32)
     lg = device.router_logits(torch.from_numpy(router).cuda(), torch.from_numpy(x).cuda()).cpu().numpy()
     assert np.allclose(lg, x.astype(np.float64) @ router.astype(np.float64).T, rtol=1e-4, atol=1e-5)
+
+
+def test_local_slots_and_active_count_for_expert_parallel_decode():
+    """The device-side half of expert-parallel decode: routed ids -> this rank's local
+    slots, weights and count (`fk_moe_local_slots`), and the indexed matvec that runs
+    only that many slots (`fk_gemv_multi_active`), leaving the other outputs alone."""
+    from frink_b200 import device
+    n_exp, rows, cols, k = 8, 96, 768, 6
+    raws = np.concatenate([fo.encode(fo.Q4_K, synth_weights(rows, cols, 700 + e)) for e in range(n_exp)])
+    w = device.Weights(raws, fo.Q4_K, rows, cols, n_mats=n_exp)
+    ids = np.array([5, 1, 7, 2, 4, 0], np.int32)
+    wt = np.array([0.3, 0.1, 0.2, 0.15, 0.05, 0.2], np.float32)
+    x = torch.from_numpy(np.random.default_rng(3).standard_normal(cols).astype(np.float32)).cuda()
+    for e0, n_local in ((4, 4), (0, 4), (6, 2), (0, 8)):
+        li, lw, ln = device.moe_local_slots(torch.from_numpy(ids).cuda(), torch.from_numpy(wt).cuda(), e0, n_local)
+        mine = [(int(i) - e0, float(v)) for i, v in zip(ids, wt) if e0 <= i < e0 + n_local]
+        n = int(ln.item())
+        assert n == len(mine)
+        assert [(int(a), float(b)) for a, b in zip(li[:n].cpu(), lw[:n].cpu())] == [(a, np.float32(b)) for a, b in mine]
+        assert not lw[n:].cpu().numpy().any()
+        # the weights of this rank's experts alone, as the rank holds them
+        per = rows * fo.row_bytes(fo.Q4_K, cols)
+        wl = device.Weights(raws[e0 * per:(e0 + n_local) * per], fo.Q4_K, rows, cols, n_mats=n_local)
+        out = torch.full((k, rows), 7.0, device="cuda")
+        device.gemv_multi_active(wl, li, x, ln, out)
+        want = device.gemv_multi(wl, li[:n].contiguous(), x) if n else None
+        got = out.cpu().numpy()
+        if n:
+            assert np.array_equal(got[:n], want.cpu().numpy())
+        assert np.all(got[n:] == 7.0)
+    assert device.device_error() == 0
