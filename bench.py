@@ -177,6 +177,11 @@ def timed_launches(steps, ring, launch, warmup):
     return e0.elapsed_time(e1)
 
 
+# DRAM bytes one launch of the bench kernel moves, from the ncu capture summarised in
+# profiles/gemv_q4_k_8192x3072_b1.md (14 234 112 read + 0 written; the algorithmic bytes are 14 200 832)
+NCU_DRAM_BYTES_PER_LAUNCH = 14234112
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -296,7 +301,8 @@ def main():
         "config": {"workload": WORKLOAD, "l2": f"inputs larger than L2: ring of {RING} weight copies, {RING * ALGO_BYTES / 1e6:.0f} MB",
                    "timing": "CUDA events around CUDA-graph replays of the launches", "algorithmic_bytes_per_step": ALGO_BYTES},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                     "traffic": None, "peak_source": f"{which} HBM copy bandwidth", "frac_of_8TBs_nominal": per_gpu / 8000.0},
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel and shape (profiles/gemv_q4_k_8192x3072_b1.md)",
+                     "peak_source": f"{which} HBM copy bandwidth", "frac_of_8TBs_nominal": per_gpu / 8000.0},
         "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{cpu_n} full C1 GEMVs in {cpu_dt:.1f} s, AVX2 fused f32 dot, rows over threads; {cpu_model()}"},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4, "d2h_bytes_per_step": ROWS * 4,

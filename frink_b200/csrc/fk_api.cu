@@ -2,6 +2,8 @@
 // launch surface of the C ABI.
 #include "fk_common.cuh"
 
+#include <string.h>
+
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -67,6 +69,8 @@ FK_EXPORT void fk_destroy(fk_ctx* ctx) {
     fk_forget_resident(ctx);
     cudaFree(ctx->x_dev);
     cudaFree(ctx->y_dev);
+    if (ctx->x_pin) cudaFreeHost(ctx->x_pin);
+    if (ctx->y_pin) cudaFreeHost(ctx->y_pin);
     cudaFree(ctx->scratch);
     cudaFree(ctx->err_flag);
     cudaFree(ctx->argmax_ws);
@@ -325,6 +329,16 @@ int grow(float** p, size_t* cap, size_t floats) {
     *cap = floats;
     return FK_OK;
 }
+int grow_pinned(float** p, float** dev_alias, size_t* cap, size_t floats, bool mapped) {
+    if (floats <= *cap) return FK_OK;
+    if (*p) cudaFreeHost(*p);
+    *p = nullptr;
+    *cap = 0;
+    FK_CUDA(cudaHostAlloc((void**)p, floats * sizeof(float), mapped ? cudaHostAllocMapped : cudaHostAllocDefault), FK_LAUNCH);
+    if (dev_alias) FK_CUDA(cudaHostGetDevicePointer((void**)dev_alias, *p, 0), FK_LAUNCH);
+    *cap = floats;
+    return FK_OK;
+}
 }  // namespace
 
 FK_EXPORT int fk_forget_resident(fk_ctx* ctx) {
@@ -356,15 +370,27 @@ FK_EXPORT int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_hos
     std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     const size_t xn = (size_t)batch * n_cols, yn = (size_t)batch * n_rows;
     if ((rc = grow(&ctx->x_dev, &ctx->x_cap, xn))) return rc;
+    if (batch <= 8) {
+        // the decode shape: a few KB each way, so the call is all latency.  x goes through a
+        // pinned buffer (a truly asynchronous copy), and the kernel writes y straight into
+        // mapped host memory, which saves the copy back and its launch.
+        if ((rc = grow_pinned(&ctx->x_pin, nullptr, &ctx->x_pin_cap, xn, false))) return rc;
+        if ((rc = grow_pinned(&ctx->y_pin, &ctx->y_pin_dev, &ctx->y_pin_cap, yn, true))) return rc;
+        memcpy(ctx->x_pin, x_batch_host, xn * sizeof(float));
+        FK_CUDA(cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, xn * sizeof(float), cudaMemcpyHostToDevice, nullptr), FK_LAUNCH);
+        ctx->h2d += xn * sizeof(float);
+        rc = fk_gemv_launch(ctx, nullptr, w, nullptr, 0, 1, ctx->x_dev, 0, batch, ctx->y_pin_dev, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+        FK_CUDA(cudaStreamSynchronize(nullptr), FK_LAUNCH);
+        memcpy(out_host, ctx->y_pin, yn * sizeof(float));
+        ctx->d2h += yn * sizeof(float);
+        return FK_OK;
+    }
     if ((rc = grow(&ctx->y_dev, &ctx->y_cap, yn))) return rc;
     FK_CUDA(cudaMemcpyAsync(ctx->x_dev, x_batch_host, xn * sizeof(float), cudaMemcpyHostToDevice, nullptr), FK_LAUNCH);
     ctx->h2d += xn * sizeof(float);
-    if (batch <= 8) {
-        rc = fk_gemv_launch(ctx, nullptr, w, nullptr, 0, 1, ctx->x_dev, 0, batch, ctx->y_dev, nullptr, nullptr, nullptr);
-    } else {
-        ctx->mu.unlock();  // fk_gemm takes the lock itself when it grows scratch
+    {
         rc = fk_gemm(ctx, nullptr, w, 0, ctx->x_dev, batch, ctx->y_dev);
-        ctx->mu.lock();
     }
     if (rc) return rc;
     FK_CUDA(cudaMemcpyAsync(out_host, ctx->y_dev, yn * sizeof(float), cudaMemcpyDeviceToHost, nullptr), FK_LAUNCH);

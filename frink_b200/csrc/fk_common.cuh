@@ -59,6 +59,13 @@ struct fk_ctx {
     size_t x_cap = 0;
     float* y_dev = nullptr;
     size_t y_cap = 0;
+    // pinned host staging of the host-buffer surface (batch <= 8): x is copied from here,
+    // y is written by the kernel straight into mapped host memory
+    float* x_pin = nullptr;
+    size_t x_pin_cap = 0;
+    float* y_pin = nullptr;
+    float* y_pin_dev = nullptr;
+    size_t y_pin_cap = 0;
     // GEMM / MoE scratch (activation q8_1 planes), grown on demand
     uint8_t* scratch = nullptr;
     size_t scratch_cap = 0;
