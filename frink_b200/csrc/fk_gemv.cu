@@ -479,7 +479,38 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         if (++f_kc == a.nchunks) { f_kc = 0; f_pair += twarps; }
     };
 
-    // Every stage of the ring is requested before the activations are touched.
+    // ---- order of the start-up.  Launched with programmatic stream serialization, this
+    // grid may start while the previous kernel of the stream still runs; weights are
+    // constants, x (and y) may belong to that kernel.  When the activations fit one pass
+    // (the usual decode shapes) the block waits for that kernel FIRST and requests x
+    // before its weights: the SM takes its deliveries in order, and x asked for after
+    // 96 KB of weights arrives after them, with the quantization and every dot product
+    // queued behind it.  In a chain of matvecs the wait is short (a block only starts
+    // once its SM's block of the previous launch has left).  Larger activations keep the
+    // other order: weights first, then the wait.
+    constexpr int QU = 4;
+    const int c4 = cols >> 2, items = NB * c4;
+    const bool early = items <= GEMV_THREADS * QU;
+    float4 v[QU], vn[QU], vu[QU];
+    auto load_acts = [&](int base) {
+#pragma unroll
+        for (int u = 0; u < QU; u++) {
+            const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+            v[u] = vn[u] = vu[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (idx < items) {
+                const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
+                if (b < a.batch) {
+                    v[u] = __ldg((const float4*)(x + (size_t)b * a.x_ld) + k4);
+                    if (a.norm_w) vn[u] = __ldg((const float4*)a.norm_w + k4);
+                    if (a.glu_up) vu[u] = __ldg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
+                }
+            }
+        }
+    };
+    if (early) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        load_acts(0);
+    }
     const int pre = njobs < a.nstages ? njobs : a.nstages;
     for (int q = 0; q < pre; q++) fill();
     if (a.pf_bytes && warp == 0) {
@@ -494,11 +525,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         }
     }
     TR(1, threadIdx.x == 0);
-    // Launched with programmatic stream serialization: this grid may start while the
-    // previous kernel of the stream is still running.  Weights are constants, so their
-    // copies go out at once; x (and y) may belong to that kernel, so wait for it here,
-    // and let the next grid start its own weight copies.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     TR(2, threadIdx.x == 0);
 
@@ -509,12 +536,20 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     __shared__ double s_part[GEMV_WARPS];
     if (a.norm_w) {
         // fused RMSNorm: squares in f32, summed in f64, the mean rounded to f32, 1/sqrtf(mean + eps)
-        const int c4n = cols >> 2;
         for (int b = 0; b < a.batch; b++) {
             double sq = 0.0;
-            for (int i = threadIdx.x; i < c4n; i += GEMV_THREADS) {
-                const float4 v = __ldg((const float4*)(x + (size_t)b * a.x_ld) + i);
-                sq += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
+            if (early) {
+#pragma unroll
+                for (int u = 0; u < QU; u++) {
+                    const int idx = u * GEMV_THREADS + (int)threadIdx.x;
+                    if (idx < items && (NB == 1 ? 0 : idx / c4) == b)
+                        sq += (double)(v[u].x * v[u].x) + (double)(v[u].y * v[u].y) + (double)(v[u].z * v[u].z) + (double)(v[u].w * v[u].w);
+                }
+            } else {
+                for (int i = threadIdx.x; i < c4; i += GEMV_THREADS) {
+                    const float4 t4 = __ldg((const float4*)(x + (size_t)b * a.x_ld) + i);
+                    sq += (double)(t4.x * t4.x) + (double)(t4.y * t4.y) + (double)(t4.z * t4.z) + (double)(t4.w * t4.w);
+                }
             }
             for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
             if (lane == 0) s_part[warp] = sq;
@@ -528,28 +563,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         }
     }
     {
-        const int c4 = cols >> 2, items = NB * c4;
-        constexpr int QU = 4;
         for (int base = 0; base < items; base += GEMV_THREADS * QU) {
-            float4 v[QU];
+            if (!early) load_acts(base);
 #pragma unroll
             for (int u = 0; u < QU; u++) {
                 const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
-                v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                 if (idx < items) {
-                    const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
+                    const int b = NB == 1 ? 0 : idx / c4;
                     if (b < a.batch) {
-                        v[u] = __ldg((const float4*)(x + (size_t)b * a.x_ld) + k4);
                         if (a.norm_w) {
-                            const float4 nw = __ldg((const float4*)a.norm_w + k4);
                             const float sc = s_scale[b];
-                            v[u].x = v[u].x * sc * nw.x; v[u].y = v[u].y * sc * nw.y;
-                            v[u].z = v[u].z * sc * nw.z; v[u].w = v[u].w * sc * nw.w;
+                            v[u].x = v[u].x * sc * vn[u].x; v[u].y = v[u].y * sc * vn[u].y;
+                            v[u].z = v[u].z * sc * vn[u].z; v[u].w = v[u].w * sc * vn[u].w;
                         }
                         if (a.glu_up) {
-                            const float4 up = __ldg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
                             float g[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                            const float uu[4] = {up.x, up.y, up.z, up.w};
+                            const float uu[4] = {vu[u].x, vu[u].y, vu[u].z, vu[u].w};
 #pragma unroll
                             for (int e = 0; e < 4; e++) {
                                 if (a.glu_act == 0) {

@@ -8,11 +8,18 @@
 
 namespace {
 
+__device__ __forceinline__ void fk_pdl_sync() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+
 // ---- embedding gather: out[i] = dequantized row ids[i]  (the kind's own dequant)
 __device__ __forceinline__ float e8m0_scale(uint32_t e) { return __uint_as_float(e == 0 ? 0x00400000u : (e << 23)); }
 
 __global__ void get_rows_kernel(const uint8_t* __restrict__ wb, size_t o0, size_t o1, size_t o2, size_t o3, size_t s0, size_t s1, size_t s2,
                                 size_t s3, int kind, int rows, int cols, const int* __restrict__ ids, float* __restrict__ out) {
+    fk_pdl_sync();
     const int i = blockIdx.y;
     int row = ids[i];
     if (row < 0 || row >= rows) row = 0;
@@ -64,6 +71,7 @@ __global__ void get_rows_kernel(const uint8_t* __restrict__ wb, size_t o0, size_
 // reference's order up to the association of the f64 sum.
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ res, const float* __restrict__ w, int cols, float eps,
                                float* __restrict__ out) {
+    fk_pdl_sync();
     const int r = blockIdx.x;
     float* xr = x + (size_t)r * cols;
     const float* rr = res ? res + (size_t)r * cols : nullptr;
@@ -134,6 +142,7 @@ __global__ void rope_kernel(float* __restrict__ x, int n_rows, int n_heads, int 
 __global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, int q_ld, int kv_ld, int n_rows,
                                int n_heads, int n_kv, int head_dim, const int* __restrict__ pos, float theta, int neox,
                                float* __restrict__ kc, float* __restrict__ vc) {
+    fk_pdl_sync();
     const int half = head_dim / 2;
     const int p0 = *pos;
     const int per_row = (n_heads + n_kv) * half;            // rotation pairs per row, q heads first
@@ -193,6 +202,7 @@ constexpr int AD_WARPS = 4, AD_TK = 64, AD_REC = 132, AD_MAX_SPLITS = 64, AD_MAX
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
             const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt) {
+    fk_pdl_sync();
     __shared__ __align__(16) float sq[128];
     __shared__ float s_p[AD_TK];
     __shared__ __align__(16) float s_acc[AD_WARPS][128];
@@ -406,6 +416,7 @@ __device__ __forceinline__ unsigned long long argmax_key(float v, int i) {
 }
 __global__ void __launch_bounds__(256)
 argmax_kernel(const float* __restrict__ x, int n, int* __restrict__ out, unsigned long long* __restrict__ ws, unsigned* __restrict__ cnt) {
+    fk_pdl_sync();
     const int row = blockIdx.y;
     const float* xr = x + (size_t)row * n;
     unsigned long long best = 0ull;
@@ -441,7 +452,10 @@ argmax_kernel(const float* __restrict__ x, int n, int* __restrict__ out, unsigne
     }
 }
 
-__global__ void add_int_kernel(int* p, int v) { *p += v; }
+__global__ void add_int_kernel(int* p, int v) {
+    fk_pdl_sync();
+    *p += v;
+}
 
 // Every kernel of a decode step asks for the same shared-memory carve-out as the GEMV
 // (the maximum): an SM that alternates between kernels with different carve-outs
@@ -457,6 +471,24 @@ template <typename K> void fk_carveout(K kern) {
 
 }  // namespace
 
+// Launch with programmatic stream serialization: the grid may be scheduled while the previous
+// kernel of the stream still runs; the kernels below call fk_pdl_sync() before they touch
+// global memory, which waits for that kernel to complete (and lets the next grid be scheduled).
+template <typename... KArgs, typename... Args>
+cudaError_t fk_launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 #define FK_LAUNCH_CHECK() do { FK_CUDA(cudaGetLastError(), FK_LAUNCH); ctx->launches++; } while (0)
 
 FK_EXPORT int fk_get_rows(fk_ctx* ctx, void* stream, fk_weight w, int mat, const int* ids_dev, int n, float* out_dev) {
@@ -465,9 +497,9 @@ FK_EXPORT int fk_get_rows(fk_ctx* ctx, void* stream, fk_weight w, int mat, const
     FkDeviceGuard g(ctx->device);
     dim3 grid((w->cols + 255) / 256 > 8 ? 8 : (w->cols + 255) / 256, n);
     FK_CARVEOUT(get_rows_kernel);
-    get_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(w->dev + (size_t)mat * w->mat_stride, w->plane_off[0], w->plane_off[1], w->plane_off[2],
+    FK_CUDA(fk_launch_pdl(get_rows_kernel, grid, dim3(256), 0, (cudaStream_t)stream, w->dev + (size_t)mat * w->mat_stride, w->plane_off[0], w->plane_off[1], w->plane_off[2],
                                                            w->plane_off[3], w->plane_stride[0], w->plane_stride[1], w->plane_stride[2],
-                                                           w->plane_stride[3], w->kind, w->rows, w->cols, ids_dev, out_dev);
+                                                           w->plane_stride[3], w->kind, w->rows, w->cols, ids_dev, out_dev), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -481,7 +513,7 @@ FK_EXPORT int fk_rmsnorm(fk_ctx* ctx, void* stream, float* x_dev, const float* r
     int threads = n_rows <= 8 ? ((cols / 4 + 31) / 32) * 32 : 256;
     threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
     FK_CARVEOUT(rmsnorm_kernel);
-    rmsnorm_kernel<<<n_rows, threads, 0, (cudaStream_t)stream>>>(x_dev, residual_dev, weight_dev, cols, eps, out_dev);
+    FK_CUDA(fk_launch_pdl(rmsnorm_kernel, dim3(n_rows), dim3(threads), 0, (cudaStream_t)stream, x_dev, residual_dev, weight_dev, cols, eps, out_dev), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -505,8 +537,8 @@ FK_EXPORT int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, 
     int blocks = (total + 255) / 256;
     if (blocks > 4096) blocks = 4096;
     FK_CARVEOUT(rope_kv_kernel);
-    rope_kv_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(q_dev, k_dev, v_dev, q_ld, kv_ld, n_rows, n_heads, n_kv, head_dim, pos_dev, theta,
-                                                           neox, k_cache_dev, v_cache_dev);
+    FK_CUDA(fk_launch_pdl(rope_kv_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, q_dev, k_dev, v_dev, q_ld, kv_ld, n_rows, n_heads, n_kv,
+                          head_dim, pos_dev, theta, neox, k_cache_dev, v_cache_dev), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -552,8 +584,8 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
         const int rc = fk_ensure_scratch(ctx, (size_t)n_q * n_heads * splits * AD_REC * sizeof(float));
         if (rc != FK_OK) return rc;
         FK_CARVEOUT(attn_kernel);
-        attn_kernel<<<dim3(splits, n_heads, n_q), AD_WARPS * 32, 0, (cudaStream_t)stream>>>(q_dev, q_ld, k_dev, v_dev, n_heads, n_kv, head_dim, pos_dev,
-                                                                                           scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt);
+        FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_q), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, k_dev, v_dev,
+                              n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt), FK_LAUNCH);
     }
     FK_LAUNCH_CHECK();
     return FK_OK;
@@ -566,7 +598,7 @@ FK_EXPORT int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_row
     int blocks = (n + 2047) / 2048;
     blocks = blocks < 1 ? 1 : blocks > ARGMAX_MAX_BLOCKS ? ARGMAX_MAX_BLOCKS : blocks;
     FK_CARVEOUT(argmax_kernel);
-    argmax_kernel<<<dim3(blocks, n_rows), 256, 0, (cudaStream_t)stream>>>(x_dev, n, out_dev, ctx->argmax_ws, ctx->argmax_cnt);
+    FK_CUDA(fk_launch_pdl(argmax_kernel, dim3(blocks, n_rows), dim3(256), 0, (cudaStream_t)stream, x_dev, n, out_dev, ctx->argmax_ws, ctx->argmax_cnt), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -575,7 +607,7 @@ FK_EXPORT int fk_add_int(fk_ctx* ctx, void* stream, int* p_dev, int v) {
     if (!ctx || !p_dev) return fk_fail(FK_INVALID, "add_int: null argument");
     FkDeviceGuard g(ctx->device);
     FK_CARVEOUT(add_int_kernel);
-    add_int_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(p_dev, v);
+    FK_CUDA(fk_launch_pdl(add_int_kernel, dim3(1), dim3(1), 0, (cudaStream_t)stream, p_dev, v), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
