@@ -23,9 +23,28 @@
 // spinning forever.
 #include "fk_common.cuh"
 
+#ifndef FK_I2F_MASK
+#define FK_I2F_MASK 0
+#endif
+#ifndef FK_EPI_F32X2
+#define FK_EPI_F32X2 0
+#endif
+
 #include <cuda.h>
 
 namespace {
+
+#ifdef FK_TRACE
+__device__ unsigned long long fk_gemm_trace[4][512];
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GTR(k_, i_, who_) do { if ((who_) && blockIdx.x == 0 && blockIdx.y == 0 && (i_) < 512) fk_gemm_trace[k_][i_] = gtime_ns(); } while (0)
+#else
+#define GTR(k_, i_, who_) do { } while (0)
+#endif
 
 constexpr int BM = 128;           // weight rows per CTA (MMA M)
 constexpr int KSTAGE = 128;       // K per pipeline stage (4 MMAs of K = 32)
@@ -382,6 +401,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
             if (c == 0) {
                 mbar_wait(acc_full(buf), (kb / S::NACC) & 1, a.err, 11);
                 tc_fence_after();
+                GTR(1, kb, warp == 0 && lane == 0);
             }
             tc_ld16(taddr0 + buf * BN + c * 16, dst);
         };
@@ -419,17 +439,39 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                             const float4 sx = lds128(dxs + 16u * BN + 4u * i);
                             sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
                         }
+#if FK_EPI_F32X2
+                        // two columns per instruction on the packed f32x2 path
+#pragma unroll
+                        for (int e = 0; e < 4; e += 2) {
+#if FK_I2F_MASK
+                            const float2 f2 = make_float2((float)(int)cur[i + e], (float)(int)cur[i + e + 1]);
+#else
+                            const float2 g2 = make_float2(__int_as_float((int)cur[i + e] + 0x4B400000), __int_as_float((int)cur[i + e + 1] + 0x4B400000));
+                            const float2 f2 = __fadd2_rn(g2, make_float2(-12582912.0f, -12582912.0f));
+#endif
+                            const float2 s2 = __fmul2_rn(make_float2(dw, dw), make_float2(dxa[e], dxa[e + 1]));
+                            float2 t2 = __ffma2_rn(s2, f2, make_float2(acc[c * 16 + i + e], acc[c * 16 + i + e + 1]));
+                            if (KIND == FK_Q4_K) t2 = __ffma2_rn(make_float2(-mw, -mw), make_float2(sxa[e], sxa[e + 1]), t2);
+                            acc[c * 16 + i + e] = t2.x;
+                            acc[c * 16 + i + e + 1] = t2.y;
+                        }
+#else
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
-                            // exact int32 -> f32 for |C| < 2^22 without the conversion pipe
-                            const float f = __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
+                            // exact int32 -> f32 for |C| < 2^22: by the magic-number add on the integer and
+                            // FP32 pipes, or (elements whose bit of FK_I2F_MASK is set) by the conversion unit,
+                            // which costs one issue slot instead of two but runs at a quarter of the rate
+                            const float f = ((FK_I2F_MASK >> e) & 1) ? (float)(int)cur[i + e]
+                                                                     : __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
                             float t = fmaf(dw * dxa[e], f, acc[c * 16 + i + e]);
                             if (KIND == FK_Q4_K) t = fmaf(-mw, sxa[e], t);
                             acc[c * 16 + i + e] = t;
                         }
+#endif
                     }
                     tc_wait_ld();
                     tc_ld_fence<16>(nxt);
+                    GTR(2, kb, warp == 0 && lane == 0 && c == 1);
                     if (kb_n < nkb && c_n == 1) {   // both halves of that accumulator are in registers: hand it back
                         tc_fence_before();
                         __syncwarp();
@@ -472,6 +514,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                 fence_proxy_async();   // generic-proxy writes -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full_a(s));
+                GTR(3, st, warp == EPI_WARPS && lane == 0);
 #pragma unroll
                 for (int i = 0; i < NR; i++) cur[i] = nxt[i];
             }
@@ -509,6 +552,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                     if (kb >= S::NACC) mbar_wait(acc_empty(buf), ((kb / S::NACC) - 1) & 1, a.err, 42);
                     tc_fence_after();
                     // K advances 32 bytes inside the 128-byte swizzle atom: +2 in the 16-byte address field
+                    GTR(0, kb, true);
                     tc_mma_i8(tmem_base + buf * BN, da + 2 * j, db + 2 * j, IDESC);
                     tc_commit(acc_full(buf));
                 }
@@ -715,6 +759,12 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
 }
 
 }  // namespace
+
+#ifdef FK_TRACE
+extern "C" __attribute__((visibility("default"))) int fk_gemm_trace_read(void* host, size_t bytes) {
+    return cudaMemcpyFromSymbol(host, fk_gemm_trace, bytes) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 // A [outer][inner] tensor of 32-bit words, unswizzled, for the other kernel files.
 int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
