@@ -128,3 +128,30 @@ def add_(a, b):
 
 def add_int_(p, v):
     p.add_(v)
+
+
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, prefetch=None):
+    """The fused matvec of the device layer, composed from the separate CPU steps."""
+    h = x.clone()
+    if norm_weight is not None:
+        h = rmsnorm(h, norm_weight, eps)
+    if glu_up is not None:
+        h = glu(h.contiguous(), glu_up.contiguous(), glu_act)
+    y = gemv(w, h, mat=mat)
+    if out is None:
+        return y
+    if accumulate:
+        out.add_(y)
+    else:
+        out.copy_(y)
+    return out
+
+
+def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache):
+    qc, kc = q.contiguous(), k.contiguous()
+    rope(qc, n_heads, head_dim, pos, theta, neox)
+    rope(kc, n_kv, head_dim, pos, theta, neox)
+    q.copy_(qc)
+    k.copy_(kc)
+    kv_append(k_cache, kc, pos)
+    kv_append(v_cache, v.contiguous(), pos)
