@@ -31,6 +31,7 @@ SYMBOLS = {
     "fk_gemv": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
     "fk_gemv_multi": (_I, [_P, _P, _P, _P, _I, _P, _I, _P]),
+    "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "fk_moe_local_slots": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "fk_gemv_isums": (_I, [_P, _P, _P, _I, _P, _P]),
@@ -42,10 +43,11 @@ SYMBOLS = {
     "fk_moe_permute": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "fk_glu": (_I, [_P, _P, _P, _P, _SZ, _I, _P]),
     "fk_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
+    "fk_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "fk_get_rows": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, C.c_float, _P]),
     "fk_rope": (_I, [_P, _P, _P, _I, _I, _I, _P, C.c_float, _I]),
-    "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P]),
+    "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P, _P, _P, C.c_float]),
     "fk_add": (_I, [_P, _P, _P, _P, _SZ]),
     "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P]),
     "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P]),

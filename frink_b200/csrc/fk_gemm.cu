@@ -24,10 +24,10 @@
 #include "fk_common.cuh"
 
 #ifndef FK_I2F_MASK
-#define FK_I2F_MASK 0
+#define FK_I2F_MASK 15
 #endif
 #ifndef FK_EPI_F32X2
-#define FK_EPI_F32X2 0
+#define FK_EPI_F32X2 1
 #endif
 
 #include <cuda.h>
@@ -440,15 +440,22 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                             sxa[0] = sx.x; sxa[1] = sx.y; sxa[2] = sx.z; sxa[3] = sx.w;
                         }
 #if FK_EPI_F32X2
-                        // two columns per instruction on the packed f32x2 path
+                        // two columns per instruction on the packed f32x2 path; int32 -> f32 (exact, |C| < 2^22)
+                        // either on the conversion unit (bit of FK_I2F_MASK set: one issue slot, a quarter of
+                        // the rate) or by the magic-number add on the integer and FP32 pipes (two slots)
 #pragma unroll
                         for (int e = 0; e < 4; e += 2) {
-#if FK_I2F_MASK
-                            const float2 f2 = make_float2((float)(int)cur[i + e], (float)(int)cur[i + e + 1]);
-#else
-                            const float2 g2 = make_float2(__int_as_float((int)cur[i + e] + 0x4B400000), __int_as_float((int)cur[i + e + 1] + 0x4B400000));
-                            const float2 f2 = __fadd2_rn(g2, make_float2(-12582912.0f, -12582912.0f));
-#endif
+                            constexpr int M2 = FK_I2F_MASK;
+                            float2 f2;
+                            if (((M2 >> e) & 3) == 3) {
+                                f2 = make_float2((float)(int)cur[i + e], (float)(int)cur[i + e + 1]);
+                            } else if (((M2 >> e) & 3) == 0) {
+                                f2 = __fadd2_rn(make_float2(__int_as_float((int)cur[i + e] + 0x4B400000), __int_as_float((int)cur[i + e + 1] + 0x4B400000)),
+                                                make_float2(-12582912.0f, -12582912.0f));
+                            } else {
+                                f2.x = ((M2 >> e) & 1) ? (float)(int)cur[i + e] : __int_as_float((int)cur[i + e] + 0x4B400000) - 12582912.0f;
+                                f2.y = ((M2 >> e) & 2) ? (float)(int)cur[i + e + 1] : __int_as_float((int)cur[i + e + 1] + 0x4B400000) - 12582912.0f;
+                            }
                             const float2 s2 = __fmul2_rn(make_float2(dw, dw), make_float2(dxa[e], dxa[e + 1]));
                             float2 t2 = __ffma2_rn(s2, f2, make_float2(acc[c * 16 + i + e], acc[c * 16 + i + e + 1]));
                             if (KIND == FK_Q4_K) t2 = __ffma2_rn(make_float2(-mw, -mw), make_float2(sxa[e], sxa[e + 1]), t2);

@@ -1402,6 +1402,17 @@ FK_EXPORT int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* i
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, nullptr);
 }
 
+FK_EXPORT int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* gate_dev, const float* up_dev,
+                                int x_stride, int glu_act, float* y_dev, const int* n_active_dev) {
+    if (!ctx || !w || !ids_dev || !gate_dev || !up_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_multi_glu: null argument");
+    if (k < 1 || k > 65535) return fk_fail(FK_INVALID, "gemv_multi_glu: k=%d", k);
+    if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_multi_glu: activation %d", glu_act);
+    if (((uintptr_t)gate_dev & 15) || ((uintptr_t)up_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_glu: inputs must be 16-byte aligned");
+    FkDeviceGuard g(ctx->device);
+    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, nullptr, 0};
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, gate_dev, x_stride, 1, y_dev, nullptr, n_active_dev, &f);
+}
+
 FK_EXPORT int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
                                    int x_stride, float* y_dev, const int* n_active_dev) {
     if (!ctx || !w || !ids_dev || !x_dev || !y_dev || !n_active_dev) return fk_fail(FK_INVALID, "gemv_multi_active: null argument");

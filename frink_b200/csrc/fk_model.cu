@@ -141,38 +141,51 @@ __global__ void rope_kernel(float* __restrict__ x, int n_rows, int n_heads, int 
 // rope(q), rope(k), and the cache append of k and v, one launch.
 __global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, int q_ld, int kv_ld, int n_rows,
                                int n_heads, int n_kv, int head_dim, const int* __restrict__ pos, float theta, int neox,
-                               float* __restrict__ kc, float* __restrict__ vc) {
+                               float* __restrict__ kc, float* __restrict__ vc, const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                               float eps) {
     fk_pdl_sync();
+    // a warp per (row, head), q heads first; a lane takes rotation pairs lane, lane + 32, ...
     const int half = head_dim / 2;
     const int p0 = *pos;
-    const int per_row = (n_heads + n_kv) * half;            // rotation pairs per row, q heads first
     const int kvw = n_kv * head_dim;
-    const int total = n_rows * per_row;
-    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const int row = idx / per_row, rem = idx % per_row, hh = rem / half, i = rem % half;
-        const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)head_dim);
-        float s, c;
-        sincosf((float)(p0 + row) * freq, &s, &c);
-        const int ia = neox ? i : 2 * i, ib = neox ? i + half : 2 * i + 1;
-        if (hh < n_heads) {
-            float* vv = q + (size_t)row * q_ld + hh * head_dim;
-            const float a = vv[ia], b = vv[ib];
-            vv[ia] = a * c - b * s;
-            vv[ib] = a * s + b * c;
-        } else {
-            const int kh = hh - n_heads;
-            float* vv = k + (size_t)row * kv_ld + kh * head_dim;
-            const float a = vv[ia], b = vv[ib];
-            const float ra = a * c - b * s, rb = a * s + b * c;
+    const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
+    const int total = n_rows * (n_heads + n_kv);
+    for (int item = blockIdx.x * wpb + (threadIdx.x >> 5); item < total; item += gridDim.x * wpb) {
+        const int row = item / (n_heads + n_kv), hh = item % (n_heads + n_kv);
+        const bool is_q = hh < n_heads;
+        const int kh = hh - n_heads;
+        float* vv = is_q ? q + (size_t)row * q_ld + hh * head_dim : k + (size_t)row * kv_ld + kh * head_dim;
+        const float* nw = is_q ? q_norm : k_norm;
+        float scale = 1.0f;
+        if (nw) {
+            // the per-head RMSNorm of Qwen3 (squares in f32, sum in f64) ahead of the rotation
+            double sq = 0.0;
+            for (int i = lane; i < head_dim; i += 32) sq += (double)(vv[i] * vv[i]);
+            for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+            scale = 1.0f / sqrtf((float)(sq / (double)head_dim) + eps);
+        }
+        for (int i = lane; i < half; i += 32) {
+            const float freq = 1.0f / powf(theta, (float)(2 * i) / (float)head_dim);
+            float sn, cs;
+            sincosf((float)(p0 + row) * freq, &sn, &cs);
+            const int ia = neox ? i : 2 * i, ib = neox ? i + half : 2 * i + 1;
+            float xa = vv[ia], xb = vv[ib];
+            if (nw) {
+                xa = xa * scale * nw[ia];
+                xb = xb * scale * nw[ib];
+            }
+            const float ra = xa * cs - xb * sn, rb = xa * sn + xb * cs;
             vv[ia] = ra;
             vv[ib] = rb;
-            float* dk = kc + (size_t)(p0 + row) * kvw + kh * head_dim;
-            dk[ia] = ra;
-            dk[ib] = rb;
-            const float* sv = v + (size_t)row * kv_ld + kh * head_dim;
-            float* dv = vc + (size_t)(p0 + row) * kvw + kh * head_dim;
-            dv[ia] = sv[ia];
-            dv[ib] = sv[ib];
+            if (!is_q) {
+                float* dk = kc + (size_t)(p0 + row) * kvw + kh * head_dim;
+                dk[ia] = ra;
+                dk[ib] = rb;
+                const float* sv = v + (size_t)row * kv_ld + kh * head_dim;
+                float* dv = vc + (size_t)(p0 + row) * kvw + kh * head_dim;
+                dv[ia] = sv[ia];
+                dv[ib] = sv[ib];
+            }
         }
     }
 }
@@ -529,16 +542,18 @@ FK_EXPORT int fk_rope(fk_ctx* ctx, void* stream, float* x_dev, int n_rows, int n
 }
 
 FK_EXPORT int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const float* v_dev, int q_ld, int kv_ld, int n_rows,
-                         int n_heads, int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev) {
+                         int n_heads, int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev,
+                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps) {
     if (!ctx || !q_dev || !k_dev || !v_dev || !pos_dev || !k_cache_dev || !v_cache_dev) return fk_fail(FK_INVALID, "rope_kv: null argument");
     if (n_rows < 1 || n_heads < 1 || n_kv < 1 || head_dim < 2 || (head_dim & 1)) return fk_fail(FK_INVALID, "rope_kv: bad shape");
     FkDeviceGuard g(ctx->device);
-    const int total = n_rows * (n_heads + n_kv) * (head_dim / 2);
-    int blocks = (total + 255) / 256;
+    if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fk_fail(FK_INVALID, "rope_kv: q and k norm weights come together");
+    const int total = n_rows * (n_heads + n_kv);          // a warp each, four warps per block
+    int blocks = (total + 3) / 4;
     if (blocks > 4096) blocks = 4096;
     FK_CARVEOUT(rope_kv_kernel);
-    FK_CUDA(fk_launch_pdl(rope_kv_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, q_dev, k_dev, v_dev, q_ld, kv_ld, n_rows, n_heads, n_kv,
-                          head_dim, pos_dev, theta, neox, k_cache_dev, v_cache_dev), FK_LAUNCH);
+    FK_CUDA(fk_launch_pdl(rope_kv_kernel, dim3(blocks), dim3(128), 0, (cudaStream_t)stream, q_dev, k_dev, v_dev, q_ld, kv_ld, n_rows, n_heads, n_kv,
+                          head_dim, pos_dev, theta, neox, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, norm_eps), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }

@@ -155,7 +155,7 @@ __global__ void glu_kernel(const float* __restrict__ gate, const float* __restri
 }
 
 __global__ void combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_of, const float* __restrict__ w,
-                               int k, int n, float* __restrict__ out) {
+                               int k, int n, float* __restrict__ out, int add) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int t = blockIdx.y;
     if (i >= n) return;
@@ -164,7 +164,7 @@ __global__ void combine_kernel(const float* __restrict__ y, const int* __restric
         const int p = pair_of ? pair_of[t * k + j] : t * k + j;
         acc += y[(size_t)p * n + i] * w[t * k + j];
     }
-    out[(size_t)t * n + i] = acc;
+    out[(size_t)t * n + i] = add ? out[(size_t)t * n + i] + acc : acc;   // the sum is formed from zero either way
 }
 
 // One warp: the chosen experts of one token that fall in [e0, e0 + n_local), packed
@@ -275,7 +275,20 @@ FK_EXPORT int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, cons
     FkDeviceGuard g(ctx->device);
     dim3 grid((n + 255) / 256, batch);
     FK_CARVEOUT(combine_kernel);
-    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev);
+    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev, 0);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_moe_combine_add(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
+                             int batch, int k, int n, float* out_dev) {
+    if (!ctx || !y_dev || !w_dev || !out_dev) return fk_fail(FK_INVALID, "moe_combine_add: null argument");
+    if (batch < 1 || batch > 65535 || k < 1 || n < 1) return fk_fail(FK_INVALID, "moe_combine_add: batch %d, k %d, n %d", batch, k, n);
+    FkDeviceGuard g(ctx->device);
+    dim3 grid((n + 255) / 256, batch);
+    FK_CARVEOUT(combine_kernel);
+    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev, 1);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;

@@ -216,22 +216,22 @@ class Decoder:
             if "qkv" in L:
                 qkv = ops.gemv_fused(L["qkv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wo"].w)
                 q, k, v = qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]
+            elif "qk" in L:
+                # v in another block format (the usual K-quant mix): two matvecs, the norm folded into both
+                qk = ops.gemv_fused(L["qk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wv"].w)
+                q, k = qk[:, :hq], qk[:, hq:hq + kvw]
+                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wo"].w)
             else:
-                h = ops.rmsnorm(x, L["attn_norm"], cfg.eps)
-                if "qk" in L:
-                    (q, k), v = L["qk"](h), L["wv"](h)
-                else:
-                    q, k, v = L["wq"](h), L["wk"](h), L["wv"](h)
-            if cfg.qk_norm:
-                q = ops.rmsnorm(q.contiguous().view(-1, hd), L["q_norm"], cfg.eps).view(n, -1)
-                k = ops.rmsnorm(k.contiguous().view(-1, hd), L["k_norm"], cfg.eps).view(n, -1)
-                v = v.contiguous()
-            ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"])
+                q = ops.gemv_fused(L["wq"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+            ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
+                        q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
             a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
             ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True, prefetch=first_ffn)
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
-                ops.add_(x, run_device_routed(L["moe"], h2, ops))
+                run_device_routed(L["moe"], h2, ops, residual=x)
             elif "gate_up" in L:
                 gu = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, prefetch=L["down"].w)
                 ops.gemv_fused(L["down"].w, gu[:, :cfg.ffn], glu_up=gu[:, cfg.ffn:], out=x, accumulate=True, prefetch=after_ffn)

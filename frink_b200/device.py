@@ -137,11 +137,14 @@ def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, gl
     return y
 
 
-def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache):
-    """One launch: rotate q and k in place (rows at pos[0] + r) and append k, v to the caches."""
+def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache, q_norm=None, k_norm=None, eps=0.0):
+    """One launch: (Qwen3: per-head RMSNorm of q and k,) rotate q and k in place (rows at
+    pos[0] + r) and append k, v to the caches.  q, k, v may be column slices of one buffer."""
     n = q.shape[0]
+    assert k.stride(0) == v.stride(0) or n == 1
     check(lib().fk_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), n, n_heads, n_kv, head_dim,
-                           _ptr(_i32(pos)), float(theta), int(neox), _ptr(k_cache), _ptr(v_cache)))
+                           _ptr(_i32(pos)), float(theta), int(neox), _ptr(k_cache), _ptr(v_cache),
+                           _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps)))
 
 
 def gemv_multi(w, ids, x, out=None):
@@ -151,6 +154,17 @@ def gemv_multi(w, ids, x, out=None):
     stride = 0 if x.dim() == 1 else x.stride(0)
     y = out if out is not None else torch.empty((k, w.rows), dtype=torch.float32, device=x.device)
     check(lib().fk_gemv_multi(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(x), stride, _ptr(y)))
+    return y
+
+
+def gemv_multi_glu(w, ids, gate, up, act=0, out=None, n_active=None):
+    """Slot j: matrix ids[j] of `w` times act(gate[j]) * up[j] -> out[j] (gate, up: [k, cols])."""
+    ids, gate, up = _i32(ids), _f32(gate), _f32(up)
+    k = ids.numel()
+    assert gate.shape == up.shape and gate.dim() == 2 and gate.shape[0] == k
+    y = out if out is not None else torch.empty((k, w.rows), dtype=torch.float32, device=gate.device)
+    check(lib().fk_gemv_multi_glu(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(gate), _ptr(up), gate.stride(0), int(act), _ptr(y),
+                                  _ptr(_i32(n_active)) if n_active is not None else None))
     return y
 
 
@@ -249,12 +263,14 @@ def glu(gate, up, act=0, out=None):
     return y
 
 
-def moe_combine(y, pair_of, w, batch, k, out=None):
+def moe_combine(y, pair_of, w, batch, k, out=None, accumulate=False):
+    """accumulate: add the combined rows into `out` (the residual stream) instead of overwriting it."""
     y, w = _f32(y), _f32(w)
     n = y.shape[-1]
+    assert not accumulate or out is not None
     o = out if out is not None else torch.empty((batch, n), dtype=torch.float32, device=y.device)
-    check(lib().fk_moe_combine(context(y.device), _stream(), _ptr(y), _ptr(_i32(pair_of)) if pair_of is not None else None,
-                               _ptr(w), batch, k, n, _ptr(o)))
+    fn = lib().fk_moe_combine_add if accumulate else lib().fk_moe_combine
+    check(fn(context(y.device), _stream(), _ptr(y), _ptr(_i32(pair_of)) if pair_of is not None else None, _ptr(w), batch, k, n, _ptr(o)))
     return o
 
 

@@ -46,19 +46,29 @@ def route(layer, x, ops=None):
     return ops.moe_route(logits, layer.k, layer.mode, layer.router_bias)
 
 
-def run_device_routed(layer, x, ops=None):
+def run_device_routed(layer, x, ops=None, residual=None):
     """Decode: one token `x` [hidden] (or a few, [b, hidden], one after another).
-    gate and up are one indexed launch each with the k chosen experts as slots."""
+    gate and up are one indexed launch each with the k chosen experts as slots.
+    residual (same shape as x): the layer's output is added into it instead of returned."""
     ops = _ops(ops)
     if x.dim() == 2:
         import torch
+        if residual is not None:
+            for t in range(x.shape[0]):
+                run_device_routed(layer, x[t], ops, residual[t])
+            return residual
         return torch.stack([run_device_routed(layer, x[t], ops) for t in range(x.shape[0])])
     ids, w = route(layer, x, ops)
     ids1 = ids.reshape(-1)
     g = ops.gemv_multi(layer.gate, ids1, x)
     u = ops.gemv_multi(layer.up, ids1, x)
-    a = ops.glu(g, u, layer.act)
-    y = ops.gemv_multi(layer.down, ids1, a)
+    if hasattr(ops, "gemv_multi_glu"):
+        y = ops.gemv_multi_glu(layer.down, ids1, g, u, layer.act)     # the activation rides in the down projection
+    else:
+        y = ops.gemv_multi(layer.down, ids1, ops.glu(g, u, layer.act))
+    if residual is not None:
+        ops.moe_combine(y, None, w, 1, layer.k, out=residual[None] if residual.dim() == 1 else residual, accumulate=True)
+        return residual
     return ops.moe_combine(y, None, w, 1, layer.k)[0]
 
 

@@ -114,6 +114,11 @@ int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* 
 int fk_gemv_multi(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
                   int x_stride, float* y_dev);
 
+/* fk_gemv_multi reading act(gate[j]) * up[j] instead of x[j] (the down projection of the
+ * chosen experts with `silu_mul_f32` / the gpt-oss activation of src/glu.rs:68 folded
+ * in); n_active_dev may be null (all k slots run). */
+int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* gate_dev, const float* up_dev,
+                      int x_stride, int glu_act, float* y_dev, const int* n_active_dev);
 /* fk_gemv_multi whose slots >= *n_active_dev do nothing (their outputs are left as
  * they are).  Expert-parallel decode runs only the chosen experts a rank owns
  * without a host round trip for the count; no counterpart in the single-device
@@ -181,6 +186,10 @@ int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev
  * y[pair_of[t*k+j]] from zero in routing order (pair_of NULL = identity). */
 int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
                    int batch, int k, int n, float* out_dev);
+/* fk_moe_combine that adds the combined rows into out (the residual stream) instead of
+ * overwriting it; the weighted sum itself is still formed from zero in routing order. */
+int fk_moe_combine_add(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
+                   int batch, int k, int n, float* out_dev);
 
 /* ---- decoder glue (next-row components: enough to run a decoder and report
  * prefill / decode tokens per second; f32 throughout) -------------------------
@@ -197,9 +206,12 @@ int fk_rmsnorm(fk_ctx* ctx, void* stream, float* x_dev, const float* residual_de
 int fk_rope(fk_ctx* ctx, void* stream, float* x_dev, int n_rows, int n_heads, int head_dim, const int* pos_dev, float theta, int neox);
 /* rope of q and k and the KV append of one step in one launch: q [n][n_heads*hd] and
  * k [n][n_kv*hd] are rotated in place (rows at *pos + r), then k and v rows are
- * written to the caches at *pos.  q_ld / kv_ld = floats between rows. */
+ * written to the caches at *pos.  q_ld / kv_ld = floats between rows.  q_norm_dev /
+ * k_norm_dev (both or neither, [head_dim]): the per-head RMSNorm of Qwen3 applied to
+ * q and k ahead of the rotation. */
 int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const float* v_dev, int q_ld, int kv_ld, int n_rows, int n_heads,
-               int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev);
+               int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev,
+               const float* q_norm_dev, const float* k_norm_dev, float norm_eps);
 /* `add_rows_f32` (kernels.rs:70): a += b. */
 int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n);
 /* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */

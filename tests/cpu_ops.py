@@ -73,10 +73,18 @@ def moe_permute(ids, n_experts):
     return torch.from_numpy(off), torch.from_numpy((order // k).astype(np.int32)), torch.from_numpy(pair_of)
 
 
-def moe_combine(y, pair_of, w, batch, k, out=None):
+def moe_combine(y, pair_of, w, batch, k, out=None, accumulate=False):
     ys, ws = y.numpy(), w.numpy().reshape(batch, k)
     po = pair_of.numpy() if pair_of is not None else np.arange(batch * k)
-    return torch.from_numpy(np.stack([fo.combine(ys[po[t * k:(t + 1) * k]], ws[t]) for t in range(batch)]))
+    r = torch.from_numpy(np.stack([fo.combine(ys[po[t * k:(t + 1) * k]], ws[t]) for t in range(batch)]))
+    if accumulate:
+        out.add_(r)
+        return out
+    return r
+
+
+def gemv_multi_glu(w, ids, gate, up, act=0, out=None, n_active=None):
+    return gemv_multi(w, ids, glu(gate, up, act))
 
 
 # ---- the decoder glue, so that `frink_b200.decoder.Decoder` runs on CPU ranks
@@ -147,8 +155,11 @@ def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, gl
     return out
 
 
-def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache):
+def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache, q_norm=None, k_norm=None, eps=0.0):
     qc, kc = q.contiguous(), k.contiguous()
+    if q_norm is not None:
+        qc = rmsnorm(qc.view(-1, head_dim), q_norm, eps).view(qc.shape[0], -1).contiguous()
+        kc = rmsnorm(kc.view(-1, head_dim), k_norm, eps).view(kc.shape[0], -1).contiguous()
     rope(qc, n_heads, head_dim, pos, theta, neox)
     rope(kc, n_kv, head_dim, pos, theta, neox)
     q.copy_(qc)

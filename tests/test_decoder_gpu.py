@@ -107,6 +107,18 @@ def test_rope_kv_strided_attention_and_wide_argmax():
         q1, k1, v1 = buf[:, :hq], buf[:, hq:hq + kvw], buf[:, hq + kvw:]
         device.rope_kv(q1, k1, v1, nh, nkv, hd, pos, 1e4, neox, kc1, vc1)
         assert torch.equal(q1, q0) and torch.equal(k1, k0) and torch.equal(kc1, kc0) and torch.equal(vc1, vc0)
+        # Qwen3's per-head q/k RMSNorm folded into the same launch
+        qn = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda()
+        kn = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda()
+        q2, k2, v2 = (t.contiguous() for t in (qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]))
+        q2 = device.rmsnorm(q2.view(-1, hd), qn, 1e-6).view(n, -1)
+        k2 = device.rmsnorm(k2.view(-1, hd), kn, 1e-6).view(n, -1)
+        kc2, vc2 = kc0.clone(), vc0.clone()
+        device.rope_kv(q2, k2, v2, nh, nkv, hd, pos, 1e4, neox, kc2, vc2)
+        buf3 = qkv.clone()
+        kc3, vc3 = kc0.clone(), vc0.clone()
+        device.rope_kv(buf3[:, :hq], buf3[:, hq:hq + kvw], buf3[:, hq + kvw:], nh, nkv, hd, pos, 1e4, neox, kc3, vc3, q_norm=qn, k_norm=kn, eps=1e-6)
+        assert torch.allclose(buf3[:, :hq], q2, rtol=1e-6, atol=1e-7) and torch.allclose(kc3, kc2, rtol=1e-6, atol=1e-7) and torch.equal(vc3, vc2)
         # a query that is a column slice of a wider buffer
         a0 = device.attention(q0, kc0, vc0, nh, nkv, hd, pos)
         a1 = device.attention(q1, kc1, vc1, nh, nkv, hd, pos)
@@ -163,3 +175,22 @@ def test_small_llama_greedy_tokens_match_the_oracle(uniform):
     # the captured-graph decode loop reproduces the eager one
     dec.reset()
     assert dec.generate(torch.from_numpy(prompt).cuda(), n_new, use_graph=True) == got
+
+
+def test_small_qwen3_moe_decoder_matches_the_cpu_decoder():
+    """A routed model with per-head q/k norms and split-half RoPE: the device decoder (grouped
+    GEMM prefill, indexed-expert fused decode) against the same decoder run on the oracle-backed
+    CPU ops."""
+    from frink_b200.decoder import Decoder
+    from tests import cpu_ops
+    from tests.test_parallel_cpu import _tiny_model
+    cfg, layers, tok, out_norm, head = _tiny_model(True)
+    dev = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=32)
+    cpu = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=32, ops=cpu_ops, device="cpu")
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32)
+    for ids in (prompt, np.array([7], np.int32), np.array([5, 9, 2], np.int32)):
+        got = dev.forward(torch.from_numpy(ids).cuda()).cpu().numpy()
+        want = cpu.forward(torch.from_numpy(ids)).numpy()
+        assert rel_l2(got, want) <= 1e-3, len(ids)
+    from frink_b200 import device
+    assert device.device_error() == 0

@@ -91,3 +91,26 @@ def test_local_slots_and_active_count_for_expert_parallel_decode():
             assert np.array_equal(got[:n], want.cpu().numpy())
         assert np.all(got[n:] == 7.0)
     assert device.device_error() == 0
+
+
+def test_indexed_down_projection_with_glu_and_combine_into_the_residual():
+    """`fk_gemv_multi_glu` = GLU kernel + `fk_gemv_multi`, bit for bit; `fk_moe_combine_add` =
+    residual + `fk_moe_combine`."""
+    from frink_b200 import device
+    n_exp, rows, cols, k = 6, 128, 512, 4
+    raws = np.concatenate([fo.encode(fo.Q4_K, synth_weights(rows, cols, 800 + e)) for e in range(n_exp)])
+    w = device.Weights(raws, fo.Q4_K, rows, cols, n_mats=n_exp)
+    rng = np.random.default_rng(11)
+    ids = torch.tensor([4, 0, 5, 2], dtype=torch.int32).cuda()
+    g = torch.from_numpy(rng.standard_normal((k, cols)).astype(np.float32)).cuda()
+    u = torch.from_numpy(rng.standard_normal((k, cols)).astype(np.float32)).cuda()
+    for act in (0, 1):
+        want = device.gemv_multi(w, ids, device.glu(g, u, act))
+        got = device.gemv_multi_glu(w, ids, g, u, act)
+        assert torch.equal(got, want)
+    wt = torch.from_numpy(rng.random(k).astype(np.float32)).cuda()
+    res = torch.from_numpy(rng.standard_normal((1, rows)).astype(np.float32)).cuda()
+    out = res.clone()
+    device.moe_combine(got, None, wt, 1, k, out=out, accumulate=True)
+    assert torch.equal(out, res + device.moe_combine(got, None, wt, 1, k))
+    assert device.device_error() == 0
