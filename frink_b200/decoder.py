@@ -207,20 +207,15 @@ class Decoder:
         hd, n = cfg.head_dim, ids.numel()
         hq, kvw = self.h_loc * hd, self.kv_loc * hd
         x = ops.get_rows(self.embd, ids)
-        # each matvec asks for the next one's weights to be warmed into L2 while it streams its own
-        wof = lambda d, name: d[name].w if name in d else None
-        for li, L in enumerate(self.layers):
-            nxt = self.layers[li + 1] if li + 1 < len(self.layers) else None
-            after_ffn = (wof(nxt, "qkv") or wof(nxt, "qk") or wof(nxt, "wq")) if nxt is not None else self.head
-            first_ffn = wof(L, "gate_up") or wof(L, "gate")
+        for L in self.layers:
             if "qkv" in L:
-                qkv = ops.gemv_fused(L["qkv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wo"].w)
+                qkv = ops.gemv_fused(L["qkv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 q, k, v = qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]
             elif "qk" in L:
                 # v in another block format (the usual K-quant mix): two matvecs, the norm folded into both
-                qk = ops.gemv_fused(L["qk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wv"].w)
+                qk = ops.gemv_fused(L["qk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 q, k = qk[:, :hq], qk[:, hq:hq + kvw]
-                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, prefetch=L["wo"].w)
+                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
             else:
                 q = ops.gemv_fused(L["wq"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
@@ -228,16 +223,16 @@ class Decoder:
             ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
                         q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
             a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
-            ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True, prefetch=first_ffn)
+            ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True)
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 run_device_routed(L["moe"], h2, ops, residual=x)
             elif "gate_up" in L:
-                gu = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, prefetch=L["down"].w)
-                ops.gemv_fused(L["down"].w, gu[:, :cfg.ffn], glu_up=gu[:, cfg.ffn:], out=x, accumulate=True, prefetch=after_ffn)
+                gu = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps)
+                ops.gemv_fused(L["down"].w, gu[:, :cfg.ffn], glu_up=gu[:, cfg.ffn:], out=x, accumulate=True)
             else:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
-                ops.gemv_fused(L["down"].w, L["gate"](h2), glu_up=L["up"](h2), out=x, accumulate=True, prefetch=after_ffn)
+                ops.gemv_fused(L["down"].w, L["gate"](h2), glu_up=L["up"](h2), out=x, accumulate=True)
         logits = ops.gemv_fused(self.head, x[n - 1:n], norm_weight=self.out_norm, eps=cfg.eps)
         ops.add_int_(self.pos, n)
         return logits

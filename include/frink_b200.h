@@ -102,8 +102,9 @@ int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev,
  * glu_up_dev: the matvec reads act(x) * glu_up, x being the gate (act 0 SiLU, 1 gpt-oss);
  * accumulate != 0: y += W x (the residual add).  x_ld = floats between batch rows of x
  * and glu_up (0 = cols).  next (may be null): the weights the NEXT matvec of the stream
- * will read; this launch asks for up to 48 MB of them to be brought into L2 while it
- * runs, which hides the next launch's start-up behind this one's stream. */
+ * will read; this launch then asks for up to 48 MB of them to be brought into L2 while it
+ * runs.  Measured on B200 in a decode chain this bought nothing (the matvec is bound by
+ * its own start-up, not by where the weights come from), so the decoder here passes null. */
 int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
                   const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next);
 
