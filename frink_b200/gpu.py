@@ -45,34 +45,47 @@ def _ctx():
 
 
 def _host(a, dt):
-    a = np.ascontiguousarray(a, dt)
-    return a, a.ctypes.data_as(C.c_void_p)
+    """A C-contiguous array of dtype `dt` (the input itself when it already is one) and its address."""
+    if not (isinstance(a, np.ndarray) and a.dtype == dt and a.flags.c_contiguous):
+        a = np.ascontiguousarray(a, dt)
+    return a, a.ctypes.data
 
 
-def _launch_matvec(kind, weights, x, rows, row_bytes, n_blocks_per_row):
+_KIND = {}
+_CTX = []
+
+
+def _launch_matvec(kind_name, weights, x, rows, row_bytes, n_blocks_per_row):
+    # the call is ~20 us of GPU work, so the wrapper keeps its own share small: kinds and the
+    # context are looked up once, addresses go over as plain integers
+    kind = _KIND.get(kind_name)
+    if kind is None:
+        kind = _KIND[kind_name] = matvec_kinds.kind_by_name(kind_name)
+    if not _CTX:
+        _CTX.append(_ctx())
     w, wp = _host(weights, np.uint8)
     xv, xp = _host(x, np.float32)
     if xv.size != n_blocks_per_row * kind.block_elems:
         raise _lib.Invalid(f"{kind.fn_name}: x has {xv.size} values, the row has {n_blocks_per_row * kind.block_elems}")
     y = np.empty(rows, np.float32)
-    check(lib().fk_launch_matvec(_ctx(), kind.tag, wp, w.size, xp, rows, row_bytes, n_blocks_per_row, y.ctypes.data_as(C.c_void_p)))
+    check(lib().fk_launch_matvec(_CTX[0], kind.tag, wp, w.size, xp, rows, row_bytes, n_blocks_per_row, y.ctypes.data))
     return y
 
 
 def launch_q4_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
-    return _launch_matvec(matvec_kinds.kind_by_name("Q4_K"), weights, x, rows, row_bytes, n_blocks_per_row)
+    return _launch_matvec("Q4_K", weights, x, rows, row_bytes, n_blocks_per_row)
 
 
 def launch_q6_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
-    return _launch_matvec(matvec_kinds.kind_by_name("Q6_K"), weights, x, rows, row_bytes, n_blocks_per_row)
+    return _launch_matvec("Q6_K", weights, x, rows, row_bytes, n_blocks_per_row)
 
 
 def launch_q8_0_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
-    return _launch_matvec(matvec_kinds.kind_by_name("Q8_0"), weights, x, rows, row_bytes, n_blocks_per_row)
+    return _launch_matvec("Q8_0", weights, x, rows, row_bytes, n_blocks_per_row)
 
 
 def launch_mxfp4_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
-    return _launch_matvec(matvec_kinds.kind_by_name("MXFP4"), weights, x, rows, row_bytes, n_blocks_per_row)
+    return _launch_matvec("MXFP4", weights, x, rows, row_bytes, n_blocks_per_row)
 
 
 @dataclass
