@@ -1158,7 +1158,16 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     a.act_bytes = act;
     const size_t smem = (size_t)act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
     auto kern = gemv_kernel<KIND, NB, DUMP>;
-    FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+    {
+        // raise the kernel's dynamic shared-memory limit only when this launch needs more than any
+        // before it on this device (the call costs about as much as the launch itself)
+        static std::atomic<int> granted[64];
+        const int dev = ctx->device & 63;
+        if ((int)smem > granted[dev].load(std::memory_order_relaxed)) {
+            FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+            granted[dev].store((int)smem, std::memory_order_relaxed);
+        }
+    }
     const int pairs = (a.rows + RS - 1) / RS;
     const int need = (pairs + 3) / 4;   // at least four row groups a block, else the activation quantization dominates
     // a persistent grid: one block per SM, shared out over the slots
@@ -1237,7 +1246,16 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
     a.act_bytes = (int)act;
     const size_t smem = act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
     auto kern = gemv_mma_kernel<KIND>;
-    FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+    {
+        // raise the kernel's dynamic shared-memory limit only when this launch needs more than any
+        // before it on this device (the call costs about as much as the launch itself)
+        static std::atomic<int> granted[64];
+        const int dev = ctx->device & 63;
+        if ((int)smem > granted[dev].load(std::memory_order_relaxed)) {
+            FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+            granted[dev].store((int)smem, std::memory_order_relaxed);
+        }
+    }
     // the activation image lives in the context's scratch block (stream-ordered like its other users)
     const int rcs = fk_ensure_scratch(ctx, (size_t)a.m_red_off);
     if (rcs != FK_OK) return rcs;
