@@ -29,7 +29,7 @@ SYMBOLS = {
     "fk_weight_shape": (_I, [_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_SZ)]),
     "fk_quantize_q8_1": (_I, [_P, _P, _P, _I, _P]),
     "fk_gemv": (_I, [_P, _P, _P, _I, _P, _I, _P]),
-    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
+    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P, _I]),
     "fk_gemv_multi": (_I, [_P, _P, _P, _P, _I, _P, _I, _P]),
     "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),

@@ -124,6 +124,7 @@ struct FkGemvFused {
     int x_ld;
     const uint8_t* pf_ptr;          // L2 prefetch of the next kernel's weights (may be null)
     unsigned long long pf_bytes;
+    int pair_glu;                   // rows are (gate, up) pairs: write act(gate) * up, rows / 2 outputs
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,

@@ -52,6 +52,7 @@ struct GemvArgs {
     const float* glu_up;   // gated activation: the kernel reads act(x) * glu_up, x being the gate
     int glu_act;           // 0 SiLU, 1 the clamped gpt-oss form
     int accumulate;        // y += result instead of y = result
+    int pair_glu;          // rows are (gate, up) pairs: y[rows/2] = act(gate) * up (1 SiLU, 2 the gpt-oss form)
     // bytes the NEXT kernel of the stream will stream (its weights): requested into L2
     // while this kernel runs, so the next one starts on warm lines
     const uint8_t* pf_ptr;
@@ -682,6 +683,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         if (row_done) {
             // Q4_K: a half warp per row pair; the others: the whole warp on one pair
             const int hw = KIND == FK_Q4_K ? lane >> 4 : 0;
+            float done[LR][NB];
 #pragma unroll
             for (int r = 0; r < LR; r++)
 #pragma unroll
@@ -692,12 +694,40 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
                     v += __shfl_xor_sync(0xffffffffu, v, 4);
                     v += __shfl_xor_sync(0xffffffffu, v, 2);
                     v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    const int row = row0 + hw * LR + r;
-                    if ((lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0) && row < rows && b < a.batch) {
-                        float* dst = y + (size_t)b * rows + row;
-                        *dst = a.accumulate ? *dst + v : v;
+                    done[r][b] = v;
+                }
+            const bool writer = (lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0);
+            if (a.pair_glu) {
+                // rows come as (gate, up) pairs (the merged projection was stacked row-interleaved):
+                // the lane holds both, so the gated activation is formed here and written once
+                const int prow = (row0 + hw * LR) >> 1;
+                if (writer && row0 + hw * LR + 1 < rows) {
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        if (b >= a.batch) break;
+                        const float gt = done[0][b], up = done[1][b];
+                        float o;
+                        if (a.pair_glu == 1) {
+                            o = (gt / (1.0f + expf(-gt))) * up;
+                        } else {
+                            const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
+                            o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                        }
+                        y[(size_t)b * (rows >> 1) + prow] = o;
                     }
                 }
+            } else {
+#pragma unroll
+                for (int r = 0; r < LR; r++)
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const int row = row0 + hw * LR + r;
+                        if (writer && row < rows && b < a.batch) {
+                            float* dst = y + (size_t)b * rows + row;
+                            *dst = a.accumulate ? *dst + done[r][b] : done[r][b];
+                        }
+                    }
+            }
         }
         if (++s == a.nstages) { s = 0; phase ^= 1u; }
         if (++kc == a.nchunks) { kc = 0; pair += twarps; }
@@ -1104,12 +1134,32 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArg
         }
         if (kp == 0) {
             const int rg = group * MM_ROWS + g;
+            if (a.pair_glu) {
+                // (gate, up) row pairs sit in neighbouring g, i.e. in lanes 4 apart
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
-                if (row < rows && b < batch) {
-                    float* dst = y + (size_t)b * rows + row;
-                    *dst = a.accumulate ? *dst + acc[i] : acc[i];
+                for (int i = 0; i < 4; i++) {
+                    const float other = __shfl_xor_sync(0xffffffffu, acc[i], 4);
+                    const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
+                    if (!(g & 1) && row + 1 < rows && b < batch) {
+                        const float gt = acc[i], up = other;
+                        float o;
+                        if (a.pair_glu == 1) {
+                            o = (gt / (1.0f + expf(-gt))) * up;
+                        } else {
+                            const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
+                            o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                        }
+                        y[(size_t)b * (rows >> 1) + (row >> 1)] = o;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
+                    if (row < rows && b < batch) {
+                        float* dst = y + (size_t)b * rows + row;
+                        *dst = a.accumulate ? *dst + acc[i] : acc[i];
+                    }
                 }
             }
         }
@@ -1339,6 +1389,7 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.glu_up = fused->glu_up;
         a.glu_act = fused->glu_act;
         a.accumulate = fused->accumulate;
+        a.pair_glu = fused->pair_glu;
         a.pf_ptr = fused->pf_ptr;
         a.pf_bytes = fused->pf_bytes;
         if (fused->x_ld) a.x_ld = fused->x_ld;
@@ -1390,8 +1441,11 @@ FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
 }
 
 FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
-                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next) {
+                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next,
+                            int pair_glu) {
     if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_fused: null argument");
+    if (pair_glu < 0 || pair_glu > 2 || (pair_glu && ((w->rows & 1) || accumulate)))
+        return fk_fail(FK_INVALID, "gemv_fused: pair_glu %d needs an even number of rows and no accumulate", pair_glu);
     if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv_fused: batch %d outside 1..8", batch);
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_fused: matrix %d of %d", mat, w->n_mats);
     if (x_ld == 0) x_ld = w->cols;
@@ -1400,7 +1454,7 @@ FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
         return fk_fail(FK_INVALID, "gemv_fused: inputs must be 16-byte aligned");
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused: activation %d", glu_act);
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, nullptr, 0};
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, nullptr, 0, pair_glu};
     if (next) {
         // at most 48 MB: what stays resident in L2 beside this kernel's own stream
         const size_t total = (size_t)next->n_mats * next->mat_stride, cap = (size_t)48 << 20;
@@ -1427,7 +1481,7 @@ FK_EXPORT int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const in
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_multi_glu: activation %d", glu_act);
     if (((uintptr_t)gate_dev & 15) || ((uintptr_t)up_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_glu: inputs must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, nullptr, 0};
+    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, nullptr, 0, 0};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, gate_dev, x_stride, 1, y_dev, nullptr, n_active_dev, &f);
 }
 

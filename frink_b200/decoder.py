@@ -72,14 +72,24 @@ class _Merged:
     several, as the reference shares one quantized input between q/k/v and gate/up
     (crates/frink-cuda/src/dp4a_launch.rs:56-62).  Returns the outputs as column slices."""
 
-    def __init__(self, ops, parts, kind, cols):
+    def __init__(self, ops, parts, kind, cols, interleave=False):
         import numpy as np
-        self.ops, self.splits = ops, [r for _, r in parts]
-        raw = np.concatenate([np.ascontiguousarray(b, np.uint8).ravel() for b, _ in parts])
+        self.ops, self.splits, self.interleave = ops, [r for _, r in parts], interleave
+        blobs = [np.ascontiguousarray(b, np.uint8).ravel() for b, _ in parts]
+        if interleave:
+            # two projections of equal height, row i of the first then row i of the second: a lane of the
+            # matvec then holds a (gate, up) pair and can write the gated activation itself
+            assert len(parts) == 2 and self.splits[0] == self.splits[1]
+            rows = self.splits[0]
+            raw = np.stack([blobs[0].reshape(rows, -1), blobs[1].reshape(rows, -1)], axis=1).reshape(-1)
+        else:
+            raw = np.concatenate(blobs)
         self.w = ops.Weights(raw, kind, sum(self.splits), cols)
 
     def __call__(self, x):
         y = self.ops.gemv(self.w, x) if x.shape[0] <= 8 else self.ops.gemm(self.w, x)
+        if self.interleave:
+            return [y[:, 0::2], y[:, 1::2]]
         outs, o = [], 0
         for r in self.splits:
             outs.append(y[:, o:o + r] if x.shape[0] == 1 else y[:, o:o + r].contiguous())
@@ -137,7 +147,7 @@ class Decoder:
             else:
                 gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, self.rank, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, self.rank, T)]
                 if k["gate"] == k["up"]:
-                    d["gate_up"] = _Merged(ops, gu, k["gate"], H)
+                    d["gate_up"] = _Merged(ops, gu, k["gate"], H, interleave=True)
                 else:
                     d["gate"] = _Linear(ops, gu[0][0], k["gate"], gu[0][1], H)
                     d["up"] = _Linear(ops, gu[1][0], k["up"], gu[1][1], H)
@@ -228,8 +238,8 @@ class Decoder:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 run_device_routed(L["moe"], h2, ops, residual=x)
             elif "gate_up" in L:
-                gu = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps)
-                ops.gemv_fused(L["down"].w, gu[:, :cfg.ffn], glu_up=gu[:, cfg.ffn:], out=x, accumulate=True)
+                act = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, pair_glu=1)
+                ops.gemv_fused(L["down"].w, act, out=x, accumulate=True)
             else:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 ops.gemv_fused(L["down"].w, L["gate"](h2), glu_up=L["up"](h2), out=x, accumulate=True)

@@ -80,6 +80,12 @@ def test_fused_gemv_equals_the_separate_kernels(kind, batch):
         want = device.gemv(w, device.glu(gu[:, :cols].contiguous(), gu[:, cols:].contiguous(), act))
         got = device.gemv_fused(w, gu[:, :cols], glu_up=gu[:, cols:], glu_act=act)
         assert torch.equal(got, want)
+    # rows read as (gate, up) pairs: the gated activation formed in the epilogue
+    full = device.gemv(w, x)
+    for act in (0, 1):
+        want = device.glu(full[:, 0::2].contiguous(), full[:, 1::2].contiguous(), act)
+        got = device.gemv_fused(w, x, pair_glu=act + 1)
+        assert got.shape == (batch, rows // 2) and torch.equal(got, want)
     res = torch.from_numpy(rng.standard_normal((batch, rows)).astype(np.float32)).cuda()
     out = res.clone()
     device.gemv_fused(w, x, out=out, accumulate=True)
