@@ -212,10 +212,28 @@ __global__ void kv_append_kernel(float* __restrict__ cache, const float* __restr
 // unnormalised output) in the workspace; the block that arrives last for the
 // (row, head) merges them and rewinds the arrival counter.
 constexpr int AD_WARPS = 4, AD_TK = 64, AD_REC = 132, AD_MAX_SPLITS = 64, AD_MAX_CNT = 4096;
+// One decode row with the step's RoPE and cache append folded in (on != 0, one query row):
+// q arrives unrotated and is (normed and) rotated in shared memory; the newest key and value
+// are taken from the projection's output (k_new / v_new), rotated in shared memory by every
+// block whose share of the keys holds that position, and written to the caches by the blocks
+// of the first query head of each KV group.  No block reads that position from the caches.
+struct AttnFuse {
+    const float* k_new;
+    const float* v_new;
+    float* kc;
+    float* vc;
+    const float* q_norm;
+    const float* k_norm;
+    float theta, eps;
+    int neox, on;
+};
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
-            const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt) {
+            const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt, const AttnFuse f) {
     fk_pdl_sync();
+    __shared__ __align__(16) float sk_new[128];
+    __shared__ __align__(16) float sv_new[128];
+    __shared__ double s_red[AD_WARPS];
     __shared__ __align__(16) float sq[128];
     __shared__ float s_p[AD_TK];
     __shared__ __align__(16) float s_acc[AD_WARPS][128];
@@ -229,6 +247,56 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) sq[i] = qr[i];
     __syncthreads();
     const size_t kv_stride = (size_t)n_kv * head_dim;
+    const int p_new = n_keys - 1;
+    const bool has_new = f.on && c0 <= p_new && p_new < c1;
+    if (f.on) {
+        // (head norm and) rotation of one head held in shared memory, at position p_new; same
+        // arithmetic as rope_kv_kernel
+        auto rope_head = [&](float* buf, const float* nw) {
+            float nscale = 1.0f;
+            if (nw) {
+                double sqs = 0.0;
+                for (int i = threadIdx.x; i < head_dim; i += blockDim.x) sqs += (double)(buf[i] * buf[i]);
+                for (int o = 16; o > 0; o >>= 1) sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
+                if (lane == 0) s_red[warp] = sqs;
+                __syncthreads();
+                double tsum = 0.0;
+                for (int i = 0; i < AD_WARPS; i++) tsum += s_red[i];
+                nscale = 1.0f / sqrtf((float)(tsum / (double)head_dim) + f.eps);
+                __syncthreads();
+            }
+            const int half = head_dim >> 1;
+            for (int i = threadIdx.x; i < half; i += blockDim.x) {
+                const float freq = 1.0f / powf(f.theta, (float)(2 * i) / (float)head_dim);
+                float sn, cs;
+                sincosf((float)p_new * freq, &sn, &cs);
+                const int ia = f.neox ? i : 2 * i, ib = f.neox ? i + half : 2 * i + 1;
+                float xa = buf[ia], xb = buf[ib];
+                if (nw) {
+                    xa = xa * nscale * nw[ia];
+                    xb = xb * nscale * nw[ib];
+                }
+                buf[ia] = xa * cs - xb * sn;
+                buf[ib] = xa * sn + xb * cs;
+            }
+            __syncthreads();
+        };
+        rope_head(sq, f.q_norm);
+        if (has_new) {
+            for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+                sk_new[i] = f.k_new[(size_t)kvh * head_dim + i];
+                sv_new[i] = f.v_new[(size_t)kvh * head_dim + i];
+            }
+            __syncthreads();
+            rope_head(sk_new, f.k_norm);
+            if (h % (n_heads / n_kv) == 0) {
+                for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
+                    f.kc[(size_t)p_new * kv_stride + (size_t)kvh * head_dim + i] = sk_new[i];
+                    f.vc[(size_t)p_new * kv_stride + (size_t)kvh * head_dim + i] = sv_new[i];
+                }
+            }
+        }
+    }
     const int hd4 = head_dim >> 2;
     float m = -INFINITY, s = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -241,14 +309,17 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
         for (int jj = 0; jj < AD_TK / AD_WARPS; jj++) {
             const int j = warp + AD_WARPS * jj;
             vv[jj] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (j < nk && owns) vv[jj] = *(const float4*)(vbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim + 4 * lane);
+            if (j < nk && owns)
+                vv[jj] = (has_new && t0 + j == p_new) ? *(const float4*)(sv_new + 4 * lane)
+                                                      : *(const float4*)(vbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim + 4 * lane);
         }
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int j = warp * 16 + i * 4 + (lane >> 3);
             float d = 0.0f;
             if (j < nk) {
-                const float4* kr = (const float4*)(kbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim);
+                const float4* kr = (has_new && t0 + j == p_new) ? (const float4*)sk_new
+                                                                : (const float4*)(kbuf + (size_t)(t0 + j) * kv_stride + (size_t)kvh * head_dim);
 #pragma unroll 4
                 for (int f = sub; f < hd4; f += 8) {
                     const float4 kv = kr[f], qv = *(const float4*)(sq + 4 * f);
@@ -599,9 +670,32 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
         const int rc = fk_ensure_scratch(ctx, (size_t)n_q * n_heads * splits * AD_REC * sizeof(float));
         if (rc != FK_OK) return rc;
         FK_CARVEOUT(attn_kernel);
+        AttnFuse nofuse{};
         FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_q), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, k_dev, v_dev,
-                              n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt), FK_LAUNCH);
+                              n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, nofuse), FK_LAUNCH);
     }
+    FK_LAUNCH_CHECK();
+    return FK_OK;
+}
+
+FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
+                                   float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
+                                   const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev) {
+    if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !k_cache_dev || !v_cache_dev || !pos_dev || !out_dev)
+        return fk_fail(FK_INVALID, "attention_rope_kv: null argument");
+    if (n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > AD_MAX_CNT)
+        return fk_fail(FK_UNSUPPORTED, "attention_rope_kv: %d/%d heads of %d", n_heads, n_kv, head_dim);
+    if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fk_fail(FK_INVALID, "attention_rope_kv: q and k norm weights come together");
+    if (((uintptr_t)q_dev | (uintptr_t)k_new_dev | (uintptr_t)v_new_dev) & 15) return fk_fail(FK_INVALID, "attention_rope_kv: inputs must be 16-byte aligned");
+    FkDeviceGuard g(ctx->device);
+    int splits = 4 * ctx->sm_count / n_heads;
+    splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
+    const int rc = fk_ensure_scratch(ctx, (size_t)n_heads * splits * AD_REC * sizeof(float));
+    if (rc != FK_OK) return rc;
+    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1};
+    FK_CARVEOUT(attn_kernel);
+    FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, 1), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, n_heads * head_dim, (const float*)k_cache_dev,
+                          (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }

@@ -230,9 +230,13 @@ class Decoder:
                 q = ops.gemv_fused(L["wq"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
-            ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
-                        q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
-            a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
+            if n == 1 and hasattr(ops, "attention_rope_kv"):
+                a = ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
+                                          q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
+            else:
+                ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
+                            q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
+                a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
             ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True)
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)

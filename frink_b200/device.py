@@ -328,6 +328,21 @@ def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out
     return o if q.dim() == 2 else o[0]
 
 
+def attention_rope_kv(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv, head_dim, pos, theta, neox=False, q_norm=None, k_norm=None, eps=0.0,
+                      scale=None, out=None):
+    """One decode row: rotate q and the new k at pos[0] (after Qwen3's head norms when given),
+    append k and v to the caches and attend over positions 0 ..= pos[0], in one launch.
+    q [1, n_heads*head_dim], k_new / v_new [1, n_kv*head_dim] (column slices are fine)."""
+    assert q.shape[0] == 1 and q.stride(-1) == 1 and k_new.stride(-1) == 1 and v_new.stride(-1) == 1
+    o = out if out is not None else torch.empty((1, n_heads * head_dim), dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    check(lib().fk_attention_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), n_heads, n_kv,
+                                     head_dim, _ptr(_i32(pos)), sc, float(theta), int(neox),
+                                     _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None,
+                                     float(eps), _ptr(o)))
+    return o
+
+
 def argmax(x, out=None):
     x = _f32(x)
     x2 = x if x.dim() == 2 else x[None]

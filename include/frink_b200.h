@@ -228,6 +228,13 @@ int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_d
  * call in flight per context. */
 int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
                  int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev);
+/* One decode row: fk_rope_kv and fk_attention in one launch.  q [n_heads*head_dim], k_new and
+ * v_new [n_kv*head_dim] are the projection's outputs for the token at *pos (unrotated); the
+ * caches hold positions 0 .. *pos - 1 and receive the rotated k and v at *pos.  q_norm_dev /
+ * k_norm_dev as in fk_rope_kv.  One call in flight per context. */
+int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
+                         float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
+                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev);
 /* Greedy sampling: index of the largest of each row, ties to the lower index; at most
  * 64 rows per call, and one call in flight per context (it uses a workspace of the context). */
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);

@@ -200,3 +200,29 @@ def test_small_qwen3_moe_decoder_matches_the_cpu_decoder():
         assert rel_l2(got, want) <= 1e-3, len(ids)
     from frink_b200 import device
     assert device.device_error() == 0
+
+
+@pytest.mark.parametrize("neox,norms", [(False, False), (True, True)])
+def test_one_row_attention_with_rope_and_cache_append_folded_in(neox, norms):
+    """`fk_attention_rope_kv` against `fk_rope_kv` followed by `fk_attention`: same caches,
+    same output (the key split over blocks is the same, so is the arithmetic per key)."""
+    from frink_b200 import device
+    rng = np.random.default_rng(21)
+    nh, nkv, hd, p0 = 8, 2, 128, 150
+    hq, kvw = nh * hd, nkv * hd
+    qkv = torch.from_numpy(rng.standard_normal((1, hq + 2 * kvw)).astype(np.float32)).cuda()
+    kc = torch.from_numpy(rng.standard_normal((256, kvw)).astype(np.float32)).cuda()
+    vc = torch.from_numpy(rng.standard_normal((256, kvw)).astype(np.float32)).cuda()
+    qn = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda() if norms else None
+    kn = torch.from_numpy((1 + 0.1 * rng.standard_normal(hd)).astype(np.float32)).cuda() if norms else None
+    for pos_v in (p0, 0, 63, 64):
+        pos = torch.tensor([pos_v], dtype=torch.int32).cuda()
+        b0, k0, v0 = qkv.clone(), kc.clone(), vc.clone()
+        device.rope_kv(b0[:, :hq], b0[:, hq:hq + kvw], b0[:, hq + kvw:], nh, nkv, hd, pos, 1e4, neox, k0, v0, q_norm=qn, k_norm=kn, eps=1e-6)
+        want = device.attention(b0[:, :hq], k0, v0, nh, nkv, hd, pos)
+        b1, k1, v1 = qkv.clone(), kc.clone(), vc.clone()
+        got = device.attention_rope_kv(b1[:, :hq], b1[:, hq:hq + kvw], b1[:, hq + kvw:], k1, v1, nh, nkv, hd, pos, 1e4, neox, q_norm=qn, k_norm=kn, eps=1e-6)
+        assert torch.equal(b1, qkv)                                  # the projection's output is left as it was
+        assert torch.allclose(k1, k0, rtol=1e-6, atol=1e-7) and torch.equal(v1, v0)
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), pos_v
+    assert device.device_error() == 0
