@@ -436,7 +436,18 @@ def model_bench(args, rank, world, local):
     from frink_b200 import device
     from frink_b200.decoder import Decoder
     cfg, layers, tok, tok_kind, out_norm = synth_model(args.model, args.layers)
-    dec = Decoder(cfg, layers, tok, tok_kind, out_norm, max_seq=1024)
+    # dense models: tensor parallel; routed models: attention replicated, experts spread over the ranks
+    # (their few KV heads do not divide by 8)
+    try:
+        dec = Decoder(cfg, layers, tok, tok_kind, out_norm, max_seq=1024, dense_parallel=cfg.n_experts == 0)
+    except ValueError as e:
+        # e.g. 3072 columns are 12 super-blocks: a row-split K-quant matrix cannot be cut 8 ways
+        if rank == 0:
+            print(json.dumps({"metric": "pp512_tg128_tok_s", "model": args.model, "n_gpus": world, "unavailable": str(e)}))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     del layers
     S, G = (512, 128) if args.model != "tiny" else (64, 16)
     prompt = torch.from_numpy(np.random.default_rng(0x70C).integers(0, cfg.vocab, S).astype(np.int32)).cuda()
@@ -489,7 +500,7 @@ def model_bench(args, rank, world, local):
         print(json.dumps({
             "metric": "pp512_tg128_tok_s", "model": args.model, "n_gpus": world, "layers": cfg.n_layers,
             "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
-            "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) + ("+ep%d" % world if cfg.n_experts else ""),
+            "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
             "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
             "tokens_head": [int(t.item()) for t in toks[:8]]}))
     if world > 1:

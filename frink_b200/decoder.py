@@ -99,12 +99,18 @@ class _Merged:
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, layers: List[LayerWeights], tok_embd, tok_kind, out_norm, output=None, output_kind=None,
-                 max_seq=1024, ops=None, group=None, device="cuda"):
+                 max_seq=1024, ops=None, group=None, device="cuda", dense_parallel=True):
+        """dense_parallel=False: attention and dense projections are replicated on every rank
+        (no collectives for them) and only the routed experts are sharded over the group --
+        the plan for MoE models whose KV heads do not divide by the number of ranks."""
         if ops is None:
             from . import device as ops
         self.cfg, self.ops, self.group, self.dev = cfg, ops, group, device
         self.rank, self.world = parallel._world(group) if group is not None or torch.distributed.is_initialized() else (0, 1)
-        T = self.world
+        T = self.world if dense_parallel else 1
+        self.t_dense = T
+        r_dense = self.rank if dense_parallel else 0     # replicated: every rank holds shard 0 of 1
+        E = self.world          # ranks the routed experts are spread over
         if cfg.n_heads % T or cfg.n_kv % T:
             raise ValueError(f"{cfg.n_heads}/{cfg.n_kv} heads do not split over {T} ranks")
         self.h_loc, self.kv_loc = cfg.n_heads // T, cfg.n_kv // T
@@ -118,7 +124,7 @@ class Decoder:
             k = L.kinds
             d = {"attn_norm": f32(L.attn_norm), "ffn_norm": f32(L.ffn_norm)}
             # q/k/v (and gate/up) as row shards of this rank, stacked where the formats agree
-            sh = lambda raw, kind, rows: parallel.shard_rows(raw, kind, rows, H, self.rank, T)
+            sh = lambda raw, kind, rows: parallel.shard_rows(raw, kind, rows, H, r_dense, T)
             qkv = [(sh(L.wq, k["wq"], cfg.n_heads * hd), k["wq"]), (sh(L.wk, k["wk"], cfg.n_kv * hd), k["wk"]),
                    (sh(L.wv, k["wv"], cfg.n_kv * hd), k["wv"])]
             if k["wq"] == k["wk"] == k["wv"]:
@@ -137,7 +143,7 @@ class Decoder:
                 d["q_norm"], d["k_norm"] = f32(L.q_norm), f32(L.k_norm)
             if cfg.n_experts:
                 router = f32(L.router)
-                if T == 1:
+                if E == 1:
                     mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
                     d["moe"] = RoutedLayer(router, mk(L.gate, cfg.ffn, H), mk(L.up, cfg.ffn, H), mk(L.down, H, cfg.ffn), k=cfg.top_k,
                                            mode=cfg.route_mode)
@@ -145,7 +151,7 @@ class Decoder:
                     d["ep"] = parallel.ExpertParallelLayer(ops, router, L.gate, L.up, L.down, k["experts"], cfg.n_experts, H, cfg.ffn,
                                                            cfg.top_k, mode=cfg.route_mode, group=group)
             else:
-                gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, self.rank, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, self.rank, T)]
+                gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, r_dense, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, r_dense, T)]
                 if k["gate"] == k["up"]:
                     d["gate_up"] = _Merged(ops, gu, k["gate"], H, interleave=True)
                 else:
@@ -170,7 +176,7 @@ class Decoder:
         ops, cfg = self.ops, self.cfg
         hd = cfg.head_dim
         n = ids.numel()
-        if n <= 8 and self.world == 1 and hasattr(ops, "gemv_fused"):
+        if n <= 8 and self.t_dense == 1 and hasattr(ops, "gemv_fused"):
             return self._forward_fused(ids)
         x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
         pending = None                                      # a block output not yet added to x
@@ -241,6 +247,11 @@ class Decoder:
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 run_device_routed(L["moe"], h2, ops, residual=x)
+            elif "ep" in L:
+                # experts spread over the ranks, everything else replicated: the one collective of the layer
+                h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
+                for t in range(n):
+                    ops.add_(x[t], L["ep"].decode(h2[t]))
             elif "gate_up" in L:
                 act = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, pair_glu=1)
                 ops.gemv_fused(L["down"].w, act, out=x, accumulate=True)

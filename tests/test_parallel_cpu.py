@@ -137,11 +137,12 @@ def _tiny_model(moe):
     return cfg, layers, tok, norm(H), head
 
 
-def _decoder_logits(moe, group_world):
+def _decoder_logits(moe, group_world, dense_parallel=True):
     from frink_b200.decoder import Decoder
     from tests import cpu_ops
     cfg, layers, tok, out_norm, head = _tiny_model(moe)
-    dec = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=32, ops=cpu_ops, device="cpu")
+    dec = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=32, ops=cpu_ops, device="cpu",
+                  dense_parallel=dense_parallel)
     assert dec.world == group_world
     prompt = torch.from_numpy(np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32))
     lg_prefill = dec.forward(prompt).numpy().copy()            # 12 rows: the batched path
@@ -155,6 +156,22 @@ def _decoder_dense_case(rank, world):
 
 def _decoder_moe_case(rank, world):
     return _decoder_logits(True, world)
+
+
+def _decoder_moe_replicated_case(rank, world):
+    return _decoder_logits(True, world, dense_parallel=False)
+
+
+def test_decoder_with_replicated_attention_and_sharded_experts_matches_one_rank():
+    """The plan for routed models on more ranks than KV heads: attention on every rank, experts
+    spread over the ranks.  Prefill (dispatch/combine) and the fused decode path."""
+    want = spawn(_decoder_moe_case, world=1)[0]
+    got = spawn(_decoder_moe_replicated_case, world=2)
+    for r in range(2):
+        for a, b in zip(got[r], want):
+            assert rel_l2(a, b) <= 1e-4
+    for a, b in zip(got[0], got[1]):
+        assert np.array_equal(a, b)
 
 
 @pytest.mark.parametrize("moe", [False, True])
