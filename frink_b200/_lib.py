@@ -42,6 +42,7 @@ SYMBOLS = {
     "fk_router_logits": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
     "fk_moe_permute": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "fk_glu": (_I, [_P, _P, _P, _P, _SZ, _I, _P]),
+    "fk_router_route": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _I, _I, _P, _P, _P]),
     "fk_moe_combine": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "fk_moe_combine_add": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "fk_get_rows": (_I, [_P, _P, _P, _I, _P, _I, _P]),

@@ -51,8 +51,9 @@ FK_EXPORT int fk_init(int device, fk_ctx** out) {
     e = cudaMalloc(&ctx->err_flag, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_ws, 64 * 64 * sizeof(unsigned long long));
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_cnt, 64 * sizeof(unsigned));
-    if (e == cudaSuccess) e = cudaMemset(ctx->argmax_cnt, 0, 64 * sizeof(unsigned));
+    // 64 counters of the argmax rows, then (index 64) the arrival counter of the fused router
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_cnt, 128 * sizeof(unsigned));
+    if (e == cudaSuccess) e = cudaMemset(ctx->argmax_cnt, 0, 128 * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->attn_cnt, 4096 * sizeof(unsigned));
     if (e == cudaSuccess) e = cudaMemset(ctx->attn_cnt, 0, 4096 * sizeof(unsigned));
     if (e != cudaSuccess) {

@@ -11,18 +11,17 @@ constexpr int TOPK_MAX_K = 16;
 // One warp per token.  Selection is by (biased) logit, ties to the lower
 // expert id; weights by `mode` (0 softmax over all, 1 renormalised over the
 // chosen, 2 softmax over the chosen only), written in selection order.
-__global__ void route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n_experts, int k,
-                             int mode, int batch, int* __restrict__ ids_out, float* __restrict__ w_out) {
-    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (t >= batch) return;
+// The whole warp calls this for token t; the logits are read with L2-coherent loads because
+// the fused kernel below reads what other blocks of the same launch have just written.
+__device__ __forceinline__ void route_token(const float* logits, const float* bias, int n_experts, int k, int mode, int t, int lane,
+                                            int* ids_out, float* w_out) {
     const float NEG_INF = __int_as_float(0xff800000);
     const float* lg = logits + (size_t)t * n_experts;
     float v[TOPK_PER_LANE];
 #pragma unroll
     for (int j = 0; j < TOPK_PER_LANE; j++) {
         const int e = lane + 32 * j;
-        v[j] = e < n_experts ? lg[e] + (bias ? bias[e] : 0.0f) : NEG_INF;
+        v[j] = e < n_experts ? __ldcg(lg + e) + (bias ? bias[e] : 0.0f) : NEG_INF;
     }
     float mx = NEG_INF;
 #pragma unroll
@@ -82,6 +81,13 @@ __global__ void route_kernel(const float* __restrict__ logits, const float* __re
         for (int s = 0; s < k; s++) w[s] = w[s] / ts;
 }
 
+__global__ void route_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int n_experts, int k,
+                             int mode, int batch, int* __restrict__ ids_out, float* __restrict__ w_out) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= batch) return;
+    route_token(logits, bias, n_experts, k, mode, t, threadIdx.x & 31, ids_out, w_out);
+}
+
 // logits[t][e] = router[e] . x[t], one warp per (e, t); f32 throughout.
 __global__ void router_logits_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ out,
                                      int rows, int cols) {
@@ -94,6 +100,32 @@ __global__ void router_logits_kernel(const float* __restrict__ w, const float* _
     for (int i = lane; i < cols; i += 32) acc += wr[i] * xt[i];
     acc = fk_warp_sum(acc);
     if (lane == 0) out[(size_t)blockIdx.y * rows + row] = acc;
+}
+
+// router_logits_kernel and route_kernel in one launch: the block that arrives last (a counter
+// of the context, rewound by that block) routes every token, a warp per token.
+__global__ void router_route_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ logits, int rows, int cols,
+                                    const float* __restrict__ bias, int k, int mode, int batch, int* __restrict__ ids_out,
+                                    float* __restrict__ w_out, unsigned* __restrict__ cnt) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row < rows) {
+        const float* wr = w + (size_t)row * cols;
+        const float* xt = x + (size_t)blockIdx.y * cols;
+        float acc = 0.0f;
+        for (int i = lane; i < cols; i += 32) acc += wr[i] * xt[i];
+        acc = fk_warp_sum(acc);
+        if (lane == 0) logits[(size_t)blockIdx.y * rows + row] = acc;
+    }
+    __shared__ bool last;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last = atomicAdd(cnt, 1u) == gridDim.x * gridDim.y - 1;
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (int t = threadIdx.x >> 5; t < batch; t += blockDim.x >> 5) route_token(logits, bias, rows, k, mode, t, lane, ids_out, w_out);
+    if (threadIdx.x == 0) *cnt = 0;
 }
 
 // Stable counting sort of the (token, slot) pairs by expert, in one block.
@@ -239,6 +271,22 @@ FK_EXPORT int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_de
     dim3 grid((n_experts + 7) / 8, batch);
     FK_CARVEOUT(router_logits_kernel);
     router_logits_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(router_dev, x_dev, logits_dev, n_experts, cols);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts, int cols, int batch,
+                              const float* bias_dev, int k, int mode, float* logits_dev, int* ids_dev, float* w_dev) {
+    if (!ctx || !router_dev || !x_dev || !logits_dev || !ids_dev || !w_dev) return fk_fail(FK_INVALID, "router_route: null argument");
+    if (n_experts < 1 || n_experts > 32 * TOPK_PER_LANE) return fk_fail(FK_UNSUPPORTED, "router_route: %d experts (limit %d)", n_experts, 32 * TOPK_PER_LANE);
+    if (k < 1 || k > TOPK_MAX_K || k > n_experts) return fk_fail(FK_UNSUPPORTED, "router_route: k=%d (limit %d, experts %d)", k, TOPK_MAX_K, n_experts);
+    if (mode < 0 || mode > 2 || batch < 1 || batch > 65535 || cols < 1) return fk_fail(FK_INVALID, "router_route: mode %d, batch %d, cols %d", mode, batch, cols);
+    FkDeviceGuard g(ctx->device);
+    dim3 grid((n_experts + 7) / 8, batch);
+    FK_CARVEOUT(router_route_kernel);
+    router_route_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(router_dev, x_dev, logits_dev, n_experts, cols, bias_dev, k, mode, batch, ids_dev, w_dev,
+                                                                ctx->argmax_cnt + 64);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;

@@ -236,6 +236,20 @@ def router_logits(router, x):
     return out
 
 
+def router_route(router, x, k, mode, bias=None):
+    """router_logits followed by moe_route, one launch: (ids [batch, k], weights [batch, k])."""
+    router, x = _f32(router), _f32(x)
+    x2 = x if x.dim() == 2 else x[None]
+    n, e = x2.shape[0], router.shape[0]
+    logits = torch.empty((n, e), dtype=torch.float32, device=x.device)
+    ids = torch.empty((n, k), dtype=torch.int32, device=x.device)
+    w = torch.empty((n, k), dtype=torch.float32, device=x.device)
+    b = _f32(bias) if bias is not None else None
+    check(lib().fk_router_route(context(x.device), _stream(), _ptr(router), _ptr(x2), e, router.shape[1], n, _ptr(b), k, mode, _ptr(logits),
+                                _ptr(ids), _ptr(w)))
+    return ids, w
+
+
 def moe_route(logits, k, mode, bias=None):
     logits = _f32(logits)
     l2 = logits if logits.dim() == 2 else logits[None]

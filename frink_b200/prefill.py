@@ -42,6 +42,8 @@ def _ops(ops):
 def route(layer, x, ops=None):
     """Router logits and top-k: ids [batch, k] int32, weights [batch, k] in routing order."""
     ops = _ops(ops)
+    if hasattr(ops, "router_route") and (x.dim() == 1 or x.shape[0] <= 8):
+        return ops.router_route(layer.router, x, layer.k, layer.mode, layer.router_bias)   # decode: one launch
     logits = ops.router_logits(layer.router, x)
     return ops.moe_route(logits, layer.k, layer.mode, layer.router_bias)
 

@@ -169,6 +169,10 @@ int fk_gemm_grouped(fk_ctx* ctx, void* stream, fk_weight w, const int* group_off
  * (biased) logit then softmax over the chosen (gpt-oss).  Ties -> lower id. */
 int fk_moe_route(fk_ctx* ctx, void* stream, const float* logits_dev, const float* bias_dev, int n_experts,
                  int k, int mode, int batch, int* ids_dev, float* w_dev);
+/* fk_router_logits and fk_moe_route in one launch (the decode step of a routed layer): the
+ * logits are still written (logits_dev [batch][n_experts]); one call in flight per context. */
+int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts, int cols, int batch,
+                    const float* bias_dev, int k, int mode, float* logits_dev, int* ids_dev, float* w_dev);
 /* `router_f32_matvec` (kernels.rs:356-378): logits[t][e] = router[e] . x[t]. */
 int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts,
                      int cols, int batch, float* logits_dev);

@@ -114,3 +114,16 @@ def test_indexed_down_projection_with_glu_and_combine_into_the_residual():
     device.moe_combine(got, None, wt, 1, k, out=out, accumulate=True)
     assert torch.equal(out, res + device.moe_combine(got, None, wt, 1, k))
     assert device.device_error() == 0
+
+
+@pytest.mark.parametrize("n_experts,k,mode,batch", [(128, 8, 1, 1), (64, 6, 0, 3), (128, 4, 2, 8)])
+def test_fused_router_equals_logits_then_route(n_experts, k, mode, batch):
+    from frink_b200 import device
+    rng = np.random.default_rng(n_experts + k)
+    hidden = 2048
+    router = torch.from_numpy((rng.standard_normal((n_experts, hidden)) * 0.05).astype(np.float32)).cuda()
+    x = torch.from_numpy(rng.standard_normal((batch, hidden)).astype(np.float32)).cuda()
+    want_ids, want_w = device.moe_route(device.router_logits(router, x), k, mode)
+    for _ in range(2):      # the second call finds the arrival counter rewound
+        ids, w = device.router_route(router, x, k, mode)
+        assert torch.equal(ids, want_ids) and torch.equal(w, want_w)
