@@ -190,9 +190,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (BASELINE config 2)")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (M = 512 against the three projection shapes)")
     ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
-                    help="whole-model pp512 / tg128 tokens per second (BASELINE configs 3 and 4) instead of the GEMV line")
+                    help="whole-model pp512 / tg128 tokens per second (the Llama-3.2-3B and Qwen3-30B-A3B shapes) instead of the GEMV line")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
     ap.add_argument("--watchdog", type=int, default=0, help="seconds after which all thread stacks are printed and the process exits")
     ap.add_argument("--no-tp-graph", action="store_true", help="--model under torchrun: launch the decode step eagerly instead of replaying a CUDA graph with the collectives captured")
@@ -541,7 +541,7 @@ def int8_peak_tops():
 
 
 def gemm_sweep(m=512, steps=200):
-    """BASELINE config 2: M = 512 tokens against 3072x3072, 8192x3072, 3072x8192
+    """The quantized prefill GEMM sweep: M = 512 tokens against 3072x3072, 8192x3072, 3072x8192
     in Q4_K, Q6_K, Q8_0 (plus MXFP4 on the 2880-wide shapes).  TFLOPS = 2*M*N*K
     over the whole fk_gemm call (activation quantization + plan + MMA kernel),
     CUDA-graph replays over a ring of weight copies larger than L2."""

@@ -59,7 +59,9 @@ def extract(text, name):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_goldens.py <checkout of antonellof/frink>")
+    root = sys.argv[1]
     out = {"source": "antonellof/frink v0.63.0", "tables": {}}
     for rel, names in WANTED.items():
         text = open(os.path.join(root, rel)).read()

@@ -1,6 +1,6 @@
 """The decoder glue and a whole small model against the CPU oracle pipeline:
 each glue kernel on its own, then greedy decoding of a random-init Llama-shaped
-model (the parity-sized stand-in for BASELINE config 3) token for token."""
+model (the parity-sized stand-in for the 3B Llama shape) token for token."""
 import numpy as np
 import pytest
 import torch

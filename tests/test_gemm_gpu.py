@@ -79,7 +79,7 @@ def test_grouped_gemm_matches_oracle(kind):
 
 
 def test_config2_shape_full_size():
-    """BASELINE config 2 cell at full size: M = 512, 8192 x 3072, Q4_K."""
+    """A cell of the prefill sweep at full size: M = 512, 8192 x 3072, Q4_K."""
     from frink_b200 import device
     rows, cols, m = 8192, 3072, 512
     raw = fo.encode(fo.Q4_K, synth_weights(rows, cols, 0x5EED))

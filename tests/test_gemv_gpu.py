@@ -154,7 +154,7 @@ def test_host_buffer_surface_and_errors():
 
 
 def test_config1_shape_q4_k_8192x3072():
-    """BASELINE config 1 at full size: Q4_K 8192 x 3072, batch 1."""
+    """The headline decode shape at full size: Q4_K 8192 x 3072, batch 1."""
     from frink_b200 import device
     raw, x, w = _case(fo.Q4_K, 8192, 3072, 1, 0x5EED)
     got = device.gemv(w, torch.from_numpy(x[0]).cuda()).cpu().numpy()
