@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libfrink_b200.so")
+# FRINK_B200_LIB names another build of the same library (a kernel variant under study)
+LIB_PATH = os.environ.get("FRINK_B200_LIB") or os.path.join(_HERE, "libfrink_b200.so")
 
 FK_OK, FK_DRIVER_INIT, FK_KERNEL, FK_LAUNCH, FK_UNSUPPORTED, FK_COMM, FK_INVALID = range(7)
 
@@ -29,7 +30,7 @@ SYMBOLS = {
     "fk_weight_shape": (_I, [_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_SZ)]),
     "fk_quantize_q8_1": (_I, [_P, _P, _P, _I, _P]),
     "fk_gemv": (_I, [_P, _P, _P, _I, _P, _I, _P]),
-    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P, _I]),
+    "fk_gemv_fused": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _I]),
     "fk_gemv_multi": (_I, [_P, _P, _P, _P, _I, _P, _I, _P]),
     "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),

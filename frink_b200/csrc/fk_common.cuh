@@ -122,8 +122,6 @@ struct FkGemvFused {
     int glu_act;
     int accumulate;
     int x_ld;
-    const uint8_t* pf_ptr;          // L2 prefetch of the next kernel's weights (may be null)
-    unsigned long long pf_bytes;
     int pair_glu;                   // rows are (gate, up) pairs: write act(gate) * up, rows / 2 outputs
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,

@@ -23,15 +23,26 @@
 #include "fk_common.cuh"
 
 #include <cuda.h>
+#include <limits.h>
+#include <stdlib.h>
+#include <algorithm>
 #include <string.h>
 
 namespace {
 
-constexpr int GEMV_THREADS = 512;
+constexpr int GEMV_THREADS = 512;   // the tensor-core form (batches of 3..8): one block per SM
 constexpr int GEMV_WARPS = GEMV_THREADS / 32;
 constexpr int LR = 2;           // weight rows a lane carries at once
 constexpr int MAX_STAGES = 4;
 constexpr int SMEM_BUDGET = 225 * 1024;
+// the general dp4a form: one block of 16 warps per SM
+constexpr int DP_THREADS = GEMV_THREADS;
+constexpr int DP_WARPS = DP_THREADS / 32;
+constexpr int DP_MINB = 1;
+constexpr int DP_SMEM_BUDGET = SMEM_BUDGET;
+// Half an SM's shared memory: what a block of the Q4_K decode kernel may take, so that the blocks
+// of two consecutive launches of a stream are resident on an SM together.
+constexpr int HALF_SM_SMEM = 112 * 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 24;
 constexpr int MMA_MIN_BATCH = 3;   // from this batch on the tensor-core form is used
 
@@ -53,10 +64,10 @@ struct GemvArgs {
     int glu_act;           // 0 SiLU, 1 the clamped gpt-oss form
     int accumulate;        // y += result instead of y = result
     int pair_glu;          // rows are (gate, up) pairs: y[rows/2] = act(gate) * up (1 SiLU, 2 the gpt-oss form)
-    // bytes the NEXT kernel of the stream will stream (its weights): requested into L2
-    // while this kernel runs, so the next one starts on warm lines
-    const uint8_t* pf_ptr;
-    unsigned long long pf_bytes;
+    // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
+    int q_srows;           // rows a stage holds (even)
+    int q_nring;           // stages resident at once
+    int q_sc_off, q_part_off, q_ring_off, q_bar_off;
 #ifdef FK_TRACE
     int trace_slot;
 #endif
@@ -143,6 +154,15 @@ __device__ __forceinline__ int dp4a4(const uint4& a, const int4& b) {
 }
 // Exact int32 -> f32 for |v| < 2^22 on the integer and FP32 pipes (no conversion unit).
 __device__ __forceinline__ float i2f(int v) { return __int_as_float(v + 0x4B400000) - 12582912.0f; }
+// roundf(x / d) bit for bit without a division per element.  x * inv (inv within an ulp of 1 / d)
+// is within 3e-5 of the rounded quotient for |x / d| <= 127, so its nearest integer is the answer
+// unless the product sits within 6e-5 of a half; only then is the quotient itself taken.
+__device__ __forceinline__ int q8_quant(float x, float d, float inv) {
+    const float t = x * inv;
+    const float r = rintf(t);
+    if (!(fabsf(fabsf(t - r) - 0.5f) >= 6.2e-5f) || !(fabsf(t) < 128.5f)) return (int)roundf(x / d);
+    return (int)r;
+}
 // Four E2M1 codes (the four nibbles of the low 16 bits of `w`) to their doubled
 // int8 values {0,1,2,3,4,6,8,12} with sign, one per byte, in nibble order.
 __device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
@@ -411,7 +431,7 @@ extern "C" __attribute__((visibility("default"))) int fk_trace_read(void* host, 
 #endif
 
 template <int KIND, int NB, bool DUMP>
-__global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     TR(0, threadIdx.x == 0);
     const int cols = a.cols, rows = a.rows;
@@ -423,6 +443,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int slot = blockIdx.y;
+    // The slot table (which expert a slot multiplies, how many slots are live) is written by the
+    // previous kernel of the stream, so a launch that has one waits for that kernel before it
+    // reads anything; a plain matvec waits later, with its weights already on their way.
+    const bool dyn = a.ids != nullptr || a.n_active != nullptr;
+    if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (a.n_active && slot >= *a.n_active) return;
     const int mat = a.ids ? a.ids[slot] : a.mat;
     const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
@@ -432,7 +457,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // ---- this warp's ring: stages, then one mbarrier per stage
     const uint32_t sbase = smem_u32(smem);
     const uint32_t ring = sbase + a.act_bytes + warp * (a.nstages * a.stage_bytes);
-    const uint32_t bars = sbase + a.act_bytes + GEMV_WARPS * (a.nstages * a.stage_bytes) + warp * (MAX_STAGES * 8);
+    const uint32_t bars = sbase + a.act_bytes + DP_WARPS * (a.nstages * a.stage_bytes) + warp * (MAX_STAGES * 8);
     if (lane == 0) {
         for (int s = 0; s < a.nstages; s++) mbar_init(bars + 8 * s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -443,7 +468,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // consecutive row groups go to consecutive BLOCKS, so a matrix with fewer groups
     // than warps still spreads over every SM
     const int gwarp = warp * gridDim.x + blockIdx.x;
-    const int twarps = gridDim.x * GEMV_WARPS;
+    const int twarps = gridDim.x * DP_WARPS;
     constexpr int RS = Geo<KIND>::ROWS;               // rows per stage
     const int npairs = (rows + RS - 1) / RS;
     const int my_pairs = gwarp < npairs ? (npairs - gwarp + twarps - 1) / twarps : 0;
@@ -489,44 +514,34 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // queued behind it.  In a chain of matvecs the wait is short (a block only starts
     // once its SM's block of the previous launch has left).  Larger activations keep the
     // other order: weights first, then the wait.
-    constexpr int QU = 4;
+    constexpr int QU = 1024 / DP_THREADS;   // float4 a thread holds per pass: 4096 columns per pass
     const int c4 = cols >> 2, items = NB * c4;
-    const bool early = items <= GEMV_THREADS * QU;
+    const bool early = items <= DP_THREADS * QU;
     float4 v[QU], vn[QU], vu[QU];
     auto load_acts = [&](int base) {
 #pragma unroll
         for (int u = 0; u < QU; u++) {
-            const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+            const int idx = base + u * DP_THREADS + (int)threadIdx.x;
             v[u] = vn[u] = vu[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (idx < items) {
                 const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
                 if (b < a.batch) {
-                    v[u] = __ldg((const float4*)(x + (size_t)b * a.x_ld) + k4);
+                    // x and glu_up may be written by the kernel this one overlaps with: read them past L1
+                    v[u] = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + k4);
                     if (a.norm_w) vn[u] = __ldg((const float4*)a.norm_w + k4);
-                    if (a.glu_up) vu[u] = __ldg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
+                    if (a.glu_up) vu[u] = __ldcg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
                 }
             }
         }
     };
     if (early) {
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (!dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
         load_acts(0);
     }
     const int pre = njobs < a.nstages ? njobs : a.nstages;
     for (int q = 0; q < pre; q++) fill();
-    if (a.pf_bytes && warp == 0) {
-        // this block's share of the next kernel's weights, 16 KB per request
-        constexpr unsigned long long PIECE = 16384;
-        const unsigned long long nblk = (unsigned long long)gridDim.x * gridDim.y, me = (unsigned long long)blockIdx.y * gridDim.x + blockIdx.x;
-        const unsigned long long pieces = (a.pf_bytes + PIECE - 1) / PIECE;
-        for (unsigned long long i = me + (unsigned long long)lane * nblk; i < pieces; i += 32ull * nblk) {
-            const unsigned long long off = i * PIECE;
-            const uint32_t n = (uint32_t)(a.pf_bytes - off < PIECE ? a.pf_bytes - off : PIECE) & ~15u;
-            if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.pf_ptr + off), "r"(n) : "memory");
-        }
-    }
     TR(1, threadIdx.x == 0);
-    if (!early) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!early && !dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     TR(2, threadIdx.x == 0);
 
@@ -534,7 +549,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
     // lanes make a run of 32; all of a thread's loads go out before any is used,
     // so the block pays one L2 round trip, not one per run.
     __shared__ float s_scale[8];
-    __shared__ double s_part[GEMV_WARPS];
+    __shared__ double s_part[DP_WARPS];
     if (a.norm_w) {
         // fused RMSNorm: squares in f32, summed in f64, the mean rounded to f32, 1/sqrtf(mean + eps)
         for (int b = 0; b < a.batch; b++) {
@@ -542,13 +557,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
             if (early) {
 #pragma unroll
                 for (int u = 0; u < QU; u++) {
-                    const int idx = u * GEMV_THREADS + (int)threadIdx.x;
+                    const int idx = u * DP_THREADS + (int)threadIdx.x;
                     if (idx < items && (NB == 1 ? 0 : idx / c4) == b)
                         sq += (double)(v[u].x * v[u].x) + (double)(v[u].y * v[u].y) + (double)(v[u].z * v[u].z) + (double)(v[u].w * v[u].w);
                 }
             } else {
-                for (int i = threadIdx.x; i < c4; i += GEMV_THREADS) {
-                    const float4 t4 = __ldg((const float4*)(x + (size_t)b * a.x_ld) + i);
+                for (int i = threadIdx.x; i < c4; i += DP_THREADS) {
+                    const float4 t4 = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + i);
                     sq += (double)(t4.x * t4.x) + (double)(t4.y * t4.y) + (double)(t4.z * t4.z) + (double)(t4.w * t4.w);
                 }
             }
@@ -557,18 +572,18 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
             __syncthreads();
             if (threadIdx.x == 0) {
                 double t = 0.0;
-                for (int i = 0; i < GEMV_WARPS; i++) t += s_part[i];
+                for (int i = 0; i < DP_WARPS; i++) t += s_part[i];
                 s_scale[b] = 1.0f / sqrtf((float)(t / (double)cols) + a.norm_eps);
             }
             __syncthreads();
         }
     }
     {
-        for (int base = 0; base < items; base += GEMV_THREADS * QU) {
+        for (int base = 0; base < items; base += DP_THREADS * QU) {
             if (!early) load_acts(base);
 #pragma unroll
             for (int u = 0; u < QU; u++) {
-                const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+                const int idx = base + u * DP_THREADS + (int)threadIdx.x;
                 if (idx < items) {
                     const int b = NB == 1 ? 0 : idx / c4;
                     if (b < a.batch) {
@@ -596,8 +611,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
             }
 #pragma unroll
             for (int u = 0; u < QU; u++) {
-                if (base + u * GEMV_THREADS + warp * 32 >= items) continue;   // nothing for this warp here (the same for all its lanes)
-                const int idx = base + u * GEMV_THREADS + (int)threadIdx.x;
+                if (base + u * DP_THREADS + warp * 32 >= items) continue;   // nothing for this warp here (the same for all its lanes)
+                const int idx = base + u * DP_THREADS + (int)threadIdx.x;
                 const bool ok = idx < items;
                 const int b = !ok || NB == 1 ? 0 : idx / c4, k4 = ok ? idx - b * c4 : 0;
                 const int kb = k4 >> 3, quad = k4 & 7;
@@ -646,7 +661,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         }
     }
     TR(10, threadIdx.x == 0);
-    TR(11, threadIdx.x == GEMV_THREADS - 1);
+    TR(11, threadIdx.x == DP_THREADS - 1);
     __syncthreads();
     TR(3, threadIdx.x == 0);
     const Act sm{sq, sd, ss, sb16, cols, nb32};
@@ -731,6 +746,299 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_kernel(const GemvArgs a)
         }
         if (++s == a.nstages) { s = 0; phase ^= 1u; }
         if (++kc == a.nchunks) { kc = 0; pair += twarps; }
+    }
+    TR(6, threadIdx.x == 0);
+    TRMAX(7, lane == 0);
+}
+
+
+// ===========================================================================
+// Q4_K, batch 1..2 (the decode matvec proper).  The launch is bound by the instructions
+// it issues once its weights are prefetched across the launch boundary, so this form
+// spends as few as the format allows:
+//   * a block owns a contiguous range of rows, i.e. one contiguous range of bytes,
+//     fetched stage by stage with a few large bulk copies (one per warp and stage);
+//   * a thread takes a unit = one 144-byte super-block of TWO neighbouring rows: the
+//     eight 6-bit scales and mins of a block are unpacked four at a time with byte-wide
+//     masks, the 64 activations of a quarter block are loaded once for both rows, and a
+//     whole block's sums are scaled by d / dmin once;
+//   * lanes of a warp hold neighbouring super-blocks, 144 bytes apart: their 16-byte
+//     loads fall on different banks as they are; the int8 activations and their run
+//     scales are stored with their 16-byte chunks XOR-swizzled by the super-block so the
+//     same holds for them;
+//   * partial sums of a row meet in shared memory and are added in super-block order,
+//     so the result does not depend on how units fell to threads.
+// The block size is chosen per launch (a multiple of 32 up to 256) so that the units of a
+// stage fill whole rounds of the block.
+#ifndef FK_Q4_THREADS
+#define FK_Q4_THREADS 512
+#endif
+constexpr int Q4_MAX_THREADS = FK_Q4_THREADS;
+__device__ __forceinline__ int q4_act_chunk(int c) { return c ^ ((c >> 4) & 7); }
+// run scales: per super-block 16 floats {d[0..7], d * run sum [0..7]} as four 16-byte chunks
+__device__ __forceinline__ int q4_sc_chunk(int sb, int i) { return 4 * sb + (i ^ ((sb >> 1) & 3)); }
+
+template <int NB, bool DUMP>
+__global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    TR(0, threadIdx.x == 0);
+    const int T = blockDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
+    const int cols = a.cols, rows = a.rows, nb32 = cols >> 5, nsb = cols >> 8;
+    int8_t* sq = (int8_t*)smem;                               // [NB][cols] int8, chunks swizzled
+    float* ssc = (float*)(smem + a.q_sc_off);                  // [NB][nsb][16]
+    float* part = (float*)(smem + a.q_part_off);               // [2][q_srows][nsb][NB]
+    const uint32_t sbase = smem_u32(smem), ring = sbase + a.q_ring_off, bars = sbase + a.q_bar_off;
+    const int slot = blockIdx.y;
+    const bool dyn = a.ids != nullptr || a.n_active != nullptr;
+    if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");   // the slot table is the previous kernel's output
+    if (a.n_active && slot >= *a.n_active) return;
+    const int mat = a.ids ? a.ids[slot] : a.mat;
+    const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
+    const float* x = a.x + (size_t)slot * a.x_stride;
+    float* y = a.y + (size_t)slot * a.batch * rows;
+    const uint32_t rb = (uint32_t)a.plane_stride[0];           // bytes of a row
+    const int S = a.q_srows, nring = a.q_nring;
+    // row pairs dealt evenly over the blocks: every SM gets one block of (nearly) the same size
+    const int npairs = (rows + 1) >> 1;
+    const int row_lo = 2 * (int)(((long long)blockIdx.x * npairs) / gridDim.x);
+    const int row_hi = min(rows, 2 * (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x));
+    const int npass = row_hi > row_lo ? (row_hi - row_lo + S - 1) / S : 0;
+
+    if (tid == 0) {
+        for (int s = 0; s < nring; s++) mbar_init(bars + 8 * s, nwarps);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    TR(8, threadIdx.x == 0);
+    // pass p -> stage p % nring: the rows' bytes in nwarps pieces, one bulk copy per warp
+    auto fill = [&](int p) {
+        if (lane != 0) return;
+        const int r0 = row_lo + p * S;
+        const uint32_t bytes = (uint32_t)min(S, row_hi - r0) * rb;
+        const uint32_t piece = ((bytes + nwarps - 1) / nwarps + 15u) & ~15u;
+        const uint32_t off = min(bytes, warp * piece), n = min(bytes - off, piece);
+        const uint32_t bar = bars + 8 * (p % nring);
+        mbar_expect_tx(bar, n);
+        if (n) bulk_g2s(ring + (p % nring) * (uint32_t)(S * rb) + off, wb + (size_t)r0 * rb + off, n, bar);
+    };
+    const int pre = min(npass, nring);
+    for (int p = 0; p < pre; p++) fill(p);
+    TR(1, threadIdx.x == 0);
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
+    TR(2, threadIdx.x == 0);
+
+    // ---- activations -> q8_1 in shared memory (the rule of fk_q8_1_lane; eight lanes make a run)
+    __shared__ float s_scale[2];
+    __shared__ double s_part[Q4_MAX_THREADS / 32];
+    const int c4 = cols >> 2, items = NB * c4;
+    if (a.norm_w) {
+        for (int b = 0; b < a.batch; b++) {
+            double sqs = 0.0;
+            for (int i = tid; i < c4; i += T) {
+                const float4 t4 = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + i);
+                sqs += (double)(t4.x * t4.x) + (double)(t4.y * t4.y) + (double)(t4.z * t4.z) + (double)(t4.w * t4.w);
+            }
+            for (int o = 16; o > 0; o >>= 1) sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
+            if (lane == 0) s_part[warp] = sqs;
+            __syncthreads();
+            if (tid == 0) {
+                double t = 0.0;
+                for (int i = 0; i < nwarps; i++) t += s_part[i];
+                s_scale[b] = 1.0f / sqrtf((float)(t / (double)cols) + a.norm_eps);
+            }
+            __syncthreads();
+        }
+    }
+    constexpr int QU = 1024 / Q4_MAX_THREADS;
+    for (int base = 0; base < items; base += QU * T) {
+        float4 v[QU], vn[QU], vu[QU];
+#pragma unroll
+        for (int u = 0; u < QU; u++) {
+            const int idx = base + u * T + tid;
+            v[u] = vn[u] = vu[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (idx < items) {
+                const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
+                if (b < a.batch) {
+                    // x and glu_up may be written by the kernel this one overlaps with: read them past L1
+                    v[u] = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + k4);
+                    if (a.norm_w) vn[u] = __ldg((const float4*)a.norm_w + k4);
+                    if (a.glu_up) vu[u] = __ldcg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < QU; u++) {
+            if (base + u * T + warp * 32 >= items) continue;   // nothing for this warp here (the same for all its lanes)
+            const int idx = base + u * T + tid;
+            const bool ok = idx < items;
+            const int b = !ok || NB == 1 ? 0 : idx / c4, k4 = ok ? idx - b * c4 : 0;
+            float4 f = v[u];
+            if (a.norm_w) {
+                const float sc = s_scale[b];
+                f.x = f.x * sc * vn[u].x; f.y = f.y * sc * vn[u].y; f.z = f.z * sc * vn[u].z; f.w = f.w * sc * vn[u].w;
+            }
+            if (a.glu_up) {
+                float g[4] = {f.x, f.y, f.z, f.w};
+                const float uu[4] = {vu[u].x, vu[u].y, vu[u].z, vu[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    if (a.glu_act == 0) {
+                        g[e] = (g[e] / (1.0f + expf(-g[e]))) * uu[e];
+                    } else {
+                        const float xg = fminf(g[e], 7.0f), yu = fminf(fmaxf(uu[e], -7.0f), 7.0f);
+                        g[e] = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                    }
+                }
+                f = make_float4(g[0], g[1], g[2], g[3]);
+            }
+            unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+            mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+            mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+            mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
+            const float amax = __uint_as_float(mb);
+            TR(9, threadIdx.x == 0 && u == 0 && base == 0);
+            const float d = amax / 127.0f;
+            float inv = 0.0f;
+            if (amax != 0.0f) asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(inv) : "f"(d));   // within an ulp of 1 / d (q8_quant wants no more)
+            const int q0 = q8_quant(f.x, d, inv), q1 = q8_quant(f.y, d, inv), q2 = q8_quant(f.z, d, inv), q3 = q8_quant(f.w, d, inv);
+            int qsum = q0 + q1 + q2 + q3;
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+            qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
+            TR(11, threadIdx.x == 0 && u == 0 && base == 0);
+            if (ok) {
+                *(uint32_t*)(sq + (size_t)b * cols + 16 * q4_act_chunk(k4 >> 2) + 4 * (k4 & 3)) =
+                    (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+                if ((k4 & 7) == 0) {
+                    const int kb = k4 >> 3, sb = kb >> 3, j = kb & 7;
+                    const float dq = fk_h2f(fk_f2h(d));   // the stored f16 scale, widened
+                    float* scb = ssc + (size_t)b * nsb * 16;
+                    scb[4 * q4_sc_chunk(sb, j >> 2) + (j & 3)] = dq;
+                    scb[4 * q4_sc_chunk(sb, 2 + (j >> 2)) + (j & 3)] = dq * (float)qsum;
+                }
+            }
+        }
+    }
+    TR(10, threadIdx.x == 0);
+    __syncthreads();
+    TR(3, threadIdx.x == 0);
+
+    for (int p = 0; p < npass; p++) {
+        const int s = p % nring;
+        const uint32_t stage = ring + s * (uint32_t)(S * rb);
+        const int r0 = row_lo + p * S, n = min(S, row_hi - r0);
+        const int units = ((n + 1) >> 1) * nsb;
+        float* pp = part + (size_t)(p & 1) * S * nsb * NB;
+        mbar_wait(bars + 8 * s, (uint32_t)(p / nring) & 1u, a.err);
+        TR(4, threadIdx.x == 0 && p == 0);
+        for (int u = tid; u < units; u += T) {
+            const int rg = u / nsb, sb = u - rg * nsb;
+            const bool two = 2 * rg + 1 < n;
+            const uint32_t blk[2] = {stage + (uint32_t)(2 * rg) * rb + (uint32_t)sb * 144u, stage + (uint32_t)(2 * rg + (two ? 1 : 0)) * rb + (uint32_t)sb * 144u};
+            uint32_t scw[2][2], mnw[2][2];
+            float dd[2], dm[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const uint4 hd = lds16(blk[r]);
+                // 6-bit scales and mins of the 8 sub-blocks, one per byte: [0..3] and [4..7]
+                scw[r][0] = hd.y & 0x3F3F3F3Fu;
+                scw[r][1] = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+                mnw[r][0] = hd.z & 0x3F3F3F3Fu;
+                mnw[r][1] = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+                dd[r] = fk_h2f((uint16_t)(hd.x & 0xFFFF));
+                dm[r] = fk_h2f((uint16_t)(hd.x >> 16));
+            }
+            float accS[2][NB], accM[2][NB];
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++) accS[r][b] = accM[r][b] = 0.0f;
+            const int key = sb & 7, skey = (sb >> 1) & 3;
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                uint32_t w[2][8];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    const uint4 wa = lds16(blk[r] + 16 + 32 * q), wc = lds16(blk[r] + 32 + 32 * q);
+                    w[r][0] = wa.x; w[r][1] = wa.y; w[r][2] = wa.z; w[r][3] = wa.w;
+                    w[r][4] = wc.x; w[r][5] = wc.y; w[r][6] = wc.z; w[r][7] = wc.w;
+                }
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const int8_t* q8 = sq + (size_t)b * cols + sb * 256;
+                    const int4 u0 = *(const int4*)(q8 + 16 * ((4 * q + 0) ^ key)), u1 = *(const int4*)(q8 + 16 * ((4 * q + 1) ^ key)),
+                               u2 = *(const int4*)(q8 + 16 * ((4 * q + 2) ^ key)), u3 = *(const int4*)(q8 + 16 * ((4 * q + 3) ^ key));
+                    const int ulo[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                    const int uhi[8] = {u2.x, u2.y, u2.z, u2.w, u3.x, u3.y, u3.z, u3.w};
+                    // runs 2q, 2q + 1 of this super-block: scale chunk q >> 1 holds d, chunk 2 + (q >> 1) d * run sum
+                    const float* scb = ssc + ((size_t)b * nsb + sb) * 16;
+                    const float2 d8 = *(const float2*)(scb + 4 * ((q >> 1) ^ skey) + 2 * (q & 1));
+                    const float2 s8 = *(const float2*)(scb + 4 * ((2 + (q >> 1)) ^ skey) + 2 * (q & 1));
+#pragma unroll
+                    for (int r = 0; r < 2; r++) {
+                        int il = 0, ih = 0;
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            il = __dp4a((int)(w[r][i] & 0x0F0F0F0Fu), ulo[i], il);
+                            ih = dp4a_us(w[r][i] & 0xF0F0F0F0u, uhi[i], ih);   // 16 x the high-nibble dot
+                        }
+                        ih >>= 4;
+                        // byte 2q & 3 (and the next) of the scale / min words, as floats via the 2^23 trick
+                        const uint32_t scv = scw[r][q >> 1], mnv = mnw[r][q >> 1];
+                        const int lo_sel = (q & 1) ? 0x7652 : 0x7650, hi_sel = (q & 1) ? 0x7653 : 0x7651;
+                        const float fsl = __uint_as_float(__byte_perm(scv, 0x4B000000u, lo_sel)) - 8388608.0f;
+                        const float fsh = __uint_as_float(__byte_perm(scv, 0x4B000000u, hi_sel)) - 8388608.0f;
+                        const float fml = __uint_as_float(__byte_perm(mnv, 0x4B000000u, lo_sel)) - 8388608.0f;
+                        const float fmh = __uint_as_float(__byte_perm(mnv, 0x4B000000u, hi_sel)) - 8388608.0f;
+                        accS[r][b] = fmaf(fsl * d8.x, i2f(il), fmaf(fsh * d8.y, i2f(ih), accS[r][b]));
+                        accM[r][b] = fmaf(fml, s8.x, fmaf(fmh, s8.y, accM[r][b]));
+                        if (DUMP && b == 0 && (r == 0 || two)) {
+                            int32_t* o = a.isums + (size_t)(r0 + 2 * rg + r) * nb32 + sb * 8 + 2 * q;
+                            o[0] = il;
+                            o[1] = ih;
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 2; r++)
+#pragma unroll
+                for (int b = 0; b < NB; b++)
+                    if (r == 0 || two) pp[((size_t)(2 * rg + r) * nsb + sb) * NB + b] = dd[r] * accS[r][b] - dm[r] * accM[r][b];
+        }
+        __syncthreads();
+        TR(5, threadIdx.x == 0 && p == 0);
+        if (p + nring < npass) fill(p + nring);   // every thread is done with the stage
+        // ---- a row's partial sums, in super-block order
+        if (a.pair_glu) {
+            for (int i = tid; i < (n >> 1) * NB; i += T) {
+                const int pr = i / NB, b = i - pr * NB;
+                if (b >= a.batch) continue;
+                float gt = 0.0f, up = 0.0f;
+                for (int k = 0; k < nsb; k++) {
+                    gt += pp[((size_t)(2 * pr) * nsb + k) * NB + b];
+                    up += pp[((size_t)(2 * pr + 1) * nsb + k) * NB + b];
+                }
+                float o;
+                if (a.pair_glu == 1) {
+                    o = (gt / (1.0f + expf(-gt))) * up;
+                } else {
+                    const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
+                    o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
+                }
+                y[(size_t)b * (rows >> 1) + ((r0 >> 1) + pr)] = o;
+            }
+        } else {
+            for (int i = tid; i < n * NB; i += T) {
+                const int rr = i / NB, b = i - rr * NB;
+                if (b >= a.batch) continue;
+                float v = 0.0f;
+                for (int k = 0; k < nsb; k++) v += pp[((size_t)rr * nsb + k) * NB + b];
+                float* dst = y + (size_t)b * rows + r0 + rr;
+                *dst = a.accumulate ? *dst + v : v;
+            }
+        }
     }
     TR(6, threadIdx.x == 0);
     TRMAX(7, lane == 0);
@@ -917,7 +1225,7 @@ __global__ void __launch_bounds__(IMG_THREADS) act_image_kernel(const GemvArgs a
     if (a.norm_w) {
         double sqs = 0.0;
         for (int i = threadIdx.x; i < c4; i += IMG_THREADS) {
-            const float4 v = __ldg((const float4*)x + i);
+            const float4 v = __ldcg((const float4*)x + i);   // past L1: the previous kernel of the stream may have written x while this block was resident
             sqs += (double)(v.x * v.x) + (double)(v.y * v.y) + (double)(v.z * v.z) + (double)(v.w * v.w);
         }
         for (int o = 16; o > 0; o >>= 1) sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
@@ -936,14 +1244,14 @@ __global__ void __launch_bounds__(IMG_THREADS) act_image_kernel(const GemvArgs a
         const bool ok = k4 < c4;
         float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (ok) {
-            v = __ldg((const float4*)x + k4);
+            v = __ldcg((const float4*)x + k4);
             if (a.norm_w) {
                 const float4 nw = __ldg((const float4*)a.norm_w + k4);
                 const float sc = s_scale;
                 v.x = v.x * sc * nw.x; v.y = v.y * sc * nw.y; v.z = v.z * sc * nw.z; v.w = v.w * sc * nw.w;
             }
             if (a.glu_up) {
-                const float4 up = __ldg((const float4*)(a.glu_up + (size_t)b * a.x_ld) + k4);
+                const float4 up = __ldcg((const float4*)(a.glu_up + (size_t)b * a.x_ld) + k4);
                 float gt[4] = {v.x, v.y, v.z, v.w};
                 const float uu[4] = {up.x, up.y, up.z, up.w};
 #pragma unroll
@@ -1169,6 +1477,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArg
     TRMAX(7, lane == 0);
 }
 
+int env_int(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
 size_t act_smem_bytes(int kind, int nb, int cols) {
     size_t s = (size_t)nb * cols + (size_t)nb * (cols / 32) * 4;
     if (kind == FK_Q4_K) s += (size_t)nb * (cols / 32) * 4;
@@ -1188,13 +1501,13 @@ int row_stage_bytes(const fk_weight_s* w, int t) {
 template <int KIND, int NB, bool DUMP>
 int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, int slots) {
     const int act = (int)act_smem_bytes(KIND, NB, a.cols);
-    const int bars = GEMV_WARPS * MAX_STAGES * 8;
-    const int ring_budget = (SMEM_BUDGET - act - bars) / GEMV_WARPS;   // bytes of ring a warp may have
+    const int bars = DP_WARPS * MAX_STAGES * 8;
     const int ntrips = (a.cols + Geo<KIND>::TRIP_COLS - 1) / Geo<KIND>::TRIP_COLS;
     // the largest K chunk that still leaves a ring of two stages (a whole row when it
     // fits): bulk copies pay a fixed cost each, and small ones (a trip of Q6_K's
     // scale planes is 64 and 32 bytes) cost more than the overlap they would buy
     constexpr int RS = Geo<KIND>::ROWS;
+    const int ring_budget = (DP_SMEM_BUDGET - act - bars) / DP_WARPS;   // bytes of ring a warp may have
     int t = ntrips;
     while (t > 1 && 2 * RS * row_stage_bytes<KIND>(w, t) > ring_budget) t--;
     if (ring_budget <= 0 || 2 * RS * row_stage_bytes<KIND>(w, t) > ring_budget)
@@ -1206,7 +1519,7 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     a.nstages = ring_budget / a.stage_bytes;
     if (a.nstages > MAX_STAGES) a.nstages = MAX_STAGES;
     a.act_bytes = act;
-    const size_t smem = (size_t)act + (size_t)GEMV_WARPS * a.nstages * a.stage_bytes + bars;
+    const size_t smem = (size_t)act + (size_t)DP_WARPS * a.nstages * a.stage_bytes + bars;
     auto kern = gemv_kernel<KIND, NB, DUMP>;
     {
         // raise the kernel's dynamic shared-memory limit only when this launch needs more than any
@@ -1226,7 +1539,7 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     dim3 grid((unsigned)(need < per_slot ? need : per_slot), (unsigned)slots);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(GEMV_THREADS);
+    cfg.blockDim = dim3(DP_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -1238,6 +1551,67 @@ int launch_one(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     ctx->launches++;
     return FK_OK;
 }
+
+// Plan and launch of gemv_q4k_kernel; *fits = false (nothing launched) when even two rows a stage
+// do not fit beside the activations, and the caller takes the general kernel.
+template <int NB, bool DUMP>
+int launch_q4k(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, int slots, bool* fits) {
+    *fits = false;
+    const int nsb = a.cols / 256;
+    const size_t rb = w->plane_stride[0];
+    const size_t fixed = (size_t)NB * a.cols + (size_t)NB * nsb * 64 + 64 + 128;   // activations, run scales, barriers, alignment
+    const size_t per_row = rb + 2 * (size_t)nsb * NB * 4;                           // a row's bytes and its partial sums (two buffers)
+    int per_slot = ctx->sm_count / slots;
+    if (per_slot < 1) per_slot = 1;
+    // The block's whole share of the matrix must fit its shared memory (half an SM's when possible,
+    // so that consecutive launches overlap): nothing is then left to request after the start.
+    // Larger matrices amortise their start-up anyway and take the general kernel.
+    int G = 0, S = 0, nring = 0;
+    const int npairs = (a.rows + 1) / 2;
+    for (size_t budget : {(size_t)HALF_SM_SMEM, (size_t)SMEM_BUDGET}) {
+        const int g1 = std::min(per_slot, (npairs + 3) / 4);
+        const int rpb = 2 * ((npairs + g1 - 1) / g1);
+        if (fixed + (size_t)rpb * per_row <= budget) {
+            G = g1; S = rpb; nring = 1;
+            break;
+        }
+    }
+    if (!S) return FK_OK;
+    *fits = true;
+    const int T = Q4_MAX_THREADS;
+    a.q_srows = S;
+    a.q_nring = nring;
+    a.q_sc_off = NB * a.cols;
+    a.q_part_off = a.q_sc_off + NB * nsb * 64;
+    a.q_ring_off = (int)(((size_t)a.q_part_off + 2 * (size_t)S * nsb * NB * 4 + 127) & ~(size_t)127);
+    a.q_bar_off = a.q_ring_off + (int)(nring * S * rb);
+    const size_t smem = (size_t)a.q_bar_off + 64;
+    auto kern = gemv_q4k_kernel<NB, DUMP>;
+    {
+        static std::atomic<int> granted[64];
+        const int dev = ctx->device & 63;
+        if ((int)smem > granted[dev].load(std::memory_order_relaxed)) {
+            FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
+            // all of the SM's L1 as shared memory, or two half-SM blocks do not fit together
+            FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared), FK_KERNEL);
+            granted[dev].store((int)smem, std::memory_order_relaxed);
+        }
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)G, (unsigned)slots);
+    cfg.blockDim = dim3((unsigned)T);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FK_CUDA(cudaLaunchKernelEx(&cfg, kern, a), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
 
 // Plan and launch of the tensor-core form; returns FK_UNSUPPORTED (quietly) when a
 // stage of one unit does not fit, and the caller falls back to the dp4a form.
@@ -1347,6 +1721,11 @@ int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight
         const int rc = launch_mma<KIND>(ctx, st, a, w, &fits);
         if (fits) return rc;
     }
+    if (KIND == FK_Q4_K && a.batch <= 1) {
+        bool fits = false;
+        const int rc = dump ? launch_q4k<1, true>(ctx, st, a, w, slots, &fits) : launch_q4k<1, false>(ctx, st, a, w, slots, &fits);
+        if (fits || rc != FK_OK) return rc;
+    }
     if (dump) return launch_one<KIND, 1, true>(ctx, st, a, w, slots);
     if (a.batch <= 1) return launch_one<KIND, 1, false>(ctx, st, a, w, slots);
     if (a.batch <= 2) return launch_one<KIND, 2, false>(ctx, st, a, w, slots);
@@ -1390,8 +1769,6 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.glu_act = fused->glu_act;
         a.accumulate = fused->accumulate;
         a.pair_glu = fused->pair_glu;
-        a.pf_ptr = fused->pf_ptr;
-        a.pf_bytes = fused->pf_bytes;
         if (fused->x_ld) a.x_ld = fused->x_ld;
     }
     a.w = w->dev;
@@ -1441,8 +1818,7 @@ FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
 }
 
 FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
-                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next,
-                            int pair_glu) {
+                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, int pair_glu) {
     if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_fused: null argument");
     if (pair_glu < 0 || pair_glu > 2 || (pair_glu && ((w->rows & 1) || accumulate)))
         return fk_fail(FK_INVALID, "gemv_fused: pair_glu %d needs an even number of rows and no accumulate", pair_glu);
@@ -1454,13 +1830,7 @@ FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
         return fk_fail(FK_INVALID, "gemv_fused: inputs must be 16-byte aligned");
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused: activation %d", glu_act);
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, nullptr, 0, pair_glu};
-    if (next) {
-        // at most 48 MB: what stays resident in L2 beside this kernel's own stream
-        const size_t total = (size_t)next->n_mats * next->mat_stride, cap = (size_t)48 << 20;
-        f.pf_ptr = next->dev;
-        f.pf_bytes = total < cap ? total : cap;
-    }
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, pair_glu};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
 }
 
@@ -1481,7 +1851,7 @@ FK_EXPORT int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const in
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_multi_glu: activation %d", glu_act);
     if (((uintptr_t)gate_dev & 15) || ((uintptr_t)up_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_glu: inputs must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, nullptr, 0, 0};
+    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, gate_dev, x_stride, 1, y_dev, nullptr, n_active_dev, &f);
 }
 

@@ -120,11 +120,10 @@ def gemv(w, x, mat=0, out=None):
     return y if x.dim() > 1 or out is not None else y[0]
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, prefetch=None, pair_glu=0):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0):
     """gemv with its elementwise neighbours folded in: reads rmsnorm(x) * norm_weight, or
     act(x) * glu_up (x the gate), and/or adds into `out` instead of overwriting it.
     x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4.
-    prefetch: the Weights the next matvec of the stream reads (warmed into L2 meanwhile).
     pair_glu (1 SiLU, 2 gpt-oss): `w` holds gate and up row-interleaved; the result is
     act(gate) * up, [batch, rows / 2]."""
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
@@ -135,7 +134,7 @@ def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, gl
     check(lib().fk_gemv_fused(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
                               _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
                               _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate)),
-                              prefetch.handle if prefetch is not None else None, int(pair_glu)))
+                              int(pair_glu)))
     return y
 
 

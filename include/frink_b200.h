@@ -101,16 +101,12 @@ int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev,
  * norm_weight_dev: the matvec reads rmsnorm(x) * norm_weight (squares summed in f64);
  * glu_up_dev: the matvec reads act(x) * glu_up, x being the gate (act 0 SiLU, 1 gpt-oss);
  * accumulate != 0: y += W x (the residual add).  x_ld = floats between batch rows of x
- * and glu_up (0 = cols).  next (may be null): the weights the NEXT matvec of the stream
- * will read; this launch then asks for up to 48 MB of them to be brought into L2 while it
- * runs.  Measured on B200 in a decode chain this bought nothing (the matvec is bound by
- * its own start-up, not by where the weights come from), so the decoder here passes null.
+ * and glu_up (0 = cols).
  * pair_glu (0 none, 1 SiLU, 2 gpt-oss): the matrix holds gate and up stacked row-interleaved
  * (gate row i, up row i, ...); the launch writes act(gate_i) * up_i, rows / 2 values per
  * batch row, so the down projection reads the activated vector directly. */
 int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
-                  const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, fk_weight next,
-                  int pair_glu);
+                  const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate, int pair_glu);
 
 /* Indexed expert GEMV: the `FX_MULTI` form (kernels.rs:166-179,
  * dp4a_launch.rs:256-314).  Slot j (0 <= j < k) multiplies matrix

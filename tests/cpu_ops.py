@@ -138,7 +138,7 @@ def add_int_(p, v):
     p.add_(v)
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, prefetch=None, pair_glu=0):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0):
     """The fused matvec of the device layer, composed from the separate CPU steps."""
     h = x.clone()
     if norm_weight is not None:
