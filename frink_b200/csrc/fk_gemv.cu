@@ -65,8 +65,7 @@ struct GemvArgs {
     int accumulate;        // y += result instead of y = result
     int pair_glu;          // rows are (gate, up) pairs: y[rows/2] = act(gate) * up (1 SiLU, 2 the gpt-oss form)
     // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
-    int q_srows;           // rows a stage holds (even)
-    int q_nring;           // stages resident at once
+    int q_lp;              // row pairs a warp tile spans (32, 16 or 8; the rest of the lanes span super-blocks)
     int q_sc_off, q_part_off, q_ring_off, q_bar_off;
 #ifdef FK_TRACE
     int trace_slot;
@@ -753,30 +752,28 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
 
 
 // ===========================================================================
-// Q4_K, batch 1..2 (the decode matvec proper).  The launch is bound by the instructions
-// it issues once its weights are prefetched across the launch boundary, so this form
-// spends as few as the format allows:
-//   * a block owns a contiguous range of rows, i.e. one contiguous range of bytes,
-//     fetched stage by stage with a few large bulk copies (one per warp and stage);
-//   * a thread takes a unit = one 144-byte super-block of TWO neighbouring rows: the
-//     eight 6-bit scales and mins of a block are unpacked four at a time with byte-wide
-//     masks, the 64 activations of a quarter block are loaded once for both rows, and a
-//     whole block's sums are scaled by d / dmin once;
-//   * lanes of a warp hold neighbouring super-blocks, 144 bytes apart: their 16-byte
-//     loads fall on different banks as they are; the int8 activations and their run
-//     scales are stored with their 16-byte chunks XOR-swizzled by the super-block so the
-//     same holds for them;
-//   * partial sums of a row meet in shared memory and are added in super-block order,
-//     so the result does not depend on how units fell to threads.
-// The block size is chosen per launch (a multiple of 32 up to 256) so that the units of a
-// stage fill whole rounds of the block.
+// Q4_K, batch 1 (the decode matvec proper), for matrices whose share per SM fits a block's
+// shared memory.  Once its weights are prefetched across the launch boundary the launch is
+// bound by the instructions it issues and the shared-memory wavefronts it makes, so this
+// form spends as few of both as the format allows:
+//   * a block owns a contiguous range of row pairs and requests ALL of it at its start
+//     (one bulk copy per row pair); the block takes half an SM, so the block of the next
+//     launch of the stream is resident beside it and has its weights in flight while this
+//     one computes (programmatic stream serialization);
+//   * a thread takes a unit = one 144-byte super-block of the two rows of a pair: the eight
+//     6-bit scales and mins of a block are unpacked four at a time with byte-wide masks, the
+//     64 activations of a quarter block are loaded once for both rows, and a block's sums
+//     are scaled by d / dmin once;
+//   * the lanes of a warp hold DIFFERENT row pairs of the SAME super-block(s): their
+//     activation loads are broadcasts (half the wavefronts of distinct addresses), and the
+//     row pairs sit 16 bytes more than a multiple of 128 apart, so the weight loads of
+//     eight neighbouring lanes fall on different banks;
+//   * partial sums of a row meet in shared memory and are added in super-block order, so
+//     the result does not depend on how units fell to threads.
 #ifndef FK_Q4_THREADS
 #define FK_Q4_THREADS 512
 #endif
 constexpr int Q4_MAX_THREADS = FK_Q4_THREADS;
-__device__ __forceinline__ int q4_act_chunk(int c) { return c ^ ((c >> 4) & 7); }
-// run scales: per super-block 16 floats {d[0..7], d * run sum [0..7]} as four 16-byte chunks
-__device__ __forceinline__ int q4_sc_chunk(int sb, int i) { return 4 * sb + (i ^ ((sb >> 1) & 3)); }
 
 template <int NB, bool DUMP>
 __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvArgs a) {
@@ -784,10 +781,10 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     TR(0, threadIdx.x == 0);
     const int T = blockDim.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
     const int cols = a.cols, rows = a.rows, nb32 = cols >> 5, nsb = cols >> 8;
-    int8_t* sq = (int8_t*)smem;                               // [NB][cols] int8, chunks swizzled
-    float* ssc = (float*)(smem + a.q_sc_off);                  // [NB][nsb][16]
-    float* part = (float*)(smem + a.q_part_off);               // [2][q_srows][nsb][NB]
-    const uint32_t sbase = smem_u32(smem), ring = sbase + a.q_ring_off, bars = sbase + a.q_bar_off;
+    int8_t* sq = (int8_t*)smem;                               // [NB][cols] int8
+    float* ssc = (float*)(smem + a.q_sc_off);                  // [NB][nsb][16]: per super-block d[0..7], d * run sum [0..7]
+    float* part = (float*)(smem + a.q_part_off);               // [block rows][nsb][NB]
+    const uint32_t sbase = smem_u32(smem), ring = sbase + a.q_ring_off, bar = sbase + a.q_bar_off;
     const int slot = blockIdx.y;
     const bool dyn = a.ids != nullptr || a.n_active != nullptr;
     if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");   // the slot table is the previous kernel's output
@@ -797,32 +794,27 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     const float* x = a.x + (size_t)slot * a.x_stride;
     float* y = a.y + (size_t)slot * a.batch * rows;
     const uint32_t rb = (uint32_t)a.plane_stride[0];           // bytes of a row
-    const int S = a.q_srows, nring = a.q_nring;
+    const uint32_t ps = 2 * rb + 16;                           // bytes between row pairs in shared memory
     // row pairs dealt evenly over the blocks: every SM gets one block of (nearly) the same size
     const int npairs = (rows + 1) >> 1;
-    const int row_lo = 2 * (int)(((long long)blockIdx.x * npairs) / gridDim.x);
-    const int row_hi = min(rows, 2 * (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x));
-    const int npass = row_hi > row_lo ? (row_hi - row_lo + S - 1) / S : 0;
+    const int pair_lo = (int)(((long long)blockIdx.x * npairs) / gridDim.x);
+    const int pair_hi = (int)(((long long)(blockIdx.x + 1) * npairs) / gridDim.x);
+    const int np = pair_hi - pair_lo, row_lo = 2 * pair_lo, n = min(rows, 2 * pair_hi) - row_lo;
 
     if (tid == 0) {
-        for (int s = 0; s < nring; s++) mbar_init(bars + 8 * s, nwarps);
+        mbar_init(bar, nwarps);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
     TR(8, threadIdx.x == 0);
-    // pass p -> stage p % nring: the rows' bytes in nwarps pieces, one bulk copy per warp
-    auto fill = [&](int p) {
-        if (lane != 0) return;
-        const int r0 = row_lo + p * S;
-        const uint32_t bytes = (uint32_t)min(S, row_hi - r0) * rb;
-        const uint32_t piece = ((bytes + nwarps - 1) / nwarps + 15u) & ~15u;
-        const uint32_t off = min(bytes, warp * piece), n = min(bytes - off, piece);
-        const uint32_t bar = bars + 8 * (p % nring);
-        mbar_expect_tx(bar, n);
-        if (n) bulk_g2s(ring + (p % nring) * (uint32_t)(S * rb) + off, wb + (size_t)r0 * rb + off, n, bar);
-    };
-    const int pre = min(npass, nring);
-    for (int p = 0; p < pre; p++) fill(p);
+    if (lane == 0) {
+        // this warp's row pairs: warp, warp + nwarps, ...
+        uint32_t total = 0;
+        for (int p = warp; p < np; p += nwarps) total += (uint32_t)min(2, n - 2 * p) * rb;
+        mbar_expect_tx(bar, total);
+        for (int p = warp; p < np; p += nwarps)
+            bulk_g2s(ring + (uint32_t)p * ps, wb + (size_t)(row_lo + 2 * p) * rb, (uint32_t)min(2, n - 2 * p) * rb, bar);
+    }
     TR(1, threadIdx.x == 0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (!dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -908,14 +900,14 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
             qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
             TR(11, threadIdx.x == 0 && u == 0 && base == 0);
             if (ok) {
-                *(uint32_t*)(sq + (size_t)b * cols + 16 * q4_act_chunk(k4 >> 2) + 4 * (k4 & 3)) =
+                *(uint32_t*)(sq + (size_t)b * cols + 4 * k4) =
                     (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
                 if ((k4 & 7) == 0) {
-                    const int kb = k4 >> 3, sb = kb >> 3, j = kb & 7;
+                    const int kb = k4 >> 3;
                     const float dq = fk_h2f(fk_f2h(d));   // the stored f16 scale, widened
-                    float* scb = ssc + (size_t)b * nsb * 16;
-                    scb[4 * q4_sc_chunk(sb, j >> 2) + (j & 3)] = dq;
-                    scb[4 * q4_sc_chunk(sb, 2 + (j >> 2)) + (j & 3)] = dq * (float)qsum;
+                    float* scb = ssc + ((size_t)b * nsb + (kb >> 3)) * 16 + (kb & 7);
+                    scb[0] = dq;
+                    scb[8] = dq * (float)qsum;
                 }
             }
         }
@@ -924,126 +916,122 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     __syncthreads();
     TR(3, threadIdx.x == 0);
 
-    for (int p = 0; p < npass; p++) {
-        const int s = p % nring;
-        const uint32_t stage = ring + s * (uint32_t)(S * rb);
-        const int r0 = row_lo + p * S, n = min(S, row_hi - r0);
-        const int units = ((n + 1) >> 1) * nsb;
-        float* pp = part + (size_t)(p & 1) * S * nsb * NB;
-        mbar_wait(bars + 8 * s, (uint32_t)(p / nring) & 1u, a.err);
-        TR(4, threadIdx.x == 0 && p == 0);
-        for (int u = tid; u < units; u += T) {
-            const int rg = u / nsb, sb = u - rg * nsb;
-            const bool two = 2 * rg + 1 < n;
-            const uint32_t blk[2] = {stage + (uint32_t)(2 * rg) * rb + (uint32_t)sb * 144u, stage + (uint32_t)(2 * rg + (two ? 1 : 0)) * rb + (uint32_t)sb * 144u};
-            uint32_t scw[2][2], mnw[2][2];
-            float dd[2], dm[2];
+    // ---- units.  A warp tile is LP row pairs x (32 / LP) super-blocks; tiles go round the warps.
+    const int LP = a.q_lp, LS = 32 / LP;
+    const int ptiles = (np + LP - 1) / LP, stiles = (nsb + LS - 1) / LS;
+    const int lp = lane % LP, ls = lane / LP;
+    mbar_wait(bar, 0u, a.err);
+    TR(4, threadIdx.x == 0);
+    for (int wt = warp; wt < ptiles * stiles; wt += nwarps) {
+        const int pt = wt / stiles, stl = wt - pt * stiles;
+        const int pr = pt * LP + lp, sb = stl * LS + ls;
+        if (pr >= np || sb >= nsb) continue;
+        const bool two = 2 * pr + 1 < n;
+        const uint32_t blk0 = ring + (uint32_t)pr * ps + (uint32_t)sb * 144u;
+        const uint32_t blk[2] = {blk0, two ? blk0 + rb : blk0};
+        uint32_t scw[2][2], mnw[2][2];
+        float dd[2], dm[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const uint4 hd = lds16(blk[r]);
+            // 6-bit scales and mins of the 8 sub-blocks, one per byte: [0..3] and [4..7]
+            scw[r][0] = hd.y & 0x3F3F3F3Fu;
+            scw[r][1] = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
+            mnw[r][0] = hd.z & 0x3F3F3F3Fu;
+            mnw[r][1] = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
+            dd[r] = fk_h2f((uint16_t)(hd.x & 0xFFFF));
+            dm[r] = fk_h2f((uint16_t)(hd.x >> 16));
+        }
+        float accS[2][NB], accM[2][NB];
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++) accS[r][b] = accM[r][b] = 0.0f;
+        // a quarter block (sub-blocks 2q, 2q + 1) per trip; rolled, so the loop body stays in the instruction cache
+#pragma unroll 1
+        for (int q = 0; q < 4; q++) {
+            uint32_t w[2][8];
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                const uint4 hd = lds16(blk[r]);
-                // 6-bit scales and mins of the 8 sub-blocks, one per byte: [0..3] and [4..7]
-                scw[r][0] = hd.y & 0x3F3F3F3Fu;
-                scw[r][1] = (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u);
-                mnw[r][0] = hd.z & 0x3F3F3F3Fu;
-                mnw[r][1] = ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u);
-                dd[r] = fk_h2f((uint16_t)(hd.x & 0xFFFF));
-                dm[r] = fk_h2f((uint16_t)(hd.x >> 16));
+                const uint4 wa = lds16(blk[r] + 16 + 32 * q), wc = lds16(blk[r] + 32 + 32 * q);
+                w[r][0] = wa.x; w[r][1] = wa.y; w[r][2] = wa.z; w[r][3] = wa.w;
+                w[r][4] = wc.x; w[r][5] = wc.y; w[r][6] = wc.z; w[r][7] = wc.w;
             }
-            float accS[2][NB], accM[2][NB];
+            // bytes 2 (q & 1), 2 (q & 1) + 1 of the scale / min words of sub-blocks 4 (q >> 1) ..
+            const uint32_t sel = (q & 1) ? 0x7652u : 0x7650u;
 #pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++) accS[r][b] = accM[r][b] = 0.0f;
-            const int key = sb & 7, skey = (sb >> 1) & 3;
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                uint32_t w[2][8];
+            for (int b = 0; b < NB; b++) {
+                const int8_t* q8 = sq + (size_t)b * cols + sb * 256 + 64 * q;
+                const int4 u0 = *(const int4*)q8, u1 = *(const int4*)(q8 + 16), u2 = *(const int4*)(q8 + 32), u3 = *(const int4*)(q8 + 48);
+                const int ulo[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                const int uhi[8] = {u2.x, u2.y, u2.z, u2.w, u3.x, u3.y, u3.z, u3.w};
+                const float* scb = ssc + ((size_t)b * nsb + sb) * 16 + 2 * q;
+                const float2 d8 = *(const float2*)scb, s8 = *(const float2*)(scb + 8);
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                    const uint4 wa = lds16(blk[r] + 16 + 32 * q), wc = lds16(blk[r] + 32 + 32 * q);
-                    w[r][0] = wa.x; w[r][1] = wa.y; w[r][2] = wa.z; w[r][3] = wa.w;
-                    w[r][4] = wc.x; w[r][5] = wc.y; w[r][6] = wc.z; w[r][7] = wc.w;
-                }
+                    int il = 0, ih = 0;
 #pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const int8_t* q8 = sq + (size_t)b * cols + sb * 256;
-                    const int4 u0 = *(const int4*)(q8 + 16 * ((4 * q + 0) ^ key)), u1 = *(const int4*)(q8 + 16 * ((4 * q + 1) ^ key)),
-                               u2 = *(const int4*)(q8 + 16 * ((4 * q + 2) ^ key)), u3 = *(const int4*)(q8 + 16 * ((4 * q + 3) ^ key));
-                    const int ulo[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-                    const int uhi[8] = {u2.x, u2.y, u2.z, u2.w, u3.x, u3.y, u3.z, u3.w};
-                    // runs 2q, 2q + 1 of this super-block: scale chunk q >> 1 holds d, chunk 2 + (q >> 1) d * run sum
-                    const float* scb = ssc + ((size_t)b * nsb + sb) * 16;
-                    const float2 d8 = *(const float2*)(scb + 4 * ((q >> 1) ^ skey) + 2 * (q & 1));
-                    const float2 s8 = *(const float2*)(scb + 4 * ((2 + (q >> 1)) ^ skey) + 2 * (q & 1));
-#pragma unroll
-                    for (int r = 0; r < 2; r++) {
-                        int il = 0, ih = 0;
-#pragma unroll
-                        for (int i = 0; i < 8; i++) {
-                            il = __dp4a((int)(w[r][i] & 0x0F0F0F0Fu), ulo[i], il);
-                            ih = dp4a_us(w[r][i] & 0xF0F0F0F0u, uhi[i], ih);   // 16 x the high-nibble dot
-                        }
-                        ih >>= 4;
-                        // byte 2q & 3 (and the next) of the scale / min words, as floats via the 2^23 trick
-                        const uint32_t scv = scw[r][q >> 1], mnv = mnw[r][q >> 1];
-                        const int lo_sel = (q & 1) ? 0x7652 : 0x7650, hi_sel = (q & 1) ? 0x7653 : 0x7651;
-                        const float fsl = __uint_as_float(__byte_perm(scv, 0x4B000000u, lo_sel)) - 8388608.0f;
-                        const float fsh = __uint_as_float(__byte_perm(scv, 0x4B000000u, hi_sel)) - 8388608.0f;
-                        const float fml = __uint_as_float(__byte_perm(mnv, 0x4B000000u, lo_sel)) - 8388608.0f;
-                        const float fmh = __uint_as_float(__byte_perm(mnv, 0x4B000000u, hi_sel)) - 8388608.0f;
-                        accS[r][b] = fmaf(fsl * d8.x, i2f(il), fmaf(fsh * d8.y, i2f(ih), accS[r][b]));
-                        accM[r][b] = fmaf(fml, s8.x, fmaf(fmh, s8.y, accM[r][b]));
-                        if (DUMP && b == 0 && (r == 0 || two)) {
-                            int32_t* o = a.isums + (size_t)(r0 + 2 * rg + r) * nb32 + sb * 8 + 2 * q;
-                            o[0] = il;
-                            o[1] = ih;
-                        }
+                    for (int i = 0; i < 8; i++) {
+                        il = __dp4a((int)(w[r][i] & 0x0F0F0F0Fu), ulo[i], il);
+                        ih = dp4a_us(w[r][i] & 0xF0F0F0F0u, uhi[i], ih);   // 16 x the high-nibble dot
+                    }
+                    ih >>= 4;
+                    // scale and min bytes as floats: 2^23 + byte, minus 2^23
+                    const uint32_t scv = (q & 2) ? scw[r][1] : scw[r][0], mnv = (q & 2) ? mnw[r][1] : mnw[r][0];
+                    const float fsl = __uint_as_float(__byte_perm(scv, 0x4B000000u, sel)) - 8388608.0f;
+                    const float fsh = __uint_as_float(__byte_perm(scv, 0x4B000000u, sel + 1)) - 8388608.0f;
+                    const float fml = __uint_as_float(__byte_perm(mnv, 0x4B000000u, sel)) - 8388608.0f;
+                    const float fmh = __uint_as_float(__byte_perm(mnv, 0x4B000000u, sel + 1)) - 8388608.0f;
+                    accS[r][b] = fmaf(fsl * d8.x, i2f(il), fmaf(fsh * d8.y, i2f(ih), accS[r][b]));
+                    accM[r][b] = fmaf(fml, s8.x, fmaf(fmh, s8.y, accM[r][b]));
+                    if (DUMP && b == 0 && (r == 0 || two)) {
+                        int32_t* o = a.isums + (size_t)(row_lo + 2 * pr + r) * nb32 + sb * 8 + 2 * q;
+                        o[0] = il;
+                        o[1] = ih;
                     }
                 }
             }
-#pragma unroll
-            for (int r = 0; r < 2; r++)
-#pragma unroll
-                for (int b = 0; b < NB; b++)
-                    if (r == 0 || two) pp[((size_t)(2 * rg + r) * nsb + sb) * NB + b] = dd[r] * accS[r][b] - dm[r] * accM[r][b];
         }
-        __syncthreads();
-        TR(5, threadIdx.x == 0 && p == 0);
-        if (p + nring < npass) fill(p + nring);   // every thread is done with the stage
-        // ---- a row's partial sums, in super-block order
-        if (a.pair_glu) {
-            for (int i = tid; i < (n >> 1) * NB; i += T) {
-                const int pr = i / NB, b = i - pr * NB;
-                if (b >= a.batch) continue;
-                float gt = 0.0f, up = 0.0f;
-                for (int k = 0; k < nsb; k++) {
-                    gt += pp[((size_t)(2 * pr) * nsb + k) * NB + b];
-                    up += pp[((size_t)(2 * pr + 1) * nsb + k) * NB + b];
-                }
-                float o;
-                if (a.pair_glu == 1) {
-                    o = (gt / (1.0f + expf(-gt))) * up;
-                } else {
-                    const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
-                    o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
-                }
-                y[(size_t)b * (rows >> 1) + ((r0 >> 1) + pr)] = o;
+#pragma unroll
+        for (int r = 0; r < 2; r++)
+#pragma unroll
+            for (int b = 0; b < NB; b++)
+                if (r == 0 || two) part[((size_t)(2 * pr + r) * nsb + sb) * NB + b] = dd[r] * accS[r][b] - dm[r] * accM[r][b];
+    }
+    __syncthreads();
+    TR(5, threadIdx.x == 0);
+    // ---- a row's partial sums, in super-block order
+    if (a.pair_glu) {
+        for (int i = tid; i < (n >> 1) * NB; i += T) {
+            const int pr = i / NB, b = i - pr * NB;
+            if (b >= a.batch) continue;
+            float gt = 0.0f, up = 0.0f;
+            for (int k = 0; k < nsb; k++) {
+                gt += part[((size_t)(2 * pr) * nsb + k) * NB + b];
+                up += part[((size_t)(2 * pr + 1) * nsb + k) * NB + b];
             }
-        } else {
-            for (int i = tid; i < n * NB; i += T) {
-                const int rr = i / NB, b = i - rr * NB;
-                if (b >= a.batch) continue;
-                float v = 0.0f;
-                for (int k = 0; k < nsb; k++) v += pp[((size_t)rr * nsb + k) * NB + b];
-                float* dst = y + (size_t)b * rows + r0 + rr;
-                *dst = a.accumulate ? *dst + v : v;
+            float o;
+            if (a.pair_glu == 1) {
+                o = (gt / (1.0f + expf(-gt))) * up;
+            } else {
+                const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
+                o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
             }
+            y[(size_t)b * (rows >> 1) + (pair_lo + pr)] = o;
+        }
+    } else {
+        for (int i = tid; i < n * NB; i += T) {
+            const int rr = i / NB, b = i - rr * NB;
+            if (b >= a.batch) continue;
+            float v = 0.0f;
+            for (int k = 0; k < nsb; k++) v += part[((size_t)rr * nsb + k) * NB + b];
+            float* dst = y + (size_t)b * rows + row_lo + rr;
+            *dst = a.accumulate ? *dst + v : v;
         }
     }
     TR(6, threadIdx.x == 0);
     TRMAX(7, lane == 0);
 }
-
 
 // ===========================================================================
 // Batches of 3..8: the per-run integer dots on the int8 tensor-core instruction
@@ -1559,32 +1547,34 @@ int launch_q4k(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     *fits = false;
     const int nsb = a.cols / 256;
     const size_t rb = w->plane_stride[0];
-    const size_t fixed = (size_t)NB * a.cols + (size_t)NB * nsb * 64 + 64 + 128;   // activations, run scales, barriers, alignment
-    const size_t per_row = rb + 2 * (size_t)nsb * NB * 4;                           // a row's bytes and its partial sums (two buffers)
+    const size_t fixed = (size_t)NB * a.cols + (size_t)NB * nsb * 64 + 64 + 128;   // activations, run scales, barrier, alignment
+    const size_t per_pair = 2 * rb + 16 + 2 * (size_t)nsb * NB * 4;                 // a row pair's bytes (padded) and its partial sums
     int per_slot = ctx->sm_count / slots;
     if (per_slot < 1) per_slot = 1;
     // The block's whole share of the matrix must fit its shared memory (half an SM's when possible,
     // so that consecutive launches overlap): nothing is then left to request after the start.
     // Larger matrices amortise their start-up anyway and take the general kernel.
-    int G = 0, S = 0, nring = 0;
     const int npairs = (a.rows + 1) / 2;
-    for (size_t budget : {(size_t)HALF_SM_SMEM, (size_t)SMEM_BUDGET}) {
-        const int g1 = std::min(per_slot, (npairs + 3) / 4);
-        const int rpb = 2 * ((npairs + g1 - 1) / g1);
-        if (fixed + (size_t)rpb * per_row <= budget) {
-            G = g1; S = rpb; nring = 1;
-            break;
-        }
-    }
-    if (!S) return FK_OK;
+    const int G = std::min(per_slot, (npairs + 3) / 4);
+    const int ppb = (npairs + G - 1) / G;      // most row pairs a block gets
+    size_t budget = 0;
+    for (size_t b : {(size_t)HALF_SM_SMEM, (size_t)SMEM_BUDGET})
+        if (!budget && fixed + (size_t)ppb * per_pair <= b) budget = b;
+    if (!budget) return FK_OK;
     *fits = true;
     const int T = Q4_MAX_THREADS;
-    a.q_srows = S;
-    a.q_nring = nring;
+    // lanes of a warp over row pairs (the rest over super-blocks): the split that leaves fewest lanes idle
+    int lp = 32, best = INT_MAX;
+    for (int c : {32, 16, 8}) {
+        const int ls = 32 / c, tiles = ((ppb + c - 1) / c) * ((nsb + ls - 1) / ls);
+        const int rounds = (tiles + T / 32 - 1) / (T / 32);
+        if (rounds < best) { best = rounds; lp = c; }
+    }
+    a.q_lp = lp;
     a.q_sc_off = NB * a.cols;
     a.q_part_off = a.q_sc_off + NB * nsb * 64;
-    a.q_ring_off = (int)(((size_t)a.q_part_off + 2 * (size_t)S * nsb * NB * 4 + 127) & ~(size_t)127);
-    a.q_bar_off = a.q_ring_off + (int)(nring * S * rb);
+    a.q_ring_off = (int)(((size_t)a.q_part_off + 2 * (size_t)ppb * nsb * NB * 4 + 127) & ~(size_t)127);
+    a.q_bar_off = a.q_ring_off + (int)((size_t)ppb * (2 * rb + 16));
     const size_t smem = (size_t)a.q_bar_off + 64;
     auto kern = gemv_q4k_kernel<NB, DUMP>;
     {
@@ -1611,7 +1601,6 @@ int launch_q4k(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
     ctx->launches++;
     return FK_OK;
 }
-
 
 // Plan and launch of the tensor-core form; returns FK_UNSUPPORTED (quietly) when a
 // stage of one unit does not fit, and the caller falls back to the dp4a form.
