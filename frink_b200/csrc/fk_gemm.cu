@@ -66,6 +66,7 @@ struct GemmArgs {
     const int* n_tiles_dev;   // grouped: number of live token tiles (nullptr = all of gridDim.y)
     const int* out_row;       // padded token row -> output row, -1 = padding
     float* out;
+    int32_t* isums;           // test hook: the raw accumulators, [token][rows][cols / run] (nullptr = off)
     int* err;
 };
 
@@ -97,6 +98,10 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* er
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -327,7 +332,7 @@ __device__ __forceinline__ void store_raw(const RawRow<KIND>& raw, int r, uint8_
     }
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool DUMP>
 __global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_dx,
             const __grid_constant__ CUtensorMap map_sx, const __grid_constant__ CUtensorMap map_w) {
@@ -430,6 +435,15 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                     const int kb_n = c == 0 ? kb : kb + 1, c_n = c ^ 1;
                     if (kb_n < nkb) issue(kb_n, c_n, nxt);
                     const uint32_t dxs = sdx_s + (uint32_t)(j * BN + chalf * CW + c * 16) * 4u;
+                    if (DUMP && row_ok) {
+                        // the exact integers of this run, before any scale touches them
+                        const int orow_d = KIND == FK_Q6_K ? wrow0 + (r >> 1) : wrow0 + r;
+                        const int nruns = KIND == FK_Q6_K ? a.cols >> 4 : nkb, run = KIND == FK_Q6_K ? 2 * kb + (r & 1) : kb;
+                        for (int i = 0; i < 16; i++) {
+                            const int dst = a.out_row[tok0 + chalf * CW + c * 16 + i];
+                            if (dst >= 0) a.isums[((size_t)dst * a.rows + orow_d) * nruns + run] = (int32_t)cur[i];
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < 16; i += 4) {
                         const float4 dx = lds128(dxs + 4u * i);
@@ -538,7 +552,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap map_q, const _
                 tma_load_2d(sa + S::A_BYTES, &map_q, st * KSTAGE, tok0, full_b(s));
                 tma_load_2d(sa + S::A_BYTES + S::B_BYTES, &map_dx, tok0, 4 * st, full_b(s));
                 if (KIND == FK_Q4_K) tma_load_2d(sa + S::A_BYTES + S::B_BYTES + S::DX_BYTES, &map_sx, tok0, 4 * st, full_b(s));
-                if (KIND == FK_Q8_0) tma_load_2d(sa, &map_w, st * KSTAGE, wrow0, full_b(s));
+                if (KIND == FK_Q8_0) tma_load_3d(sa, &map_w, st * KSTAGE, wrow0, mat, full_b(s));   // [matrix][row][k]: rows past a matrix's end read as zeros
             }
         }
     } else {
@@ -673,12 +687,26 @@ int make_map(CUtensorMap* map, CUtensorMapDataType dt, int esize, void* base, ui
     return FK_OK;
 }
 
+// The int8 plane of a stack of Q8_0 matrices as a [n_mats][rows][cols] tensor, box [1][BM][KSTAGE].
+int make_map_q8_0(CUtensorMap* map, const fk_weight_s* w) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return fk_fail(FK_DRIVER_INIT, "gemm: the driver does not export cuTensorMapEncodeTiled");
+    cuuint64_t dims[3] = {(cuuint64_t)w->cols, (cuuint64_t)w->rows, (cuuint64_t)w->n_mats};
+    cuuint64_t strides[2] = {(cuuint64_t)w->plane_stride[0], (cuuint64_t)w->mat_stride};
+    cuuint32_t box[3] = {(cuuint32_t)KSTAGE, (cuuint32_t)BM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w->dev + w->plane_off[0], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fk_fail(FK_LAUNCH, "gemm: cuTensorMapEncodeTiled failed (%d) for %d Q8_0 matrices of %d x %d", (int)r, w->n_mats, w->rows, w->cols);
+    return FK_OK;
+}
+
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool DUMP = false>
 int launch_gemm(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorMap& mq, const CUtensorMap& mdx, const CUtensorMap& msx,
                 const CUtensorMap& mw, int n_token_tiles) {
-    auto kern = gemm_kernel<KIND, BN>;
+    auto kern = gemm_kernel<KIND, BN, DUMP>;
     constexpr int SMEM = Smem<BN>::TOTAL;
     FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM), FK_KERNEL);
     constexpr int WROWS = KIND == FK_Q6_K ? BM / 2 : BM;
@@ -692,6 +720,14 @@ int launch_gemm(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorM
 template <int BN>
 int launch_by_kind(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtensorMap& mq, const CUtensorMap& mdx, const CUtensorMap& msx,
                    const CUtensorMap& mw, int n_token_tiles) {
+    if (a.isums && BN == 128) {
+        switch (a.kind) {
+            case FK_Q4_K: return launch_gemm<FK_Q4_K, 128, true>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+            case FK_Q6_K: return launch_gemm<FK_Q6_K, 128, true>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+            case FK_Q8_0: return launch_gemm<FK_Q8_0, 128, true>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+            case FK_MXFP4: return launch_gemm<FK_MXFP4, 128, true>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
+        }
+    }
     switch (a.kind) {
         case FK_Q4_K: return launch_gemm<FK_Q4_K, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
         case FK_Q6_K: return launch_gemm<FK_Q6_K, BN>(ctx, st, a, mq, mdx, msx, mw, n_token_tiles);
@@ -703,7 +739,7 @@ int launch_by_kind(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtens
 
 // Shared body of fk_gemm (group_off == nullptr) and fk_gemm_grouped.
 int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* group_off, const int* gather, const float* x,
-                int n_tokens, float* out) {
+                int n_tokens, float* out, int32_t* isums = nullptr) {
     const bool grouped = group_off != nullptr;
     const int bn = grouped ? 64 : 128;
     const int n_tiles_max = grouped ? (n_tokens + bn - 1) / bn + w->n_mats : (n_tokens + bn - 1) / bn;
@@ -743,12 +779,7 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
     if ((rc = make_map(&mdx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
     if ((rc = make_map(&msx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
     mw = mq;
-    if (w->kind == FK_Q8_0) {
-        // the int8 plane of ONE matrix as a [rows][cols] tensor: rows past the end read as zeros
-        if (grouped) return fk_fail(FK_UNSUPPORTED, "gemm_grouped: stacked Q8_0 experts are not wired to the TMA weight path yet");
-        if ((rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->dev + (size_t)mat * w->mat_stride + w->plane_off[0], w->cols, w->rows,
-                           KSTAGE, BM, CU_TENSOR_MAP_SWIZZLE_128B))) return rc;
-    }
+    if (w->kind == FK_Q8_0 && (rc = make_map_q8_0(&mw, w))) return rc;
     GemmArgs a;
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
@@ -761,6 +792,7 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
     a.n_tiles_dev = grouped ? n_tiles : nullptr;
     a.out_row = out_row;
     a.out = out;
+    a.isums = isums;
     a.err = ctx->err_flag;
     return grouped ? launch_by_kind<64>(ctx, st, a, mq, mdx, msx, mw, n_tiles_max) : launch_by_kind<128>(ctx, st, a, mq, mdx, msx, mw, n_tiles_max);
 }
@@ -784,6 +816,14 @@ FK_EXPORT int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const flo
     if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemm: matrix %d of %d", mat, w->n_mats);
     FkDeviceGuard g(ctx->device);
     return gemm_common(ctx, (cudaStream_t)stream, w, mat, nullptr, nullptr, x_dev, m, out_dev);
+}
+
+FK_EXPORT int fk_gemm_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev, int32_t* isums_dev) {
+    if (!ctx || !w || !x_dev || !out_dev || !isums_dev) return fk_fail(FK_INVALID, "gemm_isums: null argument");
+    if (m < 1) return fk_fail(FK_INVALID, "gemm_isums: m=%d", m);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemm_isums: matrix %d of %d", mat, w->n_mats);
+    FkDeviceGuard g(ctx->device);
+    return gemm_common(ctx, (cudaStream_t)stream, w, mat, nullptr, nullptr, x_dev, m, out_dev, isums_dev);
 }
 
 FK_EXPORT int fk_gemm_grouped(fk_ctx* ctx, void* stream, fk_weight w, const int* group_off_dev, const int* gather_dev,
@@ -864,10 +904,7 @@ FK_EXPORT int fk_gemm_static(fk_ctx* ctx, void* stream, fk_weight w, int mat, co
     if ((rc = make_map(&mdx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
     if ((rc = make_map(&msx, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, sx, n_pad, nkb, bn, 4, CU_TENSOR_MAP_SWIZZLE_NONE))) return rc;
     mw = mq;
-    if (w->kind == FK_Q8_0 &&
-        (rc = make_map(&mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->dev + (size_t)mat * w->mat_stride + w->plane_off[0], w->cols, w->rows, KSTAGE,
-                       BM, CU_TENSOR_MAP_SWIZZLE_128B)))
-        return rc;
+    if (w->kind == FK_Q8_0 && (rc = make_map_q8_0(&mw, w))) return rc;
     GemmArgs a;
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
@@ -880,6 +917,7 @@ FK_EXPORT int fk_gemm_static(fk_ctx* ctx, void* stream, fk_weight w, int mat, co
     a.n_tiles_dev = nullptr;
     a.out_row = out_row;
     a.out = out_dev;
+    a.isums = nullptr;
     a.err = ctx->err_flag;
     return launch_by_kind<128>(ctx, st, a, mq, mdx, msx, mw, n_tiles);
 }

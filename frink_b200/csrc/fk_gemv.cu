@@ -158,9 +158,10 @@ __device__ __forceinline__ float i2f(int v) { return __int_as_float(v + 0x4B4000
 // unless the product sits within 6e-5 of a half; only then is the quotient itself taken.
 __device__ __forceinline__ int q8_quant(float x, float d, float inv) {
     const float t = x * inv;
-    const float r = rintf(t);
+    const float tm = t + 12582912.0f;   // 1.5 * 2^23: the sum is t rounded to an integer, which its low mantissa bits hold
+    const float r = tm - 12582912.0f;
     if (!(fabsf(fabsf(t - r) - 0.5f) >= 6.2e-5f) || !(fabsf(t) < 128.5f)) return (int)roundf(x / d);
-    return (int)r;
+    return __float_as_int(tm) - 0x4B400000;
 }
 // Four E2M1 codes (the four nibbles of the low 16 bits of `w`) to their doubled
 // int8 values {0,1,2,3,4,6,8,12} with sign, one per byte, in nibble order.
@@ -907,7 +908,7 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
                     const float dq = fk_h2f(fk_f2h(d));   // the stored f16 scale, widened
                     float* scb = ssc + ((size_t)b * nsb + (kb >> 3)) * 16 + (kb & 7);
                     scb[0] = dq;
-                    scb[8] = dq * (float)qsum;
+                    scb[8] = dq * i2f(qsum);
                 }
             }
         }

@@ -204,6 +204,16 @@ def gemm(w, x, mat=0, out=None):
     return y
 
 
+def gemm_isums(w, x, mat=0):
+    """(out, isums): `gemm` plus the exact int32 dot of every run, [m, rows, cols / run]."""
+    x = _f32(x)
+    run = 16 if w.kind == 14 else 32
+    y = torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
+    isums = torch.empty((x.shape[0], w.rows, w.cols // run), dtype=torch.int32, device=x.device)
+    check(lib().fk_gemm_isums(w._ctx, _stream(), w.handle, mat, _ptr(x), x.shape[0], _ptr(y), _ptr(isums)))
+    return y, isums
+
+
 def gemm_static(w, x, mat=0, out=None):
     """`gemm` through the entry point that allocates nothing on the device: its
     scratch is a fixed block inside the library, so it can be used where device

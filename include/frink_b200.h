@@ -139,6 +139,12 @@ int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* 
  * out_dev[t * rows + r] = W[mat][r] . q8_1(x_dev[t * cols ..]),  0 <= t < m. */
 int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev);
 
+/* Test hook, the GEMM's counterpart of fk_gemv_isums (the reference's GEMM twins expose the
+ * same integers, crates/frink-cuda/src/mmq/mod.rs:230-432): fk_gemm that also writes the
+ * exact int32 dot of every run of 32 activations (16 for Q6_K) as the tensor cores
+ * delivered it, before any scale: isums_dev is [m][rows][cols / run]. */
+int fk_gemm_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev, int32_t* isums_dev);
+
 /* fk_gemm for callers that cannot allocate device memory when they need it (a
  * thread inside a stream capture, a serving loop that must avoid cudaMalloc's
  * device-wide synchronisation, a process on a fixed memory budget).  It has no

@@ -2,7 +2,11 @@
 matmul is the f64 dequantize-then-dot of the q8_1-rounded activation (what the
 device kernels read), RMSNorm sums f32 squares in f64
 (crates/frink-core/src/matmul.rs:87-95), RoPE as
-crates/frink-cuda/src/prefill/kernels.rs:402, causal GQA softmax in f64.  TEST ONLY."""
+crates/frink-cuda/src/prefill/kernels.rs:402, causal GQA softmax in f64; routed
+layers as crates/frink-moe/src/lib.rs:567 (route), :1068 (run_expert), :1246 (combine
+from zero in routing order); Qwen3's per-head q/k RMSNorm ahead of the rotation
+(crates/frink-core/src/matmul.rs:63).  Written against the reference's graph, not
+against frink_b200.decoder: it shares no code with the device decoder.  TEST ONLY."""
 import numpy as np
 
 from oracle import frink_oracle as fo
@@ -56,6 +60,9 @@ class OracleDecoder:
             q = lin(k["wq"], L.wq, c.n_heads * hd, H, h)
             kk = lin(k["wk"], L.wk, c.n_kv * hd, H, h)
             v = lin(k["wv"], L.wv, c.n_kv * hd, H, h)
+            if c.qk_norm:
+                q = rmsnorm(q.reshape(-1, hd), np.asarray(L.q_norm, np.float32), c.eps).reshape(n, -1)
+                kk = rmsnorm(kk.reshape(-1, hd), np.asarray(L.k_norm, np.float32), c.eps).reshape(n, -1)
             q = rope(q, c.n_heads, hd, self.pos, c.rope_theta, c.neox)
             kk = rope(kk, c.n_kv, hd, self.pos, c.rope_theta, c.neox)
             self.k[li] = np.concatenate([self.k[li], kk])
@@ -73,6 +80,9 @@ class OracleDecoder:
                     a[r, hh * hd:(hh + 1) * hd] = (p @ V / p.sum()).astype(np.float32)
             x = (x + lin(k["wo"], L.wo, H, c.n_heads * hd, a)).astype(np.float32)
             h2 = rmsnorm(x, np.asarray(L.ffn_norm, np.float32), c.eps)
+            if c.n_experts:
+                x = (x + self.routed(L, h2)).astype(np.float32)
+                continue
             g = lin(k["gate"], L.gate, c.ffn, H, h2)
             u = lin(k["up"], L.up, c.ffn, H, h2)
             act = fo.silu_mul(g.ravel(), u.ravel()).reshape(g.shape)
@@ -82,12 +92,34 @@ class OracleDecoder:
         self.pos += n
         return logits
 
-    def generate(self, prompt, n_new):
+    def routed(self, L, h):
+        """Router logits in f32, top-k with ties to the lower id, every chosen expert's SwiGLU FFN,
+        weighted sum from zero in routing order."""
+        c = self.cfg
+        H, F, kind = c.hidden, c.ffn, L.kinds["experts"]
+        logits = (h.astype(np.float32) @ np.asarray(L.router, np.float32).T).astype(np.float32)
+        ids, w = fo.route_top_k(logits, c.top_k, c.route_mode)
+        pg, pd = F * fo.row_bytes(kind, H), H * fo.row_bytes(kind, F)
+        gate, up, down = (np.ascontiguousarray(t, np.uint8).ravel() for t in (L.gate, L.up, L.down))
+        out = np.zeros((h.shape[0], H), np.float32)
+        for t in range(h.shape[0]):
+            ys = []
+            for e in ids[t]:
+                g = lin(kind, gate[e * pg:(e + 1) * pg], F, H, h[t:t + 1])[0]
+                u = lin(kind, up[e * pg:(e + 1) * pg], F, H, h[t:t + 1])[0]
+                ys.append(lin(kind, down[e * pd:(e + 1) * pd], H, F, fo.silu_mul(g, u)[None])[0])
+            out[t] = fo.combine(np.stack(ys), w[t])
+        return out
+
+    def generate(self, prompt, n_new, margins=None):
         out = []
         logits = self.forward(prompt)
         for _ in range(n_new):
             t = int(np.argmax(logits))
             out.append(t)
+            if margins is not None:      # gap between the chosen logit and the runner-up, relative to the logits' spread
+                top2 = np.partition(logits, -2)[-2:]
+                margins.append(float((top2[1] - top2[0]) / max(float(np.std(logits)), 1e-30)))
             if len(out) < n_new:
                 logits = self.forward([t])
         return out

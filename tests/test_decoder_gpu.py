@@ -183,6 +183,107 @@ def test_small_llama_greedy_tokens_match_the_oracle(uniform):
     assert dec.generate(torch.from_numpy(prompt).cuda(), n_new, use_graph=True) == got
 
 
+def recipe_llama(seed=7):
+    """A Llama-shaped model small enough for the f64 oracle, quantized with the Q4_K_M recipe
+    (crates/frink-cli/src/quantize/recipe.rs `use_more_bits`: Q6_K for attn_v and ffn_down on the
+    layers the rule names, Q4_K elsewhere, a Q6_K embedding)."""
+    from frink_b200.decoder import DecoderConfig, LayerWeights
+    cfg = DecoderConfig(n_layers=4, hidden=1024, n_heads=8, n_kv=2, head_dim=128, ffn=2816, vocab=4096)
+    rng = np.random.default_rng(seed)
+    H, hd, n = cfg.hidden, cfg.head_dim, cfg.n_layers
+    more = lambda i: i < n // 8 or i >= 7 * n // 8 or (i - n // 8) % 3 == 2
+    layers = []
+    for li in range(n):
+        hi = fo.Q6_K if more(li) else fo.Q4_K
+        kd = {"wq": fo.Q4_K, "wk": fo.Q4_K, "wv": hi, "wo": fo.Q4_K, "gate": fo.Q4_K, "up": fo.Q4_K, "down": hi}
+        enc = lambda name, r, c, s: fo.encode(kd[name], (rng.standard_normal((r, c)) * s).astype(np.float32))
+        layers.append(LayerWeights(
+            attn_norm=1 + 0.1 * rng.standard_normal(H), wq=enc("wq", cfg.n_heads * hd, H, 0.02), wk=enc("wk", cfg.n_kv * hd, H, 0.02),
+            wv=enc("wv", cfg.n_kv * hd, H, 0.02), wo=enc("wo", H, cfg.n_heads * hd, 0.02), ffn_norm=1 + 0.1 * rng.standard_normal(H),
+            gate=enc("gate", cfg.ffn, H, 0.02), up=enc("up", cfg.ffn, H, 0.02), down=enc("down", H, cfg.ffn, 0.02), kinds=kd))
+    assert [L.kinds["down"] for L in layers] == [fo.Q4_K, fo.Q4_K, fo.Q6_K, fo.Q6_K]
+    tok = fo.encode(fo.Q6_K, rng.standard_normal((cfg.vocab, H)).astype(np.float32))
+    head = fo.encode(fo.Q6_K, (rng.standard_normal((cfg.vocab, H)) * 0.5).astype(np.float32))
+    return cfg, layers, tok, (1 + 0.1 * rng.standard_normal(H)).astype(np.float32), head
+
+
+def decisive_head(cfg, tok, beta=0.08, seed=99):
+    """An output head whose logits have a usable top-1 margin.  Random-init logits are nearly flat
+    (the gap between the two largest of 4096 Gaussian logits is below 1e-3 of their spread somewhere
+    in any 128 steps), far below what the order of f32 sums does to a stack of q8_1 quantizers.  So
+    every token t gets a successor s(t) whose head row leans towards t's embedding (strength beta);
+    at beta = 0.08 the planted successor wins about four steps in five and the model's own logits
+    decide the rest, so the sequence still depends on every layer."""
+    rng = np.random.default_rng(seed)
+    succ = rng.permutation(cfg.vocab)
+    hf = (rng.standard_normal((cfg.vocab, cfg.hidden)) * 0.5).astype(np.float32)
+    hf[succ] += np.float32(beta) * fo.dequant(fo.Q6_K, tok).reshape(cfg.vocab, cfg.hidden)
+    return fo.encode(fo.Q6_K, hf), succ
+
+
+def test_greedy_decode_of_128_tokens_is_token_identical():
+    """128 greedy tokens after a 32-token prompt, eager and from the captured graph, against the
+    oracle pipeline (the harness frink's `verify` uses: crates/frink-cli/src/verify_engine.rs:70-93
+    compares token ids and reports the first divergence).
+
+    Token identity can only be asked where the logit margins exceed what the order of f32 sums
+    does: an activation that lands on the other side of a q8_1 rounding boundary moves a matmul's
+    output by 1e-4, the next quantizers amplify that, and after four layers the logits of the two
+    pipelines differ by several 1e-3 of their spread (printed below, and bounded).  The head is
+    therefore `decisive_head`; the oracle's smallest top-2 margin over the 128 steps is 0.04 of the
+    spread, printed with the result."""
+    from frink_b200.decoder import Decoder
+    cfg, layers, tok, out_norm, _ = recipe_llama()
+    head, succ = decisive_head(cfg, tok)
+    dec = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=256)
+    ora = od.OracleDecoder(cfg, layers, tok, fo.Q6_K, out_norm, head, fo.Q6_K)
+    prompt = np.random.default_rng(0x70C).integers(0, cfg.vocab, 32).astype(np.int32)
+    n_new = 128
+    margins = []
+    want = ora.generate(list(prompt), n_new, margins=margins)
+    planted = sum(1 for a, b in zip([int(prompt[-1])] + want[:-1], want) if succ[a] == b)
+    assert min(margins) > 3e-2 and len(set(want)) == n_new and planted < 110
+    lg = dec.forward(torch.from_numpy(prompt).cuda()).cpu().numpy()[0]
+    lo = od.OracleDecoder(cfg, layers, tok, fo.Q6_K, out_norm, head, fo.Q6_K).forward(prompt)
+    dist = float(np.abs(lg - lo).max() / np.std(lo))
+    print(f"prefill logits: rel-L2 to the oracle {rel_l2(lg, lo):.2e}, largest difference {dist:.2e} of the logits' spread; "
+          f"{planted} of {n_new} steps take the planted successor")
+    assert rel_l2(lg, lo) <= 2e-2 and dist <= 5e-2     # measured: 7.5e-3 and 2.9e-2
+    dec.reset()
+    got = dec.generate(torch.from_numpy(prompt).cuda(), n_new)
+    first = next((i for i in range(n_new) if got[i] != want[i]), None)
+    print(f"128-token greedy decode: first divergence {first}; smallest top-2 logit margin {min(margins):.3e} (in units of the logits' spread) "
+          f"at token {int(np.argmin(margins))}; {len(set(want))} distinct tokens")
+    assert first is None, f"first divergence at generated token {first}: {got[first]} vs {want[first]} (margin there {margins[first]:.3e})"
+    dec.reset()
+    assert dec.generate(torch.from_numpy(prompt).cuda(), n_new, use_graph=True) == want
+    from frink_b200 import device
+    assert device.device_error() == 0
+
+
+def test_small_qwen3_moe_decoder_matches_an_independent_oracle():
+    """The routed graph (per-head q/k norms, split-half RoPE, router -> top-k -> experts ->
+    combine) against `tests/oracle_decoder.py`, which composes the oracle's functions in the
+    reference's order and shares no code with `frink_b200.decoder`: logits of a prefill and of
+    decode rows, then greedy tokens."""
+    from frink_b200.decoder import Decoder
+    from tests.test_parallel_cpu import _tiny_model
+    cfg, layers, tok, out_norm, head = _tiny_model(True)
+    dev = Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=64)
+    ora = od.OracleDecoder(cfg, layers, tok, fo.Q8_0, out_norm, head, fo.Q8_0)
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32)
+    for ids in (prompt, np.array([7], np.int32), np.array([5, 9, 2], np.int32)):
+        got = dev.forward(torch.from_numpy(ids).cuda()).cpu().numpy()[0]
+        want = ora.forward(ids)
+        assert rel_l2(got, want) <= 1e-3, len(ids)
+    dev.reset()
+    ora = od.OracleDecoder(cfg, layers, tok, fo.Q8_0, out_norm, head, fo.Q8_0)
+    want = ora.generate(list(prompt), 24)
+    assert dev.generate(torch.from_numpy(prompt).cuda(), 24) == want
+    from frink_b200 import device
+    assert device.device_error() == 0
+
+
 def test_small_qwen3_moe_decoder_matches_the_cpu_decoder():
     """A routed model with per-head q/k norms and split-half RoPE: the device decoder (grouped
     GEMM prefill, indexed-expert fused decode) against the same decoder run on the oracle-backed

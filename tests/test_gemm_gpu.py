@@ -55,7 +55,26 @@ def test_gemm_mxfp4_2880_columns():
     assert rel_l2(got, want) <= REL_L2 and max_abs_over_inf(got, want) <= MAX_ABS
 
 
-@pytest.mark.parametrize("kind", [fo.Q4_K, fo.Q6_K, fo.MXFP4])
+@pytest.mark.parametrize("kind", KINDS)
+def test_gemm_integers_are_exact(kind):
+    """The accumulators the tensor cores deliver, read before any scale: every per-run int32
+    dot (32 activations; 16 for Q6_K) of every token equals the oracle's twin integers."""
+    from frink_b200 import device
+    rows, cols, m = 200, 1024 if kind != fo.MXFP4 else 960, 37
+    raw = fo.encode(kind, synth_weights(rows, cols, 71))
+    x = synth_acts(m, cols, 72)
+    w = device.Weights(raw, kind, rows, cols)
+    out, isums = device.gemm_isums(w, torch.from_numpy(x).cuda())
+    _no_device_error()
+    got = isums.cpu().numpy()
+    for t in range(m):
+        want = fo.matrix_isums(kind, raw, rows, cols, fo.quantize_q8_1(x[t]))
+        assert np.array_equal(got[t], want), f"token {t}"
+    # and the scaled result of the same launch is the plain GEMM's
+    assert np.array_equal(out.cpu().numpy(), device.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy())
+
+
+@pytest.mark.parametrize("kind", KINDS)
 def test_grouped_gemm_matches_oracle(kind):
     from frink_b200 import device
     n_exp, rows, cols, batch, k = 8, 192, 1024 if kind != fo.MXFP4 else 960, 70, 2
@@ -78,15 +97,35 @@ def test_grouped_gemm_matches_oracle(kind):
         assert rel_l2(got[lo:hi], want) <= REL_L2 and max_abs_over_inf(got[lo:hi], want) <= MAX_ABS, e
 
 
-def test_config2_shape_full_size():
-    """A cell of the prefill sweep at full size: M = 512, 8192 x 3072, Q4_K."""
+C2_CELLS = [(k, r, c) for k in (fo.Q4_K, fo.Q6_K, fo.Q8_0) for (r, c) in ((3072, 3072), (8192, 3072), (3072, 8192))]
+C2_CELLS += [(fo.MXFP4, 2880, 2880), (fo.MXFP4, 8192, 2880)]
+
+
+@pytest.mark.parametrize("kind,rows,cols", C2_CELLS)
+def test_config2_cells_full_size(kind, rows, cols):
+    """Every cell of the prefill sweep at full size (M = 512; the three projection shapes in
+    Q4_K, Q6_K, Q8_0, and the two MXFP4 shapes): the fp32 bar against the f64 oracle, and the
+    measured distance to frink's CPU integer path (Q8_K / Q8_0 activations, `matmul_q8`),
+    which differs by the activation quantizer only and is held to a stated bound."""
     from frink_b200 import device
-    rows, cols, m = 8192, 3072, 512
-    raw = fo.encode(fo.Q4_K, synth_weights(rows, cols, 0x5EED))
+    m = 512
+    raw = fo.encode(kind, synth_weights(rows, cols, 0x5EED + rows + cols))
     x = synth_acts(m, cols, 0xAC7)
-    w = device.Weights(raw, fo.Q4_K, rows, cols)
+    w = device.Weights(raw, kind, rows, cols)
     got = device.gemm(w, torch.from_numpy(x).cuda()).cpu().numpy()
     _no_device_error()
-    # the oracle on all 4.2 M outputs takes seconds with host threads
-    want = fo.matmul_f64(fo.Q4_K, raw, rows, cols, fo.q8_1_round(x))
+    want = fo.matmul_f64(kind, raw, rows, cols, fo.q8_1_round(x))
     assert rel_l2(got, want) <= REL_L2 and max_abs_over_inf(got, want) <= MAX_ABS
+    # distance to the reference's CPU vec_dot on 32 of the tokens: two different 8-bit activation
+    # quantizers (per 32 vs per 256 values), so the bound is the quantizers' noise, not 1e-3
+    cpu = fo.matmul_q8(kind, raw, rows, cols, x[:32], threads=fo.host_threads())
+    dist = rel_l2(got[:32], cpu)
+    print(f"distance to frink CPU integer path: kind {kind} {rows}x{cols}: rel-L2 {dist:.3e}")
+    assert dist <= CPU_PATH_BOUND[kind], dist
+
+
+# rel-L2 between this library's q8_1 results and frink's CPU integer path.  Measured on these
+# shapes: Q4_K / Q6_K 8.1e-3 (Q8_K activations: one scale per 256 values against q8_1's one per 32;
+# each is 5.3e-3 .. 7.0e-3 from the unquantized product), Q8_0 and MXFP4 4.7e-5 (the Q8_0 and q8_1
+# activation rules differ only in how the scale is rounded).
+CPU_PATH_BOUND = {fo.Q4_K: 1.2e-2, fo.Q6_K: 1.2e-2, fo.Q8_0: 2e-4, fo.MXFP4: 2e-4}

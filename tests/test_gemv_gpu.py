@@ -78,11 +78,15 @@ def test_gemv_matches_oracle(kind, batch):
         twin = np.array([fo.dp4a_row(kind, raw[r * rb:(r + 1) * rb], y8) for r in range(rows)], np.float32)
         scale = np.abs(fo.dequant(kind, raw).reshape(rows, cols).astype(np.float64) * fo.q8_1_round(x[0])).sum(axis=1)
         assert np.all(np.abs(got[0] - twin) <= 1e-5 * scale + 1e-4 * np.maximum(np.abs(twin), 1.0) * 1e-2)
-        # reported, not gated: distance to frink's CPU paths on the raw activations
+        # distance to frink's CPU paths on the raw activations: not the parity bar (another 8-bit
+        # activation quantizer, or none), but held to the size of that quantizer's noise.  Measured:
+        # to the integer path 8e-3 (K-quants, Q8_K activations) / 5e-5 (Q8_0, MXFP4); to the f32 path 5e-3.
         l2 = fo.matmul_q8(kind, raw, rows, cols, x)
         l0 = fo.matvec_f32(kind, raw, rows, cols, x)
-        print(f"kind {kind}: rel-L2 to oracle(q8_1 acts) {rel_l2(got, want):.2e}; to CPU int-dot path {rel_l2(got, l2):.2e}; "
-              f"to CPU f32-dot path on raw x {rel_l2(got, l0):.2e}")
+        d2, d0 = rel_l2(got, l2), rel_l2(got, l0)
+        print(f"kind {kind}: rel-L2 to oracle(q8_1 acts) {rel_l2(got, want):.2e}; to CPU int-dot path {d2:.2e}; "
+              f"to CPU f32-dot path on raw x {d0:.2e}")
+        assert d2 <= (1.5e-2 if kind in (fo.Q4_K, fo.Q6_K) else 3e-4) and d0 <= 1e-2
 
 
 @pytest.mark.parametrize("kind", KINDS)
