@@ -38,6 +38,8 @@ SYMBOLS = {
     "fk_gemv_isums": (_I, [_P, _P, _P, _I, _P, _P]),
     "fk_gemm": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_gemm_isums": (_I, [_P, _P, _P, _I, _P, _I, _P, _P]),
+    "fk_gemm_q8k": (_I, [_P, _P, _P, _I, _P, _I, _P]),
+    "fk_gemm_q8k_isums": (_I, [_P, _P, _P, _I, _P, _I, _P, _P]),
     "fk_gemm_static": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_gemm_grouped": (_I, [_P, _P, _P, _P, _P, _P, _I, _P]),
     "fk_moe_route": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P]),

@@ -129,6 +129,7 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
                    const FkGemvFused* fused);
 int fk_ensure_scratch(fk_ctx* ctx, size_t bytes);
 // `map` points at a CUtensorMap (128 bytes, 64-byte aligned): [outer][inner] 32-bit words, no swizzle
+int fk_make_map_2d(void* map, int dtype, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, int swizzle);
 int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer, uint32_t box_inner, uint32_t box_outer);
 
 // device helpers --------------------------------------------------------------

@@ -30,9 +30,10 @@
 #define FK_EPI_F32X2 1
 #endif
 
-#include <cuda.h>
+#include "fk_tc.cuh"
 
 namespace {
+using namespace fk_tc;
 
 #ifdef FK_TRACE
 __device__ unsigned long long fk_gemm_trace[4][512];
@@ -53,7 +54,6 @@ constexpr int UNPACK_WARPS = 2;
 // epilogue warps: four (one per TMEM lane quadrant) for every 32 token columns of the tile
 __host__ __device__ constexpr int epi_warps(int bn) { return bn / 32 * 4; }
 __host__ __device__ constexpr int gemm_threads(int bn) { return (epi_warps(bn) + UNPACK_WARPS + 2) * 32; }
-constexpr uint32_t WAIT_LIMIT = 1u << 24;
 
 struct GemmArgs {
     const uint8_t* w;         // matrix 0 of the weight handle
@@ -69,113 +69,6 @@ struct GemmArgs {
     int32_t* isums;           // test hook: the raw accumulators, [token][rows][cols / run] (nullptr = off)
     int* err;
 };
-
-// ------------------------------------------------------------------ PTX glue
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait: gives up after WAIT_LIMIT polls, records where, and lets the
-// caller run on (its results are then garbage, the host sees the error word).
-__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* err, int code) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return;
-    }
-    atomicCAS(err, 0, code);
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-    // the predicate is "accumulate onto D": always false here, every run starts a fresh accumulator
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
-          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
-          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
-          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// The 32 registers a tcgen05.ld filled are defined, as far as the compiler can
-// tell, at the load itself; this pins their first use behind the wait.
-template <int N>
-__device__ __forceinline__ void tc_ld_fence(uint32_t* v) {
-#pragma unroll
-    for (int i = 0; i < N; i++) asm volatile("" : "+r"(v[i]) :: "memory");
-}
-
-// K-major operand tile, rows of 128 bytes, 128-byte swizzle, 8-row groups 1024
-// bytes apart: start address, LBO = 16 B (unused by this layout), SBO = 1024 B,
-// descriptor version 1, layout type 2 (SWIZZLE_128B).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-// kind::i8: D = s32 (2 at bit 4), A and B signed 8-bit (1 at bits 7 and 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t umma_idesc_i8(int m, int n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ uint4 ldg16(const uint8_t* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
-    uint32_t pos, neg, out;
-    const uint32_t sel = w & 0x7777u;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pos) : "r"(0x03020100u), "r"(0x0C080604u), "r"(sel));
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(0xFDFEFF00u), "r"(0xF4F8FAFCu), "r"(sel));
-    const uint32_t pick = 0x3210u | ((w & 0x8888u) >> 1);
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(pos), "r"(neg), "r"(pick));
-    return out;
-}
-__device__ __forceinline__ float e8m0_half(uint32_t e) {
-    return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
-}
-
-__device__ __forceinline__ float4 lds128(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-    return v;
-}
 
 // Shared memory map (offsets from a 1024-byte aligned base).
 template <int BN> struct Smem {
@@ -804,6 +697,16 @@ extern "C" __attribute__((visibility("default"))) int fk_gemm_trace_read(void* h
     return cudaMemcpyFromSymbol(host, fk_gemm_trace, bytes) == cudaSuccess ? 0 : 1;
 }
 #endif
+
+// General 2-D map for the other kernel files: dtype 0 = uint8, 1 = uint16, 2 = uint32, 3 = float32;
+// swizzle 0 = none, 1 = 32 B, 2 = 64 B, 3 = 128 B.
+int fk_make_map_2d(void* map, int dtype, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, int swizzle) {
+    static const CUtensorMapDataType dt[4] = {CU_TENSOR_MAP_DATA_TYPE_UINT8, CU_TENSOR_MAP_DATA_TYPE_UINT16, CU_TENSOR_MAP_DATA_TYPE_UINT32,
+                                              CU_TENSOR_MAP_DATA_TYPE_FLOAT32};
+    static const int es[4] = {1, 2, 4, 4};
+    static const CUtensorMapSwizzle sw[4] = {CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_SWIZZLE_128B};
+    return make_map((CUtensorMap*)map, dt[dtype], es[dtype], base, inner, outer, box_inner, box_outer, sw[swizzle]);
+}
 
 // A [outer][inner] tensor of 32-bit words, unswizzled, for the other kernel files.
 int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {

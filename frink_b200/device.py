@@ -214,6 +214,24 @@ def gemm_isums(w, x, mat=0):
     return y, isums
 
 
+def gemm_q8k(w, x, mat=0, out=None):
+    """out[t, r] = W[mat][r] . q8_k(x[t]): the GEMM on frink's CPU activation rule (Q4_K weights)."""
+    x = _f32(x)
+    assert x.dim() == 2 and x.shape[1] == w.cols
+    y = out if out is not None else torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
+    check(lib().fk_gemm_q8k(w._ctx, _stream(), w.handle, mat, _ptr(x), x.shape[0], _ptr(y)))
+    return y
+
+
+def gemm_q8k_isums(w, x, mat=0):
+    """(out, isums): `gemm_q8k` plus the exact integers per super-block, [m, rows, cols / 256, 2]."""
+    x = _f32(x)
+    y = torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
+    isums = torch.empty((x.shape[0], w.rows, w.cols // 256, 2), dtype=torch.int32, device=x.device)
+    check(lib().fk_gemm_q8k_isums(w._ctx, _stream(), w.handle, mat, _ptr(x), x.shape[0], _ptr(y), _ptr(isums)))
+    return y, isums
+
+
 def gemm_static(w, x, mat=0, out=None):
     """`gemm` through the entry point that allocates nothing on the device: its
     scratch is a fixed block inside the library, so it can be used where device

@@ -145,6 +145,19 @@ int fk_gemm(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev,
  * delivered it, before any scale: isums_dev is [m][rows][cols / run]. */
 int fk_gemm_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev, int32_t* isums_dev);
 
+/* The prefill GEMM on frink's CPU activation rule: Q8_K activations (one f32 scale and sixteen
+ * 16-value sums per 256 values, `quantize_activations_q8_k`, crates/frink-quant/src/act_quant.rs:
+ * 69-104) against Q4_K weights, the integers of `dot_q4_k_q8` (crates/frink-quant/src/lib.rs:
+ * 822-869) taken on the tensor cores over whole super-blocks.  Its results match frink's CPU
+ * batched path (`WeightMatrix::apply_batch_with_acts`, crates/frink-core/src/weight_matrix.rs:1716)
+ * to f32 summation order; they differ from fk_gemm's by the activation quantizer (q8_1 there).
+ * Other kinds return FK_UNSUPPORTED (use fk_gemm). */
+int fk_gemm_q8k(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev);
+/* Test hook: fk_gemm_q8k that also writes, per (token, row, super-block), the two exact integers
+ * of the CPU vec_dot (sum of scale * sub-block dot, sum of min * sub-block sum) as the tensor
+ * cores delivered them: isums_dev is [m][rows][cols / 256][2]. */
+int fk_gemm_q8k_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev, int32_t* isums_dev);
+
 /* fk_gemm for callers that cannot allocate device memory when they need it (a
  * thread inside a stream capture, a serving loop that must avoid cudaMalloc's
  * device-wide synchronisation, a process on a fixed memory budget).  It has no

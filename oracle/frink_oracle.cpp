@@ -1087,6 +1087,40 @@ FKO_API void fko_q8_1_dequant(const uint8_t* y, int nb, float* out) { q8_1_dequa
 
 // L2 integer dot of one row.  K-quants take Q8_K activations (q, d, bsums);
 // Q8_0 and MXFP4 take Q8_0-form activations (q, d; bsums ignored).
+// The exact integers of dot_q4_k_q8_scalar (crates/frink-quant/src/lib.rs:822-869) per super-block:
+// out[2 b] = sum over the four trips of sc1 * isum1 + sc2 * isum2, out[2 b + 1] = sum_min.
+FKO_API void fko_row_isums_q4k_q8k(const uint8_t* row, int nblk, const int8_t* aq, const int16_t* bs, int32_t* out) {
+    for (int b = 0; b < nblk; b++) {
+        const uint8_t* blk = row + (size_t)b * Q4K_BYTES;
+        const uint8_t* scales = blk + 4;
+        const uint8_t* qs = blk + 16;
+        const int8_t* q8 = aq + (size_t)b * 256;
+        const int16_t* bsums = bs + b * 16;
+        int sum_min = 0;
+        for (int i = 0; i < 8; i++) {
+            uint8_t sc, m;
+            q4k_scale_min(i, scales, &sc, &m);
+            sum_min += (int)m * ((int)bsums[2 * i] + (int)bsums[2 * i + 1]);
+        }
+        long long S = 0;
+        int q_off = 0, base = 0, is = 0;
+        for (int it = 0; it < 4; it++) {
+            uint8_t sc1, sc2, m;
+            q4k_scale_min(is, scales, &sc1, &m);
+            q4k_scale_min(is + 1, scales, &sc2, &m);
+            int isum1 = 0, isum2 = 0;
+            for (int l = 0; l < 32; l++) isum1 += (int)(qs[q_off + l] & 0x0F) * (int)q8[base + l];
+            for (int l = 0; l < 32; l++) isum2 += (int)(qs[q_off + l] >> 4) * (int)q8[base + 32 + l];
+            S += (long long)sc1 * isum1 + (long long)sc2 * isum2;
+            q_off += 32;
+            base += 64;
+            is += 2;
+        }
+        out[2 * b] = (int32_t)S;
+        out[2 * b + 1] = sum_min;
+    }
+}
+
 FKO_API float fko_dot_q8(int kind, const uint8_t* row, int nblk, const int8_t* q, const float* d, const int16_t* bsums) {
     switch (kind) {
         case 12: return dot_q4_k_q8k(row, nblk, q, d, bsums);

@@ -60,6 +60,7 @@ def lib():
         L.fko_encode_mt.restype = C.c_long
         L.fko_encode_mt.argtypes = [C.c_int, f32p, C.c_long, u8p, C.c_int]
         L.fko_nearest_int.argtypes = [C.c_float]
+        L.fko_row_isums_q4k_q8k.argtypes = [u8p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
         L.fko_matvec_f32.argtypes = [C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_int, f32p, C.c_int, C.c_int]
         L.fko_matmul_q8.argtypes = [C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_int, f32p, C.c_int]
         L.fko_matmul_f64.argtypes = [C.c_int, u8p, C.c_int, C.c_int, f32p, C.c_int, f64p, C.c_int]
@@ -174,6 +175,19 @@ def dot_q8(kind, row, x):
         return float(lib().fko_dot_q8(kind, _p(row), nblk, _p(q), _p(d), _p(bs)))
     q, d = quantize_q8_0_act(x, 1)
     return float(lib().fko_dot_q8(kind, _p(row), nblk, _p(q), _p(d), None))
+
+
+def matrix_isums_q4k_q8k(w, rows, cols, x):
+    """The exact integers of the reference's CPU Q4_K vec_dot on Q8_K activations, per super-block:
+    [rows, cols / 256, 2] = (sum of scale * sub-block dot, sum of min * sub-block sum)."""
+    w = _c(w, np.uint8).ravel()
+    q, d, bs = quantize_q8_k(x)
+    nblk = cols // 256
+    rb = nblk * 144
+    out = np.empty((rows, nblk, 2), np.int32)
+    for r in range(rows):
+        lib().fko_row_isums_q4k_q8k(_p(w[r * rb:(r + 1) * rb]), nblk, _p(q), _p(bs), _p(out[r]))
+    return out
 
 
 def dp4a_row(kind, row, y, nwarps=4):
