@@ -12,24 +12,43 @@
 // a third, small contraction (K = 16 on the f16 path: the mins against the sixteen 16-value sums,
 // all exact).  The accumulators are drained once per 256 K instead of once per 32.
 //
-// One CTA = 128 weight rows x 128 tokens, the tokens as two halves of 64 with their own
-// accumulators (HI, LO, M: 6 x 64 tensor-memory columns), so that the epilogue of one half runs
-// under the MMAs of the other.  The unpacked weights never touch shared memory: the A operand
-// lives in tensor memory (the remaining 128 columns hold one super-block: 4 stages of K = 64,
-// hi and lo).  14 warps with fixed roles:
-//   warps 0..7   epilogue (TMEM lane quadrant = warp & 3, token half = warp >> 2)
-//   warps 8..11  unpack: packed Q4_K block (shared memory, staged by TMA) -> nib * s1, nib * s0
+// One CTA = 128 weight rows x 128 tokens: three accumulators (HI, LO, M) of 128 tensor-memory
+// columns each.  The unpacked weights never touch shared memory: the A operand lives in tensor
+// memory (the remaining 128 columns hold one super-block: 4 stages of K = 64, hi and lo), so an
+// MMA reads shared memory only for the activations.  A super-block is an MMA phase (16 int8 MMAs
+// of N = 128 at the tensor core's full rate and one small f16 one) and an epilogue phase; the
+// unpack of the next super-block and all copies run under both.  22 warps with fixed roles:
+//   warps 0..15  epilogue (TMEM lane quadrant = warp & 3, 32 of the 128 token columns each):
+//                four per scheduler, so one warp's tensor-memory loads fly under another's arithmetic
+//   warps 16..19 unpack: packed Q4_K block (shared memory, staged by TMA) -> nib * s1, nib * s0
 //                -> tensor memory (tcgen05.st), and the mins / d / dmin of the block
-//   warp 12      TMA producer: weight blocks, activation tiles, their scales and 16-value sums
-//   warp 13      MMA issuer + tensor-memory allocation
+//   warp 20      TMA producer: weight blocks, activation tiles, their scales and 16-value sums
+//   warp 21      MMA issuer + tensor-memory allocation
 // Every wait is bounded and raises the context's error word instead of spinning forever.
 #include "fk_tc.cuh"
+
+#include <type_traits>
 
 namespace {
 using namespace fk_tc;
 
-constexpr int BM = 128, BN = 128, NH = 64;
-constexpr int EPI_WARPS = 8, UNPACK_WARPS = 4;
+#ifdef FK_TRACE
+__device__ unsigned long long fk_gemm8k_trace[12][64];
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define GTR(k_, i_, who_) do { if ((who_) && blockIdx.x == 0 && blockIdx.y == 0 && (i_) < 64) fk_gemm8k_trace[k_][i_] = gtime_ns(); } while (0)
+#define GTW(k_, i_, who_, stmt_) do { const unsigned long long t__ = gtime_ns(); stmt_; if ((who_) && blockIdx.x == 0 && blockIdx.y == 0 && (i_) < 64) fk_gemm8k_trace[k_][i_] += gtime_ns() - t__; } while (0)
+#else
+#define GTR(k_, i_, who_) do { } while (0)
+#define GTW(k_, i_, who_, stmt_) do { stmt_; } while (0)
+#endif
+
+constexpr int BM = 128, BN = 128;
+constexpr int EPI_WARPS = 16, UNPACK_WARPS = 4;
+constexpr int EC = 32;   // token columns an epilogue warp owns
 constexpr int THREADS = (EPI_WARPS + UNPACK_WARPS + 2) * 32;
 constexpr int WS = 3;   // weight blocks in flight (one super-block of 128 rows each)
 constexpr int BS = 4;   // activation tiles in flight (128 tokens x K = 128)
@@ -39,7 +58,7 @@ constexpr int AP_BYTES = BM * 32, DD_BYTES = BM * 8;
 constexpr int OFF_W = 0, OFF_B = OFF_W + WS * W_BYTES, OFF_X = OFF_B + BS * B_BYTES, OFF_AP = OFF_X + XS * X_BYTES;
 constexpr int OFF_DD = OFF_AP + 2 * AP_BYTES, OFF_BAR = OFF_DD + 2 * DD_BYTES, SMEM_TOTAL = OFF_BAR + 512 + 1024;
 // tensor-memory columns
-constexpr int COL_ACC = 0;        // half h: HI at 192 h, LO at 192 h + 64, M at 192 h + 128
+constexpr int COL_HI = 0, COL_LO = 128, COL_MN = 256;
 constexpr int COL_A = 384;        // stage s (K = 64): hi at 32 s, lo at 32 s + 16
 
 struct Args8k {
@@ -65,7 +84,7 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
     int nb = 0;
     auto bars = [&](int n) { const uint32_t b = bar0 + 8u * nb; nb += n; return b; };
     const uint32_t w_full = bars(WS), w_empty = bars(WS), b_full = bars(BS), b_empty = bars(BS), x_full = bars(XS), x_empty = bars(XS);
-    const uint32_t a_full = bars(4), a_empty = bars(4), ap_full = bars(2), ap_empty = bars(2), acc_full = bars(2), acc_empty = bars(2);
+    const uint32_t a_full = bars(4), a_empty = bars(4), ap_full = bars(2), ap_empty = bars(2), acc_full = bars(1), acc_empty = bars(1);
     uint32_t* tmem_word = (uint32_t*)(smem + OFF_BAR + 8 * nb);
 
     if (threadIdx.x == 0) {
@@ -73,10 +92,9 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
         for (int i = 0; i < BS; i++) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
         for (int i = 0; i < XS; i++) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1 + EPI_WARPS); }
         for (int i = 0; i < 4; i++) { mbar_init(a_full + 8 * i, UNPACK_WARPS); mbar_init(a_empty + 8 * i, 1); }
-        for (int i = 0; i < 2; i++) {
-            mbar_init(ap_full + 8 * i, UNPACK_WARPS); mbar_init(ap_empty + 8 * i, 1 + EPI_WARPS);
-            mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, EPI_WARPS / 2);
-        }
+        for (int i = 0; i < 2; i++) { mbar_init(ap_full + 8 * i, UNPACK_WARPS); mbar_init(ap_empty + 8 * i, 1 + EPI_WARPS); }
+        mbar_init(acc_full, 1);
+        mbar_init(acc_empty, EPI_WARPS);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == EPI_WARPS + UNPACK_WARPS + 1) {   // the MMA warp owns tensor memory
@@ -90,66 +108,77 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
 
     if (warp < EPI_WARPS) {
         // ------------------------------------------------------------------ epilogue
-        const int quad = warp & 3, h = warp >> 2;
+        const int quad = warp & 3, cg = warp >> 2;
         const int r = quad * 32 + lane, row = wrow0 + r;
-        const uint32_t tl = tmem_base + ((uint32_t)(quad * 32) << 16) + COL_ACC + 192 * h;
-        float acc[NH];
+        const int col0 = cg * EC;                             // first token column of this warp inside the tile
+        const uint32_t tl = tmem_base + ((uint32_t)(quad * 32) << 16) + cg * EC;
+        float acc[EC];
 #pragma unroll
-        for (int i = 0; i < NH; i++) acc[i] = 0.0f;
+        for (int i = 0; i < EC; i++) acc[i] = 0.0f;
         for (int sb = 0; sb < nsb; sb++) {
             const int xs = sb % XS, ap = sb & 1;
-            mbar_wait(ap_full + 8 * ap, (sb >> 1) & 1, a.err, 60);
+            mbar_wait_parked(ap_full + 8 * ap, (sb >> 1) & 1, a.err, 60);
             const float2 dd = *(const float2*)(smem + OFF_DD + ap * DD_BYTES + r * 8);
-            mbar_wait(x_full + 8 * xs, (sb / XS) & 1, a.err, 61);
-            const uint32_t das = sbase + OFF_X + xs * X_BYTES + BP_BYTES + (uint32_t)(h * NH) * 4u;
-            mbar_wait(acc_full + 8 * h, sb & 1, a.err, 62);
+            mbar_wait_parked(x_full + 8 * xs, (sb / XS) & 1, a.err, 61);
+            const uint32_t das = sbase + OFF_X + xs * X_BYTES + BP_BYTES + (uint32_t)col0 * 4u;
+            mbar_wait_parked(acc_full, sb & 1, a.err, 62);
             tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < NH / 16; c++) {
-                uint32_t hi[16], lo[16], mn[16];
-                tc_ld16(tl + c * 16, hi);
-                tc_ld16(tl + 64 + c * 16, lo);
-                tc_ld16(tl + 128 + c * 16, mn);
+            for (int c = 0; c < EC / 8; c++) {
+                uint32_t hi[8], lo[8], mn[8];
+                tc_ld8(tl + COL_HI + c * 8, hi);
+                tc_ld8(tl + COL_LO + c * 8, lo);
+                tc_ld8(tl + COL_MN + c * 8, mn);
                 tc_wait_ld();
-                tc_ld_fence<16>(hi);
-                tc_ld_fence<16>(lo);
-                tc_ld_fence<16>(mn);
+                tc_ld_fence<8>(hi);
+                tc_ld_fence<8>(lo);
+                tc_ld_fence<8>(mn);
 #pragma unroll
-                for (int i = 0; i < 16; i += 4) {
-                    const float4 da4 = lds128(das + (uint32_t)(c * 16 + i) * 4u);
-                    const float da[4] = {da4.x, da4.y, da4.z, da4.w};
+                for (int i = 0; i < 8; i += 4) {
+                    const float4 da4 = lds128(das + (uint32_t)(c * 8 + i) * 4u);
+                    // S = 8 HI + LO.  Columns 0, 1 of the four: both halves made floats by the 2^23 trick (exact: each is
+                    // below 2^22) and joined by one fused multiply-add, which rounds the exact sum once; columns 2, 3: the
+                    // integer sum through the conversion unit, which rounds the same way.  Two pipes share the work.
+                    const float2 fh = __fadd2_rn(make_float2(__int_as_float((int)hi[i] + 0x4B400000), __int_as_float((int)hi[i + 1] + 0x4B400000)),
+                                                 make_float2(-12582912.0f, -12582912.0f));
+                    const float2 fl = __fadd2_rn(make_float2(__int_as_float((int)lo[i] + 0x4B400000), __int_as_float((int)lo[i + 1] + 0x4B400000)),
+                                                 make_float2(-12582912.0f, -12582912.0f));
+                    const float2 s01 = __ffma2_rn(fh, make_float2(8.0f, 8.0f), fl);
+                    const float2 s23 = make_float2((float)(8 * (int)hi[i + 2] + (int)lo[i + 2]), (float)(8 * (int)hi[i + 3] + (int)lo[i + 3]));
+                    const float2 m01 = make_float2(__uint_as_float(mn[i]), __uint_as_float(mn[i + 1]));
+                    const float2 m23 = make_float2(__uint_as_float(mn[i + 2]), __uint_as_float(mn[i + 3]));
+                    const float2 nd = make_float2(-dd.y, -dd.y), dv = make_float2(dd.x, dd.x);
+                    const float2 t01 = __ffma2_rn(nd, m01, __fmul2_rn(dv, s01));
+                    const float2 t23 = __ffma2_rn(nd, m23, __fmul2_rn(dv, s23));
+                    const float2 a01 = __ffma2_rn(make_float2(da4.x, da4.y), t01, make_float2(acc[c * 8 + i], acc[c * 8 + i + 1]));
+                    const float2 a23 = __ffma2_rn(make_float2(da4.z, da4.w), t23, make_float2(acc[c * 8 + i + 2], acc[c * 8 + i + 3]));
+                    acc[c * 8 + i] = a01.x; acc[c * 8 + i + 1] = a01.y; acc[c * 8 + i + 2] = a23.x; acc[c * 8 + i + 3] = a23.y;
+                    if (DUMP && row < a.rows) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        // S = 8 HI + LO: both exact as floats (below 2^22), the fused multiply-add rounds the exact sum once
-                        const float fh = __int_as_float((int)hi[i + e] + 0x4B400000) - 12582912.0f;
-                        const float fl = __int_as_float((int)lo[i + e] + 0x4B400000) - 12582912.0f;
-                        const float fs = fmaf(fh, 8.0f, fl);
-                        const float fm = __uint_as_float(mn[i + e]);
-                        acc[c * 16 + i + e] = fmaf(da[e], fmaf(-dd.y, fm, dd.x * fs), acc[c * 16 + i + e]);
-                        if (DUMP && row < a.rows) {
-                            const int dst = a.out_row[tok0 + h * NH + c * 16 + i + e];
+                        for (int e = 0; e < 4; e++) {
+                            const int dst = a.out_row[tok0 + col0 + c * 8 + i + e];
                             if (dst >= 0) {
                                 int32_t* o = a.isums + (((size_t)dst * a.rows + row) * nsb + sb) * 2;
                                 o[0] = 8 * (int)hi[i + e] + (int)lo[i + e];
-                                o[1] = (int)fm;
+                                o[1] = (int)__uint_as_float(mn[i + e]);
                             }
                         }
                     }
                 }
             }
-            // the accumulators of this half, this block's scales and this super-block's activation scales are free again
+            // the accumulators, this block's scales and this super-block's activation scales are free again
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(acc_empty + 8 * h);
+                mbar_arrive(acc_empty);
                 mbar_arrive(x_empty + 8 * xs);
                 mbar_arrive(ap_empty + 8 * ap);
             }
         }
         if (row < a.rows) {
 #pragma unroll
-            for (int i = 0; i < NH; i++) {
-                const int dst = a.out_row[tok0 + h * NH + i];
+            for (int i = 0; i < EC; i++) {
+                const int dst = a.out_row[tok0 + col0 + i];
                 if (dst >= 0) a.out[(size_t)dst * a.rows + row] = acc[i];
             }
         }
@@ -159,13 +188,13 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
         const uint32_t ta = tmem_base + ((uint32_t)(quad * 32) << 16) + COL_A;
         for (int sb = 0; sb < nsb; sb++) {
             const int ws = sb % WS, ap = sb & 1;
-            mbar_wait(w_full + 8 * ws, (sb / WS) & 1, a.err, 70);
+            mbar_wait_parked(w_full + 8 * ws, (sb / WS) & 1, a.err, 70);
             const uint32_t blk = sbase + OFF_W + ws * W_BYTES + (uint32_t)r * 144u;
             const uint4 hd = lds16(blk);
             // 6-bit scales and mins of the 8 sub-blocks, one per byte: [0..3] and [4..7]
             const uint32_t scw[2] = {hd.y & 0x3F3F3F3Fu, (hd.w & 0x0F0F0F0Fu) | ((hd.y >> 2) & 0x30303030u)};
             const uint32_t mnw[2] = {hd.z & 0x3F3F3F3Fu, ((hd.w >> 4) & 0x0F0F0F0Fu) | ((hd.z >> 2) & 0x30303030u)};
-            if (sb >= 2) mbar_wait(ap_empty + 8 * ap, ((sb >> 1) - 1) & 1, a.err, 71);
+            if (sb >= 2) mbar_wait_parked(ap_empty + 8 * ap, ((sb >> 1) - 1) & 1, a.err, 71);
             *(float2*)(smem + OFF_DD + ap * DD_BYTES + r * 8) = make_float2(fk_h2f((uint16_t)(hd.x & 0xFFFF)), fk_h2f((uint16_t)(hd.x >> 16)));
             {
                 // the mins as f16, each twice (one per 16-value sum of its sub-block): a 128 x 16 K-major operand in
@@ -203,7 +232,7 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
                     lo[8 + i] = hn * b0;
                 }
                 if (sb >= 1) {
-                    mbar_wait(a_empty + 8 * s, (sb - 1) & 1, a.err, 72);
+                    mbar_wait_parked(a_empty + 8 * s, (sb - 1) & 1, a.err, 72);
                     tc_fence_after();
                 }
                 tc_st16(ta + 32 * s, hi);
@@ -212,6 +241,9 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(a_full + 8 * s);
+#ifdef FK_TRACE
+                if (lane == 0 && blockIdx.x == 0 && blockIdx.y == 0 && sb < 64 && s == 3) atomicMax(&fk_gemm8k_trace[11][sb], gtime_ns());
+#endif
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(w_empty + 8 * ws);
@@ -221,16 +253,16 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
         if (lane == 0) {
             for (int sb = 0; sb < nsb; sb++) {
                 const int ws = sb % WS, xs = sb % XS;
-                if (sb >= WS) mbar_wait(w_empty + 8 * ws, ((sb / WS) - 1) & 1, a.err, 80);
+                if (sb >= WS) mbar_wait_parked_thread(w_empty + 8 * ws, ((sb / WS) - 1) & 1, a.err, 80);
                 mbar_expect_tx(w_full + 8 * ws, W_BYTES);
                 tma_load_2d(sbase + OFF_W + ws * W_BYTES, &map_w, sb * 36, wrow0, w_full + 8 * ws);
-                if (sb >= XS) mbar_wait(x_empty + 8 * xs, ((sb / XS) - 1) & 1, a.err, 81);
+                if (sb >= XS) mbar_wait_parked_thread(x_empty + 8 * xs, ((sb / XS) - 1) & 1, a.err, 81);
                 mbar_expect_tx(x_full + 8 * xs, BP_BYTES + DA_BYTES);
                 tma_load_2d(sbase + OFF_X + xs * X_BYTES, &map_bs, sb * 16, tok0, x_full + 8 * xs);
                 tma_load_2d(sbase + OFF_X + xs * X_BYTES + BP_BYTES, &map_da, tok0, sb, x_full + 8 * xs);
                 for (int t = 0; t < 2; t++) {
                     const int kt = 2 * sb + t, bt = kt % BS;
-                    if (kt >= BS) mbar_wait(b_empty + 8 * bt, ((kt / BS) - 1) & 1, a.err, 82);
+                    if (kt >= BS) mbar_wait_parked_thread(b_empty + 8 * bt, ((kt / BS) - 1) & 1, a.err, 82);
                     mbar_expect_tx(b_full + 8 * bt, B_BYTES);
                     tma_load_2d(sbase + OFF_B + bt * B_BYTES, &map_q, kt * 128, tok0, b_full + 8 * bt);
                 }
@@ -238,48 +270,53 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
         }
     } else {
         // -------------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t IDESC_I8 = umma_idesc_i8(BM, NH), IDESC_F16 = umma_idesc_f16(BM, NH);
-            for (int sb = 0; sb < nsb; sb++) {
-                const int xs = sb % XS, ap = sb & 1;
-                for (int h = 0; h < 2; h++) {
-                    if (sb >= 1) mbar_wait(acc_empty + 8 * h, (sb - 1) & 1, a.err, 90);
+        // One lane issues every MMA, and what it executes between two of them is time the tensor core
+        // idles.  So the whole warp walks the loop in uniform control flow (only the instructions
+        // themselves are predicated on the lane) and super-blocks are taken two at a time: ring slots
+        // then depend on the parity only, every descriptor is a constant offset from the shared-memory
+        // base, and the accumulate flags are constants.
+        {
+            constexpr uint32_t IDESC_I8 = umma_idesc_i8(BM, BN), IDESC_F16 = umma_idesc_f16(BM, BN);
+            const uint32_t on = lane == 0 ? 1u : 0u;
+            const uint32_t ta = tmem_base + COL_A, d_hi = tmem_base + COL_HI, d_lo = tmem_base + COL_LO, d_mn = tmem_base + COL_MN;
+            auto super_block = [&](auto parity, int sb) {
+                constexpr int P = decltype(parity)::value;      // sb & 1: activation tiles 2 P, 2 P + 1 of the ring of 4, extras slot P, A' slot P
+                static_assert(BS == 4 && XS == 2, "ring slots are tied to the parity of the super-block");
+                // the K = 128 activation tiles (128-byte swizzle, 8-row groups 1024 bytes apart); the mins (f16, K = 16, plain core
+                // matrices 128 bytes apart along K, 8-row groups 256 apart); the 16-value sums (f16, 32-byte swizzle, groups 256 apart)
+                const uint64_t db0 = umma_desc(sbase + OFF_B + (2 * P) * B_BYTES), db1 = umma_desc(sbase + OFF_B + (2 * P + 1) * B_BYTES);
+                const uint64_t dap = umma_desc_of(sbase + OFF_AP + P * AP_BYTES, 128, 256, 0);
+                const uint64_t dbp = umma_desc_of(sbase + OFF_X + P * X_BYTES, 16, 256, 6);
+                if (sb >= 1) mbar_wait_spin(acc_empty, (sb - 1) & 1, a.err, 90);
+                GTR(0, sb, lane == 0);
+#pragma unroll
+                for (int s = 0; s < 4; s++) {
+                    GTW((s == 0 ? 4 : s == 1 ? 6 : s == 2 ? 8 : 9), sb, lane == 0, mbar_wait_spin(a_full + 8 * s, sb & 1, a.err, 91));
+                    if (s == 0) mbar_wait_spin(b_full + 8 * (2 * P), (sb >> 1) & 1, a.err, 92);
+                    if (s == 2) mbar_wait_spin(b_full + 8 * (2 * P + 1), (sb >> 1) & 1, a.err, 92);
                     tc_fence_after();
-                    const uint32_t d_hi = tmem_base + COL_ACC + 192 * h, d_lo = d_hi + 64, d_mn = d_hi + 128;
-                    for (int s = 0; s < 4; s++) {
-                        const int kt = 2 * sb + (s >> 1), bt = kt % BS;
-                        if (h == 0) {
-                            mbar_wait(a_full + 8 * s, sb & 1, a.err, 91);
-                            if (!(s & 1)) mbar_wait(b_full + 8 * bt, (kt / BS) & 1, a.err, 92);
-                            tc_fence_after();
-                        }
-                        // the half's 64 token rows of the K = 128 tile (128-byte swizzle, 8-row groups 1024 bytes apart)
-                        const uint64_t db = umma_desc(sbase + OFF_B + bt * B_BYTES + h * (NH * 128));
-                        for (int j = 0; j < 2; j++) {
-                            const uint32_t acc_on = (s | j) ? 1u : 0u;
-                            const uint64_t dbk = db + 2 * ((s & 1) * 2 + j);   // K advances 32 bytes inside the swizzle atom
-                            tc_mma_i8_ts(d_hi, tmem_base + COL_A + 32 * s + 8 * j, dbk, IDESC_I8, acc_on);
-                            tc_mma_i8_ts(d_lo, tmem_base + COL_A + 32 * s + 16 + 8 * j, dbk, IDESC_I8, acc_on);
-                        }
-                        if (h == 1) {
-                            tc_commit(a_empty + 8 * s);                 // both halves have read this stage of A
-                            if (s & 1) tc_commit(b_empty + 8 * bt);     // and this activation tile
-                        }
+                    const uint64_t db = s < 2 ? db0 : db1;
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const uint64_t dbk = db + 2 * ((s & 1) * 2 + j);   // K advances 32 bytes inside the 128-byte swizzle atom
+                        tc_mma_i8_ts_if(on, d_hi, ta + 32 * s + 8 * j, dbk, IDESC_I8, (s | j) ? 1u : 0u);
+                        tc_mma_i8_ts_if(on, d_lo, ta + 32 * s + 16 + 8 * j, dbk, IDESC_I8, (s | j) ? 1u : 0u);
                     }
-                    if (h == 0) {
-                        mbar_wait(x_full + 8 * xs, (sb / XS) & 1, a.err, 93);
-                        mbar_wait(ap_full + 8 * ap, (sb >> 1) & 1, a.err, 94);
-                        tc_fence_after();
-                    }
-                    // M: mins (f16, K = 16, plain core-matrix layout) x 16-value sums (f16, 32-byte swizzle, 8-row groups 256 bytes apart)
-                    tc_mma_f16_ss(d_mn, umma_desc_of(sbase + OFF_AP + ap * AP_BYTES, 128, 256, 0),
-                                  umma_desc_of(sbase + OFF_X + xs * X_BYTES + h * (NH * 32), 16, 256, 6), IDESC_F16, 0u);
-                    tc_commit(acc_full + 8 * h);
-                    if (h == 1) {
-                        tc_commit(x_empty + 8 * xs);
-                        tc_commit(ap_empty + 8 * ap);
-                    }
+                    GTR(1 + 2 * s, sb, lane == 0);
+                    tc_commit_if(on, a_empty + 8 * s);                         // this stage of A may be overwritten
+                    if (s == 1) tc_commit_if(on, b_empty + 8 * (2 * P));       // and these activation tiles
+                    if (s == 3) tc_commit_if(on, b_empty + 8 * (2 * P + 1));
                 }
+                mbar_wait_spin(x_full + 8 * P, (sb >> 1) & 1, a.err, 93); mbar_wait_spin(ap_full + 8 * P, (sb >> 1) & 1, a.err, 94);
+                tc_fence_after();
+                tc_mma_f16_ss_if(on, d_mn, dap, dbp, IDESC_F16, 0u); tc_commit_if(on, acc_full);
+                GTR(2, sb, lane == 0);
+                tc_commit_if(on, x_empty + 8 * P);
+                tc_commit_if(on, ap_empty + 8 * P);
+            };
+            for (int sb = 0; sb < nsb; sb += 2) {
+                super_block(std::integral_constant<int, 0>{}, sb);
+                if (sb + 1 < nsb) super_block(std::integral_constant<int, 1>{}, sb + 1);
             }
         }
     }
@@ -397,6 +434,12 @@ int gemm8k(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x, i
 }
 
 }  // namespace
+
+#ifdef FK_TRACE
+FK_EXPORT int fk_gemm8k_trace_read(void* host, size_t bytes) {
+    return cudaMemcpyFromSymbol(host, fk_gemm8k_trace, bytes) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 FK_EXPORT int fk_gemm_q8k(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int m, float* out_dev) {
     if (!ctx || !w || !x_dev || !out_dev) return fk_fail(FK_INVALID, "gemm_q8k: null argument");

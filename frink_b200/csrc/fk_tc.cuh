@@ -32,6 +32,29 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* er
     }
     atomicCAS(err, 0, code);
 }
+// The same for warps that may wait long (a whole MMA phase): the hardware parks the thread until the
+// phase completes or the hint (in nanoseconds) runs out, instead of the warp polling shared memory --
+// sixteen polling warps take the bandwidth the tensor core needs for its operand reads.
+// For the one thread whose time is the tensor core's (the MMA issuer): a non-suspending test in a tight loop.
+__device__ __forceinline__ void mbar_wait_spin(uint32_t bar, uint32_t parity, int* err, int code) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return;
+    }
+    atomicCAS(err, 0, code);
+}
+__device__ __forceinline__ void mbar_wait_parked_thread(uint32_t bar, uint32_t parity, int* err, int code) {
+    for (uint32_t i = 0; i < (1u << 20); i++) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(4000u) : "memory");
+        if (ok) return;
+    }
+    atomicCAS(err, 0, code);
+}
+__device__ __forceinline__ void mbar_wait_parked(uint32_t bar, uint32_t parity, int* err, int code) { mbar_wait_parked_thread(bar, parity, err, code); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
@@ -68,6 +91,10 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* v) {
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
           "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld8(uint32_t taddr, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]) : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // The 32 registers a tcgen05.ld filled are defined, as far as the compiler can
@@ -130,6 +157,22 @@ __device__ __forceinline__ void tc_mma_f16_ss(uint32_t tmem_d, uint64_t adesc, u
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+// The same, issued by the lane(s) whose `on` is non-zero while the whole warp stays in uniform control flow: operands
+// that are the same for every lane can then live in uniform registers, which the instruction reads them from.
+__device__ __forceinline__ void tc_mma_i8_ts_if(uint32_t on, uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %9, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(on) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16_ss_if(uint32_t on, uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %9, 0;\n\t"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0), "r"(on) : "memory");
+}
+__device__ __forceinline__ void tc_commit_if(uint32_t on, uint32_t bar) {
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %1, 0;\n\t@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+                 ::"r"(bar), "r"(on) : "memory");
 }
 __device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* v) {
     asm volatile(
