@@ -31,6 +31,9 @@ ROWS, COLS, KIND_NAME, KIND = 8192, 3072, "q4_k", 12
 RING = 40  # weight copies cycled through: 40 x 14.16 MB = 566 MB, 4.5x the 126 MB L2
 ALGO_BYTES = ROWS * (COLS // 256) * 144 + COLS * 4 + ROWS * 4  # 14 200 832
 WORKLOAD = f"C1: Q4_K decode GEMV, weight {ROWS}x{COLS}, batch 1"
+# the same dictionary in both arms (ours and --impl reference), so that the two lines name one configuration
+CONFIG = {"workload": WORKLOAD, "algorithmic_bytes_per_step": ALGO_BYTES,
+          "l2": f"inputs larger than the cache between timed iterations: ring of weight copies ({RING} x 14.2 MB on the GPU, 8 x 14.2 MB on the host)"}
 
 
 def load_peaks():
@@ -139,7 +142,7 @@ def run_reference(args, rank, world):
         "impl": "reference", "metric": "q4_k_gemv_gbs", "value": v, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32 (fused dequant dot)", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "arm": "frink CPU decode path (AVX2 fused f32 dot), C++ restatement"},
+        "config": CONFIG, "arm": "frink CPU decode path (AVX2 fused f32 dot), C++ restatement of the reference (Rust; no toolchain here)",
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{args.steps} full GEMVs over 8 weight copies; {cpu_model()}"},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -177,9 +180,43 @@ def timed_launches(steps, ring, launch, warmup):
     return e0.elapsed_time(e1)
 
 
-# DRAM bytes one launch of the bench kernel moves, from the ncu capture summarised in
-# profiles/gemv_q4_k_8192x3072_b1.md (14 234 112 read + 0 written; the algorithmic bytes are 14 200 832)
-NCU_DRAM_BYTES_PER_LAUNCH = 14234112
+def timed_steps(steps, ring, launch, warmup, min_launches=2000):
+    """The timed region of `steps` launches, repeated: a region of a few dozen launches is
+    ~100 us, and one sample of it carries a graph launch's own latency and loses the overlap
+    of neighbouring launches at both ends.  The same `steps`-launch region is therefore
+    recorded R times back to back into one CUDA graph (R * steps >= min_launches launches over
+    the ring of weight copies), timed between ONE pair of CUDA events; the time of one region
+    is that total / R.  A second pass replays a graph of one region R times, each between its
+    own events, for the spread.  Returns (ms per region, dict)."""
+    import torch
+    repeats = max(1, -(-min_launches // steps))
+    g_all = graph_of(repeats * steps, launch)
+    g_one = graph_of(steps, launch)
+    for _ in range(2):
+        g_all.replay()
+    for _ in range(max(1, -(-warmup // max(steps, 1)))):
+        g_one.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g_all.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    total = e0.elapsed_time(e1)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(repeats)]
+    for a0, a1 in ev:
+        a0.record()
+        g_one.replay()
+        a1.record()
+    torch.cuda.synchronize()
+    ms = sorted(a0.elapsed_time(a1) for a0, a1 in ev)
+    return total / repeats, {"repeats": repeats, "us_per_step": total / repeats / steps * 1e3, "single_region_us_per_step_min": ms[0] / steps * 1e3,
+                             "single_region_us_per_step_median": ms[len(ms) // 2] / steps * 1e3, "single_region_us_per_step_max": ms[-1] / steps * 1e3}
+
+
+# DRAM bytes one launch of the bench kernel moves, from one ncu capture of this kernel and shape
+# (14 230 272 read + 0 written; the algorithmic bytes are 14 200 832)
+NCU_DRAM_BYTES_PER_LAUNCH = 14230272
 
 
 def main():
@@ -188,7 +225,9 @@ def main():
     ap.add_argument("--steps", type=int, default=4000)
     ap.add_argument("--warmup", type=int, default=200)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--extras", action="store_true", help="also time the other kinds, batches and a large matrix")
+    ap.add_argument("--extras", action="store_true", help="(kept for old command lines: the table of other kinds, batches and shapes is part of the default line)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the table of other kinds, batches and shapes")
+    ap.add_argument("--no-models", action="store_true", help="skip the whole-model pp512 / tg128 block")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (M = 512 against the three projection shapes)")
     ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
@@ -248,10 +287,10 @@ def main():
     if rank == 0:
         sampler.start()
     barrier()
-    ms = timed_launches(args.steps, RING, launch, args.warmup)
+    ms, spread = timed_steps(args.steps, RING, launch, args.warmup)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    launches = args.steps  # one kernel of this library per step (graph replays are not seen by the host counter)
+    launches = args.steps * spread["repeats"]  # one kernel of this library per step, in every repeat of the timed region
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -279,9 +318,23 @@ def main():
         e2e_s = float(t.item())
     e2e = world * ALGO_BYTES * e2e_steps / e2e_s / 1e9
 
+    # ---- partitioned figures: the whole models (tensor / expert parallel under torchrun) and the row-split
+    # projection with its collective.  Every rank takes part; rank 0 keeps the results.
+    models, tp_split = {}, None
+    for w_ in ws:
+        w_.release()
+    ws.clear()
+    torch.cuda.empty_cache()
+    if not args.no_models:
+        for name in ("llama3b", "qwen3moe"):
+            r_ = run_model(name, rank, world)
+            if rank == 0:
+                models[name] = r_
+    if world > 1:
+        tp_split = tp_row_split(rank, world)
+
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        leave(world)
         return
 
     peak, which = load_peaks()
@@ -298,10 +351,11 @@ def main():
         "metric": "q4_k_gemv_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8 x int4 dp4a, f32 accumulate", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "l2": f"inputs larger than L2: ring of {RING} weight copies, {RING * ALGO_BYTES / 1e6:.0f} MB",
-                   "timing": "CUDA events around CUDA-graph replays of the launches", "algorithmic_bytes_per_step": ALGO_BYTES},
+        "config": CONFIG,
+        "timing": f"the {args.steps}-launch region recorded {spread['repeats']} times back to back into one CUDA graph, one pair of CUDA events around its "
+                  "replay; value and ms_per_step are that total per region; timing_spread: one region per graph, every replay timed on its own", "timing_spread": spread,
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel and shape (profiles/gemv_q4_k_8192x3072_b1.md)",
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH, "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this kernel and shape",
                      "peak_source": f"{which} HBM copy bandwidth", "frac_of_8TBs_nominal": per_gpu / 8000.0},
         "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{cpu_n} full C1 GEMVs in {cpu_dt:.1f} s, AVX2 fused f32 dot, rows over threads; {cpu_model()}"},
@@ -311,19 +365,22 @@ def main():
         "gpu_launches": launches, "clocks": clocks,
         "parity": {"rel_l2_device": rel, "rel_l2_e2e": rel_e2e, "bar": 1e-3},
     }
+    if models:
+        line["models"] = models
+    if tp_split:
+        line["tp_row_split"] = tp_split
     if world == 1 and not args.no_gemm:
         line["gemm"] = gemm_sweep()
-    if args.extras and world == 1:
+    if world == 1 and not args.no_extras:
         line["extras"] = extras(peak)
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    leave(world)
 
 
 def single_case(args):
     """`--case [gemv:|gemm:]kind:rows:cols:n`: `--steps` plain (un-graphed) launches of
     one shape over a ring of weight copies larger than L2 (n = batch for the GEMV,
-    tokens for the GEMM); what the ncu captures under profiles/ run."""
+    tokens for the GEMM); the command the ncu captures run."""
     import torch
     from frink_b200 import device
     from oracle import frink_oracle as fo
@@ -384,6 +441,7 @@ def synth_model(name, n_layers=0):
     rng = np.random.default_rng(0x5EED0000)
     H, hd = cfg.hidden, cfg.head_dim
     cache = {}
+    norm = lambda n: (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)   # not all ones: the stream must not settle on one token
 
     def enc(tag, kind, rows, cols, variant):
         key = (tag, kind, rows, cols, variant)
@@ -407,49 +465,64 @@ def synth_model(name, n_layers=0):
                     cache[key] = np.tile(enc(tag, Q4, r, c, var), E)
                 return cache[key]
             layers.append(LayerWeights(
-                attn_norm=np.ones(H, np.float32), wq=enc("wq", Q8, cfg.n_heads * hd, H, var), wk=enc("wk", Q8, cfg.n_kv * hd, H, var),
-                wv=enc("wv", Q8, cfg.n_kv * hd, H, var), wo=enc("wo", Q8, H, cfg.n_heads * hd, var), ffn_norm=np.ones(H, np.float32),
+                attn_norm=norm(H), wq=enc("wq", Q8, cfg.n_heads * hd, H, var), wk=enc("wk", Q8, cfg.n_kv * hd, H, var),
+                wv=enc("wv", Q8, cfg.n_kv * hd, H, var), wo=enc("wo", Q8, H, cfg.n_heads * hd, var), ffn_norm=norm(H),
                 gate=ex("eg", cfg.ffn, H), up=ex("eu", cfg.ffn, H), down=ex("ed", H, cfg.ffn),
-                router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=np.ones(hd, np.float32),
-                k_norm=np.ones(hd, np.float32), kinds=kd))
+                router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=norm(hd),
+                k_norm=norm(hd), kinds=kd))
         else:
             more = use_more_bits(i, cfg.n_layers)
             kd = {"wq": Q4, "wk": Q4, "wv": Q6 if more else Q4, "wo": Q4, "gate": Q4, "up": Q4, "down": Q6 if more else Q4}
             layers.append(LayerWeights(
-                attn_norm=np.ones(H, np.float32), wq=enc("wq", kd["wq"], cfg.n_heads * hd, H, var), wk=enc("wk", kd["wk"], cfg.n_kv * hd, H, var),
-                wv=enc("wv", kd["wv"], cfg.n_kv * hd, H, var), wo=enc("wo", kd["wo"], H, cfg.n_heads * hd, var), ffn_norm=np.ones(H, np.float32),
+                attn_norm=norm(H), wq=enc("wq", kd["wq"], cfg.n_heads * hd, H, var), wk=enc("wk", kd["wk"], cfg.n_kv * hd, H, var),
+                wv=enc("wv", kd["wv"], cfg.n_kv * hd, H, var), wo=enc("wo", kd["wo"], H, cfg.n_heads * hd, var), ffn_norm=norm(H),
                 gate=enc("gate", kd["gate"], cfg.ffn, H, var), up=enc("up", kd["up"], cfg.ffn, H, var), down=enc("down", kd["down"], H, cfg.ffn, var),
                 kinds=kd))
     tok_kind = Q6
-    base = fo.encode(tok_kind, (rng.standard_normal((4096, H), dtype=np.float32) * np.float32(0.02)))
-    tok = np.tile(base, -(-cfg.vocab // 4096))[: cfg.vocab * fo.row_bytes(tok_kind, H)].copy()
-    return cfg, layers, tok, tok_kind, np.ones(H, np.float32)
+
+    def vocab_matrix(std):
+        base = fo.encode(tok_kind, (rng.standard_normal((4096, H), dtype=np.float32) * np.float32(std)))
+        m = np.tile(base, -(-cfg.vocab // 4096))[: cfg.vocab * fo.row_bytes(tok_kind, H)].copy()
+        # every copy of the 4096 rows gets its own super-block scale (the f16 at the end of each 210-byte Q6_K block), so
+        # no two rows of the vocabulary are the same and an argmax does not fall back on the lowest id of a tie
+        blocks = m.reshape(-1, 210)
+        per_copy = 4096 * (H // 256)
+        d16 = blocks[:, 208:210].copy().view(np.float16).astype(np.float32).ravel()
+        d16 *= 1.0 + 0.004 * (np.arange(d16.size) // per_copy).astype(np.float32)
+        blocks[:, 208:210] = d16.astype(np.float16).view(np.uint8).reshape(-1, 2)
+        return m
+    # An output head of its own (with a tied head a random-init model answers every token with itself) and an embedding
+    # of unit scale, so that the token just read stays visible in the residual stream beside what the 0.02-scale
+    # layers add: the greedy stream then moves from token to token and the router sees a different row every step.
+    return cfg, layers, vocab_matrix(1.0), tok_kind, norm(H), vocab_matrix(0.02)
 
 
-def model_bench(args, rank, world, local):
+# per decode token, GGUF weight bytes every GPU streams together (layers + output head), and prefill matmul FLOPs of 512 tokens
+MODEL_ROOFLINE = {"llama3b": {"bytes_per_token": 2010839040, "pp512_flops": 2.89e12}}
+
+
+def run_model(name, rank, world, n_layers=0, tp_graph=True):
     """pp512 / tg128 of a random-init model of the named shape: prefill of 512 random
     token ids (GEMM path), then 128 greedy tokens with the decode step replayed from a
-    CUDA graph.  Under torchrun, dense layers are tensor parallel and experts expert
-    parallel.  Times are CUDA events, max over ranks; weights stay resident."""
+    CUDA graph.  Under torchrun, dense layers are tensor parallel (NCCL all-reduce after
+    wo / down) and experts expert parallel (replicated attention, one NCCL all-reduce of
+    the partial expert sums per layer).  Times are CUDA events, max over ranks; weights
+    stay resident.  Returns the result as a dict (rank 0) or None."""
     import torch
     import torch.distributed as dist
     from frink_b200 import device
     from frink_b200.decoder import Decoder
-    cfg, layers, tok, tok_kind, out_norm = synth_model(args.model, args.layers)
+    cfg, layers, tok, tok_kind, out_norm, head = synth_model(name, n_layers)
     # dense models: tensor parallel; routed models: attention replicated, experts spread over the ranks
     # (their few KV heads do not divide by 8)
     try:
-        dec = Decoder(cfg, layers, tok, tok_kind, out_norm, max_seq=1024, dense_parallel=cfg.n_experts == 0)
+        dec = Decoder(cfg, layers, tok, tok_kind, out_norm, output=head, output_kind=tok_kind, max_seq=1024, dense_parallel=cfg.n_experts == 0)
     except ValueError as e:
-        # e.g. 3072 columns are 12 super-blocks: a row-split K-quant matrix cannot be cut 8 ways
-        if rank == 0:
-            print(json.dumps({"metric": "pp512_tg128_tok_s", "model": args.model, "n_gpus": world, "unavailable": str(e)}))
         if world > 1:
             dist.barrier()
-            dist.destroy_process_group()
-        return
+        return {"model": name, "n_gpus": world, "unavailable": str(e)} if rank == 0 else None
     del layers
-    S, G = (512, 128) if args.model != "tiny" else (64, 16)
+    S, G = (512, 128) if name != "tiny" else (64, 16)
     prompt = torch.from_numpy(np.random.default_rng(0x70C).integers(0, cfg.vocab, S).astype(np.int32)).cuda()
 
     def sync():
@@ -478,7 +551,7 @@ def model_bench(args, rank, world, local):
         pp.append(ms)
     pp_ms = float(np.median(pp[1:]))
     cur = first.clone()
-    use_graph = world == 1 or not args.no_tp_graph
+    use_graph = world == 1 or tp_graph
     if use_graph:
         g, out = dec.capture_decode(cur)
         step = lambda: (g.replay(), cur.copy_(out))
@@ -495,26 +568,92 @@ def model_bench(args, rank, world, local):
             toks.append(cur.clone())
     tg_ms, _ = timed(run_decode)
     err = device.device_error()
+    wbytes = sum(v.w.gguf_bytes for L in dec.layers for v in L.values() if hasattr(v, "w") and hasattr(v.w, "gguf_bytes"))
+    res = {
+        "model": name, "n_gpus": world, "layers": cfg.n_layers,
+        "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
+        "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
+        "collective": None if world == 1 else ("nccl all_reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts
+                                               else "nccl all_reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer"),
+        "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
+        "tokens_head": [int(t.item()) for t in toks[:8]], "distinct_tokens": len({int(t.item()) for t in toks})}
+    roof = MODEL_ROOFLINE.get(name)
+    if roof and not n_layers:
+        hbm, _ = load_peaks()
+        res["tg_frac_of_hbm"] = roof["bytes_per_token"] / world / (tg_ms / G * 1e-3) / 1e9 / hbm
+        res["pp_tflops"] = roof["pp512_flops"] / (pp_ms * 1e-3) / 1e12
+    # a live CUDA graph that holds captured collectives keeps the communicator busy: drop it before anything else uses the group
+    sync()
+    if use_graph:
+        del step, g, out
+        dec._graph = dec._gout = None
+    del dec
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    return res if rank == 0 else None
+
+
+def model_bench(args, rank, world, local):
+    res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph)
     if rank == 0:
-        wbytes = sum(v.w.gguf_bytes for L in dec.layers for v in L.values() if hasattr(v, "w") and hasattr(v.w, "gguf_bytes"))
-        print(json.dumps({
-            "metric": "pp512_tg128_tok_s", "model": args.model, "n_gpus": world, "layers": cfg.n_layers,
-            "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
-            "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
-            "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
-            "tokens_head": [int(t.item()) for t in toks[:8]]}))
+        res["metric"] = "pp512_tg128_tok_s"
+        print(json.dumps(res))
+    leave(world)
+
+
+def leave(world):
+    """After captured collectives were replayed, destroy_process_group() may never return: leave without the teardown."""
+    import torch
     if world > 1:
-        # a live CUDA graph that holds captured collectives keeps the communicator busy and
-        # destroy_process_group() then never returns: drop the graph first, and leave
-        # without the teardown if a graph was used
-        sync()
-        if use_graph:
-            del step, g, out
-            dec._graph = dec._gout = None
-            torch.cuda.synchronize()
-            sys.stdout.flush()
-            os._exit(0)
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        os._exit(0)
+
+
+def tp_row_split(rank, world, steps=400):
+    """The row-split (K-split) projection of a decode step with its collective: the 3072 x 8192 Q4_K `down` matrix cut
+    into K ranges of 8192 / world columns, one per rank, each rank's partial product summed over the ranks.  Timed as
+    a graph of `steps` such pairs (matvec over a ring of weight copies, then the reduction), CUDA events, max over ranks."""
+    import torch
+    import torch.distributed as dist
+    from frink_b200 import device, parallel
+    from oracle import frink_oracle as fo
+    rows, cols = 3072, 8192
+    rng = np.random.default_rng(7)
+    base = fo.encode(fo.Q4_K, (rng.standard_normal((512, cols), dtype=np.float32) * np.float32(0.02)))
+    raw = np.tile(base, rows // 512)
+    local_raw, cl = parallel.shard_cols(raw, fo.Q4_K, rows, cols, rank, world)
+    raw_d = torch.from_numpy(local_raw).cuda()
+    ring = max(2, int(300e6 // local_raw.size) + 1)
+    ws = [device.Weights(raw_d, fo.Q4_K, rows, cl) for _ in range(ring)]
+    x = torch.from_numpy(rng.standard_normal((1, cl), dtype=np.float32)).cuda()
+    y = torch.empty((1, rows), dtype=torch.float32, device="cuda")
+
+    def launch(i):
+        device.gemv(ws[i % ring], x, out=y)
+        dist.all_reduce(y, op=dist.ReduceOp.SUM)
+    for i in range(5):
+        launch(i)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = graph_of(steps, launch)
+    g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    del g
+    for w in ws:
+        w.release()
+    nbytes = rows * fo.row_bytes(fo.Q4_K, cols) + cols * 4 + rows * 4
+    return {"shape": f"Q4_K {rows}x{cols} cut into {world} K ranges of {cl} columns", "us_per_step": ms / steps * 1e3,
+            "GBs_all_ranks": nbytes / (ms / steps * 1e-3) / 1e9, "collective": "nccl all_reduce(sum, f32 [3072]) after every matvec, captured in the graph"}
 
 
 def int8_peak_tops():
@@ -540,16 +679,21 @@ def int8_peak_tops():
         return None
 
 
-def gemm_sweep(m=512, steps=200):
+def gemm_sweep(m=512, steps=100, cpu_seconds=0.4):
     """The quantized prefill GEMM sweep: M = 512 tokens against 3072x3072, 8192x3072, 3072x8192
-    in Q4_K, Q6_K, Q8_0 (plus MXFP4 on the 2880-wide shapes).  TFLOPS = 2*M*N*K
-    over the whole fk_gemm call (activation quantization + plan + MMA kernel),
-    CUDA-graph replays over a ring of weight copies larger than L2."""
+    in Q4_K, Q6_K, Q8_0 (plus MXFP4 on the 2880-wide shapes).  TFLOPS = 2*M*N*K over the whole
+    call (activation quantization + plan + MMA kernel), CUDA-graph replays over a ring of weight
+    copies larger than L2.  Two activation rules: "q8_1" (fk_gemm: per-32 scales, the decode
+    kernels' rule, all kinds) and "q8_k" (fk_gemm_q8k: frink's CPU rule, per-256 scales, Q4_K).
+    Beside every cell the reference's CPU batched path (Q8_K / Q8_0 activation quantization +
+    integer row dots, the oracle port, not the 8-row repacked kernels) on all host threads, timed
+    on a bounded sample of the tokens."""
     import torch
     from frink_b200 import device
     from oracle import frink_oracle as fo
     rng = np.random.default_rng(2)
     peak = int8_peak_tops()
+    threads = fo.host_threads()
     cells = []
     shapes = [(3072, 3072), (8192, 3072), (3072, 8192)]
     todo = [(k, r, c) for k in ("q4_k", "q6_k", "q8_0") for (r, c) in shapes] + [("mxfp4", 2880, 2880), ("mxfp4", 8192, 2880)]
@@ -561,23 +705,34 @@ def gemm_sweep(m=512, steps=200):
         raw_d = torch.from_numpy(raw).cuda()
         ring = max(2, int(300e6 // raw.size) + 1)
         ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
-        xd = torch.from_numpy(rng.standard_normal((m, cols), dtype=np.float32)).cuda()
+        x = rng.standard_normal((m, cols), dtype=np.float32)
+        xd = torch.from_numpy(x).cuda()
         out = torch.empty((m, rows), dtype=torch.float32, device="cuda")
-
-        def launch(i):
-            device.gemm(ws[i % ring], xd, out=out)
-        for i in range(3):
-            launch(i)
-        torch.cuda.synchronize()
-        ms = timed_launches(steps, ring, launch, 10)
-        tf = 2.0 * m * rows * cols * steps / (ms * 1e-3) / 1e12
-        cells.append({"kind": name, "rows": rows, "cols": cols, "m": m, "us": ms / steps * 1e3, "tflops": tf,
-                      "frac_of_measured_int8": tf / peak if peak else None, "frac_of_nominal_4500": tf / 4500.0})
+        # the CPU arm: 16 tokens at a time until cpu_seconds have passed
+        n_tok, t0 = 0, time.perf_counter()
+        while time.perf_counter() - t0 < cpu_seconds:
+            fo.matmul_q8(kind, raw, rows, cols, x[(n_tok % m):(n_tok % m) + 16], threads=threads)
+            n_tok += 16
+        cpu_tf = 2.0 * n_tok * rows * cols / (time.perf_counter() - t0) / 1e12
+        rules = [("q8_1", device.gemm)] + ([("q8_k", device.gemm_q8k)] if name == "q4_k" else [])
+        for rule, fn in rules:
+            def launch(i):
+                fn(ws[i % ring], xd, out=out)
+            for i in range(3):
+                launch(i)
+            torch.cuda.synchronize()
+            ms = timed_launches(steps, ring, launch, 10)
+            tf = 2.0 * m * rows * cols * steps / (ms * 1e-3) / 1e12
+            cells.append({"kind": name, "rows": rows, "cols": cols, "m": m, "activations": rule, "us": ms / steps * 1e3, "tflops": tf,
+                          "frac_of_measured_int8": tf / peak if peak else None, "frac_of_nominal_4500": tf / 4500.0,
+                          "cpu_baseline": {"value": cpu_tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                                           "sample": f"{n_tok} of the {m} tokens; frink CPU vec_dot, non-repacked"}})
         for w in ws:
             w.release()
     err = device.device_error()
     return {"cells": cells, "int8_peak_tops_measured": peak, "int8_peak_tops_nominal": 4500.0, "device_error_word": err,
-            "note": "bit-exact int8 per-32-run path; the f32 rescale after every K=32 MMA bounds it, not the tensor pipe"}
+            "note": "q8_1: exact per-32-run integers, one f32 rescale per K = 32 MMA bounds it; q8_k: sub-block scales folded into the "
+                    "int8 operand (two MMAs per K step), one drain per 256 K"}
 
 
 def extras(peak):
@@ -599,7 +754,7 @@ def extras(peak):
         ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
         xd = torch.from_numpy(rng.standard_normal((batch, cols), dtype=np.float32)).cuda()
         yd = torch.empty((batch, rows), dtype=torch.float32, device="cuda")
-        steps = 2000 if small else 100
+        steps = 1000 if small else 60
 
         def launch(i):
             device.gemv(ws[i % ring], xd, out=yd)

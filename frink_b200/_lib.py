@@ -35,6 +35,7 @@ SYMBOLS = {
     "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "fk_moe_local_slots": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
+    "fk_moe_localize": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "fk_gemv_isums": (_I, [_P, _P, _P, _I, _P, _P]),
     "fk_gemm": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_gemm_isums": (_I, [_P, _P, _P, _I, _P, _I, _P, _P]),

@@ -786,14 +786,9 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     float* ssc = (float*)(smem + a.q_sc_off);                  // [NB][nsb][16]: per super-block d[0..7], d * run sum [0..7]
     float* part = (float*)(smem + a.q_part_off);               // [block rows][nsb][NB]
     const uint32_t sbase = smem_u32(smem), ring = sbase + a.q_ring_off, bar = sbase + a.q_bar_off;
-    const int slot = blockIdx.y;
-    const bool dyn = a.ids != nullptr || a.n_active != nullptr;
-    if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");   // the slot table is the previous kernel's output
-    if (a.n_active && slot >= *a.n_active) return;
-    const int mat = a.ids ? a.ids[slot] : a.mat;
-    const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
-    const float* x = a.x + (size_t)slot * a.x_stride;
-    float* y = a.y + (size_t)slot * a.batch * rows;
+    const uint8_t* wb = a.w + (size_t)a.mat * a.mat_stride;
+    const float* x = a.x;
+    float* y = a.y;
     const uint32_t rb = (uint32_t)a.plane_stride[0];           // bytes of a row
     const uint32_t ps = 2 * rb + 16;                           // bytes between row pairs in shared memory
     // row pairs dealt evenly over the blocks: every SM gets one block of (nearly) the same size
@@ -818,46 +813,22 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     }
     TR(1, threadIdx.x == 0);
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (!dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     TR(2, threadIdx.x == 0);
 
     // ---- activations -> q8_1 in shared memory (the rule of fk_q8_1_lane; eight lanes make a run)
-    __shared__ float s_scale[2];
-    __shared__ double s_part[Q4_MAX_THREADS / 32];
     const int c4 = cols >> 2, items = NB * c4;
-    if (a.norm_w) {
-        for (int b = 0; b < a.batch; b++) {
-            double sqs = 0.0;
-            for (int i = tid; i < c4; i += T) {
-                const float4 t4 = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + i);
-                sqs += (double)(t4.x * t4.x) + (double)(t4.y * t4.y) + (double)(t4.z * t4.z) + (double)(t4.w * t4.w);
-            }
-            for (int o = 16; o > 0; o >>= 1) sqs += __shfl_xor_sync(0xffffffffu, sqs, o);
-            if (lane == 0) s_part[warp] = sqs;
-            __syncthreads();
-            if (tid == 0) {
-                double t = 0.0;
-                for (int i = 0; i < nwarps; i++) t += s_part[i];
-                s_scale[b] = 1.0f / sqrtf((float)(t / (double)cols) + a.norm_eps);
-            }
-            __syncthreads();
-        }
-    }
     constexpr int QU = 1024 / Q4_MAX_THREADS;
     for (int base = 0; base < items; base += QU * T) {
-        float4 v[QU], vn[QU], vu[QU];
+        float4 v[QU];
 #pragma unroll
         for (int u = 0; u < QU; u++) {
             const int idx = base + u * T + tid;
-            v[u] = vn[u] = vu[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             if (idx < items) {
                 const int b = NB == 1 ? 0 : idx / c4, k4 = idx - b * c4;
-                if (b < a.batch) {
-                    // x and glu_up may be written by the kernel this one overlaps with: read them past L1
-                    v[u] = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + k4);
-                    if (a.norm_w) vn[u] = __ldg((const float4*)a.norm_w + k4);
-                    if (a.glu_up) vu[u] = __ldcg((const float4*)(a.glu_up + (size_t)slot * a.x_stride + (size_t)b * a.x_ld) + k4);
-                }
+                // x may be written by the kernel this one overlaps with: read it past L1
+                if (b < a.batch) v[u] = __ldcg((const float4*)(x + (size_t)b * a.x_ld) + k4);
             }
         }
 #pragma unroll
@@ -866,25 +837,7 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
             const int idx = base + u * T + tid;
             const bool ok = idx < items;
             const int b = !ok || NB == 1 ? 0 : idx / c4, k4 = ok ? idx - b * c4 : 0;
-            float4 f = v[u];
-            if (a.norm_w) {
-                const float sc = s_scale[b];
-                f.x = f.x * sc * vn[u].x; f.y = f.y * sc * vn[u].y; f.z = f.z * sc * vn[u].z; f.w = f.w * sc * vn[u].w;
-            }
-            if (a.glu_up) {
-                float g[4] = {f.x, f.y, f.z, f.w};
-                const float uu[4] = {vu[u].x, vu[u].y, vu[u].z, vu[u].w};
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    if (a.glu_act == 0) {
-                        g[e] = (g[e] / (1.0f + expf(-g[e]))) * uu[e];
-                    } else {
-                        const float xg = fminf(g[e], 7.0f), yu = fminf(fmaxf(uu[e], -7.0f), 7.0f);
-                        g[e] = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
-                    }
-                }
-                f = make_float4(g[0], g[1], g[2], g[3]);
-            }
+            const float4 f = v[u];
             unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
             mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
             mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
@@ -1002,33 +955,12 @@ __global__ void __launch_bounds__(Q4_MAX_THREADS, 2) gemv_q4k_kernel(const GemvA
     __syncthreads();
     TR(5, threadIdx.x == 0);
     // ---- a row's partial sums, in super-block order
-    if (a.pair_glu) {
-        for (int i = tid; i < (n >> 1) * NB; i += T) {
-            const int pr = i / NB, b = i - pr * NB;
-            if (b >= a.batch) continue;
-            float gt = 0.0f, up = 0.0f;
-            for (int k = 0; k < nsb; k++) {
-                gt += part[((size_t)(2 * pr) * nsb + k) * NB + b];
-                up += part[((size_t)(2 * pr + 1) * nsb + k) * NB + b];
-            }
-            float o;
-            if (a.pair_glu == 1) {
-                o = (gt / (1.0f + expf(-gt))) * up;
-            } else {
-                const float xg = fminf(gt, 7.0f), yu = fminf(fmaxf(up, -7.0f), 7.0f);
-                o = (xg / (1.0f + expf(1.702f * -xg))) * (yu + 1.0f);
-            }
-            y[(size_t)b * (rows >> 1) + (pair_lo + pr)] = o;
-        }
-    } else {
-        for (int i = tid; i < n * NB; i += T) {
-            const int rr = i / NB, b = i - rr * NB;
-            if (b >= a.batch) continue;
-            float v = 0.0f;
-            for (int k = 0; k < nsb; k++) v += part[((size_t)rr * nsb + k) * NB + b];
-            float* dst = y + (size_t)b * rows + row_lo + rr;
-            *dst = a.accumulate ? *dst + v : v;
-        }
+    for (int i = tid; i < n * NB; i += T) {
+        const int rr = i / NB, b = i - rr * NB;
+        if (b >= a.batch) continue;
+        float v = 0.0f;
+        for (int k = 0; k < nsb; k++) v += part[((size_t)rr * nsb + k) * NB + b];
+        y[(size_t)b * rows + row_lo + rr] = v;
     }
     TR(6, threadIdx.x == 0);
     TRMAX(7, lane == 0);
@@ -1466,11 +1398,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArg
     TRMAX(7, lane == 0);
 }
 
-int env_int(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-
 size_t act_smem_bytes(int kind, int nb, int cols) {
     size_t s = (size_t)nb * cols + (size_t)nb * (cols / 32) * 4;
     if (kind == FK_Q4_K) s += (size_t)nb * (cols / 32) * 4;
@@ -1589,7 +1516,7 @@ int launch_q4k(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, i
         }
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)G, (unsigned)slots);
+    cfg.gridDim = dim3((unsigned)G);
     cfg.blockDim = dim3((unsigned)T);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
@@ -1711,7 +1638,12 @@ int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight
         const int rc = launch_mma<KIND>(ctx, st, a, w, &fits);
         if (fits) return rc;
     }
-    if (KIND == FK_Q4_K && a.batch <= 1) {
+    // The block-owned Q4_K kernel takes the plain matvec (and the integer test hook): in a chain of those it is
+    // 4.3 us against 5.4 us a launch (8192 x 3072).  It waits for its whole share before the first dot product, which
+    // costs it inside a decoder step, where the kernel before a matvec is short and hides nothing (688 against 798
+    // tokens per second on the 3B Llama shape): the fused and indexed forms keep the general kernel and its rings.
+    const bool plain = !a.ids && !a.n_active && !a.norm_w && !a.glu_up && !a.pair_glu && !a.accumulate;
+    if (KIND == FK_Q4_K && a.batch <= 1 && (plain || dump)) {
         bool fits = false;
         const int rc = dump ? launch_q4k<1, true>(ctx, st, a, w, slots, &fits) : launch_q4k<1, false>(ctx, st, a, w, slots, &fits);
         if (fits || rc != FK_OK) return rc;

@@ -222,6 +222,18 @@ __global__ void local_slots_kernel(const int* __restrict__ ids, const float* __r
     if (lane == 0) *out_n = n;
 }
 
+// Expert-parallel prefill with replicated activations: pair i keeps its expert as a local id when a rank owns it,
+// else it joins the dummy group n_local with weight 0 (the grouped GEMM never reads that group).
+__global__ void localize_kernel(const int* __restrict__ ids, const float* __restrict__ w, int n, int e0, int n_local,
+                                int* __restrict__ ids_out, float* __restrict__ w_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int id = ids[i];
+    const bool mine = id >= e0 && id < e0 + n_local;
+    ids_out[i] = mine ? id - e0 : n_local;
+    w_out[i] = mine ? w[i] : 0.0f;
+}
+
 // Every kernel of a decode step asks for the same shared-memory carve-out as the GEMV
 // (the maximum): an SM that alternates between kernels with different carve-outs
 // re-partitions its L1 between them, which costs more than these kernels run.
@@ -243,6 +255,17 @@ FK_EXPORT int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, 
     FkDeviceGuard g(ctx->device);
     FK_CARVEOUT(local_slots_kernel);
     local_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ids_dev, w_dev, k, e0, n_local, out_ids_dev, out_w_dev, out_n_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_moe_localize(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int pairs, int e0, int n_local,
+                              int* out_ids_dev, float* out_w_dev) {
+    if (!ctx || !ids_dev || !w_dev || !out_ids_dev || !out_w_dev) return fk_fail(FK_INVALID, "moe_localize: null argument");
+    if (pairs < 1 || n_local < 1) return fk_fail(FK_INVALID, "moe_localize: pairs %d, local experts %d", pairs, n_local);
+    FkDeviceGuard g(ctx->device);
+    localize_kernel<<<(pairs + 255) / 256, 256, 0, (cudaStream_t)stream>>>(ids_dev, w_dev, pairs, e0, n_local, out_ids_dev, out_w_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;

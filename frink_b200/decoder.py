@@ -263,20 +263,9 @@ class Decoder:
         return logits
 
     def _ep_prefill(self, ep, h2):
-        """Activations are replicated under TP, so every rank holds all rows: each takes
-        its share of the rows through the dispatch/combine path and the results are gathered."""
-        n, P, r = h2.shape[0], self.world, self.rank
-        per = -(-n // P)
-        lo, hi = min(n, r * per), min(n, (r + 1) * per)
-        mine = ep.prefill(h2[lo:hi].contiguous()) if hi > lo else h2.new_zeros((0, h2.shape[1]))
-        parts = [h2.new_empty((min(n, (i + 1) * per) - min(n, i * per), h2.shape[1])) for i in range(P)]
-        for i in range(P):   # row counts may differ by rank: one broadcast per owner
-            buf = mine if i == r else parts[i]
-            if buf.shape[0]:
-                torch.distributed.broadcast(buf, src=torch.distributed.get_global_rank(self.group, i) if self.group is not None else i,
-                                            group=self.group)
-        parts[r] = mine
-        return torch.cat(parts)
+        """Activations are replicated, so every rank holds all rows: each routes them all, serves the pairs of
+        its own experts and the partial sums are all-reduced (`ExpertParallelLayer.prefill_replicated`)."""
+        return ep.prefill_replicated(h2)
 
     def prefill(self, ids):
         """Prompt of S token ids -> the first generated token (device int32 [1])."""

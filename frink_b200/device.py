@@ -187,6 +187,14 @@ def moe_local_slots(ids, w, e0, n_local):
     return oi, ow, on
 
 
+def moe_localize(ids, w, e0, n_local):
+    """ids, w [batch, k] -> local ids (n_local where another rank owns the expert) and weights (0 there)."""
+    ids, w = _i32(ids), _f32(w)
+    oi, ow = torch.empty_like(ids), torch.empty_like(w)
+    check(lib().fk_moe_localize(context(ids.device), _stream(), _ptr(ids), _ptr(w), ids.numel(), e0, n_local, _ptr(oi), _ptr(ow)))
+    return oi, ow
+
+
 def gemv_isums(w, x, mat=0):
     x = _f32(x)
     run = 16 if w.kind == 14 else 32

@@ -166,12 +166,40 @@ class ExpertParallelLayer:
             dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
-    # ---- prefill: tokens sharded over ranks, dispatch / combine all-to-all
+    # ---- prefill over replicated activations: no dispatch at all.  Every rank holds every row (the decoder's
+    # activations are replicated under tensor parallelism), routes all of them the same way, runs the pairs whose
+    # expert it owns, and the weighted partial sums meet in ONE all-reduce.  No counts travel, nothing syncs
+    # with the host, and every rank makes the same collective calls whatever the row count.
+    def prefill_replicated(self, x):
+        from .prefill import route
+        ops, L, k = self.ops, self.layer, self.k
+        b = x.shape[0]
+        ids, w = route(L, x, ops)
+        lids, lw = ops.moe_localize(ids, w, self.e0, self.n_local)
+        # the pairs of other ranks' experts fall into a group past the last local expert, which no GEMM serves
+        group_off, gather, pair_of = ops.moe_permute(lids, self.n_local + 1)
+        pairs = b * k
+        g = ops.gemm_grouped(L.gate, group_off, gather, x, pairs)
+        u = ops.gemm_grouped(L.up, group_off, gather, x, pairs)
+        a = ops.glu(g, u, L.act)
+        y = torch.zeros((pairs, self.hidden), dtype=torch.float32, device=x.device)   # rows nobody writes carry weight 0: keep them finite
+        y = ops.gemm_grouped(L.down, group_off, None, a, pairs, out=y)
+        out = ops.moe_combine(y, pair_of, lw, b, k)
+        if self.world > 1:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    # ---- prefill: tokens sharded over ranks, dispatch / combine all-to-all.  Every rank of the group must call
+    # this, also with no rows of its own (it still serves its experts for the other ranks' rows).
     def prefill(self, x_local):
         from .prefill import experts_forward_grouped, route
         ops, L, k, P = self.ops, self.layer, self.k, self.world
         b = x_local.shape[0]
-        ids, w = route(L, x_local, ops)
+        if b:
+            ids, w = route(L, x_local, ops)
+        else:
+            ids = torch.zeros((0, k), dtype=torch.int32, device=x_local.device)
+            w = torch.zeros((0, k), dtype=torch.float32, device=x_local.device)
         ids1 = ids.reshape(-1).to(torch.int64)
         order = torch.argsort(ids1, stable=True)        # by expert, hence by owner rank; tokens ascending inside
         send_rows = x_local[(order // k)].contiguous()
@@ -202,6 +230,8 @@ class ExpertParallelLayer:
             dist.all_to_all_single(back, y.contiguous(), s_cnt, r_cnt, group=self.group)
         else:
             back = y
+        if not b:
+            return x_local.new_zeros((0, self.hidden))
         inv = torch.empty_like(order)
         inv[order] = torch.arange(b * k, device=order.device)
         return ops.moe_combine(back, inv.to(torch.int32), w, b, k)

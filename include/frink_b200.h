@@ -202,6 +202,11 @@ int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int
  * local ids with their weights (the rest: expert 0, weight 0); *out_n = count. */
 int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int k, int e0, int n_local,
                        int* out_ids_dev, float* out_w_dev, int* out_n_dev);
+/* Expert-parallel prefill over replicated activations (no reference counterpart): every rank routes
+ * all tokens; pair i keeps its expert as the local id ids[i] - e0 when e0 <= ids[i] < e0 + n_local,
+ * else it gets the id n_local (a group no expert serves) and weight 0. */
+int fk_moe_localize(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int pairs, int e0, int n_local,
+                    int* out_ids_dev, float* out_w_dev);
 /* `silu_mul_f32` / `swiglu_oai_f32` (crates/frink-cuda/src/glu.rs:42,68):
  * act 0 = silu(gate) * up, 1 = gpt-oss clamped SwiGLU (alpha 1.702, limit 7). */
 int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const float* up_dev, size_t n, int act,

@@ -73,6 +73,11 @@ def moe_permute(ids, n_experts):
     return torch.from_numpy(off), torch.from_numpy((order // k).astype(np.int32)), torch.from_numpy(pair_of)
 
 
+def moe_localize(ids, w, e0, n_local):
+    mine = (ids >= e0) & (ids < e0 + n_local)
+    return torch.where(mine, ids - e0, torch.full_like(ids, n_local)).to(torch.int32), torch.where(mine, w, torch.zeros_like(w))
+
+
 def moe_combine(y, pair_of, w, batch, k, out=None, accumulate=False):
     ys, ws = y.numpy(), w.numpy().reshape(batch, k)
     po = pair_of.numpy() if pair_of is not None else np.arange(batch * k)

@@ -68,6 +68,12 @@ def test_fused_gemv_equals_the_separate_kernels(kind, batch):
     from frink_b200 import device
     rng = np.random.default_rng(5 + batch)
     rows, cols = 520, 1024
+    # One kernel serves the plain and the fused launch of a shape, so the two agree bit for bit -- except Q4_K at batch 1,
+    # where the plain matvec has a kernel of its own (another f32 summation order; both are tied to the oracle elsewhere).
+    if kind == fo.Q4_K and batch == 1:
+        same = lambda a, b: torch.allclose(a, b, rtol=2e-5, atol=2e-6 * float(b.abs().max()))
+    else:
+        same = torch.equal
     w = device.Weights(fo.encode(kind, synth_weights(rows, cols, 11)), kind, rows, cols)
     x = torch.from_numpy(rng.standard_normal((batch, cols)).astype(np.float32)).cuda()
     nw = torch.from_numpy((1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)).cuda()
@@ -79,17 +85,17 @@ def test_fused_gemv_equals_the_separate_kernels(kind, batch):
     for act in (0, 1):
         want = device.gemv(w, device.glu(gu[:, :cols].contiguous(), gu[:, cols:].contiguous(), act))
         got = device.gemv_fused(w, gu[:, :cols], glu_up=gu[:, cols:], glu_act=act)
-        assert torch.equal(got, want)
+        assert same(got, want)
     # rows read as (gate, up) pairs: the gated activation formed in the epilogue
     full = device.gemv(w, x)
     for act in (0, 1):
         want = device.glu(full[:, 0::2].contiguous(), full[:, 1::2].contiguous(), act)
         got = device.gemv_fused(w, x, pair_glu=act + 1)
-        assert got.shape == (batch, rows // 2) and torch.equal(got, want)
+        assert got.shape == (batch, rows // 2) and same(got, want)
     res = torch.from_numpy(rng.standard_normal((batch, rows)).astype(np.float32)).cuda()
     out = res.clone()
     device.gemv_fused(w, x, out=out, accumulate=True)
-    assert torch.equal(out, res + device.gemv(w, x))
+    assert same(out, res + device.gemv(w, x))
     assert device.device_error() == 0
 
 

@@ -109,6 +109,43 @@ def test_expert_parallel_matches_single_rank():
         assert np.array_equal(pre, want[rank * 3:(rank + 1) * 3])   # dispatch/combine keeps the single-rank order: same bits
 
 
+def _ep_ragged_case(rank, world):
+    """9 rows over 4 ranks: shares of 3, 3, 3 and NONE -- the last rank still has to make every collective call."""
+    from frink_b200 import parallel
+    from tests import cpu_ops
+    n_exp, hidden, ffn, k = 8, 256, 512, 2
+    raws = {n: np.concatenate([fo.encode(fo.Q4_K, synth_weights(r, c, 100 * i + e)) for e in range(n_exp)])
+            for i, (n, r, c) in enumerate((("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)))}
+    router = torch.from_numpy((np.random.default_rng(1).standard_normal((n_exp, hidden)) * 0.5).astype(np.float32))
+    ep = parallel.ExpertParallelLayer(cpu_ops, router, raws["gate"], raws["up"], raws["down"], fo.Q4_K, n_exp, hidden, ffn, k)
+    x = torch.from_numpy(np.random.default_rng(2).standard_normal((9, hidden)).astype(np.float32))
+    per = -(-9 // world)
+    lo, hi = min(9, rank * per), min(9, (rank + 1) * per)
+    sharded = ep.prefill(x[lo:hi].contiguous()).numpy()     # tokens sharded: two all-to-alls, also from the rank with no rows
+    replicated = ep.prefill_replicated(x).numpy()           # activations replicated: one all-reduce
+    return lo, hi, sharded, replicated
+
+
+def test_expert_parallel_prefill_with_a_rank_that_has_no_rows():
+    from frink_b200 import prefill
+    from tests import cpu_ops
+    n_exp, hidden, ffn, k = 8, 256, 512, 2
+    raws = {n: np.concatenate([fo.encode(fo.Q4_K, synth_weights(r, c, 100 * i + e)) for e in range(n_exp)])
+            for i, (n, r, c) in enumerate((("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)))}
+    router = torch.from_numpy((np.random.default_rng(1).standard_normal((n_exp, hidden)) * 0.5).astype(np.float32))
+    mk = lambda n, r, c: cpu_ops.Weights(raws[n], fo.Q4_K, r, c, n_mats=n_exp)
+    layer = prefill.RoutedLayer(router, mk("gate", ffn, hidden), mk("up", ffn, hidden), mk("down", hidden, ffn), k=k, mode=1)
+    x = torch.from_numpy(np.random.default_rng(2).standard_normal((9, hidden)).astype(np.float32))
+    want = prefill.run_device_routed_batch(layer, x, cpu_ops).numpy()
+    res = spawn(_ep_ragged_case, world=4)
+    assert [hi - lo for lo, hi, _, _ in res] == [3, 3, 3, 0]
+    for lo, hi, sharded, replicated in res:
+        assert np.array_equal(sharded, want[lo:hi])               # dispatch / combine keeps the single-rank order: same bits
+        assert rel_l2(replicated, want) <= 1e-6                   # partial sums all-reduced: the order of a few adds
+    for r in res[1:]:
+        assert np.array_equal(r[3], res[0][3])                    # and every rank ends with the same rows
+
+
 def _tiny_model(moe):
     from frink_b200.decoder import DecoderConfig, LayerWeights
     rng = np.random.default_rng(21)
