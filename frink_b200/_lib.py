@@ -60,6 +60,13 @@ SYMBOLS = {
     "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),
     "fk_add_int": (_I, [_P, _P, _P, _I]),
+    "fk_comm_create": (_I, [_P, _SZ, _I, _I, _P, C.POINTER(_P)]),
+    "fk_comm_connect": (_I, [_P, _P]),
+    "fk_comm_connect_local": (_I, [_P, C.POINTER(_P)]),
+    "fk_comm_arena": (_I, [_P, C.POINTER(_P), C.POINTER(_SZ)]),
+    "fk_comm_destroy": (_I, [_P]),
+    "fk_comm_channel_bytes": (_SZ, [_I, _I]),
+    "fk_allreduce": (_I, [_P, _P, _P, _SZ, _I, _P, _P, _I, _I, _I]),
     "fk_launch_matvec": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _P]),
     "fk_launch_mul_mm": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _I, _P]),
     "fk_forget_resident": (_I, [_P]),

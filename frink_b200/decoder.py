@@ -99,10 +99,12 @@ class _Merged:
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, layers: List[LayerWeights], tok_embd, tok_kind, out_norm, output=None, output_kind=None,
-                 max_seq=1024, ops=None, group=None, device="cuda", dense_parallel=True):
+                 max_seq=1024, ops=None, group=None, device="cuda", dense_parallel=True, comm=None):
         """dense_parallel=False: attention and dense projections are replicated on every rank
         (no collectives for them) and only the routed experts are sharded over the group --
-        the plan for MoE models whose KV heads do not divide by the number of ranks."""
+        the plan for MoE models whose KV heads do not divide by the number of ranks.
+        comm (`frink_b200.comm.Comm`): decode rows are summed across ranks by the peer-memory
+        all-reduce; without it every sum is a `torch.distributed` all-reduce."""
         if ops is None:
             from . import device as ops
         self.cfg, self.ops, self.group, self.dev = cfg, ops, group, device
@@ -138,7 +140,7 @@ class Decoder:
             if T == 1:
                 d["wo"] = _Linear(ops, L.wo, k["wo"], H, cfg.n_heads * hd)
             else:
-                d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True)
+                d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True, comm=comm)
             if cfg.qk_norm:
                 d["q_norm"], d["k_norm"] = f32(L.q_norm), f32(L.k_norm)
             if cfg.n_experts:
@@ -149,7 +151,7 @@ class Decoder:
                                            mode=cfg.route_mode)
                 else:
                     d["ep"] = parallel.ExpertParallelLayer(ops, router, L.gate, L.up, L.down, k["experts"], cfg.n_experts, H, cfg.ffn,
-                                                           cfg.top_k, mode=cfg.route_mode, group=group)
+                                                           cfg.top_k, mode=cfg.route_mode, group=group, comm=comm)
             else:
                 gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, r_dense, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, r_dense, T)]
                 if k["gate"] == k["up"]:
@@ -160,7 +162,7 @@ class Decoder:
                 if T == 1:
                     d["down"] = _Linear(ops, L.down, k["down"], H, cfg.ffn)
                 else:
-                    d["down"] = parallel.RowParallelLinear(ops, L.down, k["down"], H, cfg.ffn, group, input_is_sharded=True)
+                    d["down"] = parallel.RowParallelLinear(ops, L.down, k["down"], H, cfg.ffn, group, input_is_sharded=True, comm=comm)
             d["k"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
             d["v"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
             self.layers.append(d)

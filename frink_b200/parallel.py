@@ -81,9 +81,13 @@ class ColumnParallelLinear:
 class RowParallelLinear:
     """y = sum over ranks of W[:, K range of the rank] x[K range]: one all-reduce."""
 
-    def __init__(self, ops, raw, kind, rows, cols, group=None, input_is_sharded=False):
+    def __init__(self, ops, raw, kind, rows, cols, group=None, input_is_sharded=False, comm=None):
+        """comm (`frink_b200.comm.Comm`): decode rows (at most 8) are summed by the peer-memory all-reduce
+        instead of the library collective, whose fixed cost is several matvecs at these sizes."""
         self.ops, self.group, self.input_is_sharded = ops, group, input_is_sharded
         self.rank, self.world = _world(group)
+        self.comm = comm if comm is not None and self.world > 1 else None
+        self.ch = self.comm.channel(8 * rows) if self.comm else None
         local, self.cols_local = shard_cols(raw, kind, rows, cols, self.rank, self.world)
         self.rows, self.cols = rows, cols
         self.w = ops.Weights(local, kind, rows, self.cols_local)
@@ -94,7 +98,10 @@ class RowParallelLinear:
             x2 = x2[:, self.rank * self.cols_local:(self.rank + 1) * self.cols_local].contiguous()
         y = self.ops.gemv(self.w, x2) if x2.shape[0] <= 8 else self.ops.gemm(self.w, x2)
         if self.world > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            if self.comm is not None and x2.shape[0] <= 8:
+                self.comm.all_reduce(self.ch, y)
+            else:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
         return y if x.dim() == 2 else y[0]
 
 
@@ -116,10 +123,12 @@ class TensorParallelFFN:
 class ExpertParallelLayer:
     """A routed layer whose experts are split over the ranks of `group`."""
 
-    def __init__(self, ops, router, gate_raw, up_raw, down_raw, kind, n_experts, hidden, ffn, k, mode=1, act=0, group=None):
+    def __init__(self, ops, router, gate_raw, up_raw, down_raw, kind, n_experts, hidden, ffn, k, mode=1, act=0, group=None, comm=None):
         from .prefill import RoutedLayer
         self.ops, self.group = ops, group
         self.rank, self.world = _world(group)
+        self.comm = comm if comm is not None and self.world > 1 else None
+        self.ch = self.comm.channel(8 * hidden) if self.comm else None
         if n_experts % self.world:
             raise ValueError(f"{n_experts} experts do not split over {self.world} ranks")
         self.n_experts, self.n_local = n_experts, n_experts // self.world
@@ -163,7 +172,10 @@ class ExpertParallelLayer:
                 y = ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act))
                 out = ops.moe_combine(y, None, w1[mine].contiguous()[None], 1, n)[0]
         if self.world > 1:
-            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+            if self.comm is not None:
+                self.comm.all_reduce(self.ch, out)
+            else:
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
     # ---- prefill over replicated activations: no dispatch at all.  Every rank holds every row (the decoder's

@@ -50,6 +50,7 @@ typedef enum fk_kind {
 
 typedef struct fk_ctx fk_ctx;
 typedef struct fk_weight_s* fk_weight;
+typedef struct fk_comm fk_comm;
 
 /* ---- context ------------------------------------------------------------
  * Replaces `gpu::shared_device` / `gpu::probe` (crates/frink-cuda/src/
@@ -264,6 +265,29 @@ int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const fl
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);
 /* *p += v on the device (the position word of a captured decode step). */
 int fk_add_int(fk_ctx* ctx, void* stream, int* p_dev, int v);
+
+/* ---- multi-GPU: peer-memory all-reduce ---------------------------------------
+ * The reference is single-device (crates/frink-cuda/src/gpu.rs:219); these have no counterpart
+ * there.  One process per GPU of one box.  Every rank creates an arena and publishes its 64-byte
+ * handle (CUDA IPC) to the others by whatever transport the host has (torch.distributed here);
+ * fk_comm_connect maps the peers' arenas.  An arena is carved into channels at the same offsets
+ * on every rank, fk_comm_channel_bytes(world, n_max) bytes each (256-byte aligned offsets); a
+ * channel serves all-reduces of up to n_max floats, one at a time.
+ *
+ * fk_allreduce: dst = (accumulate ? dst : 0) + sum over ranks of src, the same bits on every
+ * rank (slots are added in rank order).  One kernel: peer stores of src into every rank's slot,
+ * a flag per rank and part, a wait bounded by timeout_us (0 = two seconds) that raises the
+ * device error word 60 instead of hanging, then the sum.  The counters live on the device, so
+ * a captured launch may be replayed.  n a multiple of 4, buffers 16-byte aligned. */
+int fk_comm_create(fk_ctx* ctx, size_t arena_bytes, int rank, int world, uint8_t* handle_out_64, fk_comm** out);
+int fk_comm_connect(fk_comm* comm, const uint8_t* handles_world_x_64);
+/* Test hook: peers given as device pointers of this GPU (the time-out path is tested on one GPU). */
+int fk_comm_connect_local(fk_comm* comm, void* const* peer_arenas_dev);
+int fk_comm_arena(fk_comm* comm, void** arena_dev, size_t* bytes);
+int fk_comm_destroy(fk_comm* comm);
+size_t fk_comm_channel_bytes(int world, int n_max);
+int fk_allreduce(fk_ctx* ctx, void* stream, fk_comm* comm, size_t channel_off, int n_max, const float* src_dev, float* dst_dev, int n,
+                 int accumulate, int timeout_us);
 
 /* ---- host-buffer launch surface -------------------------------------------
  * What frink-core binds (crates/frink-core/src/weight_matrix/gpu_backend.rs:

@@ -1,0 +1,61 @@
+"""The peer-memory all-reduce on ONE GPU: the single-rank case, and the bounded wait -- an
+all-reduce of a two-rank communicator whose peer never shows up gives up after its time limit,
+raises the device error word and leaves the context usable (no rank exits, nothing hangs)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_single_rank_allreduce_is_a_copy():
+    from frink_b200 import device
+    from frink_b200._lib import check, lib
+    ctx = device.context()
+    h, handle = C.c_void_p(), (C.c_uint8 * 64)()
+    check(lib().fk_comm_create(ctx, 1 << 20, 0, 1, handle, C.byref(h)))
+    x = torch.randn(3072, device="cuda")
+    y = torch.full_like(x, 2.0)
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    check(lib().fk_allreduce(ctx, s, h, 0, 3072, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), 3072, 1, 0))
+    torch.cuda.synchronize()
+    assert torch.equal(y, x + 2.0) and device.device_error() == 0
+    check(lib().fk_comm_destroy(h))
+
+
+def test_a_peer_that_never_arrives_times_out_with_an_error_word():
+    from frink_b200 import device
+    from frink_b200._lib import check, lib
+    ctx = device.context()
+    assert device.device_error() == 0
+    a, b, handle = C.c_void_p(), C.c_void_p(), (C.c_uint8 * 64)()
+    check(lib().fk_comm_create(ctx, 1 << 20, 0, 2, handle, C.byref(a)))     # "rank 0" of two
+    check(lib().fk_comm_create(ctx, 1 << 20, 1, 2, handle, C.byref(b)))     # the arena that stands for rank 1: nobody runs it
+    arena_b = C.c_void_p()
+    check(lib().fk_comm_arena(b, C.byref(arena_b), None))
+    peers = (C.c_void_p * 2)(None, arena_b)
+    check(lib().fk_comm_connect_local(a, peers))
+    x = torch.randn(1024, device="cuda")
+    y = torch.empty_like(x)
+    s = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    check(lib().fk_allreduce(ctx, s, a, 0, 1024, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), 1024, 0, 3000))   # 3 ms limit
+    e1.record()
+    torch.cuda.synchronize()
+    assert 2.0 <= e0.elapsed_time(e1) <= 200.0            # it waited its limit, not forever
+    assert device.device_error() == 60                    # and said so (the call resets the word)
+    assert device.device_error() == 0
+    # the context is as usable as before
+    from oracle import frink_oracle as fo
+    from tests.helpers import synth_weights
+    raw = fo.encode(fo.Q8_0, synth_weights(64, 256, 1))
+    w = device.Weights(raw, fo.Q8_0, 64, 256)
+    xv = np.random.default_rng(0).standard_normal(256).astype(np.float32)
+    got = device.gemv(w, torch.from_numpy(xv).cuda()).cpu().numpy()
+    want = fo.matmul_f64(fo.Q8_0, raw, 64, 256, fo.q8_1_round(xv))[0]
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) <= 1e-3
+    check(lib().fk_comm_destroy(a))
+    check(lib().fk_comm_destroy(b))

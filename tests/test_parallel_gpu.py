@@ -46,8 +46,68 @@ def _worker(rank, world, port, ret):
         got = ep.prefill(x[rank * per:(rank + 1) * per].contiguous()).cpu().numpy()
         out["ep_pre_equal"] = bool(np.array_equal(got, ref[rank * per:(rank + 1) * per]))
         out["ep_dec"] = rel_l2(ep.decode(x[0]).cpu().numpy(), prefill.run_device_routed(layer, x[0]).cpu().numpy())
+        # the peer-memory all-reduce against the library's: sizes from one part to many, in place and accumulating,
+        # many in a row on one channel (the two generations of slots), and replayed from a CUDA graph
+        from frink_b200.comm import Comm
+        comm = Comm(arena_bytes=64 << 20)
+        ok = True
+        for n in (4, 3072, 8 * 3072, 100000):
+            ch = comm.channel(n)
+            for it in range(6):
+                v = torch.from_numpy(np.random.default_rng(1000 * rank + 10 * n + it).standard_normal(n).astype(np.float32)).cuda()
+                want = v.clone()
+                dist.all_reduce(want)
+                base = torch.full_like(v, 0.5)
+                got = comm.all_reduce(ch, v.clone())
+                acc = comm.all_reduce(ch, v.clone(), dst=base.clone(), accumulate=True)
+                ok = ok and torch.allclose(got, want, rtol=1e-6, atol=1e-6) and torch.allclose(acc, want + 0.5, rtol=1e-6, atol=1e-6)
+                everyone = [torch.empty_like(got) for _ in range(world)]
+                dist.all_gather(everyone, got)
+                ok = ok and all(torch.equal(e, got) for e in everyone)        # the same bits on every rank
+        ch = comm.channel(3072)
+        v = torch.ones(3072, device="cuda") * (rank + 1)
+        buf = torch.empty_like(v)
+        graph = torch.cuda.CUDAGraph()
+        comm.all_reduce(ch, v, dst=buf)
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph):
+            for _ in range(5):
+                comm.all_reduce(ch, v, dst=buf)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        ok = ok and bool((buf == world * (world + 1) / 2).all())
+        out["ar_ok"] = bool(ok)
+        # row-split projection and expert layer with the peer-memory all-reduce in place of the library's
+        tp2 = parallel.TensorParallelFFN(device, g, u, d, fo.Q4_K, fo.Q6_K, hidden, ffn)
+        tp2.down = parallel.RowParallelLinear(device, d, fo.Q6_K, hidden, ffn, input_is_sharded=True, comm=comm)
+        out["tp_dec_comm"] = rel_l2(tp2(x[:2]).cpu().numpy(), ref_dec.cpu().numpy())
+        ep2 = parallel.ExpertParallelLayer(device, router, raws["gate"], raws["up"], raws["down"], fo.Q4_K, n_exp, hidden, 512, k, comm=comm)
+        out["ep_dec_comm"] = rel_l2(ep2.decode(x[0]).cpu().numpy(), prefill.run_device_routed(layer, x[0]).cpu().numpy())
+        out["ep_pre_replicated"] = rel_l2(ep2.prefill_replicated(x).cpu().numpy(), ref)
+        # time: 12 KB vectors, 200 in a graph
+        def timed(fn):
+            gr = torch.cuda.CUDAGraph()
+            fn()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gr):
+                for _ in range(200):
+                    fn()
+            gr.replay()
+            torch.cuda.synchronize()
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / 200 * 1e3
+        out["us_peer_allreduce_12KB"] = timed(lambda: comm.all_reduce(ch, v, dst=buf))
+        out["us_nccl_allreduce_12KB"] = timed(lambda: dist.all_reduce(buf))
         torch.cuda.synchronize()
         out["err"] = device.device_error()
+        dist.barrier()
+        comm.close()
         ret[rank] = out
     finally:
         dist.destroy_process_group()
@@ -65,3 +125,5 @@ def test_tp_and_ep_over_nccl_match_single_gpu():
         assert o["err"] == 0
         assert o["tp_dec"] <= 1e-5 and o["tp_pre"] <= 1e-5, o
         assert o["ep_pre_equal"] and o["ep_dec"] <= 1e-6, o
+        assert o["ar_ok"] and o["tp_dec_comm"] <= 1e-5 and o["ep_dec_comm"] <= 1e-6 and o["ep_pre_replicated"] <= 1e-6, o
+    print({k: v for k, v in ret[0].items() if k.startswith("us_")})
