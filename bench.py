@@ -235,6 +235,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
     ap.add_argument("--watchdog", type=int, default=0, help="seconds after which all thread stacks are printed and the process exits")
     ap.add_argument("--no-tp-graph", action="store_true", help="--model under torchrun: launch the decode step eagerly instead of replaying a CUDA graph with the collectives captured")
+    ap.add_argument("--nccl-only", action="store_true", help="under torchrun: sum decode rows with NCCL instead of the peer-memory all-reduce")
     ap.add_argument("--case", default=None, help="kind:rows:cols:batch -- plain launches of one GEMV shape (for ncu captures)")
     args = ap.parse_args()
     if args.watchdog:
@@ -303,19 +304,25 @@ def main():
     x_pin = torch.from_numpy(x).pin_memory()
     raws = [raw.copy() for _ in range(RING)]
     nb = COLS // 256
-    e2e_steps = max(50, min(args.steps, 1000))
+    # five regions of e2e_steps calls each, every region closed by a synchronize and reduced to the slowest rank; the
+    # median region is reported (a region is tens of milliseconds, so one host hiccup would otherwise decide the figure)
+    e2e_steps = max(400, min(args.steps, 1000))
     for i in range(RING):
         y_host = gpu.launch_q4_k_matvec(raws[i], x_pin.numpy(), ROWS, nb * 144, nb)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        y_host = gpu.launch_q4_k_matvec(raws[i % RING], x_pin.numpy(), ROWS, nb * 144, nb)
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    regions = []
+    for _ in range(5):
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            y_host = gpu.launch_q4_k_matvec(raws[i % RING], x_pin.numpy(), ROWS, nb * 144, nb)
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([sec], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        regions.append(sec)
+    e2e_s = float(np.median(regions))
     e2e = world * ALGO_BYTES * e2e_steps / e2e_s / 1e9
 
     # ---- partitioned figures: the whole models (tensor / expert parallel under torchrun) and the row-split
@@ -325,13 +332,17 @@ def main():
         w_.release()
     ws.clear()
     torch.cuda.empty_cache()
+    comm = None
+    if world > 1 and not args.nccl_only:
+        from frink_b200.comm import Comm
+        comm = Comm(arena_bytes=512 << 20)
     if not args.no_models:
         for name in ("llama3b", "qwen3moe"):
-            r_ = run_model(name, rank, world)
+            r_ = run_model(name, rank, world, comm=comm)
             if rank == 0:
                 models[name] = r_
     if world > 1:
-        tp_split = tp_row_split(rank, world)
+        tp_split = tp_row_split(rank, world, comm)
 
     if rank != 0:
         leave(world)
@@ -360,7 +371,8 @@ def main():
         "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{cpu_n} full C1 GEMVs in {cpu_dt:.1f} s, AVX2 fused f32 dot, rows over threads; {cpu_model()}"},
         "e2e": {"value": e2e, "unit": "GB/s", "h2d_bytes_per_step": COLS * 4, "d2h_bytes_per_step": ROWS * 4,
-                "steps": e2e_steps, "ms_per_step": e2e_s / e2e_steps * 1e3,
+                "steps": e2e_steps, "regions": 5, "ms_per_step": e2e_s / e2e_steps * 1e3,
+                "ms_per_step_regions": [r_ / e2e_steps * 1e3 for r_ in regions],
                 "api": "gpu.launch_q4_k_matvec(host weights, host x) -> host y, weights resident"},
         "gpu_launches": launches, "clocks": clocks,
         "parity": {"rel_l2_device": rel, "rel_l2_e2e": rel_e2e, "bar": 1e-3},
@@ -501,7 +513,7 @@ def synth_model(name, n_layers=0):
 MODEL_ROOFLINE = {"llama3b": {"bytes_per_token": 2010839040, "pp512_flops": 2.89e12}}
 
 
-def run_model(name, rank, world, n_layers=0, tp_graph=True):
+def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None):
     """pp512 / tg128 of a random-init model of the named shape: prefill of 512 random
     token ids (GEMM path), then 128 greedy tokens with the decode step replayed from a
     CUDA graph.  Under torchrun, dense layers are tensor parallel (NCCL all-reduce after
@@ -516,7 +528,8 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True):
     # dense models: tensor parallel; routed models: attention replicated, experts spread over the ranks
     # (their few KV heads do not divide by 8)
     try:
-        dec = Decoder(cfg, layers, tok, tok_kind, out_norm, output=head, output_kind=tok_kind, max_seq=1024, dense_parallel=cfg.n_experts == 0)
+        dec = Decoder(cfg, layers, tok, tok_kind, out_norm, output=head, output_kind=tok_kind, max_seq=1024, dense_parallel=cfg.n_experts == 0,
+                      comm=comm)
     except ValueError as e:
         if world > 1:
             dist.barrier()
@@ -554,12 +567,13 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True):
     use_graph = world == 1 or tp_graph
     if use_graph:
         g, out = dec.capture_decode(cur)
-        step = lambda: (g.replay(), cur.copy_(out))
+        step = lambda: (dec.replay(), cur.copy_(out))
     else:
         step = lambda: cur.copy_(dec.decode_step(cur))
     for _ in range(3):
         step()
     dec.pos.fill_(S)
+    dec._pos_host = S
     toks = []
 
     def run_decode():
@@ -573,8 +587,12 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True):
         "model": name, "n_gpus": world, "layers": cfg.n_layers,
         "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
         "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
-        "collective": None if world == 1 else ("nccl all_reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts
-                                               else "nccl all_reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer"),
+        "collective": None if world == 1 else (
+            ("all-reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts else
+             "all-reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer") +
+            ("; decode: in the epilogue of the row-split matvec (dense) / this library's all-reduce kernel (expert sums): peer stores over NVLink, "
+             "each value with its arrival count, rank-order sum; prefill: NCCL" if comm is not None
+             else "; NCCL")),
         "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
         "tokens_head": [int(t.item()) for t in toks[:8]], "distinct_tokens": len({int(t.item()) for t in toks})}
     roof = MODEL_ROOFLINE.get(name)
@@ -594,7 +612,11 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True):
 
 
 def model_bench(args, rank, world, local):
-    res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph)
+    comm = None
+    if world > 1 and not args.nccl_only:
+        from frink_b200.comm import Comm
+        comm = Comm(arena_bytes=512 << 20)
+    res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph, comm)
     if rank == 0:
         res["metric"] = "pp512_tg128_tok_s"
         print(json.dumps(res))
@@ -610,10 +632,11 @@ def leave(world):
         os._exit(0)
 
 
-def tp_row_split(rank, world, steps=400):
+def tp_row_split(rank, world, comm=None, steps=400):
     """The row-split (K-split) projection of a decode step with its collective: the 3072 x 8192 Q4_K `down` matrix cut
-    into K ranges of 8192 / world columns, one per rank, each rank's partial product summed over the ranks.  Timed as
-    a graph of `steps` such pairs (matvec over a ring of weight copies, then the reduction), CUDA events, max over ranks."""
+    into K ranges of 8192 / world columns, one per rank, each rank's partial product summed over the ranks -- by NCCL,
+    and by this library's peer-memory all-reduce.  Timed as a graph of `steps` such pairs (matvec over a ring of weight
+    copies, then the reduction), CUDA events, max over ranks."""
     import torch
     import torch.distributed as dist
     from frink_b200 import device, parallel
@@ -628,32 +651,45 @@ def tp_row_split(rank, world, steps=400):
     ws = [device.Weights(raw_d, fo.Q4_K, rows, cl) for _ in range(ring)]
     x = torch.from_numpy(rng.standard_normal((1, cl), dtype=np.float32)).cuda()
     y = torch.empty((1, rows), dtype=torch.float32, device="cuda")
-
-    def launch(i):
-        device.gemv(ws[i % ring], x, out=y)
-        dist.all_reduce(y, op=dist.ReduceOp.SUM)
-    for i in range(5):
-        launch(i)
-    torch.cuda.synchronize()
-    dist.barrier()
-    g = graph_of(steps, launch)
-    g.replay()
-    torch.cuda.synchronize()
-    dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    g.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    del g
+    nbytes = rows * fo.row_bytes(fo.Q4_K, cols) + cols * 4 + rows * 4
+    out = {"shape": f"Q4_K {rows}x{cols} cut into {world} K ranges of {cl} columns"}
+    ch = comm.channel(rows) if comm is not None else None
+    arms = ["nccl"] + (["peer_memory_kernel", "peer_memory"] if comm is not None else [])
+    for name in arms:
+        def launch(i):
+            if name == "peer_memory":         # one launch: the matvec sums over the ranks in its epilogue
+                device.gemv_fused(ws[i % ring], x, out=y, allreduce=(comm, ch))
+                return
+            device.gemv(ws[i % ring], x, out=y)
+            if name == "nccl":
+                dist.all_reduce(y, op=dist.ReduceOp.SUM)
+            else:
+                comm.all_reduce(ch, y)
+        for i in range(5):
+            launch(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = graph_of(steps, launch)
+        g.replay()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        del g
+        out[name] = {"us_per_step": ms / steps * 1e3, "GBs_all_ranks": nbytes / (ms / steps * 1e-3) / 1e9,
+                     "collective": {"nccl": "nccl all_reduce(sum, f32 [3072]) after every matvec",
+                                    "peer_memory_kernel": "this library's all-reduce kernel after every matvec: peer stores over NVLink, each value with its arrival "
+                                                          "count, rank-order sum",
+                                    "peer_memory": "the same exchange in the matvec's own epilogue: one launch a step"}[name] + "; captured in the graph"}
     for w in ws:
         w.release()
-    nbytes = rows * fo.row_bytes(fo.Q4_K, cols) + cols * 4 + rows * 4
-    return {"shape": f"Q4_K {rows}x{cols} cut into {world} K ranges of {cl} columns", "us_per_step": ms / steps * 1e3,
-            "GBs_all_ranks": nbytes / (ms / steps * 1e-3) / 1e9, "collective": "nccl all_reduce(sum, f32 [3072]) after every matvec, captured in the graph"}
+    return out
 
 
 def int8_peak_tops():

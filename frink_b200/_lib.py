@@ -53,11 +53,12 @@ SYMBOLS = {
     "fk_get_rows": (_I, [_P, _P, _P, _I, _P, _I, _P]),
     "fk_rmsnorm": (_I, [_P, _P, _P, _P, _P, _I, _I, C.c_float, _P]),
     "fk_rope": (_I, [_P, _P, _P, _I, _I, _I, _P, C.c_float, _I]),
-    "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P, _P, _P, C.c_float]),
+    "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P, _P, _P, C.c_float, _I]),
     "fk_add": (_I, [_P, _P, _P, _P, _SZ]),
-    "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P]),
-    "fk_attention_rope_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P]),
-    "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P]),
+    "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P, _I]),
+    "fk_attention_rope_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I]),
+    "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P, _I]),
+    "fk_reserve_scratch": (_I, [_P, _SZ]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),
     "fk_add_int": (_I, [_P, _P, _P, _I]),
     "fk_comm_create": (_I, [_P, _SZ, _I, _I, _P, C.POINTER(_P)]),
@@ -67,6 +68,7 @@ SYMBOLS = {
     "fk_comm_destroy": (_I, [_P]),
     "fk_comm_channel_bytes": (_SZ, [_I, _I]),
     "fk_allreduce": (_I, [_P, _P, _P, _SZ, _I, _P, _P, _I, _I, _I]),
+    "fk_gemv_fused_allreduce": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P, _SZ, _I, _I]),
     "fk_launch_matvec": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _P]),
     "fk_launch_mul_mm": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _I, _P]),
     "fk_forget_resident": (_I, [_P]),

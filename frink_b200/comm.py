@@ -33,7 +33,7 @@ class Comm:
 
     def channel(self, n_max):
         """A channel for all-reduces of up to n_max floats: (offset, n_max)."""
-        n_max = (int(n_max) + 3) & ~3
+        n_max = int(n_max)
         size = (lib().fk_comm_channel_bytes(self.world, n_max) + 255) & ~255
         off = self._next
         if off + size > self.arena_bytes:

@@ -73,6 +73,7 @@ FK_EXPORT void fk_destroy(fk_ctx* ctx) {
     if (ctx->x_pin) cudaFreeHost(ctx->x_pin);
     if (ctx->y_pin) cudaFreeHost(ctx->y_pin);
     cudaFree(ctx->scratch);
+    for (uint8_t* p : ctx->scratch_retired) cudaFree(p);
     cudaFree(ctx->err_flag);
     cudaFree(ctx->argmax_ws);
     cudaFree(ctx->argmax_cnt);
@@ -97,20 +98,31 @@ FK_EXPORT int fk_counters(fk_ctx* ctx, uint64_t* h2d, uint64_t* d2h, uint64_t* l
     return FK_OK;
 }
 
-int fk_ensure_scratch(fk_ctx* ctx, size_t bytes) {
+// The workspace only grows, and a block that was ever handed out is kept until fk_destroy: its address is inside
+// launches that may still be queued, and inside CUDA graphs that may be replayed at any later time.  Growth allocates,
+// which a stream capture does not allow: a call that needs more than is reserved while `st` is being captured fails
+// with FK_INVALID (reserve with fk_reserve_scratch before capturing).
+int fk_ensure_scratch(fk_ctx* ctx, cudaStream_t st, size_t bytes) {
     std::lock_guard<std::recursive_mutex> lk(ctx->mu);
     if (bytes <= ctx->scratch_cap) return FK_OK;
-    size_t cap = bytes + (bytes >> 2) + 4096;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone)
+        return fk_fail(FK_INVALID, "the workspace has %zu bytes and this call needs %zu: it cannot grow inside a stream capture (fk_reserve_scratch first)",
+                       ctx->scratch_cap, bytes);
+    size_t cap = bytes + (bytes >> 1) + 4096;
+    if (cap < FK_SCRATCH_MIN) cap = FK_SCRATCH_MIN;
     uint8_t* p = nullptr;
     FK_CUDA(cudaMalloc(&p, cap), FK_LAUNCH);
-    if (ctx->scratch) {
-        // whatever was enqueued against the old block has to finish first
-        FK_CUDA(cudaDeviceSynchronize(), FK_LAUNCH);
-        cudaFree(ctx->scratch);
-    }
+    if (ctx->scratch) ctx->scratch_retired.push_back(ctx->scratch);
     ctx->scratch = p;
     ctx->scratch_cap = cap;
     return FK_OK;
+}
+
+FK_EXPORT int fk_reserve_scratch(fk_ctx* ctx, size_t bytes) {
+    if (!ctx) return fk_fail(FK_INVALID, "reserve_scratch: null context");
+    FkDeviceGuard g(ctx->device);
+    return fk_ensure_scratch(ctx, nullptr, bytes);
 }
 
 // ------------------------------------------------------- weight registration

@@ -3,17 +3,10 @@
 // library collective's fixed cost is several times the matvec it follows.
 //
 // Every rank owns an arena (one cudaMalloc block, shared with the other ranks of the box through
-// CUDA IPC) and carves it into channels at the same offsets on every rank.  A channel holds
-//   slots [2][world][n_max] f32   -- what every rank contributed, two generations
-//   flags [world][FK_AR_FLAGS] u32 -- flags[q][b]: how many times rank q has delivered part b
-//   seen  [FK_AR_FLAGS] u32        -- how many all-reduces this rank has finished on part b
-// An all-reduce number t (t = seen + 1, counted on the device, so a replayed CUDA graph keeps
-// counting) of part b: store the local values into slot (t & 1, my rank) of EVERY rank (plain peer
-// stores), make them visible system-wide, store flags[my rank][b] = t on every rank; wait until
-// the local flags[q][b] >= t for all q; add the slots in rank order (every rank gets the same
-// bits); seen[b] = t.  Two generations are enough: a peer can be at most one all-reduce ahead,
-// because its next one needs this rank's next contribution.  No rank reads another rank's
-// memory, and nothing here is a multicast.
+// CUDA IPC) and carves it into channels at the same offsets on every rank; the channel's layout
+// and the per-element protocol (a value travels with its own arrival count in one 8-byte store)
+// are in fk_comm.cuh.  The kernel here is the standalone form; the row-split matvec runs the same
+// two steps in its epilogue.
 //
 // Every wait is bounded in time (the caller's limit, two seconds by default) and raises the
 // context's error word (60) instead of hanging; the call then returns garbage and the host sees
@@ -24,47 +17,31 @@
 
 namespace {
 
-__device__ __forceinline__ unsigned long long gtime_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
+constexpr int AR_THREADS = 256, AR_PER_THREAD = 4;
 
-// Part b of `n` floats is [b * per, min(n, (b + 1) * per)), per a multiple of 4; one block per part.
-__global__ void __launch_bounds__(256) allreduce_kernel(FkArChannel ch, float* __restrict__ buf, int n, int per, int accumulate_into,
-                                                         float* __restrict__ dst, int* __restrict__ err) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");            // buf is the previous kernel's output
+__global__ void __launch_bounds__(AR_THREADS) allreduce_kernel(FkArChannel ch, const float* __restrict__ src, int n, int accumulate_into,
+                                                                float* __restrict__ dst, int* __restrict__ err) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");            // src is the previous kernel's output
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    const int b = blockIdx.x, lo = b * per, hi = min(n, lo + per);
-    __shared__ unsigned s_target;
-    if (threadIdx.x == 0) s_target = fk_ar_seen(ch)[b] + 1u;
-    __syncthreads();
-    const unsigned target = s_target;
-    // 1. my values into my slot on every rank
-    for (int q = 0; q < ch.world; q++) {
-        float* slot = fk_ar_slot(ch, q, target & 1u, ch.rank);
-        for (int i = lo + 4 * (int)threadIdx.x; i < hi; i += 4 * blockDim.x) *(float4*)(slot + i) = *(const float4*)(buf + i);
-    }
-    __threadfence_system();
-    __syncthreads();
-    // 2. tell every rank; 3. wait for every rank
-    if (threadIdx.x < ch.world) fk_ar_signal(ch, threadIdx.x, b, target);
-    if (threadIdx.x < ch.world) fk_ar_wait(ch, threadIdx.x, b, target, err);
-    __syncthreads();
-    // 4. the sum, in rank order
-    for (int i = lo + 4 * (int)threadIdx.x; i < hi; i += 4 * blockDim.x) {
-        float4 acc = __ldcg((const float4*)(fk_ar_slot(ch, ch.rank, target & 1u, 0) + i));   // past L1: peers wrote these
-        for (int q = 1; q < ch.world; q++) {
-            const float4 v = __ldcg((const float4*)(fk_ar_slot(ch, ch.rank, target & 1u, q) + i));
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    const int i0 = blockIdx.x * AR_THREADS * AR_PER_THREAD + threadIdx.x;
+    float v[AR_PER_THREAD];
+    unsigned t[AR_PER_THREAD];
+#pragma unroll
+    for (int j = 0; j < AR_PER_THREAD; j++) {
+        const int i = i0 + j * AR_THREADS;
+        if (i < n) {
+            v[j] = src[i];
+            t[j] = fk_ar_send(ch, i, v[j]);
         }
-        if (accumulate_into) {
-            const float4 o = *(const float4*)(dst + i);
-            acc.x += o.x; acc.y += o.y; acc.z += o.z; acc.w += o.w;
-        }
-        *(float4*)(dst + i) = acc;
     }
-    if (threadIdx.x == 0) fk_ar_seen(ch)[b] = target;
+#pragma unroll
+    for (int j = 0; j < AR_PER_THREAD; j++) {
+        const int i = i0 + j * AR_THREADS;
+        if (i < n) {
+            const float s = fk_ar_recv(ch, i, t[j], v[j], err);
+            dst[i] = accumulate_into ? dst[i] + s : s;
+        }
+    }
 }
 
 }  // namespace
@@ -144,7 +121,7 @@ FK_EXPORT size_t fk_comm_channel_bytes(int world, int n_max) { return fk_ar_chan
 
 int fk_ar_channel(fk_comm* c, size_t channel_off, int n_max, int timeout_us, FkArChannel* ch) {
     if (!c->connected && c->world > 1) return fk_fail(FK_COMM, "all-reduce: the communicator is not connected");
-    if (channel_off % 256 || channel_off + fk_ar_channel_bytes(c->world, n_max) > c->bytes)
+    if (channel_off % 256 || n_max < 1 || channel_off + fk_ar_channel_bytes(c->world, n_max) > c->bytes)
         return fk_fail(FK_INVALID, "all-reduce: a channel of %d floats at offset %zu does not fit the arena of %zu bytes", n_max, channel_off, c->bytes);
     ch->rank = c->rank;
     ch->world = c->world;
@@ -157,26 +134,22 @@ int fk_ar_channel(fk_comm* c, size_t channel_off, int n_max, int timeout_us, FkA
 FK_EXPORT int fk_allreduce(fk_ctx* ctx, void* stream, fk_comm* c, size_t channel_off, int n_max, const float* src_dev, float* dst_dev, int n,
                            int accumulate, int timeout_us) {
     if (!ctx || !c || !src_dev || !dst_dev) return fk_fail(FK_INVALID, "allreduce: null argument");
-    if (n < 1 || n > n_max || (n & 3) || ((uintptr_t)src_dev & 15) || ((uintptr_t)dst_dev & 15))
-        return fk_fail(FK_INVALID, "allreduce: n=%d (channel %d) must be a multiple of 4 and the buffers 16-byte aligned", n, n_max);
+    if (n < 1 || n > n_max) return fk_fail(FK_INVALID, "allreduce: n=%d outside the channel's 1..%d", n, n_max);
     FkDeviceGuard g(ctx->device);
     FkArChannel ch;
     int rc = fk_ar_channel(c, channel_off, n_max, timeout_us, &ch);
     if (rc) return rc;
-    // parts of at least 4 KB, at most FK_AR_FLAGS of them
-    int per = ((n + FK_AR_FLAGS - 1) / FK_AR_FLAGS + 3) & ~3;
-    if (per < 1024) per = 1024;
-    const int parts = (n + per - 1) / per;
+    const int parts = (n + AR_THREADS * AR_PER_THREAD - 1) / (AR_THREADS * AR_PER_THREAD);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)parts);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(AR_THREADS);
     cfg.stream = (cudaStream_t)stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    FK_CUDA(cudaLaunchKernelEx(&cfg, allreduce_kernel, ch, (float*)src_dev, n, per, accumulate, dst_dev, ctx->err_flag), FK_LAUNCH);
+    FK_CUDA(cudaLaunchKernelEx(&cfg, allreduce_kernel, ch, src_dev, n, accumulate, dst_dev, ctx->err_flag), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }

@@ -10,6 +10,7 @@
 #include <mutex>
 #include <string>
 #include <utility>
+#include <vector>
 
 #include "../../include/frink_b200.h"
 
@@ -69,6 +70,7 @@ struct fk_ctx {
     // GEMM / MoE scratch (activation q8_1 planes), grown on demand
     uint8_t* scratch = nullptr;
     size_t scratch_cap = 0;
+    std::vector<uint8_t*> scratch_retired;   // outgrown blocks: queued launches and captured graphs may still name them
     // device word kernels raise when a bounded wait gives up
     int* err_flag = nullptr;
     // argmax: per-(row, block) keys and per-row arrival counters (64 x 64 keys, 64 counters);
@@ -123,11 +125,13 @@ struct FkGemvFused {
     int accumulate;
     int x_ld;
     int pair_glu;                   // rows are (gate, up) pairs: write act(gate) * up, rows / 2 outputs
+    const struct FkArChannel* ar;   // sum the results over the ranks of this channel in the epilogue (null: no)
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
                    const FkGemvFused* fused);
-int fk_ensure_scratch(fk_ctx* ctx, size_t bytes);
+constexpr size_t FK_SCRATCH_MIN = (size_t)64 << 20;
+int fk_ensure_scratch(fk_ctx* ctx, cudaStream_t st, size_t bytes);
 // `map` points at a CUtensorMap (128 bytes, 64-byte aligned): [outer][inner] 32-bit words, no swizzle
 int fk_make_map_2d(void* map, int dtype, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, int swizzle);
 int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer, uint32_t box_inner, uint32_t box_outer);

@@ -644,7 +644,7 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
     size_t off_src = align_up(off_sx + (size_t)nkb * n_pad * 4, 1024);
     size_t off_out = off_src + (size_t)n_pad * 4, off_te = off_out + (size_t)n_pad * 4;
     size_t off_nt = off_te + (size_t)n_tiles_max * 4, total = off_nt + 16;
-    int rc = fk_ensure_scratch(ctx, total);
+    int rc = fk_ensure_scratch(ctx, st, total);
     if (rc) return rc;
     uint8_t* sc = ctx->scratch;
     int8_t* q = (int8_t*)(sc + off_q);

@@ -394,7 +394,7 @@ int gemm8k(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x, i
     const size_t off_bs = align_up(off_da + (size_t)nsb * n_pad * 4, 1024);
     const size_t off_src = align_up(off_bs + (size_t)n_pad * nsb * 32, 1024);
     const size_t off_out = off_src + (size_t)n_pad * 4, total = off_out + (size_t)n_pad * 4;
-    int rc = fk_ensure_scratch(ctx, total);
+    int rc = fk_ensure_scratch(ctx, st, total);
     if (rc) return rc;
     uint8_t* sc = ctx->scratch;
     int8_t* q = (int8_t*)sc;

@@ -28,6 +28,8 @@
 #include <algorithm>
 #include <string.h>
 
+#include "fk_comm.cuh"
+
 namespace {
 
 constexpr int GEMV_THREADS = 512;   // the tensor-core form (batches of 3..8): one block per SM
@@ -64,6 +66,8 @@ struct GemvArgs {
     int glu_act;           // 0 SiLU, 1 the clamped gpt-oss form
     int accumulate;        // y += result instead of y = result
     int pair_glu;          // rows are (gate, up) pairs: y[rows/2] = act(gate) * up (1 SiLU, 2 the gpt-oss form)
+    int ar_on;             // the epilogue sums the results over the ranks of `ar` (element index: b * rows + row)
+    FkArChannel ar;
     // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
     int q_lp;              // row pairs a warp tile spans (32, 16 or 8; the rest of the lanes span super-blocks)
     int q_sc_off, q_part_off, q_ring_off, q_bar_off;
@@ -732,14 +736,27 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
                     }
                 }
             } else {
+                // row-split across GPUs: every value goes to the peers first, then the peers' values are awaited,
+                // so the link's latency is paid once for the lane's LR * NB values
+                if (a.ar_on) {
+#pragma unroll
+                    for (int r = 0; r < LR; r++)
+#pragma unroll
+                        for (int b = 0; b < NB; b++) {
+                            const int row = row0 + hw * LR + r;
+                            if (writer && row < rows && b < a.batch) fk_ar_send(a.ar, b * rows + row, done[r][b]);
+                        }
+                }
 #pragma unroll
                 for (int r = 0; r < LR; r++)
 #pragma unroll
                     for (int b = 0; b < NB; b++) {
                         const int row = row0 + hw * LR + r;
                         if (writer && row < rows && b < a.batch) {
+                            float v = done[r][b];
+                            if (a.ar_on) v = fk_ar_recv(a.ar, b * rows + row, fk_ar_sent(a.ar)[b * rows + row], v, a.err);
                             float* dst = y + (size_t)b * rows + row;
-                            *dst = a.accumulate ? *dst + done[r][b] : done[r][b];
+                            *dst = a.accumulate ? *dst + v : v;
                         }
                     }
             }
@@ -1382,12 +1399,21 @@ __global__ void __launch_bounds__(GEMV_THREADS, 1) gemv_mma_kernel(const GemvArg
                     }
                 }
             } else {
+                if (a.ar_on) {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
+                        if (row < rows && b < batch) fk_ar_send(a.ar, b * rows + row, acc[i]);
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
                     const int row = rg + 8 * (i >> 1), b = 2 * t + (i & 1);
                     if (row < rows && b < batch) {
+                        float v = acc[i];
+                        if (a.ar_on) v = fk_ar_recv(a.ar, b * rows + row, fk_ar_sent(a.ar)[b * rows + row], v, a.err);
                         float* dst = y + (size_t)b * rows + row;
-                        *dst = a.accumulate ? *dst + acc[i] : acc[i];
+                        *dst = a.accumulate ? *dst + v : v;
                     }
                 }
             }
@@ -1598,7 +1624,7 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
         }
     }
     // the activation image lives in the context's scratch block (stream-ordered like its other users)
-    const int rcs = fk_ensure_scratch(ctx, (size_t)a.m_red_off);
+    const int rcs = fk_ensure_scratch(ctx, st, (size_t)a.m_red_off);
     if (rcs != FK_OK) return rcs;
     const uint8_t* img = ctx->scratch;
     const int gpr = GEMV_WARPS / ks;
@@ -1642,7 +1668,7 @@ int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight
     // 4.3 us against 5.4 us a launch (8192 x 3072).  It waits for its whole share before the first dot product, which
     // costs it inside a decoder step, where the kernel before a matvec is short and hides nothing (688 against 798
     // tokens per second on the 3B Llama shape): the fused and indexed forms keep the general kernel and its rings.
-    const bool plain = !a.ids && !a.n_active && !a.norm_w && !a.glu_up && !a.pair_glu && !a.accumulate;
+    const bool plain = !a.ids && !a.n_active && !a.norm_w && !a.glu_up && !a.pair_glu && !a.accumulate && !a.ar_on;
     if (KIND == FK_Q4_K && a.batch <= 1 && (plain || dump)) {
         bool fits = false;
         const int rc = dump ? launch_q4k<1, true>(ctx, st, a, w, slots, &fits) : launch_q4k<1, false>(ctx, st, a, w, slots, &fits);
@@ -1692,6 +1718,10 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.accumulate = fused->accumulate;
         a.pair_glu = fused->pair_glu;
         if (fused->x_ld) a.x_ld = fused->x_ld;
+        if (fused->ar) {
+            a.ar_on = 1;
+            a.ar = *fused->ar;
+        }
     }
     a.w = w->dev;
     a.mat_stride = w->mat_stride;
@@ -1752,7 +1782,33 @@ FK_EXPORT int fk_gemv_fused(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
         return fk_fail(FK_INVALID, "gemv_fused: inputs must be 16-byte aligned");
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused: activation %d", glu_act);
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, pair_glu};
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, pair_glu, nullptr};
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
+}
+
+// The row-split matvec of a tensor-parallel decode step with its all-reduce in the epilogue: every rank holds the
+// columns [rank * cols, (rank + 1) * cols) of the full matrix as `w`, and
+//   y[b][row] (+)= sum over ranks of W_rank x_rank
+// -- the lane that finishes a row stores its partial into every peer's channel slot (NVLink) and adds what the peers
+// stored here, in rank order, so every rank ends with the same bits.  One launch; the link's latency is paid once at
+// the kernel's tail instead of a second kernel's launch, flag and wait.
+FK_EXPORT int fk_gemv_fused_allreduce(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                                      const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate,
+                                      fk_comm* comm, size_t channel_off, int n_max, int timeout_us) {
+    if (!ctx || !w || !x_dev || !y_dev || !comm) return fk_fail(FK_INVALID, "gemv_fused_allreduce: null argument");
+    if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv_fused_allreduce: batch %d outside 1..8", batch);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_fused_allreduce: matrix %d of %d", mat, w->n_mats);
+    if (x_ld == 0) x_ld = w->cols;
+    if (x_ld < w->cols || (x_ld & 3)) return fk_fail(FK_INVALID, "gemv_fused_allreduce: x_ld %d (columns %d, must be a multiple of 4)", x_ld, w->cols);
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)glu_up_dev & 15) || ((uintptr_t)norm_weight_dev & 15))
+        return fk_fail(FK_INVALID, "gemv_fused_allreduce: inputs must be 16-byte aligned");
+    if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_fused_allreduce: activation %d", glu_act);
+    if ((long long)batch * w->rows > n_max) return fk_fail(FK_INVALID, "gemv_fused_allreduce: %d x %d values do not fit a channel of %d", batch, w->rows, n_max);
+    FkDeviceGuard g(ctx->device);
+    FkArChannel ch;
+    const int rc = fk_ar_channel(comm, channel_off, n_max, timeout_us, &ch);
+    if (rc) return rc;
+    FkGemvFused f{norm_weight_dev, norm_eps, glu_up_dev, glu_act, accumulate, x_ld, 0, comm->world > 1 ? &ch : nullptr};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
 }
 
@@ -1773,7 +1829,7 @@ FK_EXPORT int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const in
     if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_multi_glu: activation %d", glu_act);
     if (((uintptr_t)gate_dev & 15) || ((uintptr_t)up_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_glu: inputs must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
-    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0};
+    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0, nullptr};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, gate_dev, x_stride, 1, y_dev, nullptr, n_active_dev, &f);
 }
 
@@ -1793,7 +1849,7 @@ FK_EXPORT int fk_gemv_isums(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
     if ((uintptr_t)x_dev & 15) return fk_fail(FK_INVALID, "gemv_isums: x_dev must be 16-byte aligned");
     FkDeviceGuard g(ctx->device);
     // y is not wanted: park it in the context's scratch
-    int rc = fk_ensure_scratch(ctx, (size_t)w->rows * sizeof(float));
+    int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)w->rows * sizeof(float));
     if (rc) return rc;
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, 1, (float*)ctx->scratch, isums_dev, nullptr, nullptr);
 }

@@ -120,6 +120,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     }
 }
 
+// Rows [p0, p0 + n_rows) must lie inside a cache of `cache_rows` rows: otherwise the kernel does nothing (every block
+// returns before its first access) and the context's error word becomes 95.
+__device__ __forceinline__ bool fk_cache_overrun(int p0, int n_rows, int cache_rows, int* err) {
+    if (p0 >= 0 && p0 + n_rows <= cache_rows) return false;
+    if (threadIdx.x == 0) atomicCAS(err, 0, 95);
+    return true;
+}
+
 // ---- RoPE in place over [n_rows][n_heads][head_dim]; row r sits at *pos + r.
 __global__ void rope_kernel(float* __restrict__ x, int n_rows, int n_heads, int head_dim, const int* __restrict__ pos, float theta, int neox) {
     const int half = head_dim / 2;
@@ -142,11 +150,12 @@ __global__ void rope_kernel(float* __restrict__ x, int n_rows, int n_heads, int 
 __global__ void rope_kv_kernel(float* __restrict__ q, float* __restrict__ k, const float* __restrict__ v, int q_ld, int kv_ld, int n_rows,
                                int n_heads, int n_kv, int head_dim, const int* __restrict__ pos, float theta, int neox,
                                float* __restrict__ kc, float* __restrict__ vc, const float* __restrict__ q_norm, const float* __restrict__ k_norm,
-                               float eps) {
+                               float eps, int cache_rows, int* __restrict__ err) {
     fk_pdl_sync();
     // a warp per (row, head), q heads first; a lane takes rotation pairs lane, lane + 32, ...
     const int half = head_dim / 2;
     const int p0 = *pos;
+    if (fk_cache_overrun(p0, n_rows, cache_rows, err)) return;
     const int kvw = n_kv * head_dim;
     const int lane = threadIdx.x & 31, wpb = blockDim.x >> 5;
     const int total = n_rows * (n_heads + n_kv);
@@ -196,7 +205,9 @@ __global__ void add_kernel(float* __restrict__ a, const float* __restrict__ b, s
 }
 
 // ---- KV append: rows [*pos, *pos + n_rows) of the cache <- src
-__global__ void kv_append_kernel(float* __restrict__ cache, const float* __restrict__ src, size_t row_elems, int n_rows, const int* __restrict__ pos) {
+__global__ void kv_append_kernel(float* __restrict__ cache, const float* __restrict__ src, size_t row_elems, int n_rows, const int* __restrict__ pos,
+                                 int cache_rows, int* __restrict__ err) {
+    if (fk_cache_overrun(*pos, n_rows, cache_rows, err)) return;
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < row_elems * n_rows) cache[(size_t)(*pos) * row_elems + i] = src[i];
 }
@@ -229,8 +240,10 @@ struct AttnFuse {
 };
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
-            const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt, const AttnFuse f) {
+            const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt, const AttnFuse f,
+            int cache_rows, int* __restrict__ err) {
     fk_pdl_sync();
+    if (fk_cache_overrun(*pos, (int)gridDim.z, cache_rows, err)) return;
     __shared__ __align__(16) float sk_new[128];
     __shared__ __align__(16) float sv_new[128];
     __shared__ double s_red[AD_WARPS];
@@ -401,7 +414,8 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
 constexpr int PF_ROWS = 32, PF_WARPS = 8, PF_RPW = PF_ROWS / PF_WARPS;
 __global__ void __launch_bounds__(PF_WARPS * 32)
 attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_q, int n_heads, int n_kv,
-                    int head_dim, const int* __restrict__ pos, float scale, float* __restrict__ out) {
+                    int head_dim, const int* __restrict__ pos, float scale, float* __restrict__ out, int cache_rows, int* __restrict__ err) {
+    if (fk_cache_overrun(*pos, n_q, cache_rows, err)) return;
     extern __shared__ __align__(16) float sm[];
     const int kpad = head_dim + 4;
     float* sq = sm;                          // [32][head_dim]
@@ -614,8 +628,9 @@ FK_EXPORT int fk_rope(fk_ctx* ctx, void* stream, float* x_dev, int n_rows, int n
 
 FK_EXPORT int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const float* v_dev, int q_ld, int kv_ld, int n_rows,
                          int n_heads, int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev,
-                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps) {
+                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, int cache_rows) {
     if (!ctx || !q_dev || !k_dev || !v_dev || !pos_dev || !k_cache_dev || !v_cache_dev) return fk_fail(FK_INVALID, "rope_kv: null argument");
+    if (cache_rows < n_rows) return fk_fail(FK_INVALID, "rope_kv: %d rows into caches of %d rows", n_rows, cache_rows);
     if (n_rows < 1 || n_heads < 1 || n_kv < 1 || head_dim < 2 || (head_dim & 1)) return fk_fail(FK_INVALID, "rope_kv: bad shape");
     FkDeviceGuard g(ctx->device);
     if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fk_fail(FK_INVALID, "rope_kv: q and k norm weights come together");
@@ -624,7 +639,7 @@ FK_EXPORT int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, 
     if (blocks > 4096) blocks = 4096;
     FK_CARVEOUT(rope_kv_kernel);
     FK_CUDA(fk_launch_pdl(rope_kv_kernel, dim3(blocks), dim3(128), 0, (cudaStream_t)stream, q_dev, k_dev, v_dev, q_ld, kv_ld, n_rows, n_heads, n_kv,
-                          head_dim, pos_dev, theta, neox, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, norm_eps), FK_LAUNCH);
+                          head_dim, pos_dev, theta, neox, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, norm_eps, cache_rows, ctx->err_flag), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
@@ -639,19 +654,22 @@ FK_EXPORT int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev
     return FK_OK;
 }
 
-FK_EXPORT int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev) {
+FK_EXPORT int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev,
+                           int cache_rows) {
     if (!ctx || !cache_dev || !src_dev || !pos_dev || n_rows < 1) return fk_fail(FK_INVALID, "kv_append: bad argument");
+    if (cache_rows < n_rows) return fk_fail(FK_INVALID, "kv_append: %d rows into a cache of %d rows", n_rows, cache_rows);
     FkDeviceGuard g(ctx->device);
     const size_t n = row_elems * n_rows;
     FK_CARVEOUT(kv_append_kernel);
-    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(cache_dev, src_dev, row_elems, n_rows, pos_dev);
+    kv_append_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(cache_dev, src_dev, row_elems, n_rows, pos_dev, cache_rows, ctx->err_flag);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }
 
 FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
-                           int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev) {
+                           int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows) {
     if (!ctx || !q_dev || !k_dev || !v_dev || !pos_dev || !out_dev) return fk_fail(FK_INVALID, "attention: null argument");
+    if (cache_rows < n_q) return fk_fail(FK_INVALID, "attention: %d queries over caches of %d rows", n_q, cache_rows);
     if (n_q < 1 || n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > 65535)
         return fk_fail(FK_UNSUPPORTED, "attention: %d queries, %d/%d heads of %d", n_q, n_heads, n_kv, head_dim);
     if (q_ld == 0) q_ld = n_heads * head_dim;
@@ -662,17 +680,17 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
         FK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
         FK_CARVEOUT(attn_prefill_kernel);
         attn_prefill_kernel<<<dim3((n_q + PF_ROWS - 1) / PF_ROWS, n_heads), PF_WARPS * 32, smem, (cudaStream_t)stream>>>(
-            q_dev, q_ld, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev);
+            q_dev, q_ld, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, cache_rows, ctx->err_flag);
     } else {
         if (n_q * n_heads > AD_MAX_CNT) return fk_fail(FK_UNSUPPORTED, "attention: %d rows x %d heads", n_q, n_heads);
         int splits = 4 * ctx->sm_count / (n_heads * n_q);
         splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
-        const int rc = fk_ensure_scratch(ctx, (size_t)n_q * n_heads * splits * AD_REC * sizeof(float));
+        const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_q * n_heads * splits * AD_REC * sizeof(float));
         if (rc != FK_OK) return rc;
         FK_CARVEOUT(attn_kernel);
         AttnFuse nofuse{};
         FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_q), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, k_dev, v_dev,
-                              n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, nofuse), FK_LAUNCH);
+                              n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, nofuse, cache_rows, ctx->err_flag), FK_LAUNCH);
     }
     FK_LAUNCH_CHECK();
     return FK_OK;
@@ -680,9 +698,10 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
 
 FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
                                    float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
-                                   const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev) {
+                                   const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows) {
     if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !k_cache_dev || !v_cache_dev || !pos_dev || !out_dev)
         return fk_fail(FK_INVALID, "attention_rope_kv: null argument");
+    if (cache_rows < 1) return fk_fail(FK_INVALID, "attention_rope_kv: caches of %d rows", cache_rows);
     if (n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > AD_MAX_CNT)
         return fk_fail(FK_UNSUPPORTED, "attention_rope_kv: %d/%d heads of %d", n_heads, n_kv, head_dim);
     if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fk_fail(FK_INVALID, "attention_rope_kv: q and k norm weights come together");
@@ -690,12 +709,13 @@ FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev
     FkDeviceGuard g(ctx->device);
     int splits = 4 * ctx->sm_count / n_heads;
     splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
-    const int rc = fk_ensure_scratch(ctx, (size_t)n_heads * splits * AD_REC * sizeof(float));
+    const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_heads * splits * AD_REC * sizeof(float));
     if (rc != FK_OK) return rc;
     AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1};
     FK_CARVEOUT(attn_kernel);
     FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, 1), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, n_heads * head_dim, (const float*)k_cache_dev,
-                          (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f), FK_LAUNCH);
+                          (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f, cache_rows,
+                          ctx->err_flag), FK_LAUNCH);
     FK_LAUNCH_CHECK();
     return FK_OK;
 }

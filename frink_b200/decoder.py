@@ -108,6 +108,7 @@ class Decoder:
         if ops is None:
             from . import device as ops
         self.cfg, self.ops, self.group, self.dev = cfg, ops, group, device
+        self.comm = comm
         self.rank, self.world = parallel._world(group) if group is not None or torch.distributed.is_initialized() else (0, 1)
         T = self.world if dense_parallel else 1
         self.t_dense = T
@@ -168,17 +169,26 @@ class Decoder:
             self.layers.append(d)
         self.pos = torch.zeros(1, dtype=torch.int32, device=device)
         self.max_seq = max_seq
+        self._pos_host = 0          # the device position's host mirror: what the cache capacity is checked against
         self._graph = None
 
     def reset(self):
         self.pos.zero_()
+        self._pos_host = 0
+
+    def _claim(self, n):
+        """Refuse, before anything is launched, rows that would run past the KV caches."""
+        if self._pos_host + n > self.max_seq:
+            raise ValueError(f"{n} more rows at position {self._pos_host} do not fit KV caches of {self.max_seq} rows")
+        self._pos_host += n
 
     # ---- one forward over n rows (token ids on the device); returns logits of the last row
     def forward(self, ids):
         ops, cfg = self.ops, self.cfg
         hd = cfg.head_dim
         n = ids.numel()
-        if n <= 8 and self.t_dense == 1 and hasattr(ops, "gemv_fused"):
+        self._claim(n)
+        if n <= 8 and hasattr(ops, "gemv_fused") and (self.t_dense == 1 or self.comm is not None):
             return self._forward_fused(ids)
         x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
         pending = None                                      # a block output not yet added to x
@@ -217,11 +227,21 @@ class Decoder:
         return logits
 
     def _forward_fused(self, ids):
-        """The decode form on one GPU (at most 8 rows): each RMSNorm rides in the prologue of
-        the matvec that reads it, SiLU(gate) * up in the prologue of the down projection, and
-        wo / down add straight into the residual stream; q, k, v stay column slices of the
-        merged projection's output.  Six launches per dense layer."""
+        """The decode form (at most 8 rows): each RMSNorm rides in the prologue of the matvec that
+        reads it, SiLU(gate) * up in the prologue of the down projection, and wo / down add
+        straight into the residual stream; q, k, v stay column slices of the merged projection's
+        output.  Six launches per dense layer.  Tensor-parallel (with a `Comm`): the same six
+        launches on this rank's heads and FFN columns; wo and down are row-split and their
+        matvec's epilogue sums the partial rows over the ranks through peer memory, so the
+        residual stream stays replicated (and bit-identical) on every rank."""
         ops, cfg = self.ops, self.cfg
+
+        def into_residual(lin, inp, is_padded=False, **kw):
+            if isinstance(lin, parallel.RowParallelLinear):
+                ops.gemv_fused(lin.w, inp if is_padded else lin.padded(inp), out=x, accumulate=True, allreduce=(lin.comm, lin.ch), **kw)
+            else:
+                ops.gemv_fused(lin.w, inp, out=x, accumulate=True, **kw)
+
         hd, n = cfg.head_dim, ids.numel()
         hq, kvw = self.h_loc * hd, self.kv_loc * hd
         x = ops.get_rows(self.embd, ids)
@@ -238,14 +258,27 @@ class Decoder:
                 q = ops.gemv_fused(L["wq"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
-            if n == 1 and hasattr(ops, "attention_rope_kv"):
+            window = getattr(L["wo"], "window", None)
+            if n == 1 and hasattr(ops, "attention_rope_kv") and window is not None:
+                # this rank's heads are a K range cut inside the blocks of wo: attention writes straight into the window
+                # of the zero-padded row the local product reads
+                if not hasattr(L["wo"], "row"):
+                    L["wo"].row = torch.zeros((1, L["wo"].cols_local), dtype=torch.float32, device=x.device)
+                ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
+                                      q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps,
+                                      out=L["wo"].row[:, window[0]:window[0] + window[1]])
+                a = None
+            elif n == 1 and hasattr(ops, "attention_rope_kv"):
                 a = ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
                                           q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
             else:
                 ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
                             q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
                 a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
-            ops.gemv_fused(L["wo"].w, a, out=x, accumulate=True)
+            if a is None:
+                into_residual(L["wo"], L["wo"].row, is_padded=True)
+            else:
+                into_residual(L["wo"], a)
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 run_device_routed(L["moe"], h2, ops, residual=x)
@@ -256,10 +289,10 @@ class Decoder:
                     ops.add_(x[t], L["ep"].decode(h2[t]))
             elif "gate_up" in L:
                 act = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, pair_glu=1)
-                ops.gemv_fused(L["down"].w, act, out=x, accumulate=True)
+                into_residual(L["down"], act)
             else:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
-                ops.gemv_fused(L["down"].w, L["gate"](h2), glu_up=L["up"](h2), out=x, accumulate=True)
+                into_residual(L["down"], L["gate"](h2), glu_up=L["up"](h2))
         logits = ops.gemv_fused(self.head, x[n - 1:n], norm_weight=self.out_norm, eps=cfg.eps)
         ops.add_int_(self.pos, n)
         return logits
@@ -279,17 +312,26 @@ class Decoder:
     def capture_decode(self, tok):
         """Capture one decode step (reads `tok`, writes the returned tensor, advances
         the position word) into a CUDA graph; `replay()` runs it again."""
-        pos0 = self.pos.clone()
+        pos0, host0 = self.pos.clone(), self._pos_host
+        if host0 + 2 > self.max_seq:
+            raise ValueError(f"capturing at position {host0} needs two free rows in KV caches of {self.max_seq} rows (the warm-up steps write there)")
         for _ in range(2):                      # warm up outside the capture, then put the position back
             self.decode_step(tok)
         self.pos.copy_(pos0)
+        self._pos_host = host0
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             out = self.decode_step(tok)
         self.pos.copy_(pos0)
+        self._pos_host = host0
         self._graph, self._gout = g, out
         return g, out
+
+    def replay(self):
+        """One more step of the captured graph (the position advances on the device and in its host mirror)."""
+        self._claim(1)
+        self._graph.replay()
 
     def generate(self, prompt_ids, n_new, use_graph=False):
         """Greedy: returns the n_new generated token ids (list of int)."""
@@ -299,7 +341,7 @@ class Decoder:
             cur = tok.clone()
             g, out = self.capture_decode(cur)
             for _ in range(n_new - 1):
-                g.replay()
+                self.replay()
                 cur.copy_(out)
                 outs.append(out.clone())
         else:

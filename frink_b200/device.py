@@ -120,17 +120,27 @@ def gemv(w, x, mat=0, out=None):
     return y if x.dim() > 1 or out is not None else y[0]
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0, allreduce=None):
     """gemv with its elementwise neighbours folded in: reads rmsnorm(x) * norm_weight, or
     act(x) * glu_up (x the gate), and/or adds into `out` instead of overwriting it.
     x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4.
     pair_glu (1 SiLU, 2 gpt-oss): `w` holds gate and up row-interleaved; the result is
-    act(gate) * up, [batch, rows / 2]."""
+    act(gate) * up, [batch, rows / 2].
+    allreduce = (`frink_b200.comm.Comm`, channel): `w` is this rank's column range of a row-split
+    matrix and the result is summed over the ranks by the matvec's epilogue."""
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
     batch, ld = x.shape[0], x.stride(0) if x.shape[0] > 1 else max(x.stride(0), w.cols)
     if glu_up is not None:
         assert glu_up.shape == x.shape and glu_up.stride(1) == 1 and (batch == 1 or glu_up.stride(0) == x.stride(0))
     y = out if out is not None else torch.empty((batch, w.rows // 2 if pair_glu else w.rows), dtype=torch.float32, device=x.device)
+    if allreduce is not None:
+        comm, (off, n_max) = allreduce
+        assert not pair_glu
+        check(lib().fk_gemv_fused_allreduce(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
+                                            _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
+                                            _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate)),
+                                            comm._h, off, n_max, comm.timeout_us))
+        return y
     check(lib().fk_gemv_fused(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
                               _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
                               _ptr(glu_up) if glu_up is not None else None, int(glu_act), int(bool(accumulate)),
@@ -145,7 +155,8 @@ def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache
     assert k.stride(0) == v.stride(0) or n == 1
     check(lib().fk_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), n, n_heads, n_kv, head_dim,
                            _ptr(_i32(pos)), float(theta), int(neox), _ptr(k_cache), _ptr(v_cache),
-                           _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps)))
+                           _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps),
+                           min(k_cache.shape[0], v_cache.shape[0])))
 
 
 def gemv_multi(w, ids, x, out=None):
@@ -361,7 +372,7 @@ def kv_append(cache, src, pos):
     """cache [T, row] rows [*pos, *pos + n) <- src [n, row]."""
     src = _f32(src)
     n = 1 if src.dim() == 1 else src.shape[0]
-    check(lib().fk_kv_append(context(cache.device), _stream(), _ptr(cache), _ptr(src), cache.shape[1], n, _ptr(_i32(pos))))
+    check(lib().fk_kv_append(context(cache.device), _stream(), _ptr(cache), _ptr(src), cache.shape[1], n, _ptr(_i32(pos)), cache.shape[0]))
 
 
 def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
@@ -373,7 +384,7 @@ def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out
     sc = float(scale) if scale is not None else head_dim ** -0.5
     ld = q2.stride(0) if q2.shape[0] > 1 else 0
     check(lib().fk_attention(context(q.device), _stream(), _ptr(q2), ld, _ptr(k_cache), _ptr(v_cache), q2.shape[0], n_heads, n_kv, head_dim,
-                             _ptr(_i32(pos)), sc, _ptr(o)))
+                             _ptr(_i32(pos)), sc, _ptr(o), min(k_cache.shape[0], v_cache.shape[0])))
     return o if q.dim() == 2 else o[0]
 
 
@@ -388,7 +399,7 @@ def attention_rope_kv(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv, head_dim
     check(lib().fk_attention_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), n_heads, n_kv,
                                      head_dim, _ptr(_i32(pos)), sc, float(theta), int(neox),
                                      _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None,
-                                     float(eps), _ptr(o)))
+                                     float(eps), _ptr(o), min(k_cache.shape[0], v_cache.shape[0])))
     return o
 
 

@@ -52,6 +52,59 @@ def shard_cols(raw, kind, rows, cols, rank, world):
     return np.ascontiguousarray(m[:, rank * per:(rank + 1) * per]).ravel(), per * be
 
 
+def mask_outside(raw, kind, rows, cols, lo, hi):
+    """The GGUF bytes with everything outside columns [lo, hi) made to contribute exactly zero, without
+    touching a quant: Q4_K sub-blocks of 32 get scale 0 and min 0, Q6_K groups of 16 get scale 0.  lo and hi
+    are multiples of 32 (Q4_K) / 16 (Q6_K).  The integers of the columns inside are untouched, so a product
+    with the masked matrix is the single-GPU product restricted to the window."""
+    bb, be = BLOCK[kind]
+    m = np.ascontiguousarray(raw, np.uint8).reshape(rows, cols // be, bb).copy()
+    if kind == 12:
+        if lo % 32 or hi % 32:
+            raise ValueError("a Q4_K window is cut in units of 32 columns")
+        sc = m[:, :, 4:16]                      # 8 six-bit scales and 8 six-bit mins in 12 bytes
+        for j in range(cols // 32):
+            if lo <= j * 32 < hi:
+                continue
+            b, k = divmod(j, 8)
+            if k < 4:                           # low six bits of bytes k (scale) and k + 4 (min)
+                sc[:, b, k] &= 0xC0
+                sc[:, b, k + 4] &= 0xC0
+            else:                               # byte k + 4 (low nibbles) and the top two bits of bytes k - 4, k
+                sc[:, b, k + 4] = 0
+                sc[:, b, k - 4] &= 0x3F
+                sc[:, b, k] &= 0x3F
+    elif kind == 14:
+        if lo % 16 or hi % 16:
+            raise ValueError("a Q6_K window is cut in units of 16 columns")
+        sc = m[:, :, 192:208]                   # 16 int8 scales, one per 16 columns in order
+        for j in range(cols // 16):
+            if not lo <= j * 16 < hi:
+                sc[:, j // 16, j % 16] = 0
+    else:
+        raise ValueError("32-wide formats are cut on block boundaries; no mask is needed")
+    return m.ravel()
+
+
+def shard_cols_window(raw, kind, rows, cols, rank, world):
+    """The K range [rank cols/world, (rank+1) cols/world) of every row when it does not fall on the format's
+    block boundaries (3072 columns of a 256-wide format over 8 ranks: 384 columns a rank): the rank holds the
+    whole blocks that cover its range, with the columns outside masked to contribute zero
+    -> (bytes, local cols, offset of the range inside them, its width).  The input of the local product is
+    the rank's activations at [offset, offset + width) of a row of local cols, anything finite elsewhere."""
+    bb, be = BLOCK[kind]
+    if cols % world or (cols // world) % 32:
+        raise ValueError(f"{cols} columns do not split over {world} ranks in units of 32")
+    w = cols // world
+    lo, hi = rank * w, (rank + 1) * w
+    b0, b1 = lo // be, (hi + be - 1) // be
+    nb = max((((r + 1) * w + be - 1) // be) - (r * w) // be for r in range(world))   # the same width on every rank
+    if b0 + nb > cols // be:
+        b0 = cols // be - nb
+    masked = mask_outside(raw, kind, rows, cols, lo, hi).reshape(rows, cols // be, bb)
+    return np.ascontiguousarray(masked[:, b0:b0 + nb]).ravel(), nb * be, lo - b0 * be, w
+
+
 def _world(group=None):
     if not dist.is_available() or not dist.is_initialized():
         return 0, 1
@@ -88,14 +141,31 @@ class RowParallelLinear:
         self.rank, self.world = _world(group)
         self.comm = comm if comm is not None and self.world > 1 else None
         self.ch = self.comm.channel(8 * rows) if self.comm else None
-        local, self.cols_local = shard_cols(raw, kind, rows, cols, self.rank, self.world)
+        bb, be = BLOCK[kind]
+        self.window = None           # (offset, width) when the rank's K range is cut inside blocks
+        if (cols // be) % self.world:
+            local, self.cols_local, off, width = shard_cols_window(raw, kind, rows, cols, self.rank, self.world)
+            self.window = (off, width)
+        else:
+            local, self.cols_local = shard_cols(raw, kind, rows, cols, self.rank, self.world)
         self.rows, self.cols = rows, cols
         self.w = ops.Weights(local, kind, rows, self.cols_local)
+
+    def padded(self, x2):
+        """x2 [n, width] (this rank's K range) as the [n, local cols] input of the local product."""
+        if self.window is None:
+            return x2
+        off, width = self.window
+        p = torch.zeros((x2.shape[0], self.cols_local), dtype=x2.dtype, device=x2.device)
+        p[:, off:off + width] = x2
+        return p
 
     def __call__(self, x):
         x2 = x if x.dim() == 2 else x[None]
         if not self.input_is_sharded:
-            x2 = x2[:, self.rank * self.cols_local:(self.rank + 1) * self.cols_local].contiguous()
+            w_ = self.cols // self.world
+            x2 = x2[:, self.rank * w_:(self.rank + 1) * w_].contiguous()
+        x2 = self.padded(x2)
         y = self.ops.gemv(self.w, x2) if x2.shape[0] <= 8 else self.ops.gemm(self.w, x2)
         if self.world > 1:
             if self.comm is not None and x2.shape[0] <= 8:

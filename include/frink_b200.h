@@ -5,8 +5,20 @@
  * `WeightMatrix` backend seam.  Every entry point below names the frink
  * interface it replaces (file:line inside the frink project, v0.63.0).  All
  * functions return an `fk_status`; a failing call leaves a message that
- * `fk_last_error` returns (per calling thread).  The library is thread safe;
- * no host allocation crosses the ABI (callers pass every output buffer).
+ * `fk_last_error` returns (per calling thread).  No host allocation crosses
+ * the ABI (callers pass every output buffer).
+ *
+ * Threads: calls on different contexts are independent; calls on one context
+ * are serialised where they touch its tables (registration, residency).  The
+ * GEMM, the batch 3..8 matvec, the split attention and fk_gemv_isums use ONE
+ * workspace of the context, in stream order: two streams (or threads) must not
+ * have such calls of one context in flight together.  The workspace only grows
+ * and an outgrown block is kept until fk_destroy, so a launch that is queued,
+ * or captured in a CUDA graph, never points at freed memory; growing it
+ * allocates, which a stream capture forbids, so a call that needs more than is
+ * reserved while its stream is being captured fails with FK_INVALID -- run the
+ * call once before capturing, or fk_reserve_scratch.  64 MiB are taken on
+ * first use.
  *
  * Pointers named `*_dev` are CUDA device pointers on the context's device,
  * pointers named `*_host` are ordinary host memory.  `stream` is a
@@ -238,28 +250,35 @@ int fk_rope(fk_ctx* ctx, void* stream, float* x_dev, int n_rows, int n_heads, in
  * k [n][n_kv*hd] are rotated in place (rows at *pos + r), then k and v rows are
  * written to the caches at *pos.  q_ld / kv_ld = floats between rows.  q_norm_dev /
  * k_norm_dev (both or neither, [head_dim]): the per-head RMSNorm of Qwen3 applied to
- * q and k ahead of the rotation. */
+ * q and k ahead of the rotation.
+ *
+ * cache_rows (here and in the three calls below) is the number of rows T the K/V buffers hold.
+ * The position lives on the device, so the host cannot refuse an overrun: a kernel that finds
+ * *pos + rows > cache_rows does nothing at all and raises the device error word 95. */
 int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const float* v_dev, int q_ld, int kv_ld, int n_rows, int n_heads,
                int n_kv, int head_dim, const int* pos_dev, float theta, int neox, float* k_cache_dev, float* v_cache_dev,
-               const float* q_norm_dev, const float* k_norm_dev, float norm_eps);
+               const float* q_norm_dev, const float* k_norm_dev, float norm_eps, int cache_rows);
+/* Grow the context's workspace to at least `bytes` (it never shrinks). */
+int fk_reserve_scratch(fk_ctx* ctx, size_t bytes);
 /* `add_rows_f32` (kernels.rs:70): a += b. */
 int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n);
 /* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */
-int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev);
+int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev,
+                 int cache_rows);
 /* `causal_gqa_prefill_f32` / `decode_attn_*` (kernels.rs:488, src/decode_attn.rs:125):
  * query row r at position *pos + r attends keys 0..=*pos + r of K/V [T][n_kv][head_dim].
  * q_ld = floats between query rows (0 = n_heads * head_dim).  With fewer than 16 query rows
  * the keys are split over many blocks that meet in a workspace of the context: one such
  * call in flight per context. */
 int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
-                 int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev);
+                 int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows);
 /* One decode row: fk_rope_kv and fk_attention in one launch.  q [n_heads*head_dim], k_new and
  * v_new [n_kv*head_dim] are the projection's outputs for the token at *pos (unrotated); the
  * caches hold positions 0 .. *pos - 1 and receive the rotated k and v at *pos.  q_norm_dev /
  * k_norm_dev as in fk_rope_kv.  One call in flight per context. */
 int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
                          float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
-                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev);
+                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows);
 /* Greedy sampling: index of the largest of each row, ties to the lower index; at most
  * 64 rows per call, and one call in flight per context (it uses a workspace of the context). */
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);
@@ -275,10 +294,16 @@ int fk_add_int(fk_ctx* ctx, void* stream, int* p_dev, int v);
  * channel serves all-reduces of up to n_max floats, one at a time.
  *
  * fk_allreduce: dst = (accumulate ? dst : 0) + sum over ranks of src, the same bits on every
- * rank (slots are added in rank order).  One kernel: peer stores of src into every rank's slot,
- * a flag per rank and part, a wait bounded by timeout_us (0 = two seconds) that raises the
- * device error word 60 instead of hanging, then the sum.  The counters live on the device, so
- * a captured launch may be replayed.  n a multiple of 4, buffers 16-byte aligned. */
+ * rank (values are added in rank order).  One kernel: every value is stored into every peer's
+ * slot together with the all-reduce's number for that element (one 8-byte store, so no fence
+ * and no separate flag), the local slots are read until their number matches -- a wait bounded
+ * by timeout_us (0 = two seconds) that raises the device error word 60 instead of hanging --
+ * and summed.  The per-element numbers live on the device, so a captured launch may be
+ * replayed.  Every rank must issue the same all-reduces on a channel in the same order.
+ *
+ * fk_gemv_fused_allreduce: fk_gemv_fused (without pair_glu) on this rank's column range of a
+ * row-split matrix, the sum over ranks done by the matvec's own epilogue (element b * rows + row
+ * of the channel): the tensor-parallel form of the wo / down projections of a decode step. */
 int fk_comm_create(fk_ctx* ctx, size_t arena_bytes, int rank, int world, uint8_t* handle_out_64, fk_comm** out);
 int fk_comm_connect(fk_comm* comm, const uint8_t* handles_world_x_64);
 /* Test hook: peers given as device pointers of this GPU (the time-out path is tested on one GPU). */
@@ -288,6 +313,9 @@ int fk_comm_destroy(fk_comm* comm);
 size_t fk_comm_channel_bytes(int world, int n_max);
 int fk_allreduce(fk_ctx* ctx, void* stream, fk_comm* comm, size_t channel_off, int n_max, const float* src_dev, float* dst_dev, int n,
                  int accumulate, int timeout_us);
+int fk_gemv_fused_allreduce(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                            const float* norm_weight_dev, float norm_eps, const float* glu_up_dev, int glu_act, int accumulate,
+                            fk_comm* comm, size_t channel_off, int n_max, int timeout_us);
 
 /* ---- host-buffer launch surface -------------------------------------------
  * What frink-core binds (crates/frink-core/src/weight_matrix/gpu_backend.rs:

@@ -333,3 +333,91 @@ def test_one_row_attention_with_rope_and_cache_append_folded_in(neox, norms):
         assert torch.allclose(k1, k0, rtol=1e-6, atol=1e-7) and torch.equal(v1, v0)
         assert torch.allclose(got, want, rtol=1e-5, atol=1e-6), pos_v
     assert device.device_error() == 0
+
+
+def test_rows_past_the_kv_caches_are_refused_on_the_host_and_on_the_device():
+    """The decoder counts positions on the host and raises before launching; the kernels themselves, whose
+    position word lives on the device, do nothing and raise error word 95 when *pos + rows passes the caches."""
+    from frink_b200 import device
+    from frink_b200.decoder import Decoder
+    cfg, layers, tok, out_norm, head = small_llama(uniform=True)
+    dec = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=24)
+    prompt = torch.from_numpy(np.random.default_rng(1).integers(0, cfg.vocab, 20).astype(np.int32)).cuda()
+    t = dec.prefill(prompt)
+    for _ in range(4):
+        t = dec.decode_step(t)
+    with pytest.raises(ValueError):
+        dec.decode_step(t)                      # position 24 of 24
+    dec.reset()
+    dec.prefill(prompt)
+    for _ in range(3):
+        dec.decode_step(t)
+    with pytest.raises(ValueError):
+        dec.capture_decode(t)                   # the two warm-up steps would need rows 23 and 24
+    with pytest.raises(ValueError):
+        dec.forward(prompt)                     # 20 more rows at 23
+    assert device.device_error() == 0
+    # the device-side guard: a cache of 8 rows, position 7, two rows
+    kc, vc = torch.zeros((8, 256), device="cuda"), torch.zeros((8, 256), device="cuda")
+    pos = torch.tensor([7], dtype=torch.int32, device="cuda")
+    q, k, v = torch.randn(2, 512, device="cuda"), torch.randn(2, 256, device="cuda"), torch.randn(2, 256, device="cuda")
+    device.rope_kv(q, k, v, 4, 2, 128, pos, 10000.0, False, kc, vc)
+    torch.cuda.synchronize()
+    assert device.device_error() == 95 and not kc.any() and not vc.any()
+    device.kv_append(kc, k, pos)
+    torch.cuda.synchronize()
+    assert device.device_error() == 95 and not kc.any()
+    out = torch.full((2, 512), 3.0, device="cuda")
+    device.attention(q, kc, vc, 4, 2, 128, pos, out=out)
+    torch.cuda.synchronize()
+    assert device.device_error() == 95 and bool((out == 3.0).all())
+    pos.fill_(8)
+    out1 = torch.full((1, 512), 3.0, device="cuda")
+    device.attention_rope_kv(q[:1], k[:1], v[:1], kc, vc, 4, 2, 128, pos, 10000.0, out=out1)
+    torch.cuda.synchronize()
+    assert device.device_error() == 95 and bool((out1 == 3.0).all()) and not kc.any()
+    pos.fill_(6)                                # rows 6 and 7 fit
+    device.rope_kv(q, k, v, 4, 2, 128, pos, 10000.0, False, kc, vc)
+    torch.cuda.synchronize()
+    assert device.device_error() == 0 and kc[6:].any() and not kc[:6].any()
+
+
+def test_the_workspace_never_moves_under_a_captured_graph(monkeypatch):
+    """A call that needs more workspace than is reserved fails inside a stream capture instead of allocating there;
+    outside a capture the workspace grows, and the block a graph captured earlier points at stays alive and untouched
+    by the move."""
+    import ctypes as C
+    from frink_b200 import _lib, device
+    from frink_b200._lib import check, lib
+    idx = torch.cuda.current_device()
+    device.context()
+    fresh = C.c_void_p()
+    check(lib().fk_init(idx, C.byref(fresh)))
+    monkeypatch.setitem(device._contexts, idx, fresh)          # a context whose workspace is still empty
+    try:
+        raw = fo.encode(fo.Q8_0, synth_weights(256, 1024, 1))
+        w = device.Weights(raw, fo.Q8_0, 256, 1024)
+        small = torch.randn(64, 1024, device="cuda")
+        big = torch.randn(70000, 1024, device="cuda")          # ~80 MB of q8_1 image: more than the 64 MiB taken on first use
+        y, ybig = torch.empty(64, 256, device="cuda"), torch.empty(70000, 256, device="cuda")
+        device.gemm(w, small, out=y)                           # first use reserves the minimum
+        torch.cuda.synchronize()
+        want = y.clone()
+        g = torch.cuda.CUDAGraph()
+        with pytest.raises(_lib.Invalid):
+            with torch.cuda.graph(g):
+                device.gemm(w, big, out=ybig)
+        torch.cuda.synchronize()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            device.gemm(w, small, out=y)
+        device.gemm(w, big, out=ybig)                          # grows the workspace: the old block stays
+        torch.cuda.synchronize()
+        assert torch.isfinite(ybig).all()
+        y.zero_()
+        g2.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y, want) and device.device_error() == 0
+        w.release()
+    finally:
+        lib().fk_destroy(fresh)

@@ -223,3 +223,50 @@ def test_decoder_sharded_over_two_ranks_matches_one(moe):
             assert rel_l2(a, b) <= 1e-4
     for a, b in zip(got[0], got[1]):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("kind", [fo.Q4_K, fo.Q6_K])
+def test_a_k_range_cut_inside_blocks_is_the_product_restricted_to_the_window(kind):
+    """3072 columns over 8 ranks: 384 columns a rank, one and a half 256-wide blocks.  Each rank holds whole
+    blocks with the columns outside its window masked (scales zeroed, quants untouched); the partial
+    products over the padded inputs add up to the unsharded product, and what a rank's shard decodes to
+    is the matrix inside its window and zero outside."""
+    from frink_b200 import parallel
+    rows, cols, world = 24, 3072, 8
+    raw = fo.encode(kind, synth_weights(rows, cols, 21))
+    x = np.random.default_rng(3).standard_normal((2, cols)).astype(np.float32)
+    xq = fo.q8_1_round(x)
+    want = fo.matmul_f64(kind, raw, rows, cols, xq)
+    full = fo.dequant(kind, raw).reshape(rows, cols)
+    total = np.zeros_like(want)
+    for rank in range(world):
+        loc, cl, off, width = parallel.shard_cols_window(raw, kind, rows, cols, rank, world)
+        assert width == 384 and cl == 512 and off in (0, 128)
+        lo = rank * width
+        dq = fo.dequant(kind, loc).reshape(rows, cl)
+        assert np.array_equal(dq[:, off:off + width], full[:, lo:lo + width])
+        assert not dq[:, :off].any() and not dq[:, off + width:].any()
+        xp = np.full((2, cl), 7.0, np.float32)           # anything finite outside the window
+        xp[:, off:off + width] = x[:, lo:lo + width]
+        total += fo.matmul_f64(kind, loc, rows, cl, fo.q8_1_round(xp))
+    assert rel_l2(total, want) <= 1e-6
+
+
+def _row_window_case(rank, world):
+    from frink_b200 import parallel
+    from tests import cpu_ops
+    raw = fo.encode(fo.Q4_K, synth_weights(16, 1536, 31))
+    x = torch.from_numpy(np.random.default_rng(6).standard_normal((2, 1536)).astype(np.float32))
+    lin = parallel.RowParallelLinear(cpu_ops, raw, fo.Q4_K, 16, 1536, input_is_sharded=True)
+    assert lin.window is not None and lin.cols_local == 512
+    return lin(x[:, rank * 384:(rank + 1) * 384].contiguous()).numpy()
+
+
+def test_row_split_over_four_ranks_of_six_blocks():
+    """1536 columns (six Q4_K blocks) over four ranks: every rank's 384 columns are cut inside a block."""
+    from tests import cpu_ops
+    raw = fo.encode(fo.Q4_K, synth_weights(16, 1536, 31))
+    x = torch.from_numpy(np.random.default_rng(6).standard_normal((2, 1536)).astype(np.float32))
+    want = cpu_ops.gemv(cpu_ops.Weights(raw, fo.Q4_K, 16, 1536), x).numpy()
+    for y in spawn(_row_window_case, world=4):
+        assert rel_l2(y, want) <= 1e-5
