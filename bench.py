@@ -233,6 +233,8 @@ def main():
     ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
                     help="whole-model pp512 / tg128 tokens per second (the Llama-3.2-3B and Qwen3-30B-A3B shapes) instead of the GEMV line")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
+    ap.add_argument("--profile-region", choices=["pp", "tg", "tg_batch8"], default=None,
+                    help="with --model: bracket this timed region with cudaProfilerStart/Stop (for a profiler run with capture off at start)")
     ap.add_argument("--watchdog", type=int, default=0, help="seconds after which all thread stacks are printed and the process exits")
     ap.add_argument("--no-tp-graph", action="store_true", help="--model under torchrun: launch the decode step eagerly instead of replaying a CUDA graph with the collectives captured")
     ap.add_argument("--nccl-only", action="store_true", help="under torchrun: sum decode rows with NCCL instead of the peer-memory all-reduce")
@@ -453,7 +455,10 @@ def synth_model(name, n_layers=0):
     rng = np.random.default_rng(0x5EED0000)
     H, hd = cfg.hidden, cfg.head_dim
     cache = {}
-    norm = lambda n: (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)   # not all ones: the stream must not settle on one token
+    # Norm weights of random sign: layers reuse two sets of matrix bytes, and the same matrices applied over and over
+    # would pull the residual stream onto their dominant direction (one token for ever, one route through the experts);
+    # a different sign pattern on every layer's input channels makes the layers act like different matrices.
+    norm = lambda n: ((1.0 + 0.1 * rng.standard_normal(n)) * rng.choice([-1.0, 1.0], n)).astype(np.float32)
 
     def enc(tag, kind, rows, cols, variant):
         key = (tag, kind, rows, cols, variant)
@@ -513,7 +518,7 @@ def synth_model(name, n_layers=0):
 MODEL_ROOFLINE = {"llama3b": {"bytes_per_token": 2010839040, "pp512_flops": 2.89e12}}
 
 
-def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None):
+def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_region=None):
     """pp512 / tg128 of a random-init model of the named shape: prefill of 512 random
     token ids (GEMM path), then 128 greedy tokens with the decode step replayed from a
     CUDA graph.  Under torchrun, dense layers are tensor parallel (NCCL all-reduce after
@@ -543,13 +548,17 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn):
+    def timed(fn, region=None):
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if region is not None and region == profile_region:
+            torch.cuda.profiler.start()      # a profiler started with its capture off takes only this region
         e0.record()
         r = fn()
         e1.record()
         sync()
+        if region is not None and region == profile_region:
+            torch.cuda.profiler.stop()
         ms = e0.elapsed_time(e1)
         if world > 1:
             t = torch.tensor([ms], device="cuda")
@@ -560,7 +569,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None):
     pp = []
     for _ in range(1 + 3):       # one warm-up, three timed
         dec.reset()
-        ms, first = timed(lambda: dec.prefill(prompt))
+        ms, first = timed(lambda: dec.prefill(prompt), "pp" if _ == 3 else None)
         pp.append(ms)
     pp_ms = float(np.median(pp[1:]))
     cur = first.clone()
@@ -580,13 +589,40 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None):
         for _ in range(G):
             step()
             toks.append(cur.clone())
-    tg_ms, _ = timed(run_decode)
+    tg_ms, _ = timed(run_decode, "tg")
+    # ---- a decode batch of eight independent sequences (their own KV caches and positions), one token each per step
+    b8 = None
+    if use_graph and (world == 1 or comm is not None):
+        del step, g, out
+        dec._graph = dec._gout = None
+        NB8 = 8
+        dec.alloc_seqs(NB8)
+        cur8 = torch.cat([dec.prefill_seq(s_, prompt) for s_ in range(NB8)])
+        # the sequences start from different tokens so that their routes differ
+        cur8 = ((cur8 + torch.arange(NB8, device="cuda", dtype=torch.int32) * 37) % cfg.vocab).to(torch.int32).contiguous()
+        g8, out8 = dec.capture_decode_seqs(cur8)
+        step8 = lambda: (dec.replay_seqs(), cur8.copy_(out8))
+        for _ in range(3):
+            step8()
+        seen8 = []
+
+        def run8():
+            for _ in range(G):
+                step8()
+                seen8.append(cur8.clone())
+        b8_ms, _ = timed(run8, "tg_batch8")
+        b8 = {"sequences": NB8, "steps": G, "ms": b8_ms, "tok_s": NB8 * G / (b8_ms * 1e-3),
+              "distinct_tokens": len({int(v) for t_ in seen8 for v in t_.tolist()})}
+        sync()
+        del step8, g8, out8
+        dec._graph_seqs = None
+        use_graph = False
     err = device.device_error()
     wbytes = sum(v.w.gguf_bytes for L in dec.layers for v in L.values() if hasattr(v, "w") and hasattr(v.w, "gguf_bytes"))
     res = {
         "model": name, "n_gpus": world, "layers": cfg.n_layers,
         "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
-        "decode_graph": bool(use_graph), "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
+        "decode_graph": bool(world == 1 or tp_graph), "tg_batch8": b8, "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
         "collective": None if world == 1 else (
             ("all-reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts else
              "all-reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer") +
@@ -616,7 +652,7 @@ def model_bench(args, rank, world, local):
     if world > 1 and not args.nccl_only:
         from frink_b200.comm import Comm
         comm = Comm(arena_bytes=512 << 20)
-    res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph, comm)
+    res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph, comm, args.profile_region)
     if rank == 0:
         res["metric"] = "pp512_tg128_tok_s"
         print(json.dumps(res))

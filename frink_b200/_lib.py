@@ -34,6 +34,7 @@ SYMBOLS = {
     "fk_gemv_multi": (_I, [_P, _P, _P, _P, _I, _P, _I, _P]),
     "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),
+    "fk_moe_local_pairs": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "fk_moe_local_slots": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "fk_moe_localize": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),
     "fk_gemv_isums": (_I, [_P, _P, _P, _I, _P, _P]),
@@ -57,6 +58,7 @@ SYMBOLS = {
     "fk_add": (_I, [_P, _P, _P, _P, _SZ]),
     "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P, _I]),
     "fk_attention_rope_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I]),
+    "fk_attention_rope_kv_seqs": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _SZ, _I, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I]),
     "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P, _I]),
     "fk_reserve_scratch": (_I, [_P, _SZ]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),

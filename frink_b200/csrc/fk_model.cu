@@ -237,13 +237,23 @@ struct AttnFuse {
     const float* k_norm;
     float theta, eps;
     int neox, on;
+    // independent sequences (seq_stride != 0): query row r is sequence r's newest token, at position pos[r], with its own
+    // caches r * seq_stride floats further on; k_new / v_new rows are k_ld / v_ld floats apart
+    size_t seq_stride;
+    int k_ld, v_ld;
 };
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
             const int* __restrict__ pos, float scale, float* __restrict__ out, float* __restrict__ ws, unsigned* __restrict__ cnt, const AttnFuse f,
             int cache_rows, int* __restrict__ err) {
     fk_pdl_sync();
-    if (fk_cache_overrun(*pos, (int)gridDim.z, cache_rows, err)) return;
+    const bool per_seq = f.seq_stride != 0;
+    const int p_row = per_seq ? pos[blockIdx.z] : *pos + (int)blockIdx.z;     // this query row's position
+    if (per_seq ? fk_cache_overrun(p_row, 1, cache_rows, err) : fk_cache_overrun(*pos, (int)gridDim.z, cache_rows, err)) return;
+    if (per_seq) {
+        kbuf += (size_t)blockIdx.z * f.seq_stride;
+        vbuf += (size_t)blockIdx.z * f.seq_stride;
+    }
     __shared__ __align__(16) float sk_new[128];
     __shared__ __align__(16) float sv_new[128];
     __shared__ double s_red[AD_WARPS];
@@ -253,7 +263,7 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
     __shared__ bool last;
     const int split = blockIdx.x, S = gridDim.x, h = blockIdx.y, r = blockIdx.z, kvh = h / (n_heads / n_kv);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
-    const int n_keys = *pos + r + 1;
+    const int n_keys = p_row + 1;
     const int chunk = ((n_keys + S - 1) / S + 15) & ~15;
     const int c0 = split * chunk, c1 = min(n_keys, c0 + chunk);
     const float* qr = q + (size_t)r * q_ld + (size_t)h * head_dim;
@@ -297,15 +307,16 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
         rope_head(sq, f.q_norm);
         if (has_new) {
             for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
-                sk_new[i] = f.k_new[(size_t)kvh * head_dim + i];
-                sv_new[i] = f.v_new[(size_t)kvh * head_dim + i];
+                sk_new[i] = f.k_new[(size_t)r * f.k_ld + (size_t)kvh * head_dim + i];
+                sv_new[i] = f.v_new[(size_t)r * f.v_ld + (size_t)kvh * head_dim + i];
             }
             __syncthreads();
             rope_head(sk_new, f.k_norm);
             if (h % (n_heads / n_kv) == 0) {
                 for (int i = threadIdx.x; i < head_dim; i += blockDim.x) {
-                    f.kc[(size_t)p_new * kv_stride + (size_t)kvh * head_dim + i] = sk_new[i];
-                    f.vc[(size_t)p_new * kv_stride + (size_t)kvh * head_dim + i] = sv_new[i];
+                    const size_t at = (size_t)r * f.seq_stride + (size_t)p_new * kv_stride + (size_t)kvh * head_dim + i;
+                    f.kc[at] = sk_new[i];
+                    f.vc[at] = sv_new[i];
                 }
             }
         }
@@ -711,9 +722,39 @@ FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev
     splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
     const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_heads * splits * AD_REC * sizeof(float));
     if (rc != FK_OK) return rc;
-    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1};
+    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, 0, 0, 0};
     FK_CARVEOUT(attn_kernel);
     FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, 1), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, n_heads * head_dim, (const float*)k_cache_dev,
+                          (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f, cache_rows,
+                          ctx->err_flag), FK_LAUNCH);
+    FK_LAUNCH_CHECK();
+    return FK_OK;
+}
+
+// One decode step of n_seqs independent sequences: row r of q / k_new / v_new is sequence r's newest token at position
+// pos[r]; sequence r's caches start r * seq_stride floats into k_cache_dev / v_cache_dev.
+FK_EXPORT int fk_attention_rope_kv_seqs(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_new_dev, const float* v_new_dev, int k_ld,
+                                        int v_ld, float* k_cache_dev, float* v_cache_dev, size_t seq_stride, int n_seqs, int n_heads, int n_kv, int head_dim,
+                                        const int* pos_dev, float scale, float theta, int neox, const float* q_norm_dev, const float* k_norm_dev,
+                                        float norm_eps, float* out_dev, int cache_rows) {
+    if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !k_cache_dev || !v_cache_dev || !pos_dev || !out_dev)
+        return fk_fail(FK_INVALID, "attention_rope_kv_seqs: null argument");
+    if (n_seqs < 1 || n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_seqs * n_heads > AD_MAX_CNT)
+        return fk_fail(FK_UNSUPPORTED, "attention_rope_kv_seqs: %d sequences, %d/%d heads of %d", n_seqs, n_heads, n_kv, head_dim);
+    if ((q_norm_dev == nullptr) != (k_norm_dev == nullptr)) return fk_fail(FK_INVALID, "attention_rope_kv_seqs: q and k norm weights come together");
+    if ((((uintptr_t)q_dev | (uintptr_t)k_new_dev | (uintptr_t)v_new_dev) & 15) || (q_ld & 3) || (k_ld & 3) || (v_ld & 3) || q_ld < n_heads * head_dim ||
+        k_ld < n_kv * head_dim || v_ld < n_kv * head_dim)
+        return fk_fail(FK_INVALID, "attention_rope_kv_seqs: inputs must be 16-byte aligned, row strides multiples of 4 and at least a row");
+    if (cache_rows < 1 || seq_stride < (size_t)cache_rows * n_kv * head_dim)
+        return fk_fail(FK_INVALID, "attention_rope_kv_seqs: caches of %d rows, %zu floats apart", cache_rows, seq_stride);
+    FkDeviceGuard g(ctx->device);
+    int splits = 4 * ctx->sm_count / (n_heads * n_seqs);
+    splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
+    const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_seqs * n_heads * splits * AD_REC * sizeof(float));
+    if (rc != FK_OK) return rc;
+    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, seq_stride, k_ld, v_ld};
+    FK_CARVEOUT(attn_kernel);
+    FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_seqs), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, (const float*)k_cache_dev,
                           (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f, cache_rows,
                           ctx->err_flag), FK_LAUNCH);
     FK_LAUNCH_CHECK();

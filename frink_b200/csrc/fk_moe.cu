@@ -234,6 +234,42 @@ __global__ void localize_kernel(const int* __restrict__ ids, const float* __rest
     w_out[i] = mine ? w[i] : 0.0f;
 }
 
+// A decode batch under expert parallelism: of the `pairs` (row, chosen expert) pairs of b rows (pair i belongs to row
+// i / k), those whose expert lies in [e0, e0 + n_local) are packed to the front as slots, in pair order:
+//   out_ids[p] local expert, out_src[p] row of the slot's activation (both 0 past the last slot),
+//   out_pair_of[i] slot of pair i (0 for another rank's pair), out_w[i] its weight (0 for another rank's pair),
+//   *out_n the number of slots.  One block; pairs <= 256.
+__global__ void __launch_bounds__(256) local_pairs_kernel(const int* __restrict__ ids, const float* __restrict__ w, int pairs, int k, int e0,
+                                                          int n_local, int* __restrict__ out_ids, int* __restrict__ out_src,
+                                                          int* __restrict__ out_pair_of, float* __restrict__ out_w, int* __restrict__ out_n) {
+    __shared__ int s_cnt[8];
+    const int i = threadIdx.x, lane = i & 31, warp = i >> 5;
+    const int id = i < pairs ? ids[i] : -1;
+    const bool mine = id >= e0 && id < e0 + n_local;
+    const unsigned m = __ballot_sync(0xffffffffu, mine);
+    if (lane == 0) s_cnt[warp] = __popc(m);
+    if (i < pairs) {
+        out_ids[i] = 0;
+        out_src[i] = 0;
+    }
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int v = 0; v < 8; v++) {
+        if (v < warp) before += s_cnt[v];
+        total += s_cnt[v];
+    }
+    const int p = before + __popc(m & ((1u << lane) - 1u));
+    if (mine) {
+        out_ids[p] = id - e0;
+        out_src[p] = i / k;
+    }
+    if (i < pairs) {
+        out_pair_of[i] = mine ? p : 0;
+        out_w[i] = mine ? w[i] : 0.0f;
+    }
+    if (i == 0) *out_n = total;
+}
+
 // Every kernel of a decode step asks for the same shared-memory carve-out as the GEMV
 // (the maximum): an SM that alternates between kernels with different carve-outs
 // re-partitions its L1 between them, which costs more than these kernels run.
@@ -255,6 +291,20 @@ FK_EXPORT int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, 
     FkDeviceGuard g(ctx->device);
     FK_CARVEOUT(local_slots_kernel);
     local_slots_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(ids_dev, w_dev, k, e0, n_local, out_ids_dev, out_w_dev, out_n_dev);
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+FK_EXPORT int fk_moe_local_pairs(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int pairs, int k, int e0, int n_local,
+                                 int* out_ids_dev, int* out_src_dev, int* out_pair_of_dev, float* out_w_dev, int* out_n_dev) {
+    if (!ctx || !ids_dev || !w_dev || !out_ids_dev || !out_src_dev || !out_pair_of_dev || !out_w_dev || !out_n_dev)
+        return fk_fail(FK_INVALID, "moe_local_pairs: null argument");
+    if (k < 1 || pairs < 1 || pairs > 256 || pairs % k) return fk_fail(FK_UNSUPPORTED, "moe_local_pairs: %d pairs of k=%d (limit 256)", pairs, k);
+    FkDeviceGuard g(ctx->device);
+    FK_CARVEOUT(local_pairs_kernel);
+    local_pairs_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(ids_dev, w_dev, pairs, k, e0, n_local, out_ids_dev, out_src_dev, out_pair_of_dev, out_w_dev,
+                                                            out_n_dev);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;

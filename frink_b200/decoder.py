@@ -16,7 +16,7 @@ from typing import Any, List, Optional
 import torch
 
 from . import parallel
-from .prefill import RoutedLayer, run_device_routed, run_device_routed_batch
+from .prefill import RoutedLayer, run_device_routed, run_device_routed_batch, run_device_routed_rows
 
 
 @dataclass
@@ -226,7 +226,70 @@ class Decoder:
         ops.add_int_(self.pos, n)
         return logits
 
-    def _forward_fused(self, ids):
+    # ---- batched decode: several independent sequences, one token each per step
+    def alloc_seqs(self, n_seqs):
+        """KV caches and positions for n_seqs (<= 8) independent sequences, decoded together by `forward_seqs`."""
+        if not 1 <= n_seqs <= 8:
+            raise ValueError("a decode batch holds 1 to 8 sequences")
+        for L in self.layers:
+            L["ks"] = torch.zeros((n_seqs,) + tuple(L["k"].shape), dtype=torch.float32, device=L["k"].device)
+            L["vs"] = torch.zeros_like(L["ks"])
+        self.seq_pos = torch.zeros(n_seqs, dtype=torch.int32, device=self.pos.device)
+        self._seq_pos_host = [0] * n_seqs
+
+    def prefill_seq(self, s, prompt_ids):
+        """Sequence s's prompt through the ordinary forward, on that sequence's caches -> its first generated token."""
+        saved = [(L["k"], L["v"]) for L in self.layers]
+        pos0, host0 = self.pos.clone(), self._pos_host
+        try:
+            for L in self.layers:
+                L["k"], L["v"] = L["ks"][s], L["vs"][s]
+            self.reset()
+            tok = self.ops.argmax(self.forward(prompt_ids))
+            self.seq_pos[s:s + 1].copy_(self.pos)
+            self._seq_pos_host[s] = self._pos_host
+        finally:
+            for L, (k_, v_) in zip(self.layers, saved):
+                L["k"], L["v"] = k_, v_
+            self.pos.copy_(pos0)
+            self._pos_host = host0
+        return tok
+
+    def forward_seqs(self, toks):
+        """toks [n_seqs] (device int32), sequence r's newest token -> logits [n_seqs, vocab]; every position advances."""
+        n = toks.numel()
+        if n != len(self._seq_pos_host):
+            raise ValueError(f"{n} tokens for {len(self._seq_pos_host)} sequences")
+        if max(self._seq_pos_host) + 1 > self.max_seq:
+            raise ValueError(f"a sequence at position {max(self._seq_pos_host)} has filled its KV cache of {self.max_seq} rows")
+        self._seq_pos_host = [p + 1 for p in self._seq_pos_host]
+        return self._forward_fused(toks, seqs=True)
+
+    def capture_decode_seqs(self, toks):
+        """`forward_seqs` + argmax captured in a CUDA graph (reads `toks`, returns the graph and the next tokens)."""
+        pos0, host0 = self.seq_pos.clone(), list(self._seq_pos_host)
+        if max(host0) + 2 > self.max_seq:
+            raise ValueError("capturing needs two free rows in every KV cache (the warm-up steps write there)")
+        for _ in range(2):
+            self.ops.argmax(self.forward_seqs(toks))
+        self.seq_pos.copy_(pos0)
+        self._seq_pos_host = list(host0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = self.ops.argmax(self.forward_seqs(toks))
+        self.seq_pos.copy_(pos0)
+        self._seq_pos_host = list(host0)
+        self._graph_seqs = g
+        return g, out
+
+    def replay_seqs(self):
+        if max(self._seq_pos_host) + 1 > self.max_seq:
+            raise ValueError(f"a sequence has filled its KV cache of {self.max_seq} rows")
+        self._seq_pos_host = [p + 1 for p in self._seq_pos_host]
+        self._graph_seqs.replay()
+
+    def _forward_fused(self, ids, seqs=False):
         """The decode form (at most 8 rows): each RMSNorm rides in the prologue of the matvec that
         reads it, SiLU(gate) * up in the prologue of the down projection, and wo / down add
         straight into the residual stream; q, k, v stay column slices of the merged projection's
@@ -259,7 +322,10 @@ class Decoder:
                 k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
                 v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
             window = getattr(L["wo"], "window", None)
-            if n == 1 and hasattr(ops, "attention_rope_kv") and window is not None:
+            if seqs:
+                a = ops.attention_rope_kv_seqs(q, k, v, L["ks"], L["vs"], self.h_loc, self.kv_loc, hd, self.seq_pos, cfg.rope_theta, cfg.neox,
+                                               q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
+            elif n == 1 and hasattr(ops, "attention_rope_kv") and window is not None:
                 # this rank's heads are a K range cut inside the blocks of wo: attention writes straight into the window
                 # of the zero-padded row the local product reads
                 if not hasattr(L["wo"], "row"):
@@ -272,6 +338,8 @@ class Decoder:
                 a = ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
                                           q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
             else:
+                if n > 1 and k.stride(0) != v.stride(0):
+                    k, v = k.contiguous(), v.contiguous()          # the cache append wants one row stride for both
                 ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
                             q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
                 a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
@@ -281,18 +349,27 @@ class Decoder:
                 into_residual(L["wo"], a)
             if "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
-                run_device_routed(L["moe"], h2, ops, residual=x)
+                if n > 1 and hasattr(ops, "gemv_multi_glu"):
+                    run_device_routed_rows(L["moe"], h2, ops, residual=x)      # all rows' (row, expert) pairs as slots of one launch
+                else:
+                    run_device_routed(L["moe"], h2, ops, residual=x)
             elif "ep" in L:
                 # experts spread over the ranks, everything else replicated: the one collective of the layer
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
-                for t in range(n):
-                    ops.add_(x[t], L["ep"].decode(h2[t]))
+                if n > 1:
+                    ops.add_(x, L["ep"].decode_rows(h2))
+                else:
+                    ops.add_(x[0], L["ep"].decode(h2[0]))
             elif "gate_up" in L:
                 act = ops.gemv_fused(L["gate_up"].w, x, norm_weight=L["ffn_norm"], eps=cfg.eps, pair_glu=1)
                 into_residual(L["down"], act)
             else:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 into_residual(L["down"], L["gate"](h2), glu_up=L["up"](h2))
+        if seqs:
+            logits = ops.gemv_fused(self.head, x, norm_weight=self.out_norm, eps=cfg.eps)
+            self.seq_pos.add_(1)
+            return logits
         logits = ops.gemv_fused(self.head, x[n - 1:n], norm_weight=self.out_norm, eps=cfg.eps)
         ops.add_int_(self.pos, n)
         return logits

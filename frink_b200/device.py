@@ -198,6 +198,20 @@ def moe_local_slots(ids, w, e0, n_local):
     return oi, ow, on
 
 
+def moe_local_pairs(ids, w, e0, n_local):
+    """ids, w [b, k] -> (local expert per slot, source row per slot, slot of each pair, weight of each pair, slot count):
+    the pairs this rank's experts serve, packed to the front as slots."""
+    ids, w = _i32(ids), _f32(w)
+    k, pairs = ids.shape[-1], ids.numel()
+    oi = torch.empty(pairs, dtype=torch.int32, device=ids.device)
+    src, po = torch.empty_like(oi), torch.empty_like(oi)
+    ow = torch.empty(pairs, dtype=torch.float32, device=ids.device)
+    on = torch.empty(1, dtype=torch.int32, device=ids.device)
+    check(lib().fk_moe_local_pairs(context(ids.device), _stream(), _ptr(ids), _ptr(w), pairs, k, e0, n_local, _ptr(oi), _ptr(src), _ptr(po), _ptr(ow),
+                                   _ptr(on)))
+    return oi, src, po, ow, on
+
+
 def moe_localize(ids, w, e0, n_local):
     """ids, w [batch, k] -> local ids (n_local where another rank owns the expert) and weights (0 there)."""
     ids, w = _i32(ids), _f32(w)
@@ -400,6 +414,23 @@ def attention_rope_kv(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv, head_dim
                                      head_dim, _ptr(_i32(pos)), sc, float(theta), int(neox),
                                      _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None,
                                      float(eps), _ptr(o), min(k_cache.shape[0], v_cache.shape[0])))
+    return o
+
+
+def attention_rope_kv_seqs(q, k_new, v_new, k_caches, v_caches, n_heads, n_kv, head_dim, pos, theta, neox=False, q_norm=None, k_norm=None,
+                           eps=0.0, scale=None, out=None):
+    """One decode step of independent sequences: row r of q / k_new / v_new (column slices are fine) is sequence r's
+    token at position pos[r]; k_caches / v_caches are [n_seqs, T, n_kv*head_dim]."""
+    n = q.shape[0]
+    assert k_caches.dim() == 3 and k_caches.is_contiguous() and v_caches.is_contiguous() and k_caches.shape == v_caches.shape and k_caches.shape[0] >= n
+    assert q.stride(-1) == 1 and k_new.stride(-1) == 1 and v_new.stride(-1) == 1
+    assert pos.dtype == torch.int32 and pos.numel() >= n
+    o = out if out is not None else torch.empty((n, n_heads * head_dim), dtype=torch.float32, device=q.device)
+    sc = float(scale) if scale is not None else head_dim ** -0.5
+    check(lib().fk_attention_rope_kv_seqs(context(q.device), _stream(), _ptr(q), q.stride(0), _ptr(k_new), _ptr(v_new), k_new.stride(0), v_new.stride(0),
+                                          _ptr(k_caches), _ptr(v_caches), k_caches.stride(0), n, n_heads, n_kv, head_dim, _ptr(pos), sc,
+                                          float(theta), int(neox), _ptr(_f32(q_norm)) if q_norm is not None else None,
+                                          _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps), _ptr(o), k_caches.shape[1]))
     return o
 
 

@@ -268,7 +268,40 @@ class ExpertParallelLayer:
         y = ops.gemm_grouped(L.down, group_off, None, a, pairs, out=y)
         out = ops.moe_combine(y, pair_of, lw, b, k)
         if self.world > 1:
-            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+            if self.comm is not None and b <= 8:
+                self.comm.all_reduce(self.ch, out)
+            else:
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def decode_rows(self, x):
+        """A decode batch of independent rows x [b <= 8, hidden] (replicated on every rank): the (row, expert) pairs this
+        rank's experts serve become the slots of one indexed launch per projection -- packed to the front on the device,
+        the launches skip the rest -- and one all-reduce sums the weighted partial rows over the ranks."""
+        from .prefill import route
+        ops, L, k = self.ops, self.layer, self.k
+        b = x.shape[0]
+        if not hasattr(ops, "moe_local_pairs"):
+            return self.prefill_replicated(x)
+        ids, w = route(L, x, ops)
+        lid, src, pair_of, lw, n = ops.moe_local_pairs(ids, w, self.e0, self.n_local)
+        xg = x.index_select(0, src)                      # slot p reads the row its pair came from
+        pairs = b * k
+        if getattr(self, "_rows_buf", None) is None or self._rows_buf[0].shape[0] != pairs:
+            # slots past the count are skipped by the launches: what they hold must stay finite (it is weighted by 0)
+            self._rows_buf = (torch.zeros((pairs, self.ffn), dtype=torch.float32, device=x.device),
+                              torch.zeros((pairs, self.ffn), dtype=torch.float32, device=x.device),
+                              torch.zeros((pairs, self.hidden), dtype=torch.float32, device=x.device))
+        g, u, y = self._rows_buf
+        ops.gemv_multi_active(L.gate, lid, xg, n, g)
+        ops.gemv_multi_active(L.up, lid, xg, n, u)
+        ops.gemv_multi_glu(L.down, lid, g, u, L.act, out=y, n_active=n)
+        out = ops.moe_combine(y, pair_of, lw, b, k)
+        if self.world > 1:
+            if self.comm is not None:
+                self.comm.all_reduce(self.ch, out)
+            else:
+                dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.group)
         return out
 
     # ---- prefill: tokens sharded over ranks, dispatch / combine all-to-all.  Every rank of the group must call

@@ -74,6 +74,25 @@ def run_device_routed(layer, x, ops=None, residual=None):
     return ops.moe_combine(y, None, w, 1, layer.k)[0]
 
 
+def run_device_routed_rows(layer, x, ops=None, residual=None):
+    """Decode of a few independent rows x [b, hidden] (b <= 8) at once: every (row, chosen expert) pair is a slot of
+    ONE indexed launch per projection -- b * k slots, the row's activation repeated for its k slots."""
+    ops = _ops(ops)
+    b = x.shape[0]
+    ids, w = route(layer, x, ops)                         # [b, k]
+    ids1 = ids.reshape(-1)
+    xr = x.repeat_interleave(layer.k, dim=0)              # slot j reads row j // k
+    g = ops.gemv_multi(layer.gate, ids1, xr)
+    u = ops.gemv_multi(layer.up, ids1, xr)
+    if hasattr(ops, "gemv_multi_glu"):
+        y = ops.gemv_multi_glu(layer.down, ids1, g, u, layer.act)
+    else:
+        y = ops.gemv_multi(layer.down, ids1, ops.glu(g, u, layer.act))
+    if residual is not None:
+        return ops.moe_combine(y, None, w, b, layer.k, out=residual, accumulate=True)
+    return ops.moe_combine(y, None, w, b, layer.k)
+
+
 def experts_forward_grouped(layer, x, group_off, gather, pairs, ops=None):
     """gate/up/GLU/down for `pairs` permuted rows grouped by expert (`grouped_proj` x3)."""
     ops = _ops(ops)

@@ -215,6 +215,13 @@ int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int
  * local ids with their weights (the rest: expert 0, weight 0); *out_n = count. */
 int fk_moe_local_slots(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int k, int e0, int n_local,
                        int* out_ids_dev, float* out_w_dev, int* out_n_dev);
+/* The same for a decode batch of b rows (pairs = b * k <= 256, pair i belongs to row i / k): the pairs
+ * whose expert lies in [e0, e0 + n_local) become slots 0 .. *out_n - 1 in pair order -- out_ids[p] the
+ * local expert and out_src[p] the row whose activation slot p reads (0 past the last slot);
+ * out_pair_of[i] is the slot of pair i and out_w[i] its weight (slot 0, weight 0 for a pair another
+ * rank owns), the arguments fk_moe_combine takes. */
+int fk_moe_local_pairs(fk_ctx* ctx, void* stream, const int* ids_dev, const float* w_dev, int pairs, int k, int e0, int n_local,
+                       int* out_ids_dev, int* out_src_dev, int* out_pair_of_dev, float* out_w_dev, int* out_n_dev);
 /* Expert-parallel prefill over replicated activations (no reference counterpart): every rank routes
  * all tokens; pair i keeps its expert as the local id ids[i] - e0 when e0 <= ids[i] < e0 + n_local,
  * else it gets the id n_local (a group no expert serves) and weight 0. */
@@ -279,6 +286,15 @@ int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const 
 int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
                          float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
                          const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows);
+/* The same step for n_seqs independent sequences in one launch (batched decode): row r of q
+ * (rows q_ld floats apart), k_new and v_new (k_ld / v_ld apart) is sequence r's token at position
+ * pos_dev[r]; sequence r's caches begin r * seq_stride floats into k_cache_dev / v_cache_dev and
+ * hold cache_rows rows each.  out_dev [n_seqs][n_heads*head_dim].  A sequence whose position
+ * has reached cache_rows is skipped and raises the error word 95. */
+int fk_attention_rope_kv_seqs(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_new_dev, const float* v_new_dev, int k_ld,
+                              int v_ld, float* k_cache_dev, float* v_cache_dev, size_t seq_stride, int n_seqs, int n_heads, int n_kv, int head_dim,
+                              const int* pos_dev, float scale, float theta, int neox, const float* q_norm_dev, const float* k_norm_dev,
+                              float norm_eps, float* out_dev, int cache_rows);
 /* Greedy sampling: index of the largest of each row, ties to the lower index; at most
  * 64 rows per call, and one call in flight per context (it uses a workspace of the context). */
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);

@@ -78,6 +78,27 @@ def moe_localize(ids, w, e0, n_local):
     return torch.where(mine, ids - e0, torch.full_like(ids, n_local)).to(torch.int32), torch.where(mine, w, torch.zeros_like(w))
 
 
+def moe_local_pairs(ids, w, e0, n_local):
+    flat, wf = ids.reshape(-1), w.reshape(-1)
+    k = ids.shape[-1]
+    mine = (flat >= e0) & (flat < e0 + n_local)
+    n = int(mine.sum())
+    slot = torch.cumsum(mine.to(torch.int32), 0) - 1
+    lid = torch.zeros_like(flat)
+    src = torch.zeros_like(flat)
+    lid[:n] = flat[mine] - e0
+    src[:n] = (torch.arange(flat.numel())[mine] // k).to(torch.int32)
+    pair_of = torch.where(mine, slot, torch.zeros_like(slot)).to(torch.int32)
+    return lid.to(torch.int32), src.to(torch.int32), pair_of, torch.where(mine, wf, torch.zeros_like(wf)), torch.tensor([n], dtype=torch.int32)
+
+
+def gemv_multi_active(w, ids, x, n_active, out):
+    n = int(n_active[0])
+    if n:
+        out[:n] = gemv_multi(w, ids[:n], x[:n] if x.dim() == 2 else x)
+    return out
+
+
 def moe_combine(y, pair_of, w, batch, k, out=None, accumulate=False):
     ys, ws = y.numpy(), w.numpy().reshape(batch, k)
     po = pair_of.numpy() if pair_of is not None else np.arange(batch * k)
@@ -89,6 +110,11 @@ def moe_combine(y, pair_of, w, batch, k, out=None, accumulate=False):
 
 
 def gemv_multi_glu(w, ids, gate, up, act=0, out=None, n_active=None):
+    if n_active is not None:
+        n = int(n_active[0])
+        if n:
+            out[:n] = gemv_multi(w, ids[:n], glu(gate[:n].contiguous(), up[:n].contiguous(), act))
+        return out
     return gemv_multi(w, ids, glu(gate, up, act))
 
 

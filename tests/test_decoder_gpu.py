@@ -421,3 +421,58 @@ def test_the_workspace_never_moves_under_a_captured_graph(monkeypatch):
         w.release()
     finally:
         lib().fk_destroy(fresh)
+
+
+@pytest.mark.parametrize("moe", [False, True])
+def test_a_decode_batch_of_independent_sequences_matches_each_sequence_alone(moe):
+    """Eight sequences with prompts of different lengths, decoded together (one token each per step, their own KV
+    caches and positions, one launch per op for the whole batch), against each sequence decoded alone."""
+    from frink_b200 import device
+    from frink_b200.decoder import Decoder
+    if moe:
+        from tests.test_parallel_cpu import _tiny_model
+        cfg, layers, tok, out_norm, head = _tiny_model(True)
+        mk = lambda: Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=64)
+    else:
+        cfg, layers, tok, out_norm, head = small_llama(uniform=True)
+        mk = lambda: Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=64)
+    n_seqs, steps = 8, 6
+    rng = np.random.default_rng(17)
+    prompts = [torch.from_numpy(rng.integers(0, cfg.vocab, 5 + 3 * s).astype(np.int32)).cuda() for s in range(n_seqs)]
+    solo = mk()
+    want_tok, want_logits = [], []
+    for p in prompts:
+        solo.reset()
+        t = solo.prefill(p)
+        toks, lgs = [int(t.item())], []
+        for _ in range(steps):
+            lg = solo.forward(t)
+            lgs.append(lg.cpu().numpy()[0])
+            t = device.argmax(lg)
+            toks.append(int(t.item()))
+        want_tok.append(toks)
+        want_logits.append(lgs)
+    dec = mk()
+    dec.alloc_seqs(n_seqs)
+    cur = torch.cat([dec.prefill_seq(s, prompts[s]) for s in range(n_seqs)])
+    got_tok = [[int(c)] for c in cur.tolist()]
+    worst = 0.0
+    for i in range(steps):
+        lg = dec.forward_seqs(cur)
+        for s in range(n_seqs):
+            worst = max(worst, rel_l2(lg[s].cpu().numpy(), want_logits[s][i]))
+        cur = device.argmax(lg)
+        for s, c in enumerate(cur.tolist()):
+            got_tok[s].append(int(c))
+    assert device.device_error() == 0
+    # the batched step takes the tensor-core matvec (8 rows) where the single row takes the dp4a one: same integers,
+    # another f32 summation order, and q8_1 re-rounding of the activations downstream of it
+    assert worst <= 5e-3, worst
+    assert got_tok == want_tok
+    # the captured step continues where the eager ones stopped
+    g, out = dec.capture_decode_seqs(cur)
+    dec.replay_seqs()
+    torch.cuda.synchronize()
+    lg = None
+    assert out.shape[0] == n_seqs and device.device_error() == 0
+    assert dec._seq_pos_host == [int(p) for p in dec.seq_pos.tolist()]

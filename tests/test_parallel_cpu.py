@@ -87,7 +87,8 @@ def _ep_case(rank, world):
     dec = ep.decode(x[0]).numpy()
     per = 6 // world
     pre = ep.prefill(x[rank * per:(rank + 1) * per]).numpy()
-    return dec, pre
+    rows = ep.decode_rows(x).numpy()          # a decode batch: all six rows replicated on every rank
+    return dec, pre, rows
 
 
 def test_expert_parallel_matches_single_rank():
@@ -104,7 +105,8 @@ def test_expert_parallel_matches_single_rank():
     want_dec = prefill.run_device_routed(layer, x[0], cpu_ops).numpy()
     assert rel_l2(want_dec, want[0]) <= 1e-6
     res = spawn(_ep_case)
-    for rank, (dec, pre) in enumerate(res):
+    for rank, (dec, pre, rows) in enumerate(res):
+        assert rel_l2(rows, want) <= 1e-6                      # the slot form of a decode batch
         assert rel_l2(dec, want_dec) <= 1e-6                   # partial sums all-reduced: order of two adds
         assert np.array_equal(pre, want[rank * 3:(rank + 1) * 3])   # dispatch/combine keeps the single-rank order: same bits
 

@@ -136,6 +136,25 @@ def _worker(rank, world, port, ret):
         solo.reset()
         out["tp_decoder"] = worst
         out["tp_decoder_tokens"] = bool(same) and toks == solo.generate(prompt, 8)
+        # a decode batch of four independent sequences on the routed model, experts over the ranks (everything else
+        # replicated), against the same batch on one GPU
+        from tests.test_parallel_cpu import _tiny_model
+        mcfg, mlayers, mtok, mnorm, mhead = _tiny_model(True)
+        mk = lambda **kw: Decoder(mcfg, mlayers, mtok, fo.Q8_0, mnorm, output=mhead, output_kind=fo.Q8_0, max_seq=64, dense_parallel=False, **kw)
+        one, many = mk(group=solo_groups[rank]), mk(comm=comm)
+        r3 = np.random.default_rng(9)
+        prompts = [torch.from_numpy(r3.integers(0, mcfg.vocab, 4 + 2 * s_).astype(np.int32)).cuda() for s_ in range(4)]
+        one.alloc_seqs(4)
+        many.alloc_seqs(4)
+        c_one = torch.cat([one.prefill_seq(s_, prompts[s_]) for s_ in range(4)])
+        c_many = torch.cat([many.prefill_seq(s_, prompts[s_]) for s_ in range(4)])
+        seq_worst, seq_same = 0.0, torch.equal(c_one, c_many)
+        for _ in range(5):
+            l_one, l_many = one.forward_seqs(c_one), many.forward_seqs(c_one)
+            seq_worst = max(seq_worst, rel_l2(l_many.cpu().numpy(), l_one.cpu().numpy()))
+            seq_same = seq_same and torch.equal(device.argmax(l_one), device.argmax(l_many))
+            c_one = device.argmax(l_one)
+        out["ep_seqs"], out["ep_seqs_tokens"] = seq_worst, bool(seq_same)
         # time: 12 KB vectors, 200 in a graph
         def timed(fn):
             gr = torch.cuda.CUDAGraph()
@@ -177,7 +196,7 @@ def test_tp_and_ep_over_nccl_match_single_gpu():
         assert o["tp_dec"] <= 1e-5 and o["tp_pre"] <= 1e-5, o
         assert o["ep_pre_equal"] and o["ep_dec"] <= 1e-6, o
         assert o["ar_ok"] and o["tp_dec_comm"] <= 1e-5 and o["ep_dec_comm"] <= 1e-6 and o["ep_pre_replicated"] <= 1e-6, o
-        assert o["fused_ar"] <= 1e-5, o
+        assert o["fused_ar"] <= 1e-5 and o["ep_seqs"] <= 2e-3 and o["ep_seqs_tokens"], o
         # the sharded decoder sums the same products in another order and re-rounds q8_1 activations on the way
         assert o["tp_decoder"] <= 2e-3 and o["tp_decoder_tokens"], o
-    print({k: v for k, v in ret[0].items() if k.startswith("us_") or k.startswith("tp_decoder") or k == "fused_ar"})
+    print({k: v for k, v in ret[0].items() if k.startswith("us_") or k.startswith("tp_decoder") or k in ("fused_ar", "ep_seqs")})
