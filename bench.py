@@ -392,14 +392,14 @@ def main():
 
 
 def single_case(args):
-    """`--case [gemv:|gemm:]kind:rows:cols:n`: `--steps` plain (un-graphed) launches of
+    """`--case [gemv:|gemm:|gemm8k:]kind:rows:cols:n`: `--steps` plain (un-graphed) launches of
     one shape over a ring of weight copies larger than L2 (n = batch for the GEMV,
-    tokens for the GEMM); the command the ncu captures run."""
+    tokens for the GEMM; gemm8k = the Q8_K-activation GEMM); the command the ncu captures run."""
     import torch
     from frink_b200 import device
     from oracle import frink_oracle as fo
     parts = args.case.split(":")
-    op = parts.pop(0) if parts[0] in ("gemv", "gemm") else "gemv"
+    op = parts.pop(0) if parts[0] in ("gemv", "gemm", "gemm8k") else "gemv"
     name, rows, cols, n = parts
     kind, rows, cols, n = fo.KINDS[name], int(rows), int(cols), int(n)
     rng = np.random.default_rng(1)
@@ -411,7 +411,8 @@ def single_case(args):
     ws = [device.Weights(raw_d, kind, rows, cols) for _ in range(ring)]
     xd = torch.from_numpy(rng.standard_normal((n, cols), dtype=np.float32)).cuda()
     yd = torch.empty((n, rows), dtype=torch.float32, device="cuda")
-    run = (lambda i: device.gemm(ws[i % ring], xd, out=yd)) if op == "gemm" else (lambda i: device.gemv(ws[i % ring], xd, out=yd))
+    run = {"gemm": lambda i: device.gemm(ws[i % ring], xd, out=yd), "gemm8k": lambda i: device.gemm_q8k(ws[i % ring], xd, out=yd),
+           "gemv": lambda i: device.gemv(ws[i % ring], xd, out=yd)}[op]
     for i in range(args.warmup):
         run(i)
     torch.cuda.synchronize()
@@ -436,10 +437,13 @@ def use_more_bits(i, n):
 
 def synth_model(name, n_layers=0):
     """Random-init weights of the named shape, quantized by the reference's encoders
-    (oracle restatement).  To keep set-up short, two distinct layers of bytes are
-    generated per quantization pattern and the other layers reuse them (each layer still
-    gets its own device copy, so nothing is shared in HBM or L2); the embedding is 4096
-    distinct rows tiled to the vocabulary.  Throughput does not depend on the values."""
+    (oracle restatement).  To keep set-up short, two sets of matrix bytes are quantized per
+    shape; every layer takes one of them with its rows in an order of its own (and every
+    expert of a layer a rotation of its own), so no two layers or experts apply the same
+    matrix -- reused matrices add up coherently over the depth and a deep stack then answers
+    every token with the same one, one route through the experts.  The embedding is 4096
+    distinct rows tiled to the vocabulary.  `layers` is a generator (a layer's host bytes
+    exist only until they are uploaded)."""
     from frink_b200.decoder import DecoderConfig, LayerWeights
     from oracle import frink_oracle as fo
     Q4, Q6, Q8 = fo.Q4_K, fo.Q6_K, fo.Q8_0
@@ -469,32 +473,39 @@ def synth_model(name, n_layers=0):
             cache[key] = np.tile(raw, -(-rows // base_rows))[: rows * fo.row_bytes(kind, cols)].copy()
         return cache[key]
 
-    layers = []
-    for i in range(cfg.n_layers):
-        var = i % 2
-        if cfg.n_experts:
-            kd = {"wq": Q8, "wk": Q8, "wv": Q8, "wo": Q8, "experts": Q4}
-            E = cfg.n_experts
+    def shuffled(raw, kind, rows, cols, seed):
+        """The matrix with its rows in another order (whole quantized rows move, no byte changes)."""
+        rb = fo.row_bytes(kind, cols)
+        return raw.reshape(rows, rb)[np.random.default_rng(seed).permutation(rows)].ravel()
 
-            def ex(tag, r, c):   # one expert's bytes per (layer variant), stacked E times; layers of a variant share the host array
-                key = ("stack", tag, r, c, var)
-                if key not in cache:
-                    cache[key] = np.tile(enc(tag, Q4, r, c, var), E)
-                return cache[key]
-            layers.append(LayerWeights(
-                attn_norm=norm(H), wq=enc("wq", Q8, cfg.n_heads * hd, H, var), wk=enc("wk", Q8, cfg.n_kv * hd, H, var),
-                wv=enc("wv", Q8, cfg.n_kv * hd, H, var), wo=enc("wo", Q8, H, cfg.n_heads * hd, var), ffn_norm=norm(H),
-                gate=ex("eg", cfg.ffn, H), up=ex("eu", cfg.ffn, H), down=ex("ed", H, cfg.ffn),
-                router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=norm(hd),
-                k_norm=norm(hd), kinds=kd))
-        else:
-            more = use_more_bits(i, cfg.n_layers)
-            kd = {"wq": Q4, "wk": Q4, "wv": Q6 if more else Q4, "wo": Q4, "gate": Q4, "up": Q4, "down": Q6 if more else Q4}
-            layers.append(LayerWeights(
-                attn_norm=norm(H), wq=enc("wq", kd["wq"], cfg.n_heads * hd, H, var), wk=enc("wk", kd["wk"], cfg.n_kv * hd, H, var),
-                wv=enc("wv", kd["wv"], cfg.n_kv * hd, H, var), wo=enc("wo", kd["wo"], H, cfg.n_heads * hd, var), ffn_norm=norm(H),
-                gate=enc("gate", kd["gate"], cfg.ffn, H, var), up=enc("up", kd["up"], cfg.ffn, H, var), down=enc("down", kd["down"], H, cfg.ffn, var),
-                kinds=kd))
+    def make_layers():
+        # a generator: a layer's host bytes are built when the decoder asks for them and dropped after the upload
+        for i in range(cfg.n_layers):
+            var = i % 2
+            sh = lambda tag, kind, r, c, j: shuffled(enc(tag, kind, r, c, var), kind, r, c, 7919 * i + j)
+            if cfg.n_experts:
+                kd = {"wq": Q8, "wk": Q8, "wv": Q8, "wo": Q8, "experts": Q4}
+                E = cfg.n_experts
+
+                def ex(tag, r, c, j):   # expert e = the layer's matrix with its rows rotated by a step of its own
+                    base = sh(tag, Q4, r, c, j).reshape(r, fo.row_bytes(Q4, c))
+                    idx = (np.arange(r)[None, :] + (np.arange(E) * 37 % r)[:, None]) % r
+                    return base[idx].ravel()
+                yield LayerWeights(
+                    attn_norm=norm(H), wq=sh("wq", Q8, cfg.n_heads * hd, H, 0), wk=sh("wk", Q8, cfg.n_kv * hd, H, 1),
+                    wv=sh("wv", Q8, cfg.n_kv * hd, H, 2), wo=sh("wo", Q8, H, cfg.n_heads * hd, 3), ffn_norm=norm(H),
+                    gate=ex("eg", cfg.ffn, H, 4), up=ex("eu", cfg.ffn, H, 5), down=ex("ed", H, cfg.ffn, 6),
+                    router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=norm(hd),
+                    k_norm=norm(hd), kinds=kd)
+            else:
+                more = use_more_bits(i, cfg.n_layers)
+                kd = {"wq": Q4, "wk": Q4, "wv": Q6 if more else Q4, "wo": Q4, "gate": Q4, "up": Q4, "down": Q6 if more else Q4}
+                yield LayerWeights(
+                    attn_norm=norm(H), wq=sh("wq", kd["wq"], cfg.n_heads * hd, H, 0), wk=sh("wk", kd["wk"], cfg.n_kv * hd, H, 1),
+                    wv=sh("wv", kd["wv"], cfg.n_kv * hd, H, 2), wo=sh("wo", kd["wo"], H, cfg.n_heads * hd, 3), ffn_norm=norm(H),
+                    gate=sh("gate", kd["gate"], cfg.ffn, H, 4), up=sh("up", kd["up"], cfg.ffn, H, 5),
+                    down=sh("down", kd["down"], H, cfg.ffn, 6), kinds=kd)
+    layers = make_layers()
     tok_kind = Q6
 
     def vocab_matrix(std):

@@ -33,7 +33,7 @@ namespace {
 using namespace fk_tc;
 
 #ifdef FK_TRACE
-__device__ unsigned long long fk_gemm8k_trace[12][64];
+__device__ unsigned long long fk_gemm8k_trace[16][64];
 __device__ __forceinline__ unsigned long long gtime_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -123,6 +123,7 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
             const uint32_t das = sbase + OFF_X + xs * X_BYTES + BP_BYTES + (uint32_t)col0 * 4u;
             mbar_wait_parked(acc_full, sb & 1, a.err, 62);
             tc_fence_after();
+            GTR(10, sb, threadIdx.x == 0);
 #pragma unroll
             for (int c = 0; c < EC / 8; c++) {
                 uint32_t hi[8], lo[8], mn[8];
@@ -169,6 +170,7 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
             // the accumulators, this block's scales and this super-block's activation scales are free again
             tc_fence_before();
             __syncwarp();
+            GTR(13, sb, threadIdx.x == 0);
             if (lane == 0) {
                 mbar_arrive(acc_empty);
                 mbar_arrive(x_empty + 8 * xs);
@@ -287,6 +289,7 @@ gemm8k_q4k_kernel(const Args8k a, const __grid_constant__ CUtensorMap map_w, con
                 const uint64_t db0 = umma_desc(sbase + OFF_B + (2 * P) * B_BYTES), db1 = umma_desc(sbase + OFF_B + (2 * P + 1) * B_BYTES);
                 const uint64_t dap = umma_desc_of(sbase + OFF_AP + P * AP_BYTES, 128, 256, 0);
                 const uint64_t dbp = umma_desc_of(sbase + OFF_X + P * X_BYTES, 16, 256, 6);
+                GTR(12, sb, lane == 0);
                 if (sb >= 1) mbar_wait_spin(acc_empty, (sb - 1) & 1, a.err, 90);
                 GTR(0, sb, lane == 0);
 #pragma unroll
