@@ -1,6 +1,6 @@
 //! Raw declarations of `libfrink_b200.so`'s C ABI, one per entry point of `include/frink_b200.h`, in the
-//! header's order and with the header's argument names.  Semantics, units and the frink interface each call
-//! replaces are documented in the header; nothing here adds behaviour.
+//! header's order and with the header's argument names (written by `bindings/rust/gen_sys.py`).  Semantics,
+//! units and the frink interface each call replaces are documented in the header; nothing here adds behaviour.
 #![allow(non_camel_case_types)]
 use std::os::raw::{c_char, c_int, c_void};
 
@@ -19,6 +19,17 @@ pub type FkWeight = *mut FkWeightS;
 #[repr(C)]
 pub struct FkComm {
     _private: [u8; 0],
+}
+/// `fk_matvec_launch`: one matvec of a multi-matvec call.
+#[repr(C)]
+#[derive(Clone, Copy)]
+pub struct FkMatvecLaunch {
+    pub kind: c_int,
+    pub weights_host: *const u8,
+    pub len: usize,
+    pub rows: c_int,
+    pub row_bytes: c_int,
+    pub n_blocks_per_row: c_int,
 }
 
 /// `fk_status`.
@@ -94,6 +105,7 @@ extern "C" {
         n: c_int,
         y_dev: *mut u8,
     ) -> c_int;
+    pub fn fk_quantize_q8_1_host(ctx: *mut FkCtx, x_host: *const f32, n: c_int, y_host: *mut u8) -> c_int;
     pub fn fk_gemv(
         ctx: *mut FkCtx,
         stream: *mut c_void,
@@ -525,6 +537,23 @@ extern "C" {
         rows: c_int,
         row_bytes: c_int,
         n_blocks_per_row: c_int,
+        y_host: *mut f32,
+    ) -> c_int;
+    pub fn fk_launch_matvec_multi(
+        ctx: *mut FkCtx,
+        x_host: *const f32,
+        n_cols: c_int,
+        launches: *const FkMatvecLaunch,
+        n: c_int,
+        y_hosts: *const *mut f32,
+    ) -> c_int;
+    pub fn fk_launch_dense_ffn_swiglu(
+        ctx: *mut FkCtx,
+        gate: *const FkMatvecLaunch,
+        up: *const FkMatvecLaunch,
+        down: *const FkMatvecLaunch,
+        x_host: *const f32,
+        n_cols: c_int,
         y_host: *mut f32,
     ) -> c_int;
     pub fn fk_launch_mul_mm(

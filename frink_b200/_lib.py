@@ -72,6 +72,9 @@ SYMBOLS = {
     "fk_allreduce": (_I, [_P, _P, _P, _SZ, _I, _P, _P, _I, _I, _I]),
     "fk_gemv_fused_allreduce": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I, _I, _P, _SZ, _I, _I]),
     "fk_launch_matvec": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _P]),
+    "fk_quantize_q8_1_host": (_I, [_P, _P, _I, _P]),
+    "fk_launch_matvec_multi": (_I, [_P, _P, _I, _P, _I, _P]),
+    "fk_launch_dense_ffn_swiglu": (_I, [_P, _P, _P, _P, _P, _I, _P]),
     "fk_launch_mul_mm": (_I, [_P, _I, _P, _SZ, _P, _I, _I, _I, _I, _P]),
     "fk_forget_resident": (_I, [_P]),
 }

@@ -50,6 +50,8 @@ FK_EXPORT int fk_init(int device, fk_ctx** out) {
     FkDeviceGuard g(device);
     e = cudaMalloc(&ctx->err_flag, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->err_pin, sizeof(int), cudaHostAllocDefault);
+    if (e == cudaSuccess) *ctx->err_pin = 0;
     if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_ws, 64 * 64 * sizeof(unsigned long long));
     // 64 counters of the argmax rows, then (index 64) the arrival counter of the fused router
     if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_cnt, 128 * sizeof(unsigned));
@@ -75,6 +77,7 @@ FK_EXPORT void fk_destroy(fk_ctx* ctx) {
     cudaFree(ctx->scratch);
     for (uint8_t* p : ctx->scratch_retired) cudaFree(p);
     cudaFree(ctx->err_flag);
+    if (ctx->err_pin) cudaFreeHost(ctx->err_pin);
     cudaFree(ctx->argmax_ws);
     cudaFree(ctx->argmax_cnt);
     cudaFree(ctx->attn_cnt);
@@ -352,6 +355,20 @@ int grow_pinned(float** p, float** dev_alias, size_t* cap, size_t floats, bool m
     *cap = floats;
     return FK_OK;
 }
+
+// The end of a host-buffer call: the error word travels to the host in the same stream, behind the kernels, so one
+// synchronize covers both.  A kernel that gave up a bounded wait (or refused a cache overrun) left a code there: the
+// results are garbage and the call says so (frink-core's contract: `Err` -> fall back, weight_matrix.rs:3454-3493).
+int finish_host_call(fk_ctx* ctx, const char* what) {
+    FK_CUDA(cudaMemcpyAsync(ctx->err_pin, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost, nullptr), FK_LAUNCH);
+    FK_CUDA(cudaStreamSynchronize(nullptr), FK_LAUNCH);
+    const int code = *ctx->err_pin;
+    if (code) {
+        cudaMemset(ctx->err_flag, 0, sizeof(int));
+        return fk_fail(FK_LAUNCH, "%s: a kernel gave up a bounded wait (device error word %d); the result is not valid", what, code);
+    }
+    return FK_OK;
+}
 }  // namespace
 
 FK_EXPORT int fk_forget_resident(fk_ctx* ctx) {
@@ -394,7 +411,7 @@ FK_EXPORT int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_hos
         ctx->h2d += xn * sizeof(float);
         rc = fk_gemv_launch(ctx, nullptr, w, nullptr, 0, 1, ctx->x_dev, 0, batch, ctx->y_pin_dev, nullptr, nullptr, nullptr);
         if (rc) return rc;
-        FK_CUDA(cudaStreamSynchronize(nullptr), FK_LAUNCH);
+        if ((rc = finish_host_call(ctx, "launch"))) return rc;
         memcpy(out_host, ctx->y_pin, yn * sizeof(float));
         ctx->d2h += yn * sizeof(float);
         return FK_OK;
@@ -407,7 +424,7 @@ FK_EXPORT int fk_launch_mul_mm(fk_ctx* ctx, int kind, const uint8_t* weights_hos
     }
     if (rc) return rc;
     FK_CUDA(cudaMemcpyAsync(out_host, ctx->y_dev, yn * sizeof(float), cudaMemcpyDeviceToHost, nullptr), FK_LAUNCH);
-    FK_CUDA(cudaStreamSynchronize(nullptr), FK_LAUNCH);
+    if ((rc = finish_host_call(ctx, "launch_mul_mm"))) return rc;
     ctx->d2h += yn * sizeof(float);
     return FK_OK;
 }
@@ -417,4 +434,90 @@ FK_EXPORT int fk_launch_matvec(fk_ctx* ctx, int kind, const uint8_t* weights_hos
     const int be = fk_kind_block_elems(kind);
     if (be < 0) return fk_fail(FK_UNSUPPORTED, "launch_matvec: kind %d has no kernel here", kind);
     return fk_launch_mul_mm(ctx, kind, weights_host, len, x_host, rows, n_blocks_per_row * be, 1, row_bytes, y_host);
+}
+
+namespace {
+// One launch description of a multi-matvec call, checked and made resident.
+int prepare_launch(fk_ctx* ctx, const fk_matvec_launch* l, int n_cols, const char* what, fk_weight* w) {
+    if (!l || !l->weights_host) return fk_fail(FK_INVALID, "%s: null launch", what);
+    const int bb = fk_kind_block_bytes(l->kind), be = fk_kind_block_elems(l->kind);
+    if (bb < 0) return fk_fail(FK_UNSUPPORTED, "%s: kind %d has no kernel here", what, l->kind);
+    if (l->rows < 1 || l->n_blocks_per_row < 1 || l->n_blocks_per_row * be != n_cols || (size_t)l->row_bytes != (size_t)l->n_blocks_per_row * bb)
+        return fk_fail(FK_INVALID, "%s: %d rows, %d blocks of kind %d per row (%d bytes) against %d columns", what, l->rows, l->n_blocks_per_row, l->kind,
+                       l->row_bytes, n_cols);
+    return resident(ctx, l->kind, l->weights_host, l->len, l->rows, n_cols, w);
+}
+}  // namespace
+
+// `gpu::launch_matvec_multi` (crates/frink-cuda/src/matvec_launch.rs:495-536): x goes up once, the n matvecs are
+// enqueued back to back on resident weights, every result comes down, one synchronize at the edge.
+FK_EXPORT int fk_launch_matvec_multi(fk_ctx* ctx, const float* x_host, int n_cols, const fk_matvec_launch* launches, int n, float* const* y_hosts) {
+    if (!ctx || !x_host || (n > 0 && (!launches || !y_hosts))) return fk_fail(FK_INVALID, "launch_matvec_multi: null argument");
+    if (n <= 0) return FK_OK;
+    if (n > 64 || n_cols < 1) return fk_fail(FK_INVALID, "launch_matvec_multi: %d launches of %d columns", n, n_cols);
+    FkDeviceGuard g(ctx->device);
+    fk_weight ws[64];
+    size_t total = 0;
+    for (int i = 0; i < n; i++) {
+        const int rc = prepare_launch(ctx, &launches[i], n_cols, "launch_matvec_multi", &ws[i]);
+        if (rc) return rc;
+        if (!y_hosts[i]) return fk_fail(FK_INVALID, "launch_matvec_multi: null output %d", i);
+        total += ((size_t)launches[i].rows + 3) & ~(size_t)3;
+    }
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    int rc;
+    if ((rc = grow(&ctx->x_dev, &ctx->x_cap, (size_t)n_cols))) return rc;
+    if ((rc = grow_pinned(&ctx->x_pin, nullptr, &ctx->x_pin_cap, (size_t)n_cols, false))) return rc;
+    if ((rc = grow_pinned(&ctx->y_pin, &ctx->y_pin_dev, &ctx->y_pin_cap, total, true))) return rc;
+    memcpy(ctx->x_pin, x_host, (size_t)n_cols * sizeof(float));
+    FK_CUDA(cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, (size_t)n_cols * sizeof(float), cudaMemcpyHostToDevice, nullptr), FK_LAUNCH);
+    ctx->h2d += (size_t)n_cols * sizeof(float);
+    size_t off = 0;
+    for (int i = 0; i < n; i++) {
+        rc = fk_gemv_launch(ctx, nullptr, ws[i], nullptr, 0, 1, ctx->x_dev, 0, 1, ctx->y_pin_dev + off, nullptr, nullptr, nullptr);
+        if (rc) return rc;
+        off += ((size_t)launches[i].rows + 3) & ~(size_t)3;
+    }
+    if ((rc = finish_host_call(ctx, "launch_matvec_multi"))) return rc;
+    off = 0;
+    for (int i = 0; i < n; i++) {
+        memcpy(y_hosts[i], ctx->y_pin + off, (size_t)launches[i].rows * sizeof(float));
+        ctx->d2h += (size_t)launches[i].rows * sizeof(float);
+        off += ((size_t)launches[i].rows + 3) & ~(size_t)3;
+    }
+    return FK_OK;
+}
+
+// `gpu::launch_dense_ffn_swiglu` (matvec_launch.rs:554-574): gate and up matvecs, SiLU(gate) * up, the down matvec,
+// all on the device; one upload of x and one download of the result.  The gated activation rides in the down
+// projection's prologue (no launch of its own).
+FK_EXPORT int fk_launch_dense_ffn_swiglu(fk_ctx* ctx, const fk_matvec_launch* gate, const fk_matvec_launch* up, const fk_matvec_launch* down,
+                                         const float* x_host, int n_cols, float* y_host) {
+    if (!ctx || !gate || !up || !down || !x_host || !y_host) return fk_fail(FK_INVALID, "launch_dense_ffn_swiglu: null argument");
+    if (gate->rows != up->rows) return fk_fail(FK_INVALID, "launch_dense_ffn_swiglu: gate has %d rows, up %d", gate->rows, up->rows);
+    FkDeviceGuard g(ctx->device);
+    fk_weight wg, wu, wd;
+    int rc;
+    if ((rc = prepare_launch(ctx, gate, n_cols, "launch_dense_ffn_swiglu (gate)", &wg))) return rc;
+    if ((rc = prepare_launch(ctx, up, n_cols, "launch_dense_ffn_swiglu (up)", &wu))) return rc;
+    if ((rc = prepare_launch(ctx, down, gate->rows, "launch_dense_ffn_swiglu (down)", &wd))) return rc;
+    std::lock_guard<std::recursive_mutex> lk(ctx->mu);
+    const size_t ffn = (size_t)gate->rows;
+    if ((rc = grow(&ctx->x_dev, &ctx->x_cap, (size_t)n_cols))) return rc;
+    if ((rc = grow(&ctx->y_dev, &ctx->y_cap, 2 * ffn))) return rc;
+    if ((rc = grow_pinned(&ctx->x_pin, nullptr, &ctx->x_pin_cap, (size_t)n_cols, false))) return rc;
+    if ((rc = grow_pinned(&ctx->y_pin, &ctx->y_pin_dev, &ctx->y_pin_cap, (size_t)down->rows, true))) return rc;
+    memcpy(ctx->x_pin, x_host, (size_t)n_cols * sizeof(float));
+    FK_CUDA(cudaMemcpyAsync(ctx->x_dev, ctx->x_pin, (size_t)n_cols * sizeof(float), cudaMemcpyHostToDevice, nullptr), FK_LAUNCH);
+    ctx->h2d += (size_t)n_cols * sizeof(float);
+    float* g_dev = ctx->y_dev;
+    float* u_dev = ctx->y_dev + ffn;
+    if ((rc = fk_gemv_launch(ctx, nullptr, wg, nullptr, 0, 1, ctx->x_dev, 0, 1, g_dev, nullptr, nullptr, nullptr))) return rc;
+    if ((rc = fk_gemv_launch(ctx, nullptr, wu, nullptr, 0, 1, ctx->x_dev, 0, 1, u_dev, nullptr, nullptr, nullptr))) return rc;
+    FkGemvFused f{nullptr, 0.0f, u_dev, 0, 0, (int)ffn, 0, nullptr};
+    if ((rc = fk_gemv_launch(ctx, nullptr, wd, nullptr, 0, 1, g_dev, 0, 1, ctx->y_pin_dev, nullptr, nullptr, &f))) return rc;
+    if ((rc = finish_host_call(ctx, "launch_dense_ffn_swiglu"))) return rc;
+    memcpy(y_host, ctx->y_pin, (size_t)down->rows * sizeof(float));
+    ctx->d2h += (size_t)down->rows * sizeof(float);
+    return FK_OK;
 }

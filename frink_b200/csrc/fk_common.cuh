@@ -73,6 +73,7 @@ struct fk_ctx {
     std::vector<uint8_t*> scratch_retired;   // outgrown blocks: queued launches and captured graphs may still name them
     // device word kernels raise when a bounded wait gives up
     int* err_flag = nullptr;
+    int* err_pin = nullptr;        // pinned host word the host-buffer calls copy the error word into before they synchronize
     // argmax: per-(row, block) keys and per-row arrival counters (64 x 64 keys, 64 counters);
     // one argmax in flight per context
     unsigned long long* argmax_ws = nullptr;

@@ -1760,6 +1760,24 @@ FK_EXPORT int fk_quantize_q8_1(fk_ctx* ctx, void* stream, const float* x_dev, in
     return FK_OK;
 }
 
+// The same with host buffers (what `matvec_reads` of the reference-side crate calls): one upload, one download.
+FK_EXPORT int fk_quantize_q8_1_host(fk_ctx* ctx, const float* x_host, int n, uint8_t* y_host) {
+    if (!ctx || !x_host || !y_host || n < 0 || n % 32) return fk_fail(FK_INVALID, "quantize_q8_1_host: n=%d must be a multiple of 32", n);
+    if (n == 0) return FK_OK;
+    FkDeviceGuard g(ctx->device);
+    float* xd = nullptr;
+    uint8_t* yd = nullptr;
+    const size_t yb = (size_t)n / 32 * 36;
+    cudaError_t e = cudaMalloc(&xd, (size_t)n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&yd, yb);
+    if (e == cudaSuccess) e = cudaMemcpy(xd, x_host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice);
+    int rc = e == cudaSuccess ? fk_quantize_q8_1(ctx, nullptr, xd, n, yd) : fk_fail(FK_LAUNCH, "quantize_q8_1_host: %s", cudaGetErrorString(e));
+    if (rc == FK_OK && (e = cudaMemcpy(y_host, yd, yb, cudaMemcpyDeviceToHost)) != cudaSuccess) rc = fk_fail(FK_LAUNCH, "quantize_q8_1_host: %s", cudaGetErrorString(e));
+    cudaFree(xd);
+    cudaFree(yd);
+    return rc;
+}
+
 FK_EXPORT int fk_gemv(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev) {
     if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv: null argument");
     if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv: batch %d outside 1..8 (use fk_gemm)", batch);

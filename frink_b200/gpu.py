@@ -116,43 +116,43 @@ def _kind_of(launch):
     return k
 
 
+class _CLaunch(C.Structure):
+    """`fk_matvec_launch` of the C ABI."""
+    _fields_ = [("kind", C.c_int), ("weights_host", C.c_void_p), ("len", C.c_size_t), ("rows", C.c_int), ("row_bytes", C.c_int),
+                ("n_blocks_per_row", C.c_int)]
+
+
+def _c_launch(l):
+    k = _kind_of(l)
+    w, wp = _host(l.weights, np.uint8)
+    return _CLaunch(k.tag, wp, w.size, l.rows, l.row_bytes, l.n_blocks_per_row), k, w
+
+
 def launch_matvec_multi(x, launches):
     """`gpu::launch_matvec_multi` (matvec_launch.rs:495-535): one upload of `x`,
-    one matvec per launch, outputs downloaded after all were enqueued."""
-    import torch
-    from . import device
+    one matvec per launch, outputs downloaded after all were enqueued
+    (`fk_launch_matvec_multi`)."""
     if not launches:
         return []
-    xd = torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda()
-    outs = []
-    for l in launches:
-        k = _kind_of(l)
-        w = _resident(k, l)
-        outs.append(device.gemv(w, xd))
-    return [o.cpu().numpy() for o in outs]
-
-
-_res = {}
-
-
-def _resident(kind, l):
-    from . import device
-    w = np.ascontiguousarray(l.weights, np.uint8)
-    key = (w.ctypes.data, w.size, kind.tag)
-    hit = _res.get(key)
-    if hit is None:
-        hit = device.Weights(w, kind.tag, l.rows, l.n_blocks_per_row * kind.block_elems)
-        _res[key] = hit
-    return hit
+    if not _CTX:
+        _CTX.append(_ctx())
+    xv, xp = _host(x, np.float32)
+    cl = [_c_launch(l) for l in launches]
+    arr = (_CLaunch * len(cl))(*[c[0] for c in cl])
+    outs = [np.empty(l.rows, np.float32) for l in launches]
+    ptrs = (C.c_void_p * len(outs))(*[o.ctypes.data for o in outs])
+    check(lib().fk_launch_matvec_multi(_CTX[0], xp, xv.size, arr, len(cl), ptrs))
+    return outs
 
 
 def launch_dense_ffn_swiglu(gate, up, down, x):
     """`gpu::launch_dense_ffn_swiglu` (matvec_launch.rs:537-570): x up once,
-    gate and up matvecs, silu(gate)*up, down matvec, one download."""
-    import torch
-    from . import device
-    xd = torch.from_numpy(np.ascontiguousarray(x, np.float32)).cuda()
-    g = device.gemv(_resident(_kind_of(gate), gate), xd)
-    u = device.gemv(_resident(_kind_of(up), up), xd)
-    a = device.glu(g, u, 0)
-    return device.gemv(_resident(_kind_of(down), down), a).cpu().numpy()
+    gate and up matvecs, silu(gate)*up, down matvec, one download
+    (`fk_launch_dense_ffn_swiglu`)."""
+    if not _CTX:
+        _CTX.append(_ctx())
+    xv, xp = _host(x, np.float32)
+    g, u, d = _c_launch(gate), _c_launch(up), _c_launch(down)
+    y = np.empty(down.rows, np.float32)
+    check(lib().fk_launch_dense_ffn_swiglu(_CTX[0], C.byref(g[0]), C.byref(u[0]), C.byref(d[0]), xp, xv.size, y.ctypes.data))
+    return y

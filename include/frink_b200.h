@@ -100,6 +100,9 @@ int fk_weight_shape(fk_weight w, int* kind, int* n_mats, int* rows, int* cols, s
  * (f16 d = amax/127, f16 sum, 32 x int8 = roundf(x/d)).  The GEMV and GEMM
  * below quantize their activations with exactly this rule, fused. */
 int fk_quantize_q8_1(fk_ctx* ctx, void* stream, const float* x_dev, int n, uint8_t* y_dev);
+/* The same with host buffers: n floats in, n / 32 blocks of 36 bytes out (`matvec_reads`,
+ * crates/frink-cuda/src/matvec_kinds/dp4a.rs:291-303, is this followed by d * q). */
+int fk_quantize_q8_1_host(fk_ctx* ctx, const float* x_host, int n, uint8_t* y_host);
 
 /* ---- decode GEMV, batch 1..8 ---------------------------------------------
  * Replaces `q4_k_matvec_dp4a`, `q6_k_matvec_dp4a`, `q8_0_matvec_dp4a`,
@@ -343,6 +346,30 @@ int fk_gemv_fused_allreduce(fk_ctx* ctx, void* stream, fk_weight w, int mat, con
  * (crates/frink-cuda/src/gpu.rs:319-446). */
 int fk_launch_matvec(fk_ctx* ctx, int kind, const uint8_t* weights_host, size_t len, const float* x_host,
                      int rows, int row_bytes, int n_blocks_per_row, float* y_host);
+
+/* `MatvecLaunch` (crates/frink-cuda/src/matvec_launch.rs:485-493) without the kernel names: the
+ * GGML type tag selects the kernel.  `weights_host` must be a stable slice (the mmap'd tensor):
+ * residency is keyed by (pointer, length). */
+typedef struct fk_matvec_launch {
+    int kind;
+    const uint8_t* weights_host;
+    size_t len;
+    int rows;
+    int row_bytes;
+    int n_blocks_per_row;
+} fk_matvec_launch;
+/* `gpu::launch_matvec_multi` (matvec_launch.rs:495-536): x (n_cols floats) goes up once, the n
+ * matvecs are enqueued back to back, y_hosts[i] receives launches[i].rows floats; one
+ * synchronize.  n <= 64. */
+int fk_launch_matvec_multi(fk_ctx* ctx, const float* x_host, int n_cols, const fk_matvec_launch* launches, int n, float* const* y_hosts);
+/* `gpu::launch_dense_ffn_swiglu` (matvec_launch.rs:554-574): y = down (SiLU(gate x) * (up x)),
+ * one upload of x, one download of y (down->rows floats); the gated activation is formed in
+ * the down projection's prologue. */
+int fk_launch_dense_ffn_swiglu(fk_ctx* ctx, const fk_matvec_launch* gate, const fk_matvec_launch* up, const fk_matvec_launch* down,
+                               const float* x_host, int n_cols, float* y_host);
+/* All fk_launch_* calls read the device error word before they return: if a kernel of the call
+ * gave up a bounded wait the call answers FK_LAUNCH (the message names the code) and clears
+ * the word. */
 /* `mul_mm_launch::launch_mul_mm(kind, weights, x_batch, n_rows, n_cols, batch,
  * row_bytes)` (crates/frink-cuda/src/mul_mm_launch.rs:40-68);
  * out_host[token * n_rows + row].  batch 1..8 takes the GEMV. */

@@ -67,3 +67,22 @@ def test_kind_tables_agree():
         assert matvec_kinds.kind_by_name(k.fn_name) is k and matvec_kinds.kind_by_name(k.name) is k
     assert matvec_kinds.kind_by_name("q5_k_matvec") is None
     assert not mul_mm.worth_a_gemm(8) and mul_mm.worth_a_gemm(64)
+
+
+def test_the_rust_sys_crate_declares_every_entry_point_of_the_header():
+    """`bindings/rust/frink-b200-sys/src/lib.rs` is generated from the header (`bindings/rust/gen_sys.py`); a header
+    change without a regeneration shows up here."""
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    h = re.sub(r"/\*.*?\*/", "", open(os.path.join(root, "include", "frink_b200.h")).read(), flags=re.S)
+    declared = set(re.findall(r"\b(fk_\w+)\s*\(", h))
+    rs = open(os.path.join(root, "bindings", "rust", "frink-b200-sys", "src", "lib.rs")).read()
+    in_rs = set(re.findall(r"pub fn (fk_\w+)\(", rs))
+    assert declared == in_rs, (declared - in_rs, in_rs - declared)
+    # and the wrapper crate only calls what the -sys crate declares
+    used = set()
+    wrap = os.path.join(root, "bindings", "rust", "frink-cuda-b200", "src")
+    for f in os.listdir(wrap):
+        used |= set(re.findall(r"sys::(fk_\w+)", open(os.path.join(wrap, f)).read()))
+    assert used and used <= in_rs, used - in_rs

@@ -46,7 +46,21 @@ def test_a_peer_that_never_arrives_times_out_with_an_error_word():
     e1.record()
     torch.cuda.synchronize()
     assert 2.0 <= e0.elapsed_time(e1) <= 200.0            # it waited its limit, not forever
-    assert device.device_error() == 60                    # and said so (the call resets the word)
+    # the host-buffer surface reads the word before it returns: the next such call fails with it instead of handing back
+    # numbers that a broken launch may have produced, and clears it
+    from frink_b200 import gpu
+    from oracle import frink_oracle as fo
+    from tests.helpers import synth_weights
+    raw4 = fo.encode(fo.Q4_K, synth_weights(64, 256, 2))
+    xh = np.random.default_rng(1).standard_normal(256).astype(np.float32)
+    with pytest.raises(gpu.Launch, match="60"):
+        gpu.launch_q4_k_matvec(raw4, xh, 64, 144, 1)
+    assert device.device_error() == 0
+    assert np.isfinite(gpu.launch_q4_k_matvec(raw4, xh, 64, 144, 1)).all()
+    # the device-pointer calls leave the word to the caller
+    check(lib().fk_allreduce(ctx, s, a, 0, 1024, C.c_void_p(x.data_ptr()), C.c_void_p(y.data_ptr()), 1024, 0, 3000))
+    torch.cuda.synchronize()
+    assert device.device_error() == 60                    # read and reset
     assert device.device_error() == 0
     # the context is as usable as before
     from oracle import frink_oracle as fo

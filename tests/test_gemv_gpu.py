@@ -165,3 +165,31 @@ def test_config1_shape_q4_k_8192x3072():
     _check(got[None], raw, fo.Q4_K, 8192, 3072, x)
     isums = device.gemv_isums(w, torch.from_numpy(x[0]).cuda()).cpu().numpy()
     assert np.array_equal(isums, fo.matrix_isums(fo.Q4_K, raw, 8192, 3072, fo.quantize_q8_1(x[0])))
+
+
+def test_host_buffer_multi_matvec_and_dense_ffn():
+    """`gpu::launch_matvec_multi` and `gpu::launch_dense_ffn_swiglu` through the C exports of the same names:
+    the multi call equals the single launches bit for bit, the FFN equals gate / up / SiLU / down composed from
+    single launches to f32 rounding, and both sit on the oracle."""
+    from frink_b200 import gpu
+    cols, ffn, rows = 1024, 768, 512
+    x = synth_acts(1, cols, 3)[0]
+    mats = {n: (fo.encode(k, synth_weights(r, c, s)), k, r, c) for n, k, r, c, s in
+            (("q", fo.Q4_K, rows, cols, 1), ("k", fo.Q6_K, 256, cols, 2), ("gate", fo.Q4_K, ffn, cols, 3), ("up", fo.Q4_K, ffn, cols, 4),
+             ("down", fo.Q6_K, rows, ffn, 5))}
+    name = {fo.Q4_K: "q4_k_matvec", fo.Q6_K: "q6_k_matvec"}
+    mk = lambda n: gpu.MatvecLaunch(name[mats[n][1]], mats[n][0], mats[n][2], fo.row_bytes(mats[n][1], mats[n][3]), mats[n][3] // 256)
+    single = lambda n, v: {fo.Q4_K: gpu.launch_q4_k_matvec, fo.Q6_K: gpu.launch_q6_k_matvec}[mats[n][1]](
+        mats[n][0], v, mats[n][2], fo.row_bytes(mats[n][1], mats[n][3]), mats[n][3] // 256)
+    outs = gpu.launch_matvec_multi(x, [mk("q"), mk("k")])
+    assert np.array_equal(outs[0], single("q", x)) and np.array_equal(outs[1], single("k", x))
+    want_q = fo.matmul_f64(fo.Q4_K, mats["q"][0], rows, cols, fo.q8_1_round(x))[0]
+    assert rel_l2(outs[0], want_q) <= 1e-3
+    y = gpu.launch_dense_ffn_swiglu(mk("gate"), mk("up"), mk("down"), x)
+    g, u = single("gate", x), single("up", x)
+    act = fo.silu_mul(g, u)
+    assert rel_l2(y, single("down", act)) <= 1e-5
+    want = fo.matmul_f64(fo.Q6_K, mats["down"][0], rows, ffn, fo.q8_1_round(act))[0]
+    assert rel_l2(y, want) <= 1e-3
+    with pytest.raises(gpu.Unsupported):
+        gpu.launch_matvec_multi(x, [gpu.MatvecLaunch("q5_k_matvec", mats["q"][0], rows, 1, 1)])
