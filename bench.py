@@ -495,8 +495,10 @@ def synth_model(name, n_layers=0):
                     attn_norm=norm(H), wq=sh("wq", Q8, cfg.n_heads * hd, H, 0), wk=sh("wk", Q8, cfg.n_kv * hd, H, 1),
                     wv=sh("wv", Q8, cfg.n_kv * hd, H, 2), wo=sh("wo", Q8, H, cfg.n_heads * hd, 3), ffn_norm=norm(H),
                     gate=ex("eg", cfg.ffn, H, 4), up=ex("eu", cfg.ffn, H, 5), down=ex("ed", H, cfg.ffn, 6),
-                    router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), q_norm=norm(hd),
-                    k_norm=norm(hd), kinds=kd)
+                    router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)),
+                    # per-head q / k norms leave q and k at unit RMS: with weights near 1 the scores q.k / sqrt(d) reach +-11 and the
+                    # softmax picks single keys, whose values then swamp the residual stream whatever the token; 0.3 keeps it soft
+                    q_norm=norm(hd) * np.float32(0.3), k_norm=norm(hd) * np.float32(0.3), kinds=kd)
             else:
                 more = use_more_bits(i, cfg.n_layers)
                 kd = {"wq": Q4, "wk": Q4, "wv": Q6 if more else Q4, "wo": Q4, "gate": Q4, "up": Q4, "down": Q6 if more else Q4}

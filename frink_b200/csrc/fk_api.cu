@@ -48,10 +48,15 @@ FK_EXPORT int fk_init(int device, fk_ctx** out) {
     ctx->mem_bytes = prop.totalGlobalMem;
     snprintf(ctx->name, sizeof(ctx->name), "%s", prop.name);
     FkDeviceGuard g(device);
-    e = cudaMalloc(&ctx->err_flag, sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, sizeof(int));
-    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->err_pin, sizeof(int), cudaHostAllocDefault);
-    if (e == cudaSuccess) *ctx->err_pin = 0;
+    e = cudaMalloc(&ctx->err_flag, 16);
+    if (e == cudaSuccess) e = cudaMemset(ctx->err_flag, 0, 16);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->err_pin, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+        *ctx->err_pin = 0;
+        int* mirror_dev = nullptr;
+        e = cudaHostGetDevicePointer((void**)&mirror_dev, ctx->err_pin, 0);
+        if (e == cudaSuccess) e = cudaMemcpy((char*)ctx->err_flag + 8, &mirror_dev, sizeof(mirror_dev), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_ws, 64 * 64 * sizeof(unsigned long long));
     // 64 counters of the argmax rows, then (index 64) the arrival counter of the fused router
     if (e == cudaSuccess) e = cudaMalloc(&ctx->argmax_cnt, 128 * sizeof(unsigned));
@@ -356,15 +361,14 @@ int grow_pinned(float** p, float** dev_alias, size_t* cap, size_t floats, bool m
     return FK_OK;
 }
 
-// The end of a host-buffer call: the error word travels to the host in the same stream, behind the kernels, so one
-// synchronize covers both.  A kernel that gave up a bounded wait (or refused a cache overrun) left a code there: the
+// The end of a host-buffer call: one synchronize, then the error word's host mirror.  A kernel that gave up a bounded wait (or refused a cache overrun) left a code there: the
 // results are garbage and the call says so (frink-core's contract: `Err` -> fall back, weight_matrix.rs:3454-3493).
 int finish_host_call(fk_ctx* ctx, const char* what) {
-    FK_CUDA(cudaMemcpyAsync(ctx->err_pin, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost, nullptr), FK_LAUNCH);
     FK_CUDA(cudaStreamSynchronize(nullptr), FK_LAUNCH);
-    const int code = *ctx->err_pin;
+    const int code = *(volatile int*)ctx->err_pin;      // written by the kernel that raised (fk_raise), visible after the synchronize
     if (code) {
         cudaMemset(ctx->err_flag, 0, sizeof(int));
+        *ctx->err_pin = 0;
         return fk_fail(FK_LAUNCH, "%s: a kernel gave up a bounded wait (device error word %d); the result is not valid", what, code);
     }
     return FK_OK;

@@ -83,7 +83,7 @@ __device__ __forceinline__ float fk_ar_recv(const FkArChannel& ch, int i, unsign
         }
         acc += __uint_as_float(val);
     }
-    if (dead) atomicCAS(err, 0, 60);
+    if (dead) fk_raise(err, 60);
     return acc;
 }
 #endif

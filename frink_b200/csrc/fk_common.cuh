@@ -72,8 +72,8 @@ struct fk_ctx {
     size_t scratch_cap = 0;
     std::vector<uint8_t*> scratch_retired;   // outgrown blocks: queued launches and captured graphs may still name them
     // device word kernels raise when a bounded wait gives up
-    int* err_flag = nullptr;
-    int* err_pin = nullptr;        // pinned host word the host-buffer calls copy the error word into before they synchronize
+    int* err_flag = nullptr;       // 16 bytes on the device: the error word, and at byte 8 the device address of its host mirror
+    int* err_pin = nullptr;        // the mirror: mapped pinned host memory, written by the kernel that raises (fk_raise)
     // argmax: per-(row, block) keys and per-row arrival counters (64 x 64 keys, 64 counters);
     // one argmax in flight per context
     unsigned long long* argmax_ws = nullptr;
@@ -139,6 +139,18 @@ int fk_make_map_u32(void* map, void* base, uint64_t inner_words, uint64_t outer,
 
 // device helpers --------------------------------------------------------------
 #ifdef __CUDACC__
+// A kernel gives up (a bounded wait ran out, a cache would overrun): the first code wins the context's error word, and
+// the winner also stores it into the word's host mirror (mapped pinned memory whose device address sits 8 bytes after
+// the word), so that a host-buffer call sees it after its one synchronize without a copy of its own.
+__device__ __forceinline__ void fk_raise(int* err, int code) {
+    if (atomicCAS(err, 0, code) == 0) {
+        int* mirror = *(int**)(err + 2);
+        if (mirror) {
+            *(volatile int*)mirror = code;
+            __threadfence_system();
+        }
+    }
+}
 __device__ __forceinline__ float fk_h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ uint16_t fk_f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
 

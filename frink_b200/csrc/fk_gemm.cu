@@ -830,6 +830,9 @@ FK_EXPORT int fk_device_error(fk_ctx* ctx, int* code, int reset) {
     if (!ctx || !code) return fk_fail(FK_INVALID, "device_error: null argument");
     FkDeviceGuard g(ctx->device);
     FK_CUDA(cudaMemcpy(code, ctx->err_flag, sizeof(int), cudaMemcpyDeviceToHost), FK_LAUNCH);
-    if (reset && *code) FK_CUDA(cudaMemset(ctx->err_flag, 0, sizeof(int)), FK_LAUNCH);
+    if (reset && *code) {
+        FK_CUDA(cudaMemset(ctx->err_flag, 0, sizeof(int)), FK_LAUNCH);
+        *ctx->err_pin = 0;
+    }
     return FK_OK;
 }

@@ -122,7 +122,7 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* er
         if (mbar_try_wait(bar, parity)) return;
         if ((i & 63) == 63 && (*(volatile int*)err != 0 || global_ns() - t0 > 2000000000ull)) break;
     }
-    atomicCAS(err, 0, 50);   // gave up: results are garbage from here, the host reads the word
+    fk_raise(err, 50);   // gave up: results are garbage from here, the host reads the word
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"

@@ -124,7 +124,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
 // returns before its first access) and the context's error word becomes 95.
 __device__ __forceinline__ bool fk_cache_overrun(int p0, int n_rows, int cache_rows, int* err) {
     if (p0 >= 0 && p0 + n_rows <= cache_rows) return false;
-    if (threadIdx.x == 0) atomicCAS(err, 0, 95);
+    if (threadIdx.x == 0) fk_raise(err, 95);
     return true;
 }
 

@@ -30,7 +30,7 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int* er
     for (uint32_t i = 0; i < WAIT_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
     }
-    atomicCAS(err, 0, code);
+    fk_raise(err, code);
 }
 // The same for warps that may wait long (a whole MMA phase): the hardware parks the thread until the
 // phase completes or the hint (in nanoseconds) runs out, instead of the warp polling shared memory --
@@ -43,7 +43,7 @@ __device__ __forceinline__ void mbar_wait_spin(uint32_t bar, uint32_t parity, in
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return;
     }
-    atomicCAS(err, 0, code);
+    fk_raise(err, code);
 }
 __device__ __forceinline__ void mbar_wait_parked_thread(uint32_t bar, uint32_t parity, int* err, int code) {
     for (uint32_t i = 0; i < (1u << 20); i++) {
@@ -52,7 +52,7 @@ __device__ __forceinline__ void mbar_wait_parked_thread(uint32_t bar, uint32_t p
                      : "=r"(ok) : "r"(bar), "r"(parity), "r"(4000u) : "memory");
         if (ok) return;
     }
-    atomicCAS(err, 0, code);
+    fk_raise(err, code);
 }
 __device__ __forceinline__ void mbar_wait_parked(uint32_t bar, uint32_t parity, int* err, int code) { mbar_wait_parked_thread(bar, parity, err, code); }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
