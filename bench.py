@@ -468,7 +468,11 @@ def synth_model(name, n_layers=0):
         key = (tag, kind, rows, cols, variant)
         if key not in cache:
             base_rows = min(rows, 2048)
-            w = (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(0.02))
+            # 0.02 everywhere but in the routed model, whose expert FFNs are narrow (768): there attention's output -- the same
+            # vector for every position once the positions share a component, so it adds up coherently over 48 layers --
+            # would swamp what depends on the token, and the stream would repeat one token (one route) for ever
+            std = {"wo": 0.0005, "eg": 0.04, "eu": 0.04, "ed": 0.04}.get(tag, 0.02) if cfg.n_experts else 0.02
+            w = (rng.standard_normal((base_rows, cols), dtype=np.float32) * np.float32(std))
             raw = fo.encode(kind, w)
             cache[key] = np.tile(raw, -(-rows // base_rows))[: rows * fo.row_bytes(kind, cols)].copy()
         return cache[key]

@@ -29,19 +29,22 @@ def probe():
         if not torch.cuda.is_available():
             return None
         from . import device
-        ctx = device.context(0)
+        ctx = device.context()
         name = C.create_string_buffer(128)
         sms, mem = C.c_int(), C.c_size_t()
         check(lib().fk_device_info(ctx, name, 128, C.byref(sms), C.byref(mem)))
-        free, total = torch.cuda.mem_get_info(0)
+        free, total = torch.cuda.mem_get_info(torch.cuda.current_device())
         return CudaInfo(torch.cuda.device_count(), name.value.decode(), int(total), int(free))
     except Exception:
         return None
 
 
 def _ctx():
+    """The context the host-buffer calls run on: the process's current CUDA device at first use.  The reference's
+    `shared_device` is device 0 (one GPU); with one process per GPU every rank must stay on its own device --
+    bound to device 0, eight ranks took turns on one GPU and a 31 us call became a millisecond."""
     from . import device
-    return device.context(0)
+    return device.context()
 
 
 def _host(a, dt):
