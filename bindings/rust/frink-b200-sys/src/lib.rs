@@ -347,6 +347,25 @@ extern "C" {
         n: c_int,
         out_dev: *mut f32,
     ) -> c_int;
+    pub fn fk_moe_layer_workspace(n_experts: c_int, k: c_int, hidden: c_int, ffn: c_int, batch: c_int) -> usize;
+    pub fn fk_moe_layer(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        router_dev: *const f32,
+        router_bias_dev: *const f32,
+        gate: FkWeight,
+        up: FkWeight,
+        down: FkWeight,
+        k: c_int,
+        mode: c_int,
+        act: c_int,
+        x_dev: *const f32,
+        batch: c_int,
+        out_dev: *mut f32,
+        accumulate: c_int,
+        workspace_dev: *mut c_void,
+        workspace_bytes: usize,
+    ) -> c_int;
     pub fn fk_get_rows(
         ctx: *mut FkCtx,
         stream: *mut c_void,

@@ -270,6 +270,14 @@ __global__ void __launch_bounds__(256) local_pairs_kernel(const int* __restrict_
     if (i == 0) *out_n = total;
 }
 
+// out[j] = x[j / k] for j < rows * k: every slot of a decode batch gets its row's activation.
+__global__ void repeat_rows_kernel(const float* __restrict__ x, int cols4, int k, size_t n4, float* __restrict__ out) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const size_t slot = i / cols4, c = i - slot * cols4;
+    ((float4*)out)[i] = ((const float4*)x)[(slot / k) * cols4 + c];
+}
+
 // Every kernel of a decode step asks for the same shared-memory carve-out as the GEMV
 // (the maximum): an SM that alternates between kernels with different carve-outs
 // re-partitions its L1 between them, which costs more than these kernels run.
@@ -413,4 +421,92 @@ FK_EXPORT int fk_moe_combine_add(fk_ctx* ctx, void* stream, const float* y_dev, 
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
+}
+
+// ---- the routed layer in one call --------------------------------------------------------------
+namespace {
+struct MoeWs {
+    size_t logits, ids, w, group_off, gather, pair_of, xr, g, u, y, total;
+};
+MoeWs moe_ws(int n_experts, int k, int hidden, int ffn, int batch) {
+    MoeWs m{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += (bytes + 255) & ~(size_t)255; return at; };
+    const size_t pairs = (size_t)batch * k;
+    m.logits = take((size_t)batch * n_experts * 4);
+    m.ids = take(pairs * 4);
+    m.w = take(pairs * 4);
+    m.group_off = take(((size_t)n_experts + 1) * 4);
+    m.gather = take(pairs * 4);
+    m.pair_of = take(pairs * 4);
+    m.xr = take(batch <= 8 && batch > 1 ? pairs * hidden * 4 : 0);
+    m.g = take(pairs * ffn * 4);
+    m.u = take(pairs * ffn * 4);
+    m.y = take(pairs * hidden * 4);
+    m.total = off;
+    return m;
+}
+}  // namespace
+
+FK_EXPORT size_t fk_moe_layer_workspace(int n_experts, int k, int hidden, int ffn, int batch) {
+    if (n_experts < 1 || k < 1 || hidden < 1 || ffn < 1 || batch < 1) return 0;
+    return moe_ws(n_experts, k, hidden, ffn, batch).total;
+}
+
+// The resident routed layer (crates/frink-cuda/src/prefill/moe_device.rs:241-438) as one call: router, top-k, and
+//   batch <= 8 : every (row, expert) pair a slot of one indexed matvec per projection, GLU in the down projection;
+//   batch  > 8 : pairs grouped by expert, one grouped GEMM per projection;
+// then the weighted combine in routing order, written to out_dev or added into it.
+FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                           fk_weight down, int k, int mode, int act, const float* x_dev, int batch, float* out_dev, int accumulate,
+                           void* workspace_dev, size_t workspace_bytes) {
+    if (!ctx || !router_dev || !gate || !up || !down || !x_dev || !out_dev || !workspace_dev) return fk_fail(FK_INVALID, "moe_layer: null argument");
+    const int E = gate->n_mats, hidden = gate->cols, ffn = gate->rows;
+    if (up->n_mats != E || down->n_mats != E || up->rows != ffn || up->cols != hidden || down->rows != hidden || down->cols != ffn)
+        return fk_fail(FK_INVALID, "moe_layer: gate %d x [%d x %d], up %d x [%d x %d], down %d x [%d x %d] do not form an expert FFN", E, ffn, hidden,
+                       up->n_mats, up->rows, up->cols, down->n_mats, down->rows, down->cols);
+    if (batch < 1 || k < 1 || k > E) return fk_fail(FK_INVALID, "moe_layer: batch %d, k %d of %d experts", batch, k, E);
+    if (((uintptr_t)workspace_dev & 255) || ((uintptr_t)x_dev & 15)) return fk_fail(FK_INVALID, "moe_layer: workspace must be 256-byte aligned, x 16-byte aligned");
+    const MoeWs m = moe_ws(E, k, hidden, ffn, batch);
+    if (workspace_bytes < m.total) return fk_fail(FK_INVALID, "moe_layer: workspace of %zu bytes, %zu needed (fk_moe_layer_workspace)", workspace_bytes, m.total);
+    uint8_t* ws = (uint8_t*)workspace_dev;
+    float* logits = (float*)(ws + m.logits);
+    int* ids = (int*)(ws + m.ids);
+    float* w = (float*)(ws + m.w);
+    float *g = (float*)(ws + m.g), *u = (float*)(ws + m.u), *y = (float*)(ws + m.y);
+    const int pairs = batch * k;
+    int rc;
+    auto combine = accumulate ? fk_moe_combine_add : fk_moe_combine;
+    if (batch <= 8) {
+        if ((rc = fk_router_route(ctx, stream, router_dev, x_dev, E, hidden, batch, router_bias_dev, k, mode, logits, ids, w))) return rc;
+        const float* xin = x_dev;
+        int x_stride = 0;
+        if (batch > 1) {
+            float* xr = (float*)(ws + m.xr);
+            FkDeviceGuard gd(ctx->device);
+            const size_t n4 = (size_t)pairs * (hidden / 4);
+            if (hidden & 3) return fk_fail(FK_INVALID, "moe_layer: hidden %d must be a multiple of 4", hidden);
+            FK_CARVEOUT(repeat_rows_kernel);
+            repeat_rows_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x_dev, hidden / 4, k, n4, xr);
+            FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+            ctx->launches++;
+            xin = xr;
+            x_stride = hidden;
+        }
+        if ((rc = fk_gemv_multi(ctx, stream, gate, ids, pairs, xin, x_stride, g))) return rc;
+        if ((rc = fk_gemv_multi(ctx, stream, up, ids, pairs, xin, x_stride, u))) return rc;
+        if ((rc = fk_gemv_multi_glu(ctx, stream, down, ids, pairs, g, u, ffn, act, y, nullptr))) return rc;
+        return combine(ctx, stream, y, nullptr, w, batch, k, hidden, out_dev);
+    }
+    int* group_off = (int*)(ws + m.group_off);
+    int* gather = (int*)(ws + m.gather);
+    int* pair_of = (int*)(ws + m.pair_of);
+    if ((rc = fk_router_logits(ctx, stream, router_dev, x_dev, E, hidden, batch, logits))) return rc;
+    if ((rc = fk_moe_route(ctx, stream, logits, router_bias_dev, E, k, mode, batch, ids, w))) return rc;
+    if ((rc = fk_moe_permute(ctx, stream, ids, pairs, k, E, group_off, gather, pair_of))) return rc;
+    if ((rc = fk_gemm_grouped(ctx, stream, gate, group_off, gather, x_dev, pairs, g))) return rc;
+    if ((rc = fk_gemm_grouped(ctx, stream, up, group_off, gather, x_dev, pairs, u))) return rc;
+    if ((rc = fk_glu(ctx, stream, g, u, (size_t)pairs * ffn, act, g))) return rc;
+    if ((rc = fk_gemm_grouped(ctx, stream, down, group_off, nullptr, g, pairs, y))) return rc;
+    return combine(ctx, stream, y, pair_of, w, batch, k, hidden, out_dev);
 }

@@ -198,6 +198,27 @@ def moe_local_slots(ids, w, e0, n_local):
     return oi, ow, on
 
 
+def moe_layer(layer, x, out=None, accumulate=False):
+    """The routed layer in one call (`fk_moe_layer`): `layer` carries router, router_bias, gate / up / down (stacked
+    `Weights`), k, mode, act; x [batch, hidden] or [hidden].  The workspace is kept on the layer object, per batch size."""
+    x2 = _f32(x) if x.dim() == 2 else _f32(x)[None]
+    batch = x2.shape[0]
+    g = layer.gate
+    ws = layer.__dict__.setdefault("_ws", {})
+    if batch not in ws:
+        need = lib().fk_moe_layer_workspace(g.n_mats, layer.k, g.cols, g.rows, batch)
+        ws[batch] = torch.empty(need + 256, dtype=torch.uint8, device=x2.device)
+    buf = ws[batch]
+    base = (buf.data_ptr() + 255) & ~255
+    assert not accumulate or out is not None
+    o = out if out is not None else torch.empty((batch, g.cols), dtype=torch.float32, device=x2.device)
+    o2 = o if o.dim() == 2 else o[None]
+    check(lib().fk_moe_layer(g._ctx, _stream(), _ptr(_f32(layer.router)), _ptr(_f32(layer.router_bias)) if layer.router_bias is not None else None,
+                             g.handle, layer.up.handle, layer.down.handle, layer.k, int(layer.mode), int(layer.act), _ptr(x2), batch, _ptr(o2),
+                             int(bool(accumulate)), C.c_void_p(base), buf.numel() - (base - buf.data_ptr())))
+    return o if x.dim() == 2 or out is not None else o[0]
+
+
 def moe_local_pairs(ids, w, e0, n_local):
     """ids, w [b, k] -> (local expert per slot, source row per slot, slot of each pair, weight of each pair, slot count):
     the pairs this rank's experts serve, packed to the front as slots."""

@@ -19,6 +19,6 @@ def launch_mul_mm(kind, weights, x_batch, n_rows, n_cols, batch, row_bytes):
     if x.size != batch * n_cols:
         raise _lib.Invalid(f"x_batch has {x.size} values, {batch} x {n_cols} wanted")
     out = np.empty(batch * n_rows, np.float32)
-    check(lib().fk_launch_mul_mm(device.context(0), k.tag, w.ctypes.data_as(C.c_void_p), w.size, x.ctypes.data_as(C.c_void_p),
+    check(lib().fk_launch_mul_mm(device.context(), k.tag, w.ctypes.data_as(C.c_void_p), w.size, x.ctypes.data_as(C.c_void_p),
                                  n_rows, n_cols, batch, row_bytes, out.ctypes.data_as(C.c_void_p)))
     return out

@@ -53,6 +53,8 @@ def run_device_routed(layer, x, ops=None, residual=None):
     gate and up are one indexed launch each with the k chosen experts as slots.
     residual (same shape as x): the layer's output is added into it instead of returned."""
     ops = _ops(ops)
+    if hasattr(ops, "moe_layer"):
+        return ops.moe_layer(layer, x, out=residual, accumulate=residual is not None)     # the whole layer is one C call
     if x.dim() == 2:
         import torch
         if residual is not None:
@@ -78,6 +80,8 @@ def run_device_routed_rows(layer, x, ops=None, residual=None):
     """Decode of a few independent rows x [b, hidden] (b <= 8) at once: every (row, chosen expert) pair is a slot of
     ONE indexed launch per projection -- b * k slots, the row's activation repeated for its k slots."""
     ops = _ops(ops)
+    if hasattr(ops, "moe_layer"):
+        return ops.moe_layer(layer, x, out=residual, accumulate=residual is not None)
     b = x.shape[0]
     ids, w = route(layer, x, ops)                         # [b, k]
     ids1 = ids.reshape(-1)
@@ -106,6 +110,8 @@ def run_device_routed_batch(layer, x, ops=None):
     """Prefill: x [batch, hidden].  Pairs are grouped by expert (tokens ascending
     inside a group), each projection is ONE grouped GEMM over all experts."""
     ops = _ops(ops)
+    if hasattr(ops, "moe_layer") and x.shape[0] > 8:
+        return ops.moe_layer(layer, x)
     batch = x.shape[0]
     ids, w = route(layer, x, ops)
     group_off, gather, pair_of = ops.moe_permute(ids, layer.n_experts)

@@ -243,6 +243,20 @@ int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pai
 int fk_moe_combine_add(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
                    int batch, int k, int n, float* out_dev);
 
+/* The resident routed layer as ONE call (`prefill::moe_device`, crates/frink-cuda/src/prefill/
+ * moe_device.rs:241-438): router logits and top-k, the three expert projections with the
+ * gated activation, the weighted combine in routing order.  gate / up / down are stacked expert
+ * handles (n_mats experts of [ffn x hidden], [ffn x hidden], [hidden x ffn]); x_dev
+ * [batch][hidden]; out_dev [batch][hidden] is written, or added into when accumulate != 0.
+ * batch <= 8 takes the indexed matvecs (every (row, expert) pair a slot), larger batches the
+ * grouped GEMMs.  workspace_dev: fk_moe_layer_workspace(...) bytes of device memory, 256-byte
+ * aligned, owned by the caller (nothing is allocated here).  mode / act as in fk_moe_route /
+ * fk_glu. */
+size_t fk_moe_layer_workspace(int n_experts, int k, int hidden, int ffn, int batch);
+int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                 fk_weight down, int k, int mode, int act, const float* x_dev, int batch, float* out_dev, int accumulate,
+                 void* workspace_dev, size_t workspace_bytes);
+
 /* ---- decoder glue (next-row components: enough to run a decoder and report
  * prefill / decode tokens per second; f32 throughout) -------------------------
  * `get_rows` (crates/frink-cuda/src/get_rows.rs:52): out[i] = dequantized row ids[i]. */
