@@ -78,6 +78,7 @@ macro_rules! matvec {
 }
 matvec!(launch_q8_0_matvec, sys::FK_Q8_0);
 matvec!(launch_q4_k_matvec, sys::FK_Q4_K);
+matvec!(launch_q5_k_matvec, sys::FK_Q5_K);
 matvec!(launch_q6_k_matvec, sys::FK_Q6_K);
 matvec!(launch_mxfp4_matvec, sys::FK_MXFP4);
 

@@ -18,6 +18,7 @@ pub struct MatvecKind {
 
 pub const KINDS: &[MatvecKind] = &[
     MatvecKind { name: "Q4_K", module_name: "frink_b200", fn_name: "q4_k_matvec", tag: sys::FK_Q4_K, block_bytes: 144, block_elems: 256 },
+    MatvecKind { name: "Q5_K", module_name: "frink_b200", fn_name: "q5_k_matvec", tag: sys::FK_Q5_K, block_bytes: 176, block_elems: 256 },
     MatvecKind { name: "Q6_K", module_name: "frink_b200", fn_name: "q6_k_matvec", tag: sys::FK_Q6_K, block_bytes: 210, block_elems: 256 },
     MatvecKind { name: "Q8_0", module_name: "frink_b200", fn_name: "q8_0_matvec", tag: sys::FK_Q8_0, block_bytes: 34, block_elems: 32 },
     MatvecKind { name: "MXFP4", module_name: "frink_b200", fn_name: "mxfp4_matvec", tag: sys::FK_MXFP4, block_bytes: 17, block_elems: 32 },

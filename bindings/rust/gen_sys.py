@@ -56,6 +56,7 @@ pub const FK_INVALID: c_int = 6;
 /// GGML type tags the library has kernels for.
 pub const FK_Q8_0: c_int = 8;
 pub const FK_Q4_K: c_int = 12;
+pub const FK_Q5_K: c_int = 13;
 pub const FK_Q6_K: c_int = 14;
 pub const FK_MXFP4: c_int = 39;
 

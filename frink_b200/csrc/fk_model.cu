@@ -45,6 +45,22 @@ __global__ void get_rows_kernel(const uint8_t* __restrict__ wb, size_t o0, size_
             const uint8_t q = blk[16 + (j >> 1) * 32 + l];
             const int nib = (j & 1) ? (q >> 4) : (q & 0x0F);
             v = (d * (float)scv) * (float)nib - dmin * (float)mv;
+        } else if (kind == FK_Q5_K) {
+            const uint8_t* blk = wb + o0 + (size_t)row * s0 + (size_t)(e >> 8) * 176;
+            const int j = (e & 255) >> 5, l = e & 31;
+            const uint8_t* sc = blk + 4;
+            int scv, mv;
+            if (j < 4) {
+                scv = sc[j] & 63;
+                mv = sc[j + 4] & 63;
+            } else {
+                scv = (sc[j + 4] & 0x0F) | ((sc[j - 4] >> 6) << 4);
+                mv = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4);
+            }
+            const float d = fk_h2f(*(const uint16_t*)blk), dmin = fk_h2f(*(const uint16_t*)(blk + 2));
+            const uint8_t q = blk[48 + (j >> 1) * 32 + l];
+            const int code = ((j & 1) ? (q >> 4) : (q & 0x0F)) + (((blk[16 + l] >> j) & 1) << 4);
+            v = (d * (float)scv) * (float)code - dmin * (float)mv;
         } else if (kind == FK_Q6_K) {
             const int sb = e >> 8, w = e & 255, hf = w >> 7, t = w & 127, qd = t >> 5, l = t & 31;
             const uint8_t ql = wb[o0 + (size_t)row * s0 + (size_t)sb * 128 + 64 * hf + l + 32 * (qd & 1)];

@@ -254,6 +254,11 @@ def gemm(w, x, mat=0, out=None):
     x = _f32(x)
     assert x.dim() == 2 and x.shape[1] == w.cols
     y = out if out is not None else torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
+    if w.kind == 13:
+        # Q5_K has no GEMM kernel (fk_gemm answers UNSUPPORTED): batches of 8 through the matvec, the same integers
+        for i in range(0, x.shape[0], 8):
+            gemv(w, x[i:i + 8], mat=mat, out=y[i:i + 8])
+        return y
     check(lib().fk_gemm(w._ctx, _stream(), w.handle, mat, _ptr(x), x.shape[0], _ptr(y)))
     return y
 

@@ -79,6 +79,10 @@ def launch_q4_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
     return _launch_matvec("Q4_K", weights, x, rows, row_bytes, n_blocks_per_row)
 
 
+def launch_q5_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
+    return _launch_matvec("Q5_K", weights, x, rows, row_bytes, n_blocks_per_row)
+
+
 def launch_q6_k_matvec(weights, x, rows, row_bytes, n_blocks_per_row):
     return _launch_matvec("Q6_K", weights, x, rows, row_bytes, n_blocks_per_row)
 

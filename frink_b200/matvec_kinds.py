@@ -17,6 +17,7 @@ class MatvecKind:
 
 KINDS = (
     MatvecKind("Q4_K", "q4_k_matvec", 12, 144, 256),
+    MatvecKind("Q5_K", "q5_k_matvec", 13, 176, 256),
     MatvecKind("Q6_K", "q6_k_matvec", 14, 210, 256),
     MatvecKind("Q8_0", "q8_0_matvec", 8, 34, 32),
     MatvecKind("MXFP4", "mxfp4_matvec", 39, 17, 32),

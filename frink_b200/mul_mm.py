@@ -1,13 +1,14 @@
-"""Kind table of the batched GEMM: mirror of `frink_cuda::mul_mm`
+"""Kind table of the prefill GEMM: mirror of `frink_cuda::mul_mm`
 (crates/frink-cuda/src/mul_mm.rs `KINDS`, `kind_by_name`, `worth_a_gemm` :634)."""
 from .matvec_kinds import KINDS as _MV, MatvecKind as MulMmKind, kind_by_name as _by_name  # noqa: F401
 
-KINDS = _MV  # the matvec table and the GEMM table name the same kinds
+KINDS = tuple(k for k in _MV if k.name != "Q5_K")   # every matvec kind but Q5_K, which has the plain matvec only
 GEMV_MAX_BATCH = 8
 
 
 def kind_by_name(name):
-    return _by_name(name)
+    k = _by_name(name)
+    return k if k in KINDS else None
 
 
 def worth_a_gemm(batch):

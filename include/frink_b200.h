@@ -56,6 +56,7 @@ typedef enum fk_status {
 typedef enum fk_kind {
     FK_Q8_0 = 8,   /* 34 B / 32 weights  */
     FK_Q4_K = 12,  /* 144 B / 256 weights */
+    FK_Q5_K = 13,  /* 176 B / 256 weights: the plain matvec (fk_gemv, fk_gemv_isums, fk_launch_matvec) and fk_get_rows only */
     FK_Q6_K = 14,  /* 210 B / 256 weights */
     FK_MXFP4 = 39  /* 17 B / 32 weights  */
 } fk_kind;

@@ -94,7 +94,7 @@ inline int32_t i32_at(const uint8_t* p) {
 }
 inline float f32_from_bits(uint32_t b) { float f; std::memcpy(&f, &b, 4); return f; }
 
-constexpr int Q4K_BYTES = 144, Q6K_BYTES = 210, Q80_BYTES = 34, MX4_BYTES = 17, Q81_BYTES = 36;
+constexpr int Q4K_BYTES = 144, Q5K_BYTES = 176, Q6K_BYTES = 210, Q80_BYTES = 34, MX4_BYTES = 17, Q81_BYTES = 36;
 
 // crates/frink-quant/src/lib.rs:321-330 (q4_k_scale_min)
 inline void q4k_scale_min(int j, const uint8_t* s, uint8_t* sc, uint8_t* m) {
@@ -133,6 +133,31 @@ void decode_q4_k(const uint8_t* b, float* y) {
         for (int l = 0; l < 32; l++) y[o++] = d2 * (float)(qs[q_off + l] >> 4) - min2;
         q_off += 32;
         is += 2;
+    }
+}
+
+// The 256 five-bit codes (0..31) of one Q5_K block, in element order: the low four bits as Q4_K's nibbles, the fifth
+// from qh, whose 32 bytes serve all four 64-element groups at bit positions 2g (low nibbles) and 2g + 1 (high).
+// crates/frink-quant/src/lib.rs:424-460.
+void q5k_codes(const uint8_t* b, uint8_t* q) {
+    const uint8_t* qh = b + 16;
+    const uint8_t* qs = b + 48;
+    for (int g = 0; g < 4; g++)
+        for (int l = 0; l < 32; l++) {
+            q[64 * g + l] = (uint8_t)((qs[32 * g + l] & 0x0F) + (((qh[l] >> (2 * g)) & 1) << 4));
+            q[64 * g + 32 + l] = (uint8_t)((qs[32 * g + l] >> 4) + (((qh[l] >> (2 * g + 1)) & 1) << 4));
+        }
+}
+
+void decode_q5_k(const uint8_t* b, float* y) {
+    uint8_t q[256];
+    q5k_codes(b, q);
+    float d = f16_at(b), dmin = f16_at(b + 2);
+    for (int j = 0; j < 8; j++) {
+        uint8_t sc, m;
+        q4k_scale_min(j, b + 4, &sc, &m);
+        float dj = d * (float)sc, mj = dmin * (float)m;
+        for (int l = 0; l < 32; l++) y[32 * j + l] = dj * (float)q[32 * j + l] - mj;
     }
 }
 
@@ -182,10 +207,11 @@ void decode_mxfp4(const uint8_t* b, float* y) {
 }
 
 struct KindInfo { int block_bytes, block_elems; void (*decode)(const uint8_t*, float*); };
-// ggml type tags: Q8_0 = 8, Q4_K = 12, Q6_K = 14, MXFP4 = 39.
+// ggml type tags: Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, MXFP4 = 39.
 bool kind_info(int kind, KindInfo* k) {
     switch (kind) {
         case 12: *k = {Q4K_BYTES, 256, decode_q4_k}; return true;
+        case 13: *k = {Q5K_BYTES, 256, decode_q5_k}; return true;
         case 14: *k = {Q6K_BYTES, 256, decode_q6_k}; return true;
         case 8: *k = {Q80_BYTES, 32, decode_q8_0}; return true;
         case 39: *k = {MX4_BYTES, 32, decode_mxfp4}; return true;
@@ -215,6 +241,24 @@ float dot_q4_k_f32_scalar(const uint8_t* row, int nblk, const float* x) {
             q_off += 32;
             base += 64;
             is += 2;
+        }
+    }
+    return acc;
+}
+
+// crates/frink-quant/src/lib.rs:481-515: the dequantized value times x, accumulated in element order
+float dot_q5_k_f32_scalar(const uint8_t* row, int nblk, const float* x) {
+    float acc = 0.0f;
+    uint8_t q[256];
+    for (int b = 0; b < nblk; b++) {
+        const uint8_t* blk = row + (size_t)b * Q5K_BYTES;
+        q5k_codes(blk, q);
+        float d = f16_at(blk), dmin = f16_at(blk + 2);
+        for (int j = 0; j < 8; j++) {
+            uint8_t sc, m;
+            q4k_scale_min(j, blk + 4, &sc, &m);
+            float dj = d * (float)sc, mj = dmin * (float)m;
+            for (int l = 0; l < 32; l++) acc += (dj * (float)q[32 * j + l] - mj) * x[b * 256 + 32 * j + l];
         }
     }
     return acc;
@@ -279,6 +323,7 @@ float dot_mxfp4_f32_scalar(const uint8_t* row, int nblk, const float* x) {
 float dot_f32_scalar(int kind, const uint8_t* row, int nblk, const float* x) {
     switch (kind) {
         case 12: return dot_q4_k_f32_scalar(row, nblk, x);
+        case 13: return dot_q5_k_f32_scalar(row, nblk, x);
         case 14: return dot_q6_k_f32_scalar(row, nblk, x);
         case 8: return dot_q8_0_f32_scalar(row, nblk, x);
         case 39: return dot_mxfp4_f32_scalar(row, nblk, x);
@@ -426,6 +471,37 @@ float dot_q4_k_q8k(const uint8_t* row, int nblk, const int8_t* aq, const float* 
             q_off += 32;
             base += 64;
             is += 2;
+        }
+    }
+    return acc;
+}
+
+// crates/frink-quant/src/lib.rs:886-939
+float dot_q5_k_q8k(const uint8_t* row, int nblk, const int8_t* aq, const float* ad, const int16_t* bs) {
+    float acc = 0.0f;
+    uint8_t q[256];
+    for (int b = 0; b < nblk; b++) {
+        const uint8_t* blk = row + (size_t)b * Q5K_BYTES;
+        q5k_codes(blk, q);
+        float d = f16_at(blk), dmin = f16_at(blk + 2);
+        float da = ad[b];
+        const int8_t* q8 = aq + (size_t)b * 256;
+        const int16_t* bsums = bs + b * 16;
+        int sum_min = 0;
+        for (int i = 0; i < 8; i++) {
+            uint8_t sc, m;
+            q4k_scale_min(i, blk + 4, &sc, &m);
+            sum_min += (int)m * ((int)bsums[2 * i] + (int)bsums[2 * i + 1]);
+        }
+        acc -= dmin * da * (float)sum_min;
+        for (int it = 0; it < 4; it++) {
+            uint8_t sc1, sc2, m;
+            q4k_scale_min(2 * it, blk + 4, &sc1, &m);
+            q4k_scale_min(2 * it + 1, blk + 4, &sc2, &m);
+            int isum1 = 0, isum2 = 0;
+            for (int l = 0; l < 32; l++) isum1 += (int)q[64 * it + l] * (int)q8[64 * it + l];
+            for (int l = 0; l < 32; l++) isum2 += (int)q[64 * it + 32 + l] * (int)q8[64 * it + 32 + l];
+            acc += d * da * ((float)sc1 * (float)isum1 + (float)sc2 * (float)isum2);
         }
     }
     return acc;
@@ -658,8 +734,8 @@ float dp4a_matvec_row(const Dp4aKind& k, const uint8_t* row, const uint8_t* y, i
 
 // Per-run exact integer dots of one weight row against q8_1 activations: the
 // integers every dp4a word-dot above is a partial sum of.  A "run" is 32
-// activations (one q8_1 block) for Q4_K, Q8_0 and MXFP4 and 16 for Q6_K (its
-// scale granularity).  Q4_K: sum nib*q8.  Q6_K: sum (q6-32)*q8.  Q8_0: sum
+// activations (one q8_1 block) for Q4_K, Q5_K, Q8_0 and MXFP4 and 16 for Q6_K (its
+// scale granularity).  Q4_K: sum nib*q8.  Q5_K: sum (nib + 16 bit)*q8.  Q6_K: sum (q6-32)*q8.  Q8_0: sum
 // qw*q8.  MXFP4: sum kvalue_x2*q8.
 void row_isums(int kind, const uint8_t* row, int nblk, const uint8_t* y, int32_t* out) {
     if (kind == 12) {
@@ -672,6 +748,17 @@ void row_isums(int kind, const uint8_t* row, int nblk, const uint8_t* y, int32_t
                     int nib = (j & 1) ? (qs[(j / 2) * 32 + l] >> 4) : (qs[(j / 2) * 32 + l] & 0x0F);
                     s += nib * (int)(int8_t)q8[l];
                 }
+                out[b * 8 + j] = s;
+            }
+        }
+    } else if (kind == 13) {
+        uint8_t q[256];
+        for (int b = 0; b < nblk; b++) {
+            q5k_codes(row + (size_t)b * Q5K_BYTES, q);
+            for (int j = 0; j < 8; j++) {
+                const uint8_t* q8 = y + (size_t)(b * 8 + j) * Q81_BYTES + 4;
+                int s = 0;
+                for (int l = 0; l < 32; l++) s += (int)q[32 * j + l] * (int)(int8_t)q8[l];
                 out[b * 8 + j] = s;
             }
         }
@@ -885,13 +972,15 @@ inline void pack_scale_min(uint8_t* packed, int j, uint8_t ls, uint8_t lm) {
     }
 }
 
-// crates/frink-quant/src/encode/fit.rs:416-566 (fit_qk_super_block, plain path)
-// with the Q4_K grid (-1.0, 0.1, 20), nmax 15, and
-// crates/frink-quant/src/encode/q4_k.rs:83-102 (encode_block_q4_k).
-void encode_block_q4_k(const float* block, uint8_t* out) {
-    uint8_t l[256] = {0}, laux[32];
+// crates/frink-quant/src/encode/fit.rs:416-566 (fit_qk_super_block, plain path): the three-stage fit Q4_K and Q5_K share
+// -- per sub-block scale / min search over the kind's candidate grid, 6-bit packing of the eight scales and mins against
+// their maxima, and the requantization of every code against the packed (rounded) scales.
+struct QkFit { int nmax; float rmin, rdelta; int nstep; };
+void fit_qk_super_block(const float* block, const QkFit& f, uint8_t* l, uint8_t* packed, uint16_t* dh_out, uint16_t* dmh_out) {
+    uint8_t laux[32];
     float weights[32], mins[8], scales[8];
     float max_scale = 0.0f, max_min = 0.0f;
+    std::memset(l, 0, 256);
     for (int j = 0; j < 8; j++) {
         const float* xs = block + 32 * j;
         // fit.rs:327-336 (qk_sub_block_weights): not fused in the reference
@@ -900,13 +989,13 @@ void encode_block_q4_k(const float* block, uint8_t* out) {
         float av_x = std::sqrt(sum_x2 / 32.0f);
         for (int i = 0; i < 32; i++) weights[i] = av_x + std::fabs(xs[i]);
         float scale, min;
-        make_qkx2_quants(32, xs, weights, l + 32 * j, laux, 15, -1.0f, 0.1f, 20, false, &scale, &min);
+        make_qkx2_quants(32, xs, weights, l + 32 * j, laux, f.nmax, f.rmin, f.rdelta, f.nstep, false, &scale, &min);
         scales[j] = scale;
         mins[j] = min;
         if (scale > max_scale) max_scale = scale;
         if (min > max_min) max_min = min;
     }
-    uint8_t packed[12] = {0};
+    std::memset(packed, 0, 12);
     float inv_scale = max_scale > 0.0f ? 63.0f / max_scale : 0.0f;
     float inv_min = max_min > 0.0f ? 63.0f / max_min : 0.0f;
     for (int j = 0; j < 8; j++) {
@@ -926,14 +1015,43 @@ void encode_block_q4_k(const float* block, uint8_t* out) {
         float dm = dmin * (float)m;
         for (int ii = 0; ii < 32; ii++) {
             int idx = 32 * j + ii;
-            l[idx] = (uint8_t)clampi(nearest_int((block[idx] + dm) / dj), 0, 15);
+            l[idx] = (uint8_t)clampi(nearest_int((block[idx] + dm) / dj), 0, f.nmax);
         }
     }
+    *dh_out = dh;
+    *dmh_out = dmh;
+}
+
+// crates/frink-quant/src/encode/q4_k.rs:83-102 (encode_block_q4_k): the Q4_K grid (-1.0, 0.1, 20), nmax 15.
+void encode_block_q4_k(const float* block, uint8_t* out) {
+    uint8_t l[256], packed[12];
+    uint16_t dh, dmh;
+    fit_qk_super_block(block, QkFit{15, -1.0f, 0.1f, 20}, l, packed, &dh, &dmh);
     out[0] = dh & 0xFF; out[1] = dh >> 8; out[2] = dmh & 0xFF; out[3] = dmh >> 8;
     std::memcpy(out + 4, packed, 12);
     int o = 16;
     for (int j = 0; j < 256; j += 64)
         for (int i = 0; i < 32; i++) out[o++] = (uint8_t)(l[j + i] | (l[j + i + 32] << 4));
+}
+
+// crates/frink-quant/src/encode/q5_k.rs:9-62 (encode_block_q5_k): the grid (-0.5, 0.1, 15), nmax 31; the fifth bit of every
+// code goes to qh (bit 2g for the low-nibble half of 64-element group g, 2g + 1 for the high), the low four stay nibbles.
+void encode_block_q5_k(const float* block, uint8_t* out) {
+    uint8_t l[256], packed[12];
+    uint16_t dh, dmh;
+    fit_qk_super_block(block, QkFit{31, -0.5f, 0.1f, 15}, l, packed, &dh, &dmh);
+    out[0] = dh & 0xFF; out[1] = dh >> 8; out[2] = dmh & 0xFF; out[3] = dmh >> 8;
+    std::memcpy(out + 4, packed, 12);
+    uint8_t* qh = out + 16;
+    uint8_t* ql = out + 48;
+    std::memset(qh, 0, 32);
+    for (int g = 0; g < 4; g++)
+        for (int j = 0; j < 32; j++) {
+            uint8_t l1 = l[64 * g + j], l2 = l[64 * g + 32 + j];
+            if (l1 > 15) { l1 -= 16; qh[j] |= (uint8_t)(1u << (2 * g)); }
+            if (l2 > 15) { l2 -= 16; qh[j] |= (uint8_t)(2u << (2 * g)); }
+            ql[32 * g + j] = (uint8_t)(l1 | (l2 << 4));
+        }
 }
 
 // crates/frink-quant/src/encode/q6_k.rs:72-175 (encode_block_q6_k, plain path)
@@ -1124,6 +1242,7 @@ FKO_API void fko_row_isums_q4k_q8k(const uint8_t* row, int nblk, const int8_t* a
 FKO_API float fko_dot_q8(int kind, const uint8_t* row, int nblk, const int8_t* q, const float* d, const int16_t* bsums) {
     switch (kind) {
         case 12: return dot_q4_k_q8k(row, nblk, q, d, bsums);
+        case 13: return dot_q5_k_q8k(row, nblk, q, d, bsums);
         case 14: return dot_q6_k_q8k(row, nblk, q, d);
         case 8: return dot_q8_0_q8(row, nblk, q, d);
         case 39: return dot_mxfp4_q8(row, nblk, q, d);
@@ -1136,7 +1255,7 @@ FKO_API float fko_dp4a_row(int kind, const uint8_t* row, const uint8_t* y, int n
     if (!dp4a_kind(kind, &k)) return NAN;
     return dp4a_matvec_row(k, row, y, n_blocks, nwarps);
 }
-FKO_API int fko_runs_per_block(int kind) { return kind == 12 ? 8 : kind == 14 ? 16 : 1; }
+FKO_API int fko_runs_per_block(int kind) { return kind == 12 || kind == 13 ? 8 : kind == 14 ? 16 : 1; }
 FKO_API void fko_row_isums(int kind, const uint8_t* row, int nblk, const uint8_t* y, int32_t* out) { row_isums(kind, row, nblk, y, out); }
 
 // Encode `n` f32 (a whole number of blocks) as `kind`; returns bytes written or -1.
@@ -1149,6 +1268,7 @@ FKO_API long fko_encode(int kind, const float* src, long n, uint8_t* out) {
         uint8_t* o = out + b * k.block_bytes;
         switch (kind) {
             case 12: encode_block_q4_k(s, o); break;
+            case 13: encode_block_q5_k(s, o); break;
             case 14: encode_block_q6_k(s, o); break;
             case 8: encode_block_q8_0(s, o); break;
             case 39: encode_block_mxfp4(s, o); break;
@@ -1197,11 +1317,11 @@ FKO_API int fko_matvec_f32(int kind, const uint8_t* w, int rows, int cols, const
 // row dots, non-repacked.
 FKO_API int fko_matmul_q8(int kind, const uint8_t* w, int rows, int cols, const float* x, int batch, float* out, int nthreads) {
     KindInfo k;
-    if (!kind_info(kind, &k) || cols % 256 != 0 && (kind == 12 || kind == 14)) return -1;
+    if (!kind_info(kind, &k) || cols % 256 != 0 && (kind == 12 || kind == 13 || kind == 14)) return -1;
     if (cols % k.block_elems != 0) return -1;
     int nblk = cols / k.block_elems;
     size_t row_bytes = (size_t)nblk * k.block_bytes;
-    bool kq = (kind == 12 || kind == 14);
+    bool kq = (kind == 12 || kind == 13 || kind == 14);
     std::vector<int8_t> q((size_t)batch * cols);
     std::vector<float> d((size_t)batch * (kq ? cols / 256 : cols / 32));
     std::vector<int16_t> bs(kq ? (size_t)batch * cols / 16 : 1);

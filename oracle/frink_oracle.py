@@ -15,8 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libfrink_oracle.so")
 
 # ggml type tags, shared with include/frink_b200.h
-Q8_0, Q4_K, Q6_K, MXFP4 = 8, 12, 14, 39
-KINDS = {"q8_0": Q8_0, "q4_k": Q4_K, "q6_k": Q6_K, "mxfp4": MXFP4}
+Q8_0, Q4_K, Q5_K, Q6_K, MXFP4 = 8, 12, 13, 14, 39
+KINDS = {"q8_0": Q8_0, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4}
 
 
 def build(force=False):
@@ -170,7 +170,7 @@ def dot_q8(kind, row, x):
     """The reference's CPU integer vec_dot of one row (Q8_K / Q8_0 activations)."""
     row = _c(row, np.uint8).ravel()
     nblk = row.size // block_bytes(kind)
-    if kind in (Q4_K, Q6_K):
+    if kind in (Q4_K, Q5_K, Q6_K):
         q, d, bs = quantize_q8_k(x)
         return float(lib().fko_dot_q8(kind, _p(row), nblk, _p(q), _p(d), _p(bs)))
     q, d = quantize_q8_0_act(x, 1)

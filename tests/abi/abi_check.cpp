@@ -102,7 +102,7 @@ static void no_device_checks() {
     CHECK(fk_block_bytes(FK_Q4_K) == 144 && fk_block_elems(FK_Q4_K) == 256, "Q4_K block");
     CHECK(fk_block_bytes(FK_Q6_K) == 210 && fk_block_elems(FK_Q6_K) == 256, "Q6_K block");
     CHECK(fk_block_bytes(FK_MXFP4) == 17 && fk_block_elems(FK_MXFP4) == 32, "MXFP4 block");
-    CHECK(fk_block_bytes(13) < 0, "a kind without kernels has no block size");
+    CHECK(fk_block_bytes(11) < 0, "a kind without kernels has no block size");
     CHECK(fk_init(0, nullptr) == FK_INVALID, "fk_init(null)");
     CHECK(std::strlen(fk_last_error()) > 0, "a failing call leaves a message");
     CHECK(fk_device_info(nullptr, nullptr, 0, nullptr, nullptr) == FK_INVALID, "device_info(null)");
@@ -175,7 +175,7 @@ int main(int argc, char** argv) {
 
     // refusals: a row size that does not match, a kind without kernels (UNSUPPORTED keeps its meaning: use another path)
     CHECK(fk_launch_matvec(ctx, FK_Q8_0, wq.data(), wq.size(), x.data(), rows, rbc + 2, cols / 32, y.data()) == FK_INVALID, "bad row_bytes");
-    CHECK(fk_launch_matvec(ctx, 13, wq.data(), wq.size(), x.data(), rows, rbc, cols / 32, y.data()) == FK_UNSUPPORTED, "kind 13");
+    CHECK(fk_launch_matvec(ctx, 11, wq.data(), wq.size(), x.data(), rows, rbc, cols / 32, y.data()) == FK_UNSUPPORTED, "kind 11");
     int code = -1;
     CHECK(fk_device_error(ctx, &code, 1) == FK_OK && code == 0, "device error word %d", code);
     fk_forget_resident(ctx);

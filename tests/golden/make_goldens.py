@@ -20,9 +20,10 @@ WANTED = {
     ],
     "crates/frink-quant/src/encode/testdata.rs": ["REAL_WEIGHT_BLOCKS"],
     "crates/frink-quant/src/encode/q4_k.rs": ["LLAMA_CPP_Q4_K_GOLDEN"],
+    "crates/frink-quant/src/encode/q5_k.rs": ["LLAMA_CPP_Q5_K_GOLDEN"],
     "crates/frink-quant/src/encode/q6_k.rs": ["LLAMA_CPP_Q6_K_GOLDEN"],
     "crates/frink-quant/src/lib.rs": [
-        "Q4_K_TEST_BLOCK", "Q4_K_GOLDEN", "Q6_K_TEST_BLOCK", "Q6_K_GOLDEN",
+        "Q4_K_TEST_BLOCK", "Q4_K_GOLDEN", "Q5_K_TEST_BLOCK", "Q5_K_GOLDEN", "Q6_K_TEST_BLOCK", "Q6_K_GOLDEN",
         "Q6_K_SIGNED_SCALES_TEST_BLOCK", "Q6_K_SIGNED_SCALES_GOLDEN",
         "Q6_K_SIGNED_TEST_BLOCK", "Q6_K_SIGNED_GOLDEN",
         "MXFP4_GGUF_TEST_BLOCKS", "MXFP4_GGUF_GOLDEN",

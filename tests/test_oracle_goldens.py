@@ -33,6 +33,7 @@ def test_f16_conversions_match_ieee():
 # crates/frink-quant/src/lib.rs:6532, :6556, :7056, :7124 (dequant goldens, 1e-3)
 @pytest.mark.parametrize("kind,block,gold", [
     (fo.Q4_K, "Q4_K_TEST_BLOCK", "Q4_K_GOLDEN"),
+    (fo.Q5_K, "Q5_K_TEST_BLOCK", "Q5_K_GOLDEN"),
     (fo.Q6_K, "Q6_K_TEST_BLOCK", "Q6_K_GOLDEN"),
     (fo.Q6_K, "Q6_K_SIGNED_SCALES_TEST_BLOCK", "Q6_K_SIGNED_SCALES_GOLDEN"),
     (fo.Q6_K, "Q6_K_SIGNED_TEST_BLOCK", "Q6_K_SIGNED_GOLDEN"),
@@ -51,7 +52,8 @@ def test_dequant_agrees_with_gguf_py():
     quants = pytest.importorskip("gguf.quants")
     import gguf
     rng = np.random.default_rng(7)
-    for kind, qt in [(fo.Q4_K, gguf.GGMLQuantizationType.Q4_K), (fo.Q6_K, gguf.GGMLQuantizationType.Q6_K),
+    for kind, qt in [(fo.Q4_K, gguf.GGMLQuantizationType.Q4_K), (fo.Q5_K, gguf.GGMLQuantizationType.Q5_K),
+                     (fo.Q6_K, gguf.GGMLQuantizationType.Q6_K),
                      (fo.Q8_0, gguf.GGMLQuantizationType.Q8_0), (fo.MXFP4, gguf.GGMLQuantizationType.MXFP4)]:
         w = (rng.standard_normal(8 * 256) * 0.02).astype(np.float32)
         raw = fo.encode(kind, w, threads=1)
@@ -69,7 +71,7 @@ def test_q8_0_encoder_matches_llama_cpp_bytes():
 
 
 # crates/frink-quant/src/encode/q4_k.rs:279, encode/q6_k.rs (goldens over k_quant_fixture)
-@pytest.mark.parametrize("kind,gold", [(fo.Q4_K, "LLAMA_CPP_Q4_K_GOLDEN"), (fo.Q6_K, "LLAMA_CPP_Q6_K_GOLDEN")])
+@pytest.mark.parametrize("kind,gold", [(fo.Q4_K, "LLAMA_CPP_Q4_K_GOLDEN"), (fo.Q5_K, "LLAMA_CPP_Q5_K_GOLDEN"), (fo.Q6_K, "LLAMA_CPP_Q6_K_GOLDEN")])
 def test_k_quant_encoders_match_llama_cpp_bytes(kind, gold):
     x = k_quant_fixture(G["REAL_WEIGHT_BLOCKS"])
     assert x.size == 12 * 256
@@ -132,10 +134,11 @@ def _weights(kind, n_blocks, seed):
 
 
 ALL = [fo.Q4_K, fo.Q6_K, fo.Q8_0, fo.MXFP4]
+WITH_Q5 = ALL + [fo.Q5_K]      # Q5_K has no dp4a twin in the reference (its GPU matvec is generated from the dequant)
 
 
 # crates/frink-quant/src/lib.rs:6544, :6568, :7068 (fused dot == dequantize-then-dot)
-@pytest.mark.parametrize("kind", ALL)
+@pytest.mark.parametrize("kind", WITH_Q5)
 def test_fused_f32_dot_matches_dequant_then_dot(kind):
     nb = 3 * (256 // fo.block_elems(kind))
     row = _weights(kind, nb, 11)
@@ -151,7 +154,7 @@ def test_fused_f32_dot_matches_dequant_then_dot(kind):
 
 # crates/frink-quant/src/lib.rs:5624-5810, legacy_q8.rs:453-524 (the integer dot
 # tracks the float dot within the activation quantization error)
-@pytest.mark.parametrize("kind", ALL)
+@pytest.mark.parametrize("kind", WITH_Q5)
 def test_cpu_integer_dot_tracks_float_dot(kind):
     nb = 4 * (256 // fo.block_elems(kind))
     row = _weights(kind, nb, 5)
@@ -199,7 +202,7 @@ def test_q8_1_quantizer_layout_and_values():
     assert np.array_equal(fo.q8_1_dequant(y)[64:96], b2[4:].view(np.int8).astype(np.float32) * np.float32(d))
 
 
-@pytest.mark.parametrize("kind", ALL)
+@pytest.mark.parametrize("kind", WITH_Q5)
 def test_per_run_isums_reassemble_the_dp4a_twin(kind):
     """The exact per-run integers, scaled the way the block format says, give the
     dequantize-then-dot of the q8_1 input: ties the integer oracle to the formats."""
