@@ -192,4 +192,4 @@ def test_host_buffer_multi_matvec_and_dense_ffn():
     want = fo.matmul_f64(fo.Q6_K, mats["down"][0], rows, ffn, fo.q8_1_round(act))[0]
     assert rel_l2(y, want) <= 1e-3
     with pytest.raises(gpu.Unsupported):
-        gpu.launch_matvec_multi(x, [gpu.MatvecLaunch("q5_k_matvec", mats["q"][0], rows, 1, 1)])
+        gpu.launch_matvec_multi(x, [gpu.MatvecLaunch("q3_k_matvec", mats["q"][0], rows, 1, 1)])
