@@ -551,7 +551,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     # (their few KV heads do not divide by 8)
     try:
         dec = Decoder(cfg, layers, tok, tok_kind, out_norm, output=head, output_kind=tok_kind, max_seq=1024, dense_parallel=cfg.n_experts == 0,
-                      comm=comm)
+                      comm=comm, prefill_acts="q8_k")
     except ValueError as e:
         if world > 1:
             dist.barrier()
@@ -639,7 +639,8 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     res = {
         "model": name, "n_gpus": world, "layers": cfg.n_layers,
         "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
-        "decode_graph": bool(world == 1 or tp_graph), "tg_batch8": b8, "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
+        "decode_graph": bool(world == 1 or tp_graph),
+        "prefill_activations": "Q4_K projections: Q8_K (frink's CPU rule, per 256); other kinds: q8_1 (per 32); decode: q8_1", "tg_batch8": b8, "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
         "collective": None if world == 1 else (
             ("all-reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts else
              "all-reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer") +

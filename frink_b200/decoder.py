@@ -55,15 +55,24 @@ class LayerWeights:
     kinds: dict = field(default_factory=dict)   # name -> fk_kind
 
 
+def prefill_gemm(ops, w, x, acts):
+    """The GEMM of a prompt's rows.  acts = "q8_k": Q4_K weights take the GEMM on Q8_K activations (frink's CPU
+    activation rule, about twice as fast here); every other kind, and acts = "q8_1", the q8_1 GEMM whose integers
+    are the decode matvec's."""
+    if acts == "q8_k" and w.kind == 12 and hasattr(ops, "gemm_q8k"):
+        return ops.gemm_q8k(w, x)
+    return ops.gemm(w, x)
+
+
 class _Linear:
     """rows x cols projection, batch <= 8 through the GEMV, above through the GEMM."""
 
-    def __init__(self, ops, raw, kind, rows, cols):
-        self.ops = ops
+    def __init__(self, ops, raw, kind, rows, cols, acts="q8_1"):
+        self.ops, self.acts = ops, acts
         self.w = ops.Weights(raw, kind, rows, cols)
 
     def __call__(self, x):
-        return self.ops.gemv(self.w, x) if x.shape[0] <= 8 else self.ops.gemm(self.w, x)
+        return self.ops.gemv(self.w, x) if x.shape[0] <= 8 else prefill_gemm(self.ops, self.w, x, self.acts)
 
 
 class _Merged:
@@ -72,9 +81,9 @@ class _Merged:
     several, as the reference shares one quantized input between q/k/v and gate/up
     (crates/frink-cuda/src/dp4a_launch.rs:56-62).  Returns the outputs as column slices."""
 
-    def __init__(self, ops, parts, kind, cols, interleave=False):
+    def __init__(self, ops, parts, kind, cols, interleave=False, acts="q8_1"):
         import numpy as np
-        self.ops, self.splits, self.interleave = ops, [r for _, r in parts], interleave
+        self.ops, self.splits, self.interleave, self.acts = ops, [r for _, r in parts], interleave, acts
         blobs = [np.ascontiguousarray(b, np.uint8).ravel() for b, _ in parts]
         if interleave:
             # two projections of equal height, row i of the first then row i of the second: a lane of the
@@ -87,7 +96,7 @@ class _Merged:
         self.w = ops.Weights(raw, kind, sum(self.splits), cols)
 
     def __call__(self, x):
-        y = self.ops.gemv(self.w, x) if x.shape[0] <= 8 else self.ops.gemm(self.w, x)
+        y = self.ops.gemv(self.w, x) if x.shape[0] <= 8 else prefill_gemm(self.ops, self.w, x, self.acts)
         if self.interleave:
             return [y[:, 0::2], y[:, 1::2]]
         outs, o = [], 0
@@ -99,12 +108,15 @@ class _Merged:
 
 class Decoder:
     def __init__(self, cfg: DecoderConfig, layers: List[LayerWeights], tok_embd, tok_kind, out_norm, output=None, output_kind=None,
-                 max_seq=1024, ops=None, group=None, device="cuda", dense_parallel=True, comm=None):
+                 max_seq=1024, ops=None, group=None, device="cuda", dense_parallel=True, comm=None, prefill_acts="q8_1"):
         """dense_parallel=False: attention and dense projections are replicated on every rank
         (no collectives for them) and only the routed experts are sharded over the group --
         the plan for MoE models whose KV heads do not divide by the number of ranks.
         comm (`frink_b200.comm.Comm`): decode rows are summed across ranks by the peer-memory
-        all-reduce; without it every sum is a `torch.distributed` all-reduce."""
+        all-reduce; without it every sum is a `torch.distributed` all-reduce.
+        prefill_acts: "q8_1" (default: prompt rows are quantized by the decode rule, one set of integers for
+        prefill and decode) or "q8_k" (Q4_K projections of a prompt take the faster GEMM on frink's CPU
+        activation rule; decode is unchanged)."""
         if ops is None:
             from . import device as ops
         self.cfg, self.ops, self.group, self.dev = cfg, ops, group, device
@@ -131,17 +143,17 @@ class Decoder:
             qkv = [(sh(L.wq, k["wq"], cfg.n_heads * hd), k["wq"]), (sh(L.wk, k["wk"], cfg.n_kv * hd), k["wk"]),
                    (sh(L.wv, k["wv"], cfg.n_kv * hd), k["wv"])]
             if k["wq"] == k["wk"] == k["wv"]:
-                d["qkv"] = _Merged(ops, [p for p, _ in qkv], k["wq"], H)
+                d["qkv"] = _Merged(ops, [p for p, _ in qkv], k["wq"], H, acts=prefill_acts)
             elif k["wq"] == k["wk"]:
-                d["qk"] = _Merged(ops, [qkv[0][0], qkv[1][0]], k["wq"], H)
-                d["wv"] = _Linear(ops, qkv[2][0][0], k["wv"], qkv[2][0][1], H)
+                d["qk"] = _Merged(ops, [qkv[0][0], qkv[1][0]], k["wq"], H, acts=prefill_acts)
+                d["wv"] = _Linear(ops, qkv[2][0][0], k["wv"], qkv[2][0][1], H, acts=prefill_acts)
             else:
                 for name, ((raw, rows), kind) in zip(("wq", "wk", "wv"), qkv):
-                    d[name] = _Linear(ops, raw, kind, rows, H)
+                    d[name] = _Linear(ops, raw, kind, rows, H, acts=prefill_acts)
             if T == 1:
-                d["wo"] = _Linear(ops, L.wo, k["wo"], H, cfg.n_heads * hd)
+                d["wo"] = _Linear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, acts=prefill_acts)
             else:
-                d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True, comm=comm)
+                d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True, comm=comm, prefill_acts=prefill_acts)
             if cfg.qk_norm:
                 d["q_norm"], d["k_norm"] = f32(L.q_norm), f32(L.k_norm)
             if cfg.n_experts:
@@ -156,14 +168,14 @@ class Decoder:
             else:
                 gu = [parallel.shard_rows(L.gate, k["gate"], cfg.ffn, H, r_dense, T), parallel.shard_rows(L.up, k["up"], cfg.ffn, H, r_dense, T)]
                 if k["gate"] == k["up"]:
-                    d["gate_up"] = _Merged(ops, gu, k["gate"], H, interleave=True)
+                    d["gate_up"] = _Merged(ops, gu, k["gate"], H, interleave=True, acts=prefill_acts)
                 else:
-                    d["gate"] = _Linear(ops, gu[0][0], k["gate"], gu[0][1], H)
-                    d["up"] = _Linear(ops, gu[1][0], k["up"], gu[1][1], H)
+                    d["gate"] = _Linear(ops, gu[0][0], k["gate"], gu[0][1], H, acts=prefill_acts)
+                    d["up"] = _Linear(ops, gu[1][0], k["up"], gu[1][1], H, acts=prefill_acts)
                 if T == 1:
-                    d["down"] = _Linear(ops, L.down, k["down"], H, cfg.ffn)
+                    d["down"] = _Linear(ops, L.down, k["down"], H, cfg.ffn, acts=prefill_acts)
                 else:
-                    d["down"] = parallel.RowParallelLinear(ops, L.down, k["down"], H, cfg.ffn, group, input_is_sharded=True, comm=comm)
+                    d["down"] = parallel.RowParallelLinear(ops, L.down, k["down"], H, cfg.ffn, group, input_is_sharded=True, comm=comm, prefill_acts=prefill_acts)
             d["k"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
             d["v"] = torch.zeros((max_seq, self.kv_loc * hd), dtype=torch.float32, device=device)
             self.layers.append(d)

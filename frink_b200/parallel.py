@@ -134,10 +134,10 @@ class ColumnParallelLinear:
 class RowParallelLinear:
     """y = sum over ranks of W[:, K range of the rank] x[K range]: one all-reduce."""
 
-    def __init__(self, ops, raw, kind, rows, cols, group=None, input_is_sharded=False, comm=None):
+    def __init__(self, ops, raw, kind, rows, cols, group=None, input_is_sharded=False, comm=None, prefill_acts="q8_1"):
         """comm (`frink_b200.comm.Comm`): decode rows (at most 8) are summed by the peer-memory all-reduce
         instead of the library collective, whose fixed cost is several matvecs at these sizes."""
-        self.ops, self.group, self.input_is_sharded = ops, group, input_is_sharded
+        self.ops, self.group, self.input_is_sharded, self.prefill_acts = ops, group, input_is_sharded, prefill_acts
         self.rank, self.world = _world(group)
         self.comm = comm if comm is not None and self.world > 1 else None
         self.ch = self.comm.channel(8 * rows) if self.comm else None
@@ -166,7 +166,12 @@ class RowParallelLinear:
             w_ = self.cols // self.world
             x2 = x2[:, self.rank * w_:(self.rank + 1) * w_].contiguous()
         x2 = self.padded(x2)
-        y = self.ops.gemv(self.w, x2) if x2.shape[0] <= 8 else self.ops.gemm(self.w, x2)
+        if x2.shape[0] <= 8:
+            y = self.ops.gemv(self.w, x2)
+        elif self.prefill_acts == "q8_k" and self.w.kind == 12 and hasattr(self.ops, "gemm_q8k"):
+            y = self.ops.gemm_q8k(self.w, x2)       # a K range cut inside blocks is masked by zeroed scales: exact here too
+        else:
+            y = self.ops.gemm(self.w, x2)
         if self.world > 1:
             if self.comm is not None and x2.shape[0] <= 8:
                 self.comm.all_reduce(self.ch, y)

@@ -476,3 +476,30 @@ def test_a_decode_batch_of_independent_sequences_matches_each_sequence_alone(moe
     lg = None
     assert out.shape[0] == n_seqs and device.device_error() == 0
     assert dec._seq_pos_host == [int(p) for p in dec.seq_pos.tolist()]
+
+
+def test_prefill_on_q8k_activations_stays_close_to_the_q8_1_pipeline():
+    """`Decoder(prefill_acts="q8_k")`: a prompt's Q4_K projections take the GEMM on Q8_K activations (its integers are
+    frink's CPU vec_dot's, tests/test_gemm_q8k_gpu.py); the logits after a 64-token prompt stay within the distance two
+    8-bit activation quantizers put between two pipelines, and where the oracle's margin is decisive the greedy
+    continuation is the same."""
+    from frink_b200.decoder import Decoder
+    cfg, layers, tok, out_norm, _ = recipe_llama()
+    head, _ = decisive_head(cfg, tok)
+    prompt = torch.from_numpy(np.random.default_rng(0x70C).integers(0, cfg.vocab, 64).astype(np.int32)).cuda()
+    a = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=128)
+    b = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=128, prefill_acts="q8_k")
+    la, lb = a.forward(prompt).cpu().numpy()[0], b.forward(prompt).cpu().numpy()[0]
+    r = rel_l2(lb, la)
+    print(f"q8_k prefill against q8_1 prefill: rel-L2 {r:.2e}")
+    assert r <= 5e-2
+    top2 = np.sort(la)[-2:]
+    if (top2[1] - top2[0]) / np.std(la) > 0.2:
+        assert int(np.argmax(la)) == int(np.argmax(lb))
+    a.reset()
+    b.reset()
+    ga, gb = a.generate(prompt, 16), b.generate(prompt, 16)
+    same = sum(x == y for x, y in zip(ga, gb))
+    print(f"greedy continuation: {same} of 16 tokens equal")
+    from frink_b200 import device
+    assert device.device_error() == 0
