@@ -479,42 +479,61 @@ attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restri
             *(float4*)(sv + kk * head_dim + 4 * c) = vv4;
         }
         __syncthreads();
+        // the warp's rows together: a key's row of K (and of V below) is read once from shared memory for all of them.
+        // Every row's own sums run in the same order as if it were alone.
+        const int key = t0 + lane;
+        int nk[PF_RPW];
+        bool act[PF_RPW];
+        float d[PF_RPW], p[PF_RPW];
 #pragma unroll
         for (int i = 0; i < PF_RPW; i++) {
-            const int rr = warp * PF_RPW + i, r = r0 + rr;
-            if (r >= n_q) continue;
-            const int n_keys = p0 + r + 1;
-            if (t0 >= n_keys) continue;
-            const int key = t0 + lane;
-            float sc = -INFINITY;
-            if (key < n_keys) {
-                float d = 0.0f;
-                const float* kr = sk + lane * kpad;
-                const float* qr = sq + rr * head_dim;
-                for (int c = 0; c < hd4; c++) {
-                    const float4 kv4 = *(const float4*)(kr + 4 * c), qv = *(const float4*)(qr + 4 * c);
-                    d += kv4.x * qv.x + kv4.y * qv.y + kv4.z * qv.z + kv4.w * qv.w;
+            const int r = r0 + warp * PF_RPW + i;
+            nk[i] = p0 + r + 1;
+            act[i] = r < n_q && t0 < nk[i];
+            d[i] = 0.0f;
+            p[i] = 0.0f;
+        }
+        bool any = false;
+#pragma unroll
+        for (int i = 0; i < PF_RPW; i++) any = any || act[i];
+        if (!any) continue;                                  // none of the warp's rows sees this tile
+        {
+            const float* kr = sk + lane * kpad;
+            const float* qr = sq + warp * PF_RPW * head_dim;
+            for (int c = 0; c < hd4; c++) {
+                const float4 kv4 = *(const float4*)(kr + 4 * c);
+#pragma unroll
+                for (int i = 0; i < PF_RPW; i++) {
+                    const float4 qv = *(const float4*)(qr + i * head_dim + 4 * c);
+                    d[i] += kv4.x * qv.x + kv4.y * qv.y + kv4.z * qv.z + kv4.w * qv.w;
                 }
-                sc = d * scale;
             }
+        }
+        int cnt = 0;
+#pragma unroll
+        for (int i = 0; i < PF_RPW; i++) {
+            if (!act[i]) continue;
+            const float sc = key < nk[i] ? d[i] * scale : -INFINITY;
             float tm = sc;
             for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
             const float m_new = fmaxf(m[i], tm);
-            const float p = key < n_keys ? expf(sc - m_new) : 0.0f;
-            float ts = p;
+            p[i] = key < nk[i] ? expf(sc - m_new) : 0.0f;
+            float ts = p[i];
             for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
             const float corr = expf(m[i] - m_new);
             s[i] = s[i] * corr + ts;
             acc[i].x *= corr; acc[i].y *= corr; acc[i].z *= corr; acc[i].w *= corr;
-            const int cnt = min(32, n_keys - t0);
-            for (int j = 0; j < cnt; j++) {
-                const float pj = __shfl_sync(0xffffffffu, p, j);
-                if (owns) {
-                    const float4 vv = *(const float4*)(sv + j * head_dim + 4 * lane);
-                    acc[i].x += pj * vv.x; acc[i].y += pj * vv.y; acc[i].z += pj * vv.z; acc[i].w += pj * vv.w;
-                }
-            }
             m[i] = m_new;
+            cnt = max(cnt, min(32, nk[i] - t0));
+        }
+        for (int j = 0; j < cnt; j++) {
+            float4 vv = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (owns) vv = *(const float4*)(sv + j * head_dim + 4 * lane);
+#pragma unroll
+            for (int i = 0; i < PF_RPW; i++) {
+                const float pj = __shfl_sync(0xffffffffu, p[i], j);
+                acc[i].x += pj * vv.x; acc[i].y += pj * vv.y; acc[i].z += pj * vv.z; acc[i].w += pj * vv.w;
+            }
         }
     }
 #pragma unroll
