@@ -506,6 +506,44 @@ __global__ void quantize_acts_kernel(const float* __restrict__ x, const int* __r
     }
 }
 
+// The same for the kinds whose int8 plane keeps the elements in order (all but MXFP4): a thread takes four values, eight
+// lanes make a run, rows past the live tiles (`*n_tiles_dev * bn`, grouped form) are left alone -- no tile reads them.
+__global__ void quantize_acts4_kernel(const float* __restrict__ x, const int* __restrict__ src_row, int n_pad, int cols, int8_t* __restrict__ q,
+                                      float* __restrict__ dx, float* __restrict__ sx, const int* __restrict__ n_tiles_dev, int bn) {
+    const int nkb = cols >> 5;
+    const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long run = gid >> 3;
+    const int part = (int)(gid & 7);
+    const int n_live = n_tiles_dev ? min(n_pad, *n_tiles_dev * bn) : n_pad;
+    const bool ok = run < (long long)n_live * nkb;          // whole groups of eight lanes are in or out
+    const int t = ok ? (int)(run / nkb) : 0, kb = ok ? (int)(run - (long long)t * nkb) : 0;
+    const int src = ok ? src_row[t] : -1;
+    float4 f = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (src >= 0) f = __ldg((const float4*)(x + (size_t)src * cols + kb * 32) + part);
+    unsigned mb = __float_as_uint(fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+    mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+    mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+    mb = max(mb, __shfl_xor_sync(0xffffffffu, mb, 4));
+    const float amax = __uint_as_float(mb);
+    const float d = amax / 127.0f;
+    int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+    if (amax != 0.0f) {
+        q0 = (int)roundf(f.x / d); q1 = (int)roundf(f.y / d); q2 = (int)roundf(f.z / d); q3 = (int)roundf(f.w / d);
+    }
+    int qsum = q0 + q1 + q2 + q3;
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 1);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 2);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, 4);
+    if (!ok) return;
+    *(uint32_t*)(q + (size_t)t * cols + kb * 32 + part * 4) =
+        (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+    if (part == 0) {
+        const float dq = fk_h2f(fk_f2h(d));
+        dx[(size_t)kb * n_pad + t] = dq;
+        if (sx) sx[(size_t)kb * n_pad + t] = dq * (float)qsum;
+    }
+}
+
 // Dense plan: padded row t reads token t (t < m) and writes output row t.
 __global__ void dense_plan_kernel(int m, int n_pad, int* src_row, int* out_row) {
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -516,34 +554,42 @@ __global__ void dense_plan_kernel(int m, int n_pad, int* src_row, int* out_row) 
 }
 
 // Grouped plan (one block): every expert's rows padded up to whole tiles of BN.
-// Permuted row p of expert e lands at pad_off[e] + (p - group_off[e]).
+// Permuted row p of expert e lands at pad_off[e] + (p - group_off[e]).  The offsets are a serial scan by one thread
+// (a few hundred additions); everything else is spread over the block: a thread finds its row's expert by bisecting
+// the group offsets in shared memory.
 __global__ void grouped_plan_kernel(const int* __restrict__ group_off, const int* __restrict__ gather, int n_experts, int bn,
                                     int n_pad, int* src_row, int* out_row, int* tile_expert, int* n_tiles) {
-    extern __shared__ int pad_off[];  // [n_experts + 1]
+    extern __shared__ int sm_plan[];  // pad_off [n_experts + 1] | group_off [n_experts + 1]
+    int* pad_off = sm_plan;
+    int* goff = sm_plan + n_experts + 1;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) goff[e] = group_off[e];
+    __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;
         for (int e = 0; e < n_experts; e++) {
             pad_off[e] = acc;
-            const int cnt = group_off[e + 1] - group_off[e];
-            const int tiles = (cnt + bn - 1) / bn;
-            for (int i = 0; i < tiles; i++) tile_expert[acc / bn + i] = e;
-            acc += tiles * bn;
+            acc += (goff[e + 1] - goff[e] + bn - 1) / bn * bn;
         }
         pad_off[n_experts] = acc;
         *n_tiles = acc / bn;
     }
-    __syncthreads();
     for (int t = threadIdx.x; t < n_pad; t += blockDim.x) {
         src_row[t] = -1;
         out_row[t] = -1;
     }
     __syncthreads();
-    for (int e = 0; e < n_experts; e++) {
-        const int g0 = group_off[e], cnt = group_off[e + 1] - g0;
-        for (int i = threadIdx.x; i < cnt; i += blockDim.x) {
-            src_row[pad_off[e] + i] = gather ? gather[g0 + i] : g0 + i;
-            out_row[pad_off[e] + i] = g0 + i;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+        for (int tl = pad_off[e] / bn; tl < pad_off[e + 1] / bn; tl++) tile_expert[tl] = e;
+    const int pairs = goff[n_experts];
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        int lo = 0, hi = n_experts;          // the expert e with goff[e] <= p < goff[e + 1] (empty experts are skipped by the bisection)
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (goff[mid] <= p) lo = mid; else hi = mid;
         }
+        const int dst = pad_off[lo] + (p - goff[lo]);
+        src_row[dst] = gather ? gather[p] : p;
+        out_row[dst] = p;
     }
 }
 
@@ -658,14 +704,18 @@ int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* g
     int* n_tiles = (int*)(sc + off_nt);
 
     if (grouped) {
-        grouped_plan_kernel<<<1, 1024, (w->n_mats + 1) * sizeof(int), st>>>(group_off, gather, w->n_mats, bn, n_pad, src_row, out_row,
+        grouped_plan_kernel<<<1, 1024, 2 * (w->n_mats + 1) * sizeof(int), st>>>(group_off, gather, w->n_mats, bn, n_pad, src_row, out_row,
                                                                              tile_expert, n_tiles);
     } else {
         dense_plan_kernel<<<(n_pad + 255) / 256, 256, 0, st>>>(n_tokens, n_pad, src_row, out_row);
     }
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     const long long runs = (long long)n_pad * nkb;
-    quantize_acts_kernel<<<(unsigned)((runs + 7) / 8), 256, 0, st>>>(x, src_row, n_pad, w->cols, w->kind, q, dx, w->kind == FK_Q4_K ? sx : nullptr);
+    if (w->kind == FK_MXFP4)
+        quantize_acts_kernel<<<(unsigned)((runs + 7) / 8), 256, 0, st>>>(x, src_row, n_pad, w->cols, w->kind, q, dx, nullptr);
+    else
+        quantize_acts4_kernel<<<(unsigned)((runs + 31) / 32), 256, 0, st>>>(x, src_row, n_pad, w->cols, q, dx, w->kind == FK_Q4_K ? sx : nullptr,
+                                                                            grouped ? n_tiles : nullptr, bn);
     FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches += 2;
 

@@ -128,21 +128,18 @@ __global__ void router_route_kernel(const float* __restrict__ w, const float* __
     if (threadIdx.x == 0) *cnt = 0;
 }
 
-// Stable counting sort of the (token, slot) pairs by expert, in one block.
-// Warp `e mod nwarps` owns expert e: it scans the pair list 32 at a time and
-// places matches with a ballot, so pairs keep ascending order inside a group
-// and the result is the same on every run.
+// Stable counting sort of the (token, slot) pairs by expert, in one block: counts by shared-memory
+// atomics, offsets by one thread, then the pairs are placed in pair order (chunk by chunk, warp by warp,
+// lane by lane), so pairs keep ascending order inside a group and the result is the same on every run.
 __global__ void permute_kernel(const int* __restrict__ ids, int pairs, int k, int n_experts, int* __restrict__ group_off,
                                int* __restrict__ gather, int* __restrict__ pair_of) {
-    extern __shared__ int counts[];  // [n_experts + 1]
+    extern __shared__ int counts[];  // [n_experts + 1]: counts, then each expert's next free place
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int e = warp; e < n_experts; e += nwarps) {
-        int c = 0;
-        for (int p0 = 0; p0 < pairs; p0 += 32) {
-            const int p = p0 + lane;
-            c += __popc(__ballot_sync(0xffffffffu, p < pairs && ids[p] == e));
-        }
-        if (lane == 0) counts[e] = c;
+    for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = ids[p];
+        if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);      // integer counts: the order of the additions does not matter
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -157,18 +154,26 @@ __global__ void permute_kernel(const int* __restrict__ ids, int pairs, int k, in
         group_off[n_experts] = acc;
     }
     __syncthreads();
-    for (int e = warp; e < n_experts; e += nwarps) {
-        int base = counts[e];
-        for (int p0 = 0; p0 < pairs; p0 += 32) {
-            const int p = p0 + lane;
-            const bool hit = p < pairs && ids[p] == e;
-            const unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                const int pos = base + __popc(m & ((1u << lane) - 1u));
-                gather[pos] = p / k;
-                pair_of[p] = pos;
+    // Places, in pair order: a chunk of blockDim pairs at a time; inside a chunk the warps take turns (warp w holds pairs
+    // before warp w + 1's), and inside a warp the lanes with the same expert are ranked by lane.
+    for (int p0 = 0; p0 < pairs; p0 += blockDim.x) {
+        const int p = p0 + threadIdx.x;
+        int e = p < pairs ? ids[p] : -1;
+        if (e >= n_experts) e = -1;
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        const int rank = __popc(same & ((1u << lane) - 1u)), leader = __ffs(same) - 1;
+        int base = 0;
+        for (int w = 0; w < nwarps; w++) {
+            if (warp == w && e >= 0 && lane == leader) {
+                base = counts[e];
+                counts[e] = base + __popc(same);
             }
-            base += __popc(m);
+            __syncthreads();
+        }
+        base = __shfl_sync(0xffffffffu, base, leader);
+        if (e >= 0) {
+            gather[base + rank] = p / k;
+            pair_of[p] = base + rank;
         }
     }
 }
