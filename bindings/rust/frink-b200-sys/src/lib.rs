@@ -447,6 +447,8 @@ extern "C" {
         scale: f32,
         out_dev: *mut f32,
         cache_rows: c_int,
+        window: c_int,
+        sinks_dev: *const f32,
     ) -> c_int;
     pub fn fk_attention_rope_kv(
         ctx: *mut FkCtx,
@@ -468,6 +470,8 @@ extern "C" {
         norm_eps: f32,
         out_dev: *mut f32,
         cache_rows: c_int,
+        window: c_int,
+        sinks_dev: *const f32,
     ) -> c_int;
     pub fn fk_attention_rope_kv_seqs(
         ctx: *mut FkCtx,
@@ -494,6 +498,8 @@ extern "C" {
         norm_eps: f32,
         out_dev: *mut f32,
         cache_rows: c_int,
+        window: c_int,
+        sinks_dev: *const f32,
     ) -> c_int;
     pub fn fk_argmax(
         ctx: *mut FkCtx,

@@ -59,9 +59,9 @@ SYMBOLS = {
     "fk_rope_kv": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P, C.c_float, _I, _P, _P, _P, _P, C.c_float, _I]),
     "fk_add": (_I, [_P, _P, _P, _P, _SZ]),
     "fk_kv_append": (_I, [_P, _P, _P, _P, _SZ, _I, _P, _I]),
-    "fk_attention_rope_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I]),
-    "fk_attention_rope_kv_seqs": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _SZ, _I, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I]),
-    "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P, _I]),
+    "fk_attention_rope_kv": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
+    "fk_attention_rope_kv_seqs": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _SZ, _I, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
+    "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P, _I, _I, _P]),
     "fk_reserve_scratch": (_I, [_P, _SZ]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),
     "fk_add_int": (_I, [_P, _P, _P, _I]),

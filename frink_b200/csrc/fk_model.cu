@@ -257,6 +257,11 @@ struct AttnFuse {
     // caches r * seq_stride floats further on; k_new / v_new rows are k_ld / v_ld floats apart
     size_t seq_stride;
     int k_ld, v_ld;
+    // gpt-oss attention (crates/frink-core/src/attention.rs:312-322, 960-1000): a query sees only the `window` most recent
+    // keys including its own (0 = all), and one learned logit per query head (`sinks`, null = none) joins the softmax's
+    // denominator without contributing to the output
+    int window;
+    const float* sinks;
 };
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_heads, int n_kv, int head_dim,
@@ -280,8 +285,9 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
     const int split = blockIdx.x, S = gridDim.x, h = blockIdx.y, r = blockIdx.z, kvh = h / (n_heads / n_kv);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, sub = lane & 7;
     const int n_keys = p_row + 1;
-    const int chunk = ((n_keys + S - 1) / S + 15) & ~15;
-    const int c0 = split * chunk, c1 = min(n_keys, c0 + chunk);
+    const int k_lo = f.window > 0 ? max(0, n_keys - f.window) : 0;     // first visible key
+    const int chunk = ((n_keys - k_lo + S - 1) / S + 15) & ~15;
+    const int c0 = k_lo + split * chunk, c1 = min(n_keys, c0 + chunk);
     const float* qr = q + (size_t)r * q_ld + (size_t)h * head_dim;
     for (int i = threadIdx.x; i < head_dim; i += blockDim.x) sq[i] = qr[i];
     __syncthreads();
@@ -422,7 +428,7 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
         for (int o = 16; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
         if (h0) s_c[lane] = w0;
         if (h1) s_c[lane + 32] = w1;
-        if (lane == 0) s_gs = gs;
+        if (lane == 0) s_gs = f.sinks ? gs + expf(f.sinks[h] - gm) : gs;      // the sink's share of the softmax, none of the output
     }
     __syncthreads();
     if (threadIdx.x < head_dim) {
@@ -441,7 +447,8 @@ attn_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbu
 constexpr int PF_ROWS = 32, PF_WARPS = 8, PF_RPW = PF_ROWS / PF_WARPS;
 __global__ void __launch_bounds__(PF_WARPS * 32)
 attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restrict__ kbuf, const float* __restrict__ vbuf, int n_q, int n_heads, int n_kv,
-                    int head_dim, const int* __restrict__ pos, float scale, float* __restrict__ out, int cache_rows, int* __restrict__ err) {
+                    int head_dim, const int* __restrict__ pos, float scale, float* __restrict__ out, int cache_rows, int* __restrict__ err,
+                    int window, const float* __restrict__ sinks) {
     if (fk_cache_overrun(*pos, n_q, cache_rows, err)) return;
     extern __shared__ __align__(16) float sm[];
     const int kpad = head_dim + 4;
@@ -466,7 +473,10 @@ attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restri
     const bool owns = 4 * lane < head_dim;
     const int last_row = min(n_q, r0 + PF_ROWS) - 1;
     const int n_keys_max = p0 + last_row + 1;
-    for (int t0 = 0; t0 < n_keys_max; t0 += 32) {
+    // with a window, the block's first row sees the oldest key: tiles before it are skipped (32-aligned, so the tiles are
+    // the same as without a window)
+    const int t_first = window > 0 ? (max(0, p0 + r0 + 1 - window) & ~31) : 0;
+    for (int t0 = t_first; t0 < n_keys_max; t0 += 32) {
         __syncthreads();
         for (int i = threadIdx.x; i < 32 * hd4; i += blockDim.x) {
             const int kk = i / hd4, c = i % hd4;
@@ -482,14 +492,15 @@ attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restri
         // the warp's rows together: a key's row of K (and of V below) is read once from shared memory for all of them.
         // Every row's own sums run in the same order as if it were alone.
         const int key = t0 + lane;
-        int nk[PF_RPW];
+        int nk[PF_RPW], lo[PF_RPW];
         bool act[PF_RPW];
         float d[PF_RPW], p[PF_RPW];
 #pragma unroll
         for (int i = 0; i < PF_RPW; i++) {
             const int r = r0 + warp * PF_RPW + i;
             nk[i] = p0 + r + 1;
-            act[i] = r < n_q && t0 < nk[i];
+            lo[i] = window > 0 ? max(0, nk[i] - window) : 0;
+            act[i] = r < n_q && t0 < nk[i] && t0 + 32 > lo[i];
             d[i] = 0.0f;
             p[i] = 0.0f;
         }
@@ -513,11 +524,12 @@ attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restri
 #pragma unroll
         for (int i = 0; i < PF_RPW; i++) {
             if (!act[i]) continue;
-            const float sc = key < nk[i] ? d[i] * scale : -INFINITY;
+            const bool vis = key < nk[i] && key >= lo[i];
+            const float sc = vis ? d[i] * scale : -INFINITY;
             float tm = sc;
             for (int o = 16; o > 0; o >>= 1) tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, o));
             const float m_new = fmaxf(m[i], tm);
-            p[i] = key < nk[i] ? expf(sc - m_new) : 0.0f;
+            p[i] = vis ? expf(sc - m_new) : 0.0f;
             float ts = p[i];
             for (int o = 16; o > 0; o >>= 1) ts += __shfl_xor_sync(0xffffffffu, ts, o);
             const float corr = expf(m[i] - m_new);
@@ -540,7 +552,7 @@ attn_prefill_kernel(const float* __restrict__ q, int q_ld, const float* __restri
     for (int i = 0; i < PF_RPW; i++) {
         const int r = r0 + warp * PF_RPW + i;
         if (r < n_q && owns) {
-            const float inv = 1.0f / s[i];
+            const float inv = 1.0f / (sinks ? s[i] + expf(sinks[h] - m[i]) : s[i]);
             float* orow = out + ((size_t)r * n_heads + h) * head_dim + 4 * lane;
             orow[0] = acc[i].x * inv; orow[1] = acc[i].y * inv; orow[2] = acc[i].z * inv; orow[3] = acc[i].w * inv;
         }
@@ -713,9 +725,10 @@ FK_EXPORT int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const fl
 }
 
 FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
-                           int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows) {
+                           int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows, int window,
+                           const float* sinks_dev) {
     if (!ctx || !q_dev || !k_dev || !v_dev || !pos_dev || !out_dev) return fk_fail(FK_INVALID, "attention: null argument");
-    if (cache_rows < n_q) return fk_fail(FK_INVALID, "attention: %d queries over caches of %d rows", n_q, cache_rows);
+    if (cache_rows < n_q || window < 0) return fk_fail(FK_INVALID, "attention: %d queries over caches of %d rows, window %d", n_q, cache_rows, window);
     if (n_q < 1 || n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > 65535)
         return fk_fail(FK_UNSUPPORTED, "attention: %d queries, %d/%d heads of %d", n_q, n_heads, n_kv, head_dim);
     if (q_ld == 0) q_ld = n_heads * head_dim;
@@ -726,7 +739,7 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
         FK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_KERNEL);
         FK_CARVEOUT(attn_prefill_kernel);
         attn_prefill_kernel<<<dim3((n_q + PF_ROWS - 1) / PF_ROWS, n_heads), PF_WARPS * 32, smem, (cudaStream_t)stream>>>(
-            q_dev, q_ld, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, cache_rows, ctx->err_flag);
+            q_dev, q_ld, k_dev, v_dev, n_q, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, cache_rows, ctx->err_flag, window, sinks_dev);
     } else {
         if (n_q * n_heads > AD_MAX_CNT) return fk_fail(FK_UNSUPPORTED, "attention: %d rows x %d heads", n_q, n_heads);
         int splits = 4 * ctx->sm_count / (n_heads * n_q);
@@ -735,6 +748,8 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
         if (rc != FK_OK) return rc;
         FK_CARVEOUT(attn_kernel);
         AttnFuse nofuse{};
+        nofuse.window = window;
+        nofuse.sinks = sinks_dev;
         FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_q), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, k_dev, v_dev,
                               n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, nofuse, cache_rows, ctx->err_flag), FK_LAUNCH);
     }
@@ -744,9 +759,11 @@ FK_EXPORT int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_
 
 FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
                                    float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
-                                   const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows) {
+                                   const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows, int window,
+                                   const float* sinks_dev) {
     if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !k_cache_dev || !v_cache_dev || !pos_dev || !out_dev)
         return fk_fail(FK_INVALID, "attention_rope_kv: null argument");
+    if (window < 0) return fk_fail(FK_INVALID, "attention_rope_kv: window %d", window);
     if (cache_rows < 1) return fk_fail(FK_INVALID, "attention_rope_kv: caches of %d rows", cache_rows);
     if (n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_heads > AD_MAX_CNT)
         return fk_fail(FK_UNSUPPORTED, "attention_rope_kv: %d/%d heads of %d", n_heads, n_kv, head_dim);
@@ -757,7 +774,7 @@ FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev
     splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
     const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_heads * splits * AD_REC * sizeof(float));
     if (rc != FK_OK) return rc;
-    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, 0, 0, 0};
+    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, 0, 0, 0, window, sinks_dev};
     FK_CARVEOUT(attn_kernel);
     FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, 1), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, n_heads * head_dim, (const float*)k_cache_dev,
                           (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f, cache_rows,
@@ -771,7 +788,7 @@ FK_EXPORT int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev
 FK_EXPORT int fk_attention_rope_kv_seqs(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_new_dev, const float* v_new_dev, int k_ld,
                                         int v_ld, float* k_cache_dev, float* v_cache_dev, size_t seq_stride, int n_seqs, int n_heads, int n_kv, int head_dim,
                                         const int* pos_dev, float scale, float theta, int neox, const float* q_norm_dev, const float* k_norm_dev,
-                                        float norm_eps, float* out_dev, int cache_rows) {
+                                        float norm_eps, float* out_dev, int cache_rows, int window, const float* sinks_dev) {
     if (!ctx || !q_dev || !k_new_dev || !v_new_dev || !k_cache_dev || !v_cache_dev || !pos_dev || !out_dev)
         return fk_fail(FK_INVALID, "attention_rope_kv_seqs: null argument");
     if (n_seqs < 1 || n_heads < 1 || n_kv < 1 || n_heads % n_kv || head_dim > 128 || (head_dim & 3) || n_seqs * n_heads > AD_MAX_CNT)
@@ -787,7 +804,7 @@ FK_EXPORT int fk_attention_rope_kv_seqs(fk_ctx* ctx, void* stream, const float* 
     splits = splits < 1 ? 1 : splits > AD_MAX_SPLITS ? AD_MAX_SPLITS : splits;
     const int rc = fk_ensure_scratch(ctx, (cudaStream_t)stream, (size_t)n_seqs * n_heads * splits * AD_REC * sizeof(float));
     if (rc != FK_OK) return rc;
-    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, seq_stride, k_ld, v_ld};
+    AttnFuse f{k_new_dev, v_new_dev, k_cache_dev, v_cache_dev, q_norm_dev, k_norm_dev, theta, norm_eps, neox, 1, seq_stride, k_ld, v_ld, window, sinks_dev};
     FK_CARVEOUT(attn_kernel);
     FK_CUDA(fk_launch_pdl(attn_kernel, dim3(splits, n_heads, n_seqs), dim3(AD_WARPS * 32), 0, (cudaStream_t)stream, q_dev, q_ld, (const float*)k_cache_dev,
                           (const float*)v_cache_dev, n_heads, n_kv, head_dim, pos_dev, scale, out_dev, (float*)ctx->scratch, ctx->attn_cnt, f, cache_rows,

@@ -13,6 +13,7 @@ experts are expert parallel (`parallel.ExpertParallelLayer.decode`)."""
 from dataclasses import dataclass, field
 from typing import Any, List, Optional
 
+import numpy as np
 import torch
 
 from . import parallel
@@ -35,6 +36,13 @@ class DecoderConfig:
     n_experts: int = 0          # > 0: routed FFN
     top_k: int = 0
     route_mode: int = 1
+    sliding_window: int = 0     # gpt-oss: > 0 = windowed layers see only this many most recent keys
+    swa_period: int = 0         # which layers are windowed: all (0), or layer i with i % period < period - 1 (gpt-oss: 2)
+
+    def window_of(self, layer):
+        if self.sliding_window <= 0:
+            return 0
+        return self.sliding_window if self.swa_period <= 0 or layer % self.swa_period < self.swa_period - 1 else 0
 
 
 @dataclass
@@ -52,6 +60,7 @@ class LayerWeights:
     router: Any = None          # f32 [n_experts, hidden]
     q_norm: Any = None
     k_norm: Any = None
+    sinks: Any = None           # gpt-oss attention sinks, f32 [n_heads]
     kinds: dict = field(default_factory=dict)   # name -> fk_kind
 
 
@@ -156,6 +165,9 @@ class Decoder:
                 d["wo"] = parallel.RowParallelLinear(ops, L.wo, k["wo"], H, cfg.n_heads * hd, group, input_is_sharded=True, comm=comm, prefill_acts=prefill_acts)
             if cfg.qk_norm:
                 d["q_norm"], d["k_norm"] = f32(L.q_norm), f32(L.k_norm)
+            # attention options of the layer: the window (0 = full) and this rank's heads' sinks
+            d["window"] = cfg.window_of(len(self.layers))
+            d["sinks"] = None if L.sinks is None else f32(np.asarray(L.sinks, np.float32)[r_dense * self.h_loc:(r_dense + 1) * self.h_loc])
             if cfg.n_experts:
                 router = f32(L.router)
                 if E == 1:
@@ -222,7 +234,7 @@ class Decoder:
                 ops.rope(k, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox)
                 ops.kv_append(L["k"], k, self.pos)
                 ops.kv_append(L["v"], v, self.pos)
-            a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
+            a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, window=L["window"], sinks=L["sinks"])
             o = L["wo"](a)
             h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps, residual=o)
             if "moe" in L:
@@ -336,7 +348,7 @@ class Decoder:
             window = getattr(L["wo"], "window", None)
             if seqs:
                 a = ops.attention_rope_kv_seqs(q, k, v, L["ks"], L["vs"], self.h_loc, self.kv_loc, hd, self.seq_pos, cfg.rope_theta, cfg.neox,
-                                               q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
+                                               q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps, window=L["window"], sinks=L["sinks"])
             elif n == 1 and hasattr(ops, "attention_rope_kv") and window is not None:
                 # this rank's heads are a K range cut inside the blocks of wo: attention writes straight into the window
                 # of the zero-padded row the local product reads
@@ -344,17 +356,17 @@ class Decoder:
                     L["wo"].row = torch.zeros((1, L["wo"].cols_local), dtype=torch.float32, device=x.device)
                 ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
                                       q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps,
-                                      out=L["wo"].row[:, window[0]:window[0] + window[1]])
+                                      out=L["wo"].row[:, window[0]:window[0] + window[1]], window=L["window"], sinks=L["sinks"])
                 a = None
             elif n == 1 and hasattr(ops, "attention_rope_kv"):
                 a = ops.attention_rope_kv(q, k, v, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox,
-                                          q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
+                                          q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps, window=L["window"], sinks=L["sinks"])
             else:
                 if n > 1 and k.stride(0) != v.stride(0):
                     k, v = k.contiguous(), v.contiguous()          # the cache append wants one row stride for both
                 ops.rope_kv(q, k, v, self.h_loc, self.kv_loc, hd, self.pos, cfg.rope_theta, cfg.neox, L["k"], L["v"],
                             q_norm=L.get("q_norm"), k_norm=L.get("k_norm"), eps=cfg.eps)
-                a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos)
+                a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, window=L["window"], sinks=L["sinks"])
             if a is None:
                 into_residual(L["wo"], L["wo"].row, is_padded=True)
             else:

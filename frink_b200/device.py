@@ -415,21 +415,26 @@ def kv_append(cache, src, pos):
     check(lib().fk_kv_append(context(cache.device), _stream(), _ptr(cache), _ptr(src), cache.shape[1], n, _ptr(_i32(pos)), cache.shape[0]))
 
 
-def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
+def _sinks(sinks):
+    return _ptr(_f32(sinks)) if sinks is not None else None
+
+
+def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None, window=0, sinks=None):
     """q: [n, n_heads * head_dim] with any row stride that is a multiple of 4 floats (a column
-    slice of a merged q/k/v output works), or one row."""
+    slice of a merged q/k/v output works), or one row.  window > 0: only the `window` most recent
+    keys; sinks [n_heads]: gpt-oss's per-head logit in the softmax's denominator."""
     assert q.is_cuda and q.dtype == torch.float32 and q.stride(-1) == 1
     q2 = q if q.dim() == 2 else q[None]
     o = out if out is not None else torch.empty((q2.shape[0], n_heads * head_dim), dtype=torch.float32, device=q.device)
     sc = float(scale) if scale is not None else head_dim ** -0.5
     ld = q2.stride(0) if q2.shape[0] > 1 else 0
     check(lib().fk_attention(context(q.device), _stream(), _ptr(q2), ld, _ptr(k_cache), _ptr(v_cache), q2.shape[0], n_heads, n_kv, head_dim,
-                             _ptr(_i32(pos)), sc, _ptr(o), min(k_cache.shape[0], v_cache.shape[0])))
+                             _ptr(_i32(pos)), sc, _ptr(o), min(k_cache.shape[0], v_cache.shape[0]), int(window), _sinks(sinks)))
     return o if q.dim() == 2 else o[0]
 
 
 def attention_rope_kv(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv, head_dim, pos, theta, neox=False, q_norm=None, k_norm=None, eps=0.0,
-                      scale=None, out=None):
+                      scale=None, out=None, window=0, sinks=None):
     """One decode row: rotate q and the new k at pos[0] (after Qwen3's head norms when given),
     append k and v to the caches and attend over positions 0 ..= pos[0], in one launch.
     q [1, n_heads*head_dim], k_new / v_new [1, n_kv*head_dim] (column slices are fine)."""
@@ -439,12 +444,12 @@ def attention_rope_kv(q, k_new, v_new, k_cache, v_cache, n_heads, n_kv, head_dim
     check(lib().fk_attention_rope_kv(context(q.device), _stream(), _ptr(q), _ptr(k_new), _ptr(v_new), _ptr(k_cache), _ptr(v_cache), n_heads, n_kv,
                                      head_dim, _ptr(_i32(pos)), sc, float(theta), int(neox),
                                      _ptr(_f32(q_norm)) if q_norm is not None else None, _ptr(_f32(k_norm)) if k_norm is not None else None,
-                                     float(eps), _ptr(o), min(k_cache.shape[0], v_cache.shape[0])))
+                                     float(eps), _ptr(o), min(k_cache.shape[0], v_cache.shape[0]), int(window), _sinks(sinks)))
     return o
 
 
 def attention_rope_kv_seqs(q, k_new, v_new, k_caches, v_caches, n_heads, n_kv, head_dim, pos, theta, neox=False, q_norm=None, k_norm=None,
-                           eps=0.0, scale=None, out=None):
+                           eps=0.0, scale=None, out=None, window=0, sinks=None):
     """One decode step of independent sequences: row r of q / k_new / v_new (column slices are fine) is sequence r's
     token at position pos[r]; k_caches / v_caches are [n_seqs, T, n_kv*head_dim]."""
     n = q.shape[0]
@@ -456,7 +461,8 @@ def attention_rope_kv_seqs(q, k_new, v_new, k_caches, v_caches, n_heads, n_kv, h
     check(lib().fk_attention_rope_kv_seqs(context(q.device), _stream(), _ptr(q), q.stride(0), _ptr(k_new), _ptr(v_new), k_new.stride(0), v_new.stride(0),
                                           _ptr(k_caches), _ptr(v_caches), k_caches.stride(0), n, n_heads, n_kv, head_dim, _ptr(pos), sc,
                                           float(theta), int(neox), _ptr(_f32(q_norm)) if q_norm is not None else None,
-                                          _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps), _ptr(o), k_caches.shape[1]))
+                                          _ptr(_f32(k_norm)) if k_norm is not None else None, float(eps), _ptr(o), k_caches.shape[1],
+                                          int(window), _sinks(sinks)))
     return o
 
 

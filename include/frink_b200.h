@@ -290,20 +290,25 @@ int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n
 /* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */
 int fk_kv_append(fk_ctx* ctx, void* stream, float* cache_dev, const float* src_dev, size_t row_elems, int n_rows, const int* pos_dev,
                  int cache_rows);
-/* `causal_gqa_prefill_f32` / `decode_attn_*` (kernels.rs:488, src/decode_attn.rs:125):
+/* window, sinks_dev (this call and the two below; gpt-oss, crates/frink-core/src/attention.rs:312-322,960-1000):
+ * window > 0: a query sees only the `window` most recent keys including its own (0 = all); sinks_dev
+ * [n_heads] (NULL = none): one logit per query head that joins the softmax's denominator, unscaled, and
+ * contributes nothing to the output.
+ * `causal_gqa_prefill_f32` / `decode_attn_*` (kernels.rs:488, src/decode_attn.rs:125):
  * query row r at position *pos + r attends keys 0..=*pos + r of K/V [T][n_kv][head_dim].
  * q_ld = floats between query rows (0 = n_heads * head_dim).  With fewer than 16 query rows
  * the keys are split over many blocks that meet in a workspace of the context: one such
  * call in flight per context. */
 int fk_attention(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_dev, const float* v_dev, int n_q, int n_heads,
-                 int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows);
+                 int n_kv, int head_dim, const int* pos_dev, float scale, float* out_dev, int cache_rows, int window,
+                 const float* sinks_dev);
 /* One decode row: fk_rope_kv and fk_attention in one launch.  q [n_heads*head_dim], k_new and
  * v_new [n_kv*head_dim] are the projection's outputs for the token at *pos (unrotated); the
  * caches hold positions 0 .. *pos - 1 and receive the rotated k and v at *pos.  q_norm_dev /
  * k_norm_dev as in fk_rope_kv.  One call in flight per context. */
 int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const float* k_new_dev, const float* v_new_dev, float* k_cache_dev,
                          float* v_cache_dev, int n_heads, int n_kv, int head_dim, const int* pos_dev, float scale, float theta, int neox,
-                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows);
+                         const float* q_norm_dev, const float* k_norm_dev, float norm_eps, float* out_dev, int cache_rows, int window, const float* sinks_dev);
 /* The same step for n_seqs independent sequences in one launch (batched decode): row r of q
  * (rows q_ld floats apart), k_new and v_new (k_ld / v_ld apart) is sequence r's token at position
  * pos_dev[r]; sequence r's caches begin r * seq_stride floats into k_cache_dev / v_cache_dev and
@@ -312,7 +317,7 @@ int fk_attention_rope_kv(fk_ctx* ctx, void* stream, const float* q_dev, const fl
 int fk_attention_rope_kv_seqs(fk_ctx* ctx, void* stream, const float* q_dev, int q_ld, const float* k_new_dev, const float* v_new_dev, int k_ld,
                               int v_ld, float* k_cache_dev, float* v_cache_dev, size_t seq_stride, int n_seqs, int n_heads, int n_kv, int head_dim,
                               const int* pos_dev, float scale, float theta, int neox, const float* q_norm_dev, const float* k_norm_dev,
-                              float norm_eps, float* out_dev, int cache_rows);
+                              float norm_eps, float* out_dev, int cache_rows, int window, const float* sinks_dev);
 /* Greedy sampling: index of the largest of each row, ties to the lower index; at most
  * 64 rows per call, and one call in flight per context (it uses a workspace of the context). */
 int fk_argmax(fk_ctx* ctx, void* stream, const float* x_dev, int n_rows, int n, int* out_dev);

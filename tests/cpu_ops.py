@@ -142,7 +142,7 @@ def kv_append(cache, src, pos):
     cache[p:p + src.shape[0]] = src
 
 
-def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None):
+def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out=None, window=0, sinks=None):
     p0, n, grp = int(pos[0]), q.shape[0], n_heads // n_kv
     qn, K, V = q.numpy().astype(np.float64), k_cache.numpy().astype(np.float64), v_cache.numpy().astype(np.float64)
     o = np.zeros((n, n_heads * head_dim), np.float32)
@@ -150,9 +150,12 @@ def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out
         T = p0 + r + 1
         for h in range(n_heads):
             kv = h // grp
-            s = K[:T, kv * head_dim:(kv + 1) * head_dim] @ qn[r, h * head_dim:(h + 1) * head_dim] * head_dim ** -0.5
-            p = np.exp(s - s.max())
-            o[r, h * head_dim:(h + 1) * head_dim] = p @ V[:T, kv * head_dim:(kv + 1) * head_dim] / p.sum()
+            lo = max(0, T - window) if window else 0
+            s = K[lo:T, kv * head_dim:(kv + 1) * head_dim] @ qn[r, h * head_dim:(h + 1) * head_dim] * head_dim ** -0.5
+            mx = max(s.max(), float(sinks[h])) if sinks is not None else s.max()
+            p = np.exp(s - mx)
+            den = p.sum() + (np.exp(float(sinks[h]) - mx) if sinks is not None else 0.0)
+            o[r, h * head_dim:(h + 1) * head_dim] = p @ V[lo:T, kv * head_dim:(kv + 1) * head_dim] / den
     return torch.from_numpy(o)
 
 

@@ -503,3 +503,86 @@ def test_prefill_on_q8k_activations_stays_close_to_the_q8_1_pipeline():
     print(f"greedy continuation: {same} of 16 tokens equal")
     from frink_b200 import device
     assert device.device_error() == 0
+
+
+@pytest.mark.parametrize("n_q", [1, 5, 40])
+@pytest.mark.parametrize("window,with_sinks", [(0, True), (48, False), (48, True), (7, True)])
+def test_sliding_window_and_sinks(n_q, window, with_sinks):
+    """gpt-oss attention (crates/frink-core/src/attention.rs:312-322, 960-1000): only the `window` most recent keys
+    are seen, and a per-head sink logit joins the softmax's denominator -- the split-key decode kernel (1 and 5 rows)
+    and the prefill kernel (40 rows) against a float64 restatement."""
+    from frink_b200 import device
+    from tests import cpu_ops
+    n_heads, n_kv, hd, p0 = 8, 2, 64, 100
+    rng = np.random.default_rng(31 + n_q + window)
+    kc = torch.from_numpy(rng.standard_normal((256, n_kv * hd)).astype(np.float32))
+    vc = torch.from_numpy(rng.standard_normal((256, n_kv * hd)).astype(np.float32))
+    q = torch.from_numpy(rng.standard_normal((n_q, n_heads * hd)).astype(np.float32))
+    sinks = torch.from_numpy((rng.standard_normal(n_heads) * 2).astype(np.float32)) if with_sinks else None
+    pos = torch.tensor([p0], dtype=torch.int32)
+    want = cpu_ops.attention(q, kc, vc, n_heads, n_kv, hd, pos, window=window, sinks=sinks).numpy()
+    got = device.attention(q.cuda(), kc.cuda(), vc.cuda(), n_heads, n_kv, hd, pos.cuda(), window=window,
+                           sinks=None if sinks is None else sinks.cuda()).cpu().numpy()
+    assert rel_l2(got, want) <= 2e-6
+    if with_sinks and window == 0:
+        plain = device.attention(q.cuda(), kc.cuda(), vc.cuda(), n_heads, n_kv, hd, pos.cuda()).cpu().numpy()
+        assert rel_l2(got, plain) > 1e-3           # the sink takes weight away from the real keys
+    assert device.device_error() == 0
+
+
+def test_fused_decode_attention_with_window_and_sinks_for_one_and_many_sequences():
+    from frink_b200 import device
+    n_heads, n_kv, hd, window = 8, 2, 64, 20
+    rng = np.random.default_rng(77)
+    sinks = torch.from_numpy(rng.standard_normal(n_heads).astype(np.float32)).cuda()
+    kcs = torch.from_numpy(rng.standard_normal((3, 128, n_kv * hd)).astype(np.float32)).cuda()
+    vcs = torch.from_numpy(rng.standard_normal((3, 128, n_kv * hd)).astype(np.float32)).cuda()
+    pos = torch.tensor([90, 5, 33], dtype=torch.int32, device="cuda")
+    q = torch.from_numpy(rng.standard_normal((3, n_heads * hd)).astype(np.float32)).cuda()
+    k = torch.from_numpy(rng.standard_normal((3, n_kv * hd)).astype(np.float32)).cuda()
+    v = torch.from_numpy(rng.standard_normal((3, n_kv * hd)).astype(np.float32)).cuda()
+    # reference: per sequence, the separate kernels (rotation + append, then attention with the same window and sinks)
+    want = []
+    for s_ in range(3):
+        kc, vc = kcs[s_].clone(), vcs[s_].clone()
+        q1, k1 = q[s_:s_ + 1].clone(), k[s_:s_ + 1].clone()
+        device.rope_kv(q1, k1, v[s_:s_ + 1], n_heads, n_kv, hd, pos[s_:s_ + 1], 10000.0, False, kc, vc)
+        want.append(device.attention(q1, kc, vc, n_heads, n_kv, hd, pos[s_:s_ + 1], window=window, sinks=sinks))
+    want = torch.cat(want)
+    one = device.attention_rope_kv(q[:1].clone(), k[:1].clone(), v[:1], kcs[0].clone(), vcs[0].clone(), n_heads, n_kv, hd, pos[:1], 10000.0,
+                                   window=window, sinks=sinks)
+    assert rel_l2(one.cpu().numpy(), want[:1].cpu().numpy()) <= 2e-6
+    many = device.attention_rope_kv_seqs(q.clone(), k.clone(), v, kcs.clone(), vcs.clone(), n_heads, n_kv, hd, pos, 10000.0, window=window, sinks=sinks)
+    assert rel_l2(many.cpu().numpy(), want.cpu().numpy()) <= 2e-6
+    assert device.device_error() == 0
+
+
+def test_decoder_with_alternating_windowed_layers_and_sinks_matches_the_cpu_decoder():
+    """gpt-oss's attention pattern on a small dense model: layer 0 windowed (8 keys), layer 1 full, a sink logit per
+    head in both -- prompt through the prefill kernel, then single rows and a few rows through the split-key kernel
+    (fused with rotation and cache append for one row), against the same decoder on the oracle-backed CPU ops."""
+    import dataclasses
+    from frink_b200.decoder import Decoder
+    from tests import cpu_ops
+    cfg, layers, tok, out_norm, head = small_llama(uniform=True)
+    cfg = dataclasses.replace(cfg, sliding_window=8, swa_period=2)
+    rng = np.random.default_rng(41)
+    layers = [dataclasses.replace(L, sinks=rng.standard_normal(cfg.n_heads).astype(np.float32)) for L in layers]
+    assert [cfg.window_of(i) for i in range(2)] == [8, 0]
+    dev = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=64)
+    cpu = Decoder(cfg, layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=64, ops=cpu_ops, device="cpu")
+    prompt = rng.integers(0, cfg.vocab, 20).astype(np.int32)
+    for ids in (prompt, np.array([7], np.int32), np.array([11], np.int32), np.array([5, 9, 2], np.int32), np.array([3], np.int32)):
+        got = dev.forward(torch.from_numpy(ids).cuda()).cpu().numpy()
+        want = cpu.forward(torch.from_numpy(ids)).numpy()
+        # two f32 pipelines: mostly equal to 1e-5, but one activation on the other side of a q8_1 rounding boundary moves
+        # the logits by up to 1e-2 (with or without window and sinks); the kernels themselves are held to 2e-6 above
+        assert rel_l2(got, want) <= 2e-2, len(ids)
+    # and the window matters: the same model without it answers differently
+    plain = Decoder(dataclasses.replace(cfg, sliding_window=0), layers, tok, fo.Q6_K, out_norm, output=head, output_kind=fo.Q6_K, max_seq=64)
+    a = plain.forward(torch.from_numpy(prompt).cuda()).cpu().numpy()
+    dev.reset()
+    b = dev.forward(torch.from_numpy(prompt).cuda()).cpu().numpy()
+    assert rel_l2(b, a) > 5e-2
+    from frink_b200 import device
+    assert device.device_error() == 0
