@@ -421,6 +421,15 @@ extern "C" {
         cache_rows: c_int,
     ) -> c_int;
     pub fn fk_reserve_scratch(ctx: *mut FkCtx, bytes: usize) -> c_int;
+    pub fn fk_add_bias(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        y_dev: *mut f32,
+        bias_dev: *const f32,
+        ids_dev: *const c_int,
+        n_rows: c_int,
+        cols: c_int,
+    ) -> c_int;
     pub fn fk_add(ctx: *mut FkCtx, stream: *mut c_void, a_dev: *mut f32, b_dev: *const f32, n: usize) -> c_int;
     pub fn fk_kv_append(
         ctx: *mut FkCtx,

@@ -63,6 +63,7 @@ SYMBOLS = {
     "fk_attention_rope_kv_seqs": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _P, _P, _SZ, _I, _I, _I, _I, _P, C.c_float, C.c_float, _I, _P, _P, C.c_float, _P, _I, _I, _P]),
     "fk_attention": (_I, [_P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P, C.c_float, _P, _I, _I, _P]),
     "fk_reserve_scratch": (_I, [_P, _SZ]),
+    "fk_add_bias": (_I, [_P, _P, _P, _P, _P, _I, _I]),
     "fk_argmax": (_I, [_P, _P, _P, _I, _I, _P]),
     "fk_add_int": (_I, [_P, _P, _P, _I]),
     "fk_comm_create": (_I, [_P, _SZ, _I, _I, _P, C.POINTER(_P)]),

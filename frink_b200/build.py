@@ -6,7 +6,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libfrink_b200.so")
-SOURCES = ["fk_api.cu", "fk_gemv.cu", "fk_gemv_q5k.cu", "fk_gemm.cu", "fk_gemm8k.cu", "fk_moe.cu", "fk_model.cu", "fk_comm.cu"]
+SOURCES = ["fk_api.cu", "fk_gemv.cu", "fk_gemv_q5k.cu", "fk_gemv_bf16.cu", "fk_gemm.cu", "fk_gemm8k.cu", "fk_moe.cu", "fk_model.cu", "fk_comm.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",

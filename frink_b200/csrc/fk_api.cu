@@ -188,7 +188,7 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
     size_t stride[4] = {0, 0, 0, 0};
     const size_t c = (size_t)cols;
     switch (kind) {
-        case FK_Q4_K: case FK_Q5_K: stride[0] = w->gguf_row_bytes; break;
+        case FK_Q4_K: case FK_Q5_K: case FK_BF16: stride[0] = w->gguf_row_bytes; break;
         case FK_Q8_0: stride[0] = c; stride[1] = pad16(c / 16); break;
         case FK_Q6_K: stride[0] = c / 2; stride[1] = c / 4; stride[2] = c / 16; stride[3] = pad16(c / 256 * 2); break;
         case FK_MXFP4: stride[0] = c / 2; stride[1] = pad16(c / 32); break;
@@ -214,7 +214,7 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
         const uint8_t* src = raw_dev + (size_t)m * mat_raw;
         uint8_t* dst = w->dev + (size_t)m * w->mat_stride;
         switch (kind) {
-            case FK_Q4_K: case FK_Q5_K:
+            case FK_Q4_K: case FK_Q5_K: case FK_BF16:
                 e = cudaMemcpyAsync(dst, src, mat_raw, cudaMemcpyDeviceToDevice, st);
                 break;
             case FK_Q8_0:
@@ -245,7 +245,7 @@ int make_weight(fk_ctx* ctx, const uint8_t* raw_dev, size_t len, int kind, int n
 
 int check_shape(const char* who, size_t len, int kind, int n_mats, int rows, int cols) {
     const int bb = fk_kind_block_bytes(kind), be = fk_kind_block_elems(kind);
-    if (bb < 0) return fk_fail(FK_UNSUPPORTED, "%s: kind %d is not one of Q8_0, Q4_K, Q5_K, Q6_K, MXFP4", who, kind);
+    if (bb < 0) return fk_fail(FK_UNSUPPORTED, "%s: kind %d is not one of Q8_0, Q4_K, Q5_K, Q6_K, MXFP4, BF16", who, kind);
     if (n_mats < 1 || rows < 1 || cols < 1) return fk_fail(FK_INVALID, "%s: %d matrices of %d x %d", who, n_mats, rows, cols);
     if (cols % be) return fk_fail(FK_INVALID, "%s: %d columns is not a whole number of %d-element blocks", who, cols, be);
     if (cols % 32) return fk_fail(FK_INVALID, "%s: %d columns is not a whole number of q8_1 runs", who, cols);

@@ -107,11 +107,11 @@ struct FkDeviceGuard {
 };
 
 static inline int fk_kind_block_bytes(int kind) {
-    switch (kind) { case FK_Q8_0: return 34; case FK_Q4_K: return 144; case FK_Q5_K: return 176; case FK_Q6_K: return 210; case FK_MXFP4: return 17; }
+    switch (kind) { case FK_Q8_0: return 34; case FK_Q4_K: return 144; case FK_Q5_K: return 176; case FK_Q6_K: return 210; case FK_MXFP4: return 17; case FK_BF16: return 2; }
     return -1;
 }
 static inline int fk_kind_block_elems(int kind) {
-    switch (kind) { case FK_Q8_0: return 32; case FK_Q4_K: return 256; case FK_Q5_K: return 256; case FK_Q6_K: return 256; case FK_MXFP4: return 32; }
+    switch (kind) { case FK_Q8_0: return 32; case FK_Q4_K: return 256; case FK_Q5_K: return 256; case FK_Q6_K: return 256; case FK_MXFP4: return 32; case FK_BF16: return 1; }
     return -1;
 }
 // activations per exact integer run (the weight-scale granularity)
@@ -133,6 +133,7 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
                    const FkGemvFused* fused);
 constexpr size_t FK_SCRATCH_MIN = (size_t)64 << 20;
 int fk_ensure_scratch(fk_ctx* ctx, cudaStream_t st, size_t bytes);
+int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev);
 int fk_gemv_q5k_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev, int32_t* isums_dev);
 // `map` points at a CUtensorMap (128 bytes, 64-byte aligned): [outer][inner] 32-bit words, no swizzle
 int fk_make_map_2d(void* map, int dtype, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, int swizzle);

@@ -680,8 +680,8 @@ int launch_by_kind(fk_ctx* ctx, cudaStream_t st, const GemmArgs& a, const CUtens
 int gemm_common(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const int* group_off, const int* gather, const float* x,
                 int n_tokens, float* out, int32_t* isums = nullptr) {
     const bool grouped = group_off != nullptr;
-    if (w->kind == FK_Q5_K)   // before anything is enqueued: the caller takes batches of 8 through the matvec
-        return fk_fail(FK_UNSUPPORTED, "gemm: Q5_K has the plain matvec only");
+    if (w->kind == FK_Q5_K || w->kind == FK_BF16)   // before anything is enqueued: the caller takes batches of 8 through the matvec
+        return fk_fail(FK_UNSUPPORTED, "gemm: kind %d has the plain matvec only", w->kind);
     const int bn = grouped ? 64 : 128;
     const int n_tiles_max = grouped ? (n_tokens + bn - 1) / bn + w->n_mats : (n_tokens + bn - 1) / bn;
     const int n_pad = n_tiles_max * bn;

@@ -1742,6 +1742,9 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
     const bool dump = isums_dev != nullptr;
     switch (w->kind) {
         case FK_Q4_K: return launch_kind<FK_Q4_K>(ctx, st, a, w, slots, dump);
+        case FK_BF16:
+            if (ids_dev || n_active_dev || fused || isums_dev) return fk_fail(FK_UNSUPPORTED, "gemv: BF16 has the plain matvec only (nothing is quantized: no integer hook)");
+            return fk_gemv_bf16_launch(ctx, st, w, mat, x_dev, batch, y_dev);
         case FK_Q5_K:
             // the plain matvec only: the fused, indexed and row-split forms have no Q5_K kernel (the caller composes them
             // from the separate kernels, as it would for any kind this library does not fuse)

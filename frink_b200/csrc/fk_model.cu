@@ -45,6 +45,8 @@ __global__ void get_rows_kernel(const uint8_t* __restrict__ wb, size_t o0, size_
             const uint8_t q = blk[16 + (j >> 1) * 32 + l];
             const int nib = (j & 1) ? (q >> 4) : (q & 0x0F);
             v = (d * (float)scv) * (float)nib - dmin * (float)mv;
+        } else if (kind == FK_BF16) {
+            v = __uint_as_float((uint32_t)*(const uint16_t*)(wb + o0 + (size_t)row * s0 + (size_t)e * 2) << 16);
         } else if (kind == FK_Q5_K) {
             const uint8_t* blk = wb + o0 + (size_t)row * s0 + (size_t)(e >> 8) * 176;
             const int j = (e & 255) >> 5, l = e & 31;

@@ -198,6 +198,14 @@ def moe_local_slots(ids, w, e0, n_local):
     return oi, ow, on
 
 
+def add_bias_(y, bias, ids=None):
+    """y [n, cols] += bias [cols], or += bias[ids[r]] row by row (the expert of every slot): gpt-oss's projection biases."""
+    y2 = y if y.dim() == 2 else y[None]
+    assert y2.is_contiguous() and y2.dtype == torch.float32
+    check(lib().fk_add_bias(context(y.device), _stream(), _ptr(y2), _ptr(_f32(bias)), _ptr(_i32(ids)) if ids is not None else None, y2.shape[0], y2.shape[1]))
+    return y
+
+
 def moe_layer(layer, x, out=None, accumulate=False):
     """The routed layer in one call (`fk_moe_layer`): `layer` carries router, router_bias, gate / up / down (stacked
     `Weights`), k, mode, act; x [batch, hidden] or [hidden].  The workspace is kept on the layer object, per batch size."""
@@ -254,8 +262,8 @@ def gemm(w, x, mat=0, out=None):
     x = _f32(x)
     assert x.dim() == 2 and x.shape[1] == w.cols
     y = out if out is not None else torch.empty((x.shape[0], w.rows), dtype=torch.float32, device=x.device)
-    if w.kind == 13:
-        # Q5_K has no GEMM kernel (fk_gemm answers UNSUPPORTED): batches of 8 through the matvec, the same integers
+    if w.kind in (13, 30):
+        # Q5_K and BF16 have no GEMM kernel (fk_gemm answers UNSUPPORTED): batches of 8 through the matvec, the same integers
         for i in range(0, x.shape[0], 8):
             gemv(w, x[i:i + 8], mat=mat, out=y[i:i + 8])
         return y

@@ -58,6 +58,7 @@ typedef enum fk_kind {
     FK_Q4_K = 12,  /* 144 B / 256 weights */
     FK_Q5_K = 13,  /* 176 B / 256 weights: the plain matvec (fk_gemv, fk_gemv_isums, fk_launch_matvec) and fk_get_rows only */
     FK_Q6_K = 14,  /* 210 B / 256 weights */
+    FK_BF16 = 30,  /* 2 B / weight, not quantized (gpt-oss attention projections): the plain matvec on f32 activations and fk_get_rows only */
     FK_MXFP4 = 39  /* 17 B / 32 weights  */
 } fk_kind;
 
@@ -285,6 +286,10 @@ int fk_rope_kv(fk_ctx* ctx, void* stream, float* q_dev, float* k_dev, const floa
                const float* q_norm_dev, const float* k_norm_dev, float norm_eps, int cache_rows);
 /* Grow the context's workspace to at least `bytes` (it never shrinks). */
 int fk_reserve_scratch(fk_ctx* ctx, size_t bytes);
+/* gpt-oss's projection biases (crates/frink-models/src/models/gpt_oss.rs:9-12,46; `run_expert_oai`,
+ * crates/frink-moe/src/lib.rs:1039-1060): y [n_rows][cols] += bias [cols]; with ids_dev [n_rows] (the expert of every
+ * slot of an indexed matvec) += row ids[r] of bias [n_experts][cols]. */
+int fk_add_bias(fk_ctx* ctx, void* stream, float* y_dev, const float* bias_dev, const int* ids_dev, int n_rows, int cols);
 /* `add_rows_f32` (kernels.rs:70): a += b. */
 int fk_add(fk_ctx* ctx, void* stream, float* a_dev, const float* b_dev, size_t n);
 /* `kv_append_f32` (kernels.rs:664): cache rows [*pos, *pos + n_rows) <- src. */

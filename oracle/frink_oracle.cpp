@@ -206,6 +206,9 @@ void decode_mxfp4(const uint8_t* b, float* y) {
     }
 }
 
+// BF16: the upper half of an f32 (crates/frink-quant/src/lib.rs:232-250); a "block" is one value.
+void decode_bf16(const uint8_t* b, float* y) { y[0] = f32_from_bits((uint32_t)(b[0] | (b[1] << 8)) << 16); }
+
 struct KindInfo { int block_bytes, block_elems; void (*decode)(const uint8_t*, float*); };
 // ggml type tags: Q8_0 = 8, Q4_K = 12, Q5_K = 13, Q6_K = 14, MXFP4 = 39.
 bool kind_info(int kind, KindInfo* k) {
@@ -215,6 +218,7 @@ bool kind_info(int kind, KindInfo* k) {
         case 14: *k = {Q6K_BYTES, 256, decode_q6_k}; return true;
         case 8: *k = {Q80_BYTES, 32, decode_q8_0}; return true;
         case 39: *k = {MX4_BYTES, 32, decode_mxfp4}; return true;
+        case 30: *k = {2, 1, decode_bf16}; return true;
     }
     return false;
 }
@@ -1272,6 +1276,14 @@ FKO_API long fko_encode(int kind, const float* src, long n, uint8_t* out) {
             case 14: encode_block_q6_k(s, o); break;
             case 8: encode_block_q8_0(s, o); break;
             case 39: encode_block_mxfp4(s, o); break;
+            case 30: {   // round to nearest even on the upper half (test data; the reference only reads this format)
+                uint32_t u;
+                std::memcpy(&u, s, 4);
+                u += 0x7FFFu + ((u >> 16) & 1u);
+                o[0] = (uint8_t)(u >> 16);
+                o[1] = (uint8_t)(u >> 24);
+                break;
+            }
         }
     }
     return nb * k.block_bytes;

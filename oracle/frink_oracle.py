@@ -15,8 +15,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "libfrink_oracle.so")
 
 # ggml type tags, shared with include/frink_b200.h
-Q8_0, Q4_K, Q5_K, Q6_K, MXFP4 = 8, 12, 13, 14, 39
-KINDS = {"q8_0": Q8_0, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4}
+Q8_0, Q4_K, Q5_K, Q6_K, MXFP4, BF16 = 8, 12, 13, 14, 39, 30
+KINDS = {"q8_0": Q8_0, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K, "mxfp4": MXFP4, "bf16": BF16}
 
 
 def build(force=False):
