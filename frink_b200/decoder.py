@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from . import parallel
-from .prefill import RoutedLayer, run_device_routed, run_device_routed_batch, run_device_routed_rows
+from .prefill import RoutedLayer, run_device_routed, run_device_routed_batch, run_device_routed_oai, run_device_routed_rows
 
 
 @dataclass
@@ -36,6 +36,7 @@ class DecoderConfig:
     n_experts: int = 0          # > 0: routed FFN
     top_k: int = 0
     route_mode: int = 1
+    oai: bool = False           # gpt-oss layers: biased projections, biased experts with the clamped SwiGLU, router bias
     sliding_window: int = 0     # gpt-oss: > 0 = windowed layers see only this many most recent keys
     swa_period: int = 0         # which layers are windowed: all (0), or layer i with i % period < period - 1 (gpt-oss: 2)
 
@@ -61,6 +62,14 @@ class LayerWeights:
     q_norm: Any = None
     k_norm: Any = None
     sinks: Any = None           # gpt-oss attention sinks, f32 [n_heads]
+    bq: Any = None              # gpt-oss biases: q / k / v / attention output rows, the router's, and [n_experts, rows] per expert projection
+    bk: Any = None
+    bv: Any = None
+    bo: Any = None
+    router_bias: Any = None
+    gate_b: Any = None
+    up_b: Any = None
+    down_b: Any = None
     kinds: dict = field(default_factory=dict)   # name -> fk_kind
 
 
@@ -135,6 +144,8 @@ class Decoder:
         self.t_dense = T
         r_dense = self.rank if dense_parallel else 0     # replicated: every rank holds shard 0 of 1
         E = self.world          # ranks the routed experts are spread over
+        if cfg.oai and self.world > 1:
+            raise ValueError("the gpt-oss layer form runs on one GPU here (its biases are not sharded)")
         if cfg.n_heads % T or cfg.n_kv % T:
             raise ValueError(f"{cfg.n_heads}/{cfg.n_kv} heads do not split over {T} ranks")
         self.h_loc, self.kv_loc = cfg.n_heads // T, cfg.n_kv // T
@@ -168,7 +179,16 @@ class Decoder:
             # attention options of the layer: the window (0 = full) and this rank's heads' sinks
             d["window"] = cfg.window_of(len(self.layers))
             d["sinks"] = None if L.sinks is None else f32(np.asarray(L.sinks, np.float32)[r_dense * self.h_loc:(r_dense + 1) * self.h_loc])
-            if cfg.n_experts:
+            if cfg.oai:
+                for name in ("bq", "bk", "bv", "bo"):
+                    if getattr(L, name) is not None:
+                        d[name] = f32(getattr(L, name))
+            if cfg.n_experts and cfg.oai:
+                mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
+                d["moe"] = RoutedLayer(f32(L.router), mk(L.gate, cfg.ffn, H), mk(L.up, cfg.ffn, H), mk(L.down, H, cfg.ffn), k=cfg.top_k,
+                                       mode=cfg.route_mode, act=1, router_bias=None if L.router_bias is None else f32(L.router_bias))
+                d["moe_b"] = (f32(L.gate_b), f32(L.up_b), f32(L.down_b))
+            elif cfg.n_experts:
                 router = f32(L.router)
                 if E == 1:
                     mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
@@ -212,7 +232,7 @@ class Decoder:
         hd = cfg.head_dim
         n = ids.numel()
         self._claim(n)
-        if n <= 8 and hasattr(ops, "gemv_fused") and (self.t_dense == 1 or self.comm is not None):
+        if n <= 8 and hasattr(ops, "gemv_fused") and (self.t_dense == 1 or self.comm is not None) and not cfg.oai:
             return self._forward_fused(ids)
         x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
         pending = None                                      # a block output not yet added to x
@@ -224,6 +244,8 @@ class Decoder:
                 (q, k), v = L["qk"](h), L["wv"](h)
             else:
                 q, k, v = L["wq"](h), L["wk"](h), L["wv"](h)
+            if "bq" in L:
+                q, k, v = (ops.add_bias_(t_.contiguous(), L[b_]) for t_, b_ in ((q, "bq"), (k, "bk"), (v, "bv")))
             if cfg.qk_norm:
                 q = ops.rmsnorm(q.view(-1, hd), L["q_norm"], cfg.eps).view(n, -1)
                 k = ops.rmsnorm(k.view(-1, hd), L["k_norm"], cfg.eps).view(n, -1)
@@ -236,8 +258,12 @@ class Decoder:
                 ops.kv_append(L["v"], v, self.pos)
             a = ops.attention(q, L["k"], L["v"], self.h_loc, self.kv_loc, hd, self.pos, window=L["window"], sinks=L["sinks"])
             o = L["wo"](a)
+            if "bo" in L:
+                ops.add_bias_(o, L["bo"])
             h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps, residual=o)
-            if "moe" in L:
+            if "moe_b" in L:
+                pending = run_device_routed_oai(L["moe"], L["moe_b"], h2, ops)
+            elif "moe" in L:
                 pending = run_device_routed(L["moe"], h2, ops) if n <= 8 else run_device_routed_batch(L["moe"], h2, ops)
             elif "ep" in L:
                 pending = torch.stack([L["ep"].decode(h2[t]) for t in range(n)]) if n <= 8 else self._ep_prefill(L["ep"], h2)
@@ -282,6 +308,8 @@ class Decoder:
     def forward_seqs(self, toks):
         """toks [n_seqs] (device int32), sequence r's newest token -> logits [n_seqs, vocab]; every position advances."""
         n = toks.numel()
+        if self.cfg.oai:
+            raise ValueError("batched sequences are not built for the gpt-oss layer form")
         if n != len(self._seq_pos_host):
             raise ValueError(f"{n} tokens for {len(self._seq_pos_host)} sequences")
         if max(self._seq_pos_host) + 1 > self.max_seq:

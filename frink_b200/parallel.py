@@ -25,7 +25,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-BLOCK = {8: (34, 32), 12: (144, 256), 14: (210, 256), 39: (17, 32)}   # kind -> (bytes, elems)
+BLOCK = {8: (34, 32), 12: (144, 256), 13: (176, 256), 14: (210, 256), 39: (17, 32), 30: (2, 1)}   # kind -> (bytes, elems)
 
 
 def shard_rows(raw, kind, rows, cols, rank, world):

@@ -18,7 +18,8 @@ class Weights:
 
 def _mm(w, m, x):
     x = np.ascontiguousarray(x, np.float32).reshape(-1, w.cols)
-    return fo.matmul_f64(w.kind, w.mat(m), w.rows, w.cols, fo.q8_1_round(x), threads=1).astype(np.float32)
+    xq = x if w.kind == fo.BF16 else fo.q8_1_round(x)          # BF16 weights meet f32 activations; the block formats q8_1's
+    return fo.matmul_f64(w.kind, w.mat(m), w.rows, w.cols, xq, threads=1).astype(np.float32)
 
 
 def gemv(w, x, mat=0, out=None):
@@ -162,6 +163,12 @@ def attention(q, k_cache, v_cache, n_heads, n_kv, head_dim, pos, scale=None, out
 def argmax(x, out=None):
     x2 = x if x.dim() == 2 else x[None]
     return torch.argmax(x2, dim=1).to(torch.int32)
+
+
+def add_bias_(y, bias, ids=None):
+    y2 = y if y.dim() == 2 else y[None]
+    y2.add_(bias if ids is None else bias[ids.long()])
+    return y
 
 
 def add_(a, b):
