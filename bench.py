@@ -230,7 +230,7 @@ def main():
     ap.add_argument("--no-models", action="store_true", help="skip the whole-model pp512 / tg128 block")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-gemm", action="store_true", help="skip the prefill GEMM sweep (M = 512 against the three projection shapes)")
-    ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "tiny"],
+    ap.add_argument("--model", default=None, choices=["llama3b", "qwen3moe", "gptoss", "tiny"],
                     help="whole-model pp512 / tg128 tokens per second (the Llama-3.2-3B and Qwen3-30B-A3B shapes) instead of the GEMV line")
     ap.add_argument("--layers", type=int, default=0, help="with --model: override the layer count")
     ap.add_argument("--profile-region", choices=["pp", "tg", "tg_batch8"], default=None,
@@ -339,7 +339,7 @@ def main():
         from frink_b200.comm import Comm
         comm = Comm(arena_bytes=512 << 20)
     if not args.no_models:
-        for name in ("llama3b", "qwen3moe"):
+        for name in ("llama3b", "qwen3moe", "gptoss"):
             r_ = run_model(name, rank, world, comm=comm)
             if rank == 0:
                 models[name] = r_
@@ -452,6 +452,11 @@ def synth_model(name, n_layers=0):
     elif name == "qwen3moe":
         cfg = DecoderConfig(n_layers=48, hidden=2048, n_heads=32, n_kv=4, head_dim=128, ffn=768, vocab=151936, rope_theta=1000000.0,
                             eps=1e-6, neox=True, qk_norm=True, n_experts=128, top_k=8, route_mode=1)
+    elif name == "gptoss":
+        # gpt-oss-20b: BF16 attention projections with biases and sinks, every other layer windowed (128), 32 MXFP4 experts
+        # (top 4) with biases and the clamped SwiGLU, BF16 embedding and head
+        cfg = DecoderConfig(n_layers=24, hidden=2880, n_heads=64, n_kv=8, head_dim=64, ffn=2880, vocab=201088, rope_theta=150000.0,
+                            eps=1e-5, neox=True, n_experts=32, top_k=4, route_mode=1, oai=True, sliding_window=128, swa_period=2)
     else:
         cfg = DecoderConfig(n_layers=2, hidden=512, n_heads=4, n_kv=2, head_dim=128, ffn=1024, vocab=4096)
     if n_layers:
@@ -487,6 +492,24 @@ def synth_model(name, n_layers=0):
         for i in range(cfg.n_layers):
             var = i % 2
             sh = lambda tag, kind, r, c, j: shuffled(enc(tag, kind, r, c, var), kind, r, c, 7919 * i + j)
+            if cfg.oai:
+                BF, MX, E = fo.BF16, fo.MXFP4, cfg.n_experts
+                kd = {"wq": BF, "wk": BF, "wv": BF, "wo": BF, "experts": MX}
+                vec = lambda n_, s_: (rng.standard_normal(n_) * s_).astype(np.float32)
+
+                def exo(tag, r, c, j):
+                    base = sh(tag, MX, r, c, j).reshape(r, fo.row_bytes(MX, c))
+                    idx = (np.arange(r)[None, :] + (np.arange(E) * 37 % r)[:, None]) % r
+                    return base[idx].ravel()
+                yield LayerWeights(
+                    attn_norm=norm(H), wq=sh("wq", BF, cfg.n_heads * hd, H, 0), wk=sh("wk", BF, cfg.n_kv * hd, H, 1),
+                    wv=sh("wv", BF, cfg.n_kv * hd, H, 2), wo=sh("wo", BF, H, cfg.n_heads * hd, 3), ffn_norm=norm(H),
+                    gate=exo("eg", cfg.ffn, H, 4), up=exo("eu", cfg.ffn, H, 5), down=exo("ed", H, cfg.ffn, 6),
+                    router=(rng.standard_normal((E, H), dtype=np.float32) * np.float32(0.02)), sinks=vec(cfg.n_heads, 1.0),
+                    bq=vec(cfg.n_heads * hd, 0.02), bk=vec(cfg.n_kv * hd, 0.02), bv=vec(cfg.n_kv * hd, 0.02), bo=vec(H, 0.02),
+                    router_bias=vec(E, 0.1), gate_b=vec(E * cfg.ffn, 0.02).reshape(E, cfg.ffn), up_b=vec(E * cfg.ffn, 0.02).reshape(E, cfg.ffn),
+                    down_b=vec(E * H, 0.02).reshape(E, H), kinds=kd)
+                continue
             if cfg.n_experts:
                 kd = {"wq": Q8, "wk": Q8, "wv": Q8, "wo": Q8, "experts": Q4}
                 E = cfg.n_experts
@@ -512,7 +535,17 @@ def synth_model(name, n_layers=0):
                     gate=sh("gate", kd["gate"], cfg.ffn, H, 4), up=sh("up", kd["up"], cfg.ffn, H, 5),
                     down=sh("down", kd["down"], H, cfg.ffn, 6), kinds=kd)
     layers = make_layers()
-    tok_kind = Q6
+    tok_kind = fo.BF16 if cfg.oai else Q6
+
+    def vocab_matrix_bf16(std):
+        base = rng.standard_normal((4096, H), dtype=np.float32) * np.float32(std)
+        copies = -(-cfg.vocab // 4096)
+        # every copy of the 4096 rows at a scale of its own, so that no two rows of the vocabulary are the same
+        parts = [fo.encode(tok_kind, base * np.float32(1.0 + 0.004 * c)) for c in range(copies)]
+        return np.concatenate(parts)[: cfg.vocab * fo.row_bytes(tok_kind, H)].copy()
+
+    if cfg.oai:
+        return cfg, layers, vocab_matrix_bf16(1.0), tok_kind, norm(H), vocab_matrix_bf16(0.02)
 
     def vocab_matrix(std):
         base = fo.encode(tok_kind, (rng.standard_normal((4096, H), dtype=np.float32) * np.float32(std)))
@@ -546,6 +579,8 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     import torch.distributed as dist
     from frink_b200 import device
     from frink_b200.decoder import Decoder
+    if name == "gptoss" and world > 1:
+        return {"model": name, "n_gpus": world, "unavailable": "the gpt-oss layer form runs on one GPU here (its biases are not sharded)"} if rank == 0 else None
     cfg, layers, tok, tok_kind, out_norm, head = synth_model(name, n_layers)
     # dense models: tensor parallel; routed models: attention replicated, experts spread over the ranks
     # (their few KV heads do not divide by 8)
@@ -609,7 +644,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     tg_ms, _ = timed(run_decode, "tg")
     # ---- a decode batch of eight independent sequences (their own KV caches and positions), one token each per step
     b8 = None
-    if use_graph and (world == 1 or comm is not None):
+    if use_graph and (world == 1 or comm is not None) and not cfg.oai:      # (batched sequences are not built for the gpt-oss layer form)
         del step, g, out
         dec._graph = dec._gout = None
         NB8 = 8
@@ -640,7 +675,8 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
         "model": name, "n_gpus": world, "layers": cfg.n_layers,
         "pp_tokens": S, "pp_ms": pp_ms, "pp_tok_s": S / (pp_ms * 1e-3), "tg_tokens": G, "tg_ms": tg_ms, "tg_tok_s": G / (tg_ms * 1e-3),
         "decode_graph": bool(world == 1 or tp_graph),
-        "prefill_activations": "Q4_K projections: Q8_K (frink's CPU rule, per 256); other kinds: q8_1 (per 32); decode: q8_1", "tg_batch8": b8, "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
+        "prefill_activations": ("BF16 projections: f32 (library f32 GEMM for prompt rows, this library's matvec for decode); MXFP4 experts: q8_1" if cfg.oai else
+                                "Q4_K projections: Q8_K (frink's CPU rule, per 256); other kinds: q8_1 (per 32); decode: q8_1"), "tg_batch8": b8, "parallelism": ("tp%d" % world) if not cfg.n_experts else ("dense replicated, ep%d" % world),
         "collective": None if world == 1 else (
             ("all-reduce(sum, f32 [rows, hidden]) after wo and down" if not cfg.n_experts else
              "all-reduce(sum, f32 [rows, hidden]) of the partial expert sums, one per layer") +

@@ -73,6 +73,17 @@ class LayerWeights:
     kinds: dict = field(default_factory=dict)   # name -> fk_kind
 
 
+def bf16_as_f32(ops, raw, kind, rows, cols):
+    """BF16 weights widened to an f32 matrix on the device, for a prompt's rows: this library has no BF16 GEMM, and a
+    plain f32 GEMM is the math library's (cuBLAS through torch; TF32 off, so the products are the matvec's).  None for
+    every other kind and off the GPU."""
+    if kind != 30 or getattr(ops, "__name__", "") != "frink_b200.device":
+        return None
+    import numpy as np
+    bits = torch.from_numpy(np.ascontiguousarray(raw, np.uint8).ravel().view(np.uint16).astype(np.int32)).cuda()
+    return (bits << 16).view(torch.float32).view(rows, cols)
+
+
 def prefill_gemm(ops, w, x, acts):
     """The GEMM of a prompt's rows.  acts = "q8_k": Q4_K weights take the GEMM on Q8_K activations (frink's CPU
     activation rule, about twice as fast here); every other kind, and acts = "q8_1", the q8_1 GEMM whose integers
@@ -88,9 +99,12 @@ class _Linear:
     def __init__(self, ops, raw, kind, rows, cols, acts="q8_1"):
         self.ops, self.acts = ops, acts
         self.w = ops.Weights(raw, kind, rows, cols)
+        self.w32 = bf16_as_f32(ops, raw, kind, rows, cols)
 
     def __call__(self, x):
-        return self.ops.gemv(self.w, x) if x.shape[0] <= 8 else prefill_gemm(self.ops, self.w, x, self.acts)
+        if x.shape[0] <= 8:
+            return self.ops.gemv(self.w, x)
+        return x @ self.w32.T if self.w32 is not None else prefill_gemm(self.ops, self.w, x, self.acts)
 
 
 class _Merged:
@@ -112,9 +126,13 @@ class _Merged:
         else:
             raw = np.concatenate(blobs)
         self.w = ops.Weights(raw, kind, sum(self.splits), cols)
+        self.w32 = bf16_as_f32(ops, raw, kind, sum(self.splits), cols)
 
     def __call__(self, x):
-        y = self.ops.gemv(self.w, x) if x.shape[0] <= 8 else prefill_gemm(self.ops, self.w, x, self.acts)
+        if x.shape[0] <= 8:
+            y = self.ops.gemv(self.w, x)
+        else:
+            y = x @ self.w32.T if self.w32 is not None else prefill_gemm(self.ops, self.w, x, self.acts)
         if self.interleave:
             return [y[:, 0::2], y[:, 1::2]]
         outs, o = [], 0
