@@ -644,7 +644,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     tg_ms, _ = timed(run_decode, "tg")
     # ---- a decode batch of eight independent sequences (their own KV caches and positions), one token each per step
     b8 = None
-    if use_graph and (world == 1 or comm is not None) and not cfg.oai:      # (batched sequences are not built for the gpt-oss layer form)
+    if use_graph and (world == 1 or comm is not None):
         del step, g, out
         dec._graph = dec._gout = None
         NB8 = 8

@@ -166,6 +166,33 @@ extern "C" {
         y_dev: *mut f32,
         n_active_dev: *const c_int,
     ) -> c_int;
+    pub fn fk_gemv_biased(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        w: FkWeight,
+        mat: c_int,
+        x_dev: *const f32,
+        x_ld: c_int,
+        batch: c_int,
+        y_dev: *mut f32,
+        norm_weight_dev: *const f32,
+        norm_eps: f32,
+        bias_dev: *const f32,
+        accumulate: c_int,
+    ) -> c_int;
+    pub fn fk_gemv_multi_biased(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        w: FkWeight,
+        ids_dev: *const c_int,
+        k: c_int,
+        x_dev: *const f32,
+        up_dev: *const f32,
+        x_stride: c_int,
+        glu_act: c_int,
+        bias_dev: *const f32,
+        y_dev: *mut f32,
+    ) -> c_int;
     pub fn fk_gemv_isums(
         ctx: *mut FkCtx,
         stream: *mut c_void,
@@ -357,6 +384,27 @@ extern "C" {
         gate: FkWeight,
         up: FkWeight,
         down: FkWeight,
+        k: c_int,
+        mode: c_int,
+        act: c_int,
+        x_dev: *const f32,
+        batch: c_int,
+        out_dev: *mut f32,
+        accumulate: c_int,
+        workspace_dev: *mut c_void,
+        workspace_bytes: usize,
+    ) -> c_int;
+    pub fn fk_moe_layer_biased(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        router_dev: *const f32,
+        router_bias_dev: *const f32,
+        gate: FkWeight,
+        up: FkWeight,
+        down: FkWeight,
+        gate_bias_dev: *const f32,
+        up_bias_dev: *const f32,
+        down_bias_dev: *const f32,
         k: c_int,
         mode: c_int,
         act: c_int,

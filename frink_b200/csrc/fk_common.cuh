@@ -127,13 +127,15 @@ struct FkGemvFused {
     int x_ld;
     int pair_glu;                   // rows are (gate, up) pairs: write act(gate) * up, rows / 2 outputs
     const struct FkArChannel* ar;   // sum the results over the ranks of this channel in the epilogue (null: no)
+    const float* bias = nullptr;    // [rows] added to the result; with ids: [n_mats][rows], slot j gets the row of matrix ids[j]
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
                    const FkGemvFused* fused);
 constexpr size_t FK_SCRATCH_MIN = (size_t)64 << 20;
 int fk_ensure_scratch(fk_ctx* ctx, cudaStream_t st, size_t bytes);
-int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev);
+int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                        const float* norm_w, float norm_eps, const float* bias, int accumulate);
 int fk_gemv_q5k_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev, int32_t* isums_dev);
 // `map` points at a CUtensorMap (128 bytes, 64-byte aligned): [outer][inner] 32-bit words, no swizzle
 int fk_make_map_2d(void* map, int dtype, void* base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer, int swizzle);

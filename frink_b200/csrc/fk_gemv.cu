@@ -68,6 +68,7 @@ struct GemvArgs {
     int pair_glu;          // rows are (gate, up) pairs: y[rows/2] = act(gate) * up (1 SiLU, 2 the gpt-oss form)
     int ar_on;             // the epilogue sums the results over the ranks of `ar` (element index: b * rows + row)
     FkArChannel ar;
+    const float* bias;     // added to the finished dot products (before the gated activation of pair_glu): [rows], or with ids [n_mats][rows]
     // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
     int q_lp;              // row pairs a warp tile spans (32, 16 or 8; the rest of the lanes span super-blocks)
     int q_sc_off, q_part_off, q_ring_off, q_bar_off;
@@ -716,6 +717,15 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
                     done[r][b] = v;
                 }
             const bool writer = (lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0);
+            if (a.bias && writer) {
+#pragma unroll
+                for (int r = 0; r < LR; r++) {
+                    const int row = row0 + hw * LR + r;
+                    const float bv = row < rows ? a.bias[(a.ids ? (size_t)mat * rows : 0) + row] : 0.0f;
+#pragma unroll
+                    for (int b = 0; b < NB; b++) done[r][b] += bv;
+                }
+            }
             if (a.pair_glu) {
                 // rows come as (gate, up) pairs (the merged projection was stacked row-interleaved):
                 // the lane holds both, so the gated activation is formed here and written once
@@ -1659,7 +1669,7 @@ int launch_mma(fk_ctx* ctx, cudaStream_t st, GemvArgs a, const fk_weight_s* w, b
 
 template <int KIND>
 int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight_s* w, int slots, bool dump) {
-    if (!dump && a.batch >= MMA_MIN_BATCH && slots == 1 && !a.ids) {
+    if (!dump && a.batch >= MMA_MIN_BATCH && slots == 1 && !a.ids && !a.bias) {
         bool fits = false;
         const int rc = launch_mma<KIND>(ctx, st, a, w, &fits);
         if (fits) return rc;
@@ -1668,7 +1678,7 @@ int launch_kind(fk_ctx* ctx, cudaStream_t st, const GemvArgs& a, const fk_weight
     // 4.3 us against 5.4 us a launch (8192 x 3072).  It waits for its whole share before the first dot product, which
     // costs it inside a decoder step, where the kernel before a matvec is short and hides nothing (688 against 798
     // tokens per second on the 3B Llama shape): the fused and indexed forms keep the general kernel and its rings.
-    const bool plain = !a.ids && !a.n_active && !a.norm_w && !a.glu_up && !a.pair_glu && !a.accumulate && !a.ar_on;
+    const bool plain = !a.ids && !a.n_active && !a.norm_w && !a.glu_up && !a.pair_glu && !a.accumulate && !a.ar_on && !a.bias;
     if (KIND == FK_Q4_K && a.batch <= 1 && (plain || dump)) {
         bool fits = false;
         const int rc = dump ? launch_q4k<1, true>(ctx, st, a, w, slots, &fits) : launch_q4k<1, false>(ctx, st, a, w, slots, &fits);
@@ -1718,6 +1728,7 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.accumulate = fused->accumulate;
         a.pair_glu = fused->pair_glu;
         if (fused->x_ld) a.x_ld = fused->x_ld;
+        a.bias = fused->bias;
         if (fused->ar) {
             a.ar_on = 1;
             a.ar = *fused->ar;
@@ -1743,8 +1754,11 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
     switch (w->kind) {
         case FK_Q4_K: return launch_kind<FK_Q4_K>(ctx, st, a, w, slots, dump);
         case FK_BF16:
-            if (ids_dev || n_active_dev || fused || isums_dev) return fk_fail(FK_UNSUPPORTED, "gemv: BF16 has the plain matvec only (nothing is quantized: no integer hook)");
-            return fk_gemv_bf16_launch(ctx, st, w, mat, x_dev, batch, y_dev);
+            // nothing is quantized (no integer hook); the norm, bias and add-into forms are built, the gated, indexed and
+            // row-split ones are not
+            if (ids_dev || n_active_dev || isums_dev || (fused && (fused->glu_up || fused->pair_glu || fused->ar)))
+                return fk_fail(FK_UNSUPPORTED, "gemv: BF16 has the plain matvec with an optional norm, bias and add-into only");
+            return fk_gemv_bf16_launch(ctx, st, w, mat, x_dev, a.x_ld, batch, y_dev, a.norm_w, a.norm_eps, a.bias, a.accumulate);
         case FK_Q5_K:
             // the plain matvec only: the fused, indexed and row-split forms have no Q5_K kernel (the caller composes them
             // from the separate kernels, as it would for any kind this library does not fuse)
@@ -1857,6 +1871,39 @@ FK_EXPORT int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const in
     FkDeviceGuard g(ctx->device);
     FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0, nullptr};
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, gate_dev, x_stride, 1, y_dev, nullptr, n_active_dev, &f);
+}
+
+// gpt-oss's projections carry a bias row (crates/frink-models/src/models/gpt_oss.rs:9-12,46); it is added by the lane
+// that finishes the row, so a biased projection is still one launch:  y[b] (+)= W rmsnorm?(x[b]) + bias.
+FK_EXPORT int fk_gemv_biased(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                             const float* norm_weight_dev, float norm_eps, const float* bias_dev, int accumulate) {
+    if (!ctx || !w || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_biased: null argument");
+    if (batch < 1 || batch > 8) return fk_fail(FK_UNSUPPORTED, "gemv_biased: batch %d outside 1..8", batch);
+    if (mat < 0 || mat >= w->n_mats) return fk_fail(FK_INVALID, "gemv_biased: matrix %d of %d", mat, w->n_mats);
+    if (x_ld == 0) x_ld = w->cols;
+    if (x_ld < w->cols || (x_ld & 3)) return fk_fail(FK_INVALID, "gemv_biased: x_ld %d (columns %d, must be a multiple of 4)", x_ld, w->cols);
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)norm_weight_dev & 15)) return fk_fail(FK_INVALID, "gemv_biased: inputs must be 16-byte aligned");
+    FkDeviceGuard g(ctx->device);
+    FkGemvFused f{norm_weight_dev, norm_eps, nullptr, 0, accumulate, x_ld, 0, nullptr};
+    f.bias = bias_dev;
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, nullptr, mat, 1, x_dev, 0, batch, y_dev, nullptr, nullptr, &f);
+}
+
+// The indexed expert matvec with every expert's own bias row (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060):
+// slot j:  y[j] = W[ids[j]] in_j + bias[ids[j]],  in_j = x[j] (up_dev null) or act(x[j]) * up[j] (x the BIASED gate).
+FK_EXPORT int fk_gemv_multi_biased(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev, const float* up_dev,
+                                   int x_stride, int glu_act, const float* bias_dev, float* y_dev) {
+    if (!ctx || !w || !ids_dev || !x_dev || !y_dev || !bias_dev) return fk_fail(FK_INVALID, "gemv_multi_biased: null argument");
+    if (w->kind == FK_BF16 || w->kind == FK_Q5_K) return fk_fail(FK_UNSUPPORTED, "gemv_multi_biased: kind %d has no indexed form", w->kind);
+    if (k < 1 || k > 65535) return fk_fail(FK_INVALID, "gemv_multi_biased: k=%d", k);
+    if (glu_act < 0 || glu_act > 1) return fk_fail(FK_UNSUPPORTED, "gemv_multi_biased: activation %d", glu_act);
+    if (x_stride != 0 && x_stride < w->cols) return fk_fail(FK_INVALID, "gemv_multi_biased: x_stride %d < cols %d", x_stride, w->cols);
+    if (up_dev && x_stride == 0) return fk_fail(FK_INVALID, "gemv_multi_biased: the gated form reads one row per slot (x_stride 0)");
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)up_dev & 15) || (x_stride & 3)) return fk_fail(FK_INVALID, "gemv_multi_biased: inputs must be 16-byte aligned");
+    FkDeviceGuard g(ctx->device);
+    FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0, nullptr};
+    f.bias = bias_dev;
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, &f);
 }
 
 FK_EXPORT int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,

@@ -2,18 +2,44 @@
 // gpt-oss keeps its attention projections in this format.  Nothing is quantized here -- the activations stay f32 and the
 // products are accumulated in f32 -- so this matvec shares only the calling convention with the block formats.
 // A warp per row, a lane on 8 weights (one 16-byte load) per trip, four trips in flight; the activations come through
-// the read-only cache (every warp of an SM reads the same vector).  Plain matvec for batches of 1..8, and the
-// elementwise pieces a gpt-oss layer adds around its projections (bias rows).
+// the read-only cache (every warp of an SM reads the same vector).  Batches of 1..8; optionally the RMSNorm of the
+// input in the prologue, a bias row and add-into-y in the epilogue (a gpt-oss projection is one launch), and the
+// standalone bias add for outputs of the GEMM path.
 #include "fk_common.cuh"
 
 namespace {
 
 constexpr int BF_THREADS = 256, BF_WARPS = BF_THREADS / 32;
 
-template <int NB>
-__global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* __restrict__ w, size_t row_elems, const float* __restrict__ x,
-                                                               float* __restrict__ y, int rows, int cols, int batch) {
+// NORM: the block first stages rmsnorm(x[b]) * norm_w for its batch rows in shared memory (every block repeats the few
+// thousand multiply-adds).  The sum of squares is not added in the order of the separate norm launch: the fused form
+// agrees with it to rounding, not to the bit, as in the block-format matvecs.
+template <int NB, bool NORM>
+__global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* __restrict__ w, size_t row_elems, const float* __restrict__ x, int x_ld,
+                                                               float* __restrict__ y, int rows, int cols, int batch,
+                                                               const float* __restrict__ norm_w, float eps, const float* __restrict__ bias,
+                                                               int accumulate) {
+    extern __shared__ __align__(16) float xs[];              // NORM: [NB][cols]
+    __shared__ float red[BF_WARPS];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (NORM) {
+        for (int b = 0; b < NB && b < batch; b++) {
+            float ss = 0.0f;
+            for (int c = threadIdx.x; c < cols; c += BF_THREADS) {
+                const float v = x[(size_t)b * x_ld + c];
+                ss = fmaf(v, v, ss);
+            }
+            ss = fk_warp_sum(ss);
+            if (lane == 0) red[warp] = ss;
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int i = 0; i < BF_WARPS; i++) tot += red[i];
+            const float scale = rsqrtf(tot / (float)cols + eps);
+            for (int c = threadIdx.x; c < cols; c += BF_THREADS) xs[(size_t)b * cols + c] = x[(size_t)b * x_ld + c] * scale * norm_w[c];
+            __syncthreads();
+        }
+    }
     const int wid = blockIdx.x * BF_WARPS + warp, nw = gridDim.x * BF_WARPS;
     const int c8 = cols >> 3;                               // 16-byte chunks of a row
     for (int row = wid; row < rows; row += nw) {
@@ -42,7 +68,14 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
 #pragma unroll
                 for (int b = 0; b < NB; b++) {
                     if (b >= batch) break;
-                    const float4 x0 = __ldg((const float4*)(x + (size_t)b * cols) + 2 * c), x1 = __ldg((const float4*)(x + (size_t)b * cols) + 2 * c + 1);
+                    float4 x0, x1;
+                    if (NORM) {
+                        x0 = ((const float4*)(xs + (size_t)b * cols))[2 * c];
+                        x1 = ((const float4*)(xs + (size_t)b * cols))[2 * c + 1];
+                    } else {
+                        x0 = __ldg((const float4*)(x + (size_t)b * x_ld) + 2 * c);
+                        x1 = __ldg((const float4*)(x + (size_t)b * x_ld) + 2 * c + 1);
+                    }
                     acc[b] = fmaf(f[0], x0.x, fmaf(f[1], x0.y, fmaf(f[2], x0.z, fmaf(f[3], x0.w, acc[b]))));
                     acc[b] = fmaf(f[4], x1.x, fmaf(f[5], x1.y, fmaf(f[6], x1.z, fmaf(f[7], x1.w, acc[b]))));
                 }
@@ -50,8 +83,12 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
         }
 #pragma unroll
         for (int b = 0; b < NB; b++) {
-            const float v = fk_warp_sum(acc[b]);             // xor butterfly: the same order on every run
-            if (lane == 0 && b < batch) y[(size_t)b * rows + row] = v;
+            float v = fk_warp_sum(acc[b]);                   // xor butterfly: the same order on every run
+            if (lane == 0 && b < batch) {
+                if (bias) v += bias[row];
+                float* dst = y + (size_t)b * rows + row;
+                *dst = accumulate ? *dst + v : v;
+            }
         }
     }
 }
@@ -66,20 +103,35 @@ __global__ void add_bias_kernel(float* __restrict__ y, const float* __restrict__
 
 }  // namespace
 
-int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int batch, float* y_dev) {
+template <int NB>
+static int launch_bf16(fk_ctx* ctx, cudaStream_t st, int blocks, const uint16_t* wp, size_t row_elems, const float* x, int x_ld, float* y, int rows,
+                       int cols, int batch, const float* norm_w, float eps, const float* bias, int accumulate) {
+    if (norm_w) {
+        const size_t smem = (size_t)NB * cols * sizeof(float);
+        if (smem > 200 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): a fused norm over %d rows of %d columns does not fit shared memory", NB, cols);
+        if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_LAUNCH);
+        gemv_bf16_kernel<NB, true><<<blocks, BF_THREADS, smem, st>>>(wp, row_elems, x, x_ld, y, rows, cols, batch, norm_w, eps, bias, accumulate);
+    } else {
+        gemv_bf16_kernel<NB, false><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x, x_ld, y, rows, cols, batch, nullptr, 0.0f, bias, accumulate);
+    }
+    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    ctx->launches++;
+    return FK_OK;
+}
+
+int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                        const float* norm_w, float norm_eps, const float* bias, int accumulate) {
     if (w->cols & 7) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): %d columns is not a multiple of 8", w->cols);
     const uint16_t* wp = (const uint16_t*)(w->dev + (size_t)mat * w->mat_stride + w->plane_off[0]);
     const size_t row_elems = w->plane_stride[0] / 2;
     int blocks = ctx->sm_count * 8;
     const int need = (w->rows + BF_WARPS - 1) / BF_WARPS;
     if (blocks > need) blocks = need;
-    if (batch <= 1) gemv_bf16_kernel<1><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x_dev, y_dev, w->rows, w->cols, batch);
-    else if (batch <= 2) gemv_bf16_kernel<2><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x_dev, y_dev, w->rows, w->cols, batch);
-    else if (batch <= 4) gemv_bf16_kernel<4><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x_dev, y_dev, w->rows, w->cols, batch);
-    else gemv_bf16_kernel<8><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x_dev, y_dev, w->rows, w->cols, batch);
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
-    ctx->launches++;
-    return FK_OK;
+    if (x_ld == 0) x_ld = w->cols;
+    if (batch <= 1) return launch_bf16<1>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
+    if (batch <= 2) return launch_bf16<2>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
+    if (batch <= 4) return launch_bf16<4>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
+    return launch_bf16<8>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
 }
 
 // gpt-oss adds a bias to q, k, v and the attention output, to the router logits and to every expert projection

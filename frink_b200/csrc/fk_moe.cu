@@ -275,6 +275,21 @@ __global__ void __launch_bounds__(256) local_pairs_kernel(const int* __restrict_
     if (i == 0) *out_n = total;
 }
 
+// y[r][c] += bias[expert of permuted row r][c]: the rows of a grouped GEMM's output are sorted by expert, group_off [E + 1]
+// says where each expert's rows start, so a thread finds its row's expert by bisection
+__global__ void add_bias_grouped_kernel(float* __restrict__ y, const float* __restrict__ bias, const int* __restrict__ group_off, int n_experts,
+                                        int n_rows, int cols) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_rows * cols) return;
+    const int r = (int)(i / cols), c = (int)(i - (size_t)r * cols);
+    int lo = 0, hi = n_experts;                      // the expert e with group_off[e] <= r < group_off[e + 1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (group_off[mid] <= r) lo = mid; else hi = mid;
+    }
+    y[i] += bias[(size_t)lo * cols + c];
+}
+
 // out[j] = x[j / k] for j < rows * k: every slot of a decode batch gets its row's activation.
 __global__ void repeat_rows_kernel(const float* __restrict__ x, int cols4, int k, size_t n4, float* __restrict__ out) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -462,9 +477,9 @@ FK_EXPORT size_t fk_moe_layer_workspace(int n_experts, int k, int hidden, int ff
 //   batch <= 8 : every (row, expert) pair a slot of one indexed matvec per projection, GLU in the down projection;
 //   batch  > 8 : pairs grouped by expert, one grouped GEMM per projection;
 // then the weighted combine in routing order, written to out_dev or added into it.
-FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
-                           fk_weight down, int k, int mode, int act, const float* x_dev, int batch, float* out_dev, int accumulate,
-                           void* workspace_dev, size_t workspace_bytes) {
+static int moe_layer_impl(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                          fk_weight down, const float* gate_b, const float* up_b, const float* down_b, int k, int mode, int act, const float* x_dev,
+                          int batch, float* out_dev, int accumulate, void* workspace_dev, size_t workspace_bytes) {
     if (!ctx || !router_dev || !gate || !up || !down || !x_dev || !out_dev || !workspace_dev) return fk_fail(FK_INVALID, "moe_layer: null argument");
     const int E = gate->n_mats, hidden = gate->cols, ffn = gate->rows;
     if (up->n_mats != E || down->n_mats != E || up->rows != ffn || up->cols != hidden || down->rows != hidden || down->cols != ffn)
@@ -498,6 +513,13 @@ FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, c
             xin = xr;
             x_stride = hidden;
         }
+        if (gate_b) {
+            // every slot's bias row is added by the lane that finishes the row: still three launches
+            if ((rc = fk_gemv_multi_biased(ctx, stream, gate, ids, pairs, xin, nullptr, x_stride, 0, gate_b, g))) return rc;
+            if ((rc = fk_gemv_multi_biased(ctx, stream, up, ids, pairs, xin, nullptr, x_stride, 0, up_b, u))) return rc;
+            if ((rc = fk_gemv_multi_biased(ctx, stream, down, ids, pairs, g, u, ffn, act, down_b, y))) return rc;
+            return combine(ctx, stream, y, nullptr, w, batch, k, hidden, out_dev);
+        }
         if ((rc = fk_gemv_multi(ctx, stream, gate, ids, pairs, xin, x_stride, g))) return rc;
         if ((rc = fk_gemv_multi(ctx, stream, up, ids, pairs, xin, x_stride, u))) return rc;
         if ((rc = fk_gemv_multi_glu(ctx, stream, down, ids, pairs, g, u, ffn, act, y, nullptr))) return rc;
@@ -509,9 +531,39 @@ FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, c
     if ((rc = fk_router_logits(ctx, stream, router_dev, x_dev, E, hidden, batch, logits))) return rc;
     if ((rc = fk_moe_route(ctx, stream, logits, router_bias_dev, E, k, mode, batch, ids, w))) return rc;
     if ((rc = fk_moe_permute(ctx, stream, ids, pairs, k, E, group_off, gather, pair_of))) return rc;
+    auto add_bias = [&](float* t, const float* bias, int cols) -> int {
+        if (!bias) return FK_OK;
+        FkDeviceGuard gd(ctx->device);
+        const size_t n = (size_t)pairs * cols;
+        add_bias_grouped_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(t, bias, group_off, E, pairs, cols);
+        FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+        ctx->launches++;
+        return FK_OK;
+    };
     if ((rc = fk_gemm_grouped(ctx, stream, gate, group_off, gather, x_dev, pairs, g))) return rc;
+    if ((rc = add_bias(g, gate_b, ffn))) return rc;
     if ((rc = fk_gemm_grouped(ctx, stream, up, group_off, gather, x_dev, pairs, u))) return rc;
+    if ((rc = add_bias(u, up_b, ffn))) return rc;
     if ((rc = fk_glu(ctx, stream, g, u, (size_t)pairs * ffn, act, g))) return rc;
     if ((rc = fk_gemm_grouped(ctx, stream, down, group_off, nullptr, g, pairs, y))) return rc;
+    if ((rc = add_bias(y, down_b, hidden))) return rc;
     return combine(ctx, stream, y, pair_of, w, batch, k, hidden, out_dev);
+}
+
+FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                           fk_weight down, int k, int mode, int act, const float* x_dev, int batch, float* out_dev, int accumulate,
+                           void* workspace_dev, size_t workspace_bytes) {
+    return moe_layer_impl(ctx, stream, router_dev, router_bias_dev, gate, up, down, nullptr, nullptr, nullptr, k, mode, act, x_dev, batch, out_dev,
+                          accumulate, workspace_dev, workspace_bytes);
+}
+
+// gpt-oss's routed layer (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060): fk_moe_layer whose expert projections
+// each carry a bias table [n_experts][rows]; the activation (act = 1, the clamped form) is applied to the BIASED gate and up.
+FK_EXPORT int fk_moe_layer_biased(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                                  fk_weight down, const float* gate_bias_dev, const float* up_bias_dev, const float* down_bias_dev, int k, int mode,
+                                  int act, const float* x_dev, int batch, float* out_dev, int accumulate, void* workspace_dev,
+                                  size_t workspace_bytes) {
+    if (!gate_bias_dev || !up_bias_dev || !down_bias_dev) return fk_fail(FK_INVALID, "moe_layer_biased: the three bias tables come together");
+    return moe_layer_impl(ctx, stream, router_dev, router_bias_dev, gate, up, down, gate_bias_dev, up_bias_dev, down_bias_dev, k, mode, act, x_dev,
+                          batch, out_dev, accumulate, workspace_dev, workspace_bytes);
 }

@@ -201,6 +201,11 @@ class Decoder:
                 for name in ("bq", "bk", "bv", "bo"):
                     if getattr(L, name) is not None:
                         d[name] = f32(getattr(L, name))
+                # the bias rows of the stacked projections, stacked the same way (the decode form adds them in the matvec)
+                if "qkv" in d and all(n_ in d for n_ in ("bq", "bk", "bv")):
+                    d["bqkv"] = torch.cat([d["bq"], d["bk"], d["bv"]])
+                elif "qk" in d and "bq" in d and "bk" in d:
+                    d["bqk"] = torch.cat([d["bq"], d["bk"]])
             if cfg.n_experts and cfg.oai:
                 mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
                 d["moe"] = RoutedLayer(f32(L.router), mk(L.gate, cfg.ffn, H), mk(L.up, cfg.ffn, H), mk(L.down, H, cfg.ffn), k=cfg.top_k,
@@ -250,7 +255,7 @@ class Decoder:
         hd = cfg.head_dim
         n = ids.numel()
         self._claim(n)
-        if n <= 8 and hasattr(ops, "gemv_fused") and (self.t_dense == 1 or self.comm is not None) and not cfg.oai:
+        if n <= 8 and hasattr(ops, "gemv_fused") and (self.t_dense == 1 or self.comm is not None):
             return self._forward_fused(ids)
         x = ops.get_rows(self.embd, ids)                    # residual stream [n, hidden]
         pending = None                                      # a block output not yet added to x
@@ -326,8 +331,6 @@ class Decoder:
     def forward_seqs(self, toks):
         """toks [n_seqs] (device int32), sequence r's newest token -> logits [n_seqs, vocab]; every position advances."""
         n = toks.numel()
-        if self.cfg.oai:
-            raise ValueError("batched sequences are not built for the gpt-oss layer form")
         if n != len(self._seq_pos_host):
             raise ValueError(f"{n} tokens for {len(self._seq_pos_host)} sequences")
         if max(self._seq_pos_host) + 1 > self.max_seq:
@@ -370,6 +373,8 @@ class Decoder:
         ops, cfg = self.ops, self.cfg
 
         def into_residual(lin, inp, is_padded=False, **kw):
+            if kw.get("bias") is None:
+                kw.pop("bias", None)
             if isinstance(lin, parallel.RowParallelLinear):
                 ops.gemv_fused(lin.w, inp if is_padded else lin.padded(inp), out=x, accumulate=True, allreduce=(lin.comm, lin.ch), **kw)
             else:
@@ -379,18 +384,20 @@ class Decoder:
         hq, kvw = self.h_loc * hd, self.kv_loc * hd
         x = ops.get_rows(self.embd, ids)
         for L in self.layers:
+            def normed(name, bias=None):
+                # the attention norm rides in the prologue of every projection that reads it, a gpt-oss bias row in its epilogue
+                kw = {} if L.get(bias) is None else {"bias": L[bias]}
+                return ops.gemv_fused(L[name].w, x, norm_weight=L["attn_norm"], eps=cfg.eps, **kw)
             if "qkv" in L:
-                qkv = ops.gemv_fused(L["qkv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                qkv = normed("qkv", "bqkv")
                 q, k, v = qkv[:, :hq], qkv[:, hq:hq + kvw], qkv[:, hq + kvw:]
             elif "qk" in L:
                 # v in another block format (the usual K-quant mix): two matvecs, the norm folded into both
-                qk = ops.gemv_fused(L["qk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                qk = normed("qk", "bqk")
                 q, k = qk[:, :hq], qk[:, hq:hq + kvw]
-                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                v = normed("wv", "bv")
             else:
-                q = ops.gemv_fused(L["wq"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
-                k = ops.gemv_fused(L["wk"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
-                v = ops.gemv_fused(L["wv"].w, x, norm_weight=L["attn_norm"], eps=cfg.eps)
+                q, k, v = normed("wq", "bq"), normed("wk", "bk"), normed("wv", "bv")
             window = getattr(L["wo"], "window", None)
             if seqs:
                 a = ops.attention_rope_kv_seqs(q, k, v, L["ks"], L["vs"], self.h_loc, self.kv_loc, hd, self.seq_pos, cfg.rope_theta, cfg.neox,
@@ -416,8 +423,11 @@ class Decoder:
             if a is None:
                 into_residual(L["wo"], L["wo"].row, is_padded=True)
             else:
-                into_residual(L["wo"], a)
-            if "moe" in L:
+                into_residual(L["wo"], a, bias=L.get("bo"))
+            if "moe_b" in L:
+                h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
+                run_device_routed_oai(L["moe"], L["moe_b"], h2, ops, residual=x)
+            elif "moe" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 if n > 1 and hasattr(ops, "gemv_multi_glu"):
                     run_device_routed_rows(L["moe"], h2, ops, residual=x)      # all rows' (row, expert) pairs as slots of one launch

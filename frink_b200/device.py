@@ -120,19 +120,25 @@ def gemv(w, x, mat=0, out=None):
     return y if x.dim() > 1 or out is not None else y[0]
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0, allreduce=None):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0, allreduce=None, bias=None):
     """gemv with its elementwise neighbours folded in: reads rmsnorm(x) * norm_weight, or
     act(x) * glu_up (x the gate), and/or adds into `out` instead of overwriting it.
     x (and glu_up) are [batch <= 8, cols] with any row stride that is a multiple of 4.
     pair_glu (1 SiLU, 2 gpt-oss): `w` holds gate and up row-interleaved; the result is
     act(gate) * up, [batch, rows / 2].
     allreduce = (`frink_b200.comm.Comm`, channel): `w` is this rank's column range of a row-split
-    matrix and the result is summed over the ranks by the matvec's epilogue."""
+    matrix and the result is summed over the ranks by the matvec's epilogue.
+    bias [rows]: added to the result by the same launch (`fk_gemv_biased`; with a norm and/or accumulate only)."""
     assert x.is_cuda and x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
     batch, ld = x.shape[0], x.stride(0) if x.shape[0] > 1 else max(x.stride(0), w.cols)
     if glu_up is not None:
         assert glu_up.shape == x.shape and glu_up.stride(1) == 1 and (batch == 1 or glu_up.stride(0) == x.stride(0))
     y = out if out is not None else torch.empty((batch, w.rows // 2 if pair_glu else w.rows), dtype=torch.float32, device=x.device)
+    if bias is not None:
+        assert glu_up is None and not pair_glu and allreduce is None and bias.numel() == w.rows
+        check(lib().fk_gemv_biased(w._ctx, _stream(), w.handle, mat, _ptr(x), ld, batch, _ptr(y),
+                                   _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps), _ptr(_f32(bias)), int(bool(accumulate))))
+        return y
     if allreduce is not None:
         comm, (off, n_max) = allreduce
         assert not pair_glu
@@ -159,22 +165,29 @@ def rope_kv(q, k, v, n_heads, n_kv, head_dim, pos, theta, neox, k_cache, v_cache
                            min(k_cache.shape[0], v_cache.shape[0])))
 
 
-def gemv_multi(w, ids, x, out=None):
-    """Slot j: matrix ids[j] of `w` times x[j] (or the one shared x) -> out[j]."""
+def gemv_multi(w, ids, x, out=None, bias=None):
+    """Slot j: matrix ids[j] of `w` times x[j] (or the one shared x) -> out[j]; with bias [n_mats, rows], + bias[ids[j]]."""
     ids, x = _i32(ids), _f32(x)
     k = ids.numel()
     stride = 0 if x.dim() == 1 else x.stride(0)
     y = out if out is not None else torch.empty((k, w.rows), dtype=torch.float32, device=x.device)
+    if bias is not None:
+        check(lib().fk_gemv_multi_biased(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(x), None, stride, 0, _ptr(_f32(bias)), _ptr(y)))
+        return y
     check(lib().fk_gemv_multi(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(x), stride, _ptr(y)))
     return y
 
 
-def gemv_multi_glu(w, ids, gate, up, act=0, out=None, n_active=None):
-    """Slot j: matrix ids[j] of `w` times act(gate[j]) * up[j] -> out[j] (gate, up: [k, cols])."""
+def gemv_multi_glu(w, ids, gate, up, act=0, out=None, n_active=None, bias=None):
+    """Slot j: matrix ids[j] of `w` times act(gate[j]) * up[j] -> out[j] (gate, up: [k, cols]); with bias, + bias[ids[j]]."""
     ids, gate, up = _i32(ids), _f32(gate), _f32(up)
     k = ids.numel()
     assert gate.shape == up.shape and gate.dim() == 2 and gate.shape[0] == k
     y = out if out is not None else torch.empty((k, w.rows), dtype=torch.float32, device=gate.device)
+    if bias is not None:
+        assert n_active is None
+        check(lib().fk_gemv_multi_biased(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(gate), _ptr(up), gate.stride(0), int(act), _ptr(_f32(bias)), _ptr(y)))
+        return y
     check(lib().fk_gemv_multi_glu(w._ctx, _stream(), w.handle, _ptr(ids), k, _ptr(gate), _ptr(up), gate.stride(0), int(act), _ptr(y),
                                   _ptr(_i32(n_active)) if n_active is not None else None))
     return y
@@ -206,9 +219,10 @@ def add_bias_(y, bias, ids=None):
     return y
 
 
-def moe_layer(layer, x, out=None, accumulate=False):
+def moe_layer(layer, x, out=None, accumulate=False, biases=None):
     """The routed layer in one call (`fk_moe_layer`): `layer` carries router, router_bias, gate / up / down (stacked
-    `Weights`), k, mode, act; x [batch, hidden] or [hidden].  The workspace is kept on the layer object, per batch size."""
+    `Weights`), k, mode, act; x [batch, hidden] or [hidden].  The workspace is kept on the layer object, per batch size.
+    biases = (gate_b, up_b, down_b), each [n_experts, rows]: gpt-oss's form (`fk_moe_layer_biased`)."""
     x2 = _f32(x) if x.dim() == 2 else _f32(x)[None]
     batch = x2.shape[0]
     g = layer.gate
@@ -221,7 +235,15 @@ def moe_layer(layer, x, out=None, accumulate=False):
     assert not accumulate or out is not None
     o = out if out is not None else torch.empty((batch, g.cols), dtype=torch.float32, device=x2.device)
     o2 = o if o.dim() == 2 else o[None]
-    check(lib().fk_moe_layer(g._ctx, _stream(), _ptr(_f32(layer.router)), _ptr(_f32(layer.router_bias)) if layer.router_bias is not None else None,
+    rb = _ptr(_f32(layer.router_bias)) if layer.router_bias is not None else None
+    if biases is not None:
+        gb, ub, db = (_f32(t) for t in biases)
+        assert gb.shape == (g.n_mats, g.rows) and ub.shape == gb.shape and db.shape == (g.n_mats, g.cols)
+        check(lib().fk_moe_layer_biased(g._ctx, _stream(), _ptr(_f32(layer.router)), rb, g.handle, layer.up.handle, layer.down.handle,
+                                        _ptr(gb), _ptr(ub), _ptr(db), layer.k, int(layer.mode), int(layer.act), _ptr(x2), batch, _ptr(o2),
+                                        int(bool(accumulate)), C.c_void_p(base), buf.numel() - (base - buf.data_ptr())))
+        return o if x.dim() == 2 or out is not None else o[0]
+    check(lib().fk_moe_layer(g._ctx, _stream(), _ptr(_f32(layer.router)), rb,
                              g.handle, layer.up.handle, layer.down.handle, layer.k, int(layer.mode), int(layer.act), _ptr(x2), batch, _ptr(o2),
                              int(bool(accumulate)), C.c_void_p(base), buf.numel() - (base - buf.data_ptr())))
     return o if x.dim() == 2 or out is not None else o[0]

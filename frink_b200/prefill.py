@@ -97,13 +97,17 @@ def run_device_routed_rows(layer, x, ops=None, residual=None):
     return ops.moe_combine(y, None, w, b, layer.k)
 
 
-def run_device_routed_oai(layer, biases, x, ops=None):
+def run_device_routed_oai(layer, biases, x, ops=None, residual=None):
     """gpt-oss's routed layer (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060): every expert projection has a
     bias row of its own (biases = (gate_b, up_b, down_b), each [n_experts, rows]) and the activation is the clamped
-    SwiGLU (`layer.act` = 1), applied to the BIASED gate and up.  x [b, hidden] -> [b, hidden].  Up to 8 rows: every
-    (row, expert) pair a slot of the indexed matvecs; more: pairs grouped by expert through the grouped GEMMs."""
+    SwiGLU (`layer.act` = 1), applied to the BIASED gate and up.  x [b, hidden] -> [b, hidden], or added into
+    `residual`.  Up to 8 rows: every (row, expert) pair a slot of the indexed matvecs; more: pairs grouped by expert
+    through the grouped GEMMs.  An `ops` with `moe_layer` runs it as one C call (`fk_moe_layer_biased`: the biases
+    ride in the matvecs' epilogues); the composition below is what that call does, from the separate entry points."""
     import torch
     ops = _ops(ops)
+    if hasattr(ops, "moe_layer"):
+        return ops.moe_layer(layer, x, out=residual, accumulate=residual is not None, biases=biases)
     gate_b, up_b, down_b = biases
     b, k = x.shape[0], layer.k
     ids, w = route(layer, x, ops)
@@ -113,15 +117,18 @@ def run_device_routed_oai(layer, biases, x, ops=None):
         g = ops.add_bias_(ops.gemv_multi(layer.gate, ids1, xr), gate_b, ids1)
         u = ops.add_bias_(ops.gemv_multi(layer.up, ids1, xr), up_b, ids1)
         y = ops.add_bias_(ops.gemv_multi_glu(layer.down, ids1, g, u, layer.act), down_b, ids1)
-        return ops.moe_combine(y, None, w, b, k)
-    pairs = b * k
-    group_off, gather, pair_of = ops.moe_permute(ids, layer.n_experts)
-    # the expert of every permuted row, from the group offsets (no host round trip)
-    expert_of = torch.searchsorted(group_off[1:].to(torch.int64), torch.arange(pairs, device=group_off.device), right=True).to(torch.int32)
-    g = ops.add_bias_(ops.gemm_grouped(layer.gate, group_off, gather, x, pairs), gate_b, expert_of)
-    u = ops.add_bias_(ops.gemm_grouped(layer.up, group_off, gather, x, pairs), up_b, expert_of)
-    a = ops.glu(g, u, layer.act)
-    y = ops.add_bias_(ops.gemm_grouped(layer.down, group_off, None, a, pairs), down_b, expert_of)
+        pair_of = None
+    else:
+        pairs = b * k
+        group_off, gather, pair_of = ops.moe_permute(ids, layer.n_experts)
+        # the expert of every permuted row, from the group offsets (no host round trip)
+        expert_of = torch.searchsorted(group_off[1:].to(torch.int64), torch.arange(pairs, device=group_off.device), right=True).to(torch.int32)
+        g = ops.add_bias_(ops.gemm_grouped(layer.gate, group_off, gather, x, pairs), gate_b, expert_of)
+        u = ops.add_bias_(ops.gemm_grouped(layer.up, group_off, gather, x, pairs), up_b, expert_of)
+        a = ops.glu(g, u, layer.act)
+        y = ops.add_bias_(ops.gemm_grouped(layer.down, group_off, None, a, pairs), down_b, expert_of)
+    if residual is not None:
+        return ops.moe_combine(y, pair_of, w, b, k, out=residual, accumulate=True)
     return ops.moe_combine(y, pair_of, w, b, k)
 
 

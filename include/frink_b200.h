@@ -145,6 +145,17 @@ int fk_gemv_multi_glu(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev
 int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,
                          int x_stride, float* y_dev, const int* n_active_dev);
 
+/* Biased projections of a gpt-oss layer (crates/frink-models/src/models/gpt_oss.rs:9-12,46) as one launch:
+ *   y[b] (+)= W rmsnorm?(x[b]) + bias        (norm_weight_dev, bias_dev may be null; bias_dev is [rows]).
+ * Every kind with a matvec except Q5_K; BF16 included (its only fused forms are these). */
+int fk_gemv_biased(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float* x_dev, int x_ld, int batch, float* y_dev,
+                   const float* norm_weight_dev, float norm_eps, const float* bias_dev, int accumulate);
+/* fk_gemv_multi / fk_gemv_multi_glu with every expert's own bias row (`run_expert_oai`, crates/frink-moe/src/
+ * lib.rs:1039-1060): slot j: y[j] = W[ids[j]] in_j + bias_dev[ids[j]], in_j = x[j], or act(x[j]) * up[j] when
+ * up_dev is given (x then being the biased gate); bias_dev is [n_mats][rows]. */
+int fk_gemv_multi_biased(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev, const float* up_dev,
+                         int x_stride, int glu_act, const float* bias_dev, float* y_dev);
+
 /* Test hook (the reference's twins expose the same integers,
  * crates/frink-cuda/src/dp4a_twin.rs:142-231): the exact int32 dot of every
  * run of 32 activations (16 for Q6_K) of every row against q8_1(x), computed
@@ -258,6 +269,14 @@ size_t fk_moe_layer_workspace(int n_experts, int k, int hidden, int ffn, int bat
 int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
                  fk_weight down, int k, int mode, int act, const float* x_dev, int batch, float* out_dev, int accumulate,
                  void* workspace_dev, size_t workspace_bytes);
+/* gpt-oss's routed layer (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060): fk_moe_layer whose three
+ * expert projections carry a bias table each ([n_experts][ffn], [n_experts][ffn], [n_experts][hidden]); the
+ * activation is applied to the biased gate and up.  Decode batches add the bias in the matvec's epilogue;
+ * the grouped GEMM path adds it with a launch per projection. */
+int fk_moe_layer_biased(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                        fk_weight down, const float* gate_bias_dev, const float* up_bias_dev, const float* down_bias_dev, int k, int mode,
+                        int act, const float* x_dev, int batch, float* out_dev, int accumulate, void* workspace_dev,
+                        size_t workspace_bytes);
 
 /* ---- decoder glue (next-row components: enough to run a decoder and report
  * prefill / decode tokens per second; f32 throughout) -------------------------

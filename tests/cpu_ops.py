@@ -179,7 +179,7 @@ def add_int_(p, v):
     p.add_(v)
 
 
-def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0):
+def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, glu_act=0, accumulate=False, pair_glu=0, bias=None):
     """The fused matvec of the device layer, composed from the separate CPU steps."""
     h = x.clone()
     if norm_weight is not None:
@@ -187,6 +187,8 @@ def gemv_fused(w, x, out=None, mat=0, norm_weight=None, eps=0.0, glu_up=None, gl
     if glu_up is not None:
         h = glu(h.contiguous(), glu_up.contiguous(), glu_act)
     y = gemv(w, h, mat=mat)
+    if bias is not None:
+        y = y + bias
     if pair_glu:
         y = glu(y[:, 0::2].contiguous(), y[:, 1::2].contiguous(), pair_glu - 1)
     if out is None:

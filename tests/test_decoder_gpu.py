@@ -423,13 +423,17 @@ def test_the_workspace_never_moves_under_a_captured_graph(monkeypatch):
         lib().fk_destroy(fresh)
 
 
-@pytest.mark.parametrize("moe", [False, True])
+@pytest.mark.parametrize("moe", [False, True, "oai"])
 def test_a_decode_batch_of_independent_sequences_matches_each_sequence_alone(moe):
     """Eight sequences with prompts of different lengths, decoded together (one token each per step, their own KV
     caches and positions, one launch per op for the whole batch), against each sequence decoded alone."""
     from frink_b200 import device
     from frink_b200.decoder import Decoder
-    if moe:
+    if moe == "oai":
+        # gpt-oss's layer form: biased BF16 projections (one launch each), sinks, a windowed layer, biased MXFP4 experts
+        cfg, layers, tok, out_norm, head = tiny_gpt_oss()
+        mk = lambda: Decoder(cfg, layers, tok, fo.BF16, out_norm, output=head, output_kind=fo.BF16, max_seq=64)
+    elif moe:
         from tests.test_parallel_cpu import _tiny_model
         cfg, layers, tok, out_norm, head = _tiny_model(True)
         mk = lambda: Decoder(cfg, layers, tok, fo.Q8_0, out_norm, output=head, output_kind=fo.Q8_0, max_seq=64)

@@ -100,3 +100,41 @@ def test_config4_shaped_routed_layer():
     # decode and prefill take their gate / up sums in different f32 orders; where that moves a gated
     # activation across a q8_1 rounding boundary the down projection's input differs by one step
     assert rel_l2(got_d, got[:8]) <= 1e-3
+
+
+def test_biased_routed_layer_one_call_against_the_composition_and_the_oracle():
+    """gpt-oss's routed layer (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060) as one C call: the biases ride
+    in the indexed matvecs' epilogues (decode) or follow the grouped GEMMs (prefill).  Bit-identical to the same layer
+    composed from the separate entry points, and equal to the oracle's composition with the bias rows added."""
+    import types
+    from frink_b200 import device, prefill
+    kind, n_exp, k, hidden, ffn, mode, act = fo.MXFP4, 8, 2, 576, 320, 1, 1
+    raws, router, layer = build_layer(kind, n_exp, hidden, ffn, k, mode, act, 1200)
+    rng = np.random.default_rng(9)
+    gb, ub, db = (rng.standard_normal((n_exp, n)).astype(np.float32) * 0.2 for n in (ffn, ffn, hidden))
+    biases = tuple(torch.from_numpy(b).cuda() for b in (gb, ub, db))
+    x = rng.standard_normal((40, hidden)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    separate = types.SimpleNamespace(**{n: getattr(device, n) for n in dir(device) if not n.startswith("_") and n != "moe_layer"})
+    for rows in (1, 4, 8, 40):
+        one = prefill.run_device_routed_oai(layer, biases, xd[:rows])
+        assert torch.equal(one, prefill.run_device_routed_oai(layer, biases, xd[:rows], separate)), rows
+        res = torch.randn(rows, hidden, device="cuda")
+        want = res + one
+        prefill.run_device_routed_oai(layer, biases, xd[:rows], residual=res)
+        assert torch.equal(res, want), rows
+    # the oracle's composition on three rows
+    logits = (x[:3] @ router.T).astype(np.float32)
+    ids, w = fo.route_top_k(logits, k, mode)
+    want = np.zeros((3, hidden), np.float32)
+    for t in range(3):
+        ys = []
+        for e in ids[t]:
+            xq = fo.q8_1_round(x[t])
+            g = fo.matmul_f64(kind, raws["gate"][e], ffn, hidden, xq)[0].astype(np.float32) + gb[e]
+            u = fo.matmul_f64(kind, raws["up"][e], ffn, hidden, xq)[0].astype(np.float32) + ub[e]
+            ys.append(fo.matmul_f64(kind, raws["down"][e], hidden, ffn, fo.q8_1_round(fo.swiglu_oai(g, u)))[0].astype(np.float32) + db[e])
+        want[t] = fo.combine(np.stack(ys), w[t])
+    got = prefill.run_device_routed_oai(layer, biases, xd[:3]).cpu().numpy()
+    assert rel_l2(got, want) <= 1e-3 and max_abs_over_inf(got, want) <= 2e-3
+    assert device.device_error() == 0
