@@ -1,8 +1,8 @@
 // BF16 weights (ggml type 30; crates/frink-quant/src/lib.rs:232-250: the upper half of an f32, widened exactly):
 // gpt-oss keeps its attention projections in this format.  Nothing is quantized here -- the activations stay f32 and the
 // products are accumulated in f32 -- so this matvec shares only the calling convention with the block formats.
-// A warp per row, a lane on 8 weights (one 16-byte load) per trip, four trips in flight; the activations come through
-// the read-only cache (every warp of an SM reads the same vector).  Batches of 1..8; optionally the RMSNorm of the
+// One or two warps per row, a lane on 8 weights (one 16-byte load) at a time with up to eight such loads in flight; the
+// activations come through the read-only cache (every warp of an SM reads the same vector).  Batches of 1..8; optionally the RMSNorm of the
 // input in the prologue, a bias row and add-into-y in the epilogue (a gpt-oss projection is one launch), and the
 // standalone bias add for outputs of the GEMM path.
 #include "fk_common.cuh"
@@ -14,14 +14,38 @@ constexpr int BF_THREADS = 256, BF_WARPS = BF_THREADS / 32;
 // NORM: the block first stages rmsnorm(x[b]) * norm_w for its batch rows in shared memory (every block repeats the few
 // thousand multiply-adds).  The sum of squares is not added in the order of the separate norm launch: the fused form
 // agrees with it to rounding, not to the bit, as in the block-format matvecs.
-template <int NB, bool NORM>
+// S warps share a row (each on its own run of K, the partial sums added in warp order by the first of them), so that a
+// matrix of a few thousand rows still has every SM's load queues full; U 16-byte loads a lane has in flight.
+// The grid may start while the previous kernel of the stream still runs (programmatic stream serialization): weights
+// are constants, so a warp requests its first trip of them BEFORE it waits for that kernel, and touches x, the bias and
+// y only after.
+template <int NB, bool NORM, int S, int U>
 __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* __restrict__ w, size_t row_elems, const float* __restrict__ x, int x_ld,
                                                                float* __restrict__ y, int rows, int cols, int batch,
                                                                const float* __restrict__ norm_w, float eps, const float* __restrict__ bias,
                                                                int accumulate) {
     extern __shared__ __align__(16) float xs[];              // NORM: [NB][cols]
     __shared__ float red[BF_WARPS];
+    __shared__ float part[BF_WARPS][NB];
+    constexpr int RPB = BF_WARPS / S;                        // rows a block works on at a time
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int rin = warp / S, prt = warp % S;
+    const int c8 = cols >> 3;                                // 16-byte chunks of a row
+    const int cpp = S == 1 ? c8 : ((((c8 + S - 1) / S) + 31) & ~31);   // chunks of a row one of its S warps takes
+    const int cb = prt * cpp, ce = cb + cpp < c8 ? cb + cpp : c8;
+    uint4 wv[U];
+    auto request = [&](int row, int c0) {
+        const uint4* rp = (const uint4*)(w + (size_t)row * row_elems);
+#pragma unroll
+        for (int u = 0; u < U; u++) {
+            const int c = c0 + u * 32 + lane;
+            wv[u] = row < rows && c < ce ? __ldg(rp + c) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    int rbase = blockIdx.x * RPB;
+    request(rbase + rin, cb);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (NORM) {
         for (int b = 0; b < NB && b < batch; b++) {
             float ss = 0.0f;
@@ -40,24 +64,19 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
             __syncthreads();
         }
     }
-    const int wid = blockIdx.x * BF_WARPS + warp, nw = gridDim.x * BF_WARPS;
-    const int c8 = cols >> 3;                               // 16-byte chunks of a row
-    for (int row = wid; row < rows; row += nw) {
-        const uint4* rp = (const uint4*)(w + (size_t)row * row_elems);
+    bool requested = true;                                   // the first trip of the first row is already on its way
+    for (; rbase < rows; rbase += gridDim.x * RPB) {         // (the same trip count for every warp of the block: it meets at a barrier)
+        const int row = rbase + rin;
         float acc[NB];
 #pragma unroll
         for (int b = 0; b < NB; b++) acc[b] = 0.0f;
-        for (int c0 = 0; c0 < c8; c0 += 4 * 32) {
-            uint4 wv[4];
+        for (int c0 = cb; c0 < ce; c0 += U * 32) {
+            if (!requested) request(row, c0);
+            requested = false;
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < U; u++) {
                 const int c = c0 + u * 32 + lane;
-                wv[u] = c < c8 ? __ldg(rp + c) : make_uint4(0u, 0u, 0u, 0u);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int c = c0 + u * 32 + lane;
-                if (c >= c8) continue;
+                if (c >= ce) continue;
                 const uint32_t ww[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
                 float f[8];
 #pragma unroll
@@ -81,10 +100,29 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
                 }
             }
         }
+        requested = false;
 #pragma unroll
-        for (int b = 0; b < NB; b++) {
-            float v = fk_warp_sum(acc[b]);                   // xor butterfly: the same order on every run
-            if (lane == 0 && b < batch) {
+        for (int b = 0; b < NB; b++) acc[b] = fk_warp_sum(acc[b]);   // xor butterfly: the same order on every run
+        if (S > 1) {
+            if (lane == 0)
+#pragma unroll
+                for (int b = 0; b < NB; b++) part[warp][b] = acc[b];
+            __syncthreads();
+            if (prt == 0)
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    float v = part[warp][b];
+#pragma unroll
+                    for (int s2 = 1; s2 < S; s2++) v += part[warp + s2][b];
+                    acc[b] = v;
+                }
+            __syncthreads();
+        }
+        if (prt == 0 && lane == 0 && row < rows) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                if (b >= batch) break;
+                float v = acc[b];
                 if (bias) v += bias[row];
                 float* dst = y + (size_t)b * rows + row;
                 *dst = accumulate ? *dst + v : v;
@@ -103,18 +141,33 @@ __global__ void add_bias_kernel(float* __restrict__ y, const float* __restrict__
 
 }  // namespace
 
-template <int NB>
-static int launch_bf16(fk_ctx* ctx, cudaStream_t st, int blocks, const uint16_t* wp, size_t row_elems, const float* x, int x_ld, float* y, int rows,
+template <int NB, int S, int U>
+static int launch_bf16(fk_ctx* ctx, cudaStream_t st, const uint16_t* wp, size_t row_elems, const float* x, int x_ld, float* y, int rows,
                        int cols, int batch, const float* norm_w, float eps, const float* bias, int accumulate) {
+    constexpr int RPB = BF_WARPS / S;
+    int blocks = ctx->sm_count * 4;                          // what is resident at once at 64 registers a thread
+    const int need = (rows + RPB - 1) / RPB;
+    if (blocks > need) blocks = need;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(BF_THREADS);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     if (norm_w) {
         const size_t smem = (size_t)NB * cols * sizeof(float);
         if (smem > 200 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): a fused norm over %d rows of %d columns does not fit shared memory", NB, cols);
-        if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<NB, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_LAUNCH);
-        gemv_bf16_kernel<NB, true><<<blocks, BF_THREADS, smem, st>>>(wp, row_elems, x, x_ld, y, rows, cols, batch, norm_w, eps, bias, accumulate);
+        auto kern = gemv_bf16_kernel<NB, true, S, U>;
+        if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_LAUNCH);
+        cfg.dynamicSmemBytes = smem;
+        FK_CUDA(cudaLaunchKernelEx(&cfg, kern, wp, row_elems, x, x_ld, y, rows, cols, batch, norm_w, eps, bias, accumulate), FK_LAUNCH);
     } else {
-        gemv_bf16_kernel<NB, false><<<blocks, BF_THREADS, 0, st>>>(wp, row_elems, x, x_ld, y, rows, cols, batch, nullptr, 0.0f, bias, accumulate);
+        auto kern = gemv_bf16_kernel<NB, false, S, U>;
+        FK_CUDA(cudaLaunchKernelEx(&cfg, kern, wp, row_elems, x, x_ld, y, rows, cols, batch, (const float*)nullptr, 0.0f, bias, accumulate), FK_LAUNCH);
     }
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }
@@ -124,14 +177,17 @@ int fk_gemv_bf16_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, int mat, cons
     if (w->cols & 7) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): %d columns is not a multiple of 8", w->cols);
     const uint16_t* wp = (const uint16_t*)(w->dev + (size_t)mat * w->mat_stride + w->plane_off[0]);
     const size_t row_elems = w->plane_stride[0] / 2;
-    int blocks = ctx->sm_count * 8;
-    const int need = (w->rows + BF_WARPS - 1) / BF_WARPS;
-    if (blocks > need) blocks = need;
     if (x_ld == 0) x_ld = w->cols;
-    if (batch <= 1) return launch_bf16<1>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
-    if (batch <= 2) return launch_bf16<2>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
-    if (batch <= 4) return launch_bf16<4>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
-    return launch_bf16<8>(ctx, st, blocks, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate);
+    // a matrix with fewer rows than the device holds warps: two warps a row, so that every SM has loads in flight
+    const bool split = w->rows < ctx->sm_count * 48 && w->cols >= 1024;
+#define FK_BF16_GO(NB_, S_, U_) \
+    return launch_bf16<NB_, S_, U_>(ctx, st, wp, row_elems, x_dev, x_ld, y_dev, w->rows, w->cols, batch, norm_w, norm_eps, bias, accumulate)
+    if (batch <= 1) { if (split) FK_BF16_GO(1, 2, 8); FK_BF16_GO(1, 1, 8); }
+    if (batch <= 2) { if (split) FK_BF16_GO(2, 2, 8); FK_BF16_GO(2, 1, 8); }
+    if (batch <= 4) { if (split) FK_BF16_GO(4, 2, 4); FK_BF16_GO(4, 1, 4); }
+    if (split) FK_BF16_GO(8, 2, 4);
+    FK_BF16_GO(8, 1, 4);
+#undef FK_BF16_GO
 }
 
 // gpt-oss adds a bias to q, k, v and the attention output, to the router logits and to every expert projection

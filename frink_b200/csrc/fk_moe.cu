@@ -109,11 +109,35 @@ __global__ void router_route_kernel(const float* __restrict__ w, const float* __
                                     float* __restrict__ w_out, unsigned* __restrict__ cnt) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
+    // The sum of a lane runs over i = lane, lane + 32, ... in that order (the order the separate logits kernel uses);
+    // the loads of RU steps go out together, so a row of a few thousand columns costs a few memory round trips, not
+    // one per step.  The router's weights are constants: the first steps' are requested before the wait for the
+    // kernel that writes x (this grid may start while that kernel still runs).
+    constexpr int RU = 16;
+    const float* wr = w + (size_t)(row < rows ? row : 0) * cols;
+    const float* xt = x + (size_t)blockIdx.y * cols;
+    float wa[RU];
+#pragma unroll
+    for (int u = 0; u < RU; u++) {
+        const int i = lane + 32 * u;
+        wa[u] = row < rows && i < cols ? __ldg(wr + i) : 0.0f;
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (row < rows) {
-        const float* wr = w + (size_t)row * cols;
-        const float* xt = x + (size_t)blockIdx.y * cols;
         float acc = 0.0f;
-        for (int i = lane; i < cols; i += 32) acc += wr[i] * xt[i];
+        for (int i0 = lane; i0 < cols; i0 += 32 * RU) {
+            float xa[RU];
+#pragma unroll
+            for (int u = 0; u < RU; u++) {
+                const int i = i0 + 32 * u;
+                if (i0 != lane) wa[u] = i < cols ? __ldg(wr + i) : 0.0f;
+                xa[u] = i < cols ? xt[i] : 0.0f;
+            }
+#pragma unroll
+            for (int u = 0; u < RU; u++)
+                if (i0 + 32 * u < cols) acc += wa[u] * xa[u];
+        }
         acc = fk_warp_sum(acc);
         if (lane == 0) logits[(size_t)blockIdx.y * rows + row] = acc;
     }
@@ -386,9 +410,17 @@ FK_EXPORT int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev
     FkDeviceGuard g(ctx->device);
     dim3 grid((n_experts + 7) / 8, batch);
     FK_CARVEOUT(router_route_kernel);
-    router_route_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(router_dev, x_dev, logits_dev, n_experts, cols, bias_dev, k, mode, batch, ids_dev, w_dev,
-                                                                ctx->argmax_cnt + 64);
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    FK_CUDA(cudaLaunchKernelEx(&cfg, router_route_kernel, router_dev, x_dev, logits_dev, n_experts, cols, bias_dev, k, mode, batch, ids_dev, w_dev,
+                               (unsigned*)(ctx->argmax_cnt + 64)), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }
