@@ -193,6 +193,21 @@ extern "C" {
         bias_dev: *const f32,
         y_dev: *mut f32,
     ) -> c_int;
+    pub fn fk_gemv_multi_gate_up(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        gate: FkWeight,
+        up: FkWeight,
+        ids_dev: *const c_int,
+        k: c_int,
+        x_dev: *const f32,
+        x_stride: c_int,
+        norm_weight_dev: *const f32,
+        norm_eps: f32,
+        gate_bias_dev: *const f32,
+        up_bias_dev: *const f32,
+        y_dev: *mut f32,
+    ) -> c_int;
     pub fn fk_gemv_isums(
         ctx: *mut FkCtx,
         stream: *mut c_void,
@@ -408,6 +423,29 @@ extern "C" {
         k: c_int,
         mode: c_int,
         act: c_int,
+        x_dev: *const f32,
+        batch: c_int,
+        out_dev: *mut f32,
+        accumulate: c_int,
+        workspace_dev: *mut c_void,
+        workspace_bytes: usize,
+    ) -> c_int;
+    pub fn fk_moe_layer_normed(
+        ctx: *mut FkCtx,
+        stream: *mut c_void,
+        router_dev: *const f32,
+        router_bias_dev: *const f32,
+        gate: FkWeight,
+        up: FkWeight,
+        down: FkWeight,
+        gate_bias_dev: *const f32,
+        up_bias_dev: *const f32,
+        down_bias_dev: *const f32,
+        k: c_int,
+        mode: c_int,
+        act: c_int,
+        norm_weight_dev: *const f32,
+        norm_eps: f32,
         x_dev: *const f32,
         batch: c_int,
         out_dev: *mut f32,

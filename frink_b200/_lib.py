@@ -35,10 +35,12 @@ SYMBOLS = {
     "fk_gemv_multi_glu": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
     "fk_gemv_biased": (_I, [_P, _P, _P, _I, _P, _I, _I, _P, _P, C.c_float, _P, _I]),
     "fk_gemv_multi_biased": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P]),
+    "fk_gemv_multi_gate_up": (_I, [_P, _P, _P, _P, _P, _I, _P, _I, _P, C.c_float, _P, _P, _P]),
     "fk_gemv_multi_active": (_I, [_P, _P, _P, _P, _I, _P, _I, _P, _P]),
     "fk_moe_layer_workspace": (_SZ, [_I, _I, _I, _I, _I]),
     "fk_moe_layer": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _I, _P, _SZ]),
     "fk_moe_layer_biased": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _I, _P, _SZ]),
+    "fk_moe_layer_normed": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P, C.c_float, _P, _I, _P, _I, _P, _SZ]),
     "fk_moe_local_pairs": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P, _P]),
     "fk_moe_local_slots": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, _P]),
     "fk_moe_localize": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P]),

@@ -128,6 +128,10 @@ struct FkGemvFused {
     int pair_glu;                   // rows are (gate, up) pairs: write act(gate) * up, rows / 2 outputs
     const struct FkArChannel* ar;   // sum the results over the ranks of this channel in the epilogue (null: no)
     const float* bias = nullptr;    // [rows] added to the result; with ids: [n_mats][rows], slot j gets the row of matrix ids[j]
+    // a second stack of matrices of the same geometry (indexed form only): the launch has 2 k slots, slot k + j multiplies
+    // matrix ids[j] of w2 with slot j's input (bias2 its bias table) -- gate and up of the chosen experts in one launch
+    fk_weight w2 = nullptr;
+    const float* bias2 = nullptr;
 };
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,

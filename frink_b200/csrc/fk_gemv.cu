@@ -69,6 +69,9 @@ struct GemvArgs {
     int ar_on;             // the epilogue sums the results over the ranks of `ar` (element index: b * rows + row)
     FkArChannel ar;
     const float* bias;     // added to the finished dot products (before the gated activation of pair_glu): [rows], or with ids [n_mats][rows]
+    const uint8_t* w2;     // indexed form: slots >= split multiply matrix ids[slot - split] of this second stack (same geometry) with
+    int split;             //   the input of slot - split; bias2 is their bias table
+    const float* bias2;
     // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
     int q_lp;              // row pairs a warp tile spans (32, 16 or 8; the rest of the lanes span super-blocks)
     int q_sc_off, q_part_off, q_ring_off, q_bar_off;
@@ -454,9 +457,12 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
     const bool dyn = a.ids != nullptr || a.n_active != nullptr;
     if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (a.n_active && slot >= *a.n_active) return;
-    const int mat = a.ids ? a.ids[slot] : a.mat;
-    const uint8_t* wb = a.w + (size_t)mat * a.mat_stride;
-    const float* x = a.x + (size_t)slot * a.x_stride;
+    const bool second = a.w2 != nullptr && slot >= a.split;          // gate and up in one launch: the up half of the slots
+    const int in_slot = second ? slot - a.split : slot;
+    const int mat = a.ids ? a.ids[in_slot] : a.mat;
+    const uint8_t* wb = (second ? a.w2 : a.w) + (size_t)mat * a.mat_stride;
+    const float* x = a.x + (size_t)in_slot * a.x_stride;
+    const float* bias = second ? a.bias2 : a.bias;
     float* y = a.y + (size_t)slot * a.batch * rows;
 
     // ---- this warp's ring: stages, then one mbarrier per stage
@@ -717,11 +723,11 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
                     done[r][b] = v;
                 }
             const bool writer = (lane & 15) == 0 && (KIND == FK_Q4_K || lane == 0);
-            if (a.bias && writer) {
+            if (bias && writer) {
 #pragma unroll
                 for (int r = 0; r < LR; r++) {
                     const int row = row0 + hw * LR + r;
-                    const float bv = row < rows ? a.bias[(a.ids ? (size_t)mat * rows : 0) + row] : 0.0f;
+                    const float bv = row < rows ? bias[(a.ids ? (size_t)mat * rows : 0) + row] : 0.0f;
 #pragma unroll
                     for (int b = 0; b < NB; b++) done[r][b] += bv;
                 }
@@ -1729,6 +1735,11 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
         a.pair_glu = fused->pair_glu;
         if (fused->x_ld) a.x_ld = fused->x_ld;
         a.bias = fused->bias;
+        if (fused->w2) {
+            a.w2 = fused->w2->dev;
+            a.split = slots / 2;
+            a.bias2 = fused->bias2;
+        }
         if (fused->ar) {
             a.ar_on = 1;
             a.ar = *fused->ar;
@@ -1904,6 +1915,33 @@ FK_EXPORT int fk_gemv_multi_biased(fk_ctx* ctx, void* stream, fk_weight w, const
     FkGemvFused f{nullptr, 0.0f, up_dev, glu_act, 0, 0, 0, nullptr};
     f.bias = bias_dev;
     return fk_gemv_launch(ctx, (cudaStream_t)stream, w, ids_dev, 0, k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, &f);
+}
+
+// gate and up of the chosen experts in ONE launch of 2 k slots (they read the same input and have the same shape):
+//   y[j]     = gate[ids[j]] in_j (+ gate_bias[ids[j]])        j < k
+//   y[k + j] = up[ids[j]]   in_j (+ up_bias[ids[j]])
+// in_j = x[j], or rmsnorm(x[j]) * norm_weight when a norm weight is given (the layer's norm folded into the matvec).
+FK_EXPORT int fk_gemv_multi_gate_up(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
+                                    int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
+                                    const float* up_bias_dev, float* y_dev) {
+    if (!ctx || !gate || !up || !ids_dev || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_multi_gate_up: null argument");
+    if (gate->kind != up->kind || gate->rows != up->rows || gate->cols != up->cols || gate->n_mats != up->n_mats || gate->mat_stride != up->mat_stride)
+        return fk_fail(FK_INVALID, "gemv_multi_gate_up: gate and up must be stacks of the same kind and shape");
+    for (int i = 0; i < 4; i++)
+        if (gate->plane_off[i] != up->plane_off[i] || gate->plane_stride[i] != up->plane_stride[i])
+            return fk_fail(FK_INVALID, "gemv_multi_gate_up: gate and up are laid out differently");
+    if (gate->kind == FK_BF16 || gate->kind == FK_Q5_K) return fk_fail(FK_UNSUPPORTED, "gemv_multi_gate_up: kind %d has no indexed form", gate->kind);
+    if ((gate_bias_dev == nullptr) != (up_bias_dev == nullptr)) return fk_fail(FK_INVALID, "gemv_multi_gate_up: the two bias tables come together");
+    if (k < 1 || 2 * k > 65535) return fk_fail(FK_INVALID, "gemv_multi_gate_up: k=%d", k);
+    if (x_stride != 0 && x_stride < gate->cols) return fk_fail(FK_INVALID, "gemv_multi_gate_up: x_stride %d < cols %d", x_stride, gate->cols);
+    if (((uintptr_t)x_dev & 15) || ((uintptr_t)norm_weight_dev & 15) || (x_stride & 3))
+        return fk_fail(FK_INVALID, "gemv_multi_gate_up: inputs must be 16-byte aligned and x_stride a multiple of 4");
+    FkDeviceGuard g(ctx->device);
+    FkGemvFused f{norm_weight_dev, norm_eps, nullptr, 0, 0, 0, 0, nullptr};
+    f.bias = gate_bias_dev;
+    f.w2 = up;
+    f.bias2 = up_bias_dev;
+    return fk_gemv_launch(ctx, (cudaStream_t)stream, gate, ids_dev, 0, 2 * k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, &f);
 }
 
 FK_EXPORT int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,

@@ -35,11 +35,12 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
     const int cb = prt * cpp, ce = cb + cpp < c8 ? cb + cpp : c8;
     uint4 wv[U];
     auto request = [&](int row, int c0) {
-        const uint4* rp = (const uint4*)(w + (size_t)row * row_elems);
+        // every load unconditional, on a clamped address (what lies past the row's end is not used): they go out together
+        const uint4* rp = (const uint4*)(w + (size_t)(row < rows ? row : rows - 1) * row_elems);
 #pragma unroll
         for (int u = 0; u < U; u++) {
             const int c = c0 + u * 32 + lane;
-            wv[u] = row < rows && c < ce ? __ldg(rp + c) : make_uint4(0u, 0u, 0u, 0u);
+            wv[u] = __ldg(rp + (c < ce ? c : 0));
         }
     };
     int rbase = blockIdx.x * RPB;

@@ -106,7 +106,7 @@ __global__ void router_logits_kernel(const float* __restrict__ w, const float* _
 // of the context, rewound by that block) routes every token, a warp per token.
 __global__ void router_route_kernel(const float* __restrict__ w, const float* __restrict__ x, float* __restrict__ logits, int rows, int cols,
                                     const float* __restrict__ bias, int k, int mode, int batch, int* __restrict__ ids_out,
-                                    float* __restrict__ w_out, unsigned* __restrict__ cnt) {
+                                    float* __restrict__ w_out, unsigned* __restrict__ cnt, const float* __restrict__ norm_w, float norm_eps) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     // The sum of a lane runs over i = lane, lane + 32, ... in that order (the order the separate logits kernel uses);
@@ -120,19 +120,53 @@ __global__ void router_route_kernel(const float* __restrict__ w, const float* __
 #pragma unroll
     for (int u = 0; u < RU; u++) {
         const int i = lane + 32 * u;
-        wa[u] = row < rows && i < cols ? __ldg(wr + i) : 0.0f;
+        wa[u] = __ldg(wr + (i < cols ? i : 0));       // (every load unconditional, on a clamped index: they go out together)
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    // norm_w: x is the residual stream and the router reads rmsnorm(x) * norm_w -- the values the separate norm launch
+    // writes (squares in f32, summed in f64, the mean rounded to f32; element = x * scale * weight), formed on the fly
+    float scale = 1.0f;
+    if (norm_w) {
+        __shared__ double sq_part[32];
+        double sq = 0.0;
+        for (int i0 = threadIdx.x; i0 < cols; i0 += 8 * blockDim.x) {     // eight loads in flight a thread
+            float xv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int i = i0 + u * blockDim.x;
+                xv[u] = xt[i < cols ? i : 0];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++)
+                if (i0 + u * (int)blockDim.x < cols) sq += (double)(xv[u] * xv[u]);
+        }
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (lane == 0) sq_part[threadIdx.x >> 5] = sq;
+        __syncthreads();
+        double t = 0.0;
+        for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += sq_part[i];
+        scale = 1.0f / sqrtf((float)(t / (double)cols) + norm_eps);
+    }
     if (row < rows) {
         float acc = 0.0f;
         for (int i0 = lane; i0 < cols; i0 += 32 * RU) {
-            float xa[RU];
+            float xa[RU], na[RU];
 #pragma unroll
             for (int u = 0; u < RU; u++) {
                 const int i = i0 + 32 * u;
-                if (i0 != lane) wa[u] = i < cols ? __ldg(wr + i) : 0.0f;
-                xa[u] = i < cols ? xt[i] : 0.0f;
+                const int ic = i < cols ? i : 0;
+                if (i0 != lane) wa[u] = __ldg(wr + ic);
+                xa[u] = xt[ic];
+            }
+            if (norm_w) {                                                 // (one test a trip, the loads of the trip together)
+#pragma unroll
+                for (int u = 0; u < RU; u++) {
+                    const int i = i0 + 32 * u;
+                    na[u] = __ldg(norm_w + (i < cols ? i : 0));
+                }
+#pragma unroll
+                for (int u = 0; u < RU; u++) xa[u] = xa[u] * scale * na[u];
             }
 #pragma unroll
             for (int u = 0; u < RU; u++)
@@ -401,8 +435,9 @@ FK_EXPORT int fk_router_logits(fk_ctx* ctx, void* stream, const float* router_de
     return FK_OK;
 }
 
-FK_EXPORT int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts, int cols, int batch,
-                              const float* bias_dev, int k, int mode, float* logits_dev, int* ids_dev, float* w_dev) {
+static int router_route_launch(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts, int cols, int batch,
+                               const float* bias_dev, int k, int mode, float* logits_dev, int* ids_dev, float* w_dev, const float* norm_w,
+                               float norm_eps) {
     if (!ctx || !router_dev || !x_dev || !logits_dev || !ids_dev || !w_dev) return fk_fail(FK_INVALID, "router_route: null argument");
     if (n_experts < 1 || n_experts > 32 * TOPK_PER_LANE) return fk_fail(FK_UNSUPPORTED, "router_route: %d experts (limit %d)", n_experts, 32 * TOPK_PER_LANE);
     if (k < 1 || k > TOPK_MAX_K || k > n_experts) return fk_fail(FK_UNSUPPORTED, "router_route: k=%d (limit %d, experts %d)", k, TOPK_MAX_K, n_experts);
@@ -420,9 +455,14 @@ FK_EXPORT int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     FK_CUDA(cudaLaunchKernelEx(&cfg, router_route_kernel, router_dev, x_dev, logits_dev, n_experts, cols, bias_dev, k, mode, batch, ids_dev, w_dev,
-                               (unsigned*)(ctx->argmax_cnt + 64)), FK_LAUNCH);
+                               (unsigned*)(ctx->argmax_cnt + 64), norm_w, norm_eps), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
+}
+
+FK_EXPORT int fk_router_route(fk_ctx* ctx, void* stream, const float* router_dev, const float* x_dev, int n_experts, int cols, int batch,
+                              const float* bias_dev, int k, int mode, float* logits_dev, int* ids_dev, float* w_dev) {
+    return router_route_launch(ctx, stream, router_dev, x_dev, n_experts, cols, batch, bias_dev, k, mode, logits_dev, ids_dev, w_dev, nullptr, 0.0f);
 }
 
 FK_EXPORT int fk_moe_permute(fk_ctx* ctx, void* stream, const int* ids_dev, int pairs, int k, int n_experts,
@@ -492,8 +532,8 @@ MoeWs moe_ws(int n_experts, int k, int hidden, int ffn, int batch) {
     m.gather = take(pairs * 4);
     m.pair_of = take(pairs * 4);
     m.xr = take(batch <= 8 && batch > 1 ? pairs * hidden * 4 : 0);
-    m.g = take(pairs * ffn * 4);
-    m.u = take(pairs * ffn * 4);
+    m.g = take(2 * pairs * ffn * 4);                 // gate rows, then the up rows directly behind them (one launch may write both)
+    m.u = m.g + pairs * ffn * 4;
     m.y = take(pairs * hidden * 4);
     m.total = off;
     return m;
@@ -511,7 +551,8 @@ FK_EXPORT size_t fk_moe_layer_workspace(int n_experts, int k, int hidden, int ff
 // then the weighted combine in routing order, written to out_dev or added into it.
 static int moe_layer_impl(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
                           fk_weight down, const float* gate_b, const float* up_b, const float* down_b, int k, int mode, int act, const float* x_dev,
-                          int batch, float* out_dev, int accumulate, void* workspace_dev, size_t workspace_bytes) {
+                          int batch, float* out_dev, int accumulate, void* workspace_dev, size_t workspace_bytes,
+                          const float* norm_w = nullptr, float norm_eps = 0.0f) {
     if (!ctx || !router_dev || !gate || !up || !down || !x_dev || !out_dev || !workspace_dev) return fk_fail(FK_INVALID, "moe_layer: null argument");
     const int E = gate->n_mats, hidden = gate->cols, ffn = gate->rows;
     if (up->n_mats != E || down->n_mats != E || up->rows != ffn || up->cols != hidden || down->rows != hidden || down->cols != ffn)
@@ -529,8 +570,9 @@ static int moe_layer_impl(fk_ctx* ctx, void* stream, const float* router_dev, co
     const int pairs = batch * k;
     int rc;
     auto combine = accumulate ? fk_moe_combine_add : fk_moe_combine;
+    if (norm_w && batch > 8) return fk_fail(FK_UNSUPPORTED, "moe_layer_normed: the norm is folded into the decode form only (batch <= 8), got %d rows", batch);
     if (batch <= 8) {
-        if ((rc = fk_router_route(ctx, stream, router_dev, x_dev, E, hidden, batch, router_bias_dev, k, mode, logits, ids, w))) return rc;
+        if ((rc = router_route_launch(ctx, stream, router_dev, x_dev, E, hidden, batch, router_bias_dev, k, mode, logits, ids, w, norm_w, norm_eps))) return rc;
         const float* xin = x_dev;
         int x_stride = 0;
         if (batch > 1) {
@@ -544,6 +586,16 @@ static int moe_layer_impl(fk_ctx* ctx, void* stream, const float* router_dev, co
             ctx->launches++;
             xin = xr;
             x_stride = hidden;
+        }
+        if (norm_w) {
+            // x is the residual stream: the norm rides in the router's and the matvec's prologue, and gate and up (same
+            // input, same shape) are the two halves of ONE launch of 2 * pairs slots -- four launches for the layer
+            if (gate->kind == FK_BF16 || gate->kind == FK_Q5_K) return fk_fail(FK_UNSUPPORTED, "moe_layer_normed: kind %d has no indexed form", gate->kind);
+            if ((rc = fk_gemv_multi_gate_up(ctx, stream, gate, up, ids, pairs, xin, x_stride, norm_w, norm_eps, gate_b, up_b, g))) return rc;
+            if (down_b) rc = fk_gemv_multi_biased(ctx, stream, down, ids, pairs, g, u, ffn, act, down_b, y);
+            else rc = fk_gemv_multi_glu(ctx, stream, down, ids, pairs, g, u, ffn, act, y, nullptr);
+            if (rc) return rc;
+            return combine(ctx, stream, y, nullptr, w, batch, k, hidden, out_dev);
         }
         if (gate_b) {
             // every slot's bias row is added by the lane that finishes the row: still three launches
@@ -587,6 +639,20 @@ FK_EXPORT int fk_moe_layer(fk_ctx* ctx, void* stream, const float* router_dev, c
                            void* workspace_dev, size_t workspace_bytes) {
     return moe_layer_impl(ctx, stream, router_dev, router_bias_dev, gate, up, down, nullptr, nullptr, nullptr, k, mode, act, x_dev, batch, out_dev,
                           accumulate, workspace_dev, workspace_bytes);
+}
+
+// The decode form of the routed layer on the RESIDUAL stream: x_dev is un-normalized, the layer's RMSNorm (weight
+// norm_weight_dev) is folded into the router and into the gate / up launch, which is one launch for both projections.
+// Bias tables are optional (all three or none).  batch <= 8 only.
+FK_EXPORT int fk_moe_layer_normed(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                                  fk_weight down, const float* gate_bias_dev, const float* up_bias_dev, const float* down_bias_dev, int k, int mode,
+                                  int act, const float* norm_weight_dev, float norm_eps, const float* x_dev, int batch, float* out_dev,
+                                  int accumulate, void* workspace_dev, size_t workspace_bytes) {
+    if (!norm_weight_dev) return fk_fail(FK_INVALID, "moe_layer_normed: null norm weight");
+    const int nb = (gate_bias_dev != nullptr) + (up_bias_dev != nullptr) + (down_bias_dev != nullptr);
+    if (nb != 0 && nb != 3) return fk_fail(FK_INVALID, "moe_layer_normed: the three bias tables come together");
+    return moe_layer_impl(ctx, stream, router_dev, router_bias_dev, gate, up, down, gate_bias_dev, up_bias_dev, down_bias_dev, k, mode, act, x_dev,
+                          batch, out_dev, accumulate, workspace_dev, workspace_bytes, norm_weight_dev, norm_eps);
 }
 
 // gpt-oss's routed layer (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060): fk_moe_layer whose expert projections

@@ -424,7 +424,10 @@ class Decoder:
                 into_residual(L["wo"], L["wo"].row, is_padded=True)
             else:
                 into_residual(L["wo"], a, bias=L.get("bo"))
-            if "moe_b" in L:
+            if ("moe" in L or "moe_b" in L) and hasattr(ops, "moe_layer"):
+                # the whole routed layer on the residual stream: the norm rides in the router and in the gate / up launch
+                ops.moe_layer(L["moe"], x, out=x, accumulate=True, biases=L.get("moe_b"), norm=(L["ffn_norm"], cfg.eps))
+            elif "moe_b" in L:
                 h2 = ops.rmsnorm(x, L["ffn_norm"], cfg.eps)
                 run_device_routed_oai(L["moe"], L["moe_b"], h2, ops, residual=x)
             elif "moe" in L:

@@ -219,10 +219,26 @@ def add_bias_(y, bias, ids=None):
     return y
 
 
-def moe_layer(layer, x, out=None, accumulate=False, biases=None):
+def gemv_multi_gate_up(gate, up, ids, x, norm_weight=None, eps=0.0, gate_bias=None, up_bias=None, out=None):
+    """gate and up of the chosen experts in one launch: out [2 k, rows], rows j < k = gate[ids[j]] in_j, rows k + j =
+    up[ids[j]] in_j (in_j = x[j] or the one shared x; with norm_weight, its RMSNorm), plus the experts' bias rows."""
+    ids, x = _i32(ids), _f32(x)
+    k = ids.numel()
+    stride = 0 if x.dim() == 1 else x.stride(0)
+    y = out if out is not None else torch.empty((2 * k, gate.rows), dtype=torch.float32, device=x.device)
+    check(lib().fk_gemv_multi_gate_up(gate._ctx, _stream(), gate.handle, up.handle, _ptr(ids), k, _ptr(x), stride,
+                                      _ptr(_f32(norm_weight)) if norm_weight is not None else None, float(eps),
+                                      _ptr(_f32(gate_bias)) if gate_bias is not None else None,
+                                      _ptr(_f32(up_bias)) if up_bias is not None else None, _ptr(y)))
+    return y
+
+
+def moe_layer(layer, x, out=None, accumulate=False, biases=None, norm=None):
     """The routed layer in one call (`fk_moe_layer`): `layer` carries router, router_bias, gate / up / down (stacked
     `Weights`), k, mode, act; x [batch, hidden] or [hidden].  The workspace is kept on the layer object, per batch size.
-    biases = (gate_b, up_b, down_b), each [n_experts, rows]: gpt-oss's form (`fk_moe_layer_biased`)."""
+    biases = (gate_b, up_b, down_b), each [n_experts, rows]: gpt-oss's form (`fk_moe_layer_biased`).
+    norm = (weight, eps): x is the un-normalized residual stream (at most 8 rows) and the layer's RMSNorm is folded into
+    the router and the gate / up launch (`fk_moe_layer_normed`: four launches)."""
     x2 = _f32(x) if x.dim() == 2 else _f32(x)[None]
     batch = x2.shape[0]
     g = layer.gate
@@ -236,6 +252,14 @@ def moe_layer(layer, x, out=None, accumulate=False, biases=None):
     o = out if out is not None else torch.empty((batch, g.cols), dtype=torch.float32, device=x2.device)
     o2 = o if o.dim() == 2 else o[None]
     rb = _ptr(_f32(layer.router_bias)) if layer.router_bias is not None else None
+    if norm is not None:
+        gb, ub, db = (_f32(t) for t in biases) if biases is not None else (None, None, None)
+        check(lib().fk_moe_layer_normed(g._ctx, _stream(), _ptr(_f32(layer.router)), rb, g.handle, layer.up.handle, layer.down.handle,
+                                        _ptr(gb) if gb is not None else None, _ptr(ub) if ub is not None else None,
+                                        _ptr(db) if db is not None else None, layer.k, int(layer.mode), int(layer.act),
+                                        _ptr(_f32(norm[0])), float(norm[1]), _ptr(x2), batch, _ptr(o2),
+                                        int(bool(accumulate)), C.c_void_p(base), buf.numel() - (base - buf.data_ptr())))
+        return o if x.dim() == 2 or out is not None else o[0]
     if biases is not None:
         gb, ub, db = (_f32(t) for t in biases)
         assert gb.shape == (g.n_mats, g.rows) and ub.shape == gb.shape and db.shape == (g.n_mats, g.cols)

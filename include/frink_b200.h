@@ -156,6 +156,14 @@ int fk_gemv_biased(fk_ctx* ctx, void* stream, fk_weight w, int mat, const float*
 int fk_gemv_multi_biased(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev, const float* up_dev,
                          int x_stride, int glu_act, const float* bias_dev, float* y_dev);
 
+/* gate and up of the chosen experts in one launch of 2 k slots (same input, same shape; the reference shares one
+ * quantized input between them, crates/frink-cuda/src/dp4a_launch.rs:56-62): y_dev [2 k][rows], rows j < k from
+ * `gate`, rows k + j from `up`, both of expert ids_dev[j] on input j.  norm_weight_dev (optional): the input is
+ * rmsnorm(x[j]) * norm_weight; the bias tables ([n_mats][rows]) are optional and come together. */
+int fk_gemv_multi_gate_up(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
+                          int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
+                          const float* up_bias_dev, float* y_dev);
+
 /* Test hook (the reference's twins expose the same integers,
  * crates/frink-cuda/src/dp4a_twin.rs:142-231): the exact int32 dot of every
  * run of 32 activations (16 for Q6_K) of every row against q8_1(x), computed
@@ -277,6 +285,15 @@ int fk_moe_layer_biased(fk_ctx* ctx, void* stream, const float* router_dev, cons
                         fk_weight down, const float* gate_bias_dev, const float* up_bias_dev, const float* down_bias_dev, int k, int mode,
                         int act, const float* x_dev, int batch, float* out_dev, int accumulate, void* workspace_dev,
                         size_t workspace_bytes);
+
+/* The decode form (batch <= 8) of the routed layer on the RESIDUAL stream: x_dev is un-normalized and the layer's
+ * RMSNorm (`rmsnorm_rows_f32`, crates/frink-cuda/src/prefill/kernels.rs:26) is folded into the router and into the
+ * gate / up launch, which is ONE indexed launch for both projections (fk_gemv_multi_gate_up): four launches a layer.
+ * Bias tables: all three or none (null).  out_dev may be x_dev with accumulate != 0 (the layer added into the stream). */
+int fk_moe_layer_normed(fk_ctx* ctx, void* stream, const float* router_dev, const float* router_bias_dev, fk_weight gate, fk_weight up,
+                        fk_weight down, const float* gate_bias_dev, const float* up_bias_dev, const float* down_bias_dev, int k, int mode,
+                        int act, const float* norm_weight_dev, float norm_eps, const float* x_dev, int batch, float* out_dev,
+                        int accumulate, void* workspace_dev, size_t workspace_bytes);
 
 /* ---- decoder glue (next-row components: enough to run a decoder and report
  * prefill / decode tokens per second; f32 throughout) -------------------------

@@ -138,3 +138,38 @@ def test_biased_routed_layer_one_call_against_the_composition_and_the_oracle():
     got = prefill.run_device_routed_oai(layer, biases, xd[:3]).cpu().numpy()
     assert rel_l2(got, want) <= 1e-3 and max_abs_over_inf(got, want) <= 2e-3
     assert device.device_error() == 0
+
+
+@pytest.mark.parametrize("kind,biased", [(fo.MXFP4, True), (fo.Q4_K, False), (fo.Q8_0, False)])
+def test_routed_layer_on_the_residual_stream_is_the_separate_launches_to_the_bit(kind, biased):
+    """fk_moe_layer_normed: the RMSNorm folded into the router and the matvec, gate and up as the two halves of one
+    launch.  The same routes and the same output bits as norm launch + fk_moe_layer(_biased), for 1, 3 and 8 rows; and
+    fk_gemv_multi_gate_up alone against the two indexed launches."""
+    from frink_b200 import device, prefill
+    n_exp, k, hidden, ffn, mode, act = 8, 2, 512, 256, 1, 1 if biased else 0
+    raws, router, layer = build_layer(kind, n_exp, hidden, ffn, k, mode, act, 1500)
+    rng = np.random.default_rng(21)
+    biases = None
+    if biased:
+        biases = tuple(torch.from_numpy(rng.standard_normal((n_exp, n)).astype(np.float32) * 0.2).cuda() for n in (ffn, ffn, hidden))
+    nw = torch.from_numpy((1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)).cuda()
+    eps = 1e-5
+    x = torch.from_numpy(rng.standard_normal((8, hidden)).astype(np.float32) * 1.7).cuda()
+    for rows in (1, 3, 8):
+        res = x[:rows].clone()
+        h = device.rmsnorm(res.clone(), nw, eps)
+        want = res + (device.moe_layer(layer, h, biases=biases) if biased else device.moe_layer(layer, h))
+        got = res.clone()
+        device.moe_layer(layer, got, out=got, accumulate=True, biases=biases, norm=(nw, eps))
+        assert torch.equal(got, want), rows
+    # the two-projection launch alone
+    ids = torch.tensor([5, 1, 5], dtype=torch.int32, device="cuda")
+    xs = x[:3].contiguous()
+    both = device.gemv_multi_gate_up(layer.gate, layer.up, ids, xs)
+    assert torch.equal(both[:3], device.gemv_multi(layer.gate, ids, xs)) and torch.equal(both[3:], device.gemv_multi(layer.up, ids, xs))
+    h3 = device.rmsnorm(xs.clone(), nw, eps)
+    both = device.gemv_multi_gate_up(layer.gate, layer.up, ids, xs, norm_weight=nw, eps=eps)
+    assert torch.equal(both[:3], device.gemv_multi(layer.gate, ids, h3)) and torch.equal(both[3:], device.gemv_multi(layer.up, ids, h3))
+    with pytest.raises(Exception):
+        device.moe_layer(layer, x.repeat(2, 1), norm=(nw, eps))        # 16 rows: the folded form is the decode form
+    assert device.device_error() == 0
