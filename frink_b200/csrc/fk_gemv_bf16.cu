@@ -48,11 +48,28 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (NORM) {
-        for (int b = 0; b < NB && b < batch; b++) {
+        constexpr int XP = 16;                               // values of a row a thread holds (rows of up to 4096 columns)
+        const bool held = cols <= BF_THREADS * XP;
+#pragma unroll 1
+        for (int b = 0; b < NB && b < batch; b++) {          // (not unrolled: one row's values in registers at a time)
             float ss = 0.0f;
-            for (int c = threadIdx.x; c < cols; c += BF_THREADS) {
-                const float v = x[(size_t)b * x_ld + c];
-                ss = fmaf(v, v, ss);
+            float xv[XP], nv[XP];
+            if (held) {
+                // the row and the norm weight are read once, every load on a clamped index so that they all go out together
+#pragma unroll
+                for (int u = 0; u < XP; u++) {
+                    const int c = threadIdx.x + u * BF_THREADS, cc = c < cols ? c : 0;
+                    xv[u] = x[(size_t)b * x_ld + cc];
+                    nv[u] = __ldg(norm_w + cc);
+                }
+#pragma unroll
+                for (int u = 0; u < XP; u++)
+                    if ((int)threadIdx.x + u * BF_THREADS < cols) ss = fmaf(xv[u], xv[u], ss);
+            } else {
+                for (int c = threadIdx.x; c < cols; c += BF_THREADS) {
+                    const float v = x[(size_t)b * x_ld + c];
+                    ss = fmaf(v, v, ss);
+                }
             }
             ss = fk_warp_sum(ss);
             if (lane == 0) red[warp] = ss;
@@ -61,7 +78,15 @@ __global__ void __launch_bounds__(BF_THREADS) gemv_bf16_kernel(const uint16_t* _
 #pragma unroll
             for (int i = 0; i < BF_WARPS; i++) tot += red[i];
             const float scale = rsqrtf(tot / (float)cols + eps);
-            for (int c = threadIdx.x; c < cols; c += BF_THREADS) xs[(size_t)b * cols + c] = x[(size_t)b * x_ld + c] * scale * norm_w[c];
+            if (held) {
+#pragma unroll
+                for (int u = 0; u < XP; u++) {
+                    const int c = threadIdx.x + u * BF_THREADS;
+                    if (c < cols) xs[(size_t)b * cols + c] = xv[u] * scale * nv[u];
+                }
+            } else {
+                for (int c = threadIdx.x; c < cols; c += BF_THREADS) xs[(size_t)b * cols + c] = x[(size_t)b * x_ld + c] * scale * norm_w[c];
+            }
             __syncthreads();
         }
     }
@@ -146,7 +171,18 @@ template <int NB, int S, int U>
 static int launch_bf16(fk_ctx* ctx, cudaStream_t st, const uint16_t* wp, size_t row_elems, const float* x, int x_ld, float* y, int rows,
                        int cols, int batch, const float* norm_w, float eps, const float* bias, int accumulate) {
     constexpr int RPB = BF_WARPS / S;
-    int blocks = ctx->sm_count * 4;                          // what is resident at once at 64 registers a thread
+    const size_t norm_smem = norm_w ? (size_t)NB * cols * sizeof(float) : 0;
+    if (norm_smem > 200 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): a fused norm over %d rows of %d columns does not fit shared memory", NB, cols);
+    // one wave: as many blocks as are resident at once (the rows are dealt out in a grid-stride loop)
+    int per_sm = 0;
+    if (norm_w) {
+        if (norm_smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(gemv_bf16_kernel<NB, true, S, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)norm_smem), FK_LAUNCH);
+        FK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_bf16_kernel<NB, true, S, U>, BF_THREADS, norm_smem), FK_LAUNCH);
+    } else {
+        FK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemv_bf16_kernel<NB, false, S, U>, BF_THREADS, 0), FK_LAUNCH);
+    }
+    if (per_sm < 1) per_sm = 1;
+    int blocks = ctx->sm_count * per_sm;
     const int need = (rows + RPB - 1) / RPB;
     if (blocks > need) blocks = need;
     cudaLaunchConfig_t cfg = {};
@@ -159,11 +195,8 @@ static int launch_bf16(fk_ctx* ctx, cudaStream_t st, const uint16_t* wp, size_t 
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     if (norm_w) {
-        const size_t smem = (size_t)NB * cols * sizeof(float);
-        if (smem > 200 * 1024) return fk_fail(FK_UNSUPPORTED, "gemv (BF16): a fused norm over %d rows of %d columns does not fit shared memory", NB, cols);
         auto kern = gemv_bf16_kernel<NB, true, S, U>;
-        if (smem > 48 * 1024) FK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), FK_LAUNCH);
-        cfg.dynamicSmemBytes = smem;
+        cfg.dynamicSmemBytes = norm_smem;
         FK_CUDA(cudaLaunchKernelEx(&cfg, kern, wp, row_elems, x, x_ld, y, rows, cols, batch, norm_w, eps, bias, accumulate), FK_LAUNCH);
     } else {
         auto kern = gemv_bf16_kernel<NB, false, S, U>;
