@@ -182,6 +182,16 @@ __device__ __forceinline__ uint32_t e2m1x2_4(uint32_t w) {
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(pos), "r"(neg), "r"(pick));
     return out;
 }
+// The same codes split by sign: the doubled magnitudes of the four codes in the low 16 bits of `w` whose sign bit is
+// CLEAR, zero bytes for the others.  The code nibble itself is the selector: its low three bits pick the magnitude, and
+// a set sign bit makes prmt replicate the picked byte's top bit -- clear for every magnitude -- over the byte, i.e. 0.
+// e2m1_pos4(w ^ 0x8888) is then the magnitudes of the NEGATIVE codes, and a dot product with the signed values is the
+// difference of two dp4a: the same integer as with e2m1x2_4, with fewer instructions per code.
+__device__ __forceinline__ uint32_t e2m1_pos4(uint32_t w) {
+    uint32_t out;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(0x03020100u), "r"(0x0C080604u), "r"(w));
+    return out;
+}
 __device__ __forceinline__ float e8m0_half(uint32_t e) {
     return __uint_as_float(e < 2 ? (0x00200000u << e) : ((e - 1u) << 23));
 }
@@ -383,17 +393,19 @@ __device__ __forceinline__ void eat(const GemvArgs& a, const Act& sm, uint32_t s
             wq = lds16(plane_at<KIND>(a, stage, r, 0) + (tl * 32 + lane) * 16);
             dw = e8m0_half(lds_u8(plane_at<KIND>(a, stage, r, 1) + tl * 32 + lane));
         }
-        uint4 va, vb;
-        va.x = e2m1x2_4(wq.x); va.y = e2m1x2_4(wq.x >> 16);
-        va.z = e2m1x2_4(wq.y); va.w = e2m1x2_4(wq.y >> 16);
-        vb.x = e2m1x2_4(wq.z); vb.y = e2m1x2_4(wq.z >> 16);
-        vb.z = e2m1x2_4(wq.w); vb.w = e2m1x2_4(wq.w >> 16);
+        // magnitudes of the positive and of the negative codes (e2m1_pos4): the block's integer dot is their difference
+        const uint4 wn = make_uint4(wq.x ^ 0x88888888u, wq.y ^ 0x88888888u, wq.z ^ 0x88888888u, wq.w ^ 0x88888888u);
+        uint4 pa, pb, na, nb;
+        pa.x = e2m1_pos4(wq.x); pa.y = e2m1_pos4(wq.x >> 16); pa.z = e2m1_pos4(wq.y); pa.w = e2m1_pos4(wq.y >> 16);
+        pb.x = e2m1_pos4(wq.z); pb.y = e2m1_pos4(wq.z >> 16); pb.z = e2m1_pos4(wq.w); pb.w = e2m1_pos4(wq.w >> 16);
+        na.x = e2m1_pos4(wn.x); na.y = e2m1_pos4(wn.x >> 16); na.z = e2m1_pos4(wn.y); na.w = e2m1_pos4(wn.y >> 16);
+        nb.x = e2m1_pos4(wn.z); nb.y = e2m1_pos4(wn.z >> 16); nb.z = e2m1_pos4(wn.w); nb.w = e2m1_pos4(wn.w >> 16);
 #pragma unroll
         for (int b = 0; b < NB; b++) {
             const int8_t* q8 = sm.q + (size_t)b * sm.cols + ks * 32;
             const int sw = 16 * ((ks >> 2) & 1);   // act_chunk<FK_MXFP4> for chunks 2 ks, 2 ks + 1
             const int4 ua = *(const int4*)(q8 + sw), ub = *(const int4*)(q8 + (16 ^ sw));
-            const int is = dp4a4(va, ua) + dp4a4(vb, ub);
+            const int is = (dp4a4(pa, ua) + dp4a4(pb, ub)) - (dp4a4(na, ua) + dp4a4(nb, ub));
             acc[b] += dw * sm.d[b * sm.nb32 + ks] * i2f(is);
             if (DUMP && b == 0 && live) a.isums[(size_t)row * sm.nb32 + kb] = is;
         }
