@@ -871,7 +871,9 @@ def extras(peak):
     cases = [("q4_k", 12, 8192, 3072, 1), ("q4_k", 12, 8192, 3072, 2), ("q4_k", 12, 8192, 3072, 4), ("q4_k", 12, 8192, 3072, 8),
              ("q6_k", 14, 8192, 3072, 8), ("q8_0", 8, 8192, 3072, 8), ("mxfp4", 39, 8192, 2880, 8), ("q6_k", 14, 8192, 3072, 1), ("q8_0", 8, 8192, 3072, 1),
              ("mxfp4", 39, 8192, 2880, 1), ("q4_k", 12, 3072, 8192, 1), ("q6_k", 14, 128256, 3072, 1), ("q4_k", 12, 65536, 8192, 1),
-             ("q5_k", 13, 8192, 3072, 1), ("q5_k", 13, 65536, 8192, 1)]
+             ("q5_k", 13, 8192, 3072, 1), ("q5_k", 13, 65536, 8192, 1),
+             # gpt-oss-20b's BF16 tensors: the merged q/k/v projection and the output head
+             ("bf16", 30, 5120, 2880, 1), ("bf16", 30, 201088, 2880, 1)]
     for name, kind, rows, cols, batch in cases:
         small = rows * cols <= 8192 * 8192
         base = fo.encode(kind, (rng.standard_normal((min(rows, 1024), cols), dtype=np.float32) * np.float32(0.02)))
