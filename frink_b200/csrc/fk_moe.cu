@@ -109,18 +109,20 @@ __global__ void router_route_kernel(const float* __restrict__ w, const float* __
                                     float* __restrict__ w_out, unsigned* __restrict__ cnt, const float* __restrict__ norm_w, float norm_eps) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    // The sum of a lane runs over i = lane, lane + 32, ... in that order (the order the separate logits kernel uses);
-    // the loads of RU steps go out together, so a row of a few thousand columns costs a few memory round trips, not
-    // one per step.  The router's weights are constants: the first steps' are requested before the wait for the
-    // kernel that writes x (this grid may start while that kernel still runs).
-    constexpr int RU = 16;
+    // The sum of a lane runs over i = lane, lane + 32, ... in that order (the order the separate logits kernel uses), so
+    // a warp walks its row alone; what can be parallel is the memory: the router's weights are constants, and a lane
+    // requests its whole share of the row (up to RU steps, 3072 columns) BEFORE the wait for the kernel that writes x --
+    // this grid may start while that kernel still runs -- on clamped indices, so that every load is unconditional and
+    // they all go out together.  x (normalized, if asked) is staged once a block in shared memory.
+    constexpr int RU = 96;
+    extern __shared__ __align__(16) float xs[];                  // [cols]
     const float* wr = w + (size_t)(row < rows ? row : 0) * cols;
     const float* xt = x + (size_t)blockIdx.y * cols;
     float wa[RU];
 #pragma unroll
     for (int u = 0; u < RU; u++) {
         const int i = lane + 32 * u;
-        wa[u] = __ldg(wr + (i < cols ? i : 0));       // (every load unconditional, on a clamped index: they go out together)
+        wa[u] = __ldg(wr + (i < cols ? i : 0));
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -148,29 +150,36 @@ __global__ void router_route_kernel(const float* __restrict__ w, const float* __
         for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += sq_part[i];
         scale = 1.0f / sqrtf((float)(t / (double)cols) + norm_eps);
     }
+    for (int i0 = threadIdx.x; i0 < cols; i0 += 8 * blockDim.x) {
+        float xv[8], nv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int i = i0 + u * blockDim.x, ic = i < cols ? i : 0;
+            xv[u] = xt[ic];
+            nv[u] = norm_w ? __ldg(norm_w + ic) : 1.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int i = i0 + u * blockDim.x;
+            if (i < cols) xs[i] = norm_w ? xv[u] * scale * nv[u] : xv[u];
+        }
+    }
+    __syncthreads();
     if (row < rows) {
         float acc = 0.0f;
         for (int i0 = lane; i0 < cols; i0 += 32 * RU) {
-            float xa[RU], na[RU];
-#pragma unroll
-            for (int u = 0; u < RU; u++) {
-                const int i = i0 + 32 * u;
-                const int ic = i < cols ? i : 0;
-                if (i0 != lane) wa[u] = __ldg(wr + ic);
-                xa[u] = xt[ic];
-            }
-            if (norm_w) {                                                 // (one test a trip, the loads of the trip together)
+            if (i0 != lane) {
 #pragma unroll
                 for (int u = 0; u < RU; u++) {
                     const int i = i0 + 32 * u;
-                    na[u] = __ldg(norm_w + (i < cols ? i : 0));
+                    wa[u] = __ldg(wr + (i < cols ? i : 0));
                 }
-#pragma unroll
-                for (int u = 0; u < RU; u++) xa[u] = xa[u] * scale * na[u];
             }
 #pragma unroll
-            for (int u = 0; u < RU; u++)
-                if (i0 + 32 * u < cols) acc += wa[u] * xa[u];
+            for (int u = 0; u < RU; u++) {
+                const int i = i0 + 32 * u;
+                if (i < cols) acc += wa[u] * xs[i];
+            }
         }
         acc = fk_warp_sum(acc);
         if (lane == 0) logits[(size_t)blockIdx.y * rows + row] = acc;
@@ -449,6 +458,10 @@ static int router_route_launch(fk_ctx* ctx, void* stream, const float* router_de
     cfg.gridDim = grid;
     cfg.blockDim = dim3(256);
     cfg.stream = (cudaStream_t)stream;
+    cfg.dynamicSmemBytes = (size_t)cols * sizeof(float);             // x (normalized), staged once a block
+    if (cfg.dynamicSmemBytes > 200 * 1024) return fk_fail(FK_UNSUPPORTED, "router_route: %d columns do not fit shared memory", cols);
+    if (cfg.dynamicSmemBytes > 48 * 1024)
+        FK_CUDA(cudaFuncSetAttribute(router_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes), FK_LAUNCH);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
