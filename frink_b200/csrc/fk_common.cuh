@@ -132,7 +132,13 @@ struct FkGemvFused {
     // matrix ids[j] of w2 with slot j's input (bias2 its bias table) -- gate and up of the chosen experts in one launch
     fk_weight w2 = nullptr;
     const float* bias2 = nullptr;
+    // indexed form: x is at least two launches old (older than the kernel that writes ids), so the activations may be
+    // prepared before the wait on that kernel
+    int x_ready = 0;
 };
+int fk_gemv_multi_gate_up_launch(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
+                                 int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
+                                 const float* up_bias_dev, float* y_dev, int x_ready);
 int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev, int mat, int slots,
                    const float* x_dev, int x_stride, int batch, float* y_dev, int32_t* isums_dev, const int* n_active_dev,
                    const FkGemvFused* fused);

@@ -72,6 +72,8 @@ struct GemvArgs {
     const uint8_t* w2;     // indexed form: slots >= split multiply matrix ids[slot - split] of this second stack (same geometry) with
     int split;             //   the input of slot - split; bias2 is their bias table
     const float* bias2;
+    int x_ready;           // indexed form: x was written before the kernel that wrote ids STARTED its work (it is two or more
+                           //   launches old), so it may be read -- and the activations prepared -- before the wait on that kernel
     // plan of the Q4_K batch 1..2 kernel (block-owned row ranges)
     int q_lp;              // row pairs a warp tile spans (32, 16 or 8; the rest of the lanes span super-blocks)
     int q_sc_off, q_part_off, q_ring_off, q_bar_off;
@@ -467,11 +469,14 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
     // previous kernel of the stream, so a launch that has one waits for that kernel before it
     // reads anything; a plain matvec waits later, with its weights already on their way.
     const bool dyn = a.ids != nullptr || a.n_active != nullptr;
-    if (dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (a.n_active && slot >= *a.n_active) return;
+    // ... unless x is older than that kernel (x_ready): then only the slot table is waited for, after the activations
+    // have been normalized and quantized -- the prologue runs while the kernel that picks the experts still does
+    const bool late = dyn && a.x_ready != 0;
+    if (dyn && !late) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (!late && a.n_active && slot >= *a.n_active) return;
     const bool second = a.w2 != nullptr && slot >= a.split;          // gate and up in one launch: the up half of the slots
     const int in_slot = second ? slot - a.split : slot;
-    const int mat = a.ids ? a.ids[in_slot] : a.mat;
+    int mat = a.ids && !late ? a.ids[in_slot] : a.mat;
     const uint8_t* wb = (second ? a.w2 : a.w) + (size_t)mat * a.mat_stride;
     const float* x = a.x + (size_t)in_slot * a.x_stride;
     const float* bias = second ? a.bias2 : a.bias;
@@ -510,7 +515,7 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
     const uint32_t f_pstride = (uint32_t)(f_p == 0 ? a.plane_stride[0] : f_p == 1 ? a.plane_stride[1] : f_p == 2 ? a.plane_stride[2] : a.plane_stride[3]);
     const uint32_t f_chunk = f_whole ? f_pstride : (uint32_t)a.trips_per_chunk * (uint32_t)trip_bytes<KIND>(f_p);
     const uint32_t f_dst = plane_at<KIND>(a, 0u, f_r, f_p);
-    const uint8_t* f_src = wb + f_poff + (size_t)f_r * f_pstride;
+    const uint8_t* f_src = wb + f_poff + (size_t)f_r * f_pstride;      // (late: set again once the slot table may be read)
     int f_stage = 0, f_kc = 0, f_pair = gwarp;
     auto fill = [&]() {
         const uint32_t stage = ring + f_stage * a.stage_bytes, bar = bars + 8 * f_stage;
@@ -562,10 +567,11 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
         load_acts(0);
     }
     const int pre = njobs < a.nstages ? njobs : a.nstages;
-    for (int q = 0; q < pre; q++) fill();
+    if (!late)
+        for (int q = 0; q < pre; q++) fill();
     TR(1, threadIdx.x == 0);
     if (!early && !dyn) asm volatile("griddepcontrol.wait;" ::: "memory");
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (!late) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     TR(2, threadIdx.x == 0);
 
     // ---- activations -> q8_1 in shared memory.  A thread takes one float4, eight
@@ -685,6 +691,16 @@ __global__ void __launch_bounds__(DP_THREADS, DP_MINB) gemv_kernel(const GemvArg
     }
     TR(10, threadIdx.x == 0);
     TR(11, threadIdx.x == DP_THREADS - 1);
+    if (late) {
+        // the activations are ready in shared memory; now the slot table, then this slot's weights
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+        if (a.n_active && slot >= *a.n_active) return;               // (the whole block: nothing is in flight yet)
+        if (a.ids) mat = __ldcg(a.ids + in_slot);
+        wb = (second ? a.w2 : a.w) + (size_t)mat * a.mat_stride;
+        f_src = wb + f_poff + (size_t)f_r * f_pstride;
+        for (int q = 0; q < pre; q++) fill();
+    }
     __syncthreads();
     TR(3, threadIdx.x == 0);
     const Act sm{sq, sd, ss, sb16, cols, nb32};
@@ -1752,6 +1768,7 @@ int fk_gemv_launch(fk_ctx* ctx, cudaStream_t st, fk_weight w, const int* ids_dev
             a.split = slots / 2;
             a.bias2 = fused->bias2;
         }
+        a.x_ready = fused->x_ready;
         if (fused->ar) {
             a.ar_on = 1;
             a.ar = *fused->ar;
@@ -1933,9 +1950,9 @@ FK_EXPORT int fk_gemv_multi_biased(fk_ctx* ctx, void* stream, fk_weight w, const
 //   y[j]     = gate[ids[j]] in_j (+ gate_bias[ids[j]])        j < k
 //   y[k + j] = up[ids[j]]   in_j (+ up_bias[ids[j]])
 // in_j = x[j], or rmsnorm(x[j]) * norm_weight when a norm weight is given (the layer's norm folded into the matvec).
-FK_EXPORT int fk_gemv_multi_gate_up(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
-                                    int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
-                                    const float* up_bias_dev, float* y_dev) {
+int fk_gemv_multi_gate_up_launch(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
+                                 int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
+                                 const float* up_bias_dev, float* y_dev, int x_ready) {
     if (!ctx || !gate || !up || !ids_dev || !x_dev || !y_dev) return fk_fail(FK_INVALID, "gemv_multi_gate_up: null argument");
     if (gate->kind != up->kind || gate->rows != up->rows || gate->cols != up->cols || gate->n_mats != up->n_mats || gate->mat_stride != up->mat_stride)
         return fk_fail(FK_INVALID, "gemv_multi_gate_up: gate and up must be stacks of the same kind and shape");
@@ -1953,7 +1970,15 @@ FK_EXPORT int fk_gemv_multi_gate_up(fk_ctx* ctx, void* stream, fk_weight gate, f
     f.bias = gate_bias_dev;
     f.w2 = up;
     f.bias2 = up_bias_dev;
+    f.x_ready = x_ready;
     return fk_gemv_launch(ctx, (cudaStream_t)stream, gate, ids_dev, 0, 2 * k, x_dev, x_stride, 1, y_dev, nullptr, nullptr, &f);
+}
+
+FK_EXPORT int fk_gemv_multi_gate_up(fk_ctx* ctx, void* stream, fk_weight gate, fk_weight up, const int* ids_dev, int k, const float* x_dev,
+                                    int x_stride, const float* norm_weight_dev, float norm_eps, const float* gate_bias_dev,
+                                    const float* up_bias_dev, float* y_dev) {
+    return fk_gemv_multi_gate_up_launch(ctx, stream, gate, up, ids_dev, k, x_dev, x_stride, norm_weight_dev, norm_eps, gate_bias_dev, up_bias_dev,
+                                        y_dev, 0);
 }
 
 FK_EXPORT int fk_gemv_multi_active(fk_ctx* ctx, void* stream, fk_weight w, const int* ids_dev, int k, const float* x_dev,

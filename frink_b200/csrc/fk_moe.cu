@@ -260,6 +260,10 @@ __global__ void glu_kernel(const float* __restrict__ gate, const float* __restri
 
 __global__ void combine_kernel(const float* __restrict__ y, const int* __restrict__ pair_of, const float* __restrict__ w,
                                int k, int n, float* __restrict__ out, int add) {
+    // launched with programmatic stream serialization: wait for the kernel that wrote y, and let the next one (a
+    // matvec that requests its weights before it waits in turn) be scheduled now
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const int t = blockIdx.y;
     if (i >= n) return;
@@ -502,6 +506,19 @@ FK_EXPORT int fk_glu(fk_ctx* ctx, void* stream, const float* gate_dev, const flo
     return FK_OK;
 }
 
+static cudaError_t launch_combine(dim3 grid, cudaStream_t st, const float* y, const int* pair_of, const float* w, int k, int n, float* out, int add) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, combine_kernel, y, pair_of, w, k, n, out, add);
+}
+
 FK_EXPORT int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, const int* pair_of_dev, const float* w_dev,
                              int batch, int k, int n, float* out_dev) {
     if (!ctx || !y_dev || !w_dev || !out_dev) return fk_fail(FK_INVALID, "moe_combine: null argument");
@@ -509,8 +526,7 @@ FK_EXPORT int fk_moe_combine(fk_ctx* ctx, void* stream, const float* y_dev, cons
     FkDeviceGuard g(ctx->device);
     dim3 grid((n + 255) / 256, batch);
     FK_CARVEOUT(combine_kernel);
-    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev, 0);
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    FK_CUDA(launch_combine(grid, (cudaStream_t)stream, y_dev, pair_of_dev, w_dev, k, n, out_dev, 0), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }
@@ -522,8 +538,7 @@ FK_EXPORT int fk_moe_combine_add(fk_ctx* ctx, void* stream, const float* y_dev, 
     FkDeviceGuard g(ctx->device);
     dim3 grid((n + 255) / 256, batch);
     FK_CARVEOUT(combine_kernel);
-    combine_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y_dev, pair_of_dev, w_dev, k, n, out_dev, 1);
-    FK_CUDA(cudaGetLastError(), FK_LAUNCH);
+    FK_CUDA(launch_combine(grid, (cudaStream_t)stream, y_dev, pair_of_dev, w_dev, k, n, out_dev, 1), FK_LAUNCH);
     ctx->launches++;
     return FK_OK;
 }
@@ -604,7 +619,11 @@ static int moe_layer_impl(fk_ctx* ctx, void* stream, const float* router_dev, co
             // x is the residual stream: the norm rides in the router's and the matvec's prologue, and gate and up (same
             // input, same shape) are the two halves of ONE launch of 2 * pairs slots -- four launches for the layer
             if (gate->kind == FK_BF16 || gate->kind == FK_Q5_K) return fk_fail(FK_UNSUPPORTED, "moe_layer_normed: kind %d has no indexed form", gate->kind);
-            if ((rc = fk_gemv_multi_gate_up(ctx, stream, gate, up, ids, pairs, xin, x_stride, norm_w, norm_eps, gate_b, up_b, g))) return rc;
+            // one row: x is the caller's residual stream, complete before the router started, so the matvec may normalize
+            // and quantize it while the router still picks the experts (several rows: x was repeated by the launch before)
+            if ((rc = fk_gemv_multi_gate_up_launch(ctx, stream, gate, up, ids, pairs, xin, x_stride, norm_w, norm_eps, gate_b, up_b, g,
+                                                   batch == 1 ? 1 : 0)))
+                return rc;
             if (down_b) rc = fk_gemv_multi_biased(ctx, stream, down, ids, pairs, g, u, ffn, act, down_b, y);
             else rc = fk_gemv_multi_glu(ctx, stream, down, ids, pairs, g, u, ffn, act, y, nullptr);
             if (rc) return rc;
