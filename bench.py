@@ -337,7 +337,7 @@ def main():
     comm = None
     if world > 1 and not args.nccl_only:
         from frink_b200.comm import Comm
-        comm = Comm(arena_bytes=512 << 20)
+        comm = Comm(arena_bytes=1 << 30)
     if not args.no_models:
         for name in ("llama3b", "qwen3moe", "gptoss"):
             r_ = run_model(name, rank, world, comm=comm)
@@ -579,8 +579,6 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     import torch.distributed as dist
     from frink_b200 import device
     from frink_b200.decoder import Decoder
-    if name == "gptoss" and world > 1:
-        return {"model": name, "n_gpus": world, "unavailable": "the gpt-oss layer form runs on one GPU here (its biases are not sharded)"} if rank == 0 else None
     cfg, layers, tok, tok_kind, out_norm, head = synth_model(name, n_layers)
     # dense models: tensor parallel; routed models: attention replicated, experts spread over the ranks
     # (their few KV heads do not divide by 8)
@@ -705,7 +703,7 @@ def model_bench(args, rank, world, local):
     comm = None
     if world > 1 and not args.nccl_only:
         from frink_b200.comm import Comm
-        comm = Comm(arena_bytes=512 << 20)
+        comm = Comm(arena_bytes=1 << 30)
     res = run_model(args.model, rank, world, args.layers, not args.no_tp_graph, comm, args.profile_region)
     if rank == 0:
         res["metric"] = "pp512_tg128_tok_s"

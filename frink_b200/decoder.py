@@ -162,8 +162,9 @@ class Decoder:
         self.t_dense = T
         r_dense = self.rank if dense_parallel else 0     # replicated: every rank holds shard 0 of 1
         E = self.world          # ranks the routed experts are spread over
-        if cfg.oai and self.world > 1:
-            raise ValueError("the gpt-oss layer form runs on one GPU here (its biases are not sharded)")
+        if cfg.oai and T > 1:
+            raise ValueError("the gpt-oss layer form has no tensor-parallel variant (its projection biases are not sharded): "
+                             "run it with dense_parallel=False (attention replicated, experts spread over the ranks)")
         if cfg.n_heads % T or cfg.n_kv % T:
             raise ValueError(f"{cfg.n_heads}/{cfg.n_kv} heads do not split over {T} ranks")
         self.h_loc, self.kv_loc = cfg.n_heads // T, cfg.n_kv // T
@@ -206,7 +207,12 @@ class Decoder:
                     d["bqkv"] = torch.cat([d["bq"], d["bk"], d["bv"]])
                 elif "qk" in d and "bq" in d and "bk" in d:
                     d["bqk"] = torch.cat([d["bq"], d["bk"]])
-            if cfg.n_experts and cfg.oai:
+            if cfg.n_experts and cfg.oai and E > 1:
+                d["ep"] = parallel.ExpertParallelLayer(ops, f32(L.router), L.gate, L.up, L.down, k["experts"], cfg.n_experts, H, cfg.ffn,
+                                                       cfg.top_k, mode=cfg.route_mode, act=1, group=group, comm=comm,
+                                                       router_bias=None if L.router_bias is None else f32(L.router_bias),
+                                                       biases=(f32(L.gate_b), f32(L.up_b), f32(L.down_b)))
+            elif cfg.n_experts and cfg.oai:
                 mk = lambda raw, r, c: ops.Weights(raw, k["experts"], r, c, n_mats=cfg.n_experts)
                 d["moe"] = RoutedLayer(f32(L.router), mk(L.gate, cfg.ffn, H), mk(L.up, cfg.ffn, H), mk(L.down, H, cfg.ffn), k=cfg.top_k,
                                        mode=cfg.route_mode, act=1, router_bias=None if L.router_bias is None else f32(L.router_bias))

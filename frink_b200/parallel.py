@@ -198,7 +198,11 @@ class TensorParallelFFN:
 class ExpertParallelLayer:
     """A routed layer whose experts are split over the ranks of `group`."""
 
-    def __init__(self, ops, router, gate_raw, up_raw, down_raw, kind, n_experts, hidden, ffn, k, mode=1, act=0, group=None, comm=None):
+    def __init__(self, ops, router, gate_raw, up_raw, down_raw, kind, n_experts, hidden, ffn, k, mode=1, act=0, group=None, comm=None,
+                 router_bias=None, biases=None):
+        """router_bias [n_experts] and biases = (gate_b, up_b, down_b), each [n_experts, rows] (tensors on the ops' device):
+        gpt-oss's form (`run_expert_oai`, crates/frink-moe/src/lib.rs:1039-1060) -- the router and its bias are replicated,
+        every rank keeps the bias rows of its own experts."""
         from .prefill import RoutedLayer
         self.ops, self.group = ops, group
         self.rank, self.world = _world(group)
@@ -217,7 +221,18 @@ class ExpertParallelLayer:
             return ops.Weights(raw[self.e0 * per:(self.e0 + self.n_local) * per], kind, rows, cols, n_mats=self.n_local)
 
         self.layer = RoutedLayer(router, local(gate_raw, ffn, hidden), local(up_raw, ffn, hidden), local(down_raw, hidden, ffn),
-                                 k=k, mode=mode, act=act, n_experts=n_experts)
+                                 k=k, mode=mode, act=act, n_experts=n_experts, router_bias=router_bias)
+        # this rank's bias rows, and one row of zeros behind them: the group "some other rank's expert" of the prefill
+        # permutation (and nothing else) indexes it
+        self.biases = None
+        if biases is not None:
+            self.biases = tuple(torch.cat([b[self.e0:self.e0 + self.n_local], torch.zeros_like(b[:1])]).contiguous() for b in biases)
+
+    def _bias(self, t, which, ids):
+        """t [slots, rows] += this rank's bias row of every slot's (local) expert; nothing without biases."""
+        if self.biases is not None:
+            self.ops.add_bias_(t, self.biases[which], ids)
+        return t
 
     # ---- decode: activation replicated, partial combine, one all-reduce
     def decode(self, x):
@@ -231,9 +246,10 @@ class ExpertParallelLayer:
             g = torch.zeros((k, self.ffn), dtype=torch.float32, device=x.device)
             u = torch.zeros_like(g)
             y = torch.zeros((k, self.hidden), dtype=torch.float32, device=x.device)
-            ops.gemv_multi_active(L.gate, lid, x, n, g)
-            ops.gemv_multi_active(L.up, lid, x, n, u)
-            ops.gemv_multi_active(L.down, lid, ops.glu(g, u, L.act), n, y)
+            # (slots past the count hold zeros plus expert 0's bias row: finite, and weighted by 0)
+            self._bias(ops.gemv_multi_active(L.gate, lid, x, n, g), 0, lid)
+            self._bias(ops.gemv_multi_active(L.up, lid, x, n, u), 1, lid)
+            self._bias(ops.gemv_multi_active(L.down, lid, ops.glu(g, u, L.act), n, y), 2, lid)
             out = ops.moe_combine(y, None, lw[None], 1, k)[0]
         else:
             ids1, w1 = ids.reshape(-1), w.reshape(-1)
@@ -242,9 +258,9 @@ class ExpertParallelLayer:
             n = int(mine.sum().item())
             if n:
                 lid = (ids1[mine] - self.e0).to(torch.int32).contiguous()
-                g = ops.gemv_multi(L.gate, lid, x)
-                u = ops.gemv_multi(L.up, lid, x)
-                y = ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act))
+                g = self._bias(ops.gemv_multi(L.gate, lid, x), 0, lid)
+                u = self._bias(ops.gemv_multi(L.up, lid, x), 1, lid)
+                y = self._bias(ops.gemv_multi(L.down, lid, ops.glu(g, u, L.act)), 2, lid)
                 out = ops.moe_combine(y, None, w1[mine].contiguous()[None], 1, n)[0]
         if self.world > 1:
             if self.comm is not None:
@@ -266,11 +282,16 @@ class ExpertParallelLayer:
         # the pairs of other ranks' experts fall into a group past the last local expert, which no GEMM serves
         group_off, gather, pair_of = ops.moe_permute(lids, self.n_local + 1)
         pairs = b * k
-        g = ops.gemm_grouped(L.gate, group_off, gather, x, pairs)
-        u = ops.gemm_grouped(L.up, group_off, gather, x, pairs)
+        expert_of = None
+        if self.biases is not None:
+            # the (local) expert of every permuted row, from the group offsets; rows of other ranks' experts get the zero row
+            expert_of = torch.searchsorted(group_off[1:].to(torch.int64), torch.arange(pairs, device=group_off.device), right=True)
+            expert_of = expert_of.clamp_(max=self.n_local).to(torch.int32)
+        g = self._bias(ops.gemm_grouped(L.gate, group_off, gather, x, pairs), 0, expert_of)
+        u = self._bias(ops.gemm_grouped(L.up, group_off, gather, x, pairs), 1, expert_of)
         a = ops.glu(g, u, L.act)
         y = torch.zeros((pairs, self.hidden), dtype=torch.float32, device=x.device)   # rows nobody writes carry weight 0: keep them finite
-        y = ops.gemm_grouped(L.down, group_off, None, a, pairs, out=y)
+        y = self._bias(ops.gemm_grouped(L.down, group_off, None, a, pairs, out=y), 2, expert_of)
         out = ops.moe_combine(y, pair_of, lw, b, k)
         if self.world > 1:
             if self.comm is not None and b <= 8:
@@ -298,9 +319,9 @@ class ExpertParallelLayer:
                               torch.zeros((pairs, self.ffn), dtype=torch.float32, device=x.device),
                               torch.zeros((pairs, self.hidden), dtype=torch.float32, device=x.device))
         g, u, y = self._rows_buf
-        ops.gemv_multi_active(L.gate, lid, xg, n, g)
-        ops.gemv_multi_active(L.up, lid, xg, n, u)
-        ops.gemv_multi_glu(L.down, lid, g, u, L.act, out=y, n_active=n)
+        self._bias(ops.gemv_multi_active(L.gate, lid, xg, n, g), 0, lid)
+        self._bias(ops.gemv_multi_active(L.up, lid, xg, n, u), 1, lid)
+        self._bias(ops.gemv_multi_glu(L.down, lid, g, u, L.act, out=y, n_active=n), 2, lid)
         out = ops.moe_combine(y, pair_of, lw, b, k)
         if self.world > 1:
             if self.comm is not None:

@@ -5,6 +5,8 @@ import os
 
 import numpy as np
 
+from oracle import frink_oracle as fo
+
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "frink_goldens.json")
 
 
@@ -75,3 +77,28 @@ def max_abs_over_inf(got, want):
     got = np.asarray(got, np.float64).ravel()
     want = np.asarray(want, np.float64).ravel()
     return float(np.max(np.abs(got - want)) / max(np.max(np.abs(want)), 1e-30))
+
+
+def tiny_gpt_oss(seed=5):
+    """A two-layer model of gpt-oss's layer form: BF16 attention projections with biases, sinks, layer 0 windowed,
+    four MXFP4 experts (top 2) with a bias per expert projection, the clamped SwiGLU and a router bias."""
+    from frink_b200.decoder import DecoderConfig, LayerWeights
+    cfg = DecoderConfig(n_layers=2, hidden=256, n_heads=8, n_kv=2, head_dim=64, ffn=256, vocab=512, rope_theta=150000.0, eps=1e-5, neox=True,
+                        n_experts=4, top_k=2, route_mode=1, oai=True, sliding_window=8, swa_period=2)
+    rng = np.random.default_rng(seed)
+    H, hd, E = cfg.hidden, cfg.head_dim, cfg.n_experts
+    bf = lambda r, c, s: fo.encode(fo.BF16, (rng.standard_normal((r, c)) * s).astype(np.float32))
+    mx = lambda r, c: np.concatenate([fo.encode(fo.MXFP4, (rng.standard_normal((r, c)) * 0.05).astype(np.float32)) for _ in range(E)])
+    vec = lambda n, s=0.1: (rng.standard_normal(n) * s).astype(np.float32)
+    layers = []
+    for _ in range(cfg.n_layers):
+        layers.append(LayerWeights(
+            attn_norm=1 + vec(H), wq=bf(cfg.n_heads * hd, H, 0.05), wk=bf(cfg.n_kv * hd, H, 0.05), wv=bf(cfg.n_kv * hd, H, 0.05),
+            wo=bf(H, cfg.n_heads * hd, 0.05), ffn_norm=1 + vec(H), gate=mx(cfg.ffn, H), up=mx(cfg.ffn, H), down=mx(H, cfg.ffn),
+            router=(rng.standard_normal((E, H)) * 0.5).astype(np.float32), sinks=vec(cfg.n_heads, 1.0),
+            bq=vec(cfg.n_heads * hd), bk=vec(cfg.n_kv * hd), bv=vec(cfg.n_kv * hd), bo=vec(H), router_bias=vec(E, 0.5),
+            gate_b=vec(E * cfg.ffn).reshape(E, cfg.ffn), up_b=vec(E * cfg.ffn).reshape(E, cfg.ffn), down_b=vec(E * H).reshape(E, H),
+            kinds={"wq": fo.BF16, "wk": fo.BF16, "wv": fo.BF16, "wo": fo.BF16, "experts": fo.MXFP4}))
+    tok = fo.encode(fo.BF16, rng.standard_normal((cfg.vocab, H)).astype(np.float32))
+    head = fo.encode(fo.BF16, (rng.standard_normal((cfg.vocab, H)) * 0.5).astype(np.float32))
+    return cfg, layers, tok, (1 + vec(H)).astype(np.float32), head

@@ -201,6 +201,48 @@ def _decoder_moe_replicated_case(rank, world):
     return _decoder_logits(True, world, dense_parallel=False)
 
 
+def _decoder_oai_logits(rank, world):
+    from frink_b200.decoder import Decoder
+    from tests import cpu_ops
+    from tests.helpers import tiny_gpt_oss
+    cfg, layers, tok, out_norm, head = tiny_gpt_oss()
+    dec = Decoder(cfg, layers, tok, fo.BF16, out_norm, output=head, output_kind=fo.BF16, max_seq=32, ops=cpu_ops, device="cpu",
+                  dense_parallel=False)
+    assert dec.world == world
+    prompt = torch.from_numpy(np.random.default_rng(3).integers(0, cfg.vocab, 12).astype(np.int32))
+    outs = [dec.forward(prompt).numpy().copy()]                                        # 12 rows: grouped GEMMs with the bias rows
+    outs.append(dec.forward(torch.tensor([7], dtype=torch.int32)).numpy().copy())      # one row
+    outs.append(dec.forward(torch.tensor([5, 9, 2], dtype=torch.int32)).numpy().copy())   # a few rows: slots
+    return outs
+
+
+def test_gpt_oss_form_with_sharded_experts_matches_one_rank():
+    """gpt-oss's layer form on two ranks: attention (and its biases) replicated, the experts AND their bias rows spread
+    over the ranks, the router bias replicated.  Prompt rows, one row and a few rows against the same decoder on one rank."""
+    want = spawn(_decoder_oai_logits, world=1)[0]
+    got = spawn(_decoder_oai_logits, world=2)
+    for r in range(2):
+        for a, b in zip(got[r], want):
+            assert rel_l2(a, b) <= 1e-4
+    for a, b in zip(got[0], got[1]):
+        assert np.array_equal(a, b)
+    # the tensor-parallel plan has no gpt-oss variant: refused when the decoder is built
+    msgs = spawn(_oai_tp_refused, world=2)
+    assert all(m and "tensor-parallel" in m for m in msgs)
+
+
+def _oai_tp_refused(rank, world):
+    from frink_b200.decoder import Decoder
+    from tests import cpu_ops
+    from tests.helpers import tiny_gpt_oss
+    cfg, layers, tok, out_norm, head = tiny_gpt_oss()
+    try:
+        Decoder(cfg, layers, tok, fo.BF16, out_norm, output=head, output_kind=fo.BF16, max_seq=32, ops=cpu_ops, device="cpu")
+    except ValueError as e:
+        return str(e)
+    return None
+
+
 def test_decoder_with_replicated_attention_and_sharded_experts_matches_one_rank():
     """The plan for routed models on more ranks than KV heads: attention on every rank, experts
     spread over the ranks.  Prefill (dispatch/combine) and the fused decode path."""

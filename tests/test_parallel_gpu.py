@@ -155,6 +155,21 @@ def _worker(rank, world, port, ret):
             seq_same = seq_same and torch.equal(device.argmax(l_one), device.argmax(l_many))
             c_one = device.argmax(l_one)
         out["ep_seqs"], out["ep_seqs_tokens"] = seq_worst, bool(seq_same)
+        # gpt-oss's layer form with its experts (and their bias rows) over the ranks, attention and its biases replicated:
+        # prompt, single rows from the captured graph, a batch of sequences, against one GPU
+        from tests.helpers import tiny_gpt_oss
+        ocfg, olayers, otok, onorm, ohead = tiny_gpt_oss()
+        mko = lambda **kw: Decoder(ocfg, olayers, otok, fo.BF16, onorm, output=ohead, output_kind=fo.BF16, max_seq=64, dense_parallel=False, **kw)
+        o_one, o_many = mko(group=solo_groups[rank]), mko(comm=comm)
+        oprompt = torch.from_numpy(np.random.default_rng(4).integers(0, ocfg.vocab, 14).astype(np.int32)).cuda()
+        oai_worst = rel_l2(o_many.forward(oprompt).cpu().numpy(), o_one.forward(oprompt).cpu().numpy())
+        for ids_ in ([7], [5, 9, 2], [100]):
+            t_ = torch.tensor(ids_, dtype=torch.int32, device="cuda")
+            oai_worst = max(oai_worst, rel_l2(o_many.forward(t_).cpu().numpy(), o_one.forward(t_).cpu().numpy()))
+        o_one.reset()
+        o_many.reset()
+        out["oai_ep"] = oai_worst
+        out["oai_ep_tokens"] = o_many.generate(oprompt, 6, use_graph=True) == o_one.generate(oprompt, 6)
         # time: 12 KB vectors, 200 in a graph
         def timed(fn):
             gr = torch.cuda.CUDAGraph()
@@ -197,6 +212,7 @@ def test_tp_and_ep_over_nccl_match_single_gpu():
         assert o["ep_pre_equal"] and o["ep_dec"] <= 1e-6, o
         assert o["ar_ok"] and o["tp_dec_comm"] <= 1e-5 and o["ep_dec_comm"] <= 1e-6 and o["ep_pre_replicated"] <= 1e-6, o
         assert o["fused_ar"] <= 1e-5 and o["ep_seqs"] <= 2e-3 and o["ep_seqs_tokens"], o
+        assert o["oai_ep"] <= 2e-3 and o["oai_ep_tokens"], o
         # the sharded decoder sums the same products in another order and re-rounds q8_1 activations on the way
         assert o["tp_decoder"] <= 2e-3 and o["tp_decoder_tokens"], o
     print({k: v for k, v in ret[0].items() if k.startswith("us_") or k.startswith("tp_decoder") or k in ("fused_ar", "ep_seqs")})
