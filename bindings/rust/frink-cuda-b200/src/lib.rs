@@ -12,5 +12,6 @@ pub mod matvec_kinds;
 pub mod matvec_launch;
 pub mod mul_mm;
 pub mod mul_mm_launch;
+pub mod prefill;
 
 pub use gpu::CudaError;
