@@ -46,3 +46,46 @@ def test_decoder_host_logic_matches_the_oracle_pipeline():
         lg3 = dec.forward(torch.from_numpy(three)).numpy()[0]          # three rows through the fused path
         assert rel_l2(lg3, ora.forward(three)) <= 1e-5
         assert int(dec.pos[0]) == 14
+
+
+def test_gpt_oss_routed_layer_host_logic_against_the_oracle_composition():
+    """`prefill.run_device_routed_oai` (router bias, per-expert bias rows, the clamped SwiGLU on the biased gate and up)
+    on the CPU ops, for a few rows (slots of the indexed matvecs) and for more than eight (pairs grouped by expert, the
+    expert of every permuted row found from the group offsets), against the reference's composition written out:
+    route_top_k -> per expert gate/up + bias -> swiglu_oai -> down + bias -> combine
+    (crates/frink-moe/src/lib.rs:567, 1039-1060, 1246)."""
+    from frink_b200 import prefill
+    E, k, H, F = 6, 2, 128, 96
+    rng = np.random.default_rng(31)
+    raws = {n: [fo.encode(fo.MXFP4, (rng.standard_normal((r, c)) * 0.05).astype(np.float32)) for _ in range(E)]
+            for n, r, c in (("gate", F, H), ("up", F, H), ("down", H, F))}
+    mk = lambda n, r, c: cpu_ops.Weights(np.concatenate(raws[n]), fo.MXFP4, r, c, n_mats=E)
+    router = (rng.standard_normal((E, H)) * 0.5).astype(np.float32)
+    rb = (rng.standard_normal(E) * 0.5).astype(np.float32)
+    gb, ub, db = (rng.standard_normal((E, n)).astype(np.float32) * 0.2 for n in (F, F, H))
+    layer = prefill.RoutedLayer(torch.from_numpy(router), mk("gate", F, H), mk("up", F, H), mk("down", H, F), k=k, mode=1, act=1,
+                                router_bias=torch.from_numpy(rb))
+    biases = tuple(torch.from_numpy(b) for b in (gb, ub, db))
+    x = rng.standard_normal((12, H)).astype(np.float32)
+
+    def want_rows(xs):
+        ids, w = fo.route_top_k((xs @ router.T).astype(np.float32), k, 1, rb)
+        out = np.zeros((xs.shape[0], H), np.float32)
+        for t in range(xs.shape[0]):
+            ys = []
+            for e in ids[t]:
+                xq = fo.q8_1_round(xs[t])
+                g = fo.matmul_f64(fo.MXFP4, raws["gate"][e], F, H, xq)[0].astype(np.float32) + gb[e]
+                u = fo.matmul_f64(fo.MXFP4, raws["up"][e], F, H, xq)[0].astype(np.float32) + ub[e]
+                ys.append(fo.matmul_f64(fo.MXFP4, raws["down"][e], H, F, fo.q8_1_round(fo.swiglu_oai(g, u)))[0].astype(np.float32) + db[e])
+            out[t] = fo.combine(np.stack(ys), w[t])
+        return out
+
+    for rows in (1, 3, 12):
+        got = prefill.run_device_routed_oai(layer, biases, torch.from_numpy(x[:rows]), cpu_ops).numpy()
+        assert rel_l2(got, want_rows(x[:rows])) <= 1e-5, rows
+    # added into a residual stream instead of returned
+    res = torch.from_numpy(rng.standard_normal((3, H)).astype(np.float32))
+    base = res.numpy().copy()
+    prefill.run_device_routed_oai(layer, biases, torch.from_numpy(x[:3]), cpu_ops, residual=res)
+    assert rel_l2(res.numpy(), base + want_rows(x[:3])) <= 1e-5
