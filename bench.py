@@ -585,7 +585,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
     try:
         dec = Decoder(cfg, layers, tok, tok_kind, out_norm, output=head, output_kind=tok_kind, max_seq=1024, dense_parallel=cfg.n_experts == 0,
                       comm=comm, prefill_acts="q8_k")
-    except ValueError as e:
+    except (ValueError, MemoryError) as e:      # (a shape that does not split over the ranks; an all-reduce arena that is full: the same on every rank)
         if world > 1:
             dist.barrier()
         return {"model": name, "n_gpus": world, "unavailable": str(e)} if rank == 0 else None
