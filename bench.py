@@ -565,7 +565,11 @@ def synth_model(name, n_layers=0):
 
 
 # per decode token, GGUF weight bytes every GPU streams together (layers + output head), and prefill matmul FLOPs of 512 tokens
-MODEL_ROOFLINE = {"llama3b": {"bytes_per_token": 2010839040, "pp512_flops": 2.89e12}}
+# (routed shapes: the bytes of the CHOSEN experts, the attention, the router and the head; one GPU only -- under expert
+# parallelism the replicated part does not divide by the ranks)
+MODEL_ROOFLINE = {"llama3b": {"bytes_per_token": 2010839040, "pp512_flops": 2.89e12},
+                  "qwen3moe": {"bytes_per_token": 2287392768, "pp512_flops": 2.80e12, "one_gpu_only": True},
+                  "gptoss": {"bytes_per_token": 3710177280, "pp512_flops": 3.10e12, "one_gpu_only": True}}
 
 
 def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_region=None):
@@ -684,7 +688,7 @@ def run_model(name, rank, world, n_layers=0, tp_graph=True, comm=None, profile_r
         "dense_weight_bytes_per_rank": wbytes, "device_error_word": err, "data": "synthetic random-init, quantized by the reference's encoders",
         "tokens_head": [int(t.item()) for t in toks[:8]], "distinct_tokens": len({int(t.item()) for t in toks})}
     roof = MODEL_ROOFLINE.get(name)
-    if roof and not n_layers:
+    if roof and not n_layers and (world == 1 or not roof.get("one_gpu_only")):
         hbm, _ = load_peaks()
         res["tg_frac_of_hbm"] = roof["bytes_per_token"] / world / (tg_ms / G * 1e-3) / 1e9 / hbm
         res["pp_tflops"] = roof["pp512_flops"] / (pp_ms * 1e-3) / 1e12
